@@ -1,0 +1,48 @@
+"""The device memory behind the cache manager: for each group one array
+`[layers, pages, 2 (k, v), kv_heads, page_size, head_dim]` (a layer's slice is what
+its kernels get; inside a page the layout is head-major, so the keys of one
+(page, head) are one dense `[page_size, head_dim]` tile), and for each layer with a
+fixed-size state one array `[slots, *shape]`.
+(The reference keeps one f16 buffer, K region then V region, layer folded into the
+page index: crates/cuda/src/decode.rs:664-698.)
+"""
+from __future__ import annotations
+
+from typing import Dict, List
+
+import torch
+
+from .manager import CacheManager
+
+
+class CacheStorage:
+    def __init__(self, manager: CacheManager, dtype: torch.dtype, device):
+        self.manager = manager
+        self.dtype = dtype
+        self.device = torch.device(device)
+        self.group_arrays: List[torch.Tensor] = []
+        self.layer_kv: Dict[str, torch.Tensor] = {}
+        for g in manager.groups:
+            arr = torch.zeros((len(g.layers), g.pool.total, 2, g.spec.kv_heads, manager.page_size, g.spec.head_dim),
+                              dtype=dtype, device=self.device)
+            self.group_arrays.append(arr)
+            for li, name in enumerate(g.layers):
+                self.layer_kv[name] = arr[li]
+        self.layer_state: Dict[str, torch.Tensor] = {}
+        for name, spec in manager.states.items():
+            sdt = dtype if spec.dtype == "act" else getattr(torch, spec.dtype)
+            self.layer_state[name] = torch.zeros((manager.max_seqs,) + tuple(spec.shape), dtype=sdt, device=self.device)
+
+    def zero_slot(self, slot: int) -> None:
+        """A fixed-size state starts at zero when its request is admitted."""
+        for t in self.layer_state.values():
+            t[slot].zero_()
+
+    def bytes(self) -> int:
+        return sum(a.numel() * a.element_size() for a in self.group_arrays) + \
+            sum(a.numel() * a.element_size() for a in self.layer_state.values())
+
+    @staticmethod
+    def bytes_per_page(manager_groups, page_size: int, dtype: torch.dtype) -> int:
+        isz = torch.empty((), dtype=dtype).element_size()
+        return sum(len(g.layers) * 2 * g.spec.kv_heads * page_size * g.spec.head_dim * isz for g in manager_groups)

@@ -1,0 +1,68 @@
+// Shared helpers of the hand-written sm_100a kernels: element types, conversions,
+// deterministic reductions and the error convention of the C entry points.
+//
+// Every entry point is `extern "C" int rb_*(…, void* stream)`, takes raw device
+// pointers, launches on the given stream and returns 0, a negative code for a
+// refused argument (the text is kept per thread, see rb_last_error) or the
+// positive cudaError_t of the launch.  No entry point allocates.
+#pragma once
+#include <cuda_runtime.h>
+#include <cuda_bf16.h>
+#include <stdint.h>
+#include <stdio.h>
+
+enum RbDtype { RB_F32 = 0, RB_BF16 = 1 };
+
+typedef __nv_bfloat16 bf16;
+
+template <typename T> __device__ __forceinline__ float to_f32(T v);
+template <> __device__ __forceinline__ float to_f32<float>(float v) { return v; }
+template <> __device__ __forceinline__ float to_f32<bf16>(bf16 v) { return __bfloat162float(v); }
+
+template <typename T> __device__ __forceinline__ T from_f32(float v);
+template <> __device__ __forceinline__ float from_f32<float>(float v) { return v; }
+template <> __device__ __forceinline__ bf16 from_f32<bf16>(float v) { return __float2bfloat16_rn(v); }
+
+// Fixed-order warp reductions (butterfly: every lane ends with the same value, and
+// the order of additions does not depend on anything but the lane count).
+__device__ __forceinline__ float warp_sum(float v) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+    return v;
+}
+__device__ __forceinline__ float warp_max(float v) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
+    return v;
+}
+
+// Block sum over blockDim.x threads (a multiple of 32, at most 1024); `red` holds 32 floats.
+__device__ __forceinline__ float block_sum(float v, float* red) {
+    v = warp_sum(v);
+    const int lane = threadIdx.x & 31, wid = threadIdx.x >> 5;
+    __syncthreads();
+    if (lane == 0) red[wid] = v;
+    __syncthreads();
+    const int nw = (blockDim.x + 31) >> 5;
+    float r = (lane < nw) ? red[lane] : 0.0f;
+    r = warp_sum(r);
+    return r;
+}
+__device__ __forceinline__ float block_max(float v, float* red) {
+    v = warp_max(v);
+    const int lane = threadIdx.x & 31, wid = threadIdx.x >> 5;
+    __syncthreads();
+    if (lane == 0) red[wid] = v;
+    __syncthreads();
+    const int nw = (blockDim.x + 31) >> 5;
+    float r = (lane < nw) ? red[lane] : -INFINITY;
+    r = warp_max(r);
+    return r;
+}
+
+// ---- host side -----------------------------------------------------------
+void rb_set_error(const char* fmt, ...);
+#define RB_REFUSE(...) do { rb_set_error(__VA_ARGS__); return -1; } while (0)
+#define RB_LAUNCH_RESULT() ((int)cudaGetLastError())
+
+static inline int rb_ceil_div(long long a, long long b) { return (int)((a + b - 1) / b); }

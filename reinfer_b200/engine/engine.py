@@ -1,0 +1,285 @@
+"""The engine: a model, its cache, and ONE step function.
+
+`step(entries)` takes a batch of (request, its next tokens, the places among them whose
+logits are wanted): portions of prompts beside single decoded tokens, cut anywhere.  It
+runs only those tokens, as one batch, against what earlier steps left in the cache, and
+returns float32 logits on the device for the wanted places, in the order of the entries
+and of their `want` lists.  The reference has three separate calls for this and cannot
+continue a prompt (crates/cuda/src/engine.rs:3739 `step`, :5218 `prefill_batch`, :5853
+`batch_decode_step`; bin/reinfer/src/sched_loop.rs:188-195); here one launch sequence
+serves every composition of the batch.
+
+Everything the kernels need to know about the batch goes to the device as one int32
+block per step (token ids, positions, entry of each token, per-entry tables, and per
+cache group the store slots and the block tables), staged in pinned memory.
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass, field
+from typing import Dict, Hashable, List, Optional, Sequence
+
+import numpy as np
+import torch
+
+from .. import ops
+from ..cache import CacheManager, CacheStorage, OutOfPages
+from ..config.registry import load_config, resolve_architecture
+from ..parts.context import GroupView, LayerCache, StepContext
+from ..parts.model import Model
+from ..weights.loader import load_state, random_state
+
+
+class EngineError(RuntimeError):
+    pass
+
+
+class EmbeddingOov(EngineError):
+    """A token id outside the vocabulary, refused before any launch
+    (crates/cuda/src/engine.rs:3784-3786)."""
+
+
+@dataclass
+class StepEntry:
+    request_id: Hashable
+    tokens: Sequence[int]
+    want: Sequence[int] = ()                 # indices into `tokens`
+
+
+_DTYPES = {"float32": torch.float32, "fp32": torch.float32, "f32": torch.float32,
+           "bfloat16": torch.bfloat16, "bf16": torch.bfloat16}
+
+
+def parse_dtype(d) -> torch.dtype:
+    if isinstance(d, torch.dtype):
+        if d not in (torch.float32, torch.bfloat16):
+            raise EngineError(f"dtype {d}: the engine runs in float32 or bfloat16")
+        return d
+    try:
+        return _DTYPES[str(d).lower()]
+    except KeyError:
+        raise EngineError(f"dtype {d!r}: expected float32 or bfloat16") from None
+
+
+class _Staging:
+    """A small ring of pinned int32 buffers; a buffer is reused only after the copy that read
+    it has finished (an event per buffer)."""
+
+    def __init__(self, n_buffers: int = 4, capacity: int = 1 << 16):
+        self.bufs = [torch.empty(capacity, dtype=torch.int32, pin_memory=True) for _ in range(n_buffers)]
+        self.events: List[Optional[torch.cuda.Event]] = [None] * n_buffers
+        self.i = 0
+
+    def upload(self, host: np.ndarray, device) -> torch.Tensor:
+        n = host.shape[0]
+        i = self.i
+        self.i = (self.i + 1) % len(self.bufs)
+        if self.events[i] is not None:
+            self.events[i].synchronize()
+        if self.bufs[i].numel() < n:
+            self.bufs[i] = torch.empty(max(n, 2 * self.bufs[i].numel()), dtype=torch.int32, pin_memory=True)
+        self.bufs[i][:n].numpy()[:] = host
+        dev = torch.empty(n, dtype=torch.int32, device=device)
+        dev.copy_(self.bufs[i][:n], non_blocking=True)
+        ev = torch.cuda.Event()
+        ev.record()
+        self.events[i] = ev
+        return dev
+
+
+class Engine:
+    """Built from a model folder (`from_model_dir`) or from a configuration with random
+    weights made on the device (`from_config`)."""
+
+    def __init__(self, config, spec, state: Dict[str, torch.Tensor], dtype: torch.dtype, *,
+                 page_size: int = 16, num_pages: Optional[int] = None, max_tokens: Optional[int] = None,
+                 max_num_seqs: int = 64, device="cuda:0", memory_fraction: float = 0.9):
+        self.device = torch.device(device)
+        torch.cuda.set_device(self.device)
+        ops.require_device()
+        self.config = config
+        self.dtype = dtype
+        self.model = Model(spec)
+        self.model.bind(state)
+        self.model.prepare(self.device, dtype)
+        self.vocab_size = spec.vocab_size
+        paged, states = self.model.cache_layout()
+        self.page_size = int(page_size)
+        if num_pages is None:
+            if max_tokens is not None:
+                num_pages = max(1, -(-int(max_tokens) // self.page_size))
+            else:
+                num_pages = self._pages_from_memory(paged, memory_fraction, max_num_seqs)
+        self.cache = CacheManager(paged, states, self.page_size, int(num_pages), int(max_num_seqs))
+        self.storage = CacheStorage(self.cache, dtype, self.device)
+        self._staging = _Staging()
+        self.steps_run = 0
+
+    # ---- construction ---------------------------------------------------------------
+    @classmethod
+    def from_model_dir(cls, model_dir: str, dtype="bfloat16", device="cuda:0", **kw) -> "Engine":
+        dt = parse_dtype(dtype)
+        arch, config = load_config(model_dir)
+        spec = arch.build_spec(config)
+        expected = Model(spec).param_specs()
+        state = load_state(model_dir, expected, dt, torch.device(device), ignorable=spec.ignorable_tensors)
+        return cls(config, spec, state, dt, device=device, **kw)
+
+    @classmethod
+    def from_config(cls, config, seed: int = 0, dtype="bfloat16", device="cuda:0", **kw) -> "Engine":
+        """Random weights drawn on the device (no files): for measurements at full size."""
+        dt = parse_dtype(dtype)
+        arch = resolve_architecture(config.to_dict())
+        spec = arch.build_spec(config)
+        expected = Model(spec).param_specs()
+        state = random_state(expected, seed, dt, torch.device(device))
+        return cls(config, spec, state, dt, device=device, **kw)
+
+    def _pages_from_memory(self, paged, fraction: float, max_num_seqs: int) -> int:
+        """pages = floor((fraction * total - in use) / bytes per page)
+        (crates/memory/src/budget.rs:99-155)."""
+        from ..cache.manager import group_layers
+        isz = 4 if self.dtype == torch.float32 else 2
+        per_page = sum(len(n) * 2 * s.kv_heads * self.page_size * s.head_dim * isz for s, n in group_layers(paged))
+        if per_page == 0:
+            return 1
+        free, total = torch.cuda.mem_get_info(self.device)
+        budget = int(total * fraction) - (total - free)
+        n = budget // per_page
+        if n < 1:
+            raise EngineError("no memory left for the cache after the weights")
+        return int(n)
+
+    # ---- the step ----------------------------------------------------------------------
+    def step(self, entries: Sequence[StepEntry]) -> Optional[torch.Tensor]:
+        ctx, want_rows, lens_after = self._prepare(entries)
+        if ctx is None:
+            return None
+        logits = self.model.forward(ctx, want_rows)
+        for rid, n in lens_after:
+            self.cache.commit(rid, n)
+        self.steps_run += 1
+        return logits
+
+    def finish(self, request_id) -> None:
+        """The request is over: its pages and its slot are given back."""
+        if request_id in self.cache:
+            self.cache.release(request_id)
+
+    def _prepare(self, entries: Sequence[StepEntry]):
+        entries = [e for e in entries if len(e.tokens) > 0]
+        if not entries:
+            return None, None, []
+        seen = set()
+        for e in entries:
+            if e.request_id in seen:
+                raise EngineError(f"request {e.request_id!r} appears twice in one step")
+            seen.add(e.request_id)
+            for t in e.tokens:
+                if not 0 <= int(t) < self.vocab_size:
+                    raise EmbeddingOov(f"request {e.request_id!r}: token id {t} outside the vocabulary of {self.vocab_size}")
+            for w in e.want:
+                if not 0 <= int(w) < len(e.tokens):
+                    raise EngineError(f"request {e.request_id!r}: wanted place {w} outside its {len(e.tokens)} tokens")
+        cm = self.cache
+        # enough slots and pages for the whole batch, before anything is changed
+        new = [e for e in entries if e.request_id not in cm]
+        if len(new) > cm.free_slots():
+            raise OutOfPages(f"{len(new)} new requests but {cm.free_slots()} free slots")
+        need = 0
+        for e in entries:
+            cur = cm.length(e.request_id) if e.request_id in cm else 0
+            have = len(cm.table(e.request_id, 0)) if (e.request_id in cm and cm.groups) else 0
+            need += max(0, cm.pages_for(cur + len(e.tokens)) - have)
+        if need > cm.free_pages():
+            raise OutOfPages(f"the step needs {need} more pages, {cm.free_pages()} are free")
+        for e in new:
+            slot = cm.admit(e.request_id)
+            self.storage.zero_slot(slot)
+        # decode entries first, each kind in the order given
+        order = sorted(range(len(entries)), key=lambda i: (len(entries[i].tokens) != 1, i))
+        internal = [entries[i] for i in order]
+        E = len(internal)
+        q_len = [len(e.tokens) for e in internal]
+        start = [cm.length(e.request_id) for e in internal]
+        for e, s, n in zip(internal, start, q_len):
+            cm.reserve(e.request_id, s + n)
+        q_start = np.zeros(E + 1, dtype=np.int64)
+        np.cumsum(q_len, out=q_start[1:])
+        T = int(q_start[-1])
+        n_decode = sum(1 for n in q_len if n == 1)
+        slots = [cm.slot(e.request_id) for e in internal]
+        # wanted rows in the caller's order
+        pos_in_internal = {id(e): k for k, e in enumerate(internal)}
+        want_rows = [int(q_start[pos_in_internal[id(e)]]) + int(w) for e in entries for w in e.want]
+        R = len(want_rows)
+
+        n_groups = len(cm.groups)
+        max_pages = [max(1, max(len(cm.table(e.request_id, g)) for e in internal)) for g in range(n_groups)]
+        # layout of the int32 block
+        off = {}
+        cur = 0
+
+        def take(name, n):
+            nonlocal cur
+            off[name] = (cur, n)
+            cur += (n + 3) // 4 * 4                     # 16-byte aligned sections
+
+        take("token_ids", T); take("positions", T); take("tok_entry", T)
+        take("cu_q", E + 1); take("kv_len", E); take("entry_slot", E); take("want_rows", max(R, 1))
+        for g in range(n_groups):
+            take(f"kv_slot{g}", T); take(f"block_table{g}", E * max_pages[g])
+        host = np.zeros(cur, dtype=np.int32)
+
+        def sec(name):
+            o, n = off[name]
+            return host[o:o + n]
+
+        tok, pos, ent = sec("token_ids"), sec("positions"), sec("tok_entry")
+        for k, e in enumerate(internal):
+            a, b = int(q_start[k]), int(q_start[k + 1])
+            tok[a:b] = np.asarray(e.tokens, dtype=np.int32)
+            pos[a:b] = np.arange(start[k], start[k] + q_len[k], dtype=np.int32)
+            ent[a:b] = k
+        sec("cu_q")[:] = q_start
+        sec("kv_len")[:] = np.asarray(start) + np.asarray(q_len)
+        sec("entry_slot")[:] = slots
+        if R:
+            sec("want_rows")[:] = want_rows
+        for g in range(n_groups):
+            ks = sec(f"kv_slot{g}")
+            bt = sec(f"block_table{g}").reshape(E, max_pages[g])
+            bt[:] = -1
+            for k, e in enumerate(internal):
+                table = cm.table(e.request_id, g)
+                bt[k, :len(table)] = table
+                a, b = int(q_start[k]), int(q_start[k + 1])
+                ks[a:b] = cm.write_slots(e.request_id, g, start[k], q_len[k])
+        dev = self._staging.upload(host, self.device)
+
+        def dsec(name):
+            o, n = off[name]
+            return dev[o:o + n]
+
+        views = []
+        for g, grp in enumerate(cm.groups):
+            views.append(GroupView(page_size=self.page_size,
+                                   block_table=dsec(f"block_table{g}").view(E, max_pages[g]),
+                                   kv_slot=dsec(f"kv_slot{g}"), max_pages=max_pages[g], window=grp.window))
+        layer_caches: Dict[str, LayerCache] = {}
+        for layer in self.model.layers:
+            src = layer.spec.cache_from or layer.name
+            lc = LayerCache(write=layer.spec.cache_from is None)
+            if src in cm.group_of_layer:
+                lc.kv = self.storage.layer_kv[src]
+                lc.group = views[cm.group_of_layer[src]]
+            if layer.name in self.storage.layer_state:
+                lc.state = self.storage.layer_state[layer.name]
+            layer_caches[layer.name] = lc
+        ctx = StepContext(dtype=self.dtype, device=self.device, n_tokens=T, n_entries=E, n_decode=n_decode,
+                          token_ids=dsec("token_ids"), positions=dsec("positions"), tok_entry=dsec("tok_entry"),
+                          cu_q=dsec("cu_q"), kv_len=dsec("kv_len"), entry_slot=dsec("entry_slot"),
+                          q_start=[int(v) for v in q_start], start_pos=list(start), slots=slots,
+                          max_q_len=max(q_len), max_kv_len=max(s + n for s, n in zip(start, q_len)),
+                          layer_caches=layer_caches)
+        lens_after = [(e.request_id, s + n) for e, s, n in zip(internal, start, q_len)]
+        return ctx, (dsec("want_rows") if R else None), lens_after

@@ -1,0 +1,2 @@
+"""Architectures: each module turns its typed configuration into a ModelSpec and
+registers itself under the architecture's name."""

@@ -1,0 +1,205 @@
+"""Python face of the kernel library: loads the shared library that
+`csrc/build.py` builds and wraps each C entry point in a function that takes
+torch tensors (as storage only: pointers, shapes and dtypes are read, no torch
+operator runs).  Kernels launch on torch's current CUDA stream, so they order with
+torch's allocator and can be captured into CUDA graphs.
+
+There is no fallback: without the library, or on a device that is not sm_100,
+every call raises.
+"""
+from __future__ import annotations
+
+import ctypes
+from ctypes import c_void_p, c_int, c_float, c_longlong, c_char_p
+from typing import Optional
+
+import torch
+
+from .csrc import build as _build
+
+F32, BF16 = 0, 1
+_DT = {torch.float32: F32, torch.bfloat16: BF16}
+
+
+class KernelError(RuntimeError):
+    pass
+
+
+_lib = None
+
+
+def lib():
+    """The loaded library (built at the first call if needed)."""
+    global _lib
+    if _lib is None:
+        path = _build.ensure_built()
+        try:
+            _lib = ctypes.CDLL(path)
+        except OSError as e:
+            raise KernelError(f"cannot load the kernel library {path}: {e}") from None
+        _lib.rb_last_error.restype = c_char_p
+        if _lib.rb_abi_version() != 1:
+            raise KernelError("kernel library has another ABI version")
+    return _lib
+
+
+_checked_device = False
+
+
+def require_device() -> None:
+    """Fail loudly unless a CUDA device of compute capability 10.x is current."""
+    global _checked_device
+    if _checked_device:
+        return
+    if not torch.cuda.is_available():
+        raise KernelError("no CUDA device: reinfer_b200 runs on a B200 (sm_100a) only and has no CPU path")
+    cc = lib().rb_device_cc()
+    if cc < 0:
+        raise KernelError(f"CUDA error {-cc} while reading the device's compute capability")
+    if cc // 10 != 10:
+        raise KernelError(f"device has compute capability {cc / 10:.1f}; the kernels are built for sm_100a only")
+    _checked_device = True
+
+
+def _check(rc: int, what: str) -> None:
+    if rc == 0:
+        return
+    if rc < 0:
+        raise KernelError(f"{what}: {lib().rb_last_error().decode()}")
+    raise KernelError(f"{what}: CUDA error {rc} at launch")
+
+
+def _stream() -> c_void_p:
+    return c_void_p(torch.cuda.current_stream().cuda_stream)
+
+
+def _p(t: Optional[torch.Tensor]) -> c_void_p:
+    return c_void_p(0 if t is None else t.data_ptr())
+
+
+def dt(t: torch.Tensor) -> int:
+    try:
+        return _DT[t.dtype]
+    except KeyError:
+        raise KernelError(f"dtype {t.dtype} is not float32 or bfloat16") from None
+
+
+def _need(cond: bool, msg: str) -> None:
+    if not cond:
+        raise KernelError(msg)
+
+
+# ------------------------------------------------------------------ wrappers
+def embed_gather(table: torch.Tensor, ids: torch.Tensor, out: torch.Tensor) -> None:
+    """out[t,:] (float32) = table[ids[t],:]"""
+    _need(out.dtype == torch.float32 and ids.dtype == torch.int32, "embed_gather: out float32, ids int32")
+    _need(table.is_contiguous() and out.is_contiguous(), "embed_gather: contiguous tensors")
+    _check(lib().rb_embed_gather(_p(table), dt(table), _p(ids), _p(out), c_int(ids.numel()),
+                                 c_int(table.shape[1]), c_int(table.shape[0]), _stream()), "embed_gather")
+
+
+def add_rmsnorm(x: torch.Tensor, delta: Optional[torch.Tensor], w: torch.Tensor, out: torch.Tensor,
+                eps: float, row_idx: Optional[torch.Tensor] = None) -> None:
+    """x (float32, [rows,h]) += delta if given; out[r] = rmsnorm(x[row_idx[r] or r]) * w."""
+    _need(x.dtype == torch.float32 and x.is_contiguous() and out.is_contiguous(), "rmsnorm: x float32 contiguous")
+    h = x.shape[-1]
+    rows = out.numel() // h
+    if delta is not None:
+        _need(delta.is_contiguous() and delta.numel() == x.numel(), "rmsnorm: delta has x's shape")
+    _check(lib().rb_add_rmsnorm(_p(x), _p(delta), c_int(dt(delta) if delta is not None else F32), _p(w), c_int(dt(w)),
+                                _p(out), c_int(dt(out)), _p(row_idx), c_int(rows), c_int(h), c_float(eps),
+                                _stream()), "add_rmsnorm")
+
+
+def residual_add(x: torch.Tensor, delta: torch.Tensor) -> None:
+    _need(x.dtype == torch.float32 and x.is_contiguous() and delta.is_contiguous() and x.numel() == delta.numel(),
+          "residual_add: x float32, same size")
+    _check(lib().rb_residual_add(_p(x), _p(delta), c_int(dt(delta)), c_longlong(x.numel()), _stream()), "residual_add")
+
+
+def qknorm_rope_append(qkv: torch.Tensor, qw: Optional[torch.Tensor], kw: Optional[torch.Tensor],
+                       inv_freq: Optional[torch.Tensor], positions: Optional[torch.Tensor],
+                       kv_slot: Optional[torch.Tensor], q_out: torch.Tensor, cache: Optional[torch.Tensor],
+                       QH: int, KH: int, d: int, rot: int, page_size: int, eps: float,
+                       k_out: Optional[torch.Tensor] = None) -> None:
+    """Per-head RMSNorm of q and k (if weights are given), rotation of the first `rot` dims (if
+    rot > 0), q -> q_out, k and v -> the cache at kv_slot (or k -> k_out, v untouched)."""
+    n = qkv.shape[0]
+    _need(qkv.is_contiguous() and q_out.is_contiguous(), "qknorm_rope_append: contiguous")
+    _need(qkv.shape[-1] == (QH + 2 * KH) * d, "qknorm_rope_append: qkv width")
+    wd = dt(qw) if qw is not None else F32
+    if qw is not None:
+        _need(kw is not None and kw.dtype == qw.dtype, "qknorm_rope_append: q/k norm weights of one dtype")
+    _check(lib().rb_qknorm_rope_append(_p(qkv), c_int(dt(qkv)), _p(qw), _p(kw), c_int(wd), _p(inv_freq),
+                                       _p(positions), _p(kv_slot), _p(q_out), _p(k_out), _p(cache),
+                                       c_int(dt(cache) if cache is not None else dt(qkv)),
+                                       c_int(n), c_int(QH), c_int(KH), c_int(d), c_int(rot), c_int(page_size),
+                                       c_float(eps), _stream()), "qknorm_rope_append")
+
+
+def kv_append(k: torch.Tensor, v: torch.Tensor, kv_slot: torch.Tensor, cache: torch.Tensor,
+              KH: int, d: int, page_size: int) -> None:
+    """k, v: [T, KH*d] views (row stride free, heads contiguous) -> cache pages."""
+    _need(k.dtype == v.dtype == cache.dtype, "kv_append: one dtype")
+    _need(k.stride(-1) == 1 and v.stride(-1) == 1, "kv_append: rows contiguous")
+    _check(lib().rb_kv_append(_p(k), c_longlong(k.stride(0)), _p(v), c_longlong(v.stride(0)), _p(kv_slot), _p(cache),
+                              c_int(dt(k)), c_int(k.shape[0]), c_int(KH), c_int(d), c_int(page_size), _stream()),
+           "kv_append")
+
+
+def swiglu(gu: torch.Tensor, out: torch.Tensor) -> None:
+    _need(gu.is_contiguous() and out.is_contiguous() and gu.dtype == out.dtype, "swiglu: contiguous, one dtype")
+    F_ = out.shape[-1]
+    _need(gu.shape[-1] == 2 * F_, "swiglu: input is [gate | up]")
+    _check(lib().rb_swiglu(_p(gu), _p(out), c_int(dt(gu)), c_int(out.numel() // F_), c_int(F_), _stream()), "swiglu")
+
+
+def gemm_ref(a: torch.Tensor, w: torch.Tensor, c: torch.Tensor, accumulate: bool = False) -> None:
+    """c[M,N] (=|+=) a[M,K] @ w[N,K]^T on the CUDA cores in 32-bit."""
+    M, K = a.shape
+    N = w.shape[0]
+    _need(w.shape[1] == K and tuple(c.shape) == (M, N), "gemm: shapes")
+    _need(a.stride(1) == 1 and w.stride(1) == 1 and c.stride(1) == 1, "gemm: rows contiguous")
+    _check(lib().rb_gemm_ref(_p(a), c_int(dt(a)), _p(w), c_int(dt(w)), _p(c), c_int(dt(c)), c_int(int(accumulate)),
+                             c_int(M), c_int(N), c_int(K), c_longlong(a.stride(0)), c_longlong(w.stride(0)),
+                             c_longlong(c.stride(0)), _stream()), "gemm_ref")
+
+
+def paged_attention_ref(q: torch.Tensor, cache: torch.Tensor, block_table: torch.Tensor, tok_row: torch.Tensor,
+                        positions: torch.Tensor, out: torch.Tensor, QH: int, KH: int, d: int, page_size: int,
+                        window: int, scale: float) -> None:
+    _need(q.is_contiguous() and out.is_contiguous() and cache.is_contiguous() and block_table.is_contiguous(),
+          "attention: contiguous")
+    _need(q.dtype == cache.dtype == out.dtype, "attention: one dtype for q, cache and out")
+    _check(lib().rb_paged_attention_ref(_p(q), _p(cache), c_int(dt(q)), _p(block_table), _p(tok_row), _p(positions),
+                                        _p(out), c_int(q.shape[0]), c_int(QH), c_int(KH), c_int(d), c_int(page_size),
+                                        c_int(block_table.shape[1]), c_int(window), c_float(scale), _stream()),
+           "paged_attention_ref")
+
+
+def attention(ctx, q: torch.Tensor, cache: torch.Tensor, group, out: torch.Tensor, QH: int, KH: int, d: int,
+              window: int, scale: float) -> None:
+    """Attention of a step's tokens over their requests' pages; picks the kernel by dtype and
+    by what the batch holds.  float32 always runs the plain kernel."""
+    paged_attention_ref(q, cache, group.block_table, ctx.tok_entry, ctx.positions, out, QH, KH, d,
+                        group.page_size, window, scale)
+
+
+def sample(logits: torch.Tensor, row_idx: Optional[torch.Tensor], params: torch.Tensor, history: Optional[torch.Tensor],
+           work: torch.Tensor, out_tokens: torch.Tensor, rows: int) -> None:
+    """params: uint8 tensor holding `rows` RbSampleParams records (see sampling/sampler.py)."""
+    _need(logits.dtype == torch.float32 and logits.stride(1) == 1, "sample: float32 logits")
+    vocab = logits.shape[1]
+    hist_cap = history.shape[1] if history is not None else 0
+    _need(work.numel() >= rows * vocab and work.dtype == torch.float32, "sample: scratch of rows*vocab floats")
+    _check(lib().rb_sample(_p(logits), c_longlong(logits.stride(0)), _p(row_idx), _p(params), _p(history),
+                           c_int(hist_cap), _p(work), _p(out_tokens), c_int(rows), c_int(vocab), _stream()), "sample")
+
+
+def fast_gemm_available() -> bool:
+    """True once the tensor-core product is part of the library."""
+    return hasattr(lib(), "rb_gemm_bf16")
+
+
+def sample_params_size() -> int:
+    return int(lib().rb_sample_params_size())

@@ -1,0 +1,125 @@
+"""Interfaces of the parts and the registry that maps a kind to a class.
+
+Categories: 'norm', 'position', 'mixer', 'ffn', 'block', 'embedding', 'lm_head'.
+A part is constructed from `PartSpec.params` (keyword arguments) on the CPU, without
+touching a device; it declares its tensors with `param_specs()` (local name ->
+ParamSpec) and receives them, already on the device and in their kept dtype, through
+`bind()`.  No part knows which model it is in.
+
+  Norm.forward(ctx, x, out=None, delta=None, row_idx=None) -> Tensor
+      x: the float32 residual stream [T, h]; if `delta` is given it is added into x
+      first.  Returns the normalised rows in the activation dtype.
+  PositionEncoding.apply(ctx, q, k, positions) -> None          (in place, generic path)
+      q [T, QH, d], k [T, KH, d].  A mixer may ask `fused_rotary()` for (inv_freq,
+      rotated_width) and apply the rotation inside its own kernel instead.
+  Mixer.forward(ctx, xn, residual, cache) -> None
+      xn: normalised input [T, h] in the activation dtype; the mixer ADDS its output
+      into `residual` (float32 [T, h]).  `cache` is the LayerCache of the layer
+      (parts/context.py).  `cache_spec()` / `state_spec()` say what the layer needs
+      from the cache manager: paged keys/values and/or a fixed-size state per request.
+  FeedForward.forward(ctx, xn, residual) -> None                 (same convention)
+  Block.forward(ctx, x, cache) -> None                           (x updated in place)
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass
+from typing import Any, Callable, Dict, Mapping, Optional, Tuple
+
+import torch
+
+from ..weights.params import ParamSpec
+from .spec import PartSpec
+
+
+@dataclass(frozen=True)
+class PagedKVSpec:
+    """Keys and values of every token (or of the last `window` tokens) in pages."""
+    kv_heads: int
+    head_dim: int
+    window: Optional[int] = None
+
+
+@dataclass(frozen=True)
+class SlotStateSpec:
+    """A state of fixed size per live request, zeroed when the request is admitted."""
+    shape: Tuple[int, ...]
+    dtype: str = "float32"                      # "float32" or "act" (the activation dtype)
+
+
+class Part:
+    def param_specs(self) -> Dict[str, ParamSpec]:
+        return {}
+
+    def bind(self, tensors: Mapping[str, torch.Tensor]) -> None:
+        """`tensors`: local name -> device tensor, for every name of param_specs() that
+        the checkpoint (or an optional tensor's fallback) supplied."""
+
+
+class Norm(Part):
+    def forward(self, ctx, x, out=None, delta=None, row_idx=None):
+        raise NotImplementedError
+
+
+class PositionEncoding(Part):
+    def apply(self, ctx, q, k, positions) -> None:
+        raise NotImplementedError
+
+    def fused_rotary(self):
+        """(inv_freq float32 device tensor [rot/2], rot) if this encoding is a plain
+        rotation of pairs (p, p+rot/2) by pos*inv_freq[p], else None."""
+        return None
+
+    def prepare(self, device) -> None:
+        """Build device-side tables (called once, after the weights are bound)."""
+
+
+class Mixer(Part):
+    def cache_spec(self) -> Optional[PagedKVSpec]:
+        return None
+
+    def state_spec(self) -> Optional[SlotStateSpec]:
+        return None
+
+    def prepare(self, device, dtype) -> None:
+        pass
+
+    def forward(self, ctx, xn, residual, cache) -> None:
+        raise NotImplementedError
+
+
+class FeedForward(Part):
+    def forward(self, ctx, xn, residual) -> None:
+        raise NotImplementedError
+
+
+_REGISTRY: Dict[Tuple[str, str], Callable[..., Any]] = {}
+
+
+def register_part(category: str, kind: str, factory: Callable[..., Any]) -> None:
+    """Register `factory(**params)` under (category, kind).  Re-registering replaces."""
+    _REGISTRY[(category, kind)] = factory
+
+
+def unregister_part(category: str, kind: str) -> None:
+    _REGISTRY.pop((category, kind), None)
+
+
+def build_part(category: str, spec: PartSpec):
+    _ensure_builtin()
+    try:
+        factory = _REGISTRY[(category, spec.kind)]
+    except KeyError:
+        known = sorted(k for c, k in _REGISTRY if c == category)
+        raise KeyError(f"no {category} part of kind '{spec.kind}' is registered (known: {known})") from None
+    return factory(**dict(spec.params))
+
+
+_done = False
+
+
+def _ensure_builtin() -> None:
+    global _done
+    if _done:
+        return
+    _done = True
+    from . import norm, rope, attention, ffn, embedding, block  # noqa: F401  (each registers itself)

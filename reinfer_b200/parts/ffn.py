@@ -1,0 +1,40 @@
+"""SwiGLU feed-forward: down( silu(x Wg^T) * (x Wu^T) ), no bias
+(crates/cuda/src/engine.rs:4288-4314; crates/cuda/kernels/dense_kernels.cu:236-248).
+Gate and up rows are concatenated once at load into one `[2F, h]` matrix so that one
+product serves both (the reference runs two)."""
+from __future__ import annotations
+
+import torch
+
+from .. import ops
+from ..weights.params import ParamSpec
+from .base import FeedForward, register_part
+from .linear import matmul
+
+
+class SwiGLU(FeedForward):
+    def __init__(self, hidden: int, intermediate: int):
+        self.hidden, self.inter = int(hidden), int(intermediate)
+        self.w_gate_up = None
+        self.w_down = None
+
+    def param_specs(self):
+        return {"gate_proj.weight": ParamSpec((self.inter, self.hidden)),
+                "up_proj.weight": ParamSpec((self.inter, self.hidden)),
+                "down_proj.weight": ParamSpec((self.hidden, self.inter))}
+
+    def bind(self, tensors):
+        g, u = tensors["gate_proj.weight"], tensors["up_proj.weight"]
+        if g.dtype != u.dtype:
+            g, u = g.float(), u.float()
+        self.w_gate_up = torch.cat([g, u], dim=0).contiguous()
+        self.w_down = tensors["down_proj.weight"]
+
+    def forward(self, ctx, xn, residual) -> None:
+        gu = matmul(ctx, xn, self.w_gate_up)
+        act = torch.empty((xn.shape[0], self.inter), dtype=xn.dtype, device=xn.device)
+        ops.swiglu(gu, act)
+        matmul(ctx, act, self.w_down, out=residual, accumulate=True)
+
+
+register_part("ffn", "swiglu", SwiGLU)

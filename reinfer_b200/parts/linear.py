@@ -1,0 +1,35 @@
+"""y = x W^T for a weight kept `[out, in]` as the checkpoint stores it (the
+reference transposes at load, crates/cuda/src/engine.rs:6523-6540; here both
+operands are K-major, which is what the tensor cores want too).
+
+`matmul` picks the kernel: the tensor-core kernels take bfloat16 x bfloat16; every
+other combination (the whole 32-bit path; a weight kept in 32 bits beside 16-bit
+activations) runs the plain FMA kernel.  The destination is a new tensor in the
+activation dtype, a given tensor, or - with `accumulate=True` - a float32 tensor
+that the product is added into (the residual stream).
+"""
+from __future__ import annotations
+
+from typing import Optional
+
+import torch
+
+from .. import ops
+
+
+def matmul(ctx, a: torch.Tensor, w: torch.Tensor, out: Optional[torch.Tensor] = None,
+           out_dtype: Optional[torch.dtype] = None, accumulate: bool = False) -> torch.Tensor:
+    M, N = a.shape[0], w.shape[0]
+    if out is None:
+        if accumulate:
+            raise ValueError("matmul: accumulation needs a destination")
+        out = torch.empty((M, N), dtype=out_dtype or a.dtype, device=a.device)
+    if accumulate and out.dtype != torch.float32:
+        raise ValueError("matmul: accumulation needs a float32 destination")
+    if M == 0:
+        return out
+    if a.dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and ops.fast_gemm_available():
+        ops.gemm_bf16(a, w, out, accumulate)
+    else:
+        ops.gemm_ref(a, w, out, accumulate)
+    return out

@@ -1,0 +1,138 @@
+"""A model built from a `ModelSpec`: embedding, layers (each a block of four parts),
+final norm, output head, and the order in which layers run.  The class knows no
+architecture; everything it does is driven by the spec.
+"""
+from __future__ import annotations
+
+from typing import Dict, List, Mapping, Optional, Tuple
+
+import torch
+
+from ..weights.params import ParamSpec
+from .base import PagedKVSpec, SlotStateSpec, _REGISTRY, _ensure_builtin, build_part
+from .spec import LayerSpec, ModelSpec, PartSpec
+
+
+class Layer:
+    def __init__(self, spec: LayerSpec):
+        self.spec = spec
+        self.name = spec.name
+        self.mixer_norm = build_part("norm", spec.mixer_norm)
+        self.mixer = build_part("mixer", spec.mixer)
+        self.ffn_norm = build_part("norm", spec.ffn_norm)
+        self.ffn = build_part("ffn", spec.ffn)
+        _ensure_builtin()
+        try:
+            block_cls = _REGISTRY[("block", spec.block)]
+        except KeyError:
+            raise KeyError(f"no block arrangement '{spec.block}' is registered") from None
+        self.block = block_cls(self.mixer_norm, self.mixer, self.ffn_norm, self.ffn)
+
+    def parts(self):
+        s = self.spec
+        return ((s.mixer_norm, self.mixer_norm), (s.mixer, self.mixer), (s.ffn_norm, self.ffn_norm), (s.ffn, self.ffn))
+
+
+class Model:
+    def __init__(self, spec: ModelSpec):
+        self.spec = spec
+        self.embedding = build_part("embedding", spec.embedding)
+        self.layers: List[Layer] = [Layer(ls) for ls in spec.layers]
+        names = [l.name for l in self.layers]
+        if len(set(names)) != len(names):
+            raise ValueError("layer names must be unique")
+        self.final_norm = build_part("norm", spec.final_norm)
+        self.lm_head = build_part("lm_head", spec.lm_head)
+        self.order = spec.run_order()
+        for i in self.order:
+            if not 0 <= i < len(self.layers):
+                raise ValueError(f"run order names layer {i} of {len(self.layers)}")
+        by_name = {l.name: l for l in self.layers}
+        for l in self.layers:
+            src = l.spec.cache_from
+            if src is not None:
+                if src not in by_name:
+                    raise ValueError(f"layer {l.name} reads the cache of unknown layer {src}")
+                if by_name[src].spec.cache_from is not None:
+                    raise ValueError(f"layer {l.name} reads the cache of {src}, which has none of its own")
+                if by_name[src].mixer.cache_spec() != l.mixer.cache_spec():
+                    raise ValueError(f"layer {l.name} and {src} need different caches")
+
+    # ---- tensors -------------------------------------------------------------
+    def _all_parts(self):
+        s = self.spec
+        yield s.embedding, self.embedding
+        for l in self.layers:
+            yield from l.parts()
+        yield s.final_norm, self.final_norm
+        yield s.lm_head, self.lm_head
+
+    def param_specs(self) -> Dict[str, ParamSpec]:
+        out: Dict[str, ParamSpec] = {}
+        for pspec, part in self._all_parts():
+            for local, ps in part.param_specs().items():
+                name = pspec.prefix + local
+                if name in out and out[name] != ps:
+                    raise ValueError(f"tensor {name} is declared twice with different specs")
+                out[name] = ps
+        return out
+
+    def bind(self, state: Mapping[str, torch.Tensor]) -> None:
+        """Hand every part its tensors.  An optional tensor that is absent is replaced by its
+        fallback (another global name); a tied output head gets the embedding table."""
+        for pspec, part in self._all_parts():
+            local: Dict[str, torch.Tensor] = {}
+            for name, ps in part.param_specs().items():
+                g = pspec.prefix + name
+                if g in state:
+                    local[name] = state[g]
+                elif ps.optional and ps.fallback and ps.fallback in state:
+                    local[name] = state[ps.fallback]
+                elif not ps.optional:
+                    raise KeyError(f"tensor {g} was not loaded")
+            if part is self.lm_head and getattr(part, "tied", False):
+                local["weight"] = state[self.spec.embedding.prefix + "weight"]
+            part.bind(local)
+
+    def prepare(self, device, dtype) -> None:
+        for l in self.layers:
+            l.mixer.prepare(device, dtype)
+
+    # ---- what the cache manager has to provide -------------------------------
+    def cache_layout(self):
+        """(paged, states): paged maps each layer that owns pages to its PagedKVSpec; states
+        maps each layer with a fixed-size state to its SlotStateSpec.  Layers that read
+        another layer's cache own nothing."""
+        paged: Dict[str, PagedKVSpec] = {}
+        states: Dict[str, SlotStateSpec] = {}
+        for l in self.layers:
+            cs, ss = l.mixer.cache_spec(), l.mixer.state_spec()
+            if cs is not None and l.spec.cache_from is None:
+                paged[l.name] = cs
+            if ss is not None:
+                states[l.name] = ss
+        return paged, states
+
+    def cache_source(self, layer_name: str) -> str:
+        for l in self.layers:
+            if l.name == layer_name:
+                return l.spec.cache_from or l.name
+        raise KeyError(layer_name)
+
+    # ---- the forward pass of one step ------------------------------------------
+    def forward(self, ctx, want_rows: Optional[torch.Tensor]) -> Optional[torch.Tensor]:
+        """Run the step's tokens through every layer in run order; return float32 logits
+        [len(want_rows), vocab] for the wanted token rows (None if none are wanted)."""
+        x = self.embedding.forward(ctx)
+        for i in self.order:
+            layer = self.layers[i]
+            layer.block.forward(ctx, x, ctx.layer_caches[layer.name])
+        if want_rows is None or want_rows.numel() == 0:
+            return None
+        xn = self.final_norm.forward(ctx, x, row_idx=want_rows)
+        return self.lm_head.forward(ctx, xn)
+
+
+def expected_params(spec: ModelSpec) -> Dict[str, ParamSpec]:
+    """Tensor names and shapes of a spec (parts are built on the CPU; no device is touched)."""
+    return Model(spec).param_specs()

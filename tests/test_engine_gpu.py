@@ -1,0 +1,149 @@
+"""The engine against the plain implementation, in 32-bit and in bfloat16, under every
+way of cutting the work: whole, tail one by one, portions down to two tokens, mixed
+batches over a pool so small that pages are used again."""
+from __future__ import annotations
+
+import json
+import os
+import subprocess
+import sys
+
+import numpy as np
+import pytest
+import torch
+
+import plain_qwen3 as plain
+import tiny
+
+pytestmark = pytest.mark.gpu
+
+# |engine - plain| <= TOL * max|plain logit| of the row
+TOL = {"float32": 1e-4, "bfloat16": 3e-2}
+
+
+@pytest.fixture(scope="module")
+def models(tmp_path_factory):
+    out = {}
+    for which in ("A", "B"):
+        for store, dt in (("f32", torch.float32), ("bf16", torch.bfloat16)):
+            d = str(tmp_path_factory.mktemp(f"tiny{which}_{store}"))
+            tiny.make_model_dir(d, which, dt)
+            out[(which, store)] = d
+    return out
+
+
+_truth_cache = {}
+
+
+def truth(model_dir, seqs):
+    key = (model_dir, tuple((r, tuple(t)) for r, t in seqs.items()))
+    if key not in _truth_cache:
+        cfg, w = plain.read_model(model_dir)
+        _truth_cache[key] = {r: plain.forward(cfg, w, t) for r, t in seqs.items()}
+    return _truth_cache[key]
+
+
+def run_steps(engine, steps):
+    """-> {(request, position): logits row (cpu float64)}"""
+    from reinfer_b200.engine import StepEntry
+    got = {}
+    done = {}
+    for entries, end in steps:
+        logits = engine.step([StepEntry(r, t, w) for r, t, w in entries])
+        row = 0
+        for r, t, w in entries:
+            base = done.get(r, 0)
+            for k in w:
+                got[(r, base + k)] = logits[row].double().cpu()
+                row += 1
+            done[r] = base + len(t)
+        for r in end:
+            engine.finish(r)
+            done.pop(r, None)
+        engine.cache.check()
+    return got
+
+
+def compare(got, want, tol):
+    worst = 0.0
+    for (r, p), row in got.items():
+        ref = want[r][p]
+        scale = ref.abs().max().item()
+        err = (row - ref).abs().max().item() / scale
+        worst = max(worst, err)
+        assert err <= tol, f"request {r} position {p}: error {err:.3e} of the logit scale (limit {tol})"
+        top2 = torch.topk(ref, 2).values
+        if (top2[0] - top2[1]).item() > 2 * tol * scale:
+            assert int(row.argmax()) == int(ref.argmax()), f"request {r} position {p}: other argmax"
+    return worst
+
+
+CUTS = {"whole": tiny.cut_whole, "tail": tiny.cut_tail_one_by_one, "portions": tiny.cut_portions,
+        "mixed": tiny.cut_mixed}
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("which", ["A", "B"])
+@pytest.mark.parametrize("cut", list(CUTS))
+def test_cuts_match_plain(models, which, dtype, cut):
+    from reinfer_b200.engine import Engine
+    model_dir = models[(which, "f32" if dtype == "float32" else "bf16")]
+    seqs = tiny.sequences(which)
+    steps = CUTS[cut](seqs)
+    pool = tiny.pool_tokens_needed(steps)
+    engine = Engine.from_model_dir(model_dir, dtype=dtype, page_size=tiny.TINY[which][2], max_tokens=pool,
+                                   max_num_seqs=4)
+    got = run_steps(engine, steps)
+    assert len(got) == sum(len(t) for t in seqs.values())
+    compare(got, truth(model_dir, seqs), TOL[dtype])
+    assert engine.cache.free_pages() == engine.cache.total_pages()
+
+
+@pytest.mark.parametrize("which", ["A", "B"])
+def test_float32_cuts_agree_bitwise(models, which):
+    """The 32-bit kernels order their sums by position only, so every cut gives the same bits."""
+    from reinfer_b200.engine import Engine
+    model_dir = models[(which, "f32")]
+    seqs = tiny.sequences(which)
+    results = []
+    for cut in CUTS.values():
+        steps = cut(seqs)
+        engine = Engine.from_model_dir(model_dir, dtype="float32", page_size=tiny.TINY[which][2],
+                                       max_tokens=tiny.pool_tokens_needed(steps), max_num_seqs=4)
+        results.append(run_steps(engine, steps))
+    for other in results[1:]:
+        for key, row in results[0].items():
+            assert torch.equal(row, other[key]), f"{key}: bits differ between cuts"
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_trace_run_program(models, tmp_path, dtype):
+    """bin/trace_run end to end: protocol, files, pages used again."""
+    which = "B"
+    model_dir = models[(which, "f32" if dtype == "float32" else "bf16")]
+    seqs = tiny.sequences(which)
+    steps = tiny.cut_mixed(seqs, seed=11)
+    lines = []
+    for i, (entries, end) in enumerate(steps):
+        lines.append(json.dumps({"step": i, "entries": [{"id": r, "tokens": t, "want": w} for r, t, w in entries],
+                                 "end": end}))
+    out = tmp_path / "out"
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    p = subprocess.run([sys.executable, os.path.join(root, "bin", "trace_run"), "--model", model_dir, "--dtype", dtype,
+                        "--out", str(out), "--max-tokens", str(tiny.pool_tokens_needed(steps))],
+                       input="\n".join(lines) + "\n", capture_output=True, text=True, timeout=600)
+    assert p.returncode == 0, p.stderr[-2000:]
+    assert [l for l in p.stdout.splitlines() if l.startswith("done")] == [f"done {i}" for i in range(len(steps))]
+    want = truth(model_dir, seqs)
+    vocab = tiny.TINY[which][0]["vocab_size"]
+    done, got = {}, {}
+    for i, (entries, end) in enumerate(steps):
+        arr = np.fromfile(out / f"{i}.f32", dtype="<f4").reshape(-1, vocab)
+        row = 0
+        for r, t, w in entries:
+            for k in w:
+                got[(r, done.get(r, 0) + k)] = torch.from_numpy(arr[row].astype(np.float64))
+                row += 1
+            done[r] = done.get(r, 0) + len(t)
+        assert row == arr.shape[0]
+    compare(got, want, TOL[dtype])
