@@ -1,0 +1,108 @@
+"""Command line in the reference's manner: `reinfer run <model> [-n MAX_TOKENS] [-t TEMP]
+[--top-k K] [--top-p P] [--repeat-penalty R] [--seed S] [--max-model-len N] [--perf]
+[prompt ...]` (bin/reinfer/src/main.rs:246-294; defaults: -n 256, -t 1.0).  The engine
+works on token ids, so the prompt is a list of integers (separated by blanks or commas),
+from the arguments or, when there are none, from standard input; the generated ids are
+printed on one line.  `--perf` adds the reference's machine-readable line
+(main.rs:700-727).  `reinfer random-model` writes a model folder with seeded random
+weights.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import sys
+import time
+
+
+def _ids(words):
+    out = []
+    for w in words:
+        for part in w.replace(",", " ").split():
+            out.append(int(part))
+    return out
+
+
+def cmd_run(a) -> int:
+    from .engine.llm import LLM
+    from .sampling.params import SamplingParams
+    prompt = _ids(a.prompt) if a.prompt else _ids(sys.stdin.read().split())
+    if not prompt:
+        print("error: empty prompt (give token ids as arguments or on standard input)", file=sys.stderr)
+        return 2
+    t0 = time.perf_counter()
+    llm = LLM(a.model, dtype=a.dtype, max_model_len=a.max_model_len, page_size=a.page_size,
+              num_pages=a.num_pages, max_num_seqs=a.max_num_seqs, max_batch_tokens=a.max_batch_tokens,
+              seed=a.seed or 0)
+    load_s = time.perf_counter() - t0
+    sp = SamplingParams(temperature=a.temperature, top_k=a.top_k or 0, top_p=a.top_p if a.top_p is not None else 1.0,
+                        min_p=a.min_p or 0.0, repeat_penalty=a.repeat_penalty or 1.0, seed=a.seed,
+                        max_tokens=a.max_tokens)
+    t1 = time.perf_counter()
+    rid = llm.add_request(prompt, sp)
+    first = None
+    while llm.has_work():
+        llm.step()
+        if first is None and llm.requests[rid].output:
+            first = time.perf_counter() - t1
+    dt = time.perf_counter() - t1
+    r = llm.requests[rid]
+    print(" ".join(str(t) for t in r.output))
+    n = len(r.output)
+    tpot = (dt - (first or 0.0)) / max(n - 1, 1) * 1e3
+    print(f"{n} tokens in {dt:.3f}s (≈{n / dt if dt > 0 else 0:.1f} tok/s, first-token {(first or 0) * 1e3:.1f} ms), "
+          f"finish={r.finish_reason}", file=sys.stderr)
+    if a.perf:
+        print(f"PERF model={a.model} dtype={a.dtype} load_s={load_s:.2f} prompt_tokens={len(prompt)} "
+              f"new_tokens={n} ttft_ms={(first or 0) * 1e3:.3f} tpot_ms={tpot:.3f} "
+              f"tok_s={(n - 1) / (dt - (first or 0)) if n > 1 and dt > (first or 0) else 0:.2f} "
+              f"preemptions={llm.scheduler.stats['preemptions']}")
+    return 0
+
+
+def cmd_random_model(a) -> int:
+    import torch
+    from .config.registry import resolve_architecture
+    from .weights.loader import write_random_model
+    with open(a.config) as f:
+        raw = json.load(f)
+    arch = resolve_architecture(raw)
+    cfg = arch.config_cls.from_dict(raw)
+    dt = {"float32": torch.float32, "bfloat16": torch.bfloat16}[a.dtype]
+    print(write_random_model(a.out, cfg, a.seed, dt))
+    return 0
+
+
+def main(argv=None) -> int:
+    ap = argparse.ArgumentParser(prog="reinfer", description="B200-native inference engine (token ids in, token ids out)")
+    sub = ap.add_subparsers(dest="cmd", required=True)
+    r = sub.add_parser("run", help="generate from a prompt of token ids")
+    r.add_argument("model", help="local model folder (config.json + safetensors)")
+    r.add_argument("-n", dest="max_tokens", type=int, default=256, metavar="MAX_TOKENS", help="max new tokens")
+    r.add_argument("-t", dest="temperature", type=float, default=1.0, metavar="TEMP", help="0 = greedy")
+    r.add_argument("--top-k", type=int, default=None, metavar="K")
+    r.add_argument("--top-p", type=float, default=None, metavar="P")
+    r.add_argument("--min-p", type=float, default=None, metavar="P")
+    r.add_argument("--repeat-penalty", type=float, default=None, metavar="PENALTY")
+    r.add_argument("--seed", type=int, default=None, metavar="SEED")
+    r.add_argument("--max-model-len", type=int, default=None, metavar="N")
+    r.add_argument("--perf", action="store_true", help="print a machine-parseable PERF line")
+    r.add_argument("--dtype", choices=["bfloat16", "float32"], default="bfloat16")
+    r.add_argument("--page-size", type=int, default=16)
+    r.add_argument("--num-pages", type=int, default=None)
+    r.add_argument("--max-num-seqs", type=int, default=8)
+    r.add_argument("--max-batch-tokens", type=int, default=2048)
+    r.add_argument("prompt", nargs="*", help="token ids; standard input when absent")
+    r.set_defaults(fn=cmd_run)
+    m = sub.add_parser("random-model", help="write a model folder with seeded random weights")
+    m.add_argument("--config", required=True, help="a config.json of a registered architecture")
+    m.add_argument("--out", required=True)
+    m.add_argument("--seed", type=int, default=0)
+    m.add_argument("--dtype", choices=["bfloat16", "float32"], default="bfloat16")
+    m.set_defaults(fn=cmd_random_model)
+    a = ap.parse_args(argv)
+    return a.fn(a)
+
+
+if __name__ == "__main__":
+    sys.exit(main())

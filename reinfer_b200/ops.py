@@ -61,7 +61,12 @@ def require_device() -> None:
     _checked_device = True
 
 
+launches = 0          # kernels of this library launched so far (every wrapper passes through _check)
+
+
 def _check(rc: int, what: str) -> None:
+    global launches
+    launches += 1
     if rc == 0:
         return
     if rc < 0:

@@ -1,0 +1,83 @@
+"""Host side of the GPU sampler: packs one record per row of logits and launches the
+kernel (csrc/sampler.cu).  The draw of a request at its n-th generated token is a pure
+function of (its seed, n, token id): SplitMix64 stream and Gumbel noise as in the
+reference (crates/cuda/kernels/sampler_kernel.cu:61-77; crates/scheduler/src/rng.rs:
+12-50), so the tokens of a request do not depend on the batch it was in.
+"""
+from __future__ import annotations
+
+from typing import List, Optional, Sequence
+
+import numpy as np
+import torch
+
+from .. import ops
+from .params import SamplingParams
+
+HIST_CAP = 64
+_MASK64 = (1 << 64) - 1
+GOLDEN = 0x9E3779B97F4A7C15
+
+RECORD = np.dtype([("temperature", "<f4"), ("top_k", "<i4"), ("top_p", "<f4"), ("min_p", "<f4"),
+                   ("repeat_penalty", "<f4"), ("frequency_penalty", "<f4"), ("presence_penalty", "<f4"),
+                   ("hist_len", "<i4"), ("seed", "<u8"), ("step", "<u8")])
+
+
+def _mix(z: int) -> int:
+    z = ((z ^ (z >> 30)) * 0xBF58476D1CE4E5B9) & _MASK64
+    z = ((z ^ (z >> 27)) * 0x94D049BB133111EB) & _MASK64
+    return z ^ (z >> 31)
+
+
+def splitmix64(x: int) -> int:
+    """mix(x + golden)  (crates/scheduler/src/rng.rs:24-30)."""
+    return _mix((x + GOLDEN) & _MASK64)
+
+
+def request_seed(base_seed: int, arrival: int) -> int:
+    """Seed of a request that brought none: splitmix64(base ^ arrival number)
+    (bin/reinfer/src/sched_loop.rs:650-653)."""
+    return splitmix64((base_seed ^ arrival) & _MASK64)
+
+
+class Sampler:
+    def __init__(self, vocab_size: int, max_rows: int, device):
+        self.vocab = int(vocab_size)
+        self.device = torch.device(device)
+        self.max_rows = int(max_rows)
+        if ops.sample_params_size() != RECORD.itemsize:
+            raise ops.KernelError("the sampler's record layout differs between library and Python")
+        self._work = torch.empty((self.max_rows, self.vocab), dtype=torch.float32, device=self.device)
+        self._host_params = torch.empty(self.max_rows * RECORD.itemsize, dtype=torch.uint8, pin_memory=True)
+        self._host_hist = torch.empty((self.max_rows, HIST_CAP), dtype=torch.int32, pin_memory=True)
+        self._host_out = torch.empty(self.max_rows, dtype=torch.int32, pin_memory=True)
+
+    def sample(self, logits: torch.Tensor, params: Sequence[SamplingParams], seeds: Sequence[int],
+               steps: Sequence[int], histories: Optional[Sequence[Sequence[int]]] = None) -> List[int]:
+        """One token per row of `logits` ([rows, vocab] float32 on the device).  Returns host ints
+        (-1 for a row without a finite logit).  Blocks until the tokens are on the host."""
+        rows = logits.shape[0]
+        if rows == 0:
+            return []
+        if rows > self.max_rows:
+            raise ValueError(f"{rows} rows exceed the sampler's {self.max_rows}")
+        rec = np.zeros(rows, dtype=RECORD)
+        hist = self._host_hist.numpy()
+        any_hist = False
+        for r, p in enumerate(params):
+            rec[r] = (p.temperature, p.top_k, p.top_p, p.min_p, p.repeat_penalty, p.frequency_penalty,
+                      p.presence_penalty, 0, seeds[r] & _MASK64, steps[r])
+            pen = p.repeat_penalty > 1.0 or p.frequency_penalty != 0.0 or p.presence_penalty != 0.0
+            if pen and histories is not None and p.repeat_last_n > 0:
+                h = list(histories[r])[-p.repeat_last_n:]
+                hist[r, :len(h)] = h
+                rec[r]["hist_len"] = len(h)
+                any_hist = any_hist or bool(h)
+        self._host_params.numpy()[:rows * RECORD.itemsize] = rec.view(np.uint8)
+        dparams = self._host_params[:rows * RECORD.itemsize].to(self.device, non_blocking=True)
+        dhist = self._host_hist[:rows].to(self.device, non_blocking=True) if any_hist else None
+        out = torch.empty(rows, dtype=torch.int32, device=self.device)
+        ops.sample(logits, None, dparams, dhist, self._work, out, rows)
+        self._host_out[:rows].copy_(out, non_blocking=True)
+        torch.cuda.current_stream().synchronize()
+        return [int(v) for v in self._host_out[:rows].tolist()]

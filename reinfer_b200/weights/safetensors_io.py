@@ -14,6 +14,7 @@ import json
 import mmap
 import os
 import struct
+import warnings
 from typing import Dict, Iterable, List, Mapping, Tuple
 
 import numpy as np
@@ -93,7 +94,9 @@ class SafetensorsFile:
         tdt, ndt, isz = _DTYPES[tag]
         count = (en - b) // isz
         arr = np.frombuffer(self._mm, dtype=ndt, count=count, offset=self._data_start + b)
-        t = torch.from_numpy(arr.copy() if count == 0 else arr)  # read-only view; callers copy
+        with warnings.catch_warnings():
+            warnings.simplefilter("ignore", UserWarning)     # the view is read-only; callers copy, never write
+            t = torch.from_numpy(arr.copy() if count == 0 else arr)
         if tag == "BF16":
             t = t.view(torch.bfloat16)
         return t.reshape(shape)
