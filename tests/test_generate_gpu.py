@@ -1,0 +1,181 @@
+"""Generation through the entry point: greedy against the plain implementation, long
+decoding, the sampler's options, preemption on the device, the command line."""
+from __future__ import annotations
+
+import os
+import subprocess
+import sys
+
+import pytest
+import torch
+
+import plain_qwen3 as plain
+import tiny
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.fixture(scope="module")
+def model_dirs(tmp_path_factory):
+    return {w: tiny.make_model_dir(str(tmp_path_factory.mktemp(f"gen{w}")), w, torch.float32) for w in ("A", "B")}
+
+
+def plain_greedy_teacher(cfg, w, prompt, n):
+    return plain.greedy(cfg, w, prompt, n)
+
+
+@pytest.mark.parametrize("which", ["A", "B"])
+def test_greedy_matches_plain_float32(model_dirs, which):
+    from reinfer_b200 import LLM, SamplingParams
+    cfg, w = plain.read_model(model_dirs[which])
+    seqs = tiny.sequences(which, lengths=[5, 17, 33] if which == "A" else [1, 9, 24, 50])
+    llm = LLM(model_dirs[which], dtype="float32", page_size=tiny.TINY[which][2], num_pages=64, max_num_seqs=4,
+              max_batch_tokens=16, max_chunk=7)
+    outs = llm.generate(list(seqs.values()), SamplingParams(temperature=0.0, max_tokens=8, ignore_eos=True))
+    for o, p in zip(outs, seqs.values()):
+        assert o.token_ids == plain.greedy(cfg, w, p, 8) and o.finish_reason == "length"
+    assert llm.engine.cache.free_pages() == 64
+
+
+def test_greedy_bfloat16_follows_plain_teacher_forced(model_dirs, tmp_path):
+    """bfloat16 may pick another token where two logits are close; wherever it picks, the plain
+    logits of ITS sequence must call that token best or nearly so."""
+    from reinfer_b200 import LLM, SamplingParams
+    d = tiny.make_model_dir(str(tmp_path / "b16"), "B", torch.bfloat16)
+    cfg, w = plain.read_model(d)
+    prompt = tiny.sequences("B", lengths=[24])["r0"]
+    llm = LLM(d, dtype="bfloat16", page_size=8, num_pages=64, max_num_seqs=2, max_batch_tokens=64)
+    out = llm.generate(prompt, SamplingParams(temperature=0.0, max_tokens=24, ignore_eos=True))[0].token_ids
+    logits = plain.forward(cfg, w, prompt + out)
+    for i, tok in enumerate(out):
+        row = logits[len(prompt) - 1 + i]
+        assert row[tok] >= row.max() - 3e-2 * row.abs().max()
+
+
+def test_long_decoding_float32(model_dirs):
+    """One request decoded over many pages, every logit row compared at the end."""
+    from reinfer_b200.engine import Engine, StepEntry
+    which = "A"
+    cfg, w = plain.read_model(model_dirs[which])
+    seq = tiny.sequences(which, lengths=[300], seed=21)["r0"]
+    e = Engine.from_model_dir(model_dirs[which], dtype="float32", page_size=16, max_tokens=320, max_num_seqs=1)
+    rows = [e.step([StepEntry("x", seq[:4], [0, 1, 2, 3])])]
+    for t in seq[4:]:
+        rows.append(e.step([StepEntry("x", [t], [0])]))
+    got = torch.cat(rows).double().cpu()
+    ref = plain.forward(cfg, w, seq)
+    assert (got - ref).abs().max().item() <= 1e-4 * ref.abs().max().item()
+    assert torch.equal(got.argmax(-1), ref.argmax(-1))
+
+
+def test_first_tokens_of_a_sequence(model_dirs):
+    """Positions 0, 1, 2: a single key, a one-token prompt, a first page hardly begun."""
+    from reinfer_b200.engine import Engine, StepEntry
+    for which in ("A", "B"):
+        cfg, w = plain.read_model(model_dirs[which])
+        for dtype, tol in (("float32", 1e-4), ("bfloat16", 3e-2)):
+            e = Engine.from_model_dir(model_dirs[which], dtype=dtype, page_size=tiny.TINY[which][2], max_tokens=64,
+                                      max_num_seqs=2)
+            seq = [7, 3, 250]
+            ref = plain.forward(cfg, w, seq)
+            got = torch.cat([e.step([StepEntry("x", [t], [0])]) for t in seq]).double().cpu()
+            assert (got - ref).abs().max().item() <= tol * ref.abs().max().item()
+            one = e.step([StepEntry("y", [7], [0])]).double().cpu()
+            assert (one[0] - ref[0]).abs().max().item() <= tol * ref.abs().max().item()
+
+
+def test_sampler_options(model_dirs):
+    from reinfer_b200.sampling import Sampler, SamplingParams
+    torch.manual_seed(0)
+    V = 1000
+    logits = torch.randn(4, V, device="cuda") * 2
+    logits[1, 17] = float("nan"); logits[2, :] = float("-inf")
+    s = Sampler(V, 8, "cuda")
+    greedy = s.sample(logits, [SamplingParams()] * 4, [1] * 4, [0] * 4)
+    assert greedy[0] == int(logits[0].argmax()) and greedy[2] == -1
+    assert greedy[1] == int(torch.nan_to_num(logits[1], nan=-1e30).argmax())
+    tie = torch.zeros(1, V, device="cuda"); tie[0, 5] = tie[0, 900] = 3.0
+    assert s.sample(tie, [SamplingParams()], [0], [0]) == [5]                       # first maximum
+    # same (seed, step) -> same token; rows do not influence each other
+    p = SamplingParams(temperature=0.8, seed=3)
+    a = s.sample(logits[:1], [p], [3], [4])
+    b = s.sample(torch.cat([logits[3:4], logits[:1]]), [p, p], [9, 3], [0, 4])
+    assert a[0] == b[1]
+    # top_k: only the k largest are ever drawn; top_p / min_p: only the head of the distribution
+    row = logits[0:1]
+    top5 = set(torch.topk(row[0], 5).indices.tolist())
+    draws = {s.sample(row, [SamplingParams(temperature=1.5, top_k=5)], [11], [i])[0] for i in range(200)}
+    assert draws <= top5 and len(draws) >= 3
+    pr = torch.softmax(row[0] / 1.0, 0)
+    srt = torch.sort(pr, descending=True)
+    n_keep = int((torch.cumsum(srt.values, 0) < 0.5).sum()) + 1
+    nucleus = set(srt.indices[:n_keep].tolist())
+    draws = {s.sample(row, [SamplingParams(temperature=1.0, top_p=0.5)], [12], [i])[0] for i in range(200)}
+    assert draws <= nucleus and len(draws) >= 2
+    keep = set((pr >= pr.max() * 0.3).nonzero().flatten().tolist())
+    draws = {s.sample(row, [SamplingParams(temperature=1.0, min_p=0.3)], [13], [i])[0] for i in range(100)}
+    assert draws <= keep
+    # frequencies follow softmax(logits / T)
+    small = torch.tensor([[2.0, 1.0, 0.0, -1.0] + [-30.0] * (V - 4)], device="cuda")
+    n = 4000
+    counts = torch.zeros(4)
+    for i in range(0, n, 8):
+        for t in s.sample(small.expand(8, V).contiguous(), [SamplingParams(temperature=1.0)] * 8, [21] * 8, list(range(i, i + 8))):
+            counts[t] += 1
+    want = torch.softmax(torch.tensor([2.0, 1.0, 0.0, -1.0]), 0)
+    assert (counts / n - want).abs().max().item() < 0.03
+    # repetition penalty moves the choice away from a repeated best token
+    rep = torch.zeros(1, V, device="cuda"); rep[0, 7] = 2.0; rep[0, 8] = 1.9
+    assert s.sample(rep, [SamplingParams(repeat_penalty=1.5)], [0], [0], [[7, 7, 3]]) == [8]
+    assert s.sample(rep, [SamplingParams(presence_penalty=0.5)], [0], [0], [[7]]) == [8]
+    assert s.sample(rep, [SamplingParams(repeat_penalty=1.5)], [0], [0], [[3, 4]]) == [7]
+
+
+def test_temperature_generation_is_seeded_and_batch_independent(model_dirs):
+    from reinfer_b200 import LLM, SamplingParams
+    which = "B"
+    seqs = list(tiny.sequences(which, lengths=[9, 24, 50]).values())
+    sp = SamplingParams(temperature=0.8, seed=3, max_tokens=10, ignore_eos=True)
+
+    def run(prompts, **kw):
+        llm = LLM(model_dirs[which], dtype="float32", page_size=8, num_pages=64, max_num_seqs=4, **kw)
+        return [o.token_ids for o in llm.generate(prompts, sp)]
+    together = run(seqs, max_batch_tokens=16, max_chunk=7)
+    alone = [run([p], max_batch_tokens=64)[0] for p in seqs]
+    assert together == alone
+    assert together == run(seqs, max_batch_tokens=16, max_chunk=7)
+    assert len({tuple(t) for t in together}) == 3
+
+
+def test_preemption_on_the_device_keeps_outputs(model_dirs):
+    from reinfer_b200 import LLM, SamplingParams
+    which = "A"
+    seqs = list(tiny.sequences(which, lengths=[20, 25, 30]).values())
+    sp = SamplingParams(temperature=0.0, max_tokens=40, ignore_eos=True)
+    calm = LLM(model_dirs[which], dtype="float32", page_size=16, num_pages=64, max_num_seqs=4, max_batch_tokens=32)
+    want = [o.token_ids for o in calm.generate(seqs, sp)]
+    tight = LLM(model_dirs[which], dtype="float32", page_size=16, num_pages=9, max_num_seqs=4, max_batch_tokens=32)
+    outs = tight.generate(seqs, sp)
+    assert tight.last_stats["preemptions"] > 0
+    assert [o.token_ids for o in outs] == want
+    assert tight.engine.cache.free_pages() == 9
+
+
+def test_out_of_vocabulary_token_is_refused(model_dirs):
+    from reinfer_b200.engine import EmbeddingOov, Engine, StepEntry
+    e = Engine.from_model_dir(model_dirs["A"], dtype="float32", max_tokens=64, max_num_seqs=1)
+    with pytest.raises(EmbeddingOov):
+        e.step([StepEntry("x", [1, 256], [1])])
+    assert "x" not in e.cache
+
+
+def test_command_line(model_dirs):
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    cfg, w = plain.read_model(model_dirs["A"])
+    prompt = [4, 8, 15, 16, 23, 42]
+    p = subprocess.run([sys.executable, os.path.join(root, "bin", "reinfer"), "run", model_dirs["A"], "-n", "5", "-t", "0",
+                        "--dtype", "float32", "--perf"] + [str(t) for t in prompt], capture_output=True, text=True, timeout=600)
+    assert p.returncode == 0, p.stderr[-2000:]
+    lines = p.stdout.strip().splitlines()
+    assert [int(t) for t in lines[0].split()] == plain.greedy(cfg, w, prompt, 5)
+    assert lines[1].startswith("PERF ") and "tpot_ms=" in lines[1]
