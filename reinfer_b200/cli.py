@@ -100,7 +100,12 @@ def main(argv=None) -> int:
     m.add_argument("--seed", type=int, default=0)
     m.add_argument("--dtype", choices=["bfloat16", "float32"], default="bfloat16")
     m.set_defaults(fn=cmd_random_model)
-    a = ap.parse_args(argv)
+    a, extra = ap.parse_known_args(argv)
+    if extra:
+        # token ids that follow options (argparse binds a '*' positional before it sees them)
+        if a.cmd != "run" or not all(e.replace(",", "").lstrip("-").isdigit() for e in extra):
+            ap.error("unrecognized arguments: " + " ".join(extra))
+        a.prompt = list(a.prompt) + extra
     return a.fn(a)
 
 

@@ -1,0 +1,353 @@
+// The tensor-core matrix product of the bfloat16 path, written for sm_100a:
+//     C[T,N] (=|+=) X[T,K] * W[N,K]^T        X, W bfloat16 K-major; accumulation in float
+// TMA (cp.async.bulk.tensor) stages 128-byte-swizzled tiles of both operands in shared
+// memory, one elected thread issues tcgen05.mma (kind::f16, bf16 inputs) with the
+// accumulator in tensor memory, four warps read it back with tcgen05.ld and store.
+//
+// The operands are always swapped: the WEIGHT rows ride the instruction's M (128 output
+// features per CTA) and the TOKENS ride its N (16..256).  One kernel therefore serves a
+// 2,048-token prompt portion (N = 256) and a single decoded token (N = 16, operands
+// padded by TMA's out-of-bounds zero fill), and in the accumulator a thread owns one
+// output feature, so a warp's stores for one token are 32 consecutive features.
+// Small token counts give few CTAs, so K is split across CTAs (grid.z); the partial
+// sums go to a float workspace and a second kernel adds them in split order (fixed
+// order, no atomics: the reference's two-phase gemv does the same,
+// crates/cuda/kernels/gemm_m1.cu:106-123).  The reference's products are cublasGemmEx
+// and scalar gemv kernels (crates/cuda/src/gemm.rs:226-372).
+//
+// Every wait on an mbarrier is bounded: after RB_SPIN_LIMIT failed polls the CTA raises
+// an abort flag, its roles leave their loops, outstanding TMA loads are waited for (again
+// bounded), tensor memory is freed, and an error word in global memory tells the host.
+#include "common.cuh"
+#include <cuda.h>
+#include <cudaTypedefs.h>
+#include <mutex>
+#include <unordered_map>
+
+#define TC_BM 128            // output features per CTA (MMA M)
+#define TC_BK 64             // K elements per stage (128 bytes: one swizzle row)
+#define TC_THREADS 192       // warp 0: TMA, warp 1: MMA + tensor memory, warps 2..5: epilogue
+#define RB_SPIN_LIMIT (1u << 24)
+
+__device__ int g_tc_error = 0;          // 0 ok; else (code << 8 | detail) of the first failure
+
+// ------------------------------------------------------------------ PTX helpers
+__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+
+__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count));
+}
+__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ bool mbar_try(uint32_t bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
+    return ok != 0;
+}
+// Bounded wait.  Returns false if the CTA is aborting (or this wait gave up and raised the abort).
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag, int where) {
+    for (uint32_t it = 0; it < RB_SPIN_LIMIT; ++it) {
+        if (mbar_try(bar, parity)) return true;
+        if ((it & 255u) == 255u && *abort_flag) return false;
+    }
+    *abort_flag = where;
+    atomicCAS(&g_tc_error, 0, (1 << 8) | where);
+    return false;
+}
+__device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map, int x, int y, uint32_t bar) {
+    asm volatile(
+        "cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
+        ::"r"(dst), "l"(map), "r"(x), "r"(y), "r"(bar) : "memory");
+}
+__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_commit(uint32_t bar) {
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ void tc_mma_bf16(uint32_t tmem_d, uint64_t desc_a, uint64_t desc_b, uint32_t idesc, uint32_t accumulate) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+        ::"r"(tmem_d), "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate) : "memory");
+}
+__device__ __forceinline__ void tc_ld16(uint32_t taddr, uint32_t* r) {
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15}, [%16];"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+          "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
+        : "r"(taddr) : "memory");
+}
+__device__ __forceinline__ void tc_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+
+// Shared-memory operand descriptor: K-major tile, rows of 128 bytes, 128-byte swizzle,
+// 8-row groups 1024 bytes apart (SBO), descriptor version 1 (sm_100).
+__device__ __forceinline__ uint64_t make_smem_desc(uint32_t saddr) {
+    return (uint64_t)((saddr >> 4) & 0x3FFFu) | (1ull << 16) | ((uint64_t)(1024 >> 4) << 32) | (1ull << 46) | (2ull << 61);
+}
+// Instruction descriptor: D float, A and B bfloat16, both K-major, M = 128, N = BN.
+__host__ __device__ constexpr uint32_t make_idesc(int bn) {
+    return (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(bn >> 3) << 17) | ((uint32_t)(TC_BM >> 4) << 24);
+}
+
+struct TcShared {                        // after the operand stages, in dynamic shared memory
+    unsigned long long full[12];
+    unsigned long long empty[12];
+    unsigned long long acc_full;
+    uint32_t tmem_base;
+    int abort_flag;
+};
+
+// OUT_MODE 0: C = acc as bf16; 1: C = acc as float; 2: C(float) += acc; 3: workspace partial (float, [split][T][N])
+template <int BN, int STAGES>
+__global__ void __launch_bounds__(TC_THREADS, 1)
+gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_x,
+               void* __restrict__ C, float* __restrict__ ws, int T, int N, int K, long long ldc, int out_mode,
+               int kb_per_split) {
+    extern __shared__ __align__(1024) unsigned char smem_raw[];
+    constexpr uint32_t W_BYTES = TC_BM * TC_BK * 2;                 // 16 KB
+    constexpr uint32_t X_BYTES = BN * TC_BK * 2;
+    constexpr uint32_t STAGE_BYTES = W_BYTES + X_BYTES;            // multiples of 1024 (BN >= 16 -> 2 KB)
+    constexpr uint32_t TMEM_COLS = BN < 32 ? 32 : BN;
+    unsigned char* smem = (unsigned char*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+    TcShared* sh = (TcShared*)(smem + (size_t)STAGES * STAGE_BYTES);
+    const uint32_t smem_base = smem_u32(smem);
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int t0 = blockIdx.x * BN, n0 = blockIdx.y * TC_BM, split = blockIdx.z;
+    const int total_kb = (K + TC_BK - 1) / TC_BK;
+    const int kb0 = split * kb_per_split;
+    const int nkb = min(kb_per_split, total_kb - kb0);
+    volatile int* abort_flag = &sh->abort_flag;
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < STAGES; ++s) { mbar_init(smem_u32(&sh->full[s]), 1); mbar_init(smem_u32(&sh->empty[s]), 1); }
+        mbar_init(smem_u32(&sh->acc_full), 1);
+        sh->abort_flag = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+    }
+    if (warp == 1) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&sh->tmem_base)), "r"(TMEM_COLS) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem = sh->tmem_base;
+    int issued = 0;                                   // producer: k-blocks whose loads were issued
+
+    if (warp == 0) {
+        if (lane == 0) {
+            for (int kb = 0; kb < nkb; ++kb) {
+                const int s = kb % STAGES;
+                const uint32_t round = kb / STAGES;
+                if (!mbar_wait(smem_u32(&sh->empty[s]), (round & 1) ^ 1, abort_flag, 1)) break;
+                const uint32_t full = smem_u32(&sh->full[s]);
+                mbar_expect_tx(full, STAGE_BYTES);
+                const uint32_t dst = smem_base + s * STAGE_BYTES;
+                const int kx = (kb0 + kb) * TC_BK;
+                tma_load_2d(dst, &map_w, kx, n0, full);
+                tma_load_2d(dst + W_BYTES, &map_x, kx, t0, full);
+                issued = kb + 1;
+            }
+        }
+    } else if (warp == 1) {
+        if (lane == 0) {
+            constexpr uint32_t idesc = make_idesc(BN);
+            bool ok = true;
+            for (int kb = 0; kb < nkb && ok; ++kb) {
+                const int s = kb % STAGES;
+                const uint32_t round = kb / STAGES;
+                ok = mbar_wait(smem_u32(&sh->full[s]), round & 1, abort_flag, 2);
+                if (!ok) break;
+                tc_fence_after();
+                const uint32_t a = smem_base + s * STAGE_BYTES;
+                const uint64_t da = make_smem_desc(a), db = make_smem_desc(a + W_BYTES);
+#pragma unroll
+                for (int k = 0; k < TC_BK / 16; ++k)                 // 32 bytes further along K inside the swizzled row
+                    tc_mma_bf16(tmem, da + (uint64_t)(k * 2), db + (uint64_t)(k * 2), idesc, (kb | k) != 0);
+                tc_commit(smem_u32(&sh->empty[s]));                   // frees the stage when these MMAs are done
+            }
+            if (ok) tc_commit(smem_u32(&sh->acc_full));
+        }
+    } else {
+        // epilogue: warp w may read tensor-memory lanes 32*(w%4) .. +31
+        const int q = warp & 3;
+        const int feat = n0 + q * 32 + lane;
+        if (mbar_wait(smem_u32(&sh->acc_full), 0, abort_flag, 3)) {
+            tc_fence_after();
+#pragma unroll 1
+            for (int c0 = 0; c0 < BN; c0 += 16) {
+                if (t0 + c0 >= T) break;                               // warp-uniform
+                uint32_t r[16];
+                tc_ld16(tmem + ((uint32_t)(q * 32) << 16) + (uint32_t)c0, r);
+                tc_ld_wait();
+                if (feat < N) {
+#pragma unroll
+                    for (int j = 0; j < 16; ++j) {
+                        const int t = t0 + c0 + j;
+                        if (t >= T) break;
+                        const float v = __uint_as_float(r[j]);
+                        if (out_mode == 0) ((bf16*)C)[(size_t)t * ldc + feat] = __float2bfloat16_rn(v);
+                        else if (out_mode == 1) ((float*)C)[(size_t)t * ldc + feat] = v;
+                        else if (out_mode == 2) ((float*)C)[(size_t)t * ldc + feat] += v;
+                        else ws[((size_t)split * T + t) * N + feat] = v;
+                    }
+                }
+            }
+        }
+    }
+    tc_fence_before();
+    __syncthreads();
+    if (*abort_flag && threadIdx.x == 0) {
+        // loads that were issued but never consumed still write this CTA's shared memory: wait for them
+        for (int kb = max(0, issued - STAGES); kb < issued; ++kb) {
+            const uint32_t bar = smem_u32(&sh->full[kb % STAGES]);
+            const uint32_t parity = (kb / STAGES) & 1;
+            for (uint32_t it = 0; it < RB_SPIN_LIMIT; ++it) if (mbar_try(bar, parity)) break;
+        }
+    }
+    __syncthreads();
+    if (warp == 1) {
+        tc_fence_after();
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(TMEM_COLS) : "memory");
+    }
+}
+
+// Sum of the split partials in split order, then store / accumulate.  mode as OUT_MODE 0..2.
+__global__ void splitk_reduce_kernel(const float* __restrict__ ws, void* __restrict__ C, int T, int N, long long ldc,
+                                     int splits, int mode) {
+    const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= (size_t)T * N) return;
+    const int t = (int)(i / N), n = (int)(i % N);
+    float v = 0.0f;
+    for (int s = 0; s < splits; ++s) v += ws[(size_t)s * T * N + i];
+    if (mode == 0) ((bf16*)C)[(size_t)t * ldc + n] = __float2bfloat16_rn(v);
+    else if (mode == 1) ((float*)C)[(size_t)t * ldc + n] = v;
+    else ((float*)C)[(size_t)t * ldc + n] += v;
+}
+
+// ------------------------------------------------------------------ host side
+static PFN_cuTensorMapEncodeTiled_v12000 get_encode() {
+    static PFN_cuTensorMapEncodeTiled_v12000 fn = nullptr;
+    static std::once_flag once;
+    std::call_once(once, [] {
+        void* p = nullptr;
+        cudaDriverEntryPointQueryResult q;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess &&
+            q == cudaDriverEntryPointSuccess)
+            fn = (PFN_cuTensorMapEncodeTiled_v12000)p;
+    });
+    return fn;
+}
+
+struct MapKey {
+    const void* ptr; long long rows, cols, ld; int box_rows;
+    bool operator==(const MapKey& o) const { return ptr == o.ptr && rows == o.rows && cols == o.cols && ld == o.ld && box_rows == o.box_rows; }
+};
+struct MapKeyHash {
+    size_t operator()(const MapKey& k) const {
+        size_t h = (size_t)k.ptr;
+        h = h * 1000003u ^ (size_t)k.rows; h = h * 1000003u ^ (size_t)k.cols;
+        h = h * 1000003u ^ (size_t)k.ld; h = h * 1000003u ^ (size_t)k.box_rows;
+        return h;
+    }
+};
+// A tensor map depends only on (address, extents, row stride, box), so a cached one never goes stale.
+static int get_map(const void* ptr, long long rows, long long cols, long long ld, int box_rows, CUtensorMap* out) {
+    static std::unordered_map<MapKey, CUtensorMap, MapKeyHash> cache;
+    static std::mutex mu;
+    MapKey key{ptr, rows, cols, ld, box_rows};
+    std::lock_guard<std::mutex> g(mu);
+    auto it = cache.find(key);
+    if (it != cache.end()) { *out = it->second; return 0; }
+    auto enc = get_encode();
+    if (!enc) RB_REFUSE("gemm: the driver offers no cuTensorMapEncodeTiled");
+    cuuint64_t dims[2] = {(cuuint64_t)cols, (cuuint64_t)rows};
+    cuuint64_t strides[1] = {(cuuint64_t)ld * 2};
+    cuuint32_t box[2] = {TC_BK, (cuuint32_t)box_rows};
+    cuuint32_t estr[2] = {1, 1};
+    CUresult r = enc(out, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(ptr), dims, strides, box, estr,
+                     CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                     CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) RB_REFUSE("gemm: cuTensorMapEncodeTiled failed with %d (ptr %p rows %lld cols %lld ld %lld)", (int)r, ptr, rows, cols, ld);
+    if (cache.size() > 8192) cache.clear();
+    cache.emplace(key, *out);
+    return 0;
+}
+
+template <int BN, int STAGES>
+static int launch_tc(const CUtensorMap& mw, const CUtensorMap& mx, void* C, float* ws, int T, int N, int K, long long ldc,
+                     int out_mode, int splits, int kb_per_split, cudaStream_t s) {
+    constexpr size_t smem = (size_t)STAGES * (TC_BM * TC_BK * 2 + BN * TC_BK * 2) + sizeof(TcShared) + 1024;
+    static bool configured = false;
+    if (!configured) {
+        cudaError_t e = cudaFuncSetAttribute(gemm_tc_kernel<BN, STAGES>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        if (e != cudaSuccess) return (int)e;
+        configured = true;
+    }
+    dim3 grid(rb_ceil_div(T, BN), rb_ceil_div(N, TC_BM), splits);
+    gemm_tc_kernel<BN, STAGES><<<grid, TC_THREADS, smem, s>>>(mw, mx, C, ws, T, N, K, ldc, out_mode, kb_per_split);
+    return RB_LAUNCH_RESULT();
+}
+
+// X [T,K] bf16 (row stride ldx), W [N,K] bf16 (row stride ldw), C [T,N] bf16 or float (row stride ldc).
+// ws: float workspace of ws_floats elements for split-K partials (may be null: no split).
+extern "C" int rb_gemm_bf16(const void* X, const void* W, void* C, int c_dtype, int accumulate, int T, int N, int K,
+                            long long ldx, long long ldw, long long ldc, float* ws, long long ws_floats,
+                            int force_splits, void* stream) {
+    if (T <= 0 || N <= 0) return 0;
+    if (K <= 0) RB_REFUSE("gemm: K=%d", K);
+    if ((ldx % 8) || (ldw % 8) || ((uintptr_t)X & 15) || ((uintptr_t)W & 15))
+        RB_REFUSE("gemm: TMA needs 16-byte aligned operands and row strides (ldx %lld, ldw %lld)", ldx, ldw);
+    if (accumulate && c_dtype != RB_F32) RB_REFUSE("gemm: accumulation needs a float destination");
+    if (c_dtype != RB_F32 && c_dtype != RB_BF16) RB_REFUSE("gemm: destination dtype %d", c_dtype);
+    cudaStream_t s = (cudaStream_t)stream;
+    const int mode = accumulate ? 2 : (c_dtype == RB_F32 ? 1 : 0);
+    const int bn = T <= 16 ? 16 : T <= 32 ? 32 : T <= 64 ? 64 : T <= 128 ? 128 : 256;
+    const int total_kb = rb_ceil_div(K, TC_BK);
+    const int ctas = rb_ceil_div(T, bn) * rb_ceil_div(N, TC_BM);
+    int splits = 1;
+    if (force_splits > 0) splits = force_splits;
+    else if (ctas < 120 && ws) {
+        splits = (148 + ctas - 1) / ctas;
+        if (splits > 16) splits = 16;
+        while (splits > 1 && total_kb / splits < 4) --splits;      // at least 4 k-blocks per CTA
+    }
+    if (splits > total_kb) splits = total_kb;
+    while (splits > 1 && (!ws || (long long)splits * T * N > ws_floats)) --splits;
+    int kb_per_split = rb_ceil_div(total_kb, splits);
+    splits = rb_ceil_div(total_kb, kb_per_split);                   // no empty split
+    CUtensorMap mw, mx;
+    if (get_map(W, N, K, ldw, TC_BM, &mw)) return -1;
+    if (get_map(X, T, K, ldx, bn, &mx)) return -1;
+    const int out_mode = splits > 1 ? 3 : mode;
+    int rc;
+    switch (bn) {
+        case 16: rc = launch_tc<16, 8>(mw, mx, C, ws, T, N, K, ldc, out_mode, splits, kb_per_split, s); break;
+        case 32: rc = launch_tc<32, 8>(mw, mx, C, ws, T, N, K, ldc, out_mode, splits, kb_per_split, s); break;
+        case 64: rc = launch_tc<64, 6>(mw, mx, C, ws, T, N, K, ldc, out_mode, splits, kb_per_split, s); break;
+        case 128: rc = launch_tc<128, 5>(mw, mx, C, ws, T, N, K, ldc, out_mode, splits, kb_per_split, s); break;
+        default: rc = launch_tc<256, 4>(mw, mx, C, ws, T, N, K, ldc, out_mode, splits, kb_per_split, s); break;
+    }
+    if (rc) return rc;
+    if (splits > 1) {
+        const long long total = (long long)T * N;
+        splitk_reduce_kernel<<<rb_ceil_div(total, 256), 256, 0, s>>>(ws, C, T, N, ldc, splits, mode);
+        return RB_LAUNCH_RESULT();
+    }
+    return 0;
+}
+
+// The error word of the tensor-core kernels (0 = none); synchronises the device.  With reset != 0 it is cleared.
+extern "C" int rb_gemm_error(int reset) {
+    int v = 0;
+    if (cudaMemcpyFromSymbol(&v, g_tc_error, sizeof(int)) != cudaSuccess) return -1;
+    if (reset && v) { int z = 0; cudaMemcpyToSymbol(g_tc_error, &z, sizeof(int)); }
+    return v;
+}

@@ -201,9 +201,37 @@ def sample(logits: torch.Tensor, row_idx: Optional[torch.Tensor], params: torch.
                            c_int(hist_cap), _p(work), _p(out_tokens), c_int(rows), c_int(vocab), _stream()), "sample")
 
 
+_gemm_ws = None
+GEMM_WS_FLOATS = 8 << 20          # 32 MB of split-K partials
+
+
 def fast_gemm_available() -> bool:
-    """True once the tensor-core product is part of the library."""
-    return hasattr(lib(), "rb_gemm_bf16")
+    return True
+
+
+def gemm_bf16(a: torch.Tensor, w: torch.Tensor, c: torch.Tensor, accumulate: bool = False, splits: int = 0) -> None:
+    """c[T,N] (=|+=) a[T,K] @ w[N,K]^T on the tensor cores (tcgen05, TMA); bf16 operands, float
+    accumulation, c bfloat16 or float32.  Operands that TMA cannot address (a row stride that is no
+    multiple of 8 elements, a base that is not 16-byte aligned) go to the plain kernel instead."""
+    global _gemm_ws
+    T, K = a.shape
+    N = w.shape[0]
+    _need(w.shape[1] == K and tuple(c.shape) == (T, N), "gemm: shapes")
+    _need(a.dtype == torch.bfloat16 and w.dtype == torch.bfloat16, "gemm_bf16: bfloat16 operands")
+    _need(a.stride(1) == 1 and w.stride(1) == 1 and c.stride(1) == 1, "gemm: rows contiguous")
+    if a.stride(0) % 8 or w.stride(0) % 8 or a.data_ptr() % 16 or w.data_ptr() % 16:
+        return gemm_ref(a, w, c, accumulate)
+    if _gemm_ws is None or _gemm_ws.device != a.device:
+        _gemm_ws = torch.empty(GEMM_WS_FLOATS, dtype=torch.float32, device=a.device)
+    _check(lib().rb_gemm_bf16(_p(a), _p(w), _p(c), c_int(dt(c)), c_int(int(accumulate)), c_int(T), c_int(N), c_int(K),
+                              c_longlong(a.stride(0)), c_longlong(w.stride(0)), c_longlong(c.stride(0)),
+                              _p(_gemm_ws), c_longlong(_gemm_ws.numel()), c_int(splits), _stream()), "gemm_bf16")
+
+
+def kernel_error(reset: bool = True) -> int:
+    """The error word that a kernel sets when one of its bounded waits gives up (0 = none).
+    Synchronises the device."""
+    return int(lib().rb_gemm_error(c_int(int(reset))))
 
 
 def sample_params_size() -> int:

@@ -1,0 +1,274 @@
+"""Each kernel alone against a plain float32 PyTorch statement of the same operation, at
+sizes other than the engine's (odd widths, partial tiles, partial pages, poisoned slots)."""
+from __future__ import annotations
+
+import math
+
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda"
+
+
+def rnd(*shape, dtype=torch.float32, scale=1.0, seed=0):
+    g = torch.Generator(device="cpu").manual_seed(seed + sum(shape))
+    return (torch.randn(*shape, generator=g) * scale).to(dtype).to(DEV)
+
+
+@pytest.mark.parametrize("T,N,K", [(1, 128, 64), (1, 4096, 4096), (5, 311, 96), (16, 256, 128), (17, 384, 200),
+                                   (33, 130, 72), (64, 1000, 512), (100, 128, 8), (129, 2048, 1024), (300, 520, 264),
+                                   (2048, 1536, 512), (8, 12288, 4096), (7, 4096, 12288)])
+@pytest.mark.parametrize("mode", ["bf16", "f32", "acc"])
+def test_gemm_tensor_core(T, N, K, mode):
+    from reinfer_b200 import ops
+    a, w = rnd(T, K, dtype=torch.bfloat16, seed=1), rnd(N, K, dtype=torch.bfloat16, scale=0.05, seed=2)
+    ref = a.float() @ w.float().t()
+    if mode == "bf16":
+        c = torch.full((T, N), float("nan"), dtype=torch.bfloat16, device=DEV)
+        ops.gemm_bf16(a, w, c)
+        want = ref
+    elif mode == "f32":
+        c = torch.full((T, N), float("nan"), dtype=torch.float32, device=DEV)
+        ops.gemm_bf16(a, w, c)
+        want = ref
+    else:
+        base = rnd(T, N, seed=3)
+        c = base.clone()
+        ops.gemm_bf16(a, w, c, accumulate=True)
+        want = base + ref
+    assert ops.kernel_error() == 0
+    tol = 1e-2 if mode == "bf16" else 2e-5 * math.sqrt(K) + 1e-6
+    err = (c.float() - want).abs().max().item() / max(want.abs().max().item(), 1e-6)
+    assert err <= tol, f"relative error {err:.3e}"
+
+
+@pytest.mark.parametrize("splits", [1, 2, 3, 7])
+def test_gemm_split_k_is_deterministic(splits):
+    from reinfer_b200 import ops
+    a, w = rnd(4, 1000, dtype=torch.bfloat16, seed=5), rnd(200, 1000, dtype=torch.bfloat16, seed=6)
+    c1 = torch.empty(4, 200, dtype=torch.float32, device=DEV)
+    c2 = torch.empty_like(c1)
+    ops.gemm_bf16(a, w, c1, splits=splits)
+    ops.gemm_bf16(a, w, c2, splits=splits)
+    assert torch.equal(c1, c2)
+    ref = a.float() @ w.float().t()
+    assert (c1 - ref).abs().max().item() <= 1e-3 * ref.abs().max().item()
+
+
+@pytest.mark.parametrize("ta,tw,tc", [(torch.float32, torch.float32, torch.float32),
+                                      (torch.bfloat16, torch.float32, torch.bfloat16),
+                                      (torch.float32, torch.bfloat16, torch.float32),
+                                      (torch.bfloat16, torch.bfloat16, torch.float32)])
+@pytest.mark.parametrize("T,N,K", [(1, 7, 5), (65, 130, 33), (70, 64, 257)])
+def test_gemm_plain(ta, tw, tc, T, N, K):
+    from reinfer_b200 import ops
+    a, w = rnd(T, K, dtype=ta, seed=1), rnd(N, K, dtype=tw, seed=2)
+    c = torch.empty(T, N, dtype=tc, device=DEV)
+    ops.gemm_ref(a, w, c)
+    ref = a.double() @ w.double().t()
+    tol = 1e-2 if tc == torch.bfloat16 else 1e-5
+    assert (c.double() - ref).abs().max().item() <= tol * ref.abs().max().item()
+    if tc == torch.float32:
+        base = rnd(T, N, seed=9)
+        c2 = base.clone()
+        ops.gemm_ref(a, w, c2, accumulate=True)
+        assert (c2.double() - (base.double() + ref)).abs().max().item() <= 1e-5 * ref.abs().max().item()
+    # a token's row does not depend on the rest of the batch (same bits alone and in the batch)
+    c1 = torch.empty(1, N, dtype=tc, device=DEV)
+    ops.gemm_ref(a[T // 2:T // 2 + 1], w, c1)
+    assert torch.equal(c1[0], c[T // 2])
+
+
+@pytest.mark.parametrize("h,rows", [(64, 1), (96, 5), (1000, 3), (4096, 2), (5120, 4)])
+@pytest.mark.parametrize("out_dtype,w_dtype", [(torch.float32, torch.float32), (torch.bfloat16, torch.bfloat16),
+                                               (torch.bfloat16, torch.float32)])
+def test_rmsnorm_and_residual(h, rows, out_dtype, w_dtype):
+    from reinfer_b200 import ops
+    eps = 3e-5
+    x, w = rnd(rows, h, scale=3.0, seed=1), (1 + rnd(h, scale=0.1, seed=2)).to(w_dtype)
+
+    def ref(xx):
+        return xx * torch.rsqrt((xx * xx).mean(-1, keepdim=True) + eps) * w.float()
+    out = torch.empty(rows, h, dtype=out_dtype, device=DEV)
+    ops.add_rmsnorm(x, None, w, out, eps)
+    tol = 1e-2 if out_dtype == torch.bfloat16 else 2e-6
+    assert (out.float() - ref(x)).abs().max().item() <= tol * ref(x).abs().max().item()
+    delta = rnd(rows, h, dtype=out_dtype, seed=3)
+    x2 = x.clone()
+    ops.add_rmsnorm(x2, delta, w, out, eps)
+    assert torch.allclose(x2, x + delta.float(), atol=1e-6)
+    assert (out.float() - ref(x + delta.float())).abs().max().item() <= tol * ref(x).abs().max().item()
+    idx = torch.tensor([rows - 1, 0], dtype=torch.int32, device=DEV)
+    out2 = torch.empty(2, h, dtype=out_dtype, device=DEV)
+    ops.add_rmsnorm(x, None, w, out2, eps, row_idx=idx)
+    assert (out2.float() - ref(x)[[rows - 1, 0]]).abs().max().item() <= tol * ref(x).abs().max().item()
+    x3 = x.clone()
+    ops.residual_add(x3, delta)
+    assert torch.allclose(x3, x + delta.float(), atol=1e-6)
+
+
+def test_embedding_gather():
+    from reinfer_b200 import ops
+    for dtype in (torch.float32, torch.bfloat16):
+        table = rnd(77, 50, dtype=dtype)
+        ids = torch.tensor([0, 76, 5, 5, 31], dtype=torch.int32, device=DEV)
+        out = torch.empty(5, 50, dtype=torch.float32, device=DEV)
+        ops.embed_gather(table, ids, out)
+        assert torch.equal(out, table[ids.long()].float())
+
+
+def _rope_ref(x, pos, theta, rot):
+    half = rot // 2
+    p = torch.arange(half, dtype=torch.float64)
+    inv = (torch.tensor(theta, dtype=torch.float64) ** (-(2 * p) / rot)).to(torch.float32).double().to(x.device)
+    ang = pos.double()[:, None] * inv[None, :]
+    c, s = torch.cos(ang)[:, None, :], torch.sin(ang)[:, None, :]
+    a, b = x[..., :half].double(), x[..., half:rot].double()
+    return torch.cat([a * c - b * s, a * s + b * c, x[..., rot:].double()], dim=-1)
+
+
+@pytest.mark.parametrize("QH,KH,d,rot,page", [(4, 2, 16, 16, 16), (6, 2, 32, 32, 8), (3, 1, 80, 48, 4), (8, 8, 128, 128, 16),
+                                              (5, 5, 256, 256, 32)])
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("norm", [True, False])
+def test_qknorm_rope_append(QH, KH, d, rot, page, dtype, norm):
+    from reinfer_b200 import ops
+    from reinfer_b200.parts.rope import RotaryEncoding
+    T, eps, theta, pages = 9, 1e-5, 5e4, 7
+    qkv = rnd(T, (QH + 2 * KH) * d, dtype=dtype, seed=4)
+    qw = (1 + rnd(d, scale=0.1, seed=5)).to(dtype) if norm else None
+    kw = (1 + rnd(d, scale=0.1, seed=6)).to(dtype) if norm else None
+    pos = torch.tensor([0, 1, 2, 40, 41, 1000, 7, 8, 9], dtype=torch.int32, device=DEV)
+    slots = torch.tensor([3, 0, page * pages - 1, 2 * page + 2, -1, page, page + 2, page + 1, 2 * page - 1], dtype=torch.int32, device=DEV)
+    cache = torch.full((pages, 2, KH, page, d), 7.0, dtype=dtype, device=DEV)
+    q_out = torch.empty(T, QH, d, dtype=dtype, device=DEV)
+    rope = RotaryEncoding(d, theta, rot)
+    rope.prepare(DEV)
+    ops.qknorm_rope_append(qkv, qw, kw, rope.inv_freq, pos, slots, q_out, cache, QH, KH, d, rot, page, eps)
+    x = qkv.float().view(T, QH + 2 * KH, d)
+    q, k, v = x[:, :QH], x[:, QH:QH + KH], x[:, QH + KH:]
+    if norm:
+        q = q * torch.rsqrt((q * q).mean(-1, keepdim=True) + eps) * qw.float()
+        k = k * torch.rsqrt((k * k).mean(-1, keepdim=True) + eps) * kw.float()
+    q, k = _rope_ref(q, pos, theta, rot), _rope_ref(k, pos, theta, rot)
+    tol = 2e-2 if dtype == torch.bfloat16 else 2e-5
+    assert (q_out.double() - q).abs().max().item() <= tol * q.abs().max().item()
+    flat = cache.permute(0, 3, 1, 2, 4).reshape(pages * page, 2, KH, d)     # [slot, kv, head, d]
+    untouched = torch.ones(pages * page, dtype=torch.bool)
+    for t in range(T):
+        sl = int(slots[t])
+        if sl < 0:
+            continue
+        untouched[sl] = False
+        assert (flat[sl, 0].double() - k[t]).abs().max().item() <= tol * k.abs().max().item()
+        assert torch.equal(flat[sl, 1], qkv.view(T, QH + 2 * KH, d)[t, QH + KH:])
+    assert bool((flat[untouched.to(DEV)] == 7.0).all())                      # nothing else was written
+
+
+def test_kv_append_and_k_out_path():
+    from reinfer_b200 import ops
+    T, QH, KH, d, page = 5, 4, 2, 32, 8
+    qkv = rnd(T, (QH + 2 * KH) * d, dtype=torch.bfloat16)
+    q_out = torch.empty(T, QH, d, dtype=torch.bfloat16, device=DEV)
+    k_out = torch.empty(T, KH, d, dtype=torch.bfloat16, device=DEV)
+    ops.qknorm_rope_append(qkv, None, None, None, None, None, q_out, None, QH, KH, d, 0, page, 1e-6, k_out=k_out)
+    assert torch.equal(q_out.view(T, -1), qkv[:, :QH * d]) and torch.equal(k_out.view(T, -1), qkv[:, QH * d:(QH + KH) * d])
+    cache = torch.zeros(3, 2, KH, page, d, dtype=torch.bfloat16, device=DEV)
+    slots = torch.tensor([0, 9, 23, -1, 8], dtype=torch.int32, device=DEV)
+    ops.kv_append(k_out.view(T, KH * d), qkv[:, (QH + KH) * d:], slots, cache, KH, d, page)
+    flat = cache.permute(0, 3, 1, 2, 4).reshape(3 * page, 2, KH, d)
+    for t, sl in enumerate(slots.tolist()):
+        if sl >= 0:
+            assert torch.equal(flat[sl, 0], k_out[t]) and torch.equal(flat[sl, 1].reshape(-1), qkv[t, (QH + KH) * d:])
+    assert flat.abs().sum(dim=(1, 2, 3)).ne(0).sum().item() == 4
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_swiglu(dtype):
+    from reinfer_b200 import ops
+    gu = rnd(7, 2 * 150, dtype=dtype, scale=3.0)
+    out = torch.empty(7, 150, dtype=dtype, device=DEV)
+    ops.swiglu(gu, out)
+    g, u = gu[:, :150].float(), gu[:, 150:].float()
+    ref = g / (1 + torch.exp(-g)) * u
+    assert (out.float() - ref).abs().max().item() <= (1e-2 if dtype == torch.bfloat16 else 1e-6) * ref.abs().max().item()
+
+
+def paged_setup(lens, q_lens, QH, KH, d, page, dtype, seed=0, poison=True):
+    """Random requests in a shuffled, sparse pool; unwritten slots hold NaN."""
+    g = torch.Generator().manual_seed(seed)
+    n_pages = sum(-(-n // page) for n in lens) + 5
+    perm = torch.randperm(n_pages, generator=g).tolist()
+    cache = torch.full((n_pages, 2, KH, page, d), float("nan") if poison else 0.0, dtype=dtype)
+    max_pages = max(-(-n // page) for n in lens) + 1
+    bt = torch.full((len(lens), max_pages), -1, dtype=torch.int32)
+    ks, vs = [], []
+    for r, n in enumerate(lens):
+        k, v = torch.randn(n, KH, d, generator=g).to(dtype), torch.randn(n, KH, d, generator=g).to(dtype)
+        ks.append(k); vs.append(v)
+        for i in range(-(-n // page)):
+            pg = perm.pop()
+            bt[r, i] = pg
+            m = min(page, n - i * page)
+            cache[pg, 0, :, :m] = k[i * page:i * page + m].transpose(0, 1)
+            cache[pg, 1, :, :m] = v[i * page:i * page + m].transpose(0, 1)
+    tok_row, positions = [], []
+    for r, (n, ql) in enumerate(zip(lens, q_lens)):
+        tok_row += [r] * ql
+        positions += list(range(n - ql, n))
+    T = len(tok_row)
+    q = torch.randn(T, QH, d, generator=g).to(dtype)
+    return dict(q=q.to(DEV), cache=cache.to(DEV), bt=bt.to(DEV), tok_row=torch.tensor(tok_row, dtype=torch.int32, device=DEV),
+                positions=torch.tensor(positions, dtype=torch.int32, device=DEV), ks=ks, vs=vs, rows=tok_row, pos=positions)
+
+
+def attention_truth(s, QH, KH, window, scale):
+    out = torch.zeros(s["q"].shape, dtype=torch.float64)
+    q = s["q"].double().cpu()
+    for t, (r, p) in enumerate(zip(s["rows"], s["pos"])):
+        lo = max(0, p - window + 1) if window > 0 else 0
+        k, v = s["ks"][r][lo:p + 1].double(), s["vs"][r][lo:p + 1].double()
+        for h in range(QH):
+            kh = h // (QH // KH)
+            pr = torch.softmax((k[:, kh] @ q[t, h]) * scale, 0)
+            out[t, h] = pr @ v[:, kh]
+    return out
+
+
+@pytest.mark.parametrize("QH,KH,d,page", [(4, 2, 16, 16), (6, 2, 32, 8), (14, 2, 64, 4), (5, 5, 80, 32), (8, 1, 128, 16)])
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("window", [0, 13])
+def test_paged_attention_plain(QH, KH, d, page, dtype, window):
+    from reinfer_b200 import ops
+    lens, q_lens = [1, 37, 64, 131], [1, 5, 1, 131]
+    s = paged_setup(lens, q_lens, QH, KH, d, page, dtype)
+    out = torch.empty_like(s["q"])
+    scale = 0.7 / math.sqrt(d)
+    ops.paged_attention_ref(s["q"], s["cache"], s["bt"], s["tok_row"], s["positions"], out, QH, KH, d, page, window, scale)
+    ref = attention_truth(s, QH, KH, window, scale)
+    assert not torch.isnan(out).any()
+    tol = 1.5e-2 if dtype == torch.bfloat16 else 1e-5
+    assert (out.double().cpu() - ref).abs().max().item() <= tol * ref.abs().max().item()
+
+
+def test_attention_finds_one_far_key():
+    """One key among hundreds gets a score that stands out; the output must be its value."""
+    from reinfer_b200 import ops
+    QH, KH, d, page = 4, 2, 32, 8
+    s = paged_setup([700], [1], QH, KH, d, page, torch.float32, seed=3)
+    far = 5
+    pg, off = int(s["bt"][0, far // page]), far % page
+    s["q"][0, :, :] = 0.0
+    s["q"][0, :, 0] = 50.0
+    s["cache"][pg, 0, :, off, 0] = 50.0
+    out = torch.empty_like(s["q"])
+    ops.paged_attention_ref(s["q"], s["cache"], s["bt"], s["tok_row"], s["positions"], out, QH, KH, d, page, 0, 1.0)
+    want = s["cache"][pg, 1, :, off]                                   # [KH, d]
+    for h in range(QH):
+        assert torch.allclose(out[0, h], want[h // 2], atol=1e-4)
+    # with a window that ends before the far key it must NOT be seen
+    ops.paged_attention_ref(s["q"], s["cache"], s["bt"], s["tok_row"], s["positions"], out, QH, KH, d, page, 699 - far, 1.0)
+    assert not torch.allclose(out[0, 0], want[0], atol=1e-2)
+    ops.paged_attention_ref(s["q"], s["cache"], s["bt"], s["tok_row"], s["positions"], out, QH, KH, d, page, 700 - far, 1.0)
+    assert torch.allclose(out[0, 0], want[0], atol=1e-4)
