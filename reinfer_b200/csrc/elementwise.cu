@@ -161,7 +161,7 @@ __global__ void qknorm_rope_append_kernel(const TA* __restrict__ qkv, const TW* 
         rstd = 1.0f / sqrtf(ss / (float)d + eps);
     }
     const int half = rot >> 1;
-    const float pos = (float)positions[t];
+    const float pos = positions ? (float)positions[t] : 0.0f;   // no rotation: no positions
     TA* qdst = is_q ? q_out + ((size_t)t * QH + hh) * d : nullptr;
     TC* kdst = nullptr;
     TA* kdst_a = (!is_q && k_out) ? k_out + ((size_t)t * KH + (hh - QH)) * d : nullptr;
