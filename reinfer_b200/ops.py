@@ -182,12 +182,65 @@ def paged_attention_ref(q: torch.Tensor, cache: torch.Tensor, block_table: torch
            "paged_attention_ref")
 
 
+def fa_group_chunk(group: int) -> int:
+    """Query heads of one kv head that share a row tile: the largest divisor of the group up to 16."""
+    for c in range(16, 0, -1):
+        if group % c == 0:
+            return c
+    return 1
+
+
+def fa_decode(q, cache, block_table, cu_q, kv_len, out, first_entry: int, n_entries: int, first_tok: int, n_splits: int,
+              QH: int, KH: int, d: int, page_size: int, window: int, scale: float) -> None:
+    """Split-K flash decoding (tensor cores) for entries that bring one token each."""
+    part_o = part_lse = None
+    if n_splits > 1:
+        part_o = torch.empty(n_entries * QH * n_splits * d, dtype=torch.float32, device=q.device)
+        part_lse = torch.empty(n_entries * QH * n_splits, dtype=torch.float32, device=q.device)
+    _check(lib().rb_fa_decode(_p(q), _p(cache), _p(block_table), _p(cu_q), _p(kv_len), _p(out), _p(part_o), _p(part_lse),
+                              c_int(first_entry), c_int(n_entries), c_int(first_tok), c_int(n_splits), c_int(QH), c_int(KH),
+                              c_int(d), c_int(page_size), c_int(block_table.shape[1]), c_int(window), c_float(scale),
+                              _stream()), "fa_decode")
+    if n_splits > 1:
+        global launches
+        launches += 1                      # the merge kernel
+
+
+def fa_prefill(q, cache, block_table, cu_q, kv_len, out, first_entry: int, n_entries: int, n_tiles: int,
+               QH: int, KH: int, d: int, page_size: int, window: int, scale: float) -> None:
+    """Paged causal flash attention (tensor cores) for entries that bring several tokens."""
+    _check(lib().rb_fa_prefill(_p(q), _p(cache), _p(block_table), _p(cu_q), _p(kv_len), _p(out), c_int(first_entry),
+                               c_int(n_entries), c_int(n_tiles), c_int(QH), c_int(KH), c_int(d), c_int(page_size),
+                               c_int(block_table.shape[1]), c_int(window), c_float(scale), _stream()), "fa_prefill")
+
+
+FA_TARGET_CTAS = 296                       # two CTAs for each of the 148 SMs
+
+
 def attention(ctx, q: torch.Tensor, cache: torch.Tensor, group, out: torch.Tensor, QH: int, KH: int, d: int,
               window: int, scale: float) -> None:
-    """Attention of a step's tokens over their requests' pages; picks the kernel by dtype and
-    by what the batch holds.  float32 always runs the plain kernel."""
-    paged_attention_ref(q, cache, group.block_table, ctx.tok_entry, ctx.positions, out, QH, KH, d,
-                        group.page_size, window, scale)
+    """Attention of a step's tokens over their requests' pages.  float32 (and head sizes the
+    tensor-core kernels do not take) runs the plain kernel; bfloat16 runs flash decoding for the
+    entries with one token and the paged flash prefill kernel for the others."""
+    if q.dtype != torch.bfloat16 or d % 8 or d > 256:
+        paged_attention_ref(q, cache, group.block_table, ctx.tok_entry, ctx.positions, out, QH, KH, d,
+                            group.page_size, window, scale)
+        return
+    _need(q.is_contiguous() and out.is_contiguous() and cache.is_contiguous() and group.block_table.is_contiguous(),
+          "attention: contiguous")
+    n_dec, E = ctx.n_decode, ctx.n_entries
+    gc = fa_group_chunk(QH // KH)
+    if n_dec:
+        ctas = n_dec * KH * (QH // KH // gc)
+        tiles = -(-ctx.max_kv_len // 64)
+        n_splits = max(1, min(-(-FA_TARGET_CTAS // ctas), tiles, 64))
+        fa_decode(q, cache, group.block_table, ctx.cu_q, ctx.kv_len, out, 0, n_dec, 0, n_splits, QH, KH, d,
+                  group.page_size, window, scale)
+    if E > n_dec:
+        tpt = 64 // gc
+        n_tiles = sum(-(-(ctx.q_start[e + 1] - ctx.q_start[e]) // tpt) for e in range(n_dec, E))
+        fa_prefill(q, cache, group.block_table, ctx.cu_q, ctx.kv_len, out, n_dec, E - n_dec, n_tiles, QH, KH, d,
+                   group.page_size, window, scale)
 
 
 def sample(logits: torch.Tensor, row_idx: Optional[torch.Tensor], params: torch.Tensor, history: Optional[torch.Tensor],

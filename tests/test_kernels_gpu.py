@@ -272,3 +272,51 @@ def test_attention_finds_one_far_key():
     assert not torch.allclose(out[0, 0], want[0], atol=1e-2)
     ops.paged_attention_ref(s["q"], s["cache"], s["bt"], s["tok_row"], s["positions"], out, QH, KH, d, page, 700 - far, 1.0)
     assert torch.allclose(out[0, 0], want[0], atol=1e-4)
+
+
+@pytest.mark.parametrize("QH,KH,d,page", [(4, 2, 16, 16), (6, 2, 32, 8), (14, 2, 64, 4), (5, 5, 80, 32), (8, 1, 128, 16),
+                                          (32, 8, 128, 16), (32, 1, 64, 16), (3, 1, 256, 64), (6, 3, 24, 8)])
+@pytest.mark.parametrize("window", [0, 37])
+def test_flash_prefill_and_decode_against_plain(QH, KH, d, page, window):
+    """The tensor-core kernels on a batch that mixes decode entries and prompt portions which
+    continue from cached pages; shuffled pages, partial last pages, NaN in every unwritten slot."""
+    from reinfer_b200 import ops
+    lens = [1, 37, 64, 300, 5, 131, 1000]
+    q_lens = [1, 1, 1, 1, 5, 70, 130]
+    s = paged_setup(lens, q_lens, QH, KH, d, page, torch.bfloat16, seed=11)
+    scale = 0.9 / math.sqrt(d)
+    ref = attention_truth(s, QH, KH, window, scale)
+    cu = [0]
+    for n in q_lens:
+        cu.append(cu[-1] + n)
+    cu_q = torch.tensor(cu, dtype=torch.int32, device=DEV)
+    kv_len = torch.tensor(lens, dtype=torch.int32, device=DEV)
+    gc = ops.fa_group_chunk(QH // KH)
+    for n_splits in (1, 3, 8):
+        out = torch.full_like(s["q"], float("nan"))
+        ops.fa_decode(s["q"], s["cache"], s["bt"], cu_q, kv_len, out, 0, 4, 0, n_splits, QH, KH, d, page, window, scale)
+        tpt = 64 // gc
+        n_tiles = sum(-(-n // tpt) for n in q_lens[4:])
+        ops.fa_prefill(s["q"], s["cache"], s["bt"], cu_q, kv_len, out, 4, 3, n_tiles, QH, KH, d, page, window, scale)
+        assert not torch.isnan(out.float()).any()
+        err = (out.double().cpu() - ref).abs().max().item() / ref.abs().max().item()
+        assert err <= 1.5e-2, f"splits {n_splits}: error {err:.3e}"
+
+
+def test_flash_decode_finds_one_far_key_across_splits():
+    from reinfer_b200 import ops
+    QH, KH, d, page = 8, 2, 64, 16
+    s = paged_setup([3000], [1], QH, KH, d, page, torch.bfloat16, seed=5)
+    cu_q = torch.tensor([0, 1], dtype=torch.int32, device=DEV)
+    kv_len = torch.tensor([3000], dtype=torch.int32, device=DEV)
+    for far in (0, 63, 64, 1537, 2999):
+        q, cache = s["q"].clone(), s["cache"].clone()
+        pg, off = int(s["bt"][0, far // page]), far % page
+        q[0] = 0.0; q[0, :, 3] = 40.0
+        cache[pg, 0, :, off, 3] = 40.0
+        for n_splits in (1, 5, 47):
+            out = torch.empty_like(q)
+            ops.fa_decode(q, cache, s["bt"], cu_q, kv_len, out, 0, 1, 0, n_splits, QH, KH, d, page, 0, 1.0)
+            want = cache[pg, 1, :, off].float()
+            for h in range(QH):
+                assert torch.allclose(out[0, h].float(), want[h // 4], atol=2e-2), (far, n_splits, h)
