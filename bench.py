@@ -168,9 +168,11 @@ def main() -> int:
     # ---- decode ---------------------------------------------------------------------------
     def decode_run(B, steps, warmup, through_llm):
         """Fill B requests to ctx_len - steps - warmup tokens, then time `steps` decode steps."""
-        start_len = max(ctx_len - steps - warmup - 1, 1)
+        # requests admitted first decode a little while the others still run their prompts; leave room
+        # so that every request is still alive, and below `context`, when the timed steps end
+        start_len = max(ctx_len - steps - warmup - 3 * B - 2, 1)
         llm = LLM(engine=engine, max_batch_tokens=2048, seed=0)
-        sp = SamplingParams(temperature=0.0, max_tokens=steps + warmup + 1, ignore_eos=True)
+        sp = SamplingParams(temperature=0.0, max_tokens=1 << 20, ignore_eos=True)
         for b in range(B):
             llm.add_request(torch.randint(0, V, (start_len,), generator=gen).tolist(), sp)
         while any(r.in_prefill for r in llm.scheduler.running) or llm.scheduler.waiting:
@@ -189,20 +191,27 @@ def main() -> int:
         wall = time.perf_counter() - w0
         dev_ms = e0.elapsed_time(e1)
         n_l = ops.launches - l0
+        assert len(llm.scheduler.running) == B and not llm.scheduler.waiting
+        kv_tokens = sum(engine.cache.length(r.request_id) for r in llm.scheduler.running) - B * steps // 2
+        graph_nodes = 0
+        for (bk, _w), g in engine._graphs.items():
+            if bk >= B:
+                graph_nodes = max(graph_nodes, g.n_launches)
+        n_l += graph_nodes * steps                      # kernels inside the replayed graph, counted at capture
         for r in list(llm.scheduler.running):
             llm.abort(r.request_id)
-        return dev_ms / steps, wall / steps * 1e3, n_l
+        return dev_ms / steps, wall / steps * 1e3, n_l, kv_tokens
 
     clocks = ClockSampler()
     clocks.start()
-    ms_dev, ms_wall, n_launch = decode_run(a.batch, a.steps, a.warmup, True)
+    ms_dev, ms_wall, n_launch, kv_tokens = decode_run(a.batch, a.steps, a.warmup, True)
     clk = clocks.finish()
-    kv_read = a.batch * (ctx_len - a.steps // 2) * kv_bytes_tok
+    kv_read = kv_tokens * kv_bytes_tok                   # tokens the live requests hold, mid-run
     achieved = (wbytes + kv_read) / (ms_dev * 1e-3) / 1e9
     points = {}
     if not a.no_points:
         for B in (1, 64):
-            m, _, _ = decode_run(B, max(8, a.steps // 4), 3, True)
+            m, _, _, _ = decode_run(B, max(8, a.steps // 4), 3, True)
             points[f"decode_b{B}"] = B / m * 1e3
     value = a.batch / ms_dev * 1e3
     out = {

@@ -36,6 +36,7 @@ struct FaArgs {
     float* part_o;                     // decode: [tokens, QH, splits, d] normalised partial outputs
     float* part_lse;                   // decode: [tokens, QH, splits] log2 of the partial softmax sums
     int QH, KH, d, page_size, max_pages, window;
+    int page_shift;                    // log2(page_size), or -1 if it is no power of two
     int Gc, chunks;                    // query heads per row tile (divides QH/KH, <= 16), tiles per kv head
     int first_entry, n_entries;        // entries this launch covers: [first_entry, first_entry + n_entries)
     int n_splits;
@@ -79,26 +80,35 @@ template <int D> struct FaSmem {
 // Copy keys [k0, k0+64) of kv head `kh` (K and V) of the request whose block-table row is `bt`
 // into one stage.  Rows at or beyond `kv_end`, rows in pages that were given back (id < 0) and
 // the padding dims d..D are zero-filled, so nothing that is not the request's own data is read.
+// A thread always copies the same 16-byte column of rows r0, r0 + RPI, ...; with a page size that
+// is a power of two (page_shift >= 0) the page of a row costs a shift and a mask.
 template <int D>
 __device__ __forceinline__ void fa_load_tile(unsigned char* stage, const FaArgs& a, const int* bt, int kh, int k0, int kv_end) {
     constexpr int CPR = D / 8;                                // 16-byte chunks per row
+    constexpr int RPI = FA_THREADS / CPR;                     // rows per pass over the tile
+    static_assert(FA_THREADS % CPR == 0 && FA_BN % RPI == 0, "tile shape");
+    const int c = threadIdx.x % CPR, r0 = threadIdx.x / CPR;
+    const bool col_ok = c * 8 < a.d;
     const size_t head_stride = (size_t)a.page_size * a.d;
-    for (int i = threadIdx.x; i < FA_BN * CPR; i += FA_THREADS) {
-        const int row = i / CPR, c = i % CPR;
-        const int key = k0 + row;
+    const size_t page_stride = 2 * (size_t)a.KH * head_stride;
+    const bf16* base = a.cache + (size_t)kh * head_stride + c * 8;
+    const size_t v_off = (size_t)a.KH * head_stride;
+    unsigned char* dst0 = stage + r0 * FaSmem<D>::STRIDE + c * 16;
+#pragma unroll
+    for (int i = 0; i < FA_BN / RPI; ++i) {
+        const int key = k0 + r0 + i * RPI;
         const bf16* src = a.cache;
         int bytes = 0;
-        if (key < kv_end && c * 8 < a.d) {
-            const int pi = key / a.page_size;
+        if (col_ok && key < kv_end) {
+            int pi, off;
+            if (a.page_shift >= 0) { pi = key >> a.page_shift; off = key & (a.page_size - 1); }
+            else { pi = key / a.page_size; off = key - pi * a.page_size; }
             const int page = pi < a.max_pages ? bt[pi] : -1;
-            if (page >= 0) {
-                src = a.cache + ((size_t)page * 2 * a.KH + kh) * head_stride + (size_t)(key % a.page_size) * a.d + c * 8;
-                bytes = 16;
-            }
+            if (page >= 0) { src = base + (size_t)page * page_stride + (size_t)off * a.d; bytes = 16; }
         }
-        unsigned char* dst = stage + row * FaSmem<D>::STRIDE + c * 16;
+        unsigned char* dst = dst0 + i * RPI * FaSmem<D>::STRIDE;
         cp_async16(dst, src, bytes);
-        cp_async16(dst + FaSmem<D>::TILE, bytes ? src + (size_t)a.KH * head_stride : src, bytes);
+        cp_async16(dst + FaSmem<D>::TILE, bytes ? src + v_off : src, bytes);
     }
 }
 
@@ -192,6 +202,7 @@ __global__ void __launch_bounds__(FA_THREADS)
 fa_prefill_kernel(const FaArgs a) {
     constexpr int NST = 2;
     extern __shared__ __align__(16) unsigned char smem[];
+    pdl_trigger(); pdl_wait();
     unsigned char* sQ = smem;
     unsigned char* stages = smem + FA_BM * FaSmem<D>::STRIDE;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -271,6 +282,7 @@ template <int D, int NST>
 __global__ void __launch_bounds__(FA_THREADS)
 fa_decode_kernel(const FaArgs a) {
     extern __shared__ __align__(16) unsigned char smem[];
+    pdl_trigger(); pdl_wait();
     unsigned char* sQ = smem;                                  // 16 rows
     unsigned char* stages = smem + 16 * FaSmem<D>::STRIDE;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -360,6 +372,7 @@ fa_decode_kernel(const FaArgs a) {
 // out[t, h, :] = sum_s w_s o_s / sum_s w_s,  w_s = 2^(lse_s - max lse), splits in ascending order
 __global__ void fa_merge_kernel(const float* __restrict__ part_o, const float* __restrict__ part_lse, bf16* __restrict__ out,
                                 int first_tok, int QH, int d, int n_splits) {
+    pdl_trigger(); pdl_wait();
     const int t = blockIdx.x, h = blockIdx.y;
     const size_t base = ((size_t)t * QH + h) * n_splits;
     float M = -INFINITY;
@@ -378,6 +391,10 @@ __global__ void fa_merge_kernel(const float* __restrict__ part_o, const float* _
 }
 
 // --------------------------------------------------------------------- host side
+static int fa_shift(int n) {
+    for (int s = 0; s < 31; ++s) if ((1 << s) == n) return s;
+    return -1;
+}
 static int fa_group_chunk(int G) {                             // largest divisor of G that is <= 16
     for (int c = 16; c >= 1; --c) if (G % c == 0) return c;
     return 1;
@@ -392,9 +409,7 @@ static int fa_launch_prefill(const FaArgs& a, int n_tiles, cudaStream_t s) {
         if (e != cudaSuccess) return (int)e;
         done = true;
     }
-    dim3 grid(n_tiles, a.KH * a.chunks);
-    fa_prefill_kernel<D><<<grid, FA_THREADS, smem, s>>>(a);
-    return RB_LAUNCH_RESULT();
+    return rb_launch(fa_prefill_kernel<D>, dim3(n_tiles, a.KH * a.chunks), dim3(FA_THREADS), smem, s, a);
 }
 template <int D, int NST>
 static int fa_launch_decode(const FaArgs& a, cudaStream_t s) {
@@ -407,9 +422,7 @@ static int fa_launch_decode(const FaArgs& a, cudaStream_t s) {
         if (e != cudaSuccess) return (int)e;
         done = true;
     }
-    dim3 grid(a.n_entries, a.KH * a.chunks, a.n_splits);
-    fa_decode_kernel<D, NST><<<grid, FA_THREADS, smem, s>>>(a);
-    return RB_LAUNCH_RESULT();
+    return rb_launch(fa_decode_kernel<D, NST>, dim3(a.n_entries, a.KH * a.chunks, a.n_splits), dim3(FA_THREADS), smem, s, a);
 }
 
 static int fa_check(int QH, int KH, int d, int page_size, int max_pages) {
@@ -430,7 +443,7 @@ extern "C" int rb_fa_prefill(const void* q, const void* cache, const int* block_
     if (fa_check(QH, KH, d, page_size, max_pages)) return -1;
     FaArgs a{};
     a.q = (const bf16*)q; a.cache = (const bf16*)cache; a.block_table = block_table; a.cu_q = cu_q; a.kv_len = kv_len;
-    a.out = (bf16*)out; a.QH = QH; a.KH = KH; a.d = d; a.page_size = page_size; a.max_pages = max_pages; a.window = window;
+    a.out = (bf16*)out; a.QH = QH; a.KH = KH; a.d = d; a.page_size = page_size; a.page_shift = fa_shift(page_size); a.max_pages = max_pages; a.window = window;
     a.Gc = fa_group_chunk(QH / KH); a.chunks = (QH / KH) / a.Gc; a.first_entry = first_entry; a.n_entries = n_entries;
     a.n_splits = 1; a.scale_log2 = scale * 1.4426950408889634f;
     cudaStream_t s = (cudaStream_t)stream;
@@ -453,7 +466,7 @@ extern "C" int rb_fa_decode(const void* q, const void* cache, const int* block_t
     FaArgs a{};
     a.q = (const bf16*)q; a.cache = (const bf16*)cache; a.block_table = block_table; a.cu_q = cu_q; a.kv_len = kv_len;
     a.out = (bf16*)out; a.part_o = part_o; a.part_lse = part_lse;
-    a.QH = QH; a.KH = KH; a.d = d; a.page_size = page_size; a.max_pages = max_pages; a.window = window;
+    a.QH = QH; a.KH = KH; a.d = d; a.page_size = page_size; a.page_shift = fa_shift(page_size); a.max_pages = max_pages; a.window = window;
     a.Gc = fa_group_chunk(QH / KH); a.chunks = (QH / KH) / a.Gc; a.first_entry = first_entry; a.n_entries = n_entries;
     a.n_splits = n_splits; a.scale_log2 = scale * 1.4426950408889634f;
     cudaStream_t s = (cudaStream_t)stream;
@@ -463,7 +476,6 @@ extern "C" int rb_fa_decode(const void* q, const void* cache, const int* block_t
     else if (d <= 128) rc = fa_launch_decode<128, 3>(a, s);
     else rc = fa_launch_decode<256, 2>(a, s);
     if (rc || n_splits == 1) return rc;
-    dim3 grid(n_entries, QH);
-    fa_merge_kernel<<<grid, 128, 0, s>>>(part_o, part_lse, (bf16*)out, first_tok, QH, d, n_splits);
-    return RB_LAUNCH_RESULT();
+    return rb_launch(fa_merge_kernel, dim3(n_entries, QH), dim3(128), 0, s, (const float*)part_o, (const float*)part_lse,
+                     (bf16*)out, first_tok, QH, d, n_splits);
 }

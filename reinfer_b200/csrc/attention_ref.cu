@@ -48,18 +48,21 @@ paged_attention_ref_kernel(const TA* __restrict__ q, const TC* __restrict__ cach
 
     for (int b0 = (lo / 32) * 32; b0 <= pos; b0 += 32) {
         const int key = b0 + lane;
-        const bool valid = key >= lo && key <= pos;
+        bool valid = key >= lo && key <= pos;
         float s = -INFINITY;
         const TC* vrow = nullptr;
+        const int page = (valid && key / page_size < max_pages) ? bt[key / page_size] : -1;
+        valid = valid && page >= 0;                            // a page that is not held: an inert padding row
         if (valid) {
-            const int page = bt[key / page_size], off = key % page_size;
+            const int off = key % page_size;
             const TC* krow = cache + (size_t)page * page_stride + (size_t)kh * head_stride + (size_t)off * d;
             vrow = krow + (size_t)KH * head_stride;
             float dot = 0.0f;
             for (int i = 0; i < d; ++i) dot = fmaf(qs[i], to_f32(krow[i]), dot);
             s = dot * scale;
         }
-        const float bm = warp_max(s);                          // finite: key b0.. includes >= 1 valid key
+        const float bm = warp_max(s);
+        if (bm == -INFINITY) continue;                         // no key in this block (warp-uniform)
         const float m_new = fmaxf(m, bm);
         const float corr = expf(m - m_new);                    // first block: exp(-inf) = 0
         const float p = valid ? expf(s - m_new) : 0.0f;

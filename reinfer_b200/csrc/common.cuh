@@ -60,7 +60,30 @@ __device__ __forceinline__ float block_max(float v, float* red) {
     return r;
 }
 
+// Programmatic dependent launch.  A kernel launched through rb_launch() may begin while its
+// predecessor in the stream is still running; it must call pdl_wait() before it touches any
+// memory that a predecessor writes or reads.  pdl_trigger() lets the successor begin.  Both are
+// no-ops for a kernel launched the ordinary way.
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void pdl_trigger() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+
 // ---- host side -----------------------------------------------------------
+extern int g_rb_pdl;                      // 1: rb_launch() asks for programmatic stream serialization
+
+template <typename... KArgs, typename... Args>
+static inline int rb_launch(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t s, Args&&... args) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid; cfg.blockDim = block; cfg.dynamicSmemBytes = smem; cfg.stream = s;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = g_rb_pdl ? 1 : 0;
+    cudaError_t e = cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);
+    if (e != cudaSuccess) { (void)cudaGetLastError(); return (int)e; }
+    return (int)cudaGetLastError();
+}
+
 void rb_set_error(const char* fmt, ...);
 #define RB_REFUSE(...) do { rb_set_error(__VA_ARGS__); return -1; } while (0)
 #define RB_LAUNCH_RESULT() ((int)cudaGetLastError())

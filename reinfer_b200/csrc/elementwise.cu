@@ -9,6 +9,7 @@
 template <typename TW>
 __global__ void embed_gather_kernel(const TW* __restrict__ table, const int* __restrict__ ids,
                                     float* __restrict__ out, int h, int vocab) {
+    pdl_trigger(); pdl_wait();
     const int t = blockIdx.x;
     int id = ids[t];
     const bool ok = (id >= 0 && id < vocab);          // the host refuses such ids before launching
@@ -24,11 +25,10 @@ extern "C" int rb_embed_gather(const void* table, int table_dtype, const int* id
     cudaStream_t s = (cudaStream_t)stream;
     const int threads = h >= 1024 ? 256 : 128;
     if (table_dtype == RB_F32)
-        embed_gather_kernel<float><<<n_tokens, threads, 0, s>>>((const float*)table, ids, out, h, vocab);
-    else if (table_dtype == RB_BF16)
-        embed_gather_kernel<bf16><<<n_tokens, threads, 0, s>>>((const bf16*)table, ids, out, h, vocab);
-    else RB_REFUSE("embed_gather: table dtype %d", table_dtype);
-    return RB_LAUNCH_RESULT();
+        return rb_launch(embed_gather_kernel<float>, dim3(n_tokens), dim3(threads), 0, s, (const float*)table, ids, out, h, vocab);
+    if (table_dtype == RB_BF16)
+        return rb_launch(embed_gather_kernel<bf16>, dim3(n_tokens), dim3(threads), 0, s, (const bf16*)table, ids, out, h, vocab);
+    RB_REFUSE("embed_gather: table dtype %d", table_dtype);
 }
 
 // ------------------------------------------------------------------ RMSNorm
@@ -38,45 +38,70 @@ extern "C" int rb_embed_gather(const void* table, int table_dtype, const int* id
 // logits are wanted); a residual sum is not combined with row_idx.
 // One block per row; each thread sums its strided elements in ascending order and the
 // block tree is fixed, so a row's result does not depend on the other rows.
-template <typename TD, typename TW, typename TO>
+template <typename TD, typename TW, typename TO, int PER>
 __global__ void add_rmsnorm_kernel(float* __restrict__ x, const TD* __restrict__ delta,
                                    const TW* __restrict__ w, TO* __restrict__ out,
                                    const int* __restrict__ row_idx, int h, float eps) {
     __shared__ float red[32];
+    pdl_trigger(); pdl_wait();
     const int r = blockIdx.x;
     const size_t in_row = row_idx ? (size_t)row_idx[r] : (size_t)r;
     float* xr = x + in_row * h;
+    // each thread keeps its strided elements in registers (PER of them; PER == 0: rows too wide, re-read)
+    float v[PER > 0 ? PER : 1];
     float ss = 0.0f;
-    if (delta) {
-        const TD* dr = delta + in_row * h;
-        for (int i = threadIdx.x; i < h; i += blockDim.x) {
-            float v = xr[i] + to_f32(dr[i]);
-            xr[i] = v;
-            ss += v * v;
+    if (PER > 0) {
+#pragma unroll
+        for (int k = 0; k < PER; ++k) {
+            const int i = threadIdx.x + k * blockDim.x;
+            float t = 0.0f;
+            if (i < h) {
+                t = xr[i];
+                if (delta) { t += to_f32(delta[in_row * h + i]); xr[i] = t; }
+            }
+            v[k] = t;
+            ss += t * t;
         }
     } else {
         for (int i = threadIdx.x; i < h; i += blockDim.x) {
-            float v = xr[i];
-            ss += v * v;
+            float t = xr[i];
+            if (delta) { t += to_f32(delta[in_row * h + i]); xr[i] = t; }
+            ss += t * t;
         }
     }
     const float total = block_sum(ss, red);
     const float rstd = 1.0f / sqrtf(total / (float)h + eps);
     TO* orow = out + (size_t)r * h;
-    for (int i = threadIdx.x; i < h; i += blockDim.x)
-        orow[i] = from_f32<TO>(xr[i] * rstd * to_f32(w[i]));
+    if (PER > 0) {
+#pragma unroll
+        for (int k = 0; k < PER; ++k) {
+            const int i = threadIdx.x + k * blockDim.x;
+            if (i < h) orow[i] = from_f32<TO>(v[k] * rstd * to_f32(w[i]));
+        }
+    } else {
+        for (int i = threadIdx.x; i < h; i += blockDim.x)
+            orow[i] = from_f32<TO>(xr[i] * rstd * to_f32(w[i]));
+    }
+}
+
+template <typename TD, typename TW, typename TO>
+static int launch_add_rmsnorm_k(float* x, const TD* delta, const TW* w, TO* out, const int* row_idx, int rows, int h,
+                                float eps, cudaStream_t s) {
+    // the summation order (thread stride, then the block tree) depends on h only, never on the batch
+    if (h <= 512) return rb_launch(add_rmsnorm_kernel<TD, TW, TO, 4>, dim3(rows), dim3(128), 0, s, x, delta, w, out, row_idx, h, eps);
+    if (h <= 2048) return rb_launch(add_rmsnorm_kernel<TD, TW, TO, 8>, dim3(rows), dim3(256), 0, s, x, delta, w, out, row_idx, h, eps);
+    if (h <= 8192) return rb_launch(add_rmsnorm_kernel<TD, TW, TO, 8>, dim3(rows), dim3(1024), 0, s, x, delta, w, out, row_idx, h, eps);
+    return rb_launch(add_rmsnorm_kernel<TD, TW, TO, 0>, dim3(rows), dim3(1024), 0, s, x, delta, w, out, row_idx, h, eps);
 }
 
 template <typename TD, typename TW>
 static int launch_add_rmsnorm_o(float* x, const void* delta, const void* w, void* out, int out_dtype,
                                 const int* row_idx, int rows, int h, float eps, cudaStream_t s) {
-    const int threads = h >= 2048 ? 512 : (h >= 512 ? 256 : 128);
     if (out_dtype == RB_F32)
-        add_rmsnorm_kernel<TD, TW, float><<<rows, threads, 0, s>>>(x, (const TD*)delta, (const TW*)w, (float*)out, row_idx, h, eps);
-    else if (out_dtype == RB_BF16)
-        add_rmsnorm_kernel<TD, TW, bf16><<<rows, threads, 0, s>>>(x, (const TD*)delta, (const TW*)w, (bf16*)out, row_idx, h, eps);
-    else RB_REFUSE("rmsnorm: out dtype %d", out_dtype);
-    return RB_LAUNCH_RESULT();
+        return launch_add_rmsnorm_k<TD, TW, float>(x, (const TD*)delta, (const TW*)w, (float*)out, row_idx, rows, h, eps, s);
+    if (out_dtype == RB_BF16)
+        return launch_add_rmsnorm_k<TD, TW, bf16>(x, (const TD*)delta, (const TW*)w, (bf16*)out, row_idx, rows, h, eps, s);
+    RB_REFUSE("rmsnorm: out dtype %d", out_dtype);
 }
 
 extern "C" int rb_add_rmsnorm(float* x, const void* delta, int delta_dtype, const void* w, int w_dtype,
@@ -97,6 +122,7 @@ extern "C" int rb_add_rmsnorm(float* x, const void* delta, int delta_dtype, cons
 // x[r,:] += delta[r,:]  (the last residual sum of a layer when nothing follows to fuse it into)
 template <typename TD>
 __global__ void residual_add_kernel(float* __restrict__ x, const TD* __restrict__ delta, size_t n) {
+    pdl_trigger(); pdl_wait();
     size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
     if (i < n) x[i] += to_f32(delta[i]);
 }
@@ -132,6 +158,7 @@ __global__ void qknorm_rope_append_kernel(const TA* __restrict__ qkv, const TW* 
                                           TA* __restrict__ q_out, TA* __restrict__ k_out,
                                           TC* __restrict__ cache, int n_tokens, int QH, int KH, int d, int rot, int page_size,
                                           float eps) {
+    pdl_trigger(); pdl_wait();
     const int heads = QH + 2 * KH;
     const long long wglobal = ((long long)blockIdx.x * blockDim.x + threadIdx.x) >> 5;
     const int lane = threadIdx.x & 31;
@@ -204,16 +231,15 @@ extern "C" int rb_qknorm_rope_append(const void* qkv, int act_dtype, const void*
     cudaStream_t s = (cudaStream_t)stream;
     const long long warps = (long long)n_tokens * (QH + 2 * KH);
     const int blocks = rb_ceil_div(warps, 4);
-#define RB_QK(TA, TW) qknorm_rope_append_kernel<TA, TW, TA><<<blocks, 128, 0, s>>>( \
+#define RB_QK(TA, TW) return rb_launch(qknorm_rope_append_kernel<TA, TW, TA>, dim3(blocks), dim3(128), 0, s, \
         (const TA*)qkv, (const TW*)qw, (const TW*)kw, inv_freq, positions, kv_slot, (TA*)q_out, (TA*)k_out, (TA*)cache, \
         n_tokens, QH, KH, d, rot, page_size, eps)
     if (act_dtype == RB_F32 && w_dtype == RB_F32) RB_QK(float, float);
-    else if (act_dtype == RB_F32 && w_dtype == RB_BF16) RB_QK(float, bf16);
-    else if (act_dtype == RB_BF16 && w_dtype == RB_F32) RB_QK(bf16, float);
-    else if (act_dtype == RB_BF16 && w_dtype == RB_BF16) RB_QK(bf16, bf16);
-    else RB_REFUSE("qknorm_rope_append: dtypes act=%d weight=%d", act_dtype, w_dtype);
+    if (act_dtype == RB_F32 && w_dtype == RB_BF16) RB_QK(float, bf16);
+    if (act_dtype == RB_BF16 && w_dtype == RB_F32) RB_QK(bf16, float);
+    if (act_dtype == RB_BF16 && w_dtype == RB_BF16) RB_QK(bf16, bf16);
 #undef RB_QK
-    return RB_LAUNCH_RESULT();
+    RB_REFUSE("qknorm_rope_append: dtypes act=%d weight=%d", act_dtype, w_dtype);
 }
 
 // Append given k [T,KH,d] (row stride k_stride elements) and v (row stride v_stride) to the cache
@@ -222,6 +248,7 @@ template <typename TA>
 __global__ void kv_append_kernel(const TA* __restrict__ k, long long k_stride, const TA* __restrict__ v,
                                  long long v_stride, const int* __restrict__ kv_slot, TA* __restrict__ cache,
                                  int n_tokens, int KH, int d, int page_size) {
+    pdl_trigger(); pdl_wait();
     const long long wglobal = ((long long)blockIdx.x * blockDim.x + threadIdx.x) >> 5;
     const int lane = threadIdx.x & 31;
     if (wglobal >= (long long)n_tokens * KH) return;
@@ -252,6 +279,7 @@ extern "C" int rb_kv_append(const void* k, long long k_stride, const void* v, lo
 // out[t,f] = g/(1+exp(-g)) * u,  g = gu[t,f], u = gu[t,F+f]   (dense_kernels.cu:202-214)
 template <typename TA>
 __global__ void swiglu_kernel(const TA* __restrict__ gu, TA* __restrict__ out, int F, size_t total) {
+    pdl_trigger(); pdl_wait();
     size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
     if (i >= total) return;
     const size_t t = i / F;
@@ -266,8 +294,7 @@ extern "C" int rb_swiglu(const void* gu, void* out, int dtype, int n_tokens, int
     cudaStream_t s = (cudaStream_t)stream;
     const size_t total = (size_t)n_tokens * F;
     const int blocks = rb_ceil_div((long long)total, 256);
-    if (dtype == RB_F32) swiglu_kernel<float><<<blocks, 256, 0, s>>>((const float*)gu, (float*)out, F, total);
-    else if (dtype == RB_BF16) swiglu_kernel<bf16><<<blocks, 256, 0, s>>>((const bf16*)gu, (bf16*)out, F, total);
-    else RB_REFUSE("swiglu: dtype %d", dtype);
-    return RB_LAUNCH_RESULT();
+    if (dtype == RB_F32) return rb_launch(swiglu_kernel<float>, dim3(blocks), dim3(256), 0, s, (const float*)gu, (float*)out, F, total);
+    if (dtype == RB_BF16) return rb_launch(swiglu_kernel<bf16>, dim3(blocks), dim3(256), 0, s, (const bf16*)gu, (bf16*)out, F, total);
+    RB_REFUSE("swiglu: dtype %d", dtype);
 }

@@ -9,10 +9,13 @@
 // 2,048-token prompt portion (N = 256) and a single decoded token (N = 16, operands
 // padded by TMA's out-of-bounds zero fill), and in the accumulator a thread owns one
 // output feature, so a warp's stores for one token are 32 consecutive features.
-// Small token counts give few CTAs, so K is split across CTAs (grid.z); the partial
-// sums go to a float workspace and a second kernel adds them in split order (fixed
-// order, no atomics: the reference's two-phase gemv does the same,
-// crates/cuda/kernels/gemm_m1.cu:106-123).  The reference's products are cublasGemmEx
+// Small token counts give few CTAs, so K is split across CTAs (grid.z).  Up to 8 splits form
+// a thread-block cluster: every CTA parks its accumulator in its own shared memory and the
+// CTAs share out the tile's tokens, each adding all ranks' partial sums for its tokens over
+// distributed shared memory in rank order, and storing them.
+// More splits than that go through a float workspace and a second kernel that adds in split
+// order.  Either way the order is fixed and there are no atomics (the reference's two-phase
+// gemv does the same, crates/cuda/kernels/gemm_m1.cu:106-123).  The reference's products are cublasGemmEx
 // and scalar gemv kernels (crates/cuda/src/gemm.rs:226-372).
 //
 // Every wait on an mbarrier is bounded: after RB_SPIN_LIMIT failed polls the CTA raises
@@ -85,6 +88,17 @@ __device__ __forceinline__ void tc_ld16(uint32_t taddr, uint32_t* r) {
 }
 __device__ __forceinline__ void tc_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
 
+__device__ __forceinline__ void cluster_sync_all() {
+    asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+__device__ __forceinline__ float ld_cluster_f32(uint32_t local_addr, uint32_t rank) {
+    uint32_t remote;
+    float v;
+    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(remote) : "r"(local_addr), "r"(rank));
+    asm volatile("ld.shared::cluster.f32 %0, [%1];" : "=f"(v) : "r"(remote) : "memory");
+    return v;
+}
+
 // Shared-memory operand descriptor: K-major tile, rows of 128 bytes, 128-byte swizzle,
 // 8-row groups 1024 bytes apart (SBO), descriptor version 1 (sm_100).
 __device__ __forceinline__ uint64_t make_smem_desc(uint32_t saddr) {
@@ -103,12 +117,13 @@ struct TcShared {                        // after the operand stages, in dynamic
     int abort_flag;
 };
 
-// OUT_MODE 0: C = acc as bf16; 1: C = acc as float; 2: C(float) += acc; 3: workspace partial (float, [split][T][N])
+// out_mode 0: C = acc as bf16; 1: C = acc as float; 2: C(float) += acc; 3: workspace partial (float, [split][T][N]).
+// csplit > 1: the grid.z CTAs of one tile are a cluster; out_mode (0..2) is applied to the sum over the cluster.
 template <int BN, int STAGES>
-__global__ void __launch_bounds__(TC_THREADS, 1)
+__global__ void __launch_bounds__(TC_THREADS, (BN <= 64 ? 2 : 1))
 gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_x,
                void* __restrict__ C, float* __restrict__ ws, int T, int N, int K, long long ldc, int out_mode,
-               int kb_per_split) {
+               int kb_per_split, int csplit) {
     extern __shared__ __align__(1024) unsigned char smem_raw[];
     constexpr uint32_t W_BYTES = TC_BM * TC_BK * 2;                 // 16 KB
     constexpr uint32_t X_BYTES = BN * TC_BK * 2;
@@ -143,7 +158,20 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
 
     if (warp == 0) {
         if (lane == 0) {
-            for (int kb = 0; kb < nkb; ++kb) {
+            // Weights never change, so their first tiles are fetched at once, while the kernels
+            // before this one may still be running; the activations wait for them to finish.
+            pdl_trigger();
+            const int pre = min(nkb, STAGES);
+            for (int kb = 0; kb < pre; ++kb) {
+                const uint32_t full = smem_u32(&sh->full[kb]);
+                mbar_expect_tx(full, STAGE_BYTES);
+                tma_load_2d(smem_base + kb * STAGE_BYTES, &map_w, (kb0 + kb) * TC_BK, n0, full);
+            }
+            pdl_wait();
+            for (int kb = 0; kb < pre; ++kb)
+                tma_load_2d(smem_base + kb * STAGE_BYTES + W_BYTES, &map_x, (kb0 + kb) * TC_BK, t0, smem_u32(&sh->full[kb]));
+            issued = pre;
+            for (int kb = pre; kb < nkb; ++kb) {
                 const int s = kb % STAGES;
                 const uint32_t round = kb / STAGES;
                 if (!mbar_wait(smem_u32(&sh->empty[s]), (round & 1) ^ 1, abort_flag, 1)) break;
@@ -179,6 +207,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
         // epilogue: warp w may read tensor-memory lanes 32*(w%4) .. +31
         const int q = warp & 3;
         const int feat = n0 + q * 32 + lane;
+        pdl_wait();                                            // C may still be in use by the kernels before
         if (mbar_wait(smem_u32(&sh->acc_full), 0, abort_flag, 3)) {
             tc_fence_after();
 #pragma unroll 1
@@ -187,13 +216,14 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
                 uint32_t r[16];
                 tc_ld16(tmem + ((uint32_t)(q * 32) << 16) + (uint32_t)c0, r);
                 tc_ld_wait();
-                if (feat < N) {
+                if (feat < N || csplit > 1) {
 #pragma unroll
                     for (int j = 0; j < 16; ++j) {
                         const int t = t0 + c0 + j;
                         if (t >= T) break;
                         const float v = __uint_as_float(r[j]);
-                        if (out_mode == 0) ((bf16*)C)[(size_t)t * ldc + feat] = __float2bfloat16_rn(v);
+                        if (csplit > 1) reinterpret_cast<float*>(smem)[(c0 + j) * TC_BM + q * 32 + lane] = v;
+                        else if (out_mode == 0) ((bf16*)C)[(size_t)t * ldc + feat] = __float2bfloat16_rn(v);
                         else if (out_mode == 1) ((float*)C)[(size_t)t * ldc + feat] = v;
                         else if (out_mode == 2) ((float*)C)[(size_t)t * ldc + feat] += v;
                         else ws[((size_t)split * T + t) * N + feat] = v;
@@ -213,6 +243,33 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
         }
     }
     __syncthreads();
+    if (csplit > 1) {
+        // every CTA of the cluster reaches both barriers, whatever happened before
+        cluster_sync_all();                                    // all accumulators are parked
+        if (warp >= 2 && !*abort_flag) {
+            // reduce-scatter: CTA `split` sums and stores the tokens c = split, split + csplit, ...;
+            // the partial sums of all ranks are fetched first (independent loads), then added in rank order
+            const int q = warp & 3;
+            const int fl = q * 32 + lane, feat = n0 + fl;
+            if (feat < N) {
+                const uint32_t mine = smem_base + (uint32_t)fl * 4;
+                for (int c = split; c < BN && t0 + c < T; c += csplit) {
+                    float part[8];
+#pragma unroll
+                    for (int r = 0; r < 8; ++r)
+                        part[r] = r < csplit ? ld_cluster_f32(mine + (uint32_t)c * TC_BM * 4, (uint32_t)r) : 0.0f;
+                    float v = part[0];
+#pragma unroll
+                    for (int r = 1; r < 8; ++r) v += part[r];
+                    const size_t at = (size_t)(t0 + c) * ldc + feat;
+                    if (out_mode == 0) ((bf16*)C)[at] = __float2bfloat16_rn(v);
+                    else if (out_mode == 1) ((float*)C)[at] = v;
+                    else ((float*)C)[at] += v;
+                }
+            }
+        }
+        cluster_sync_all();                                    // nobody leaves while its memory is being read
+    }
     if (warp == 1) {
         tc_fence_after();
         asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(TMEM_COLS) : "memory");
@@ -222,6 +279,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
 // Sum of the split partials in split order, then store / accumulate.  mode as OUT_MODE 0..2.
 __global__ void splitk_reduce_kernel(const float* __restrict__ ws, void* __restrict__ C, int T, int N, long long ldc,
                                      int splits, int mode) {
+    pdl_trigger(); pdl_wait();
     const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
     if (i >= (size_t)T * N) return;
     const int t = (int)(i / N), n = (int)(i % N);
@@ -283,7 +341,7 @@ static int get_map(const void* ptr, long long rows, long long cols, long long ld
 
 template <int BN, int STAGES>
 static int launch_tc(const CUtensorMap& mw, const CUtensorMap& mx, void* C, float* ws, int T, int N, int K, long long ldc,
-                     int out_mode, int splits, int kb_per_split, cudaStream_t s) {
+                     int out_mode, int splits, int kb_per_split, int csplit, cudaStream_t s) {
     constexpr size_t smem = (size_t)STAGES * (TC_BM * TC_BK * 2 + BN * TC_BK * 2) + sizeof(TcShared) + 1024;
     static bool configured = false;
     if (!configured) {
@@ -291,8 +349,27 @@ static int launch_tc(const CUtensorMap& mw, const CUtensorMap& mx, void* C, floa
         if (e != cudaSuccess) return (int)e;
         configured = true;
     }
-    dim3 grid(rb_ceil_div(T, BN), rb_ceil_div(N, TC_BM), splits);
-    gemm_tc_kernel<BN, STAGES><<<grid, TC_THREADS, smem, s>>>(mw, mx, C, ws, T, N, K, ldc, out_mode, kb_per_split);
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(rb_ceil_div(T, BN), rb_ceil_div(N, TC_BM), splits);
+    cfg.blockDim = dim3(TC_THREADS);
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = s;
+    cudaLaunchAttribute attr[2];
+    int na = 0;
+    if (csplit > 1) {
+        attr[na].id = cudaLaunchAttributeClusterDimension;
+        attr[na].val.clusterDim.x = 1; attr[na].val.clusterDim.y = 1; attr[na].val.clusterDim.z = csplit;
+        ++na;
+    }
+    if (g_rb_pdl) {
+        attr[na].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+        attr[na].val.programmaticStreamSerializationAllowed = 1;
+        ++na;
+    }
+    cfg.attrs = attr;
+    cfg.numAttrs = na;
+    cudaError_t e = cudaLaunchKernelEx(&cfg, gemm_tc_kernel<BN, STAGES>, mw, mx, C, ws, T, N, K, ldc, out_mode, kb_per_split, csplit);
+    if (e != cudaSuccess) { (void)cudaGetLastError(); return (int)e; }
     return RB_LAUNCH_RESULT();
 }
 
@@ -313,33 +390,47 @@ extern "C" int rb_gemm_bf16(const void* X, const void* W, void* C, int c_dtype, 
     const int total_kb = rb_ceil_div(K, TC_BK);
     const int ctas = rb_ceil_div(T, bn) * rb_ceil_div(N, TC_BM);
     int splits = 1;
+    bool via_ws = false;                                           // force_splits < 0: that many splits through the workspace
     if (force_splits > 0) splits = force_splits;
-    else if (ctas < 120 && ws) {
-        splits = (148 + ctas - 1) / ctas;
-        if (splits > 16) splits = 16;
-        while (splits > 1 && total_kb / splits < 4) --splits;      // at least 4 k-blocks per CTA
+    else if (force_splits < 0) { splits = -force_splits; via_ws = true; }
+    else if (bn <= 128) {
+        // a weight-streaming launch: fill whole waves of the 148 SMs (x 2 resident CTAs for narrow
+        // tiles).  Among the split counts that leave >= 4 k-blocks per CTA take the one whose last
+        // wave is fullest.
+        const int slots = bn <= 64 ? 296 : 148;
+        double best = 0.0;
+        for (int sp = 1; sp <= 8 && total_kb / sp >= 4; ++sp) {
+            const long long n = (long long)ctas * sp;
+            const double eff = (double)n / (double)(((n + slots - 1) / slots) * slots);
+            if (eff > best + 0.03) { best = eff; splits = sp; }
+        }
     }
     if (splits > total_kb) splits = total_kb;
-    while (splits > 1 && (!ws || (long long)splits * T * N > ws_floats)) --splits;
     int kb_per_split = rb_ceil_div(total_kb, splits);
     splits = rb_ceil_div(total_kb, kb_per_split);                   // no empty split
+    if (splits > 8) via_ws = true;                                  // larger than a portable cluster
+    if (via_ws) {
+        while (splits > 1 && (!ws || (long long)splits * T * N > ws_floats)) --splits;
+        kb_per_split = rb_ceil_div(total_kb, splits);
+        splits = rb_ceil_div(total_kb, kb_per_split);
+    }
+    const int csplit = (splits > 1 && !via_ws) ? splits : 1;
     CUtensorMap mw, mx;
     if (get_map(W, N, K, ldw, TC_BM, &mw)) return -1;
     if (get_map(X, T, K, ldx, bn, &mx)) return -1;
-    const int out_mode = splits > 1 ? 3 : mode;
+    const int out_mode = (splits > 1 && via_ws) ? 3 : mode;
     int rc;
     switch (bn) {
-        case 16: rc = launch_tc<16, 8>(mw, mx, C, ws, T, N, K, ldc, out_mode, splits, kb_per_split, s); break;
-        case 32: rc = launch_tc<32, 8>(mw, mx, C, ws, T, N, K, ldc, out_mode, splits, kb_per_split, s); break;
-        case 64: rc = launch_tc<64, 6>(mw, mx, C, ws, T, N, K, ldc, out_mode, splits, kb_per_split, s); break;
-        case 128: rc = launch_tc<128, 5>(mw, mx, C, ws, T, N, K, ldc, out_mode, splits, kb_per_split, s); break;
-        default: rc = launch_tc<256, 4>(mw, mx, C, ws, T, N, K, ldc, out_mode, splits, kb_per_split, s); break;
+        case 16: rc = launch_tc<16, 6>(mw, mx, C, ws, T, N, K, ldc, out_mode, splits, kb_per_split, csplit, s); break;
+        case 32: rc = launch_tc<32, 5>(mw, mx, C, ws, T, N, K, ldc, out_mode, splits, kb_per_split, csplit, s); break;
+        case 64: rc = launch_tc<64, 4>(mw, mx, C, ws, T, N, K, ldc, out_mode, splits, kb_per_split, csplit, s); break;
+        case 128: rc = launch_tc<128, 5>(mw, mx, C, ws, T, N, K, ldc, out_mode, splits, kb_per_split, csplit, s); break;
+        default: rc = launch_tc<256, 4>(mw, mx, C, ws, T, N, K, ldc, out_mode, splits, kb_per_split, csplit, s); break;
     }
     if (rc) return rc;
-    if (splits > 1) {
+    if (splits > 1 && via_ws) {
         const long long total = (long long)T * N;
-        splitk_reduce_kernel<<<rb_ceil_div(total, 256), 256, 0, s>>>(ws, C, T, N, ldc, splits, mode);
-        return RB_LAUNCH_RESULT();
+        return rb_launch(splitk_reduce_kernel, dim3(rb_ceil_div(total, 256)), dim3(256), 0, s, (const float*)ws, C, T, N, ldc, splits, mode);
     }
     return 0;
 }

@@ -69,7 +69,7 @@ class _Staging:
         self.events: List[Optional[torch.cuda.Event]] = [None] * n_buffers
         self.i = 0
 
-    def upload(self, host: np.ndarray, device) -> torch.Tensor:
+    def upload(self, host: np.ndarray, device, into: Optional[torch.Tensor] = None) -> torch.Tensor:
         n = host.shape[0]
         i = self.i
         self.i = (self.i + 1) % len(self.bufs)
@@ -78,8 +78,8 @@ class _Staging:
         if self.bufs[i].numel() < n:
             self.bufs[i] = torch.empty(max(n, 2 * self.bufs[i].numel()), dtype=torch.int32, pin_memory=True)
         self.bufs[i][:n].numpy()[:] = host
-        dev = torch.empty(n, dtype=torch.int32, device=device)
-        dev.copy_(self.bufs[i][:n], non_blocking=True)
+        dev = into if into is not None else torch.empty(n, dtype=torch.int32, device=device)
+        dev[:n].copy_(self.bufs[i][:n], non_blocking=True)
         ev = torch.cuda.Event()
         ev.record()
         self.events[i] = ev
@@ -92,7 +92,8 @@ class Engine:
 
     def __init__(self, config, spec, state: Dict[str, torch.Tensor], dtype: torch.dtype, *,
                  page_size: int = 16, num_pages: Optional[int] = None, max_tokens: Optional[int] = None,
-                 max_num_seqs: int = 64, device="cuda:0", memory_fraction: float = 0.9):
+                 max_num_seqs: int = 64, device="cuda:0", memory_fraction: float = 0.9,
+                 cuda_graphs: bool = True):
         self.device = torch.device(device)
         torch.cuda.set_device(self.device)
         ops.require_device()
@@ -113,6 +114,12 @@ class Engine:
         self.storage = CacheStorage(self.cache, dtype, self.device)
         self._staging = _Staging()
         self.steps_run = 0
+        # decode-only steps replay a captured CUDA graph per (batch bucket, block-table width);
+        # a model with fixed-size per-request state runs eagerly (padding rows would touch a slot)
+        self.cuda_graphs = bool(cuda_graphs) and not self.storage.layer_state
+        self._graphs: Dict[tuple, "_DecodeGraph"] = {}
+        self._graph_pool = None
+        self.graph_replays = 0
 
     # ---- construction ---------------------------------------------------------------
     @classmethod
@@ -151,6 +158,9 @@ class Engine:
 
     # ---- the step ----------------------------------------------------------------------
     def step(self, entries: Sequence[StepEntry]) -> Optional[torch.Tensor]:
+        entries = [e for e in entries if len(e.tokens) > 0]
+        if self.cuda_graphs and entries and len(entries) <= MAX_GRAPH_BATCH and all(len(e.tokens) == 1 for e in entries):
+            return self._step_graph(entries)
         ctx, want_rows, lens_after = self._prepare(entries)
         if ctx is None:
             return None
@@ -160,12 +170,44 @@ class Engine:
         self.steps_run += 1
         return logits
 
+    def _step_graph(self, entries: Sequence[StepEntry]) -> Optional[torch.Tensor]:
+        """A step of single tokens only: fill the graph's static tables and replay it."""
+        B = len(entries)
+        bucket = B if B <= 8 else -(-B // 8) * 8
+        need_pages = 1
+        for e in entries:
+            cur = self.cache.length(e.request_id) if e.request_id in self.cache else 0
+            need_pages = max(need_pages, self.cache.pages_for(cur + 1))
+        width = 8
+        while width < need_pages:
+            width *= 2
+        key = (bucket, width)
+        g = self._graphs.get(key)
+        if g is None:
+            g = _DecodeGraph(self, bucket, width)
+            self._graphs[key] = g
+        host, lens_after = self._prepare(entries, fixed=(bucket, width))
+        self._staging.upload(host, self.device, into=g.meta)
+        g.graph.replay()
+        self.graph_replays += 1
+        for rid, n in lens_after:
+            self.cache.commit(rid, n)
+        self.steps_run += 1
+        rows = [k for k, e in enumerate(entries) if len(e.want) > 0]
+        if not rows:
+            return None
+        # a copy: the graph's own buffer is overwritten by the next replay
+        return g.logits[:B].clone() if rows == list(range(B)) else g.logits[rows]
+
     def finish(self, request_id) -> None:
         """The request is over: its pages and its slot are given back."""
         if request_id in self.cache:
             self.cache.release(request_id)
 
-    def _prepare(self, entries: Sequence[StepEntry]):
+    def _prepare(self, entries: Sequence[StepEntry], fixed=None):
+        """Checks, page reservation and the step's int32 block.  With `fixed` = (entries, block-table
+        width) the block has that fixed layout (rows beyond the real entries are inert: no key is
+        read or stored for them) and is returned on the host, for a captured graph."""
         entries = [e for e in entries if len(e.tokens) > 0]
         if not entries:
             return None, None, []
@@ -215,19 +257,12 @@ class Engine:
 
         n_groups = len(cm.groups)
         max_pages = [max(1, max(len(cm.table(e.request_id, g)) for e in internal)) for g in range(n_groups)]
-        # layout of the int32 block
-        off = {}
-        cur = 0
-
-        def take(name, n):
-            nonlocal cur
-            off[name] = (cur, n)
-            cur += (n + 3) // 4 * 4                     # 16-byte aligned sections
-
-        take("token_ids", T); take("positions", T); take("tok_entry", T)
-        take("cu_q", E + 1); take("kv_len", E); take("entry_slot", E); take("want_rows", max(R, 1))
-        for g in range(n_groups):
-            take(f"kv_slot{g}", T); take(f"block_table{g}", E * max_pages[g])
+        E_real, T_real = E, T
+        if fixed is not None:
+            E = T = R = fixed[0]
+            max_pages = [fixed[1]] * n_groups
+            want_rows = list(range(R))
+        off, cur = self._layout(T, E, R, max_pages)
         host = np.zeros(cur, dtype=np.int32)
 
         def sec(name):
@@ -235,18 +270,23 @@ class Engine:
             return host[o:o + n]
 
         tok, pos, ent = sec("token_ids"), sec("positions"), sec("tok_entry")
+        ent[:] = np.arange(T, dtype=np.int32) if fixed is not None else 0
         for k, e in enumerate(internal):
             a, b = int(q_start[k]), int(q_start[k + 1])
             tok[a:b] = np.asarray(e.tokens, dtype=np.int32)
             pos[a:b] = np.arange(start[k], start[k] + q_len[k], dtype=np.int32)
             ent[a:b] = k
-        sec("cu_q")[:] = q_start
-        sec("kv_len")[:] = np.asarray(start) + np.asarray(q_len)
-        sec("entry_slot")[:] = slots
+        if fixed is not None:
+            sec("cu_q")[:] = np.arange(E + 1, dtype=np.int32)
+        else:
+            sec("cu_q")[:] = q_start
+        sec("kv_len")[:E_real] = np.asarray(start) + np.asarray(q_len)
+        sec("entry_slot")[:E_real] = slots
         if R:
             sec("want_rows")[:] = want_rows
         for g in range(n_groups):
             ks = sec(f"kv_slot{g}")
+            ks[:] = -1
             bt = sec(f"block_table{g}").reshape(E, max_pages[g])
             bt[:] = -1
             for k, e in enumerate(internal):
@@ -254,7 +294,36 @@ class Engine:
                 bt[k, :len(table)] = table
                 a, b = int(q_start[k]), int(q_start[k + 1])
                 ks[a:b] = cm.write_slots(e.request_id, g, start[k], q_len[k])
+        lens_after = [(e.request_id, s + n) for e, s, n in zip(internal, start, q_len)]
+        if fixed is not None:
+            return host, lens_after
         dev = self._staging.upload(host, self.device)
+        ctx = self._context(dev, off, T, E, n_decode, max_pages, [int(v) for v in q_start], list(start), slots,
+                            max(q_len), max(s + n for s, n in zip(start, q_len)))
+        o, n = off["want_rows"]
+        return ctx, (dev[o:o + n] if R else None), lens_after
+
+    @staticmethod
+    def _layout(T: int, E: int, R: int, max_pages):
+        """Offsets (in int32 elements, 16-byte aligned sections) of the step's block."""
+        off = {}
+        cur = 0
+
+        def take(name, n):
+            nonlocal cur
+            off[name] = (cur, n)
+            cur += (n + 3) // 4 * 4
+
+        take("token_ids", T); take("positions", T); take("tok_entry", T)
+        take("cu_q", E + 1); take("kv_len", E); take("entry_slot", E); take("want_rows", max(R, 1))
+        for g in range(len(max_pages)):
+            take(f"kv_slot{g}", T); take(f"block_table{g}", E * max_pages[g])
+        return off, cur
+
+    def _context(self, dev: torch.Tensor, off, T: int, E: int, n_decode: int, max_pages, q_start, start, slots,
+                 max_q_len: int, max_kv_len: int) -> StepContext:
+        """Views of the device block as the tables the parts read, and each layer's cache."""
+        cm = self.cache
 
         def dsec(name):
             o, n = off[name]
@@ -275,11 +344,42 @@ class Engine:
             if layer.name in self.storage.layer_state:
                 lc.state = self.storage.layer_state[layer.name]
             layer_caches[layer.name] = lc
-        ctx = StepContext(dtype=self.dtype, device=self.device, n_tokens=T, n_entries=E, n_decode=n_decode,
-                          token_ids=dsec("token_ids"), positions=dsec("positions"), tok_entry=dsec("tok_entry"),
-                          cu_q=dsec("cu_q"), kv_len=dsec("kv_len"), entry_slot=dsec("entry_slot"),
-                          q_start=[int(v) for v in q_start], start_pos=list(start), slots=slots,
-                          max_q_len=max(q_len), max_kv_len=max(s + n for s, n in zip(start, q_len)),
-                          layer_caches=layer_caches)
-        lens_after = [(e.request_id, s + n) for e, s, n in zip(internal, start, q_len)]
-        return ctx, (dsec("want_rows") if R else None), lens_after
+        return StepContext(dtype=self.dtype, device=self.device, n_tokens=T, n_entries=E, n_decode=n_decode,
+                           token_ids=dsec("token_ids"), positions=dsec("positions"), tok_entry=dsec("tok_entry"),
+                           cu_q=dsec("cu_q"), kv_len=dsec("kv_len"), entry_slot=dsec("entry_slot"),
+                           q_start=q_start, start_pos=start, slots=slots, max_q_len=max_q_len, max_kv_len=max_kv_len,
+                           layer_caches=layer_caches)
+
+
+MAX_GRAPH_BATCH = 256
+
+
+class _DecodeGraph:
+    """A captured decode step for `batch` single-token entries and block tables `width` pages wide.
+    Its tables live in `meta` (a static int32 block the engine refills before every replay); its
+    logits [batch, vocab] in `logits`."""
+
+    def __init__(self, engine: "Engine", batch: int, width: int):
+        n_groups = len(engine.cache.groups)
+        off, total = Engine._layout(batch, batch, batch, [width] * n_groups)
+        host = np.zeros(total, dtype=np.int32)
+        for name, (o, n) in off.items():
+            if name.startswith("kv_slot") or name.startswith("block_table"):
+                host[o:o + n] = -1                       # inert rows: nothing stored, nothing read
+        o, n = off["tok_entry"]; host[o:o + n] = np.arange(batch)
+        o, n = off["cu_q"]; host[o:o + n] = np.arange(batch + 1)
+        o, n = off["want_rows"]; host[o:o + n] = np.arange(batch)
+        self.meta = torch.from_numpy(host).to(engine.device)
+        ctx = engine._context(self.meta, off, batch, batch, batch, [width] * n_groups, list(range(batch + 1)),
+                              [0] * batch, [0] * batch, 1, width * engine.page_size)
+        o, n = off["want_rows"]
+        want = self.meta[o:o + n]
+        l0 = ops.launches
+        engine.model.forward(ctx, want)                  # eager once: lazy set-up must not fall into the capture
+        self.n_launches = ops.launches - l0              # kernels of this library in one replay
+        torch.cuda.synchronize()
+        if engine._graph_pool is None:
+            engine._graph_pool = torch.cuda.graph_pool_handle()
+        self.graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(self.graph, pool=engine._graph_pool):
+            self.logits = engine.model.forward(ctx, want)

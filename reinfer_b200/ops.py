@@ -10,6 +10,7 @@ every call raises.
 from __future__ import annotations
 
 import ctypes
+import os
 from ctypes import c_void_p, c_int, c_float, c_longlong, c_char_p
 from typing import Optional
 
@@ -40,6 +41,8 @@ def lib():
         _lib.rb_last_error.restype = c_char_p
         if _lib.rb_abi_version() != 1:
             raise KernelError("kernel library has another ABI version")
+        if os.environ.get("REINFER_B200_PDL", "1") == "0":
+            _lib.rb_set_pdl(0)          # launch every kernel fully serialised (for comparisons)
     return _lib
 
 
@@ -233,7 +236,7 @@ def attention(ctx, q: torch.Tensor, cache: torch.Tensor, group, out: torch.Tenso
     if n_dec:
         ctas = n_dec * KH * (QH // KH // gc)
         tiles = -(-ctx.max_kv_len // 64)
-        n_splits = max(1, min(-(-FA_TARGET_CTAS // ctas), tiles, 64))
+        n_splits = max(1, min(FA_TARGET_CTAS // ctas, tiles, 64))     # one full wave at most
         fa_decode(q, cache, group.block_table, ctx.cu_q, ctx.kv_len, out, 0, n_dec, 0, n_splits, QH, KH, d,
                   group.page_size, window, scale)
     if E > n_dec:

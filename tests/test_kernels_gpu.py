@@ -43,7 +43,7 @@ def test_gemm_tensor_core(T, N, K, mode):
     assert err <= tol, f"relative error {err:.3e}"
 
 
-@pytest.mark.parametrize("splits", [1, 2, 3, 7])
+@pytest.mark.parametrize("splits", [1, 2, 3, 7, 8, -2, -5, -11])    # > 0: one cluster; < 0: through the workspace
 def test_gemm_split_k_is_deterministic(splits):
     from reinfer_b200 import ops
     a, w = rnd(4, 1000, dtype=torch.bfloat16, seed=5), rnd(200, 1000, dtype=torch.bfloat16, seed=6)
