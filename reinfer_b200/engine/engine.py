@@ -335,15 +335,14 @@ class Engine:
                                    block_table=dsec(f"block_table{g}").view(E, max_pages[g]),
                                    kv_slot=dsec(f"kv_slot{g}"), max_pages=max_pages[g], window=grp.window))
         layer_caches: Dict[str, LayerCache] = {}
-        for layer in self.model.layers:
-            src = layer.spec.cache_from or layer.name
-            lc = LayerCache(write=layer.spec.cache_from is None)
-            if src in cm.group_of_layer:
+        for key, src, write in self.model.cache_bindings():
+            lc = LayerCache(write=write)
+            if src is not None and src in cm.group_of_layer:
                 lc.kv = self.storage.layer_kv[src]
                 lc.group = views[cm.group_of_layer[src]]
-            if layer.name in self.storage.layer_state:
-                lc.state = self.storage.layer_state[layer.name]
-            layer_caches[layer.name] = lc
+            if key in self.storage.layer_state:
+                lc.state = self.storage.layer_state[key]
+            layer_caches[key] = lc
         return StepContext(dtype=self.dtype, device=self.device, n_tokens=T, n_entries=E, n_decode=n_decode,
                            token_ids=dsec("token_ids"), positions=dsec("positions"), tok_entry=dsec("tok_entry"),
                            cu_q=dsec("cu_q"), kv_len=dsec("kv_len"), entry_slot=dsec("entry_slot"),

@@ -47,6 +47,14 @@ class Model:
         for i in self.order:
             if not 0 <= i < len(self.layers):
                 raise ValueError(f"run order names layer {i} of {len(self.layers)}")
+        # a layer that runs more than once has a cache (pages, state) of its own for every run:
+        # run k of layer `name` uses the cache key `name` (first run) or `name#k`
+        seen: Dict[int, int] = {}
+        self.run: List[Tuple[int, str]] = []
+        for i in self.order:
+            k = seen.get(i, 0)
+            seen[i] = k + 1
+            self.run.append((i, self.layers[i].name if k == 0 else f"{self.layers[i].name}#{k}"))
         by_name = {l.name: l for l in self.layers}
         for l in self.layers:
             src = l.spec.cache_from
@@ -100,33 +108,40 @@ class Model:
 
     # ---- what the cache manager has to provide -------------------------------
     def cache_layout(self):
-        """(paged, states): paged maps each layer that owns pages to its PagedKVSpec; states
-        maps each layer with a fixed-size state to its SlotStateSpec.  Layers that read
-        another layer's cache own nothing."""
+        """(paged, states): paged maps each cache key (a run of a layer) that owns pages to its
+        PagedKVSpec; states maps each key with a fixed-size state to its SlotStateSpec.  Layers
+        that read another layer's cache own no pages."""
         paged: Dict[str, PagedKVSpec] = {}
         states: Dict[str, SlotStateSpec] = {}
-        for l in self.layers:
+        for i, key in self.run:
+            l = self.layers[i]
             cs, ss = l.mixer.cache_spec(), l.mixer.state_spec()
             if cs is not None and l.spec.cache_from is None:
-                paged[l.name] = cs
+                paged[key] = cs
             if ss is not None:
-                states[l.name] = ss
+                states[key] = ss
         return paged, states
 
-    def cache_source(self, layer_name: str) -> str:
-        for l in self.layers:
-            if l.name == layer_name:
-                return l.spec.cache_from or l.name
-        raise KeyError(layer_name)
+    def cache_bindings(self):
+        """For every run: (cache key, key of the pages it reads or None, whether it stores into them)."""
+        out = []
+        for i, key in self.run:
+            l = self.layers[i]
+            if l.mixer.cache_spec() is None:
+                out.append((key, None, False))
+            elif l.spec.cache_from is not None:
+                out.append((key, l.spec.cache_from, False))
+            else:
+                out.append((key, key, True))
+        return out
 
     # ---- the forward pass of one step ------------------------------------------
     def forward(self, ctx, want_rows: Optional[torch.Tensor]) -> Optional[torch.Tensor]:
         """Run the step's tokens through every layer in run order; return float32 logits
         [len(want_rows), vocab] for the wanted token rows (None if none are wanted)."""
         x = self.embedding.forward(ctx)
-        for i in self.order:
-            layer = self.layers[i]
-            layer.block.forward(ctx, x, ctx.layer_caches[layer.name])
+        for i, key in self.run:
+            self.layers[i].block.forward(ctx, x, ctx.layer_caches[key])
         if want_rows is None or want_rows.numel() == 0:
             return None
         xn = self.final_norm.forward(ctx, x, row_idx=want_rows)
