@@ -245,3 +245,45 @@ extern "C" int rb_sample(const float* logits, long long ld_logits, const int* ro
 }
 
 extern "C" int rb_sample_params_size() { return (int)sizeof(RbSampleParams); }
+
+// ------------------------------------------------------------------------------------------
+// The sampler for callers that must not allocate (declared and described in sampler_static.h).
+// Its scratch rows are this file-scope array in device memory.  In host code the array's name
+// is only a handle; its device address comes from cudaGetSymbolAddress, looked up once per
+// device with that device current, and it is that address the kernel receives.
+#include "sampler_static.h"
+#include <mutex>
+
+static __device__ __align__(256) float g_sample_static_scratch[RB_SAMPLE_STATIC_FLOATS];
+
+#define RB_SAMPLE_STATIC_MAX_DEVICES 64
+static float* g_sample_static_addr[RB_SAMPLE_STATIC_MAX_DEVICES] = {nullptr};
+static std::mutex g_sample_static_mu;
+
+extern "C" int rb_sample_static(const float* logits, long long ld_logits, const int* row_idx, const void* params,
+                                const int* history, int hist_cap, int* out_tokens, int rows, int vocab, void* stream) {
+    if (rows <= 0) return 0;
+    if (vocab <= 0) RB_REFUSE("sample_static: vocab %d", vocab);
+    if ((unsigned long long)rows * (unsigned long long)vocab > (unsigned long long)RB_SAMPLE_STATIC_FLOATS)
+        RB_REFUSE("sample_static: %d rows x %d entries need %llu floats of scratch; the built-in array holds %u "
+                  "(use rb_sample with a buffer of your own)", rows, vocab,
+                  (unsigned long long)rows * (unsigned long long)vocab, (unsigned)RB_SAMPLE_STATIC_FLOATS);
+    int dev = 0;
+    cudaError_t e = cudaGetDevice(&dev);
+    if (e != cudaSuccess) return (int)e;
+    if (dev < 0 || dev >= RB_SAMPLE_STATIC_MAX_DEVICES) RB_REFUSE("sample_static: device index %d", dev);
+    float* scratch;
+    {
+        std::lock_guard<std::mutex> g(g_sample_static_mu);
+        if (g_sample_static_addr[dev] == nullptr) {            // first call on this device: look the address up
+            void* p = nullptr;
+            e = cudaGetSymbolAddress(&p, g_sample_static_scratch);
+            if (e != cudaSuccess) return (int)e;
+            g_sample_static_addr[dev] = (float*)p;
+        }
+        scratch = g_sample_static_addr[dev];
+    }
+    sample_kernel<<<rows, SP_THREADS, 0, (cudaStream_t)stream>>>(
+        logits, ld_logits, row_idx, (const RbSampleParams*)params, history, hist_cap, scratch, out_tokens, vocab);
+    return RB_LAUNCH_RESULT();
+}
