@@ -216,17 +216,33 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
                 uint32_t r[16];
                 tc_ld16(tmem + ((uint32_t)(q * 32) << 16) + (uint32_t)c0, r);
                 tc_ld_wait();
-                if (feat < N || csplit > 1) {
+                if (csplit > 1) {                              // park the accumulator for the cluster's reduction
 #pragma unroll
-                    for (int j = 0; j < 16; ++j) {
-                        const int t = t0 + c0 + j;
-                        if (t >= T) break;
-                        const float v = __uint_as_float(r[j]);
-                        if (csplit > 1) reinterpret_cast<float*>(smem)[(c0 + j) * TC_BM + q * 32 + lane] = v;
-                        else if (out_mode == 0) ((bf16*)C)[(size_t)t * ldc + feat] = __float2bfloat16_rn(v);
-                        else if (out_mode == 1) ((float*)C)[(size_t)t * ldc + feat] = v;
-                        else if (out_mode == 2) ((float*)C)[(size_t)t * ldc + feat] += v;
-                        else ws[((size_t)split * T + t) * N + feat] = v;
+                    for (int j = 0; j < 16; ++j)
+                        reinterpret_cast<float*>(smem)[(c0 + j) * TC_BM + q * 32 + lane] = __uint_as_float(r[j]);
+                } else if (feat < N) {
+                    const int nt = min(16, T - t0 - c0);        // tokens of this chunk that exist
+                    if (out_mode == 2) {
+                        // read-modify-write of the float residual: all loads first, so that their
+                        // latencies overlap instead of queueing behind the stores
+                        float* cp = (float*)C + (size_t)(t0 + c0) * ldc + feat;
+                        float old[16];
+#pragma unroll
+                        for (int j = 0; j < 16; ++j) old[j] = j < nt ? cp[(size_t)j * ldc] : 0.0f;
+#pragma unroll
+                        for (int j = 0; j < 16; ++j) if (j < nt) cp[(size_t)j * ldc] = old[j] + __uint_as_float(r[j]);
+                    } else if (out_mode == 0) {
+                        bf16* cp = (bf16*)C + (size_t)(t0 + c0) * ldc + feat;
+#pragma unroll
+                        for (int j = 0; j < 16; ++j) if (j < nt) cp[(size_t)j * ldc] = __float2bfloat16_rn(__uint_as_float(r[j]));
+                    } else if (out_mode == 1) {
+                        float* cp = (float*)C + (size_t)(t0 + c0) * ldc + feat;
+#pragma unroll
+                        for (int j = 0; j < 16; ++j) if (j < nt) cp[(size_t)j * ldc] = __uint_as_float(r[j]);
+                    } else {
+                        float* cp = ws + ((size_t)split * T + t0 + c0) * N + feat;
+#pragma unroll
+                        for (int j = 0; j < 16; ++j) if (j < nt) cp[(size_t)j * N] = __uint_as_float(r[j]);
                     }
                 }
             }
