@@ -119,16 +119,21 @@ struct TcShared {                        // after the operand stages, in dynamic
 
 // out_mode 0: C = acc as bf16; 1: C = acc as float; 2: C(float) += acc; 3: workspace partial (float, [split][T][N]).
 // csplit > 1: the grid.z CTAs of one tile are a cluster; out_mode (0..2) is applied to the sum over the cluster.
-template <int BN, int STAGES>
+// DUAL: W holds two matrices of N rows each (gate rows, then up rows); the CTA multiplies the same token tile
+// with the matching 128 rows of both into two accumulators and stores silu(gate) * up as bfloat16
+// (the reference's fused_cast_swiglu_f16, crates/cuda/kernels/dense_kernels.cu:236-248, as a GEMM epilogue).
+template <int BN, int STAGES, bool DUAL>
 __global__ void __launch_bounds__(TC_THREADS, (BN <= 64 ? 2 : 1))
 gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_x,
                void* __restrict__ C, float* __restrict__ ws, int T, int N, int K, long long ldc, int out_mode,
                int kb_per_split, int csplit) {
     extern __shared__ __align__(1024) unsigned char smem_raw[];
-    constexpr uint32_t W_BYTES = TC_BM * TC_BK * 2;                 // 16 KB
+    constexpr uint32_t W1_BYTES = TC_BM * TC_BK * 2;                // 16 KB per weight tile
+    constexpr uint32_t W_BYTES = (DUAL ? 2 : 1) * W1_BYTES;
     constexpr uint32_t X_BYTES = BN * TC_BK * 2;
     constexpr uint32_t STAGE_BYTES = W_BYTES + X_BYTES;            // multiples of 1024 (BN >= 16 -> 2 KB)
-    constexpr uint32_t TMEM_COLS = BN < 32 ? 32 : BN;
+    constexpr uint32_t ACC_COLS = (DUAL ? 2 : 1) * BN;
+    constexpr uint32_t TMEM_COLS = ACC_COLS < 32 ? 32 : ACC_COLS;
     unsigned char* smem = (unsigned char*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
     TcShared* sh = (TcShared*)(smem + (size_t)STAGES * STAGE_BYTES);
     const uint32_t smem_base = smem_u32(smem);
@@ -166,6 +171,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
                 const uint32_t full = smem_u32(&sh->full[kb]);
                 mbar_expect_tx(full, STAGE_BYTES);
                 tma_load_2d(smem_base + kb * STAGE_BYTES, &map_w, (kb0 + kb) * TC_BK, n0, full);
+                if (DUAL) tma_load_2d(smem_base + kb * STAGE_BYTES + W1_BYTES, &map_w, (kb0 + kb) * TC_BK, N + n0, full);
             }
             pdl_wait();
             for (int kb = 0; kb < pre; ++kb)
@@ -180,6 +186,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
                 const uint32_t dst = smem_base + s * STAGE_BYTES;
                 const int kx = (kb0 + kb) * TC_BK;
                 tma_load_2d(dst, &map_w, kx, n0, full);
+                if (DUAL) tma_load_2d(dst + W1_BYTES, &map_w, kx, N + n0, full);
                 tma_load_2d(dst + W_BYTES, &map_x, kx, t0, full);
                 issued = kb + 1;
             }
@@ -196,9 +203,12 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
                 tc_fence_after();
                 const uint32_t a = smem_base + s * STAGE_BYTES;
                 const uint64_t da = make_smem_desc(a), db = make_smem_desc(a + W_BYTES);
+                const uint64_t da2 = make_smem_desc(a + W1_BYTES);
 #pragma unroll
-                for (int k = 0; k < TC_BK / 16; ++k)                 // 32 bytes further along K inside the swizzled row
+                for (int k = 0; k < TC_BK / 16; ++k) {               // 32 bytes further along K inside the swizzled row
                     tc_mma_bf16(tmem, da + (uint64_t)(k * 2), db + (uint64_t)(k * 2), idesc, (kb | k) != 0);
+                    if (DUAL) tc_mma_bf16(tmem + BN, da2 + (uint64_t)(k * 2), db + (uint64_t)(k * 2), idesc, (kb | k) != 0);
+                }
                 tc_commit(smem_u32(&sh->empty[s]));                   // frees the stage when these MMAs are done
             }
             if (ok) tc_commit(smem_u32(&sh->acc_full));
@@ -213,16 +223,26 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
 #pragma unroll 1
             for (int c0 = 0; c0 < BN; c0 += 16) {
                 if (t0 + c0 >= T) break;                               // warp-uniform
-                uint32_t r[16];
+                uint32_t r[16], r2[16];
                 tc_ld16(tmem + ((uint32_t)(q * 32) << 16) + (uint32_t)c0, r);
+                if (DUAL) tc_ld16(tmem + ((uint32_t)(q * 32) << 16) + (uint32_t)(BN + c0), r2);
                 tc_ld_wait();
-                if (csplit > 1) {                              // park the accumulator for the cluster's reduction
+                if (csplit > 1) {                              // park the accumulator(s) for the cluster's reduction
 #pragma unroll
-                    for (int j = 0; j < 16; ++j)
+                    for (int j = 0; j < 16; ++j) {
                         reinterpret_cast<float*>(smem)[(c0 + j) * TC_BM + q * 32 + lane] = __uint_as_float(r[j]);
+                        if (DUAL) reinterpret_cast<float*>(smem)[(BN + c0 + j) * TC_BM + q * 32 + lane] = __uint_as_float(r2[j]);
+                    }
                 } else if (feat < N) {
                     const int nt = min(16, T - t0 - c0);        // tokens of this chunk that exist
-                    if (out_mode == 2) {
+                    if (DUAL) {
+                        bf16* cp = (bf16*)C + (size_t)(t0 + c0) * ldc + feat;
+#pragma unroll
+                        for (int j = 0; j < 16; ++j) {
+                            const float g = __uint_as_float(r[j]), u = __uint_as_float(r2[j]);
+                            if (j < nt) cp[(size_t)j * ldc] = __float2bfloat16_rn(g / (1.0f + expf(-g)) * u);
+                        }
+                    } else if (out_mode == 2) {
                         // read-modify-write of the float residual: all loads first, so that their
                         // latencies overlap instead of queueing behind the stores
                         float* cp = (float*)C + (size_t)(t0 + c0) * ldc + feat;
@@ -278,7 +298,15 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
 #pragma unroll
                     for (int r = 1; r < 8; ++r) v += part[r];
                     const size_t at = (size_t)(t0 + c) * ldc + feat;
-                    if (out_mode == 0) ((bf16*)C)[at] = __float2bfloat16_rn(v);
+                    if (DUAL) {
+#pragma unroll
+                        for (int r = 0; r < 8; ++r)
+                            part[r] = r < csplit ? ld_cluster_f32(mine + (uint32_t)(BN + c) * TC_BM * 4, (uint32_t)r) : 0.0f;
+                        float u = part[0];
+#pragma unroll
+                        for (int r = 1; r < 8; ++r) u += part[r];
+                        ((bf16*)C)[at] = __float2bfloat16_rn(v / (1.0f + expf(-v)) * u);
+                    } else if (out_mode == 0) ((bf16*)C)[at] = __float2bfloat16_rn(v);
                     else if (out_mode == 1) ((float*)C)[at] = v;
                     else ((float*)C)[at] += v;
                 }
@@ -355,13 +383,13 @@ static int get_map(const void* ptr, long long rows, long long cols, long long ld
     return 0;
 }
 
-template <int BN, int STAGES>
+template <int BN, int STAGES, bool DUAL>
 static int launch_tc(const CUtensorMap& mw, const CUtensorMap& mx, void* C, float* ws, int T, int N, int K, long long ldc,
                      int out_mode, int splits, int kb_per_split, int csplit, cudaStream_t s) {
-    constexpr size_t smem = (size_t)STAGES * (TC_BM * TC_BK * 2 + BN * TC_BK * 2) + sizeof(TcShared) + 1024;
+    constexpr size_t smem = (size_t)STAGES * ((DUAL ? 2 : 1) * TC_BM * TC_BK * 2 + BN * TC_BK * 2) + sizeof(TcShared) + 1024;
     static bool configured = false;
     if (!configured) {
-        cudaError_t e = cudaFuncSetAttribute(gemm_tc_kernel<BN, STAGES>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        cudaError_t e = cudaFuncSetAttribute(gemm_tc_kernel<BN, STAGES, DUAL>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         if (e != cudaSuccess) return (int)e;
         configured = true;
     }
@@ -384,7 +412,7 @@ static int launch_tc(const CUtensorMap& mw, const CUtensorMap& mx, void* C, floa
     }
     cfg.attrs = attr;
     cfg.numAttrs = na;
-    cudaError_t e = cudaLaunchKernelEx(&cfg, gemm_tc_kernel<BN, STAGES>, mw, mx, C, ws, T, N, K, ldc, out_mode, kb_per_split, csplit);
+    cudaError_t e = cudaLaunchKernelEx(&cfg, gemm_tc_kernel<BN, STAGES, DUAL>, mw, mx, C, ws, T, N, K, ldc, out_mode, kb_per_split, csplit);
     if (e != cudaSuccess) { (void)cudaGetLastError(); return (int)e; }
     return RB_LAUNCH_RESULT();
 }
@@ -437,11 +465,11 @@ extern "C" int rb_gemm_bf16(const void* X, const void* W, void* C, int c_dtype, 
     const int out_mode = (splits > 1 && via_ws) ? 3 : mode;
     int rc;
     switch (bn) {
-        case 16: rc = launch_tc<16, 6>(mw, mx, C, ws, T, N, K, ldc, out_mode, splits, kb_per_split, csplit, s); break;
-        case 32: rc = launch_tc<32, 5>(mw, mx, C, ws, T, N, K, ldc, out_mode, splits, kb_per_split, csplit, s); break;
-        case 64: rc = launch_tc<64, 4>(mw, mx, C, ws, T, N, K, ldc, out_mode, splits, kb_per_split, csplit, s); break;
-        case 128: rc = launch_tc<128, 5>(mw, mx, C, ws, T, N, K, ldc, out_mode, splits, kb_per_split, csplit, s); break;
-        default: rc = launch_tc<256, 4>(mw, mx, C, ws, T, N, K, ldc, out_mode, splits, kb_per_split, csplit, s); break;
+        case 16: rc = launch_tc<16, 6, false>(mw, mx, C, ws, T, N, K, ldc, out_mode, splits, kb_per_split, csplit, s); break;
+        case 32: rc = launch_tc<32, 5, false>(mw, mx, C, ws, T, N, K, ldc, out_mode, splits, kb_per_split, csplit, s); break;
+        case 64: rc = launch_tc<64, 4, false>(mw, mx, C, ws, T, N, K, ldc, out_mode, splits, kb_per_split, csplit, s); break;
+        case 128: rc = launch_tc<128, 5, false>(mw, mx, C, ws, T, N, K, ldc, out_mode, splits, kb_per_split, csplit, s); break;
+        default: rc = launch_tc<256, 4, false>(mw, mx, C, ws, T, N, K, ldc, out_mode, splits, kb_per_split, csplit, s); break;
     }
     if (rc) return rc;
     if (splits > 1 && via_ws) {
@@ -449,6 +477,43 @@ extern "C" int rb_gemm_bf16(const void* X, const void* W, void* C, int c_dtype, 
         return rb_launch(splitk_reduce_kernel, dim3(rb_ceil_div(total, 256)), dim3(256), 0, s, (const float*)ws, C, T, N, ldc, splits, mode);
     }
     return 0;
+}
+
+// act[T,F] (bfloat16) = silu(X Wg^T) * (X Wu^T) for Wgu = [Wg; Wu] of shape [2F, K]: one product with two
+// accumulators and the activation in the epilogue.  Splits (at most 8) reduce inside a cluster.
+extern "C" int rb_gemm_bf16_swiglu(const void* X, const void* Wgu, void* act, int T, int F, int K,
+                                   long long ldx, long long ldw, long long ldc, void* stream) {
+    if (T <= 0 || F <= 0) return 0;
+    if (K <= 0) RB_REFUSE("gemm_swiglu: K=%d", K);
+    if ((ldx % 8) || (ldw % 8) || ((uintptr_t)X & 15) || ((uintptr_t)Wgu & 15))
+        RB_REFUSE("gemm_swiglu: TMA needs 16-byte aligned operands and row strides (ldx %lld, ldw %lld)", ldx, ldw);
+    cudaStream_t s = (cudaStream_t)stream;
+    const int bn = T <= 16 ? 16 : T <= 32 ? 32 : T <= 64 ? 64 : T <= 128 ? 128 : 256;
+    const int total_kb = rb_ceil_div(K, TC_BK);
+    const int ctas = rb_ceil_div(T, bn) * rb_ceil_div(F, TC_BM);
+    int splits = 1;
+    if (bn <= 128) {
+        const int slots = bn <= 32 ? 296 : 148;
+        double best = 0.0;
+        for (int sp = 1; sp <= 8 && total_kb / sp >= 4; ++sp) {
+            const long long n = (long long)ctas * sp;
+            const double eff = (double)n / (double)(((n + slots - 1) / slots) * slots);
+            if (eff > best + 0.03) { best = eff; splits = sp; }
+        }
+    }
+    int kb_per_split = rb_ceil_div(total_kb, splits);
+    splits = rb_ceil_div(total_kb, kb_per_split);
+    const int csplit = splits > 1 ? splits : 1;
+    CUtensorMap mw, mx;
+    if (get_map(Wgu, 2LL * F, K, ldw, TC_BM, &mw)) return -1;
+    if (get_map(X, T, K, ldx, bn, &mx)) return -1;
+    switch (bn) {
+        case 16: return launch_tc<16, 3, true>(mw, mx, act, nullptr, T, F, K, ldc, 0, splits, kb_per_split, csplit, s);
+        case 32: return launch_tc<32, 3, true>(mw, mx, act, nullptr, T, F, K, ldc, 0, splits, kb_per_split, csplit, s);
+        case 64: return launch_tc<64, 4, true>(mw, mx, act, nullptr, T, F, K, ldc, 0, splits, kb_per_split, csplit, s);
+        case 128: return launch_tc<128, 4, true>(mw, mx, act, nullptr, T, F, K, ldc, 0, splits, kb_per_split, csplit, s);
+        default: return launch_tc<256, 3, true>(mw, mx, act, nullptr, T, F, K, ldc, 0, splits, kb_per_split, csplit, s);
+    }
 }
 
 // The error word of the tensor-core kernels (0 = none); synchronises the device.  With reset != 0 it is cleared.

@@ -284,6 +284,23 @@ def gemm_bf16(a: torch.Tensor, w: torch.Tensor, c: torch.Tensor, accumulate: boo
                               _p(_gemm_ws), c_longlong(_gemm_ws.numel()), c_int(splits), _stream()), "gemm_bf16")
 
 
+def gemm_bf16_swiglu(a: torch.Tensor, w_gate_up: torch.Tensor, out: torch.Tensor) -> bool:
+    """out[T,F] (bf16) = silu(a Wg^T) * (a Wu^T), w_gate_up = [Wg; Wu] of shape [2F, K]: one tensor-core
+    product with two accumulators and the activation in its epilogue.  Returns False (and does
+    nothing) if TMA cannot address the operands; the caller then runs the two-kernel form."""
+    T, K = a.shape
+    F_ = out.shape[1]
+    _need(w_gate_up.shape == (2 * F_, K) and out.shape[0] == T, "gemm_swiglu: shapes")
+    _need(a.dtype == w_gate_up.dtype == out.dtype == torch.bfloat16, "gemm_swiglu: bfloat16 tensors")
+    _need(a.stride(1) == 1 and w_gate_up.stride(1) == 1 and out.stride(1) == 1, "gemm_swiglu: rows contiguous")
+    if a.stride(0) % 8 or w_gate_up.stride(0) % 8 or a.data_ptr() % 16 or w_gate_up.data_ptr() % 16:
+        return False
+    _check(lib().rb_gemm_bf16_swiglu(_p(a), _p(w_gate_up), _p(out), c_int(T), c_int(F_), c_int(K),
+                                     c_longlong(a.stride(0)), c_longlong(w_gate_up.stride(0)), c_longlong(out.stride(0)),
+                                     _stream()), "gemm_bf16_swiglu")
+    return True
+
+
 def kernel_error(reset: bool = True) -> int:
     """The error word that a kernel sets when one of its bounded waits gives up (0 = none).
     Synchronises the device."""

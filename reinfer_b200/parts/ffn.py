@@ -1,7 +1,8 @@
 """SwiGLU feed-forward: down( silu(x Wg^T) * (x Wu^T) ), no bias
 (crates/cuda/src/engine.rs:4288-4314; crates/cuda/kernels/dense_kernels.cu:236-248).
 Gate and up rows are concatenated once at load into one `[2F, h]` matrix so that one
-product serves both (the reference runs two)."""
+product serves both (the reference runs two); in bfloat16 that product keeps two
+accumulators and applies the activation in its epilogue."""
 from __future__ import annotations
 
 import torch
@@ -31,9 +32,12 @@ class SwiGLU(FeedForward):
         self.w_down = tensors["down_proj.weight"]
 
     def forward(self, ctx, xn, residual) -> None:
-        gu = matmul(ctx, xn, self.w_gate_up)
         act = torch.empty((xn.shape[0], self.inter), dtype=xn.dtype, device=xn.device)
-        ops.swiglu(gu, act)
+        fused = xn.dtype == torch.bfloat16 and self.w_gate_up.dtype == torch.bfloat16 and \
+            ops.gemm_bf16_swiglu(xn, self.w_gate_up, act)          # activation in the product's epilogue
+        if not fused:
+            gu = matmul(ctx, xn, self.w_gate_up)
+            ops.swiglu(gu, act)
         matmul(ctx, act, self.w_down, out=residual, accumulate=True)
 
 

@@ -43,6 +43,20 @@ def test_gemm_tensor_core(T, N, K, mode):
     assert err <= tol, f"relative error {err:.3e}"
 
 
+@pytest.mark.parametrize("T,F,K", [(1, 128, 64), (1, 12288, 4096), (8, 12288, 4096), (5, 160, 96), (17, 300, 200), (40, 1000, 512),
+                                   (64, 2048, 1024), (100, 130, 72), (129, 640, 264), (300, 520, 520), (2048, 1024, 512)])
+def test_gemm_swiglu_epilogue(T, F, K):
+    from reinfer_b200 import ops
+    a = rnd(T, K, dtype=torch.bfloat16, seed=1)
+    w = rnd(2 * F, K, dtype=torch.bfloat16, scale=0.08, seed=2)
+    out = torch.full((T, F), float("nan"), dtype=torch.bfloat16, device=DEV)
+    assert ops.gemm_bf16_swiglu(a, w, out)
+    assert ops.kernel_error() == 0
+    g, u = a.float() @ w[:F].float().t(), a.float() @ w[F:].float().t()
+    ref = g / (1 + torch.exp(-g)) * u
+    assert (out.float() - ref).abs().max().item() <= 1e-2 * ref.abs().max().item()
+
+
 @pytest.mark.parametrize("splits", [1, 2, 3, 7, 8, -2, -5, -11])    # > 0: one cluster; < 0: through the workspace
 def test_gemm_split_k_is_deterministic(splits):
     from reinfer_b200 import ops
