@@ -1,0 +1,388 @@
+// Split-K flash decoding over the paged cache with the tiles brought in by TMA.
+//
+// Same arithmetic and the same division of work as fa_decode_kernel (attention_mma.cu): the
+// grouped query heads of one kv head are the rows of a 16-row tile, a request's keys are split
+// across CTAs and, inside a CTA, across four warps (16 keys of each 64-key tile per warp),
+// mma.sync m16n8k16 with an online softmax in float, merge in shared memory, then across CTAs.
+// A fifth warp is the producer: it runs ahead of the four by the depth of the pipeline (full and
+// empty mbarriers per stage), reading the block table 32 entries at a time.
+// What differs is how keys and values reach shared memory: one layer of the cache is described
+// to the TMA unit as a 2-D bfloat16 matrix [pages * 2 * kv_heads * page_size, head_dim], and one
+// elected thread issues a box copy (cp.async.bulk.tensor) per page, per K/V and per 64-column
+// half, completing on an mbarrier - a handful of instructions per 32 KB tile where the cp.async
+// loader spends thousands, which is what held that kernel at a third of the memory bandwidth.
+// Tiles land in the 128-byte swizzled layout, so ldmatrix needs no padding to avoid conflicts.
+//
+// A box copy brings whole pages.  Slots of the request's last page beyond its length hold
+// whatever was there; the rows of the last tile at or beyond the length are therefore zeroed in
+// shared memory before use, and shared memory is zeroed once at the start, so that nothing but
+// the request's own keys and values ever reaches the arithmetic.
+// Needs a page size that is a power of two >= 8 and head_dim % 8 == 0 (else fa_decode_kernel).
+#include "sm100.cuh"
+
+#define FT_WARPS 4
+#define FT_THREADS 160                       // four consumer warps and one producer warp
+#define FT_BN 64
+#define FT_HALF_BYTES (FT_BN * 128)          // 64 keys x 128 bytes
+
+struct FtArgs {
+    const bf16* q;
+    const int* block_table;
+    const int* cu_q;
+    const int* kv_len;
+    bf16* out;
+    float* part_o;
+    float* part_lse;
+    int QH, KH, d, page_size, page_shift, max_pages, window;
+    int Gc, chunks, first_entry, n_entries, n_splits;
+    float scale_log2;
+};
+
+struct FtShared {
+    unsigned long long full[4];
+    unsigned long long empty[4];
+    int abort_flag;
+};
+
+__device__ __forceinline__ void ft_ldsm_x4(uint32_t (&r)[4], uint32_t addr) {
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(addr));
+}
+__device__ __forceinline__ void ft_ldsm_x4_trans(uint32_t (&r)[4], uint32_t addr) {
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(addr));
+}
+__device__ __forceinline__ void ft_mma(float (&c)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
+    asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+                 : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+                 : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+__device__ __forceinline__ uint32_t ft_pack(float lo, float hi) {
+    __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
+    return *reinterpret_cast<uint32_t*>(&v);
+}
+// byte offset of 16-byte chunk `chunk` of row `row` in a tile of 64-column halves, 128-byte swizzle
+__device__ __forceinline__ uint32_t ft_off(int row, int chunk, int half_bytes) {
+    return (uint32_t)((chunk >> 3) * half_bytes + row * 128 + (((chunk & 7) ^ (row & 7)) << 4));
+}
+
+template <int HALVES, int NST>
+__global__ void __launch_bounds__(FT_THREADS)
+fa_decode_tma_kernel(const __grid_constant__ CUtensorMap map_kv, const FtArgs a) {
+    constexpr int D = HALVES * 64;
+    constexpr int KV_BYTES = HALVES * FT_HALF_BYTES;           // one K (or V) tile
+    constexpr int STAGE = 2 * KV_BYTES;
+    constexpr int Q_HALF = 16 * 128;
+    extern __shared__ __align__(1024) unsigned char smem_raw[];
+    unsigned char* smem = (unsigned char*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+    unsigned char* stages = smem;
+    unsigned char* sQ = smem + NST * STAGE;
+    FtShared* sh = (FtShared*)(sQ + HALVES * Q_HALF);
+    const uint32_t stages_u = smem_u32(stages), sQ_u = smem_u32(sQ);
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    volatile int* abort_flag = &sh->abort_flag;
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < NST; ++s) { mbar_init(smem_u32(&sh->full[s]), 1); mbar_init(smem_u32(&sh->empty[s]), FT_WARPS); }
+        sh->abort_flag = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    // shared memory starts at zero: rows that no copy fills are then finite
+    for (int i = threadIdx.x; i < (NST * STAGE + HALVES * Q_HALF) / 16; i += FT_THREADS)
+        reinterpret_cast<uint4*>(smem)[i] = make_uint4(0, 0, 0, 0);
+    __syncthreads();
+    pdl_trigger();
+    pdl_wait();
+
+    const int e = a.first_entry + blockIdx.x;
+    const int kh = blockIdx.y / a.chunks, chunk = blockIdx.y % a.chunks;
+    const int head0 = kh * (a.QH / a.KH) + chunk * a.Gc;
+    const int split = blockIdx.z;
+    const int kv_end = a.kv_len[e];
+    const int pos = kv_end - 1;
+    const int lo = a.window > 0 ? max(0, pos - a.window + 1) : 0;
+    const int tok = a.cu_q[e];
+    const int* bt = a.block_table + (size_t)e * a.max_pages;
+    const int t_lo = lo / FT_BN, t_hi = pos / FT_BN + 1;
+    const int per = (t_hi - t_lo + a.n_splits - 1) / a.n_splits;
+    const int t_begin = t_lo + split * per, t_end = min(t_hi, t_begin + per);
+    const int n_tiles = max(0, t_end - t_begin);
+
+    // Q rows (row r = query head head0 + r) into the swizzled layout
+    for (int i = threadIdx.x; i < a.Gc * (a.d / 8); i += FT_THREADS) {
+        const int row = i / (a.d / 8), c = i % (a.d / 8);
+        const uint4 v = *reinterpret_cast<const uint4*>(a.q + ((size_t)tok * a.QH + head0 + row) * a.d + c * 8);
+        *reinterpret_cast<uint4*>(sQ + ft_off(row, c, Q_HALF)) = v;
+    }
+    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");   // the zeroing above precedes the TMA writes
+    __syncthreads();
+
+    const int box_rows = min(a.page_size, FT_BN);
+    const int subs = FT_BN / box_rows;
+    const int rows_per_page2 = 2 * a.KH * a.page_size;            // matrix rows of one page (K and V, all heads)
+    int issued = 0;                                               // producer: tiles whose copies were issued
+
+    const int row0 = lane >> 2;
+    const int pos0 = row0 < a.Gc ? pos : -1, pos1 = row0 + 8 < a.Gc ? pos : -1;
+    float o[D / 8][4];
+#pragma unroll
+    for (int j = 0; j < D / 8; ++j) { o[j][0] = o[j][1] = o[j][2] = o[j][3] = 0.0f; }
+    float m[2] = {-INFINITY, -INFINITY}, l[2] = {0.0f, 0.0f};
+    const int koff = warp * 16;
+
+    if (warp == FT_WARPS) {
+        // ---- producer warp: runs ahead of the consumers by up to NST tiles --------------------
+        // Block-table entries are fetched 32 at a time by the whole warp and handed to lane 0.
+        int cached_first = 0, cached = -1;                        // page index of lane 0's entry; entry of this lane
+        bool have = false;
+        for (int it = 0; it < n_tiles; ++it) {
+            const int s = it % NST;
+            const int k0 = (t_begin + it) * FT_BN;
+            const int pi0 = k0 >> a.page_shift;
+            const int need_last = (k0 + (subs - 1) * box_rows) >> a.page_shift;
+            if (!have || need_last >= cached_first + 32) {
+                cached_first = pi0;
+                cached = (pi0 + lane < a.max_pages) ? bt[pi0 + lane] : -1;
+                have = true;
+            }
+            int pages[8];
+            int n_valid = 0;
+#pragma unroll
+            for (int u = 0; u < 8; ++u) {
+                const int key = k0 + u * box_rows;
+                const int idx = (key >> a.page_shift) - cached_first;
+                const int pg = __shfl_sync(0xffffffffu, cached, idx & 31);
+                pages[u] = (u < subs && key < kv_end) ? pg : -1;
+                n_valid += pages[u] >= 0;
+            }
+            bool ok = true;
+            if (lane == 0) {
+                if (it >= NST) ok = mbar_wait(smem_u32(&sh->empty[s]), ((it / NST) & 1) ^ 1, abort_flag, 5);
+                if (ok) {
+                    const uint32_t full = smem_u32(&sh->full[s]);
+                    mbar_expect_tx(full, (uint32_t)(n_valid * 2 * HALVES * box_rows * 128));
+                    const uint32_t dst0 = stages_u + s * STAGE;
+#pragma unroll
+                    for (int u = 0; u < 8; ++u) {
+                        if (pages[u] >= 0) {
+                            const int key = k0 + u * box_rows;
+                            const int y = pages[u] * rows_per_page2 + kh * a.page_size + (key & (a.page_size - 1));
+#pragma unroll
+                            for (int h = 0; h < HALVES; ++h) {
+                                tma_load_2d(dst0 + h * FT_HALF_BYTES + u * box_rows * 128, &map_kv, h * 64, y, full);
+                                tma_load_2d(dst0 + KV_BYTES + h * FT_HALF_BYTES + u * box_rows * 128, &map_kv, h * 64,
+                                            y + a.KH * a.page_size, full);
+                            }
+                        }
+                    }
+                    issued = it + 1;
+                }
+            }
+            if (!__shfl_sync(0xffffffffu, (int)ok, 0)) break;
+        }
+    } else {
+        // ---- consumer warps --------------------------------------------------------------------
+        for (int it = 0; it < n_tiles; ++it) {
+            const int s = it % NST;
+            if (!mbar_wait(smem_u32(&sh->full[s]), (it / NST) & 1, abort_flag, 4)) break;
+            const uint32_t sK = stages_u + s * STAGE, sV = sK + KV_BYTES;
+            const int k0 = (t_begin + it) * FT_BN;
+            if (k0 + FT_BN > kv_end) {
+                // the request's last tile: slots of its last page beyond its length hold foreign data
+                for (int i = threadIdx.x; i < FT_BN * HALVES * 8; i += FT_WARPS * 32) {
+                    const int row = i / (HALVES * 8), c = i % (HALVES * 8);
+                    if (k0 + row >= kv_end) {
+                        *reinterpret_cast<uint4*>(stages + s * STAGE + ft_off(row, c, FT_HALF_BYTES)) = make_uint4(0, 0, 0, 0);
+                        *reinterpret_cast<uint4*>(stages + s * STAGE + KV_BYTES + ft_off(row, c, FT_HALF_BYTES)) = make_uint4(0, 0, 0, 0);
+                    }
+                }
+                asm volatile("fence.proxy.async.shared::cta;" ::: "memory");   // before a later copy refills this stage
+                asm volatile("bar.sync 1, %0;" ::"n"(FT_WARPS * 32) : "memory");   // the four consumer warps
+            }
+            // S = Q K^T for this warp's 16 keys
+            float sc[2][4];
+#pragma unroll
+            for (int j = 0; j < 2; ++j) { sc[j][0] = sc[j][1] = sc[j][2] = sc[j][3] = 0.0f; }
+#pragma unroll
+            for (int ks = 0; ks < D / 16; ++ks) {
+                uint32_t qa[4], kb[4];
+                ft_ldsm_x4(qa, sQ_u + ft_off((lane & 7) + 8 * ((lane >> 3) & 1), ks * 2 + (lane >> 4), Q_HALF));
+                ft_ldsm_x4(kb, sK + ft_off(koff + (lane & 7) + 8 * (lane >> 4), ks * 2 + ((lane >> 3) & 1), FT_HALF_BYTES));
+                ft_mma(sc[0], qa, kb[0], kb[1]);
+                ft_mma(sc[1], qa, kb[2], kb[3]);
+            }
+            float mx0 = -INFINITY, mx1 = -INFINITY;
+#pragma unroll
+            for (int j = 0; j < 2; ++j) {
+                const int key = k0 + koff + j * 8 + 2 * (lane & 3);
+                sc[j][0] = (key >= lo && key <= pos0) ? sc[j][0] * a.scale_log2 : -INFINITY;
+                sc[j][1] = (key + 1 >= lo && key + 1 <= pos0) ? sc[j][1] * a.scale_log2 : -INFINITY;
+                sc[j][2] = (key >= lo && key <= pos1) ? sc[j][2] * a.scale_log2 : -INFINITY;
+                sc[j][3] = (key + 1 >= lo && key + 1 <= pos1) ? sc[j][3] * a.scale_log2 : -INFINITY;
+                mx0 = fmaxf(mx0, fmaxf(sc[j][0], sc[j][1]));
+                mx1 = fmaxf(mx1, fmaxf(sc[j][2], sc[j][3]));
+            }
+            mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, 1)); mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, 2));
+            mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, 1)); mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, 2));
+            const float mn0 = fmaxf(m[0], mx0), mn1 = fmaxf(m[1], mx1);
+            const float b0 = mn0 == -INFINITY ? 0.0f : mn0, b1 = mn1 == -INFINITY ? 0.0f : mn1;
+            const float c0 = exp2f(m[0] - b0), c1 = exp2f(m[1] - b1);
+            m[0] = mn0; m[1] = mn1;
+            uint32_t pa[4];
+            {
+                const float e0 = exp2f(sc[0][0] - b0), e1 = exp2f(sc[0][1] - b0), e2 = exp2f(sc[0][2] - b1), e3 = exp2f(sc[0][3] - b1);
+                const float f0 = exp2f(sc[1][0] - b0), f1 = exp2f(sc[1][1] - b0), f2 = exp2f(sc[1][2] - b1), f3 = exp2f(sc[1][3] - b1);
+                l[0] = l[0] * c0 + (e0 + e1) + (f0 + f1);
+                l[1] = l[1] * c1 + (e2 + e3) + (f2 + f3);
+                pa[0] = ft_pack(e0, e1); pa[1] = ft_pack(e2, e3); pa[2] = ft_pack(f0, f1); pa[3] = ft_pack(f2, f3);
+            }
+#pragma unroll
+            for (int j = 0; j < D / 8; ++j) { o[j][0] *= c0; o[j][1] *= c0; o[j][2] *= c1; o[j][3] *= c1; }
+#pragma unroll
+            for (int dp = 0; dp < D / 16; ++dp) {
+                uint32_t vb[4];
+                ft_ldsm_x4_trans(vb, sV + ft_off(koff + (lane & 7) + 8 * ((lane >> 3) & 1), dp * 2 + (lane >> 4), FT_HALF_BYTES));
+                ft_mma(o[2 * dp], pa, vb[0], vb[1]);
+                ft_mma(o[2 * dp + 1], pa, vb[2], vb[3]);
+            }
+            // this warp is done with the stage: the producer may refill it once all four are
+            __syncwarp();
+            if (lane == 0) mbar_arrive(smem_u32(&sh->empty[s]));
+        }
+    }
+    __syncthreads();
+    if (*abort_flag) {
+        // copies that were issued but never consumed still write this CTA's shared memory: wait for them
+        if (threadIdx.x == FT_WARPS * 32)
+            for (int it = max(0, issued - NST); it < issued; ++it)
+                for (uint32_t k = 0; k < RB_SPIN_LIMIT; ++k)
+                    if (mbar_try(smem_u32(&sh->full[it % NST]), (it / NST) & 1)) break;
+        __syncthreads();
+        return;
+    }
+    if (warp == FT_WARPS) return;                              // the producer has no part in the merge
+    // merge the four warps (fixed order), then store or hand to the merge kernel
+#pragma unroll
+    for (int i = 0; i < 2; ++i) {
+        l[i] += __shfl_xor_sync(0xffffffffu, l[i], 1);
+        l[i] += __shfl_xor_sync(0xffffffffu, l[i], 2);
+    }
+    float* sO = reinterpret_cast<float*>(stages);              // [warp][16][D]
+    float* sM = sO + FT_WARPS * 16 * D;
+    float* sL = sM + FT_WARPS * 16;
+#pragma unroll
+    for (int j = 0; j < D / 8; ++j) {
+        const int dim = j * 8 + 2 * (lane & 3);
+        sO[(warp * 16 + row0) * D + dim] = o[j][0]; sO[(warp * 16 + row0) * D + dim + 1] = o[j][1];
+        sO[(warp * 16 + row0 + 8) * D + dim] = o[j][2]; sO[(warp * 16 + row0 + 8) * D + dim + 1] = o[j][3];
+    }
+    if ((lane & 3) == 0) {
+        sM[warp * 16 + row0] = m[0]; sM[warp * 16 + row0 + 8] = m[1];
+        sL[warp * 16 + row0] = l[0]; sL[warp * 16 + row0 + 8] = l[1];
+    }
+    asm volatile("bar.sync 1, %0;" ::"n"(FT_WARPS * 32) : "memory");
+    for (int i = threadIdx.x; i < a.Gc * a.d; i += FT_WARPS * 32) {
+        const int row = i / a.d, dim = i % a.d;
+        float M = -INFINITY;
+#pragma unroll
+        for (int w = 0; w < FT_WARPS; ++w) M = fmaxf(M, sM[w * 16 + row]);
+        float L = 0.0f, O = 0.0f;
+        if (M > -INFINITY) {
+#pragma unroll
+            for (int w = 0; w < FT_WARPS; ++w) {
+                const float f = exp2f(sM[w * 16 + row] - M);
+                L += sL[w * 16 + row] * f;
+                O += sO[(w * 16 + row) * D + dim] * f;
+            }
+        }
+        const float val = L > 0.0f ? O / L : 0.0f;
+        const int head = head0 + row;
+        if (a.n_splits == 1) {
+            a.out[((size_t)tok * a.QH + head) * a.d + dim] = __float2bfloat16_rn(val);
+        } else {
+            const size_t pi = ((size_t)(tok - a.cu_q[a.first_entry]) * a.QH + head) * a.n_splits + split;
+            a.part_o[pi * a.d + dim] = val;
+            if (dim == 0) a.part_lse[pi] = L > 0.0f ? M + log2f(L) : -INFINITY;
+        }
+    }
+}
+
+// out[t, h, :] = sum_s w_s o_s / sum_s w_s,  w_s = 2^(lse_s - max lse), splits in ascending order
+__global__ void ft_merge_kernel(const float* __restrict__ part_o, const float* __restrict__ part_lse, bf16* __restrict__ out,
+                                int first_tok, int QH, int d, int n_splits) {
+    pdl_trigger(); pdl_wait();
+    const int t = blockIdx.x, h = blockIdx.y;
+    const size_t base = ((size_t)t * QH + h) * n_splits;
+    float M = -INFINITY;
+    for (int s = 0; s < n_splits; ++s) M = fmaxf(M, part_lse[base + s]);
+    for (int dim = threadIdx.x; dim < d; dim += blockDim.x) {
+        float W = 0.0f, O = 0.0f;
+        if (M > -INFINITY) {
+            for (int s = 0; s < n_splits; ++s) {
+                const float w = exp2f(part_lse[base + s] - M);
+                W += w;
+                O += w * part_o[(base + s) * d + dim];
+            }
+        }
+        out[((size_t)(first_tok + t) * QH + h) * d + dim] = __float2bfloat16_rn(W > 0.0f ? O / W : 0.0f);
+    }
+}
+
+template <int HALVES, int NST>
+static int ft_launch(const CUtensorMap& map, const FtArgs& a, cudaStream_t s) {
+    constexpr size_t pipe = (size_t)NST * 2 * HALVES * FT_HALF_BYTES;
+    constexpr size_t merge = (size_t)FT_WARPS * 16 * (HALVES * 64 + 2) * sizeof(float);
+    static_assert(merge <= pipe, "the merge buffers reuse the stages");
+    constexpr size_t smem = pipe + HALVES * 16 * 128 + sizeof(FtShared) + 1024;
+    static bool done = false;
+    if (!done) {
+        cudaError_t e = cudaFuncSetAttribute(fa_decode_tma_kernel<HALVES, NST>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        if (e != cudaSuccess) return (int)e;
+        done = true;
+    }
+    return rb_launch(fa_decode_tma_kernel<HALVES, NST>, dim3(a.n_entries, a.KH * a.chunks, a.n_splits), dim3(FT_THREADS), smem, s,
+                     map, a);
+}
+
+// As rb_fa_decode, with `cache` the layer's [num_pages, 2, KH, page_size, d] array described to TMA.
+extern "C" int rb_fa_decode_tma(const void* q, const void* cache, long long num_pages, const int* block_table, const int* cu_q,
+                                const int* kv_len, void* out, float* part_o, float* part_lse, int first_entry, int n_entries,
+                                int first_tok, int n_splits, int QH, int KH, int d, int page_size, int max_pages, int window,
+                                float scale, void* stream) {
+    if (n_entries <= 0) return 0;
+    if (QH <= 0 || KH <= 0 || QH % KH) RB_REFUSE("attention: %d query heads over %d kv heads", QH, KH);
+    if (d <= 0 || d % 8 || d > 256) RB_REFUSE("attention (TMA): head_dim %d is not a multiple of 8 up to 256", d);
+    int shift = -1;
+    for (int s = 3; s < 16; ++s) if ((1 << s) == page_size) shift = s;
+    if (shift < 0) RB_REFUSE("attention (TMA): page size %d is not a power of two >= 8", page_size);
+    if (n_splits < 1 || n_splits > 65535) RB_REFUSE("attention: %d splits", n_splits);
+    if (n_splits > 1 && (!part_o || !part_lse)) RB_REFUSE("attention: split decoding needs its scratch");
+    if (((uintptr_t)cache & 15) || ((uintptr_t)q & 15)) RB_REFUSE("attention (TMA): operands must be 16-byte aligned");
+    FtArgs a{};
+    a.q = (const bf16*)q; a.block_table = block_table; a.cu_q = cu_q; a.kv_len = kv_len; a.out = (bf16*)out;
+    a.part_o = part_o; a.part_lse = part_lse; a.QH = QH; a.KH = KH; a.d = d; a.page_size = page_size; a.page_shift = shift;
+    a.max_pages = max_pages; a.window = window;
+    const int G = QH / KH;
+    a.Gc = 1;
+    for (int c = 16; c >= 1; --c) if (G % c == 0) { a.Gc = c; break; }
+    a.chunks = G / a.Gc; a.first_entry = first_entry; a.n_entries = n_entries; a.n_splits = n_splits;
+    a.scale_log2 = scale * 1.4426950408889634f;
+    CUtensorMap map;
+    const int box_rows = page_size < FT_BN ? page_size : FT_BN;
+    if (rb_tensor_map_bf16(cache, num_pages * 2LL * KH * page_size, d, d, box_rows, &map)) return -1;
+    cudaStream_t s = (cudaStream_t)stream;
+    int rc;
+    if (d <= 64) rc = ft_launch<1, 4>(map, a, s);
+    else if (d <= 128) rc = ft_launch<2, 3>(map, a, s);
+    else rc = ft_launch<4, 2>(map, a, s);
+    if (rc || n_splits == 1) return rc;
+    return rb_launch(ft_merge_kernel, dim3(n_entries, QH), dim3(128), 0, s, (const float*)part_o, (const float*)part_lse,
+                     (bf16*)out, first_tok, QH, d, n_splits);
+}
+
+extern "C" int rb_attn_error(int reset) {
+    int v = 0;
+    if (cudaMemcpyFromSymbol(&v, g_rb_kernel_error, sizeof(int)) != cudaSuccess) return -1;
+    if (reset && v) { int z = 0; cudaMemcpyToSymbol(g_rb_kernel_error, &z, sizeof(int)); }
+    return v;
+}

@@ -21,93 +21,11 @@
 // Every wait on an mbarrier is bounded: after RB_SPIN_LIMIT failed polls the CTA raises
 // an abort flag, its roles leave their loops, outstanding TMA loads are waited for (again
 // bounded), tensor memory is freed, and an error word in global memory tells the host.
-#include "common.cuh"
-#include <cuda.h>
-#include <cudaTypedefs.h>
-#include <mutex>
-#include <unordered_map>
+#include "sm100.cuh"
 
 #define TC_BM 128            // output features per CTA (MMA M)
 #define TC_BK 64             // K elements per stage (128 bytes: one swizzle row)
 #define TC_THREADS 192       // warp 0: TMA, warp 1: MMA + tensor memory, warps 2..5: epilogue
-#define RB_SPIN_LIMIT (1u << 24)
-
-__device__ int g_tc_error = 0;          // 0 ok; else (code << 8 | detail) of the first failure
-
-// ------------------------------------------------------------------ PTX helpers
-__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
-
-__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
-    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count));
-}
-__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
-    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
-}
-__device__ __forceinline__ bool mbar_try(uint32_t bar, uint32_t parity) {
-    uint32_t ok;
-    asm volatile(
-        "{\n\t.reg .pred p;\n\t"
-        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
-        "selp.u32 %0, 1, 0, p;\n\t}"
-        : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
-    return ok != 0;
-}
-// Bounded wait.  Returns false if the CTA is aborting (or this wait gave up and raised the abort).
-__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag, int where) {
-    for (uint32_t it = 0; it < RB_SPIN_LIMIT; ++it) {
-        if (mbar_try(bar, parity)) return true;
-        if ((it & 255u) == 255u && *abort_flag) return false;
-    }
-    *abort_flag = where;
-    atomicCAS(&g_tc_error, 0, (1 << 8) | where);
-    return false;
-}
-__device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map, int x, int y, uint32_t bar) {
-    asm volatile(
-        "cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
-        ::"r"(dst), "l"(map), "r"(x), "r"(y), "r"(bar) : "memory");
-}
-__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
-__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
-__device__ __forceinline__ void tc_commit(uint32_t bar) {
-    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
-}
-__device__ __forceinline__ void tc_mma_bf16(uint32_t tmem_d, uint64_t desc_a, uint64_t desc_b, uint32_t idesc, uint32_t accumulate) {
-    asm volatile(
-        "{\n\t.reg .pred p;\n\t"
-        "setp.ne.b32 p, %4, 0;\n\t"
-        "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
-        ::"r"(tmem_d), "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate) : "memory");
-}
-__device__ __forceinline__ void tc_ld16(uint32_t taddr, uint32_t* r) {
-    asm volatile(
-        "tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15}, [%16];"
-        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
-          "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
-        : "r"(taddr) : "memory");
-}
-__device__ __forceinline__ void tc_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
-
-__device__ __forceinline__ void cluster_sync_all() {
-    asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
-}
-__device__ __forceinline__ float ld_cluster_f32(uint32_t local_addr, uint32_t rank) {
-    uint32_t remote;
-    float v;
-    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(remote) : "r"(local_addr), "r"(rank));
-    asm volatile("ld.shared::cluster.f32 %0, [%1];" : "=f"(v) : "r"(remote) : "memory");
-    return v;
-}
-
-// Shared-memory operand descriptor: K-major tile, rows of 128 bytes, 128-byte swizzle,
-// 8-row groups 1024 bytes apart (SBO), descriptor version 1 (sm_100).
-__device__ __forceinline__ uint64_t make_smem_desc(uint32_t saddr) {
-    return (uint64_t)((saddr >> 4) & 0x3FFFu) | (1ull << 16) | ((uint64_t)(1024 >> 4) << 32) | (1ull << 46) | (2ull << 61);
-}
-// Instruction descriptor: D float, A and B bfloat16, both K-major, M = 128, N = BN.
-__host__ __device__ constexpr uint32_t make_idesc(int bn) {
-    return (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(bn >> 3) << 17) | ((uint32_t)(TC_BM >> 4) << 24);
-}
 
 struct TcShared {                        // after the operand stages, in dynamic shared memory
     unsigned long long full[12];
@@ -335,54 +253,6 @@ __global__ void splitk_reduce_kernel(const float* __restrict__ ws, void* __restr
 }
 
 // ------------------------------------------------------------------ host side
-static PFN_cuTensorMapEncodeTiled_v12000 get_encode() {
-    static PFN_cuTensorMapEncodeTiled_v12000 fn = nullptr;
-    static std::once_flag once;
-    std::call_once(once, [] {
-        void* p = nullptr;
-        cudaDriverEntryPointQueryResult q;
-        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess &&
-            q == cudaDriverEntryPointSuccess)
-            fn = (PFN_cuTensorMapEncodeTiled_v12000)p;
-    });
-    return fn;
-}
-
-struct MapKey {
-    const void* ptr; long long rows, cols, ld; int box_rows;
-    bool operator==(const MapKey& o) const { return ptr == o.ptr && rows == o.rows && cols == o.cols && ld == o.ld && box_rows == o.box_rows; }
-};
-struct MapKeyHash {
-    size_t operator()(const MapKey& k) const {
-        size_t h = (size_t)k.ptr;
-        h = h * 1000003u ^ (size_t)k.rows; h = h * 1000003u ^ (size_t)k.cols;
-        h = h * 1000003u ^ (size_t)k.ld; h = h * 1000003u ^ (size_t)k.box_rows;
-        return h;
-    }
-};
-// A tensor map depends only on (address, extents, row stride, box), so a cached one never goes stale.
-static int get_map(const void* ptr, long long rows, long long cols, long long ld, int box_rows, CUtensorMap* out) {
-    static std::unordered_map<MapKey, CUtensorMap, MapKeyHash> cache;
-    static std::mutex mu;
-    MapKey key{ptr, rows, cols, ld, box_rows};
-    std::lock_guard<std::mutex> g(mu);
-    auto it = cache.find(key);
-    if (it != cache.end()) { *out = it->second; return 0; }
-    auto enc = get_encode();
-    if (!enc) RB_REFUSE("gemm: the driver offers no cuTensorMapEncodeTiled");
-    cuuint64_t dims[2] = {(cuuint64_t)cols, (cuuint64_t)rows};
-    cuuint64_t strides[1] = {(cuuint64_t)ld * 2};
-    cuuint32_t box[2] = {TC_BK, (cuuint32_t)box_rows};
-    cuuint32_t estr[2] = {1, 1};
-    CUresult r = enc(out, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(ptr), dims, strides, box, estr,
-                     CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
-                     CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-    if (r != CUDA_SUCCESS) RB_REFUSE("gemm: cuTensorMapEncodeTiled failed with %d (ptr %p rows %lld cols %lld ld %lld)", (int)r, ptr, rows, cols, ld);
-    if (cache.size() > 8192) cache.clear();
-    cache.emplace(key, *out);
-    return 0;
-}
-
 template <int BN, int STAGES, bool DUAL>
 static int launch_tc(const CUtensorMap& mw, const CUtensorMap& mx, void* C, float* ws, int T, int N, int K, long long ldc,
                      int out_mode, int splits, int kb_per_split, int csplit, cudaStream_t s) {
@@ -460,8 +330,8 @@ extern "C" int rb_gemm_bf16(const void* X, const void* W, void* C, int c_dtype, 
     }
     const int csplit = (splits > 1 && !via_ws) ? splits : 1;
     CUtensorMap mw, mx;
-    if (get_map(W, N, K, ldw, TC_BM, &mw)) return -1;
-    if (get_map(X, T, K, ldx, bn, &mx)) return -1;
+    if (rb_tensor_map_bf16(W, N, K, ldw, TC_BM, &mw)) return -1;
+    if (rb_tensor_map_bf16(X, T, K, ldx, bn, &mx)) return -1;
     const int out_mode = (splits > 1 && via_ws) ? 3 : mode;
     int rc;
     switch (bn) {
@@ -505,8 +375,8 @@ extern "C" int rb_gemm_bf16_swiglu(const void* X, const void* Wgu, void* act, in
     splits = rb_ceil_div(total_kb, kb_per_split);
     const int csplit = splits > 1 ? splits : 1;
     CUtensorMap mw, mx;
-    if (get_map(Wgu, 2LL * F, K, ldw, TC_BM, &mw)) return -1;
-    if (get_map(X, T, K, ldx, bn, &mx)) return -1;
+    if (rb_tensor_map_bf16(Wgu, 2LL * F, K, ldw, TC_BM, &mw)) return -1;
+    if (rb_tensor_map_bf16(X, T, K, ldx, bn, &mx)) return -1;
     switch (bn) {
         case 16: return launch_tc<16, 3, true>(mw, mx, act, nullptr, T, F, K, ldc, 0, splits, kb_per_split, csplit, s);
         case 32: return launch_tc<32, 3, true>(mw, mx, act, nullptr, T, F, K, ldc, 0, splits, kb_per_split, csplit, s);
@@ -519,7 +389,7 @@ extern "C" int rb_gemm_bf16_swiglu(const void* X, const void* Wgu, void* act, in
 // The error word of the tensor-core kernels (0 = none); synchronises the device.  With reset != 0 it is cleared.
 extern "C" int rb_gemm_error(int reset) {
     int v = 0;
-    if (cudaMemcpyFromSymbol(&v, g_tc_error, sizeof(int)) != cudaSuccess) return -1;
-    if (reset && v) { int z = 0; cudaMemcpyToSymbol(g_tc_error, &z, sizeof(int)); }
+    if (cudaMemcpyFromSymbol(&v, g_rb_kernel_error, sizeof(int)) != cudaSuccess) return -1;
+    if (reset && v) { int z = 0; cudaMemcpyToSymbol(g_rb_kernel_error, &z, sizeof(int)); }
     return v;
 }

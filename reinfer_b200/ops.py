@@ -209,6 +209,23 @@ def fa_decode(q, cache, block_table, cu_q, kv_len, out, first_entry: int, n_entr
         launches += 1                      # the merge kernel
 
 
+def fa_decode_tma(q, cache, block_table, cu_q, kv_len, out, first_entry: int, n_entries: int, first_tok: int, n_splits: int,
+                  QH: int, KH: int, d: int, page_size: int, window: int, scale: float) -> None:
+    """Split-K flash decoding with the key/value tiles brought in by TMA (page size a power of two >= 8)."""
+    part_o = part_lse = None
+    if n_splits > 1:
+        part_o = torch.empty(n_entries * QH * n_splits * d, dtype=torch.float32, device=q.device)
+        part_lse = torch.empty(n_entries * QH * n_splits, dtype=torch.float32, device=q.device)
+    _check(lib().rb_fa_decode_tma(_p(q), _p(cache), c_longlong(cache.shape[0]), _p(block_table), _p(cu_q), _p(kv_len), _p(out),
+                                  _p(part_o), _p(part_lse), c_int(first_entry), c_int(n_entries), c_int(first_tok),
+                                  c_int(n_splits), c_int(QH), c_int(KH), c_int(d), c_int(page_size),
+                                  c_int(block_table.shape[1]), c_int(window), c_float(scale), _stream()), "fa_decode_tma")
+
+
+def tma_pages(page_size: int) -> bool:
+    return page_size >= 8 and page_size & (page_size - 1) == 0
+
+
 def fa_prefill(q, cache, block_table, cu_q, kv_len, out, first_entry: int, n_entries: int, n_tiles: int,
                QH: int, KH: int, d: int, page_size: int, window: int, scale: float) -> None:
     """Paged causal flash attention (tensor cores) for entries that bring several tokens."""
@@ -217,6 +234,7 @@ def fa_prefill(q, cache, block_table, cu_q, kv_len, out, first_entry: int, n_ent
                                c_int(block_table.shape[1]), c_int(window), c_float(scale), _stream()), "fa_prefill")
 
 
+USE_TMA_ATTENTION = os.environ.get("REINFER_B200_TMA_ATTENTION", "1") != "0"
 FA_TARGET_CTAS = 296                       # two CTAs for each of the 148 SMs
 
 
@@ -237,8 +255,9 @@ def attention(ctx, q: torch.Tensor, cache: torch.Tensor, group, out: torch.Tenso
         ctas = n_dec * KH * (QH // KH // gc)
         tiles = -(-ctx.max_kv_len // 64)
         n_splits = max(1, min(FA_TARGET_CTAS // ctas, tiles, 64))     # one full wave at most
-        fa_decode(q, cache, group.block_table, ctx.cu_q, ctx.kv_len, out, 0, n_dec, 0, n_splits, QH, KH, d,
-                  group.page_size, window, scale)
+        decode = fa_decode_tma if (tma_pages(group.page_size) and USE_TMA_ATTENTION) else fa_decode
+        decode(q, cache, group.block_table, ctx.cu_q, ctx.kv_len, out, 0, n_dec, 0, n_splits, QH, KH, d,
+               group.page_size, window, scale)
     if E > n_dec:
         tpt = 64 // gc
         n_tiles = sum(-(-(ctx.q_start[e + 1] - ctx.q_start[e]) // tpt) for e in range(n_dec, E))
@@ -304,7 +323,9 @@ def gemm_bf16_swiglu(a: torch.Tensor, w_gate_up: torch.Tensor, out: torch.Tensor
 def kernel_error(reset: bool = True) -> int:
     """The error word that a kernel sets when one of its bounded waits gives up (0 = none).
     Synchronises the device."""
-    return int(lib().rb_gemm_error(c_int(int(reset))))
+    a = int(lib().rb_gemm_error(c_int(int(reset))))
+    b = int(lib().rb_attn_error(c_int(int(reset))))
+    return a or b
 
 
 def sample_params_size() -> int:

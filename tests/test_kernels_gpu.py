@@ -289,7 +289,8 @@ def test_attention_finds_one_far_key():
 
 
 @pytest.mark.parametrize("QH,KH,d,page", [(4, 2, 16, 16), (6, 2, 32, 8), (14, 2, 64, 4), (5, 5, 80, 32), (8, 1, 128, 16),
-                                          (32, 8, 128, 16), (32, 1, 64, 16), (3, 1, 256, 64), (6, 3, 24, 8)])
+                                          (32, 8, 128, 16), (32, 1, 64, 16), (3, 1, 256, 64), (6, 3, 24, 8), (8, 2, 128, 128),
+                                          (4, 4, 192, 16)])
 @pytest.mark.parametrize("window", [0, 37])
 def test_flash_prefill_and_decode_against_plain(QH, KH, d, page, window):
     """The tensor-core kernels on a batch that mixes decode entries and prompt portions which
@@ -306,9 +307,11 @@ def test_flash_prefill_and_decode_against_plain(QH, KH, d, page, window):
     cu_q = torch.tensor(cu, dtype=torch.int32, device=DEV)
     kv_len = torch.tensor(lens, dtype=torch.int32, device=DEV)
     gc = ops.fa_group_chunk(QH // KH)
-    for n_splits in (1, 3, 8):
+    decoders = [ops.fa_decode] + ([ops.fa_decode_tma] if ops.tma_pages(page) else [])
+    for n_splits, decode in [(n, f) for n in (1, 3, 8) for f in decoders]:
         out = torch.full_like(s["q"], float("nan"))
-        ops.fa_decode(s["q"], s["cache"], s["bt"], cu_q, kv_len, out, 0, 4, 0, n_splits, QH, KH, d, page, window, scale)
+        decode(s["q"], s["cache"], s["bt"], cu_q, kv_len, out, 0, 4, 0, n_splits, QH, KH, d, page, window, scale)
+        assert ops.kernel_error() == 0
         tpt = 64 // gc
         n_tiles = sum(-(-n // tpt) for n in q_lens[4:])
         ops.fa_prefill(s["q"], s["cache"], s["bt"], cu_q, kv_len, out, 4, 3, n_tiles, QH, KH, d, page, window, scale)
@@ -328,9 +331,9 @@ def test_flash_decode_finds_one_far_key_across_splits():
         pg, off = int(s["bt"][0, far // page]), far % page
         q[0] = 0.0; q[0, :, 3] = 40.0
         cache[pg, 0, :, off, 3] = 40.0
-        for n_splits in (1, 5, 47):
+        for n_splits, decode in [(n, f) for n in (1, 5, 47) for f in (ops.fa_decode, ops.fa_decode_tma)]:
             out = torch.empty_like(q)
-            ops.fa_decode(q, cache, s["bt"], cu_q, kv_len, out, 0, 1, 0, n_splits, QH, KH, d, page, 0, 1.0)
+            decode(q, cache, s["bt"], cu_q, kv_len, out, 0, 1, 0, n_splits, QH, KH, d, page, 0, 1.0)
             want = cache[pg, 1, :, off].float()
             for h in range(QH):
                 assert torch.allclose(out[0, h].float(), want[h // 4], atol=2e-2), (far, n_splits, h)
