@@ -32,6 +32,8 @@ HERE = os.path.dirname(os.path.abspath(__file__))
 ARCH = "sm_100a"
 FLAGS = ["-std=c++17", "-O3", "-lineinfo", "-gencode", "arch=compute_100a,code=sm_100a",
          "-Xcompiler", "-fPIC", "--expt-relaxed-constexpr"]
+# extra compiler flags (e.g. -DRB_TIMELINE for the kernels' phase timestamps); part of the build key
+FLAGS += [f for f in os.environ.get("REINFER_B200_NVCC_FLAGS", "").split() if f]
 LIB_PREFIX = "libreinfer_b200_"
 
 

@@ -27,6 +27,24 @@
 #define TC_BK 64             // K elements per stage (128 bytes: one swizzle row)
 #define TC_THREADS 192       // warp 0: TMA, warp 1: MMA + tensor memory, warps 2..5: epilogue
 
+// With -DRB_TIMELINE every CTA writes globaltimer stamps of its phases (ns) to a buffer given by
+// rb_gemm_timeline(): [cta][8] = start, set-up done, first tile landed, all MMAs issued, accumulator
+// ready, epilogue stored/parked, cluster reduction done, end.  A development aid, off by default.
+#ifdef RB_TIMELINE
+__device__ unsigned long long* g_tc_timeline = nullptr;
+__device__ __forceinline__ unsigned long long tl_now() {
+    unsigned long long t;
+    asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
+    return t;
+}
+#define TL(slot) do { if (g_tc_timeline) g_tc_timeline[(size_t)((blockIdx.z * gridDim.y + blockIdx.y) * gridDim.x + blockIdx.x) * 8 + (slot)] = tl_now(); } while (0)
+extern "C" int rb_gemm_timeline(unsigned long long* buf) {
+    return (int)cudaMemcpyToSymbol(g_tc_timeline, &buf, sizeof(buf));
+}
+#else
+#define TL(slot) do { } while (0)
+#endif
+
 struct TcShared {                        // after the operand stages, in dynamic shared memory
     unsigned long long full[12];
     unsigned long long empty[12];
@@ -63,6 +81,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
     volatile int* abort_flag = &sh->abort_flag;
 
     if (threadIdx.x == 0) {
+        TL(0);
         for (int s = 0; s < STAGES; ++s) { mbar_init(smem_u32(&sh->full[s]), 1); mbar_init(smem_u32(&sh->empty[s]), 1); }
         mbar_init(smem_u32(&sh->acc_full), 1);
         sh->abort_flag = 0;
@@ -77,6 +96,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
     __syncthreads();
     tc_fence_after();
     const uint32_t tmem = sh->tmem_base;
+    if (threadIdx.x == 0) TL(1);
     int issued = 0;                                   // producer: k-blocks whose loads were issued
 
     if (warp == 0) {
@@ -118,6 +138,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
                 const uint32_t round = kb / STAGES;
                 ok = mbar_wait(smem_u32(&sh->full[s]), round & 1, abort_flag, 2);
                 if (!ok) break;
+                if (kb == 0) TL(2);
                 tc_fence_after();
                 const uint32_t a = smem_base + s * STAGE_BYTES;
                 const uint64_t da = make_smem_desc(a), db = make_smem_desc(a + W_BYTES);
@@ -130,6 +151,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
                 tc_commit(smem_u32(&sh->empty[s]));                   // frees the stage when these MMAs are done
             }
             if (ok) tc_commit(smem_u32(&sh->acc_full));
+            TL(3);
         }
     } else {
         // epilogue: warp w may read tensor-memory lanes 32*(w%4) .. +31
@@ -138,6 +160,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
         pdl_wait();                                            // C may still be in use by the kernels before
         if (mbar_wait(smem_u32(&sh->acc_full), 0, abort_flag, 3)) {
             tc_fence_after();
+            if (threadIdx.x == 64) TL(4);
 #pragma unroll 1
             for (int c0 = 0; c0 < BN; c0 += 16) {
                 if (t0 + c0 >= T) break;                               // warp-uniform
@@ -188,6 +211,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
     }
     tc_fence_before();
     __syncthreads();
+    if (threadIdx.x == 0) TL(5);
     if (*abort_flag && threadIdx.x == 0) {
         // loads that were issued but never consumed still write this CTA's shared memory: wait for them
         for (int kb = max(0, issued - STAGES); kb < issued; ++kb) {
@@ -201,37 +225,45 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
         // every CTA of the cluster reaches both barriers, whatever happened before
         cluster_sync_all();                                    // all accumulators are parked
         if (warp >= 2 && !*abort_flag) {
-            // reduce-scatter: CTA `split` sums and stores the tokens c = split, split + csplit, ...;
-            // the partial sums of all ranks are fetched first (independent loads), then added in rank order
-            const int q = warp & 3;
-            const int fl = q * 32 + lane, feat = n0 + fl;
-            if (feat < N) {
-                const uint32_t mine = smem_base + (uint32_t)fl * 4;
-                for (int c = split; c < BN && t0 + c < T; c += csplit) {
-                    float part[8];
+            // reduce-scatter: CTA `split` sums and stores the tokens c = split, split + csplit, ...  A thread
+            // takes four neighbouring features (one 16-byte load per rank over distributed shared memory),
+            // 32 threads a token, the four epilogue warps four tokens at once; every rank's partial sums are
+            // fetched before the first is added, and they are added in rank order.
+            const int et = threadIdx.x - 64;                       // 0..127
+            const int f4 = (et & 31) * 4, tsub = et >> 5;
+            const int feat = n0 + f4;
+            for (int cb = split + tsub * csplit; cb < BN && t0 + cb < T; cb += 4 * csplit) {
+                float4 part[8], part2[8];
+                const uint32_t mine = smem_base + (uint32_t)(cb * TC_BM + f4) * 4;
 #pragma unroll
-                    for (int r = 0; r < 8; ++r)
-                        part[r] = r < csplit ? ld_cluster_f32(mine + (uint32_t)c * TC_BM * 4, (uint32_t)r) : 0.0f;
-                    float v = part[0];
+                for (int r = 0; r < 8; ++r) {
+                    part[r] = r < csplit ? ld_cluster_f32x4(mine, (uint32_t)r) : make_float4(0.f, 0.f, 0.f, 0.f);
+                    if (DUAL) part2[r] = r < csplit ? ld_cluster_f32x4(mine + (uint32_t)BN * TC_BM * 4, (uint32_t)r) : make_float4(0.f, 0.f, 0.f, 0.f);
+                }
+                float v[4] = {part[0].x, part[0].y, part[0].z, part[0].w};
 #pragma unroll
-                    for (int r = 1; r < 8; ++r) v += part[r];
-                    const size_t at = (size_t)(t0 + c) * ldc + feat;
-                    if (DUAL) {
+                for (int r = 1; r < 8; ++r) { v[0] += part[r].x; v[1] += part[r].y; v[2] += part[r].z; v[3] += part[r].w; }
+                if (DUAL) {
+                    float u[4] = {part2[0].x, part2[0].y, part2[0].z, part2[0].w};
 #pragma unroll
-                        for (int r = 0; r < 8; ++r)
-                            part[r] = r < csplit ? ld_cluster_f32(mine + (uint32_t)(BN + c) * TC_BM * 4, (uint32_t)r) : 0.0f;
-                        float u = part[0];
+                    for (int r = 1; r < 8; ++r) { u[0] += part2[r].x; u[1] += part2[r].y; u[2] += part2[r].z; u[3] += part2[r].w; }
 #pragma unroll
-                        for (int r = 1; r < 8; ++r) u += part[r];
-                        ((bf16*)C)[at] = __float2bfloat16_rn(v / (1.0f + expf(-v)) * u);
-                    } else if (out_mode == 0) ((bf16*)C)[at] = __float2bfloat16_rn(v);
-                    else if (out_mode == 1) ((float*)C)[at] = v;
-                    else ((float*)C)[at] += v;
+                    for (int i = 0; i < 4; ++i) v[i] = v[i] / (1.0f + expf(-v[i])) * u[i];
+                }
+                const size_t at = (size_t)(t0 + cb) * ldc + feat;
+#pragma unroll
+                for (int i = 0; i < 4; ++i) {
+                    if (feat + i >= N) break;
+                    if (DUAL || out_mode == 0) ((bf16*)C)[at + i] = __float2bfloat16_rn(v[i]);
+                    else if (out_mode == 1) ((float*)C)[at + i] = v[i];
+                    else ((float*)C)[at + i] += v[i];
                 }
             }
         }
+        if (threadIdx.x == 64) TL(6);
         cluster_sync_all();                                    // nobody leaves while its memory is being read
     }
+    if (threadIdx.x == 0) TL(7);
     if (warp == 1) {
         tc_fence_after();
         asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(TMEM_COLS) : "memory");
@@ -253,9 +285,38 @@ __global__ void splitk_reduce_kernel(const float* __restrict__ ws, void* __restr
 }
 
 // ------------------------------------------------------------------ host side
+// How many CTAs of this kernel can be resident at once when launched as clusters of `sp` (1: no cluster).
 template <int BN, int STAGES, bool DUAL>
-static int launch_tc(const CUtensorMap& mw, const CUtensorMap& mx, void* C, float* ws, int T, int N, int K, long long ldc,
-                     int out_mode, int splits, int kb_per_split, int csplit, cudaStream_t s) {
+static int tc_capacity(int sp, size_t smem) {
+    static int cache[9] = {0, 0, 0, 0, 0, 0, 0, 0, 0};
+    if (cache[sp]) return cache[sp];
+    int n = 0;
+    if (sp == 1) {
+        int per_sm = 0, sms = 0, dev = 0;
+        cudaGetDevice(&dev);
+        cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+        if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, gemm_tc_kernel<BN, STAGES, DUAL>, TC_THREADS, smem) == cudaSuccess)
+            n = per_sm * sms;
+    } else {
+        cudaLaunchConfig_t cfg = {};
+        cfg.gridDim = dim3(1, 1, sp); cfg.blockDim = dim3(TC_THREADS); cfg.dynamicSmemBytes = smem;
+        cudaLaunchAttribute attr[1];
+        attr[0].id = cudaLaunchAttributeClusterDimension;
+        attr[0].val.clusterDim.x = 1; attr[0].val.clusterDim.y = 1; attr[0].val.clusterDim.z = sp;
+        cfg.attrs = attr; cfg.numAttrs = 1;
+        int clusters = 0;
+        if (cudaOccupancyMaxActiveClusters(&clusters, gemm_tc_kernel<BN, STAGES, DUAL>, &cfg) == cudaSuccess) n = clusters * sp;
+    }
+    (void)cudaGetLastError();
+    if (n <= 0) n = 148;                                            // unknown: assume one CTA per SM
+    cache[sp] = n;
+    return n;
+}
+
+// want_splits: 0 = choose; > 0 = that many through a cluster (at most 8); < 0 = that many through the workspace.
+template <int BN, int STAGES, bool DUAL>
+static int launch_tc(const CUtensorMap& mw, const CUtensorMap& mx, void* C, float* ws, long long ws_floats, int T, int N, int K,
+                     long long ldc, int mode, int want_splits, cudaStream_t s) {
     constexpr size_t smem = (size_t)STAGES * ((DUAL ? 2 : 1) * TC_BM * TC_BK * 2 + BN * TC_BK * 2) + sizeof(TcShared) + 1024;
     static bool configured = false;
     if (!configured) {
@@ -263,8 +324,46 @@ static int launch_tc(const CUtensorMap& mw, const CUtensorMap& mx, void* C, floa
         if (e != cudaSuccess) return (int)e;
         configured = true;
     }
+    const int total_kb = rb_ceil_div(K, TC_BK);
+    const int t_tiles = rb_ceil_div(T, BN), n_tiles = rb_ceil_div(N, TC_BM);
+    const int tiles = t_tiles * n_tiles;
+    int splits = 1;
+    bool via_ws = false;
+    if (want_splits > 0) splits = want_splits;
+    else if (want_splits < 0) { splits = -want_splits; via_ws = true; }
+    else if (t_tiles == 1) {
+        // A weight-streaming launch (one token tile).  Estimate, for every split count that leaves >= 4
+        // k-blocks per CTA, waves x (fixed cost + the time its resident CTAs need to stream their share at
+        // full bandwidth) and take the least.  The capacity is what the device says can be resident as
+        // clusters of that size - fewer than SMs x CTAs/SM when clusters do not tile the GPCs.
+        const double kb_us = (double)(TC_BM * TC_BK * 2 * (DUAL ? 2 : 1)) / 6.5e6;   // one k-block of weights at 6.5 TB/s
+        double best = 1e30;
+        for (int sp = 1; sp <= 8 && total_kb / sp >= 4; ++sp) {
+            const int cap = tc_capacity<BN, STAGES, DUAL>(sp, smem);
+            const long long ctas = (long long)tiles * sp;
+            const long long waves = (ctas + cap - 1) / cap;
+            const long long resident = ctas < cap ? ctas : cap;
+            const double kbs = (double)rb_ceil_div(total_kb, sp);
+            const double shared_us = kbs * kb_us * (double)resident;        // all resident CTAs at the device's bandwidth
+            const double alone_us = kbs * kb_us * 6.5e6 / 45e3;              // one CTA pulls about 45 GB/s at most
+            const double cost = (double)waves * (6.0 + (sp > 1 ? 3.0 : 0.0) + (shared_us > alone_us ? shared_us : alone_us));
+            if (cost < best - 0.25) { best = cost; splits = sp; }
+        }
+    }
+    if (splits > total_kb) splits = total_kb;
+    int kb_per_split = rb_ceil_div(total_kb, splits);
+    splits = rb_ceil_div(total_kb, kb_per_split);                   // no empty split
+    if (splits > 8) via_ws = true;                                  // larger than a portable cluster
+    if (DUAL && via_ws) RB_REFUSE("gemm_swiglu: more than 8 splits are not supported");
+    if (via_ws) {
+        while (splits > 1 && (!ws || (long long)splits * T * N > ws_floats)) --splits;
+        kb_per_split = rb_ceil_div(total_kb, splits);
+        splits = rb_ceil_div(total_kb, kb_per_split);
+    }
+    const int csplit = (splits > 1 && !via_ws) ? splits : 1;
+    const int out_mode = (splits > 1 && via_ws) ? 3 : mode;
     cudaLaunchConfig_t cfg = {};
-    cfg.gridDim = dim3(rb_ceil_div(T, BN), rb_ceil_div(N, TC_BM), splits);
+    cfg.gridDim = dim3(t_tiles, n_tiles, splits);
     cfg.blockDim = dim3(TC_THREADS);
     cfg.dynamicSmemBytes = smem;
     cfg.stream = s;
@@ -284,11 +383,19 @@ static int launch_tc(const CUtensorMap& mw, const CUtensorMap& mx, void* C, floa
     cfg.numAttrs = na;
     cudaError_t e = cudaLaunchKernelEx(&cfg, gemm_tc_kernel<BN, STAGES, DUAL>, mw, mx, C, ws, T, N, K, ldc, out_mode, kb_per_split, csplit);
     if (e != cudaSuccess) { (void)cudaGetLastError(); return (int)e; }
-    return RB_LAUNCH_RESULT();
+    int rc = RB_LAUNCH_RESULT();
+    if (rc) return rc;
+    if (splits > 1 && via_ws) {
+        const long long total = (long long)T * N;
+        return rb_launch(splitk_reduce_kernel, dim3(rb_ceil_div(total, 256)), dim3(256), 0, s, (const float*)ws, C, T, N, ldc, splits, mode);
+    }
+    return 0;
 }
 
+static int tc_bn(int T) { return T <= 16 ? 16 : T <= 32 ? 32 : T <= 64 ? 64 : T <= 128 ? 128 : 256; }
+
 // X [T,K] bf16 (row stride ldx), W [N,K] bf16 (row stride ldw), C [T,N] bf16 or float (row stride ldc).
-// ws: float workspace of ws_floats elements for split-K partials (may be null: no split).
+// ws: float workspace of ws_floats elements for split-K partials beyond a cluster (may be null).
 extern "C" int rb_gemm_bf16(const void* X, const void* W, void* C, int c_dtype, int accumulate, int T, int N, int K,
                             long long ldx, long long ldw, long long ldc, float* ws, long long ws_floats,
                             int force_splits, void* stream) {
@@ -300,53 +407,17 @@ extern "C" int rb_gemm_bf16(const void* X, const void* W, void* C, int c_dtype, 
     if (c_dtype != RB_F32 && c_dtype != RB_BF16) RB_REFUSE("gemm: destination dtype %d", c_dtype);
     cudaStream_t s = (cudaStream_t)stream;
     const int mode = accumulate ? 2 : (c_dtype == RB_F32 ? 1 : 0);
-    const int bn = T <= 16 ? 16 : T <= 32 ? 32 : T <= 64 ? 64 : T <= 128 ? 128 : 256;
-    const int total_kb = rb_ceil_div(K, TC_BK);
-    const int ctas = rb_ceil_div(T, bn) * rb_ceil_div(N, TC_BM);
-    int splits = 1;
-    bool via_ws = false;                                           // force_splits < 0: that many splits through the workspace
-    if (force_splits > 0) splits = force_splits;
-    else if (force_splits < 0) { splits = -force_splits; via_ws = true; }
-    else if (bn <= 128) {
-        // a weight-streaming launch: fill whole waves of the 148 SMs (x 2 resident CTAs for narrow
-        // tiles).  Among the split counts that leave >= 4 k-blocks per CTA take the one whose last
-        // wave is fullest.
-        const int slots = bn <= 64 ? 296 : 148;
-        double best = 0.0;
-        for (int sp = 1; sp <= 8 && total_kb / sp >= 4; ++sp) {
-            const long long n = (long long)ctas * sp;
-            const double eff = (double)n / (double)(((n + slots - 1) / slots) * slots);
-            if (eff > best + 0.03) { best = eff; splits = sp; }
-        }
-    }
-    if (splits > total_kb) splits = total_kb;
-    int kb_per_split = rb_ceil_div(total_kb, splits);
-    splits = rb_ceil_div(total_kb, kb_per_split);                   // no empty split
-    if (splits > 8) via_ws = true;                                  // larger than a portable cluster
-    if (via_ws) {
-        while (splits > 1 && (!ws || (long long)splits * T * N > ws_floats)) --splits;
-        kb_per_split = rb_ceil_div(total_kb, splits);
-        splits = rb_ceil_div(total_kb, kb_per_split);
-    }
-    const int csplit = (splits > 1 && !via_ws) ? splits : 1;
+    const int bn = tc_bn(T);
     CUtensorMap mw, mx;
     if (rb_tensor_map_bf16(W, N, K, ldw, TC_BM, &mw)) return -1;
     if (rb_tensor_map_bf16(X, T, K, ldx, bn, &mx)) return -1;
-    const int out_mode = (splits > 1 && via_ws) ? 3 : mode;
-    int rc;
     switch (bn) {
-        case 16: rc = launch_tc<16, 6, false>(mw, mx, C, ws, T, N, K, ldc, out_mode, splits, kb_per_split, csplit, s); break;
-        case 32: rc = launch_tc<32, 5, false>(mw, mx, C, ws, T, N, K, ldc, out_mode, splits, kb_per_split, csplit, s); break;
-        case 64: rc = launch_tc<64, 4, false>(mw, mx, C, ws, T, N, K, ldc, out_mode, splits, kb_per_split, csplit, s); break;
-        case 128: rc = launch_tc<128, 5, false>(mw, mx, C, ws, T, N, K, ldc, out_mode, splits, kb_per_split, csplit, s); break;
-        default: rc = launch_tc<256, 4, false>(mw, mx, C, ws, T, N, K, ldc, out_mode, splits, kb_per_split, csplit, s); break;
+        case 16: return launch_tc<16, 6, false>(mw, mx, C, ws, ws_floats, T, N, K, ldc, mode, force_splits, s);
+        case 32: return launch_tc<32, 5, false>(mw, mx, C, ws, ws_floats, T, N, K, ldc, mode, force_splits, s);
+        case 64: return launch_tc<64, 4, false>(mw, mx, C, ws, ws_floats, T, N, K, ldc, mode, force_splits, s);
+        case 128: return launch_tc<128, 5, false>(mw, mx, C, ws, ws_floats, T, N, K, ldc, mode, force_splits, s);
+        default: return launch_tc<256, 4, false>(mw, mx, C, ws, ws_floats, T, N, K, ldc, mode, force_splits, s);
     }
-    if (rc) return rc;
-    if (splits > 1 && via_ws) {
-        const long long total = (long long)T * N;
-        return rb_launch(splitk_reduce_kernel, dim3(rb_ceil_div(total, 256)), dim3(256), 0, s, (const float*)ws, C, T, N, ldc, splits, mode);
-    }
-    return 0;
 }
 
 // act[T,F] (bfloat16) = silu(X Wg^T) * (X Wu^T) for Wgu = [Wg; Wu] of shape [2F, K]: one product with two
@@ -358,31 +429,16 @@ extern "C" int rb_gemm_bf16_swiglu(const void* X, const void* Wgu, void* act, in
     if ((ldx % 8) || (ldw % 8) || ((uintptr_t)X & 15) || ((uintptr_t)Wgu & 15))
         RB_REFUSE("gemm_swiglu: TMA needs 16-byte aligned operands and row strides (ldx %lld, ldw %lld)", ldx, ldw);
     cudaStream_t s = (cudaStream_t)stream;
-    const int bn = T <= 16 ? 16 : T <= 32 ? 32 : T <= 64 ? 64 : T <= 128 ? 128 : 256;
-    const int total_kb = rb_ceil_div(K, TC_BK);
-    const int ctas = rb_ceil_div(T, bn) * rb_ceil_div(F, TC_BM);
-    int splits = 1;
-    if (bn <= 128) {
-        const int slots = bn <= 32 ? 296 : 148;
-        double best = 0.0;
-        for (int sp = 1; sp <= 8 && total_kb / sp >= 4; ++sp) {
-            const long long n = (long long)ctas * sp;
-            const double eff = (double)n / (double)(((n + slots - 1) / slots) * slots);
-            if (eff > best + 0.03) { best = eff; splits = sp; }
-        }
-    }
-    int kb_per_split = rb_ceil_div(total_kb, splits);
-    splits = rb_ceil_div(total_kb, kb_per_split);
-    const int csplit = splits > 1 ? splits : 1;
+    const int bn = tc_bn(T);
     CUtensorMap mw, mx;
     if (rb_tensor_map_bf16(Wgu, 2LL * F, K, ldw, TC_BM, &mw)) return -1;
     if (rb_tensor_map_bf16(X, T, K, ldx, bn, &mx)) return -1;
     switch (bn) {
-        case 16: return launch_tc<16, 3, true>(mw, mx, act, nullptr, T, F, K, ldc, 0, splits, kb_per_split, csplit, s);
-        case 32: return launch_tc<32, 3, true>(mw, mx, act, nullptr, T, F, K, ldc, 0, splits, kb_per_split, csplit, s);
-        case 64: return launch_tc<64, 4, true>(mw, mx, act, nullptr, T, F, K, ldc, 0, splits, kb_per_split, csplit, s);
-        case 128: return launch_tc<128, 4, true>(mw, mx, act, nullptr, T, F, K, ldc, 0, splits, kb_per_split, csplit, s);
-        default: return launch_tc<256, 3, true>(mw, mx, act, nullptr, T, F, K, ldc, 0, splits, kb_per_split, csplit, s);
+        case 16: return launch_tc<16, 3, true>(mw, mx, act, nullptr, 0, T, F, K, ldc, 0, 0, s);
+        case 32: return launch_tc<32, 3, true>(mw, mx, act, nullptr, 0, T, F, K, ldc, 0, 0, s);
+        case 64: return launch_tc<64, 4, true>(mw, mx, act, nullptr, 0, T, F, K, ldc, 0, 0, s);
+        case 128: return launch_tc<128, 4, true>(mw, mx, act, nullptr, 0, T, F, K, ldc, 0, 0, s);
+        default: return launch_tc<256, 3, true>(mw, mx, act, nullptr, 0, T, F, K, ldc, 0, 0, s);
     }
 }
 

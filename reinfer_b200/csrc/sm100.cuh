@@ -79,6 +79,14 @@ __device__ __forceinline__ float ld_cluster_f32(uint32_t local_addr, uint32_t ra
     return v;
 }
 
+__device__ __forceinline__ float4 ld_cluster_f32x4(uint32_t local_addr, uint32_t rank) {
+    uint32_t remote;
+    float4 v;
+    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(remote) : "r"(local_addr), "r"(rank));
+    asm volatile("ld.shared::cluster.v4.f32 {%0,%1,%2,%3}, [%4];" : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w) : "r"(remote) : "memory");
+    return v;
+}
+
 // Shared-memory operand descriptor: K-major tile, rows of 128 bytes, 128-byte swizzle,
 // 8-row groups 1024 bytes apart (SBO), descriptor version 1 (sm_100).
 __device__ __forceinline__ uint64_t make_smem_desc(uint32_t saddr) {

@@ -235,6 +235,19 @@ def fa_prefill(q, cache, block_table, cu_q, kv_len, out, first_entry: int, n_ent
 
 
 USE_TMA_ATTENTION = os.environ.get("REINFER_B200_TMA_ATTENTION", "1") != "0"
+def decode_splits(ctas: int, tiles: int, slots: int = 296) -> int:
+    """How many CTAs share one (request, kv head)'s keys.  Model of the launch's time: waves of
+    `slots` resident CTAs, each CTA walking tiles/n tiles plus about 2.5 tile-times of fill, drain
+    and merge; the split count with the least estimate wins (ties to the smaller)."""
+    best, best_cost = 1, None
+    for n in range(1, max(1, min(64, tiles)) + 1):
+        waves = -(-ctas * n // slots)
+        cost = waves * (tiles / n + 2.5)
+        if best_cost is None or cost < best_cost - 1e-9:
+            best, best_cost = n, cost
+    return best
+
+
 FA_TARGET_CTAS = 296                       # two CTAs for each of the 148 SMs
 
 
@@ -254,7 +267,7 @@ def attention(ctx, q: torch.Tensor, cache: torch.Tensor, group, out: torch.Tenso
     if n_dec:
         ctas = n_dec * KH * (QH // KH // gc)
         tiles = -(-ctx.max_kv_len // 64)
-        n_splits = max(1, min(FA_TARGET_CTAS // ctas, tiles, 64))     # one full wave at most
+        n_splits = decode_splits(ctas, tiles)
         decode = fa_decode_tma if (tma_pages(group.page_size) and USE_TMA_ATTENTION) else fa_decode
         decode(q, cache, group.block_table, ctx.cu_q, ctx.kv_len, out, 0, n_dec, 0, n_splits, QH, KH, d,
                group.page_size, window, scale)
