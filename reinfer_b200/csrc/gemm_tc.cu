@@ -345,7 +345,7 @@ static int launch_tc(const CUtensorMap& mw, const CUtensorMap& mx, void* C, floa
             const long long resident = ctas < cap ? ctas : cap;
             const double kbs = (double)rb_ceil_div(total_kb, sp);
             const double shared_us = kbs * kb_us * (double)resident;        // all resident CTAs at the device's bandwidth
-            const double alone_us = kbs * kb_us * 6.5e6 / 45e3;              // one CTA pulls about 45 GB/s at most
+            const double alone_us = kbs * kb_us * 6.5e6 / 30e3;              // one CTA's pipeline sustains about 30 GB/s
             const double cost = (double)waves * (6.0 + (sp > 1 ? 3.0 : 0.0) + (shared_us > alone_us ? shared_us : alone_us));
             if (cost < best - 0.25) { best = cost; splits = sp; }
         }
