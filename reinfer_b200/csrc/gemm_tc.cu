@@ -327,11 +327,14 @@ static int launch_tc(const CUtensorMap& mw, const CUtensorMap& mx, void* C, floa
     const int total_kb = rb_ceil_div(K, TC_BK);
     const int t_tiles = rb_ceil_div(T, BN), n_tiles = rb_ceil_div(N, TC_BM);
     const int tiles = t_tiles * n_tiles;
+    // a cluster's CTAs park their accumulators ([tokens][128] floats, twice for DUAL) in the operand stages
+    constexpr size_t park_bytes = (size_t)(DUAL ? 2 : 1) * BN * TC_BM * sizeof(float);
+    constexpr bool can_park = park_bytes <= (size_t)STAGES * ((DUAL ? 2 : 1) * TC_BM * TC_BK * 2 + BN * TC_BK * 2);
     int splits = 1;
     bool via_ws = false;
-    if (want_splits > 0) splits = want_splits;
+    if (want_splits > 0) { splits = want_splits; via_ws = !can_park; }
     else if (want_splits < 0) { splits = -want_splits; via_ws = true; }
-    else if (t_tiles == 1) {
+    else if (t_tiles == 1 && can_park) {
         // A weight-streaming launch (one token tile).  Estimate, for every split count that leaves >= 4
         // k-blocks per CTA, waves x (fixed cost + the time its resident CTAs need to stream their share at
         // full bandwidth) and take the least.  The capacity is what the device says can be resident as
@@ -354,7 +357,7 @@ static int launch_tc(const CUtensorMap& mw, const CUtensorMap& mx, void* C, floa
     int kb_per_split = rb_ceil_div(total_kb, splits);
     splits = rb_ceil_div(total_kb, kb_per_split);                   // no empty split
     if (splits > 8) via_ws = true;                                  // larger than a portable cluster
-    if (DUAL && via_ws) RB_REFUSE("gemm_swiglu: more than 8 splits are not supported");
+    if (DUAL && via_ws) { splits = 1; via_ws = false; kb_per_split = total_kb; }   // two accumulators never go through the workspace
     if (via_ws) {
         while (splits > 1 && (!ws || (long long)splits * T * N > ws_floats)) --splits;
         kb_per_split = rb_ceil_div(total_kb, splits);

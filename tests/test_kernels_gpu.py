@@ -18,7 +18,7 @@ def rnd(*shape, dtype=torch.float32, scale=1.0, seed=0):
 
 @pytest.mark.parametrize("T,N,K", [(1, 128, 64), (1, 4096, 4096), (5, 311, 96), (16, 256, 128), (17, 384, 200),
                                    (33, 130, 72), (64, 1000, 512), (100, 128, 8), (129, 2048, 1024), (300, 520, 264),
-                                   (2048, 1536, 512), (8, 12288, 4096), (7, 4096, 12288)])
+                                   (2048, 1536, 512), (8, 12288, 4096), (7, 4096, 12288), (200, 512, 1024), (256, 384, 4096)])
 @pytest.mark.parametrize("mode", ["bf16", "f32", "acc"])
 def test_gemm_tensor_core(T, N, K, mode):
     from reinfer_b200 import ops
@@ -44,7 +44,8 @@ def test_gemm_tensor_core(T, N, K, mode):
 
 
 @pytest.mark.parametrize("T,F,K", [(1, 128, 64), (1, 12288, 4096), (8, 12288, 4096), (5, 160, 96), (17, 300, 200), (40, 1000, 512),
-                                   (64, 2048, 1024), (100, 130, 72), (129, 640, 264), (300, 520, 520), (2048, 1024, 512)])
+                                   (64, 2048, 1024), (100, 130, 72), (129, 640, 264), (300, 520, 520), (2048, 1024, 512),
+                                   (200, 512, 512), (130, 1024, 2048), (256, 256, 4096)])
 def test_gemm_swiglu_epilogue(T, F, K):
     from reinfer_b200 import ops
     a = rnd(T, K, dtype=torch.bfloat16, seed=1)
