@@ -307,6 +307,253 @@ fa_decode_tma_kernel(const __grid_constant__ CUtensorMap map_kv, const FtArgs a)
     }
 }
 
+// ------------------------------------------------------------------------------- prefill
+// Entries that bring several tokens.  A CTA owns 64 rows = 64/Gc tokens x Gc grouped query heads of one
+// kv head; each of the four consumer warps owns 16 rows and walks all 64 keys of every tile; the fifth
+// warp feeds the tiles by TMA as in the decode kernel.  Reads every page of the request, those that
+// earlier steps wrote included.  Q fragments stay in registers for head sizes up to 128.
+template <int HALVES, int NST>
+__global__ void __launch_bounds__(FT_THREADS)
+fa_prefill_tma_kernel(const __grid_constant__ CUtensorMap map_kv, const FtArgs a) {
+    constexpr int D = HALVES * 64;
+    constexpr int KV_BYTES = HALVES * FT_HALF_BYTES;
+    constexpr int STAGE = 2 * KV_BYTES;
+    constexpr int Q_HALF = 64 * 128;                           // 64 rows x 128 bytes
+    constexpr bool Q_IN_REGS = HALVES <= 2;
+    extern __shared__ __align__(1024) unsigned char smem_raw[];
+    unsigned char* smem = (unsigned char*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+    unsigned char* stages = smem;
+    unsigned char* sQ = smem + NST * STAGE;
+    FtShared* sh = (FtShared*)(sQ + HALVES * Q_HALF);
+    const uint32_t stages_u = smem_u32(stages), sQ_u = smem_u32(sQ);
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    volatile int* abort_flag = &sh->abort_flag;
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < NST; ++s) { mbar_init(smem_u32(&sh->full[s]), 1); mbar_init(smem_u32(&sh->empty[s]), FT_WARPS); }
+        sh->abort_flag = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    for (int i = threadIdx.x; i < (NST * STAGE + HALVES * Q_HALF) / 16; i += FT_THREADS)
+        reinterpret_cast<uint4*>(smem)[i] = make_uint4(0, 0, 0, 0);
+    __syncthreads();
+    pdl_trigger();
+    pdl_wait();
+
+    const int tpt = FT_BN / a.Gc;                              // tokens per CTA (64 rows)
+    int tile = blockIdx.x, e = a.first_entry, q_len = 0;
+    for (; e < a.first_entry + a.n_entries; ++e) {
+        q_len = a.cu_q[e + 1] - a.cu_q[e];
+        const int nt = (q_len + tpt - 1) / tpt;
+        if (tile < nt) break;
+        tile -= nt;
+    }
+    if (e >= a.first_entry + a.n_entries) return;              // uniform: the whole CTA leaves
+    const int q0 = tile * tpt;
+    const int n_tok = min(tpt, q_len - q0);
+    const int kh = blockIdx.y / a.chunks, chunk = blockIdx.y % a.chunks;
+    const int head0 = kh * (a.QH / a.KH) + chunk * a.Gc;
+    const int kv_end = a.kv_len[e];
+    const int start_pos = kv_end - q_len;
+    const int tok_base = a.cu_q[e] + q0;
+    const int* bt = a.block_table + (size_t)e * a.max_pages;
+    const int pos_min = start_pos + q0, pos_max = start_pos + q0 + n_tok - 1;
+    const int lo_min = a.window > 0 ? max(0, pos_min - a.window + 1) : 0;
+    const int t_begin = lo_min / FT_BN, t_end = pos_max / FT_BN + 1;
+    const int n_tiles = t_end - t_begin;
+
+    for (int i = threadIdx.x; i < n_tok * a.Gc * (a.d / 8); i += FT_THREADS) {
+        const int row = i / (a.d / 8), c = i % (a.d / 8);
+        const int ti = row / a.Gc, g = row % a.Gc;
+        const uint4 v = *reinterpret_cast<const uint4*>(a.q + ((size_t)(tok_base + ti) * a.QH + head0 + g) * a.d + c * 8);
+        *reinterpret_cast<uint4*>(sQ + ft_off(row, c, Q_HALF)) = v;
+    }
+    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+    __syncthreads();
+
+    const int box_rows = min(a.page_size, FT_BN);
+    const int subs = FT_BN / box_rows;
+    const int rows_per_page2 = 2 * a.KH * a.page_size;
+    int issued = 0;
+
+    float o[D / 8][4];
+#pragma unroll
+    for (int j = 0; j < D / 8; ++j) { o[j][0] = o[j][1] = o[j][2] = o[j][3] = 0.0f; }
+    float m[2] = {-INFINITY, -INFINITY}, l[2] = {0.0f, 0.0f};
+    const int r0 = (warp & 3) * 16 + (lane >> 2), r1 = r0 + 8;
+    const int ti0 = r0 / a.Gc, ti1 = r1 / a.Gc;
+
+    if (warp == FT_WARPS) {
+        int cached_first = 0, cached = -1;
+        bool have = false;
+        for (int it = 0; it < n_tiles; ++it) {
+            const int s = it % NST;
+            const int k0 = (t_begin + it) * FT_BN;
+            const int pi0 = k0 >> a.page_shift;
+            const int need_last = (k0 + (subs - 1) * box_rows) >> a.page_shift;
+            if (!have || need_last >= cached_first + 32) {
+                cached_first = pi0;
+                cached = (pi0 + lane < a.max_pages) ? bt[pi0 + lane] : -1;
+                have = true;
+            }
+            int pages[8];
+            int n_valid = 0;
+#pragma unroll
+            for (int u = 0; u < 8; ++u) {
+                const int key = k0 + u * box_rows;
+                const int pg = __shfl_sync(0xffffffffu, cached, ((key >> a.page_shift) - cached_first) & 31);
+                pages[u] = (u < subs && key < kv_end) ? pg : -1;
+                n_valid += pages[u] >= 0;
+            }
+            bool ok = true;
+            if (lane == 0) {
+                if (it >= NST) ok = mbar_wait(smem_u32(&sh->empty[s]), ((it / NST) & 1) ^ 1, abort_flag, 7);
+                if (ok) {
+                    const uint32_t full = smem_u32(&sh->full[s]);
+                    mbar_expect_tx(full, (uint32_t)(n_valid * 2 * HALVES * box_rows * 128));
+                    const uint32_t dst0 = stages_u + s * STAGE;
+#pragma unroll
+                    for (int u = 0; u < 8; ++u) {
+                        if (pages[u] >= 0) {
+                            const int key = k0 + u * box_rows;
+                            const int y = pages[u] * rows_per_page2 + kh * a.page_size + (key & (a.page_size - 1));
+#pragma unroll
+                            for (int h = 0; h < HALVES; ++h) {
+                                tma_load_2d(dst0 + h * FT_HALF_BYTES + u * box_rows * 128, &map_kv, h * 64, y, full);
+                                tma_load_2d(dst0 + KV_BYTES + h * FT_HALF_BYTES + u * box_rows * 128, &map_kv, h * 64,
+                                            y + a.KH * a.page_size, full);
+                            }
+                        }
+                    }
+                    issued = it + 1;
+                }
+            }
+            if (!__shfl_sync(0xffffffffu, (int)ok, 0)) break;
+        }
+    } else {
+        const int pos0 = ti0 < n_tok ? start_pos + q0 + ti0 : -1, pos1 = ti1 < n_tok ? start_pos + q0 + ti1 : -1;
+        const int lo0 = a.window > 0 ? max(0, pos0 - a.window + 1) : 0, lo1 = a.window > 0 ? max(0, pos1 - a.window + 1) : 0;
+        // keys beyond the last row of this warp are masked for all its rows: it may skip those tiles
+        const int warp_last_tok = min(n_tok - 1, (warp * 16 + 15) / a.Gc);
+        const int warp_t_end = (warp * 16) / a.Gc < n_tok ? (start_pos + q0 + warp_last_tok) / FT_BN + 1 : 0;
+        uint32_t qreg[Q_IN_REGS ? D / 16 : 1][4];
+        if (Q_IN_REGS) {
+#pragma unroll
+            for (int ks = 0; ks < D / 16; ++ks)
+                ft_ldsm_x4(qreg[ks], sQ_u + ft_off(warp * 16 + (lane & 7) + 8 * ((lane >> 3) & 1), ks * 2 + (lane >> 4), Q_HALF));
+        }
+        for (int it = 0; it < n_tiles; ++it) {
+            const int s = it % NST;
+            if (!mbar_wait(smem_u32(&sh->full[s]), (it / NST) & 1, abort_flag, 6)) break;
+            const uint32_t sK = stages_u + s * STAGE, sV = sK + KV_BYTES;
+            const int k0 = (t_begin + it) * FT_BN;
+            if (k0 + FT_BN > kv_end) {
+                for (int i = threadIdx.x; i < FT_BN * HALVES * 8; i += FT_WARPS * 32) {
+                    const int row = i / (HALVES * 8), c = i % (HALVES * 8);
+                    if (k0 + row >= kv_end) {
+                        *reinterpret_cast<uint4*>(stages + s * STAGE + ft_off(row, c, FT_HALF_BYTES)) = make_uint4(0, 0, 0, 0);
+                        *reinterpret_cast<uint4*>(stages + s * STAGE + KV_BYTES + ft_off(row, c, FT_HALF_BYTES)) = make_uint4(0, 0, 0, 0);
+                    }
+                }
+                asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+                asm volatile("bar.sync 1, %0;" ::"n"(FT_WARPS * 32) : "memory");
+            }
+            if (t_begin + it < warp_t_end) {
+                float sc[8][4];
+#pragma unroll
+                for (int j = 0; j < 8; ++j) { sc[j][0] = sc[j][1] = sc[j][2] = sc[j][3] = 0.0f; }
+#pragma unroll
+                for (int ks = 0; ks < D / 16; ++ks) {
+                    uint32_t qa[4];
+                    if (Q_IN_REGS) { qa[0] = qreg[ks][0]; qa[1] = qreg[ks][1]; qa[2] = qreg[ks][2]; qa[3] = qreg[ks][3]; }
+                    else ft_ldsm_x4(qa, sQ_u + ft_off(warp * 16 + (lane & 7) + 8 * ((lane >> 3) & 1), ks * 2 + (lane >> 4), Q_HALF));
+#pragma unroll
+                    for (int jp = 0; jp < 4; ++jp) {
+                        uint32_t kb[4];
+                        ft_ldsm_x4(kb, sK + ft_off(jp * 16 + (lane & 7) + 8 * (lane >> 4), ks * 2 + ((lane >> 3) & 1), FT_HALF_BYTES));
+                        ft_mma(sc[2 * jp], qa, kb[0], kb[1]);
+                        ft_mma(sc[2 * jp + 1], qa, kb[2], kb[3]);
+                    }
+                }
+                const bool need_mask = (k0 + FT_BN - 1 > min(pos0 < 0 ? -1 : pos0, pos1 < 0 ? -1 : pos1)) || (a.window > 0);
+                float mx0 = -INFINITY, mx1 = -INFINITY;
+#pragma unroll
+                for (int j = 0; j < 8; ++j) {
+                    const int key = k0 + j * 8 + 2 * (lane & 3);
+                    if (need_mask) {
+                        sc[j][0] = (key >= lo0 && key <= pos0) ? sc[j][0] * a.scale_log2 : -INFINITY;
+                        sc[j][1] = (key + 1 >= lo0 && key + 1 <= pos0) ? sc[j][1] * a.scale_log2 : -INFINITY;
+                        sc[j][2] = (key >= lo1 && key <= pos1) ? sc[j][2] * a.scale_log2 : -INFINITY;
+                        sc[j][3] = (key + 1 >= lo1 && key + 1 <= pos1) ? sc[j][3] * a.scale_log2 : -INFINITY;
+                    } else {
+                        sc[j][0] *= a.scale_log2; sc[j][1] *= a.scale_log2; sc[j][2] *= a.scale_log2; sc[j][3] *= a.scale_log2;
+                    }
+                    mx0 = fmaxf(mx0, fmaxf(sc[j][0], sc[j][1]));
+                    mx1 = fmaxf(mx1, fmaxf(sc[j][2], sc[j][3]));
+                }
+                mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, 1)); mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, 2));
+                mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, 1)); mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, 2));
+                const float mn0 = fmaxf(m[0], mx0), mn1 = fmaxf(m[1], mx1);
+                const float b0 = mn0 == -INFINITY ? 0.0f : mn0, b1 = mn1 == -INFINITY ? 0.0f : mn1;
+                const float c0 = exp2f(m[0] - b0), c1 = exp2f(m[1] - b1);
+                m[0] = mn0; m[1] = mn1;
+                float sum0 = 0.0f, sum1 = 0.0f;
+                uint32_t p[8][2];
+#pragma unroll
+                for (int j = 0; j < 8; ++j) {
+                    const float e0 = exp2f(sc[j][0] - b0), e1 = exp2f(sc[j][1] - b0);
+                    const float e2 = exp2f(sc[j][2] - b1), e3 = exp2f(sc[j][3] - b1);
+                    sum0 += e0 + e1; sum1 += e2 + e3;
+                    p[j][0] = ft_pack(e0, e1);
+                    p[j][1] = ft_pack(e2, e3);
+                }
+                l[0] = l[0] * c0 + sum0;
+                l[1] = l[1] * c1 + sum1;
+#pragma unroll
+                for (int j = 0; j < D / 8; ++j) { o[j][0] *= c0; o[j][1] *= c0; o[j][2] *= c1; o[j][3] *= c1; }
+#pragma unroll
+                for (int kk = 0; kk < 4; ++kk) {
+                    const uint32_t pa[4] = {p[2 * kk][0], p[2 * kk][1], p[2 * kk + 1][0], p[2 * kk + 1][1]};
+#pragma unroll
+                    for (int dp = 0; dp < D / 16; ++dp) {
+                        uint32_t vb[4];
+                        ft_ldsm_x4_trans(vb, sV + ft_off(kk * 16 + (lane & 7) + 8 * ((lane >> 3) & 1), dp * 2 + (lane >> 4), FT_HALF_BYTES));
+                        ft_mma(o[2 * dp], pa, vb[0], vb[1]);
+                        ft_mma(o[2 * dp + 1], pa, vb[2], vb[3]);
+                    }
+                }
+            }
+            __syncwarp();
+            if (lane == 0) mbar_arrive(smem_u32(&sh->empty[s]));
+        }
+    }
+    __syncthreads();
+    if (*abort_flag) {
+        if (threadIdx.x == FT_WARPS * 32)
+            for (int it = max(0, issued - NST); it < issued; ++it)
+                for (uint32_t k = 0; k < RB_SPIN_LIMIT; ++k)
+                    if (mbar_try(smem_u32(&sh->full[it % NST]), (it / NST) & 1)) break;
+        __syncthreads();
+        return;
+    }
+    if (warp == FT_WARPS) return;
+#pragma unroll
+    for (int i = 0; i < 2; ++i) {
+        l[i] += __shfl_xor_sync(0xffffffffu, l[i], 1);
+        l[i] += __shfl_xor_sync(0xffffffffu, l[i], 2);
+    }
+    const float inv0 = l[0] > 0.0f ? 1.0f / l[0] : 0.0f, inv1 = l[1] > 0.0f ? 1.0f / l[1] : 0.0f;
+#pragma unroll
+    for (int j = 0; j < D / 8; ++j) {
+        const int dim = j * 8 + 2 * (lane & 3);
+        if (dim >= a.d) continue;
+        if (ti0 < n_tok)
+            *reinterpret_cast<uint32_t*>(a.out + ((size_t)(tok_base + ti0) * a.QH + head0 + r0 % a.Gc) * a.d + dim) = ft_pack(o[j][0] * inv0, o[j][1] * inv0);
+        if (ti1 < n_tok)
+            *reinterpret_cast<uint32_t*>(a.out + ((size_t)(tok_base + ti1) * a.QH + head0 + r1 % a.Gc) * a.d + dim) = ft_pack(o[j][2] * inv1, o[j][3] * inv1);
+    }
+}
+
 // out[t, h, :] = sum_s w_s o_s / sum_s w_s,  w_s = 2^(lse_s - max lse), splits in ascending order
 __global__ void ft_merge_kernel(const float* __restrict__ part_o, const float* __restrict__ part_lse, bf16* __restrict__ out,
                                 int first_tok, int QH, int d, int n_splits) {
@@ -378,6 +625,46 @@ extern "C" int rb_fa_decode_tma(const void* q, const void* cache, long long num_
     if (rc || n_splits == 1) return rc;
     return rb_launch(ft_merge_kernel, dim3(n_entries, QH), dim3(128), 0, s, (const float*)part_o, (const float*)part_lse,
                      (bf16*)out, first_tok, QH, d, n_splits);
+}
+
+template <int HALVES, int NST>
+static int ft_launch_prefill(const CUtensorMap& map, const FtArgs& a, int n_tiles, cudaStream_t s) {
+    constexpr size_t smem = (size_t)NST * 2 * HALVES * FT_HALF_BYTES + HALVES * 64 * 128 + sizeof(FtShared) + 1024;
+    static bool done = false;
+    if (!done) {
+        cudaError_t e = cudaFuncSetAttribute(fa_prefill_tma_kernel<HALVES, NST>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        if (e != cudaSuccess) return (int)e;
+        done = true;
+    }
+    return rb_launch(fa_prefill_tma_kernel<HALVES, NST>, dim3(n_tiles, a.KH * a.chunks), dim3(FT_THREADS), smem, s, map, a);
+}
+
+// As rb_fa_prefill, with the key/value tiles brought in by TMA (page size a power of two >= 8).
+extern "C" int rb_fa_prefill_tma(const void* q, const void* cache, long long num_pages, const int* block_table, const int* cu_q,
+                                 const int* kv_len, void* out, int first_entry, int n_entries, int n_tiles, int QH, int KH, int d,
+                                 int page_size, int max_pages, int window, float scale, void* stream) {
+    if (n_entries <= 0 || n_tiles <= 0) return 0;
+    if (QH <= 0 || KH <= 0 || QH % KH) RB_REFUSE("attention: %d query heads over %d kv heads", QH, KH);
+    if (d <= 0 || d % 8 || d > 256) RB_REFUSE("attention (TMA): head_dim %d is not a multiple of 8 up to 256", d);
+    int shift = -1;
+    for (int s = 3; s < 16; ++s) if ((1 << s) == page_size) shift = s;
+    if (shift < 0) RB_REFUSE("attention (TMA): page size %d is not a power of two >= 8", page_size);
+    if (((uintptr_t)cache & 15) || ((uintptr_t)q & 15)) RB_REFUSE("attention (TMA): operands must be 16-byte aligned");
+    FtArgs a{};
+    a.q = (const bf16*)q; a.block_table = block_table; a.cu_q = cu_q; a.kv_len = kv_len; a.out = (bf16*)out;
+    a.QH = QH; a.KH = KH; a.d = d; a.page_size = page_size; a.page_shift = shift; a.max_pages = max_pages; a.window = window;
+    const int G = QH / KH;
+    a.Gc = 1;
+    for (int c = 16; c >= 1; --c) if (G % c == 0) { a.Gc = c; break; }
+    a.chunks = G / a.Gc; a.first_entry = first_entry; a.n_entries = n_entries; a.n_splits = 1;
+    a.scale_log2 = scale * 1.4426950408889634f;
+    CUtensorMap map;
+    const int box_rows = page_size < FT_BN ? page_size : FT_BN;
+    if (rb_tensor_map_bf16(cache, num_pages * 2LL * KH * page_size, d, d, box_rows, &map)) return -1;
+    cudaStream_t s = (cudaStream_t)stream;
+    if (d <= 64) return ft_launch_prefill<1, 4>(map, a, n_tiles, s);
+    if (d <= 128) return ft_launch_prefill<2, 2>(map, a, n_tiles, s);     // 82 KB: two CTAs per SM
+    return ft_launch_prefill<4, 2>(map, a, n_tiles, s);
 }
 
 extern "C" int rb_attn_error(int reset) {

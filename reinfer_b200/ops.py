@@ -222,6 +222,15 @@ def fa_decode_tma(q, cache, block_table, cu_q, kv_len, out, first_entry: int, n_
                                   c_int(block_table.shape[1]), c_int(window), c_float(scale), _stream()), "fa_decode_tma")
 
 
+def fa_prefill_tma(q, cache, block_table, cu_q, kv_len, out, first_entry: int, n_entries: int, n_tiles: int,
+                   QH: int, KH: int, d: int, page_size: int, window: int, scale: float) -> None:
+    """Paged causal flash attention with the key/value tiles brought in by TMA."""
+    _check(lib().rb_fa_prefill_tma(_p(q), _p(cache), c_longlong(cache.shape[0]), _p(block_table), _p(cu_q), _p(kv_len), _p(out),
+                                   c_int(first_entry), c_int(n_entries), c_int(n_tiles), c_int(QH), c_int(KH), c_int(d),
+                                   c_int(page_size), c_int(block_table.shape[1]), c_int(window), c_float(scale), _stream()),
+           "fa_prefill_tma")
+
+
 def tma_pages(page_size: int) -> bool:
     return page_size >= 8 and page_size & (page_size - 1) == 0
 
@@ -274,8 +283,9 @@ def attention(ctx, q: torch.Tensor, cache: torch.Tensor, group, out: torch.Tenso
     if E > n_dec:
         tpt = 64 // gc
         n_tiles = sum(-(-(ctx.q_start[e + 1] - ctx.q_start[e]) // tpt) for e in range(n_dec, E))
-        fa_prefill(q, cache, group.block_table, ctx.cu_q, ctx.kv_len, out, n_dec, E - n_dec, n_tiles, QH, KH, d,
-                   group.page_size, window, scale)
+        prefill = fa_prefill_tma if (tma_pages(group.page_size) and USE_TMA_ATTENTION) else fa_prefill
+        prefill(q, cache, group.block_table, ctx.cu_q, ctx.kv_len, out, n_dec, E - n_dec, n_tiles, QH, KH, d,
+                group.page_size, window, scale)
 
 
 def sample(logits: torch.Tensor, row_idx: Optional[torch.Tensor], params: torch.Tensor, history: Optional[torch.Tensor],

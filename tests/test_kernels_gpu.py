@@ -308,14 +308,14 @@ def test_flash_prefill_and_decode_against_plain(QH, KH, d, page, window):
     cu_q = torch.tensor(cu, dtype=torch.int32, device=DEV)
     kv_len = torch.tensor(lens, dtype=torch.int32, device=DEV)
     gc = ops.fa_group_chunk(QH // KH)
-    decoders = [ops.fa_decode] + ([ops.fa_decode_tma] if ops.tma_pages(page) else [])
-    for n_splits, decode in [(n, f) for n in (1, 3, 8) for f in decoders]:
+    kernels = [(ops.fa_decode, ops.fa_prefill)] + ([(ops.fa_decode_tma, ops.fa_prefill_tma)] if ops.tma_pages(page) else [])
+    for n_splits, (decode, prefill) in [(n, f) for n in (1, 3, 8) for f in kernels]:
         out = torch.full_like(s["q"], float("nan"))
         decode(s["q"], s["cache"], s["bt"], cu_q, kv_len, out, 0, 4, 0, n_splits, QH, KH, d, page, window, scale)
         assert ops.kernel_error() == 0
         tpt = 64 // gc
         n_tiles = sum(-(-n // tpt) for n in q_lens[4:])
-        ops.fa_prefill(s["q"], s["cache"], s["bt"], cu_q, kv_len, out, 4, 3, n_tiles, QH, KH, d, page, window, scale)
+        prefill(s["q"], s["cache"], s["bt"], cu_q, kv_len, out, 4, 3, n_tiles, QH, KH, d, page, window, scale)
         assert not torch.isnan(out.float()).any()
         err = (out.double().cpu() - ref).abs().max().item() / ref.abs().max().item()
         assert err <= 1.5e-2, f"splits {n_splits}: error {err:.3e}"
