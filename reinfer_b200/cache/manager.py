@@ -20,6 +20,8 @@ from __future__ import annotations
 from dataclasses import dataclass, field
 from typing import Dict, Hashable, List, Optional, Sequence, Tuple
 
+import numpy as np
+
 from ..parts.base import PagedKVSpec, SlotStateSpec
 
 
@@ -88,6 +90,7 @@ class _Seq:
     length: int = 0                                     # tokens whose keys are cached (committed)
     reserved: int = 0                                   # tokens that pages are held for (>= length)
     tables: List[List[int]] = field(default_factory=list)   # per group: page id per page index, -1 = given back
+    np_tables: List[np.ndarray] = field(default_factory=list)   # the same as int32 arrays (capacity grows by doubling)
 
 
 def group_layers(paged: Dict[str, PagedKVSpec]) -> List[Tuple[PagedKVSpec, Tuple[str, ...]]]:
@@ -137,6 +140,11 @@ class CacheManager:
     def table(self, rid, group: int) -> List[int]:
         return self._seq(rid).tables[group]
 
+    def table_array(self, rid, group: int) -> np.ndarray:
+        """The block table as an int32 array (a view: valid until the request grows)."""
+        s = self._seq(rid)
+        return s.np_tables[group][:len(s.tables[group])]
+
     def _seq(self, rid) -> _Seq:
         try:
             return self._seqs[rid]
@@ -166,7 +174,8 @@ class CacheManager:
         if not self._free_slots:
             raise OutOfPages("no free request slot")
         slot = self._free_slots.pop()
-        self._seqs[rid] = _Seq(slot=slot, tables=[[] for _ in self.groups])
+        self._seqs[rid] = _Seq(slot=slot, tables=[[] for _ in self.groups],
+                               np_tables=[np.full(16, -1, dtype=np.int32) for _ in self.groups])
         return slot
 
     def reserve(self, rid, new_len: int) -> None:
@@ -179,9 +188,17 @@ class CacheManager:
             if need_idx - len(t) > g.pool.free_count:
                 raise OutOfPages(f"request {rid!r} needs {need_idx - len(t)} more pages, "
                                  f"{g.pool.free_count} are free")
-        for g, t in zip(self.groups, s.tables):
-            while len(t) < need_idx:
-                t.append(g.pool.alloc())
+        for gi, (g, t) in enumerate(zip(self.groups, s.tables)):
+            if len(t) < need_idx:
+                arr = s.np_tables[gi]
+                if arr.shape[0] < need_idx:
+                    grown = np.full(max(need_idx, 2 * arr.shape[0]), -1, dtype=np.int32)
+                    grown[:len(t)] = arr[:len(t)]
+                    s.np_tables[gi] = arr = grown
+                while len(t) < need_idx:
+                    p = g.pool.alloc()
+                    arr[len(t)] = p
+                    t.append(p)
         s.reserved = max(s.reserved, new_len)
 
     def commit(self, rid, new_len: int) -> None:
@@ -191,7 +208,7 @@ class CacheManager:
         if new_len < s.length or (cap is not None and new_len > cap * self.page_size):
             raise CacheError(f"request {rid!r}: commit of {new_len} tokens outside what is reserved")
         s.length = new_len
-        for g, t in zip(self.groups, s.tables):
+        for gi, (g, t) in enumerate(zip(self.groups, s.tables)):
             if g.window is None:
                 continue
             first = min(self._first_needed_page(g, new_len), len(t))
@@ -199,6 +216,7 @@ class CacheManager:
                 if t[i] >= 0:
                     g.pool.free(t[i])
                     t[i] = -1
+                    s.np_tables[gi][i] = -1
 
     def release(self, rid) -> None:
         """The request ends: every page (latest first) and the slot go back."""
@@ -216,6 +234,11 @@ class CacheManager:
         """page*page_size+offset for the tokens at positions start..start+n-1."""
         t = self._seq(rid).tables[group]
         ps = self.page_size
+        if n == 1:
+            page = t[start // ps]
+            if page < 0:
+                raise CacheError(f"request {rid!r}: position {start} lies in a page that was given back")
+            return [page * ps + start % ps]
         out = []
         for pos in range(start, start + n):
             page = t[pos // ps]

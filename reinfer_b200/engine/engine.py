@@ -216,9 +216,14 @@ class Engine:
             if e.request_id in seen:
                 raise EngineError(f"request {e.request_id!r} appears twice in one step")
             seen.add(e.request_id)
-            for t in e.tokens:
-                if not 0 <= int(t) < self.vocab_size:
-                    raise EmbeddingOov(f"request {e.request_id!r}: token id {t} outside the vocabulary of {self.vocab_size}")
+            if len(e.tokens) == 1:
+                lo_t = hi_t = int(e.tokens[0])
+            else:
+                arr = np.asarray(e.tokens)
+                lo_t, hi_t = int(arr.min()), int(arr.max())
+            if lo_t < 0 or hi_t >= self.vocab_size:
+                raise EmbeddingOov(f"request {e.request_id!r}: token id {lo_t if lo_t < 0 else hi_t} outside the "
+                                   f"vocabulary of {self.vocab_size}")
             for w in e.want:
                 if not 0 <= int(w) < len(e.tokens):
                     raise EngineError(f"request {e.request_id!r}: wanted place {w} outside its {len(e.tokens)} tokens")
@@ -290,10 +295,17 @@ class Engine:
             bt = sec(f"block_table{g}").reshape(E, max_pages[g])
             bt[:] = -1
             for k, e in enumerate(internal):
-                table = cm.table(e.request_id, g)
-                bt[k, :len(table)] = table
+                table = cm.table_array(e.request_id, g)
+                bt[k, :table.shape[0]] = table
                 a, b = int(q_start[k]), int(q_start[k + 1])
-                ks[a:b] = cm.write_slots(e.request_id, g, start[k], q_len[k])
+                if b - a == 1:
+                    p0 = start[k]
+                    page = int(table[p0 // self.page_size])
+                    if page < 0:
+                        raise EngineError(f"request {e.request_id!r}: position {p0} lies in a page that was given back")
+                    ks[a] = page * self.page_size + p0 % self.page_size
+                else:
+                    ks[a:b] = cm.write_slots(e.request_id, g, start[k], q_len[k])
         lens_after = [(e.request_id, s + n) for e, s, n in zip(internal, start, q_len)]
         if fixed is not None:
             return host, lens_after

@@ -88,7 +88,8 @@ class LLM:
         sampled: Dict[Hashable, int] = {}
         if sampling:
             toks = self.sampler.sample(logits, [r.params for r in sampling], [r.seed for r in sampling],
-                                       [len(r.output) for r in sampling], [r.all_tokens for r in sampling])
+                                       [len(r.output) for r in sampling],
+                                       [(lambda n, r=r: r.tokens_from(max(0, r.total_len - n), min(n, r.total_len))) for r in sampling])
             sampled = {r.request_id: t for r, t in zip(sampling, toks)}
         finished += self.scheduler.update(out.batch, sampled)
         return finished

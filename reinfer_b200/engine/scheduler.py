@@ -53,6 +53,15 @@ class Request:
     def all_tokens(self) -> List[int]:
         return self.prompt + self.output
 
+    def tokens_from(self, start: int, n: int) -> List[int]:
+        """Tokens start..start+n-1 of prompt + output, without building the joined list."""
+        lp = len(self.prompt)
+        if start >= lp:
+            return self.output[start - lp:start - lp + n]
+        if start + n <= lp:
+            return self.prompt[start:start + n]
+        return self.prompt[start:] + self.output[:start + n - lp]
+
     @property
     def total_len(self) -> int:
         return len(self.prompt) + len(self.output)
@@ -161,7 +170,7 @@ class Scheduler:
             free = cm.free_pages()
             for r in decoding[:budget]:
                 free -= pages_more(r, r.num_computed + 1)
-                batch.append(Scheduled(r, r.num_computed, r.all_tokens[r.num_computed:], True))
+                batch.append(Scheduled(r, r.num_computed, r.tokens_from(r.num_computed, 1), True))
                 budget -= 1
 
             # 2. prompts in progress: their pages were promised at admission
@@ -173,8 +182,7 @@ class Scheduler:
                 n = min(rest, self.max_chunk, budget, room)
                 if n > 0:
                     free -= pages_more(r, r.num_computed + n)
-                    batch.append(Scheduled(r, r.num_computed, r.all_tokens[r.num_computed:r.num_computed + n],
-                                           n == rest))
+                    batch.append(Scheduled(r, r.num_computed, r.tokens_from(r.num_computed, n), n == rest))
                     budget -= n
                 promised += max(0, pages_more(r, r.total_len + 1) - (pages_more(r, r.num_computed + n) if n > 0 else 0))
 
@@ -203,7 +211,7 @@ class Scheduler:
                 self.waiting.popleft()
                 free -= cm.pages_for(n)
                 promised += cm.pages_for(r.total_len + 1) - cm.pages_for(n)
-                batch.append(Scheduled(r, r.num_computed, r.all_tokens[r.num_computed:r.num_computed + n], n == rest))
+                batch.append(Scheduled(r, r.num_computed, r.tokens_from(r.num_computed, n), n == rest))
                 budget -= n
                 admitted += 1
             if not batch and self.running and not preempted:

@@ -64,12 +64,21 @@ class Sampler:
         rec = np.zeros(rows, dtype=RECORD)
         hist = self._host_hist.numpy()
         any_hist = False
+        first = params[0]
+        if all(p is first for p in params):                      # the common case: one parameter set for the batch
+            rec["temperature"], rec["top_k"], rec["top_p"], rec["min_p"] = first.temperature, first.top_k, first.top_p, first.min_p
+            rec["repeat_penalty"], rec["frequency_penalty"] = first.repeat_penalty, first.frequency_penalty
+            rec["presence_penalty"] = first.presence_penalty
+        else:
+            for r, p in enumerate(params):
+                rec[r] = (p.temperature, p.top_k, p.top_p, p.min_p, p.repeat_penalty, p.frequency_penalty,
+                          p.presence_penalty, 0, 0, 0)
+        rec["seed"] = np.fromiter((sd & _MASK64 for sd in seeds), dtype=np.uint64, count=rows)
+        rec["step"] = np.fromiter(steps, dtype=np.uint64, count=rows)
         for r, p in enumerate(params):
-            rec[r] = (p.temperature, p.top_k, p.top_p, p.min_p, p.repeat_penalty, p.frequency_penalty,
-                      p.presence_penalty, 0, seeds[r] & _MASK64, steps[r])
             pen = p.repeat_penalty > 1.0 or p.frequency_penalty != 0.0 or p.presence_penalty != 0.0
             if pen and histories is not None and p.repeat_last_n > 0:
-                h = list(histories[r])[-p.repeat_last_n:]
+                h = histories[r](p.repeat_last_n) if callable(histories[r]) else list(histories[r])[-p.repeat_last_n:]
                 hist[r, :len(h)] = h
                 rec[r]["hist_len"] = len(h)
                 any_hist = any_hist or bool(h)
