@@ -3,10 +3,12 @@
     python bench.py [--gpus 1] [--steps K] [--warmup W] [--batch 8] [--context 4096]
                     [--layers L] [--impl ours|reference]
 
-Prints ONE JSON line.  `value`: decoded tokens per second at the given batch, device-timed
-(CUDA events around K decode steps: step function + sampler, tokens fed back from the host).
-`e2e`: the same through the Python entry point (`LLM.step`), wall clock, host token ids in
-(pinned staging -> device) and sampled ids out (device -> pinned) every step.  `prefill`:
+Prints ONE JSON line.  `value`: decoded tokens per second at the given batch, timed on the
+device alone: CUDA events around K decode steps launched back to back (the step's captured graph
+- every layer, the output head - and the sampler kernel), no host work in between.  `e2e`: K more
+steps of the same requests through the Python entry point (`LLM.step`: scheduler, the step's int32
+block from pinned memory to the device, the graph, the sampler, sampled ids back to pinned
+memory), by the wall clock.  `prefill`:
 one request of 2,048 tokens.  `roofline`: bytes a decode step has to read (every weight it
 uses once + the cache of the live requests) / its time, against the measured copy bandwidth.
 `points`: decode at batch 1 and 64.  A decode step reads > 16 GB of weights, far more than
@@ -180,24 +182,35 @@ def main() -> int:
         for _ in range(warmup):
             llm.step()
         torch.cuda.synchronize()
-        l0 = ops.launches
-        e0, e1 = ev(), ev()
+        # (1) end to end: K steps through the entry point, wall clock
         w0 = time.perf_counter()
-        e0.record()
         for _ in range(steps):
             llm.step()
-        e1.record()
         torch.cuda.synchronize()
         wall = time.perf_counter() - w0
-        dev_ms = e0.elapsed_time(e1)
-        n_l = ops.launches - l0
         assert len(llm.scheduler.running) == B and not llm.scheduler.waiting
-        kv_tokens = sum(engine.cache.length(r.request_id) for r in llm.scheduler.running) - B * steps // 2
-        graph_nodes = 0
-        for (bk, _w), g in engine._graphs.items():
-            if bk >= B:
-                graph_nodes = max(graph_nodes, g.n_launches)
-        n_l += graph_nodes * steps                      # kernels inside the replayed graph, counted at capture
+        kv_tokens = sum(engine.cache.length(r.request_id) for r in llm.scheduler.running)
+        # (2) the device alone: the same step's graph and the sampler kernel, K times back to back
+        bucket = B if B <= 8 else -(-B // 8) * 8
+        graph = max((g for (bk, _w), g in engine._graphs.items() if bk == bucket), key=lambda g: g.meta.numel())
+        rows = [r for r in llm.scheduler.running]
+        params = [r.params for r in rows]
+        rec_args = ([r.seed for r in rows], [len(r.output) for r in rows])
+        smp = llm.sampler
+        dparams, out_tok = smp.device_records(params, *rec_args), torch.empty(B, dtype=torch.int32, device=engine.device)
+        for _ in range(3):
+            graph.graph.replay()
+            ops.sample(graph.logits, None, dparams, None, smp._work, out_tok, B)
+        torch.cuda.synchronize()
+        e0, e1 = ev(), ev()
+        e0.record()
+        for _ in range(steps):
+            graph.graph.replay()
+            ops.sample(graph.logits, None, dparams, None, smp._work, out_tok, B)
+        e1.record()
+        torch.cuda.synchronize()
+        dev_ms = e0.elapsed_time(e1)
+        n_l = (graph.n_launches + 1) * steps            # kernels inside the replayed graph (counted at capture) + sampler
         for r in list(llm.scheduler.running):
             llm.abort(r.request_id)
         return dev_ms / steps, wall / steps * 1e3, n_l, kv_tokens
@@ -233,10 +246,14 @@ def main() -> int:
                      "peak_source": f"of {peak_src}"},
         "points": points, "clocks": clk, "load_s": load_s,
     }
-    # bytes of the int32 block the step uploads: ids, positions, entry, tables (see Engine._prepare)
+    # bytes of the int32 block the step uploads (ids, positions, entry, tables: Engine._layout) + sampler records
     B = a.batch
-    pages = -(-ctx_len // page)
-    out["e2e"]["h2d_bytes_per_step"] = 4 * (4 * ((B + 3) // 4 * 4) + 3 * ((B + 3) // 4 * 4) + B * pages + 8) + B * 48
+    bucket = B if B <= 8 else -(-B // 8) * 8
+    width = 8
+    while width < -(-ctx_len // page):
+        width *= 2
+    from reinfer_b200.engine.engine import Engine as _E
+    out["e2e"]["h2d_bytes_per_step"] = 4 * _E._layout(bucket, bucket, bucket, [width])[1] + B * 48
     print(json.dumps(out))
     return 0
 

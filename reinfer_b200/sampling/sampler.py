@@ -52,6 +52,14 @@ class Sampler:
         self._host_hist = torch.empty((self.max_rows, HIST_CAP), dtype=torch.int32, pin_memory=True)
         self._host_out = torch.empty(self.max_rows, dtype=torch.int32, pin_memory=True)
 
+    def device_records(self, params: Sequence[SamplingParams], seeds: Sequence[int], steps: Sequence[int]) -> torch.Tensor:
+        """The kernel's per-row records for rows without penalties, on the device (for callers that
+        launch `ops.sample` themselves)."""
+        rec = np.zeros(len(params), dtype=RECORD)
+        for r, p in enumerate(params):
+            rec[r] = (p.temperature, p.top_k, p.top_p, p.min_p, 1.0, 0.0, 0.0, 0, seeds[r] & _MASK64, steps[r])
+        return torch.from_numpy(rec.view(np.uint8).copy()).to(self.device)
+
     def sample(self, logits: torch.Tensor, params: Sequence[SamplingParams], seeds: Sequence[int],
                steps: Sequence[int], histories: Optional[Sequence[Sequence[int]]] = None) -> List[int]:
         """One token per row of `logits` ([rows, vocab] float32 on the device).  Returns host ints
