@@ -304,3 +304,70 @@ def test_toy_architecture_registered_built_and_stepped(tmp_path):
         unregister_architecture("ToyStatefulLM")
         for cat, kind in (("mixer", "toy_decay"), ("ffn", "toy_routed"), ("position", "toy_signflip")):
             unregister_part(cat, kind)
+
+
+def _window_spec(cfg):
+    """Two attention layers that see every key and one that sees only the last 24: two cache groups."""
+    from reinfer_b200.parts.spec import LayerSpec, ModelSpec, PartSpec
+    h = cfg.hidden
+    norm = lambda p: PartSpec("rmsnorm", {"width": h, "eps": 1e-5}, p)
+
+    def attn(p, window):
+        return PartSpec("attention", {"hidden": h, "q_heads": 4, "kv_heads": 2, "head_dim": 16, "qk_norm": True,
+                                      "qk_norm_eps": 1e-5, "window": window,
+                                      "position": {"kind": "rope", "head_dim": 16, "theta": 1e4}}, p)
+    ffn = lambda p: PartSpec("swiglu", {"hidden": h, "intermediate": 48}, p)
+    layers = tuple(LayerSpec(f"l{i}", mixer=attn(f"l{i}.att.", w), ffn=ffn(f"l{i}.ffn."), mixer_norm=norm(f"l{i}.n1."),
+                             ffn_norm=norm(f"l{i}.n2.")) for i, w in enumerate([None, 24, None]))
+    return ModelSpec(hidden_size=h, vocab_size=cfg.vocab, embedding=PartSpec("embedding", {"vocab": cfg.vocab, "hidden": h}, "emb."),
+                     layers=layers, final_norm=norm("final."), lm_head=PartSpec("linear", {"vocab": cfg.vocab, "hidden": h, "tied": True}, "head."))
+
+
+class _WinConfig(_ToyConfig):
+    def to_dict(self):
+        return {"architectures": ["ToyWindowLM"], "toy_hidden": self.hidden, "toy_vocab": self.vocab}
+
+
+@pytest.mark.parametrize("dtype,page", [("float32", 8), ("bfloat16", 8), ("bfloat16", 4)])
+def test_window_group_gives_pages_back_and_all_cuts_agree(tmp_path, dtype, page):
+    """A layer with a window lives in a cache group of its own; its pages go back to the pool as the
+    window passes them, the kernels never touch a page that was given back, and whole / portions /
+    token-by-token give the same logits (the window's edge at every kind of step boundary)."""
+    from reinfer_b200.config import register_architecture, unregister_architecture
+    from reinfer_b200.engine import Engine, StepEntry
+    from reinfer_b200.weights import write_random_model
+    register_architecture("ToyWindowLM", _WinConfig, _window_spec)
+    try:
+        d = write_random_model(str(tmp_path / "win"), _WinConfig(), seed=9, dtype=torch.float32)
+        seq = [(11 * i + 5) % 97 for i in range(150)]
+
+        def run(cuts):
+            e = Engine.from_model_dir(d, dtype=dtype, page_size=page, max_tokens=192, max_num_seqs=2)
+            assert [g.window for g in e.cache.groups] == [None, 24] and [g.layers for g in e.cache.groups] == [("l0", "l2"), ("l1",)]
+            # poison the pools: a read of a page that is not held would show
+            for arr in e.storage.group_arrays:
+                arr.fill_(float("nan"))
+            rows, i = [], 0
+            for n in cuts:
+                lg = e.step([StepEntry("a", seq[i:i + n], list(range(n)))])
+                rows.append(lg.double().cpu())
+                i += n
+                e.cache.check()
+                held = sum(1 for p in e.cache.table("a", 1) if p >= 0)
+                assert held <= -(-24 // page) + 1 + -(-n // page)            # the window's pages (+ this step's)
+            assert i == len(seq)
+            assert sum(1 for p in e.cache.table("a", 0) if p >= 0) == -(-len(seq) // page)
+            e.finish("a")
+            assert all(g.pool.in_use == 0 for g in e.cache.groups)
+            return torch.cat(rows)
+        whole = run([150])
+        assert not torch.isnan(whole).any()
+        tol = 1e-4 if dtype == "float32" else 4e-2
+        for cuts in ([23, 1, 1, 25, 2, 48, 50], [1] * 150, [100] + [1] * 50, [7] * 21 + [3]):
+            got = run(cuts)
+            err = ((got - whole).abs().max(dim=1).values / whole.abs().max(dim=1).values).max().item()
+            assert err <= tol, f"{dtype} cuts {cuts[:4]}..: {err:.2e}"
+        # the window matters: with every key visible the late logits differ
+        assert (whole[100:] - whole[100:].mean()).abs().max() > 0
+    finally:
+        unregister_architecture("ToyWindowLM")
