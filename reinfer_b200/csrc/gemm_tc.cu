@@ -270,6 +270,200 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
     }
 }
 
+// ------------------------------------------------------------------------------ persistent
+// The same product for many tokens (prompt portions): one CTA per SM walks the output tiles
+// (tile = blockIdx.x, + gridDim.x, ...; token tiles fastest, so that CTAs running side by side share a
+// weight tile in L2).  Two accumulators in tensor memory alternate: while the four epilogue warps read
+// one back and store it, the MMA thread already fills the other with the next tile, and the TMA thread
+// keeps the shared-memory ring full across tile borders - neither the epilogue nor the pipeline's fill
+// and drain leave the tensor cores idle as they do with one CTA per tile.
+struct TcPersistShared {
+    unsigned long long full[8];
+    unsigned long long empty[8];
+    unsigned long long acc_full[2];
+    unsigned long long acc_empty[2];
+    uint32_t tmem_base;
+    int abort_flag;
+};
+
+template <int BN, int STAGES, bool DUAL>
+__global__ void __launch_bounds__(TC_THREADS, 1)
+gemm_tc_persistent_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_x,
+                          void* __restrict__ C, int T, int N, int K, long long ldc, int out_mode, int t_tiles, int n_tiles) {
+    extern __shared__ __align__(1024) unsigned char smem_raw[];
+    constexpr uint32_t W1_BYTES = TC_BM * TC_BK * 2;
+    constexpr uint32_t W_BYTES = (DUAL ? 2 : 1) * W1_BYTES;
+    constexpr uint32_t X_BYTES = BN * TC_BK * 2;
+    constexpr uint32_t STAGE_BYTES = W_BYTES + X_BYTES;
+    constexpr uint32_t ACC_COLS = (DUAL ? 2 : 1) * BN;            // columns of one accumulator stage
+    static_assert(2 * ACC_COLS <= 512, "two accumulator stages must fit tensor memory");
+    constexpr uint32_t TMEM_COLS = 2 * ACC_COLS <= 32 ? 32 : 2 * ACC_COLS <= 64 ? 64 : 2 * ACC_COLS <= 128 ? 128 : 2 * ACC_COLS <= 256 ? 256 : 512;
+    unsigned char* smem = (unsigned char*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+    TcPersistShared* sh = (TcPersistShared*)(smem + (size_t)STAGES * STAGE_BYTES);
+    const uint32_t smem_base = smem_u32(smem);
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int total_tiles = t_tiles * n_tiles;
+    const int nkb = (K + TC_BK - 1) / TC_BK;
+    volatile int* abort_flag = &sh->abort_flag;
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < STAGES; ++s) { mbar_init(smem_u32(&sh->full[s]), 1); mbar_init(smem_u32(&sh->empty[s]), 1); }
+        for (int a = 0; a < 2; ++a) { mbar_init(smem_u32(&sh->acc_full[a]), 1); mbar_init(smem_u32(&sh->acc_empty[a]), 4); }
+        sh->abort_flag = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+    }
+    if (warp == 1) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&sh->tmem_base)), "r"(TMEM_COLS) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem = sh->tmem_base;
+    long long issued = 0;                               // producer: k-blocks (over all its tiles) whose loads were issued
+
+    if (warp == 0) {
+        if (lane == 0) {
+            pdl_trigger();
+            pdl_wait();
+            long long it = 0;
+            bool ok = true;
+            for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x) {
+                const int t0 = (tile % t_tiles) * BN, n0 = (tile / t_tiles) * TC_BM;
+                for (int kb = 0; kb < nkb; ++kb, ++it) {
+                    const int s = (int)(it % STAGES);
+                    const uint32_t round = (uint32_t)(it / STAGES);
+                    ok = mbar_wait(smem_u32(&sh->empty[s]), (round & 1) ^ 1, abort_flag, 11);
+                    if (!ok) break;
+                    const uint32_t full = smem_u32(&sh->full[s]);
+                    mbar_expect_tx(full, STAGE_BYTES);
+                    const uint32_t dst = smem_base + s * STAGE_BYTES;
+                    tma_load_2d(dst, &map_w, kb * TC_BK, n0, full);
+                    if (DUAL) tma_load_2d(dst + W1_BYTES, &map_w, kb * TC_BK, N + n0, full);
+                    tma_load_2d(dst + W_BYTES, &map_x, kb * TC_BK, t0, full);
+                    issued = it + 1;
+                }
+            }
+        }
+    } else if (warp == 1) {
+        if (lane == 0) {
+            constexpr uint32_t idesc = make_idesc(BN);
+            long long it = 0;
+            bool ok = true;
+            int local = 0;
+            for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x, ++local) {
+                const int a = local & 1;
+                ok = mbar_wait(smem_u32(&sh->acc_empty[a]), ((uint32_t)(local >> 1) & 1) ^ 1, abort_flag, 12);   // drained by the epilogue
+                if (!ok) break;
+                tc_fence_after();
+                const uint32_t acc = tmem + (uint32_t)a * ACC_COLS;
+                for (int kb = 0; kb < nkb; ++kb, ++it) {
+                    const int s = (int)(it % STAGES);
+                    ok = mbar_wait(smem_u32(&sh->full[s]), (uint32_t)(it / STAGES) & 1, abort_flag, 13);
+                    if (!ok) break;
+                    tc_fence_after();
+                    const uint32_t base = smem_base + s * STAGE_BYTES;
+                    const uint64_t da = make_smem_desc(base), db = make_smem_desc(base + W_BYTES);
+                    const uint64_t da2 = make_smem_desc(base + W1_BYTES);
+#pragma unroll
+                    for (int k = 0; k < TC_BK / 16; ++k) {
+                        tc_mma_bf16(acc, da + (uint64_t)(k * 2), db + (uint64_t)(k * 2), idesc, (kb | k) != 0);
+                        if (DUAL) tc_mma_bf16(acc + BN, da2 + (uint64_t)(k * 2), db + (uint64_t)(k * 2), idesc, (kb | k) != 0);
+                    }
+                    tc_commit(smem_u32(&sh->empty[s]));
+                }
+                if (ok) tc_commit(smem_u32(&sh->acc_full[a]));
+            }
+        }
+    } else {
+        const int q = warp & 3;
+        pdl_wait();
+        int local = 0;
+        for (int tile = blockIdx.x; tile < total_tiles; tile += gridDim.x, ++local) {
+            const int a = local & 1;
+            const int t0 = (tile % t_tiles) * BN, n0 = (tile / t_tiles) * TC_BM;
+            const int feat = n0 + q * 32 + lane;
+            if (!mbar_wait(smem_u32(&sh->acc_full[a]), (uint32_t)(local >> 1) & 1, abort_flag, 14)) break;
+            tc_fence_after();
+            const uint32_t acc = tmem + ((uint32_t)(q * 32) << 16) + (uint32_t)a * ACC_COLS;
+#pragma unroll 1
+            for (int c0 = 0; c0 < BN; c0 += 16) {
+                if (t0 + c0 >= T) break;
+                uint32_t r[16], r2[16];
+                tc_ld16(acc + (uint32_t)c0, r);
+                if (DUAL) tc_ld16(acc + (uint32_t)(BN + c0), r2);
+                tc_ld_wait();
+                if (feat < N) {
+                    const int nt = min(16, T - t0 - c0);
+                    if (DUAL) {
+                        bf16* cp = (bf16*)C + (size_t)(t0 + c0) * ldc + feat;
+#pragma unroll
+                        for (int j = 0; j < 16; ++j) {
+                            const float g = __uint_as_float(r[j]), u = __uint_as_float(r2[j]);
+                            if (j < nt) cp[(size_t)j * ldc] = __float2bfloat16_rn(g / (1.0f + expf(-g)) * u);
+                        }
+                    } else if (out_mode == 2) {
+                        float* cp = (float*)C + (size_t)(t0 + c0) * ldc + feat;
+                        float old[16];
+#pragma unroll
+                        for (int j = 0; j < 16; ++j) old[j] = j < nt ? cp[(size_t)j * ldc] : 0.0f;
+#pragma unroll
+                        for (int j = 0; j < 16; ++j) if (j < nt) cp[(size_t)j * ldc] = old[j] + __uint_as_float(r[j]);
+                    } else if (out_mode == 0) {
+                        bf16* cp = (bf16*)C + (size_t)(t0 + c0) * ldc + feat;
+#pragma unroll
+                        for (int j = 0; j < 16; ++j) if (j < nt) cp[(size_t)j * ldc] = __float2bfloat16_rn(__uint_as_float(r[j]));
+                    } else {
+                        float* cp = (float*)C + (size_t)(t0 + c0) * ldc + feat;
+#pragma unroll
+                        for (int j = 0; j < 16; ++j) if (j < nt) cp[(size_t)j * ldc] = __uint_as_float(r[j]);
+                    }
+                }
+            }
+            // this warp has read its quarter of the accumulator: the MMA thread may refill it once all four have
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(smem_u32(&sh->acc_empty[a]));
+        }
+    }
+    tc_fence_before();
+    __syncthreads();
+    if (*abort_flag && threadIdx.x == 0) {
+        for (long long it = issued > STAGES ? issued - STAGES : 0; it < issued; ++it) {
+            const uint32_t bar = smem_u32(&sh->full[it % STAGES]);
+            const uint32_t parity = (uint32_t)(it / STAGES) & 1;
+            for (uint32_t k = 0; k < RB_SPIN_LIMIT; ++k) if (mbar_try(bar, parity)) break;
+        }
+    }
+    __syncthreads();
+    if (warp == 1) {
+        tc_fence_after();
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(TMEM_COLS) : "memory");
+    }
+}
+
+template <int BN, int STAGES, bool DUAL>
+static int launch_tc_persistent(const CUtensorMap& mw, const CUtensorMap& mx, void* C, int T, int N, int K, long long ldc,
+                                int mode, cudaStream_t s) {
+    constexpr size_t smem = (size_t)STAGES * ((DUAL ? 2 : 1) * TC_BM * TC_BK * 2 + BN * TC_BK * 2) + sizeof(TcPersistShared) + 1024;
+    static bool configured = false;
+    static int sms = 0;
+    if (!configured) {
+        cudaError_t e = cudaFuncSetAttribute(gemm_tc_persistent_kernel<BN, STAGES, DUAL>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        if (e != cudaSuccess) return (int)e;
+        int dev = 0;
+        cudaGetDevice(&dev);
+        cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+        configured = true;
+    }
+    const int t_tiles = rb_ceil_div(T, BN), n_tiles = rb_ceil_div(N, TC_BM);
+    const int total = t_tiles * n_tiles;
+    const int grid = total < sms ? total : sms;
+    return rb_launch(gemm_tc_persistent_kernel<BN, STAGES, DUAL>, dim3(grid), dim3(TC_THREADS), smem, s, mw, mx, C, T, N, K, ldc,
+                     mode, t_tiles, n_tiles);
+}
+
 // Sum of the split partials in split order, then store / accumulate.  mode as OUT_MODE 0..2.
 __global__ void splitk_reduce_kernel(const float* __restrict__ ws, void* __restrict__ C, int T, int N, long long ldc,
                                      int splits, int mode) {
@@ -395,6 +589,10 @@ static int launch_tc(const CUtensorMap& mw, const CUtensorMap& mx, void* C, floa
     return 0;
 }
 
+static int g_tc_persistent = 1;
+// The persistent schedule for products with several token tiles on (1) or off (0); returns the old value.
+extern "C" int rb_set_gemm_persistent(int on) { int old = g_tc_persistent; g_tc_persistent = on ? 1 : 0; return old; }
+
 static int tc_bn(int T) { return T <= 16 ? 16 : T <= 32 ? 32 : T <= 64 ? 64 : T <= 128 ? 128 : 256; }
 
 // X [T,K] bf16 (row stride ldx), W [N,K] bf16 (row stride ldw), C [T,N] bf16 or float (row stride ldc).
@@ -413,6 +611,10 @@ extern "C" int rb_gemm_bf16(const void* X, const void* W, void* C, int c_dtype, 
     const int bn = tc_bn(T);
     CUtensorMap mw, mx;
     if (rb_tensor_map_bf16(W, N, K, ldw, TC_BM, &mw)) return -1;
+    if (T > 256 && force_splits == 0 && g_tc_persistent) {          // several token tiles: the persistent schedule
+        if (rb_tensor_map_bf16(X, T, K, ldx, 256, &mx)) return -1;
+        return launch_tc_persistent<256, 4, false>(mw, mx, C, T, N, K, ldc, mode, s);
+    }
     if (rb_tensor_map_bf16(X, T, K, ldx, bn, &mx)) return -1;
     switch (bn) {
         case 16: return launch_tc<16, 6, false>(mw, mx, C, ws, ws_floats, T, N, K, ldc, mode, force_splits, s);
@@ -435,6 +637,10 @@ extern "C" int rb_gemm_bf16_swiglu(const void* X, const void* Wgu, void* act, in
     const int bn = tc_bn(T);
     CUtensorMap mw, mx;
     if (rb_tensor_map_bf16(Wgu, 2LL * F, K, ldw, TC_BM, &mw)) return -1;
+    if (T > 256 && g_tc_persistent) {                               // two accumulators x two stages: 128-token tiles
+        if (rb_tensor_map_bf16(X, T, K, ldx, 128, &mx)) return -1;
+        return launch_tc_persistent<128, 4, true>(mw, mx, act, T, F, K, ldc, 0, s);
+    }
     if (rb_tensor_map_bf16(X, T, K, ldx, bn, &mx)) return -1;
     switch (bn) {
         case 16: return launch_tc<16, 3, true>(mw, mx, act, nullptr, 0, T, F, K, ldc, 0, 0, s);
