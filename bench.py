@@ -244,7 +244,7 @@ def main() -> int:
         "prefill": prefill,
         "roofline": {"bound": "hbm", "achieved": achieved, "peak": hbm_gbs, "unit": "GB/s", "frac": achieved / hbm_gbs,
                      "peak_source": f"of {peak_src}"},
-        "points": points, "clocks": clk, "load_s": load_s,
+        "points": points, "clocks": clk, "load_s": load_s, "kernel_error_word": ops.kernel_error(reset=False),
     }
     # bytes of the int32 block the step uploads (ids, positions, entry, tables: Engine._layout) + sampler records
     B = a.batch

@@ -255,8 +255,7 @@ fa_decode_tma_kernel(const __grid_constant__ CUtensorMap map_kv, const FtArgs a)
         // copies that were issued but never consumed still write this CTA's shared memory: wait for them
         if (threadIdx.x == FT_WARPS * 32)
             for (int it = max(0, issued - NST); it < issued; ++it)
-                for (uint32_t k = 0; k < RB_SPIN_LIMIT; ++k)
-                    if (mbar_try(smem_u32(&sh->full[it % NST]), (it / NST) & 1)) break;
+                mbar_drain(smem_u32(&sh->full[it % NST]), (it / NST) & 1);
         __syncthreads();
         return;
     }
@@ -531,8 +530,7 @@ fa_prefill_tma_kernel(const __grid_constant__ CUtensorMap map_kv, const FtArgs a
     if (*abort_flag) {
         if (threadIdx.x == FT_WARPS * 32)
             for (int it = max(0, issued - NST); it < issued; ++it)
-                for (uint32_t k = 0; k < RB_SPIN_LIMIT; ++k)
-                    if (mbar_try(smem_u32(&sh->full[it % NST]), (it / NST) & 1)) break;
+                mbar_drain(smem_u32(&sh->full[it % NST]), (it / NST) & 1);
         __syncthreads();
         return;
     }

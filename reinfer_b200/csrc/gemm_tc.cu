@@ -18,7 +18,7 @@
 // gemv does the same, crates/cuda/kernels/gemm_m1.cu:106-123).  The reference's products are cublasGemmEx
 // and scalar gemv kernels (crates/cuda/src/gemm.rs:226-372).
 //
-// Every wait on an mbarrier is bounded: after RB_SPIN_LIMIT failed polls the CTA raises
+// Every wait on an mbarrier is bounded (two seconds of the global timer): after that the CTA raises
 // an abort flag, its roles leave their loops, outstanding TMA loads are waited for (again
 // bounded), tensor memory is freed, and an error word in global memory tells the host.
 #include "sm100.cuh"
@@ -217,7 +217,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
         for (int kb = max(0, issued - STAGES); kb < issued; ++kb) {
             const uint32_t bar = smem_u32(&sh->full[kb % STAGES]);
             const uint32_t parity = (kb / STAGES) & 1;
-            for (uint32_t it = 0; it < RB_SPIN_LIMIT; ++it) if (mbar_try(bar, parity)) break;
+            mbar_drain(bar, parity);
         }
     }
     __syncthreads();
@@ -265,6 +265,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
     }
     if (threadIdx.x == 0) TL(7);
     if (warp == 1) {
+        __syncwarp();                                   // .sync.aligned: the MMA lane rejoins its warp first
         tc_fence_after();
         asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(TMEM_COLS) : "memory");
     }
@@ -305,6 +306,7 @@ gemm_tc_persistent_kernel(const __grid_constant__ CUtensorMap map_w, const __gri
     const int total_tiles = t_tiles * n_tiles;
     const int nkb = (K + TC_BK - 1) / TC_BK;
     volatile int* abort_flag = &sh->abort_flag;
+    if (*(volatile int*)&g_rb_kernel_error) return;               // an earlier launch gave up: fail fast, the host will see the word
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < STAGES; ++s) { mbar_init(smem_u32(&sh->full[s]), 1); mbar_init(smem_u32(&sh->empty[s]), 1); }
@@ -433,11 +435,12 @@ gemm_tc_persistent_kernel(const __grid_constant__ CUtensorMap map_w, const __gri
         for (long long it = issued > STAGES ? issued - STAGES : 0; it < issued; ++it) {
             const uint32_t bar = smem_u32(&sh->full[it % STAGES]);
             const uint32_t parity = (uint32_t)(it / STAGES) & 1;
-            for (uint32_t k = 0; k < RB_SPIN_LIMIT; ++k) if (mbar_try(bar, parity)) break;
+            mbar_drain(bar, parity);
         }
     }
     __syncthreads();
     if (warp == 1) {
+        __syncwarp();                                   // .sync.aligned: the MMA lane rejoins its warp first
         tc_fence_after();
         asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(TMEM_COLS) : "memory");
     }
@@ -590,8 +593,8 @@ static int launch_tc(const CUtensorMap& mw, const CUtensorMap& mx, void* C, floa
 }
 
 static int g_tc_persistent = 1;
-// The persistent schedule for products with several token tiles on (1) or off (0); returns the old value.
-extern "C" int rb_set_gemm_persistent(int on) { int old = g_tc_persistent; g_tc_persistent = on ? 1 : 0; return old; }
+// Schedule of products with several token tiles: 0 = one CTA per tile, 1 = persistent CTAs.  Returns the old value.
+extern "C" int rb_set_gemm_persistent(int mode) { int old = g_tc_persistent; g_tc_persistent = mode ? 1 : 0; return old; }
 
 static int tc_bn(int T) { return T <= 16 ? 16 : T <= 32 ? 32 : T <= 64 ? 64 : T <= 128 ? 128 : 256; }
 

@@ -32,15 +32,34 @@ __device__ __forceinline__ bool mbar_try(uint32_t bar, uint32_t parity) {
         : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
     return ok != 0;
 }
-// Bounded wait.  Returns false if the CTA is aborting (or this wait gave up and raised the abort).
+// Bounded wait: gives up after RB_WAIT_NS nanoseconds of the global timer (or RB_SPIN_LIMIT polls,
+// whichever comes first).  Returns false if the CTA is aborting, or if this wait gave up - then it
+// raises the CTA's abort flag and records where in the error word.
+#define RB_WAIT_NS 2000000000ull
+__device__ __forceinline__ unsigned long long rb_globaltimer() {
+    unsigned long long t;
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+    return t;
+}
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag, int where) {
+    unsigned long long t0 = 0;
     for (uint32_t it = 0; it < RB_SPIN_LIMIT; ++it) {
         if (mbar_try(bar, parity)) return true;
-        if ((it & 255u) == 255u && *abort_flag) return false;
+        if ((it & 63u) == 63u) {
+            if (*abort_flag) return false;
+            const unsigned long long now = rb_globaltimer();
+            if (t0 == 0) t0 = now;
+            else if (now - t0 > RB_WAIT_NS) break;
+        }
     }
     *abort_flag = where;
     atomicCAS(&g_rb_kernel_error, 0, (1 << 8) | where);
     return false;
+}
+// After a failed wait: let the copies that were issued into this CTA's shared memory land (bounded) before leaving.
+__device__ __forceinline__ void mbar_drain(uint32_t bar, uint32_t parity) {
+    const unsigned long long t0 = rb_globaltimer();
+    while (!mbar_try(bar, parity)) if (rb_globaltimer() - t0 > RB_WAIT_NS / 4) break;
 }
 __device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map, int x, int y, uint32_t bar) {
     asm volatile(
@@ -69,6 +88,7 @@ __device__ __forceinline__ void tc_ld16(uint32_t taddr, uint32_t* r) {
 __device__ __forceinline__ void tc_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
 
 __device__ __forceinline__ void cluster_sync_all() {
+    __syncwarp();                                       // .aligned: the whole warp must arrive together
     asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
 }
 __device__ __forceinline__ float ld_cluster_f32(uint32_t local_addr, uint32_t rank) {

@@ -41,6 +41,9 @@ def lib():
         _lib.rb_last_error.restype = c_char_p
         if _lib.rb_abi_version() != 1:
             raise KernelError("kernel library has another ABI version")
+        if os.environ.get("REINFER_B200_GEMM_SCHEDULE"):
+            # 0: one CTA per tile, 1: persistent CTAs (default) for prompt portions
+            _lib.rb_set_gemm_persistent(int(os.environ["REINFER_B200_GEMM_SCHEDULE"]))
         if os.environ.get("REINFER_B200_PDL", "1") == "0":
             _lib.rb_set_pdl(0)          # launch every kernel fully serialised (for comparisons)
     return _lib
