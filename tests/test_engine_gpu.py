@@ -147,3 +147,28 @@ def test_trace_run_program(models, tmp_path, dtype):
             done[r] = done.get(r, 0) + len(t)
         assert row == arr.shape[0]
     compare(got, want, TOL[dtype])
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_full_size_layer_shape(tmp_path, dtype):
+    """Two layers at the layer sizes of the 8B configuration (hidden 4096, 32/8 heads of 128, feed-forward
+    12288; vocabulary cut to an odd 32003): the tensor-core kernels at the sizes they serve, against the
+    plain implementation, whole and mixed with a pool that is used again."""
+    from reinfer_b200.config import Qwen3Config
+    from reinfer_b200.engine import Engine
+    from reinfer_b200.weights import write_random_model
+    raw = dict(architectures=["Qwen3ForCausalLM"], num_hidden_layers=2, hidden_size=4096, num_attention_heads=32,
+               num_key_value_heads=8, head_dim=128, intermediate_size=12288, vocab_size=32003, rope_theta=1e6,
+               rms_norm_eps=1e-6, tie_word_embeddings=False, max_position_embeddings=4096)
+    d = write_random_model(str(tmp_path / "m"), Qwen3Config.from_dict(raw), seed=3, dtype=torch.bfloat16)
+    g = torch.Generator().manual_seed(1)
+    seqs = {"a": torch.randint(0, 32003, (150,), generator=g).tolist(), "b": torch.randint(0, 32003, (70,), generator=g).tolist(),
+            "c": torch.randint(0, 32003, (300,), generator=g).tolist()}
+    cfg, w = plain.read_model(d)
+    want = {r: plain.forward(cfg, w, t, dtype=torch.float32).double() for r, t in seqs.items()}
+    for cut in (tiny.cut_whole, tiny.cut_mixed):
+        steps = cut(seqs)
+        engine = Engine.from_model_dir(d, dtype=dtype, page_size=16, max_tokens=tiny.pool_tokens_needed(steps), max_num_seqs=4)
+        got = run_steps(engine, steps)
+        compare(got, want, 2e-4 if dtype == "float32" else TOL[dtype])
+        del engine
