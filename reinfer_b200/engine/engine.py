@@ -170,8 +170,7 @@ class Engine:
         self.steps_run += 1
         return logits
 
-    def _step_graph(self, entries: Sequence[StepEntry]) -> Optional[torch.Tensor]:
-        """A step of single tokens only: fill the graph's static tables and replay it."""
+    def _graph_key(self, entries: Sequence[StepEntry]):
         B = len(entries)
         bucket = B if B <= 8 else -(-B // 8) * 8
         need_pages = 1
@@ -181,23 +180,56 @@ class Engine:
         width = 8
         while width < need_pages:
             width *= 2
-        key = (bucket, width)
+        return bucket, width
+
+    def _step_graph(self, entries: Sequence[StepEntry]) -> Optional[torch.Tensor]:
+        """A step of single tokens only: fill the graph's static tables and replay it."""
+        key = self._graph_key(entries)
+        host, lens_after = self._prepare(entries, fixed=key)
+        return self._replay(key, host, lens_after, [k for k, e in enumerate(entries) if len(e.want) > 0], len(entries))
+
+    def _replay(self, key, host, lens_after, rows, B) -> Optional[torch.Tensor]:
         g = self._graphs.get(key)
         if g is None:
-            g = _DecodeGraph(self, bucket, width)
+            g = _DecodeGraph(self, key[0], key[1])
             self._graphs[key] = g
-        host, lens_after = self._prepare(entries, fixed=(bucket, width))
         self._staging.upload(host, self.device, into=g.meta)
         g.graph.replay()
         self.graph_replays += 1
         for rid, n in lens_after:
             self.cache.commit(rid, n)
         self.steps_run += 1
-        rows = [k for k, e in enumerate(entries) if len(e.want) > 0]
         if not rows:
             return None
         # a copy: the graph's own buffer is overwritten by the next replay
         return g.logits[:B].clone() if rows == list(range(B)) else g.logits[rows]
+
+    # ---- one step ahead -----------------------------------------------------------------------
+    def prepare_ahead(self, request_ids: Sequence[Hashable]):
+        """While the step just launched still runs on the device: build the tables of the NEXT step under
+        the guess that exactly these requests go on with one token each (pages are reserved now; the token
+        ids are not known yet).  Returns a handle for `step_ahead`, or None if that step cannot be a
+        graph replay or the pages are short (the ordinary path then decides what happens)."""
+        if not self.cuda_graphs or not request_ids or len(request_ids) > MAX_GRAPH_BATCH:
+            return None
+        entries = [StepEntry(rid, [0], [0]) for rid in request_ids]
+        if any(rid not in self.cache for rid in request_ids):
+            return None
+        key = self._graph_key(entries)
+        try:
+            host, lens_after = self._prepare(entries, fixed=key)
+        except OutOfPages:
+            return None
+        return (key, tuple(request_ids), host, lens_after)
+
+    def step_ahead(self, ahead, tokens: Sequence[int]) -> torch.Tensor:
+        """Run the step prepared by `prepare_ahead` with the token ids that have arrived since."""
+        key, rids, host, lens_after = ahead
+        for t in tokens:
+            if not 0 <= int(t) < self.vocab_size:
+                raise EmbeddingOov(f"token id {t} outside the vocabulary of {self.vocab_size}")
+        host[:len(rids)] = tokens                       # the block starts with the token ids (Engine._layout)
+        return self._replay(key, host, lens_after, list(range(len(rids))), len(rids))
 
     def finish(self, request_id) -> None:
         """The request is over: its pages and its slot are given back."""

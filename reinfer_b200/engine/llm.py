@@ -52,6 +52,7 @@ class LLM:
         self._next_id = 0
         self.requests: Dict[Hashable, Request] = {}
         self.last_stats: Dict[str, float] = {}
+        self._ahead = None                      # tables of the next step, built while the device was busy
 
     # ---- requests -----------------------------------------------------------------------
     def add_request(self, prompt_token_ids: Sequence[int], params: Optional[SamplingParams] = None,
@@ -76,20 +77,34 @@ class LLM:
 
     def step(self) -> List[Request]:
         """One scheduler decision, one engine step, one sampler launch.  Returns the requests
-        that finished in it."""
+        that finished in it.
+
+        While the device runs the step, the host already builds the next step's tables under the guess
+        that the same requests simply go on decoding (`Engine.prepare_ahead`); if the next decision is
+        exactly that, only the sampled token ids are filled in before the replay."""
         out = self.scheduler.schedule()
         finished = list(out.finished)
         if not out.batch:
             return finished
-        entries = [StepEntry(s.request.request_id, s.tokens, [len(s.tokens) - 1] if s.sample else [])
-                   for s in out.batch]
-        logits = self.engine.step(entries)
+        ahead, self._ahead = self._ahead, None
+        rids = tuple(s.request.request_id for s in out.batch)
+        if ahead is not None and ahead[1] == rids and all(len(s.tokens) == 1 and s.sample for s in out.batch):
+            logits = self.engine.step_ahead(ahead, [s.tokens[0] for s in out.batch])
+        else:
+            entries = [StepEntry(s.request.request_id, s.tokens, [len(s.tokens) - 1] if s.sample else [])
+                       for s in out.batch]
+            logits = self.engine.step(entries)
         sampling = [s.request for s in out.batch if s.sample]
         sampled: Dict[Hashable, int] = {}
         if sampling:
-            toks = self.sampler.sample(logits, [r.params for r in sampling], [r.seed for r in sampling],
-                                       [len(r.output) for r in sampling],
-                                       [(lambda n, r=r: r.tokens_from(max(0, r.total_len - n), min(n, r.total_len))) for r in sampling])
+            n = self.sampler.launch(logits, [r.params for r in sampling], [r.seed for r in sampling],
+                                    [len(r.output) for r in sampling],
+                                    [(lambda k, r=r: r.tokens_from(max(0, r.total_len - k), min(k, r.total_len))) for r in sampling])
+            # the device is busy: prepare the next step if it is likely to be these requests again
+            if len(sampling) == len(out.batch) and not self.scheduler.waiting and \
+                    all(len(r.output) + 1 < r.params.max_tokens for r in sampling):
+                self._ahead = self.engine.prepare_ahead(rids)
+            toks = self.sampler.fetch(n)
             sampled = {r.request_id: t for r, t in zip(sampling, toks)}
         finished += self.scheduler.update(out.batch, sampled)
         return finished

@@ -51,6 +51,7 @@ class Sampler:
         self._host_params = torch.empty(self.max_rows * RECORD.itemsize, dtype=torch.uint8, pin_memory=True)
         self._host_hist = torch.empty((self.max_rows, HIST_CAP), dtype=torch.int32, pin_memory=True)
         self._host_out = torch.empty(self.max_rows, dtype=torch.int32, pin_memory=True)
+        self._done = torch.cuda.Event()
 
     def device_records(self, params: Sequence[SamplingParams], seeds: Sequence[int], steps: Sequence[int]) -> torch.Tensor:
         """The kernel's per-row records for rows without penalties, on the device (for callers that
@@ -64,9 +65,21 @@ class Sampler:
                steps: Sequence[int], histories: Optional[Sequence[Sequence[int]]] = None) -> List[int]:
         """One token per row of `logits` ([rows, vocab] float32 on the device).  Returns host ints
         (-1 for a row without a finite logit).  Blocks until the tokens are on the host."""
-        rows = logits.shape[0]
+        return self.fetch(self.launch(logits, params, seeds, steps, histories))
+
+    def fetch(self, rows: int) -> List[int]:
+        """The tokens of the last `launch` (waits for them)."""
         if rows == 0:
             return []
+        self._done.synchronize()
+        return [int(v) for v in self._host_out[:rows].tolist()]
+
+    def launch(self, logits: torch.Tensor, params: Sequence[SamplingParams], seeds: Sequence[int],
+               steps: Sequence[int], histories: Optional[Sequence[Sequence[int]]] = None) -> int:
+        """Launch the sampler and the copy of its tokens to pinned memory; returns the row count for `fetch`."""
+        rows = logits.shape[0]
+        if rows == 0:
+            return 0
         if rows > self.max_rows:
             raise ValueError(f"{rows} rows exceed the sampler's {self.max_rows}")
         rec = np.zeros(rows, dtype=RECORD)
@@ -96,5 +109,5 @@ class Sampler:
         out = torch.empty(rows, dtype=torch.int32, device=self.device)
         ops.sample(logits, None, dparams, dhist, self._work, out, rows)
         self._host_out[:rows].copy_(out, non_blocking=True)
-        torch.cuda.current_stream().synchronize()
-        return [int(v) for v in self._host_out[:rows].tolist()]
+        self._done.record()
+        return rows
