@@ -216,8 +216,105 @@ __global__ void qknorm_rope_append_kernel(const TA* __restrict__ qkv, const TW* 
     }
 }
 
+// The angles' cosines and sines of a step, once for all layers and heads: cs[t, p] = (cos, sin)(pos[t] * inv_freq[p]).
+__global__ void rope_table_kernel(const int* __restrict__ positions, const float* __restrict__ inv_freq,
+                                  float2* __restrict__ cs, int n_tokens, int half) {
+    pdl_trigger(); pdl_wait();
+    const int i = blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= n_tokens * half) return;
+    const int t = i / half, p = i % half;
+    float sn, c;
+    sincosf((float)positions[t] * inv_freq[p], &sn, &c);
+    cs[i] = make_float2(c, sn);
+}
+extern "C" int rb_rope_table(const int* positions, const float* inv_freq, void* cs, int n_tokens, int half, void* stream) {
+    if (n_tokens <= 0 || half <= 0) return 0;
+    return rb_launch(rope_table_kernel, dim3(rb_ceil_div((long long)n_tokens * half, 256)), dim3(256), 0, (cudaStream_t)stream,
+                     positions, inv_freq, (float2*)cs, n_tokens, half);
+}
+
+// The same operation for the common layout - bfloat16 activations and cache, the whole head rotated, head_dim a
+// multiple of 64 - with 4-byte loads and stores (a lane owns element pairs 2l, 2l+1 of both halves) and 16-byte
+// copies of the value rows; cosines and sines come from the step's table when one is given.
+template <typename TW>
+__global__ void qknorm_rope_append_vec_kernel(const bf16* __restrict__ qkv, const TW* __restrict__ qw, const TW* __restrict__ kw,
+                                              const float* __restrict__ inv_freq, const float2* __restrict__ cs_table,
+                                              const int* __restrict__ positions, const int* __restrict__ kv_slot,
+                                              bf16* __restrict__ q_out, bf16* __restrict__ cache,
+                                              int n_tokens, int QH, int KH, int d, int page_size, float eps) {
+    pdl_trigger(); pdl_wait();
+    const int heads = QH + 2 * KH;
+    const long long wglobal = ((long long)blockIdx.x * blockDim.x + threadIdx.x) >> 5;
+    const int lane = threadIdx.x & 31;
+    if (wglobal >= (long long)n_tokens * heads) return;
+    const int t = (int)(wglobal / heads);
+    const int hh = (int)(wglobal % heads);
+    const bf16* src = qkv + ((size_t)t * heads + hh) * d;
+    const int slot = kv_slot ? kv_slot[t] : -1;
+    if (hh >= QH + KH) {
+        if (slot < 0) return;
+        const int kh = hh - QH - KH;
+        const int page = slot / page_size, off = slot % page_size;
+        bf16* dst = cache + ((((size_t)page * 2 + 1) * KH + kh) * page_size + off) * d;
+        for (int i = lane; i < d / 8; i += 32)
+            reinterpret_cast<uint4*>(dst)[i] = reinterpret_cast<const uint4*>(src)[i];
+        return;
+    }
+    const bool is_q = hh < QH;
+    if (!is_q && slot < 0) return;
+    const TW* w = is_q ? qw : kw;
+    const int half = d >> 1;
+    bf16* dst;
+    if (is_q) dst = q_out + ((size_t)t * QH + hh) * d;
+    else {
+        const int page = slot / page_size, off = slot % page_size;
+        dst = cache + ((((size_t)page * 2 + 0) * KH + (hh - QH)) * page_size + off) * d;
+    }
+    // this lane's pairs: elements p, p+1 with p = 2*lane + 64*i, and their partners half further
+    float a0[4], a1[4], b0[4], b1[4];                         // head_dim <= 512
+    float ss = 0.0f;
+    const int n_it = half / 64;
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        if (i < n_it) {
+            const int p = 2 * lane + 64 * i;
+            const float2 lo = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(src + p));
+            const float2 hi = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(src + p + half));
+            a0[i] = lo.x; a1[i] = lo.y; b0[i] = hi.x; b1[i] = hi.y;
+            ss += lo.x * lo.x + lo.y * lo.y + hi.x * hi.x + hi.y * hi.y;
+        }
+    }
+    float rstd = 1.0f;
+    if (w) {
+        ss = warp_sum(ss);
+        rstd = 1.0f / sqrtf(ss / (float)d + eps);
+    }
+    const float pos = (float)positions[t];
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        if (i < n_it) {
+            const int p = 2 * lane + 64 * i;
+            float x0 = a0[i], x1 = a1[i], y0 = b0[i], y1 = b1[i];
+            if (w) {
+                x0 = x0 * rstd * to_f32(w[p]); x1 = x1 * rstd * to_f32(w[p + 1]);
+                y0 = y0 * rstd * to_f32(w[p + half]); y1 = y1 * rstd * to_f32(w[p + half + 1]);
+            }
+            float c0, s0, c1, s1;
+            if (cs_table) {
+                const float4 v = *reinterpret_cast<const float4*>(cs_table + (size_t)t * half + p);
+                c0 = v.x; s0 = v.y; c1 = v.z; s1 = v.w;
+            } else {
+                sincosf(pos * inv_freq[p], &s0, &c0);
+                sincosf(pos * inv_freq[p + 1], &s1, &c1);
+            }
+            *reinterpret_cast<__nv_bfloat162*>(dst + p) = __floats2bfloat162_rn(x0 * c0 - y0 * s0, x1 * c1 - y1 * s1);
+            *reinterpret_cast<__nv_bfloat162*>(dst + p + half) = __floats2bfloat162_rn(x0 * s0 + y0 * c0, x1 * s1 + y1 * c1);
+        }
+    }
+}
+
 extern "C" int rb_qknorm_rope_append(const void* qkv, int act_dtype, const void* qw, const void* kw, int w_dtype,
-                                     const float* inv_freq, const int* positions, const int* kv_slot,
+                                     const float* inv_freq, const void* cs_table, const int* positions, const int* kv_slot,
                                      void* q_out, void* k_out, void* cache, int cache_dtype,
                                      int n_tokens, int QH, int KH, int d, int rot, int page_size, float eps,
                                      void* stream) {
@@ -231,6 +328,16 @@ extern "C" int rb_qknorm_rope_append(const void* qkv, int act_dtype, const void*
     cudaStream_t s = (cudaStream_t)stream;
     const long long warps = (long long)n_tokens * (QH + 2 * KH);
     const int blocks = rb_ceil_div(warps, 4);
+    if (act_dtype == RB_BF16 && !k_out && cache && KH > 0 && rot == d && d % 64 == 0 && d <= 512 &&
+        (((uintptr_t)qkv | (uintptr_t)q_out | (uintptr_t)cache) & 15) == 0) {
+        if (w_dtype == RB_F32)
+            return rb_launch(qknorm_rope_append_vec_kernel<float>, dim3(blocks), dim3(128), 0, s, (const bf16*)qkv, (const float*)qw,
+                             (const float*)kw, inv_freq, (const float2*)cs_table, positions, kv_slot, (bf16*)q_out, (bf16*)cache,
+                             n_tokens, QH, KH, d, page_size, eps);
+        return rb_launch(qknorm_rope_append_vec_kernel<bf16>, dim3(blocks), dim3(128), 0, s, (const bf16*)qkv, (const bf16*)qw,
+                         (const bf16*)kw, inv_freq, (const float2*)cs_table, positions, kv_slot, (bf16*)q_out, (bf16*)cache,
+                         n_tokens, QH, KH, d, page_size, eps);
+    }
 #define RB_QK(TA, TW) return rb_launch(qknorm_rope_append_kernel<TA, TW, TA>, dim3(blocks), dim3(128), 0, s, \
         (const TA*)qkv, (const TW*)qw, (const TW*)kw, inv_freq, positions, kv_slot, (TA*)q_out, (TA*)k_out, (TA*)cache, \
         n_tokens, QH, KH, d, rot, page_size, eps)

@@ -132,7 +132,7 @@ def qknorm_rope_append(qkv: torch.Tensor, qw: Optional[torch.Tensor], kw: Option
                        inv_freq: Optional[torch.Tensor], positions: Optional[torch.Tensor],
                        kv_slot: Optional[torch.Tensor], q_out: torch.Tensor, cache: Optional[torch.Tensor],
                        QH: int, KH: int, d: int, rot: int, page_size: int, eps: float,
-                       k_out: Optional[torch.Tensor] = None) -> None:
+                       k_out: Optional[torch.Tensor] = None, cs_table: Optional[torch.Tensor] = None) -> None:
     """Per-head RMSNorm of q and k (if weights are given), rotation of the first `rot` dims (if
     rot > 0), q -> q_out, k and v -> the cache at kv_slot (or k -> k_out, v untouched)."""
     n = qkv.shape[0]
@@ -141,11 +141,19 @@ def qknorm_rope_append(qkv: torch.Tensor, qw: Optional[torch.Tensor], kw: Option
     wd = dt(qw) if qw is not None else F32
     if qw is not None:
         _need(kw is not None and kw.dtype == qw.dtype, "qknorm_rope_append: q/k norm weights of one dtype")
-    _check(lib().rb_qknorm_rope_append(_p(qkv), c_int(dt(qkv)), _p(qw), _p(kw), c_int(wd), _p(inv_freq),
+    _check(lib().rb_qknorm_rope_append(_p(qkv), c_int(dt(qkv)), _p(qw), _p(kw), c_int(wd), _p(inv_freq), _p(cs_table),
                                        _p(positions), _p(kv_slot), _p(q_out), _p(k_out), _p(cache),
                                        c_int(dt(cache) if cache is not None else dt(qkv)),
                                        c_int(n), c_int(QH), c_int(KH), c_int(d), c_int(rot), c_int(page_size),
                                        c_float(eps), _stream()), "qknorm_rope_append")
+
+
+def rope_table(positions: torch.Tensor, inv_freq: torch.Tensor) -> torch.Tensor:
+    """(cos, sin) of positions[t] * inv_freq[p] as float32 [T, half, 2]: computed once per step, read by every layer."""
+    T, half = positions.numel(), inv_freq.numel()
+    cs = torch.empty((T, half, 2), dtype=torch.float32, device=positions.device)
+    _check(lib().rb_rope_table(_p(positions), _p(inv_freq), _p(cs), c_int(T), c_int(half), _stream()), "rope_table")
+    return cs
 
 
 def kv_append(k: torch.Tensor, v: torch.Tensor, kv_slot: torch.Tensor, cache: torch.Tensor,

@@ -78,8 +78,16 @@ class Attention(Mixer):
         slots = g.kv_slot if cache.write else None
         if fused is not None:
             inv_freq, rot = fused
+            cs = None
+            if rot == d and d % 64 == 0 and xn.dtype == torch.bfloat16 and inv_freq is not None and T > 64:
+                # the angles depend on the step's positions only: for a large step the first layer tabulates
+                # their cosines and sines (a small step computes them in place and saves the launch)
+                key = ("rope", inv_freq.data_ptr(), rot)
+                cs = ctx.shared.get(key)
+                if cs is None:
+                    cs = ctx.shared[key] = ops.rope_table(ctx.positions, inv_freq)
             ops.qknorm_rope_append(qkv, self.q_norm_w, self.k_norm_w, inv_freq, ctx.positions, slots, q,
-                                   cache.kv, QH, KH, d, rot, g.page_size, self.eps)
+                                   cache.kv, QH, KH, d, rot, g.page_size, self.eps, cs_table=cs)
         else:
             # an encoding that is not a plain rotation: norm, then the part's own apply(), then append
             k = torch.empty((T, KH, d), dtype=xn.dtype, device=xn.device)

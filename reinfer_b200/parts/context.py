@@ -51,6 +51,7 @@ class StepContext:
     max_q_len: int = 0
     max_kv_len: int = 0
     layer_caches: Dict[str, LayerCache] = field(default_factory=dict)
+    shared: Dict[object, torch.Tensor] = field(default_factory=dict)   # what one layer computed for all (per step)
 
     def empty(self, shape, dtype=None) -> torch.Tensor:
         return torch.empty(shape, dtype=dtype or self.dtype, device=self.device)

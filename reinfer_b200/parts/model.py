@@ -139,6 +139,7 @@ class Model:
     def forward(self, ctx, want_rows: Optional[torch.Tensor]) -> Optional[torch.Tensor]:
         """Run the step's tokens through every layer in run order; return float32 logits
         [len(want_rows), vocab] for the wanted token rows (None if none are wanted)."""
+        ctx.shared.clear()                      # what layers share is computed anew in every pass (a captured pass included)
         x = self.embedding.forward(ctx)
         for i, key in self.run:
             self.layers[i].block.forward(ctx, x, ctx.layer_caches[key])

@@ -179,6 +179,13 @@ def test_qknorm_rope_append(QH, KH, d, rot, page, dtype, norm):
         assert (flat[sl, 0].double() - k[t]).abs().max().item() <= tol * k.abs().max().item()
         assert torch.equal(flat[sl, 1], qkv.view(T, QH + 2 * KH, d)[t, QH + KH:])
     assert bool((flat[untouched.to(DEV)] == 7.0).all())                      # nothing else was written
+    if dtype == torch.bfloat16 and rot == d and d % 64 == 0:
+        # the same with the step's table of cosines and sines: identical bits
+        cache2 = torch.full_like(cache, 7.0)
+        q2 = torch.empty_like(q_out)
+        ops.qknorm_rope_append(qkv, qw, kw, rope.inv_freq, pos, slots, q2, cache2, QH, KH, d, rot, page, eps,
+                               cs_table=ops.rope_table(pos, rope.inv_freq))
+        assert torch.equal(q2, q_out) and torch.equal(cache2, cache)
 
 
 def test_kv_append_and_k_out_path():
