@@ -172,3 +172,20 @@ def test_full_size_layer_shape(tmp_path, dtype):
         got = run_steps(engine, steps)
         compare(got, want, 2e-4 if dtype == "float32" else TOL[dtype])
         del engine
+
+
+@pytest.mark.parametrize("store,dtype", [("f32", "bfloat16"), ("bf16", "float32")])
+def test_storage_and_compute_dtype_may_differ(models, store, dtype):
+    """A folder stored in 32 bits run in bfloat16 (its tensors stay 32-bit: the plain kernels take the
+    products) and a folder stored in bfloat16 run in float32 (widened): both against the plain
+    implementation of the stored values."""
+    from reinfer_b200.engine import Engine
+    which = "B"
+    model_dir = models[(which, store)]
+    seqs = tiny.sequences(which)
+    steps = tiny.cut_mixed(seqs, seed=5)
+    engine = Engine.from_model_dir(model_dir, dtype=dtype, page_size=8, max_tokens=tiny.pool_tokens_needed(steps), max_num_seqs=4)
+    if store == "f32":
+        assert engine.model.layers[0].mixer.w_qkv.dtype == torch.float32
+    got = run_steps(engine, steps)
+    compare(got, truth(model_dir, seqs), TOL[dtype])
