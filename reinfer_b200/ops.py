@@ -268,9 +268,6 @@ def decode_splits(ctas: int, tiles: int, slots: int = 296) -> int:
     return best
 
 
-FA_TARGET_CTAS = 296                       # two CTAs for each of the 148 SMs
-
-
 def attention(ctx, q: torch.Tensor, cache: torch.Tensor, group, out: torch.Tensor, QH: int, KH: int, d: int,
               window: int, scale: float) -> None:
     """Attention of a step's tokens over their requests' pages.  float32 (and head sizes the

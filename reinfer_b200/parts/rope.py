@@ -33,8 +33,14 @@ class RotaryEncoding(PositionEncoding):
         return self.inv_freq, self.rotary_dim
 
     def apply(self, ctx, q, k, positions) -> None:
-        # the generic path: rotate q and k in place through the fused kernel with norm and cache off
-        raise NotImplementedError("RotaryEncoding is applied inside the attention kernel (fused_rotary)")
+        """The unfused form, for a mixer that does not take `fused_rotary()`: q [T, QH, d] and k [T, KH, d]
+        are rotated in place (through the same kernel, with the head norm and the cache switched off)."""
+        for x in (q, k):
+            T, heads, d = x.shape
+            out = torch.empty_like(x)
+            ops.qknorm_rope_append(x.reshape(T, heads * d), None, None, self.inv_freq, positions, None, out, None,
+                                   heads, 0, d, self.rotary_dim, 1, 0.0)
+            x.copy_(out)
 
 
 register_part("position", "rope", RotaryEncoding)

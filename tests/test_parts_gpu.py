@@ -371,3 +371,22 @@ def test_window_group_gives_pages_back_and_all_cuts_agree(tmp_path, dtype, page)
         assert (whole[100:] - whole[100:].mean()).abs().max() > 0
     finally:
         unregister_architecture("ToyWindowLM")
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_rotary_part_unfused_apply(dtype):
+    """RotaryEncoding.apply (the form a foreign mixer would call) against the plain rotation, partial width too."""
+    from reinfer_b200.parts.rope import RotaryEncoding
+    for d, rot in ((32, 32), (48, 16)):
+        r = RotaryEncoding(head_dim=d, theta=1e4, rotary_dim=rot)
+        r.prepare(DEV)
+        pos = torch.tensor([0, 3, 77, 1000], dtype=torch.int32, device=DEV)
+        q, k = torch.randn(4, 5, d, device=DEV).to(dtype), torch.randn(4, 2, d, device=DEV).to(dtype)
+        q0, k0 = q.clone(), k.clone()
+        ctx, _ = make_ctx(dtype, pos.tolist(), [0] * 4, [0, 4], [1001])
+        r.apply(ctx, q, k, pos)
+        for got, src in ((q, q0), (k, k0)):
+            ref = torch.cat([plain.rope_half_split(src[..., :rot].double().cpu(), pos.cpu(), 1e4), src[..., rot:].double().cpu()], -1)
+            # the angle is a float32 product: at position 1000 it is off by up to 6e-5 rad from the float64 angle
+            tol = 2e-2 if dtype == torch.bfloat16 else 5e-5
+            assert (got.double().cpu() - ref).abs().max().item() <= tol * ref.abs().max().item()
