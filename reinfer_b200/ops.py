@@ -258,11 +258,12 @@ USE_TMA_ATTENTION = os.environ.get("REINFER_B200_TMA_ATTENTION", "1") != "0"
 def decode_splits(ctas: int, tiles: int, slots: int = 296) -> int:
     """How many CTAs share one (request, kv head)'s keys.  Model of the launch's time: waves of
     `slots` resident CTAs, each CTA walking tiles/n tiles plus about 2.5 tile-times of fill, drain
-    and merge; the split count with the least estimate wins (ties to the smaller)."""
+    and merge, then a merge kernel that walks the n partial results; the split count with the
+    least estimate wins (ties to the smaller)."""
     best, best_cost = 1, None
     for n in range(1, max(1, min(64, tiles)) + 1):
         waves = -(-ctas * n // slots)
-        cost = waves * (tiles / n + 2.5)
+        cost = waves * (tiles / n + 2.5) + 0.12 * n        # + the merge kernel's walk over n partial results
         if best_cost is None or cost < best_cost - 1e-9:
             best, best_cost = n, cost
     return best
