@@ -483,18 +483,26 @@ __global__ void splitk_reduce_kernel(const float* __restrict__ ws, void* __restr
 
 // ------------------------------------------------------------------ host side
 // How many CTAs of this kernel can be resident at once when launched as clusters of `sp` (1: no cluster).
+// CTAs per SM come from the shared memory alone (79 registers x 192 threads never bind): the occupancy calls
+// answer one CTA per SM for these kernels although two are resident (256 CTAs were seen to start within a
+// microsecond), so their cluster count - which knows how clusters tile the GPCs - is scaled by the ratio.
 template <int BN, int STAGES, bool DUAL>
 static int tc_capacity(int sp, size_t smem) {
     static int cache[9] = {0, 0, 0, 0, 0, 0, 0, 0, 0};
     if (cache[sp]) return cache[sp];
-    int n = 0;
-    if (sp == 1) {
-        int per_sm = 0, sms = 0, dev = 0;
-        cudaGetDevice(&dev);
-        cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
-        if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, gemm_tc_kernel<BN, STAGES, DUAL>, TC_THREADS, smem) == cudaSuccess)
-            n = per_sm * sms;
-    } else {
+    int dev = 0, sms = 0, smem_sm = 0, reserved = 0;
+    cudaGetDevice(&dev);
+    cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+    cudaDeviceGetAttribute(&smem_sm, cudaDevAttrMaxSharedMemoryPerMultiprocessor, dev);
+    cudaDeviceGetAttribute(&reserved, cudaDevAttrReservedSharedMemoryPerBlock, dev);
+    int fit = (int)((size_t)smem_sm / (smem + (size_t)reserved));
+    const int bound = BN <= 64 ? 2 : 1;                             // the kernel's __launch_bounds__
+    if (fit > bound) fit = bound;
+    if (fit < 1) fit = 1;
+    int said = 0;
+    if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&said, gemm_tc_kernel<BN, STAGES, DUAL>, TC_THREADS, smem) != cudaSuccess || said < 1) said = 1;
+    int n = fit * sms;
+    if (sp > 1) {
         cudaLaunchConfig_t cfg = {};
         cfg.gridDim = dim3(1, 1, sp); cfg.blockDim = dim3(TC_THREADS); cfg.dynamicSmemBytes = smem;
         cudaLaunchAttribute attr[1];
@@ -502,12 +510,38 @@ static int tc_capacity(int sp, size_t smem) {
         attr[0].val.clusterDim.x = 1; attr[0].val.clusterDim.y = 1; attr[0].val.clusterDim.z = sp;
         cfg.attrs = attr; cfg.numAttrs = 1;
         int clusters = 0;
-        if (cudaOccupancyMaxActiveClusters(&clusters, gemm_tc_kernel<BN, STAGES, DUAL>, &cfg) == cudaSuccess) n = clusters * sp;
+        if (cudaOccupancyMaxActiveClusters(&clusters, gemm_tc_kernel<BN, STAGES, DUAL>, &cfg) == cudaSuccess && clusters > 0)
+            n = clusters * sp * (fit > said ? fit / said : 1);
+        else
+            n = sms / sp * sp;                                      // unknown: one CTA per SM
     }
     (void)cudaGetLastError();
-    if (n <= 0) n = 148;                                            // unknown: assume one CTA per SM
     cache[sp] = n;
     return n;
+}
+
+// A weight-streaming launch (one token tile).  Estimate, for every split count that leaves >= 4 k-blocks per
+// CTA, waves x (fixed cost + the time its resident CTAs need to stream their share) and take the least.  The
+// capacity is what the device says can be resident as clusters of that size - fewer than SMs x CTAs/SM when
+// clusters do not tile the GPCs.  caps (optional, 9 ints) receives the capacities that were used.
+template <int BN, int STAGES, bool DUAL>
+static int tc_choose_splits(int tiles, int total_kb, size_t smem, int* caps) {
+    const double kb_us = (double)(TC_BM * TC_BK * 2 * (DUAL ? 2 : 1)) / 6.5e6;   // one k-block of weights at 6.5 TB/s
+    double best = 1e30;
+    int splits = 1;
+    for (int sp = 1; sp <= 8 && total_kb / sp >= 4; ++sp) {
+        const int cap = tc_capacity<BN, STAGES, DUAL>(sp, smem);
+        if (caps) caps[sp] = cap;
+        const long long ctas = (long long)tiles * sp;
+        const long long waves = (ctas + cap - 1) / cap;
+        const long long resident = ctas < cap ? ctas : cap;
+        const double kbs = (double)rb_ceil_div(total_kb, sp);
+        const double shared_us = kbs * kb_us * (double)resident;        // all resident CTAs at the device's bandwidth
+        const double alone_us = kbs * kb_us * 6.5e6 / 30e3;              // one CTA's pipeline sustains about 30 GB/s
+        const double cost = (double)waves * (6.0 + (sp > 1 ? 3.0 : 0.0) + (shared_us > alone_us ? shared_us : alone_us));
+        if (cost < best - 0.25) { best = cost; splits = sp; }
+    }
+    return splits;
 }
 
 // want_splits: 0 = choose; > 0 = that many through a cluster (at most 8); < 0 = that many through the workspace.
@@ -519,6 +553,8 @@ static int launch_tc(const CUtensorMap& mw, const CUtensorMap& mx, void* C, floa
     if (!configured) {
         cudaError_t e = cudaFuncSetAttribute(gemm_tc_kernel<BN, STAGES, DUAL>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         if (e != cudaSuccess) return (int)e;
+        // the whole of the SM's memory as shared memory, so that two CTAs of the small-tile kernels fit beside each other
+        (void)cudaFuncSetAttribute(gemm_tc_kernel<BN, STAGES, DUAL>, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared);
         configured = true;
     }
     const int total_kb = rb_ceil_div(K, TC_BK);
@@ -531,25 +567,7 @@ static int launch_tc(const CUtensorMap& mw, const CUtensorMap& mx, void* C, floa
     bool via_ws = false;
     if (want_splits > 0) { splits = want_splits; via_ws = !can_park; }
     else if (want_splits < 0) { splits = -want_splits; via_ws = true; }
-    else if (t_tiles == 1 && can_park) {
-        // A weight-streaming launch (one token tile).  Estimate, for every split count that leaves >= 4
-        // k-blocks per CTA, waves x (fixed cost + the time its resident CTAs need to stream their share at
-        // full bandwidth) and take the least.  The capacity is what the device says can be resident as
-        // clusters of that size - fewer than SMs x CTAs/SM when clusters do not tile the GPCs.
-        const double kb_us = (double)(TC_BM * TC_BK * 2 * (DUAL ? 2 : 1)) / 6.5e6;   // one k-block of weights at 6.5 TB/s
-        double best = 1e30;
-        for (int sp = 1; sp <= 8 && total_kb / sp >= 4; ++sp) {
-            const int cap = tc_capacity<BN, STAGES, DUAL>(sp, smem);
-            const long long ctas = (long long)tiles * sp;
-            const long long waves = (ctas + cap - 1) / cap;
-            const long long resident = ctas < cap ? ctas : cap;
-            const double kbs = (double)rb_ceil_div(total_kb, sp);
-            const double shared_us = kbs * kb_us * (double)resident;        // all resident CTAs at the device's bandwidth
-            const double alone_us = kbs * kb_us * 6.5e6 / 30e3;              // one CTA's pipeline sustains about 30 GB/s
-            const double cost = (double)waves * (6.0 + (sp > 1 ? 3.0 : 0.0) + (shared_us > alone_us ? shared_us : alone_us));
-            if (cost < best - 0.25) { best = cost; splits = sp; }
-        }
-    }
+    else if (t_tiles == 1 && can_park) splits = tc_choose_splits<BN, STAGES, DUAL>(tiles, total_kb, smem, nullptr);
     if (splits > total_kb) splits = total_kb;
     int kb_per_split = rb_ceil_div(total_kb, splits);
     splits = rb_ceil_div(total_kb, kb_per_split);                   // no empty split
@@ -652,6 +670,26 @@ extern "C" int rb_gemm_bf16_swiglu(const void* X, const void* Wgu, void* act, in
         case 128: return launch_tc<128, 4, true>(mw, mx, act, nullptr, 0, T, F, K, ldc, 0, 0, s);
         default: return launch_tc<256, 3, true>(mw, mx, act, nullptr, 0, T, F, K, ldc, 0, 0, s);
     }
+}
+
+// What the decode product (T <= 16) would choose for N output features and K: out[0] = splits, out[1..8] = the
+// resident-CTA capacity the device reports for clusters of that size.  For tests and tuning.
+extern "C" int rb_gemm_plan(int N, int K, int dual, int* out) {
+    const int tiles = rb_ceil_div(N, TC_BM), total_kb = rb_ceil_div(K, TC_BK);
+    int caps[9] = {0};
+    if (dual) {
+        constexpr size_t smem = (size_t)3 * (2 * TC_BM * TC_BK * 2 + 16 * TC_BK * 2) + sizeof(TcShared) + 1024;
+        cudaFuncSetAttribute(gemm_tc_kernel<16, 3, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        cudaFuncSetAttribute(gemm_tc_kernel<16, 3, true>, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared);
+        out[0] = tc_choose_splits<16, 3, true>(tiles, total_kb, smem, caps);
+    } else {
+        constexpr size_t smem = (size_t)6 * (TC_BM * TC_BK * 2 + 16 * TC_BK * 2) + sizeof(TcShared) + 1024;
+        cudaFuncSetAttribute(gemm_tc_kernel<16, 6, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        cudaFuncSetAttribute(gemm_tc_kernel<16, 6, false>, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared);
+        out[0] = tc_choose_splits<16, 6, false>(tiles, total_kb, smem, caps);
+    }
+    for (int i = 1; i <= 8; ++i) out[i] = caps[i];
+    return 0;
 }
 
 // The error word of the tensor-core kernels (0 = none); synchronises the device.  With reset != 0 it is cleared.
