@@ -36,6 +36,8 @@ struct FtArgs {
     int QH, KH, d, page_size, page_shift, max_pages, window;
     int Gc, chunks, first_entry, n_entries, n_splits;
     float scale_log2;
+    const void* next_w;                     // decode: a range to call into L2 once this CTA's tiles are requested
+    long long next_bytes;
 };
 
 struct FtShared {
@@ -69,6 +71,7 @@ __device__ __forceinline__ uint32_t ft_off(int row, int chunk, int half_bytes) {
 template <int HALVES, int NST>
 __global__ void __launch_bounds__(FT_THREADS)
 fa_decode_tma_kernel(const __grid_constant__ CUtensorMap map_kv, const FtArgs a) {
+    RB_TL(4);
     constexpr int D = HALVES * 64;
     constexpr int KV_BYTES = HALVES * FT_HALF_BYTES;           // one K (or V) tile
     constexpr int STAGE = 2 * KV_BYTES;
@@ -90,10 +93,13 @@ fa_decode_tma_kernel(const __grid_constant__ CUtensorMap map_kv, const FtArgs a)
     // shared memory starts at zero: rows that no copy fills are then finite
     for (int i = threadIdx.x; i < (NST * STAGE + HALVES * Q_HALF) / 16; i += FT_THREADS)
         reinterpret_cast<uint4*>(smem)[i] = make_uint4(0, 0, 0, 0);
+    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");   // the zeroing precedes the TMA writes
     __syncthreads();
     pdl_trigger();
-    pdl_wait();
 
+    // The step's tables (lengths, block table) were complete before its first kernel began, and the keys of
+    // earlier positions were written by earlier steps: both may be read while the kernels before this one still
+    // run.  Only the query rows and the new token's key and value wait for them.
     const int e = a.first_entry + blockIdx.x;
     const int kh = blockIdx.y / a.chunks, chunk = blockIdx.y % a.chunks;
     const int head0 = kh * (a.QH / a.KH) + chunk * a.Gc;
@@ -108,14 +114,17 @@ fa_decode_tma_kernel(const __grid_constant__ CUtensorMap map_kv, const FtArgs a)
     const int t_begin = t_lo + split * per, t_end = min(t_hi, t_begin + per);
     const int n_tiles = max(0, t_end - t_begin);
 
-    // Q rows (row r = query head head0 + r) into the swizzled layout
-    for (int i = threadIdx.x; i < a.Gc * (a.d / 8); i += FT_THREADS) {
-        const int row = i / (a.d / 8), c = i % (a.d / 8);
-        const uint4 v = *reinterpret_cast<const uint4*>(a.q + ((size_t)tok * a.QH + head0 + row) * a.d + c * 8);
-        *reinterpret_cast<uint4*>(sQ + ft_off(row, c, Q_HALF)) = v;
+    if (warp < FT_WARPS) {
+        pdl_wait();
+        RB_TL_MARK();
+        // Q rows (row r = query head head0 + r) into the swizzled layout, by the consumer warps that read them
+        for (int i = threadIdx.x; i < a.Gc * (a.d / 8); i += FT_WARPS * 32) {
+            const int row = i / (a.d / 8), c = i % (a.d / 8);
+            const uint4 v = *reinterpret_cast<const uint4*>(a.q + ((size_t)tok * a.QH + head0 + row) * a.d + c * 8);
+            *reinterpret_cast<uint4*>(sQ + ft_off(row, c, Q_HALF)) = v;
+        }
+        asm volatile("bar.sync 1, %0;" ::"n"(FT_WARPS * 32) : "memory");
     }
-    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");   // the zeroing above precedes the TMA writes
-    __syncthreads();
 
     const int box_rows = min(a.page_size, FT_BN);
     const int subs = FT_BN / box_rows;
@@ -134,10 +143,11 @@ fa_decode_tma_kernel(const __grid_constant__ CUtensorMap map_kv, const FtArgs a)
         // ---- producer warp: runs ahead of the consumers by up to NST tiles --------------------
         // Block-table entries are fetched 32 at a time by the whole warp and handed to lane 0.
         int cached_first = 0, cached = -1;                        // page index of lane 0's entry; entry of this lane
-        bool have = false;
+        bool have = false, waited = false;
         for (int it = 0; it < n_tiles; ++it) {
             const int s = it % NST;
             const int k0 = (t_begin + it) * FT_BN;
+            if (!waited && k0 + FT_BN > pos) { pdl_wait(); waited = true; }   // the tile with this step's key and value
             const int pi0 = k0 >> a.page_shift;
             const int need_last = (k0 + (subs - 1) * box_rows) >> a.page_shift;
             if (!have || need_last >= cached_first + 32) {
@@ -260,6 +270,11 @@ fa_decode_tma_kernel(const __grid_constant__ CUtensorMap map_kv, const FtArgs a)
         return;
     }
     if (warp == FT_WARPS) return;                              // the producer has no part in the merge
+    // this CTA's keys and values have arrived: while the partial results are merged and the kernels after this
+    // one start up, memory would idle - the weights that the next product streams are called into L2 now
+    if (threadIdx.x == 0)
+        l2_prefetch_share(a.next_w, a.next_bytes, (blockIdx.z * gridDim.y + blockIdx.y) * gridDim.x + blockIdx.x,
+                          gridDim.x * gridDim.y * gridDim.z);
     // merge the four warps (fixed order), then store or hand to the merge kernel
 #pragma unroll
     for (int i = 0; i < 2; ++i) {
@@ -314,6 +329,7 @@ fa_decode_tma_kernel(const __grid_constant__ CUtensorMap map_kv, const FtArgs a)
 template <int HALVES, int NST>
 __global__ void __launch_bounds__(FT_THREADS)
 fa_prefill_tma_kernel(const __grid_constant__ CUtensorMap map_kv, const FtArgs a) {
+    RB_TL(10);
     constexpr int D = HALVES * 64;
     constexpr int KV_BYTES = HALVES * FT_HALF_BYTES;
     constexpr int STAGE = 2 * KV_BYTES;
@@ -555,7 +571,9 @@ fa_prefill_tma_kernel(const __grid_constant__ CUtensorMap map_kv, const FtArgs a
 // out[t, h, :] = sum_s w_s o_s / sum_s w_s,  w_s = 2^(lse_s - max lse), splits in ascending order
 __global__ void ft_merge_kernel(const float* __restrict__ part_o, const float* __restrict__ part_lse, bf16* __restrict__ out,
                                 int first_tok, int QH, int d, int n_splits) {
+    RB_TL(5);
     pdl_trigger(); pdl_wait();
+    RB_TL_MARK();
     const int t = blockIdx.x, h = blockIdx.y;
     const size_t base = ((size_t)t * QH + h) * n_splits;
     float M = -INFINITY;
@@ -593,8 +611,9 @@ static int ft_launch(const CUtensorMap& map, const FtArgs& a, cudaStream_t s) {
 extern "C" int rb_fa_decode_tma(const void* q, const void* cache, long long num_pages, const int* block_table, const int* cu_q,
                                 const int* kv_len, void* out, float* part_o, float* part_lse, int first_entry, int n_entries,
                                 int first_tok, int n_splits, int QH, int KH, int d, int page_size, int max_pages, int window,
-                                float scale, void* stream) {
+                                float scale, const void* next_w, long long next_bytes, void* stream) {
     if (n_entries <= 0) return 0;
+    if ((uintptr_t)next_w & 15) RB_REFUSE("attention: the range to prefetch must start on a 16-byte boundary");
     if (QH <= 0 || KH <= 0 || QH % KH) RB_REFUSE("attention: %d query heads over %d kv heads", QH, KH);
     if (d <= 0 || d % 8 || d > 256) RB_REFUSE("attention (TMA): head_dim %d is not a multiple of 8 up to 256", d);
     int shift = -1;
@@ -612,6 +631,7 @@ extern "C" int rb_fa_decode_tma(const void* q, const void* cache, long long num_
     for (int c = 16; c >= 1; --c) if (G % c == 0) { a.Gc = c; break; }
     a.chunks = G / a.Gc; a.first_entry = first_entry; a.n_entries = n_entries; a.n_splits = n_splits;
     a.scale_log2 = scale * 1.4426950408889634f;
+    a.next_w = next_w; a.next_bytes = next_bytes;
     CUtensorMap map;
     const int box_rows = page_size < FT_BN ? page_size : FT_BN;
     if (rb_tensor_map_bf16(cache, num_pages * 2LL * KH * page_size, d, d, box_rows, &map)) return -1;
@@ -671,3 +691,5 @@ extern "C" int rb_attn_error(int reset) {
     if (reset && v) { int z = 0; cudaMemcpyToSymbol(g_rb_kernel_error, &z, sizeof(int)); }
     return v;
 }
+
+RB_TL_SETTER(rb_attn_step_timeline)

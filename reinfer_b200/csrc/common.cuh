@@ -60,6 +60,38 @@ __device__ __forceinline__ float block_max(float v, float* red) {
     return r;
 }
 
+// With -DRB_TIMELINE thread 0 of every CTA of a kernel that opens with RB_TL(id) appends a record
+// {id << 32 | linear block index, start, end, mark} (mark: where the kernel calls RB_TL_MARK(), usually after its wait for the kernels before) (globaltimer, ns) to a buffer set through the translation
+// unit's setter (RB_TL_SETTER): word 0 of the buffer counts records, word 1 holds the capacity, records of
+// 4 words start at word 4.  A development aid for seeing how the kernels of a step overlap; off by default.
+#ifdef RB_TIMELINE
+static __device__ unsigned long long* g_rb_tl = nullptr;
+struct RbTlScope {
+    unsigned long long t0, aux;
+    int id;
+    __device__ __forceinline__ explicit RbTlScope(int id_) : aux(0), id(id_) { asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t0)); }
+    __device__ __forceinline__ void mark() { asm volatile("mov.u64 %0, %globaltimer;" : "=l"(aux)); }
+    __device__ __forceinline__ ~RbTlScope() {
+        unsigned long long* b = g_rb_tl;
+        if (!b || threadIdx.x || threadIdx.y || threadIdx.z) return;
+        unsigned long long t1;
+        asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t1));
+        const unsigned long long slot = atomicAdd(b, 1ULL);
+        if (slot >= b[1]) return;
+        unsigned long long* r = b + 4 + slot * 4;
+        r[0] = ((unsigned long long)id << 32) | (unsigned)((blockIdx.z * gridDim.y + blockIdx.y) * gridDim.x + blockIdx.x);
+        r[1] = t0; r[2] = t1; r[3] = aux;
+    }
+};
+#define RB_TL(id) RbTlScope rb_tl_scope(id)
+#define RB_TL_MARK() rb_tl_scope.mark()
+#define RB_TL_SETTER(fn) extern "C" int fn(unsigned long long* buf) { return (int)cudaMemcpyToSymbol(g_rb_tl, &buf, sizeof(buf)); }
+#else
+#define RB_TL(id) do { } while (0)
+#define RB_TL_MARK() do { } while (0)
+#define RB_TL_SETTER(fn)
+#endif
+
 // Programmatic dependent launch.  A kernel launched through rb_launch() may begin while its
 // predecessor in the stream is still running; it must call pdl_wait() before it touches any
 // memory that a predecessor writes or reads.  pdl_trigger() lets the successor begin.  Both are
@@ -79,6 +111,23 @@ static inline int rb_launch(void (*kernel)(KArgs...), dim3 grid, dim3 block, siz
     attr[0].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = attr;
     cfg.numAttrs = g_rb_pdl ? 1 : 0;
+    cudaError_t e = cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);
+    if (e != cudaSuccess) { (void)cudaGetLastError(); return (int)e; }
+    return (int)cudaGetLastError();
+}
+
+// The same for a grid whose CTAs form clusters of cluster_x along x (grid.x a multiple of it).
+template <typename... KArgs, typename... Args>
+static inline int rb_launch_cluster(void (*kernel)(KArgs...), dim3 grid, dim3 block, int cluster_x, size_t smem, cudaStream_t s, Args&&... args) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid; cfg.blockDim = block; cfg.dynamicSmemBytes = smem; cfg.stream = s;
+    cudaLaunchAttribute attr[2];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = cluster_x; attr[0].val.clusterDim.y = 1; attr[0].val.clusterDim.z = 1;
+    attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[1].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = g_rb_pdl ? 2 : 1;
     cudaError_t e = cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);
     if (e != cudaSuccess) { (void)cudaGetLastError(); return (int)e; }
     return (int)cudaGetLastError();

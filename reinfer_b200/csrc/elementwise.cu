@@ -39,14 +39,28 @@ extern "C" int rb_embed_gather(const void* table, int table_dtype, const int* id
 // One block per row; each thread sums its strided elements in ascending order and the
 // block tree is fixed, so a row's result does not depend on the other rows.
 template <typename TD, typename TW, typename TO, int PER>
-__global__ void add_rmsnorm_kernel(float* __restrict__ x, const TD* __restrict__ delta,
+__global__ void add_rmsnorm_kernel(float* __restrict__ x, const TD* __restrict__ delta, int n_delta, long long delta_stride,
                                    const TW* __restrict__ w, TO* __restrict__ out,
                                    const int* __restrict__ row_idx, int h, float eps) {
+    RB_TL(2);
     __shared__ float red[32];
-    pdl_trigger(); pdl_wait();
+    pdl_trigger();
+    // the norm's weights never change: they are fetched while the kernels before this one still run
+    float wv[PER > 0 ? PER : 1];
+    if (PER > 0) {
+#pragma unroll
+        for (int k = 0; k < PER; ++k) {
+            const int i = threadIdx.x + k * blockDim.x;
+            wv[k] = i < h ? to_f32(w[i]) : 0.0f;
+        }
+    }
+    pdl_wait();
+    RB_TL_MARK();
     const int r = blockIdx.x;
     const size_t in_row = row_idx ? (size_t)row_idx[r] : (size_t)r;
     float* xr = x + in_row * h;
+    const TD* dr = delta ? delta + in_row * h : nullptr;
+    const bool keep = delta && !row_idx;              // gathered rows are read once more by nobody: x stays as it is
     // each thread keeps its strided elements in registers (PER of them; PER == 0: rows too wide, re-read)
     float v[PER > 0 ? PER : 1];
     float ss = 0.0f;
@@ -57,7 +71,10 @@ __global__ void add_rmsnorm_kernel(float* __restrict__ x, const TD* __restrict__
             float t = 0.0f;
             if (i < h) {
                 t = xr[i];
-                if (delta) { t += to_f32(delta[in_row * h + i]); xr[i] = t; }
+                if (delta) {
+                    for (int p = 0; p < n_delta; ++p) t += to_f32(dr[(size_t)p * delta_stride + i]);   // ascending: a fixed order
+                    if (keep) xr[i] = t;
+                }
             }
             v[k] = t;
             ss += t * t;
@@ -65,7 +82,10 @@ __global__ void add_rmsnorm_kernel(float* __restrict__ x, const TD* __restrict__
     } else {
         for (int i = threadIdx.x; i < h; i += blockDim.x) {
             float t = xr[i];
-            if (delta) { t += to_f32(delta[in_row * h + i]); xr[i] = t; }
+            if (delta) {
+                for (int p = 0; p < n_delta; ++p) t += to_f32(dr[(size_t)p * delta_stride + i]);
+                xr[i] = t;
+            }
             ss += t * t;
         }
     }
@@ -76,7 +96,7 @@ __global__ void add_rmsnorm_kernel(float* __restrict__ x, const TD* __restrict__
 #pragma unroll
         for (int k = 0; k < PER; ++k) {
             const int i = threadIdx.x + k * blockDim.x;
-            if (i < h) orow[i] = from_f32<TO>(v[k] * rstd * to_f32(w[i]));
+            if (i < h) orow[i] = from_f32<TO>(v[k] * rstd * wv[k]);
         }
     } else {
         for (int i = threadIdx.x; i < h; i += blockDim.x)
@@ -85,37 +105,139 @@ __global__ void add_rmsnorm_kernel(float* __restrict__ x, const TD* __restrict__
 }
 
 template <typename TD, typename TW, typename TO>
-static int launch_add_rmsnorm_k(float* x, const TD* delta, const TW* w, TO* out, const int* row_idx, int rows, int h,
-                                float eps, cudaStream_t s) {
+static int launch_add_rmsnorm_k(float* x, const TD* delta, int n_delta, long long delta_stride, const TW* w, TO* out,
+                                const int* row_idx, int rows, int h, float eps, cudaStream_t s) {
     // the summation order (thread stride, then the block tree) depends on h only, never on the batch
-    if (h <= 512) return rb_launch(add_rmsnorm_kernel<TD, TW, TO, 4>, dim3(rows), dim3(128), 0, s, x, delta, w, out, row_idx, h, eps);
-    if (h <= 2048) return rb_launch(add_rmsnorm_kernel<TD, TW, TO, 8>, dim3(rows), dim3(256), 0, s, x, delta, w, out, row_idx, h, eps);
-    if (h <= 8192) return rb_launch(add_rmsnorm_kernel<TD, TW, TO, 8>, dim3(rows), dim3(1024), 0, s, x, delta, w, out, row_idx, h, eps);
-    return rb_launch(add_rmsnorm_kernel<TD, TW, TO, 0>, dim3(rows), dim3(1024), 0, s, x, delta, w, out, row_idx, h, eps);
+    if (h <= 512) return rb_launch(add_rmsnorm_kernel<TD, TW, TO, 4>, dim3(rows), dim3(128), 0, s, x, delta, n_delta, delta_stride, w, out, row_idx, h, eps);
+    if (h <= 2048) return rb_launch(add_rmsnorm_kernel<TD, TW, TO, 8>, dim3(rows), dim3(256), 0, s, x, delta, n_delta, delta_stride, w, out, row_idx, h, eps);
+    if (h <= 8192) return rb_launch(add_rmsnorm_kernel<TD, TW, TO, 8>, dim3(rows), dim3(1024), 0, s, x, delta, n_delta, delta_stride, w, out, row_idx, h, eps);
+    if (delta && row_idx) RB_REFUSE("rmsnorm: rows of %d elements cannot combine a residual sum with a row gather", h);
+    return rb_launch(add_rmsnorm_kernel<TD, TW, TO, 0>, dim3(rows), dim3(1024), 0, s, x, delta, n_delta, delta_stride, w, out, row_idx, h, eps);
+}
+
+// The same for a few rows of 16-bit activations (a decode step), where one CTA per row would be bound by what one
+// SM can pull from L2 - above all when delta is a stack of partial sums.  A row is shared by a cluster of RN_CL
+// CTAs: each takes a contiguous share of the columns (16-byte loads, all of a thread's loads in flight at once),
+// forms its part of the sum of squares in a fixed order, and the parts are exchanged through distributed shared
+// memory and added in rank order - so a row's result depends on h alone, not on the other rows.
+constexpr int RN_CL = 4, RN_THREADS = 256, RN_VPER = 4;
+template <typename TW>
+__global__ void __launch_bounds__(RN_THREADS)
+add_rmsnorm_cluster_kernel(float* __restrict__ x, const float* __restrict__ delta, int n_delta, long long delta_stride,
+                           const TW* __restrict__ w, bf16* __restrict__ out, const int* __restrict__ row_idx, int h, float eps) {
+    RB_TL(2);
+    __shared__ float red[32];
+    __shared__ float part_ss;
+    pdl_trigger();
+    uint32_t rank;
+    asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(rank));
+    const int share = h / RN_CL;                              // columns of this CTA, a multiple of 4
+    const int c0 = (int)rank * share;
+    // the norm's weights never change: they are fetched while the kernels before this one still run
+    float4 wv[RN_VPER];
+#pragma unroll
+    for (int k = 0; k < RN_VPER; ++k) {
+        const int i = (threadIdx.x + k * RN_THREADS) * 4;
+        wv[k] = make_float4(0.f, 0.f, 0.f, 0.f);
+        if (i < share) { wv[k].x = to_f32(w[c0 + i]); wv[k].y = to_f32(w[c0 + i + 1]); wv[k].z = to_f32(w[c0 + i + 2]); wv[k].w = to_f32(w[c0 + i + 3]); }
+    }
+    pdl_wait();
+    RB_TL_MARK();
+    const int r = blockIdx.y;
+    const size_t in_row = row_idx ? (size_t)row_idx[r] : (size_t)r;
+    float* xr = x + in_row * h + c0;
+    const float* dr = delta ? delta + in_row * h + c0 : nullptr;
+    const bool keep = delta && !row_idx;
+    float4 v[RN_VPER];
+    float ss = 0.0f;
+#pragma unroll
+    for (int k = 0; k < RN_VPER; ++k) {
+        const int i = (threadIdx.x + k * RN_THREADS) * 4;
+        float4 t = make_float4(0.f, 0.f, 0.f, 0.f);
+        if (i < share) {
+            t = *reinterpret_cast<const float4*>(xr + i);
+            if (delta) {
+                for (int p0 = 0; p0 < n_delta; p0 += 8) {      // eight partial sums in flight, added in ascending order
+                    float4 d[8];
+#pragma unroll
+                    for (int p = 0; p < 8; ++p)
+                        d[p] = p0 + p < n_delta ? *reinterpret_cast<const float4*>(dr + (size_t)(p0 + p) * delta_stride + i)
+                                                : make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+                    for (int p = 0; p < 8; ++p) if (p0 + p < n_delta) { t.x += d[p].x; t.y += d[p].y; t.z += d[p].z; t.w += d[p].w; }
+                }
+                if (keep) *reinterpret_cast<float4*>(xr + i) = t;
+            }
+        }
+        v[k] = t;
+        ss += t.x * t.x + t.y * t.y + t.z * t.z + t.w * t.w;
+    }
+    const float mine = block_sum(ss, red);
+    if (threadIdx.x == 0) part_ss = mine;
+    asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+    float total = 0.0f;
+    const uint32_t local = (uint32_t)__cvta_generic_to_shared(&part_ss);
+#pragma unroll
+    for (uint32_t c = 0; c < RN_CL; ++c) {                   // rank order: the same sum in every CTA of the row
+        uint32_t remote;
+        float f;
+        asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(remote) : "r"(local), "r"(c));
+        asm volatile("ld.shared::cluster.f32 %0, [%1];" : "=f"(f) : "r"(remote) : "memory");
+        total += f;
+    }
+    const float rstd = 1.0f / sqrtf(total / (float)h + eps);
+    bf16* orow = out + (size_t)r * h + c0;                  // 8-byte aligned: h and the share are multiples of 4
+#pragma unroll
+    for (int k = 0; k < RN_VPER; ++k) {
+        const int i = (threadIdx.x + k * RN_THREADS) * 4;
+        if (i < share) {
+            const __nv_bfloat162 lo = __floats2bfloat162_rn(v[k].x * rstd * wv[k].x, v[k].y * rstd * wv[k].y);
+            const __nv_bfloat162 hi = __floats2bfloat162_rn(v[k].z * rstd * wv[k].z, v[k].w * rstd * wv[k].w);
+            uint2 pk;
+            pk.x = *reinterpret_cast<const uint32_t*>(&lo); pk.y = *reinterpret_cast<const uint32_t*>(&hi);
+            *reinterpret_cast<uint2*>(orow + i) = pk;
+        }
+    }
+    // nobody leaves while its part of the sum may still be read
+    asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
 }
 
 template <typename TD, typename TW>
-static int launch_add_rmsnorm_o(float* x, const void* delta, const void* w, void* out, int out_dtype,
+static int launch_add_rmsnorm_o(float* x, const void* delta, int n_delta, long long delta_stride, const void* w, void* out, int out_dtype,
                                 const int* row_idx, int rows, int h, float eps, cudaStream_t s) {
     if (out_dtype == RB_F32)
-        return launch_add_rmsnorm_k<TD, TW, float>(x, (const TD*)delta, (const TW*)w, (float*)out, row_idx, rows, h, eps, s);
+        return launch_add_rmsnorm_k<TD, TW, float>(x, (const TD*)delta, n_delta, delta_stride, (const TW*)w, (float*)out, row_idx, rows, h, eps, s);
     if (out_dtype == RB_BF16)
-        return launch_add_rmsnorm_k<TD, TW, bf16>(x, (const TD*)delta, (const TW*)w, (bf16*)out, row_idx, rows, h, eps, s);
+        return launch_add_rmsnorm_k<TD, TW, bf16>(x, (const TD*)delta, n_delta, delta_stride, (const TW*)w, (bf16*)out, row_idx, rows, h, eps, s);
     RB_REFUSE("rmsnorm: out dtype %d", out_dtype);
 }
 
-extern "C" int rb_add_rmsnorm(float* x, const void* delta, int delta_dtype, const void* w, int w_dtype,
-                              void* out, int out_dtype, const int* row_idx, int rows, int h, float eps,
-                              void* stream) {
+// delta: n_delta partial sums of x's shape, delta_stride elements apart (n_delta == 1: one plain addend); they
+// are added to x in ascending order.  With row_idx the sums are formed for the gathered rows only and x is left
+// as it was (the pass ends there).
+extern "C" int rb_add_rmsnorm(float* x, const void* delta, int delta_dtype, int n_delta, long long delta_stride,
+                              const void* w, int w_dtype, void* out, int out_dtype, const int* row_idx, int rows, int h,
+                              float eps, void* stream) {
     if (rows <= 0) return 0;
     if (h <= 0) RB_REFUSE("rmsnorm: width %d", h);
-    if (delta && row_idx) RB_REFUSE("rmsnorm: a residual sum cannot be combined with a row gather");
+    if (delta && (n_delta < 1 || n_delta > 64)) RB_REFUSE("rmsnorm: %d partial sums", n_delta);
     cudaStream_t s = (cudaStream_t)stream;
     const int dd = delta ? delta_dtype : RB_F32;
-    if (dd == RB_F32 && w_dtype == RB_F32) return launch_add_rmsnorm_o<float, float>(x, delta, w, out, out_dtype, row_idx, rows, h, eps, s);
-    if (dd == RB_F32 && w_dtype == RB_BF16) return launch_add_rmsnorm_o<float, bf16>(x, delta, w, out, out_dtype, row_idx, rows, h, eps, s);
-    if (dd == RB_BF16 && w_dtype == RB_F32) return launch_add_rmsnorm_o<bf16, float>(x, delta, w, out, out_dtype, row_idx, rows, h, eps, s);
-    if (dd == RB_BF16 && w_dtype == RB_BF16) return launch_add_rmsnorm_o<bf16, bf16>(x, delta, w, out, out_dtype, row_idx, rows, h, eps, s);
+    // a stack of partial sums for a decode step's few rows of 16-bit activations: a cluster per row (the whole
+    // 32-bit path keeps the one kernel, whose sums do not depend on how many rows a step brings)
+    if (out_dtype == RB_BF16 && dd == RB_F32 && delta && n_delta > 1 && rows <= 64 && h % (4 * RN_CL) == 0 && h / RN_CL <= RN_THREADS * 4 * RN_VPER &&
+        ((((uintptr_t)x | (uintptr_t)delta) & 15) == 0) && (((uintptr_t)out) & 7) == 0 && delta_stride % 4 == 0) {
+        if (w_dtype == RB_F32)
+            return rb_launch_cluster(add_rmsnorm_cluster_kernel<float>, dim3(RN_CL, rows), dim3(RN_THREADS), RN_CL, 0, s, x,
+                                     (const float*)delta, n_delta, delta_stride, (const float*)w, (bf16*)out, row_idx, h, eps);
+        if (w_dtype == RB_BF16)
+            return rb_launch_cluster(add_rmsnorm_cluster_kernel<bf16>, dim3(RN_CL, rows), dim3(RN_THREADS), RN_CL, 0, s, x,
+                                     (const float*)delta, n_delta, delta_stride, (const bf16*)w, (bf16*)out, row_idx, h, eps);
+    }
+    if (dd == RB_F32 && w_dtype == RB_F32) return launch_add_rmsnorm_o<float, float>(x, delta, n_delta, delta_stride, w, out, out_dtype, row_idx, rows, h, eps, s);
+    if (dd == RB_F32 && w_dtype == RB_BF16) return launch_add_rmsnorm_o<float, bf16>(x, delta, n_delta, delta_stride, w, out, out_dtype, row_idx, rows, h, eps, s);
+    if (dd == RB_BF16 && w_dtype == RB_F32) return launch_add_rmsnorm_o<bf16, float>(x, delta, n_delta, delta_stride, w, out, out_dtype, row_idx, rows, h, eps, s);
+    if (dd == RB_BF16 && w_dtype == RB_BF16) return launch_add_rmsnorm_o<bf16, bf16>(x, delta, n_delta, delta_stride, w, out, out_dtype, row_idx, rows, h, eps, s);
     RB_REFUSE("rmsnorm: dtypes delta=%d weight=%d", delta_dtype, w_dtype);
 }
 
@@ -242,7 +364,9 @@ __global__ void qknorm_rope_append_vec_kernel(const bf16* __restrict__ qkv, cons
                                               const int* __restrict__ positions, const int* __restrict__ kv_slot,
                                               bf16* __restrict__ q_out, bf16* __restrict__ cache,
                                               int n_tokens, int QH, int KH, int d, int page_size, float eps) {
+    RB_TL(3);
     pdl_trigger(); pdl_wait();
+    RB_TL_MARK();
     const int heads = QH + 2 * KH;
     const long long wglobal = ((long long)blockIdx.x * blockDim.x + threadIdx.x) >> 5;
     const int lane = threadIdx.x & 31;
@@ -405,3 +529,5 @@ extern "C" int rb_swiglu(const void* gu, void* out, int dtype, int n_tokens, int
     if (dtype == RB_BF16) return rb_launch(swiglu_kernel<bf16>, dim3(blocks), dim3(256), 0, s, (const bf16*)gu, (bf16*)out, F, total);
     RB_REFUSE("swiglu: dtype %d", dtype);
 }
+
+RB_TL_SETTER(rb_elementwise_step_timeline)

@@ -22,6 +22,7 @@
 // an abort flag, its roles leave their loops, outstanding TMA loads are waited for (again
 // bounded), tensor memory is freed, and an error word in global memory tells the host.
 #include "sm100.cuh"
+#include <stdlib.h>
 
 #define TC_BM 128            // output features per CTA (MMA M)
 #define TC_BK 64             // K elements per stage (128 bytes: one swizzle row)
@@ -62,7 +63,8 @@ template <int BN, int STAGES, bool DUAL>
 __global__ void __launch_bounds__(TC_THREADS, (BN <= 64 ? 2 : 1))
 gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_x,
                void* __restrict__ C, float* __restrict__ ws, int T, int N, int K, long long ldc, int out_mode,
-               int kb_per_split, int csplit) {
+               int kb_per_split, int csplit, const void* __restrict__ next_w, long long next_bytes) {
+    RB_TL(DUAL ? 7 : 6);
     extern __shared__ __align__(1024) unsigned char smem_raw[];
     constexpr uint32_t W1_BYTES = TC_BM * TC_BK * 2;                // 16 KB per weight tile
     constexpr uint32_t W_BYTES = (DUAL ? 2 : 1) * W1_BYTES;
@@ -112,6 +114,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
                 if (DUAL) tma_load_2d(smem_base + kb * STAGE_BYTES + W1_BYTES, &map_w, (kb0 + kb) * TC_BK, N + n0, full);
             }
             pdl_wait();
+            RB_TL_MARK();
             for (int kb = 0; kb < pre; ++kb)
                 tma_load_2d(smem_base + kb * STAGE_BYTES + W_BYTES, &map_x, (kb0 + kb) * TC_BK, t0, smem_u32(&sh->full[kb]));
             issued = pre;
@@ -161,6 +164,12 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
         if (mbar_wait(smem_u32(&sh->acc_full), 0, abort_flag, 3)) {
             tc_fence_after();
             if (threadIdx.x == 64) TL(4);
+            // All of this CTA's weights have arrived.  While the product drains (the cluster's reduction, the
+            // stores) and the kernels after it start up, memory would idle: the weights that the next product
+            // streams are called into L2 now.
+            if (threadIdx.x == 64)
+                l2_prefetch_share(next_w, next_bytes, (blockIdx.z * gridDim.y + blockIdx.y) * gridDim.x + blockIdx.x,
+                                  gridDim.x * gridDim.y * gridDim.z);
 #pragma unroll 1
             for (int c0 = 0; c0 < BN; c0 += 16) {
                 if (t0 + c0 >= T) break;                               // warp-uniform
@@ -291,6 +300,7 @@ template <int BN, int STAGES, bool DUAL>
 __global__ void __launch_bounds__(TC_THREADS, 1)
 gemm_tc_persistent_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_x,
                           void* __restrict__ C, int T, int N, int K, long long ldc, int out_mode, int t_tiles, int n_tiles) {
+    RB_TL(DUAL ? 9 : 8);
     extern __shared__ __align__(1024) unsigned char smem_raw[];
     constexpr uint32_t W1_BYTES = TC_BM * TC_BK * 2;
     constexpr uint32_t W_BYTES = (DUAL ? 2 : 1) * W1_BYTES;
@@ -483,26 +493,29 @@ __global__ void splitk_reduce_kernel(const float* __restrict__ ws, void* __restr
 
 // ------------------------------------------------------------------ host side
 // How many CTAs of this kernel can be resident at once when launched as clusters of `sp` (1: no cluster).
-// CTAs per SM come from the shared memory alone (79 registers x 192 threads never bind): the occupancy calls
-// answer one CTA per SM for these kernels although two are resident (256 CTAs were seen to start within a
-// microsecond), so their cluster count - which knows how clusters tile the GPCs - is scaled by the ratio.
+// The occupancy calls answer one CTA per SM for the tensor-core kernels themselves although two are resident
+// (256 CTAs were seen to start within a microsecond), so a twin with the same threads, launch bounds and shared
+// memory is asked instead; its cluster count knows how clusters of two CTAs per SM tile the GPCs.
+template <int MINB>
+__global__ void __launch_bounds__(TC_THREADS, MINB) tc_occupancy_twin(int* p) {
+    extern __shared__ unsigned char twin_smem[];
+    if (p) p[threadIdx.x] = twin_smem[threadIdx.x];
+}
 template <int BN, int STAGES, bool DUAL>
 static int tc_capacity(int sp, size_t smem) {
     static int cache[9] = {0, 0, 0, 0, 0, 0, 0, 0, 0};
     if (cache[sp]) return cache[sp];
-    int dev = 0, sms = 0, smem_sm = 0, reserved = 0;
+    constexpr int MINB = BN <= 64 ? 2 : 1;                          // the kernel's __launch_bounds__
+    int dev = 0, sms = 148;
     cudaGetDevice(&dev);
     cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
-    cudaDeviceGetAttribute(&smem_sm, cudaDevAttrMaxSharedMemoryPerMultiprocessor, dev);
-    cudaDeviceGetAttribute(&reserved, cudaDevAttrReservedSharedMemoryPerBlock, dev);
-    int fit = (int)((size_t)smem_sm / (smem + (size_t)reserved));
-    const int bound = BN <= 64 ? 2 : 1;                             // the kernel's __launch_bounds__
-    if (fit > bound) fit = bound;
-    if (fit < 1) fit = 1;
-    int said = 0;
-    if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&said, gemm_tc_kernel<BN, STAGES, DUAL>, TC_THREADS, smem) != cudaSuccess || said < 1) said = 1;
-    int n = fit * sms;
-    if (sp > 1) {
+    (void)cudaFuncSetAttribute(tc_occupancy_twin<MINB>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    int n = 0;
+    if (sp == 1) {
+        int per_sm = 0;
+        if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, tc_occupancy_twin<MINB>, TC_THREADS, smem) == cudaSuccess)
+            n = (per_sm > MINB ? MINB : per_sm) * sms;
+    } else {
         cudaLaunchConfig_t cfg = {};
         cfg.gridDim = dim3(1, 1, sp); cfg.blockDim = dim3(TC_THREADS); cfg.dynamicSmemBytes = smem;
         cudaLaunchAttribute attr[1];
@@ -510,12 +523,10 @@ static int tc_capacity(int sp, size_t smem) {
         attr[0].val.clusterDim.x = 1; attr[0].val.clusterDim.y = 1; attr[0].val.clusterDim.z = sp;
         cfg.attrs = attr; cfg.numAttrs = 1;
         int clusters = 0;
-        if (cudaOccupancyMaxActiveClusters(&clusters, gemm_tc_kernel<BN, STAGES, DUAL>, &cfg) == cudaSuccess && clusters > 0)
-            n = clusters * sp * (fit > said ? fit / said : 1);
-        else
-            n = sms / sp * sp;                                      // unknown: one CTA per SM
+        if (cudaOccupancyMaxActiveClusters(&clusters, tc_occupancy_twin<MINB>, &cfg) == cudaSuccess) n = clusters * sp;
     }
     (void)cudaGetLastError();
+    if (n <= 0) n = sms / sp * sp;                                  // unknown: one CTA per SM
     cache[sp] = n;
     return n;
 }
@@ -530,7 +541,9 @@ static int tc_choose_splits(int tiles, int total_kb, size_t smem, int* caps) {
     double best = 1e30;
     int splits = 1;
     for (int sp = 1; sp <= 8 && total_kb / sp >= 4; ++sp) {
-        const int cap = tc_capacity<BN, STAGES, DUAL>(sp, smem);
+        // a tenth of the slots stays free: the kernels after this one then find room to start early and fetch
+        // their own first tiles while this one drains (measured inside whole decode steps)
+        const int cap = tc_capacity<BN, STAGES, DUAL>(sp, smem) * 9 / 10;
         if (caps) caps[sp] = cap;
         const long long ctas = (long long)tiles * sp;
         const long long waves = (ctas + cap - 1) / cap;
@@ -544,10 +557,25 @@ static int tc_choose_splits(int tiles, int total_kb, size_t smem, int* caps) {
     return splits;
 }
 
+// REINFER_B200_GEMM_SPLITS="NxK:S,NxK:S,..." fixes the cluster split of products with these weight shapes (N counts
+// both matrices of a gated pair), for tuning; anything else is chosen by the model above.
+static int tc_env_splits(int N, int K) {
+    static const char* env = getenv("REINFER_B200_GEMM_SPLITS");
+    if (!env) return 0;
+    for (const char* p = env; *p;) {
+        int n = 0, k = 0, sp = 0;
+        if (sscanf(p, "%dx%d:%d", &n, &k, &sp) == 3 && n == N && k == K && sp >= 1 && sp <= 8) return sp;
+        while (*p && *p != ',') ++p;
+        if (*p == ',') ++p;
+    }
+    return 0;
+}
+
 // want_splits: 0 = choose; > 0 = that many through a cluster (at most 8); < 0 = that many through the workspace.
 template <int BN, int STAGES, bool DUAL>
 static int launch_tc(const CUtensorMap& mw, const CUtensorMap& mx, void* C, float* ws, long long ws_floats, int T, int N, int K,
-                     long long ldc, int mode, int want_splits, cudaStream_t s) {
+                     long long ldc, int mode, int want_splits, const void* next_w, long long next_bytes, cudaStream_t s,
+                     bool keep_partials = false) {
     constexpr size_t smem = (size_t)STAGES * ((DUAL ? 2 : 1) * TC_BM * TC_BK * 2 + BN * TC_BK * 2) + sizeof(TcShared) + 1024;
     static bool configured = false;
     if (!configured) {
@@ -567,7 +595,10 @@ static int launch_tc(const CUtensorMap& mw, const CUtensorMap& mx, void* C, floa
     bool via_ws = false;
     if (want_splits > 0) { splits = want_splits; via_ws = !can_park; }
     else if (want_splits < 0) { splits = -want_splits; via_ws = true; }
-    else if (t_tiles == 1 && can_park) splits = tc_choose_splits<BN, STAGES, DUAL>(tiles, total_kb, smem, nullptr);
+    else if (t_tiles == 1 && can_park) {
+        splits = tc_env_splits(DUAL ? 2 * N : N, K);
+        if (!splits) splits = tc_choose_splits<BN, STAGES, DUAL>(tiles, total_kb, smem, nullptr);
+    }
     if (splits > total_kb) splits = total_kb;
     int kb_per_split = rb_ceil_div(total_kb, splits);
     splits = rb_ceil_div(total_kb, kb_per_split);                   // no empty split
@@ -579,7 +610,8 @@ static int launch_tc(const CUtensorMap& mw, const CUtensorMap& mx, void* C, floa
         splits = rb_ceil_div(total_kb, kb_per_split);
     }
     const int csplit = (splits > 1 && !via_ws) ? splits : 1;
-    const int out_mode = (splits > 1 && via_ws) ? 3 : mode;
+    if (keep_partials && !via_ws) RB_REFUSE("gemm: partial sums go through the workspace");
+    const int out_mode = ((splits > 1 || keep_partials) && via_ws) ? 3 : mode;
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3(t_tiles, n_tiles, splits);
     cfg.blockDim = dim3(TC_THREADS);
@@ -599,11 +631,11 @@ static int launch_tc(const CUtensorMap& mw, const CUtensorMap& mx, void* C, floa
     }
     cfg.attrs = attr;
     cfg.numAttrs = na;
-    cudaError_t e = cudaLaunchKernelEx(&cfg, gemm_tc_kernel<BN, STAGES, DUAL>, mw, mx, C, ws, T, N, K, ldc, out_mode, kb_per_split, csplit);
+    cudaError_t e = cudaLaunchKernelEx(&cfg, gemm_tc_kernel<BN, STAGES, DUAL>, mw, mx, C, ws, T, N, K, ldc, out_mode, kb_per_split, csplit, next_w, next_bytes);
     if (e != cudaSuccess) { (void)cudaGetLastError(); return (int)e; }
     int rc = RB_LAUNCH_RESULT();
     if (rc) return rc;
-    if (splits > 1 && via_ws) {
+    if (splits > 1 && via_ws && !keep_partials) {
         const long long total = (long long)T * N;
         return rb_launch(splitk_reduce_kernel, dim3(rb_ceil_div(total, 256)), dim3(256), 0, s, (const float*)ws, C, T, N, ldc, splits, mode);
     }
@@ -620,12 +652,13 @@ static int tc_bn(int T) { return T <= 16 ? 16 : T <= 32 ? 32 : T <= 64 ? 64 : T 
 // ws: float workspace of ws_floats elements for split-K partials beyond a cluster (may be null).
 extern "C" int rb_gemm_bf16(const void* X, const void* W, void* C, int c_dtype, int accumulate, int T, int N, int K,
                             long long ldx, long long ldw, long long ldc, float* ws, long long ws_floats,
-                            int force_splits, void* stream) {
+                            int force_splits, const void* next_w, long long next_bytes, void* stream) {
     if (T <= 0 || N <= 0) return 0;
     if (K <= 0) RB_REFUSE("gemm: K=%d", K);
     if ((ldx % 8) || (ldw % 8) || ((uintptr_t)X & 15) || ((uintptr_t)W & 15))
         RB_REFUSE("gemm: TMA needs 16-byte aligned operands and row strides (ldx %lld, ldw %lld)", ldx, ldw);
     if (accumulate && c_dtype != RB_F32) RB_REFUSE("gemm: accumulation needs a float destination");
+    if ((uintptr_t)next_w & 15) RB_REFUSE("gemm: the range to prefetch must start on a 16-byte boundary");
     if (c_dtype != RB_F32 && c_dtype != RB_BF16) RB_REFUSE("gemm: destination dtype %d", c_dtype);
     cudaStream_t s = (cudaStream_t)stream;
     const int mode = accumulate ? 2 : (c_dtype == RB_F32 ? 1 : 0);
@@ -638,20 +671,73 @@ extern "C" int rb_gemm_bf16(const void* X, const void* W, void* C, int c_dtype, 
     }
     if (rb_tensor_map_bf16(X, T, K, ldx, bn, &mx)) return -1;
     switch (bn) {
-        case 16: return launch_tc<16, 6, false>(mw, mx, C, ws, ws_floats, T, N, K, ldc, mode, force_splits, s);
-        case 32: return launch_tc<32, 5, false>(mw, mx, C, ws, ws_floats, T, N, K, ldc, mode, force_splits, s);
-        case 64: return launch_tc<64, 4, false>(mw, mx, C, ws, ws_floats, T, N, K, ldc, mode, force_splits, s);
-        case 128: return launch_tc<128, 5, false>(mw, mx, C, ws, ws_floats, T, N, K, ldc, mode, force_splits, s);
-        default: return launch_tc<256, 4, false>(mw, mx, C, ws, ws_floats, T, N, K, ldc, mode, force_splits, s);
+        case 16: return launch_tc<16, 6, false>(mw, mx, C, ws, ws_floats, T, N, K, ldc, mode, force_splits, next_w, next_bytes, s);
+        case 32: return launch_tc<32, 5, false>(mw, mx, C, ws, ws_floats, T, N, K, ldc, mode, force_splits, next_w, next_bytes, s);
+        case 64: return launch_tc<64, 4, false>(mw, mx, C, ws, ws_floats, T, N, K, ldc, mode, force_splits, next_w, next_bytes, s);
+        case 128: return launch_tc<128, 5, false>(mw, mx, C, ws, ws_floats, T, N, K, ldc, mode, force_splits, next_w, next_bytes, s);
+        default: return launch_tc<256, 4, false>(mw, mx, C, ws, ws_floats, T, N, K, ldc, mode, force_splits, next_w, next_bytes, s);
+    }
+}
+
+// How many partial sums rb_gemm_bf16_partials leaves for T tokens, N features and K: as many splits of K as
+// keep most resident CTA slots busy (two CTAs per SM for up to 64 tokens, else one) with at least four
+// 64-wide blocks of K each.  No cluster is involved, so nothing limits the count but the work.
+extern "C" int rb_gemm_partials_plan(int T, int N, int K) {
+    if (T <= 0 || N <= 0 || K <= 0) return 1;
+    int dev = 0, sms = 148;
+    cudaGetDevice(&dev);
+    cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+    const int bn = tc_bn(T);
+    // four fifths of the slots: the kernels after this one then find room to start early and fetch their own
+    // first tiles while this one drains (measured inside whole decode steps; REINFER_B200_PARTIAL_FILL for tuning)
+    static const char* fill_env = getenv("REINFER_B200_PARTIAL_FILL");
+    const double fill = fill_env ? atof(fill_env) : 0.8;
+    const int slots = (int)(sms * (bn <= 64 ? 2 : 1) * (fill > 0.05 && fill <= 1.0 ? fill : 0.8));
+    const int tiles = rb_ceil_div(T, bn) * rb_ceil_div(N, TC_BM), total_kb = rb_ceil_div(K, TC_BK);
+    int sp = slots / tiles;
+    if (sp > total_kb / 4) sp = total_kb / 4;
+    if (sp > 32) sp = 32;
+    if (sp < 1) sp = 1;
+    const int per = rb_ceil_div(total_kb, sp);
+    return rb_ceil_div(total_kb, per);
+}
+
+// partials[s][T][N] (float) = X[:, K-range s] W[:, K-range s]^T for the `splits` ranges of K that
+// rb_gemm_partials_plan names: the product without its last sum, which the kernel that reads the result
+// forms on the way (the residual sum and norm, the head norm) - no CTA waits for another.
+extern "C" int rb_gemm_bf16_partials(const void* X, const void* W, float* partials, int splits, int T, int N, int K,
+                                     long long ldx, long long ldw, const void* next_w, long long next_bytes, void* stream) {
+    if (T <= 0 || N <= 0) return 0;
+    if (K <= 0) RB_REFUSE("gemm: K=%d", K);
+    if ((ldx % 8) || (ldw % 8) || ((uintptr_t)X & 15) || ((uintptr_t)W & 15))
+        RB_REFUSE("gemm: TMA needs 16-byte aligned operands and row strides (ldx %lld, ldw %lld)", ldx, ldw);
+    if ((uintptr_t)next_w & 15) RB_REFUSE("gemm: the range to prefetch must start on a 16-byte boundary");
+    if (T > 256) RB_REFUSE("gemm: partial sums are for one token tile (%d tokens)", T);
+    if (splits != rb_gemm_partials_plan(T, N, K)) RB_REFUSE("gemm: %d partial sums where the plan names %d", splits, rb_gemm_partials_plan(T, N, K));
+    cudaStream_t s = (cudaStream_t)stream;
+    const int bn = tc_bn(T);
+    CUtensorMap mw, mx;
+    if (rb_tensor_map_bf16(W, N, K, ldw, TC_BM, &mw)) return -1;
+    if (rb_tensor_map_bf16(X, T, K, ldx, bn, &mx)) return -1;
+    const long long wsf = (long long)splits * T * N;
+    switch (bn) {
+        case 16: return launch_tc<16, 6, false>(mw, mx, nullptr, partials, wsf, T, N, K, N, 1, -splits, next_w, next_bytes, s, true);
+        case 32: return launch_tc<32, 5, false>(mw, mx, nullptr, partials, wsf, T, N, K, N, 1, -splits, next_w, next_bytes, s, true);
+        case 64: return launch_tc<64, 4, false>(mw, mx, nullptr, partials, wsf, T, N, K, N, 1, -splits, next_w, next_bytes, s, true);
+        case 128: return launch_tc<128, 5, false>(mw, mx, nullptr, partials, wsf, T, N, K, N, 1, -splits, next_w, next_bytes, s, true);
+        default: return launch_tc<256, 4, false>(mw, mx, nullptr, partials, wsf, T, N, K, N, 1, -splits, next_w, next_bytes, s, true);
     }
 }
 
 // act[T,F] (bfloat16) = silu(X Wg^T) * (X Wu^T) for Wgu = [Wg; Wu] of shape [2F, K]: one product with two
 // accumulators and the activation in the epilogue.  Splits (at most 8) reduce inside a cluster.
 extern "C" int rb_gemm_bf16_swiglu(const void* X, const void* Wgu, void* act, int T, int F, int K,
-                                   long long ldx, long long ldw, long long ldc, void* stream) {
+                                   long long ldx, long long ldw, long long ldc, int force_splits,
+                                   const void* next_w, long long next_bytes, void* stream) {
     if (T <= 0 || F <= 0) return 0;
     if (K <= 0) RB_REFUSE("gemm_swiglu: K=%d", K);
+    if (force_splits < 0 || force_splits > 8) RB_REFUSE("gemm_swiglu: %d splits (0 = choose, at most a cluster of 8)", force_splits);
+    if ((uintptr_t)next_w & 15) RB_REFUSE("gemm_swiglu: the range to prefetch must start on a 16-byte boundary");
     if ((ldx % 8) || (ldw % 8) || ((uintptr_t)X & 15) || ((uintptr_t)Wgu & 15))
         RB_REFUSE("gemm_swiglu: TMA needs 16-byte aligned operands and row strides (ldx %lld, ldw %lld)", ldx, ldw);
     cudaStream_t s = (cudaStream_t)stream;
@@ -664,11 +750,11 @@ extern "C" int rb_gemm_bf16_swiglu(const void* X, const void* Wgu, void* act, in
     }
     if (rb_tensor_map_bf16(X, T, K, ldx, bn, &mx)) return -1;
     switch (bn) {
-        case 16: return launch_tc<16, 3, true>(mw, mx, act, nullptr, 0, T, F, K, ldc, 0, 0, s);
-        case 32: return launch_tc<32, 3, true>(mw, mx, act, nullptr, 0, T, F, K, ldc, 0, 0, s);
-        case 64: return launch_tc<64, 4, true>(mw, mx, act, nullptr, 0, T, F, K, ldc, 0, 0, s);
-        case 128: return launch_tc<128, 4, true>(mw, mx, act, nullptr, 0, T, F, K, ldc, 0, 0, s);
-        default: return launch_tc<256, 3, true>(mw, mx, act, nullptr, 0, T, F, K, ldc, 0, 0, s);
+        case 16: return launch_tc<16, 3, true>(mw, mx, act, nullptr, 0, T, F, K, ldc, 0, force_splits, next_w, next_bytes, s);
+        case 32: return launch_tc<32, 3, true>(mw, mx, act, nullptr, 0, T, F, K, ldc, 0, force_splits, next_w, next_bytes, s);
+        case 64: return launch_tc<64, 4, true>(mw, mx, act, nullptr, 0, T, F, K, ldc, 0, force_splits, next_w, next_bytes, s);
+        case 128: return launch_tc<128, 4, true>(mw, mx, act, nullptr, 0, T, F, K, ldc, 0, force_splits, next_w, next_bytes, s);
+        default: return launch_tc<256, 3, true>(mw, mx, act, nullptr, 0, T, F, K, ldc, 0, force_splits, next_w, next_bytes, s);
     }
 }
 
@@ -699,3 +785,5 @@ extern "C" int rb_gemm_error(int reset) {
     if (reset && v) { int z = 0; cudaMemcpyToSymbol(g_rb_kernel_error, &z, sizeof(int)); }
     return v;
 }
+
+RB_TL_SETTER(rb_gemm_step_timeline)

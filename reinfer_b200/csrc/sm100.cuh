@@ -66,6 +66,23 @@ __device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map
         "cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
         ::"r"(dst), "l"(map), "r"(x), "r"(y), "r"(bar) : "memory");
 }
+// Ask for bytes [base + lo, base + hi) to be brought into L2, in pieces of at most 32 KB; nothing waits for them.
+// base is 16-byte aligned; the range is clipped to whole 16-byte units inside it.
+__device__ __forceinline__ void l2_prefetch_range(const unsigned char* base, long long lo, long long hi) {
+    for (long long o = lo; o < hi; o += 32768) {
+        const long long left = hi - o;
+        const uint32_t n = (uint32_t)(left < 32768 ? left : 32768) & ~15u;
+        if (n) asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(base + o), "r"(n) : "memory");
+    }
+}
+// This CTA's share (part of parts, 4 KB granules) of the first `bytes` bytes at base.
+__device__ __forceinline__ void l2_prefetch_share(const void* base, long long bytes, int part, int parts) {
+    if (!base || bytes <= 0) return;
+    const long long per = (((bytes + parts - 1) / parts) + 4095) & ~4095LL;
+    const long long lo = per * part;
+    const long long hi = lo + per < bytes ? lo + per : bytes;
+    if (lo < hi) l2_prefetch_range((const unsigned char*)base, lo, hi);
+}
 __device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
 __device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
 __device__ __forceinline__ void tc_commit(uint32_t bar) {

@@ -111,13 +111,19 @@ def embed_gather(table: torch.Tensor, ids: torch.Tensor, out: torch.Tensor) -> N
 
 def add_rmsnorm(x: torch.Tensor, delta: Optional[torch.Tensor], w: torch.Tensor, out: torch.Tensor,
                 eps: float, row_idx: Optional[torch.Tensor] = None) -> None:
-    """x (float32, [rows,h]) += delta if given; out[r] = rmsnorm(x[row_idx[r] or r]) * w."""
+    """x (float32, [rows,h]) += delta if given; out[r] = rmsnorm(x[row_idx[r] or r]) * w.
+    delta has x's shape, or one more leading dimension: partial sums [S, rows, h] that are added in
+    ascending order (what a split product leaves).  With row_idx the sum is formed for the gathered
+    rows only and x itself is left unchanged."""
     _need(x.dtype == torch.float32 and x.is_contiguous() and out.is_contiguous(), "rmsnorm: x float32 contiguous")
     h = x.shape[-1]
     rows = out.numel() // h
+    n_delta = 0
     if delta is not None:
-        _need(delta.is_contiguous() and delta.numel() == x.numel(), "rmsnorm: delta has x's shape")
-    _check(lib().rb_add_rmsnorm(_p(x), _p(delta), c_int(dt(delta) if delta is not None else F32), _p(w), c_int(dt(w)),
+        _need(delta.is_contiguous() and delta.numel() % x.numel() == 0 and delta.shape[-1] == h, "rmsnorm: delta has x's shape (or a stack of it)")
+        n_delta = delta.numel() // x.numel()
+    _check(lib().rb_add_rmsnorm(_p(x), _p(delta), c_int(dt(delta) if delta is not None else F32), c_int(n_delta),
+                                c_longlong(x.numel()), _p(w), c_int(dt(w)),
                                 _p(out), c_int(dt(out)), _p(row_idx), c_int(rows), c_int(h), c_float(eps),
                                 _stream()), "add_rmsnorm")
 
@@ -220,6 +226,69 @@ def fa_decode(q, cache, block_table, cu_q, kv_len, out, first_entry: int, n_entr
         launches += 1                      # the merge kernel
 
 
+class StreamChain:
+    """Which constant ranges (weights) the streaming kernels of one forward pass read, in order.
+
+    A decode step is bound by memory traffic, and memory idles while one product drains and the small
+    kernels after it run.  So a streaming kernel (a product over few tokens, decode attention) is told
+    which weights the next one reads and calls their first bytes into L2 once its own loads are issued.
+    The order is not declared by anyone: every pass writes down what it streamed, and a pass whose
+    ranges match the last complete pass step by step learns from it what comes next; after the last
+    range comes the first (the next step).  A pass that runs other kernels (a prompt) or another order
+    just gets no hint until two passes agree again.
+    """
+
+    def __init__(self) -> None:
+        self.known: list = []           # (address, bytes) of the last complete pass; bytes == 0: a marker, nothing to fetch
+        self.now: list = []
+        self.live = False
+
+    def begin(self) -> None:
+        self.now = []
+        self.live = True
+
+    def end(self) -> None:
+        if self.live:
+            self.known = self.now
+        self.live = False
+
+    def step(self, address: int, nbytes: int):
+        """Note that a kernel streams this range now; returns (address, bytes) of what follows, or None."""
+        if not self.live:
+            return None
+        i = len(self.now)
+        self.now.append((address, nbytes))
+        k = self.known
+        if i < len(k) and k[i] == (address, nbytes) and len(k) > 1:
+            nxt = k[(i + 1) % len(k)]
+            if nxt[1] > 0 and nxt[0] % 16 == 0:
+                return nxt
+        return None
+
+
+_chain: Optional[StreamChain] = None
+L2_PREFETCH_BYTES = int(float(os.environ.get("REINFER_B200_L2_PREFETCH_MB", "12")) * (1 << 20))
+DEFER_SUMS = os.environ.get("REINFER_B200_DEFER_SUMS", "1") != "0"   # split products leave their last sum to the next norm
+STREAMING_TOKENS = 64                       # products over at most this many tokens count as weight streaming
+
+
+def set_chain(chain: Optional[StreamChain]) -> Optional[StreamChain]:
+    """Make `chain` the one that the streaming kernels consult (None: no hints); returns the previous one."""
+    global _chain
+    old, _chain = _chain, chain
+    return old
+
+
+def _next_range(t: Optional[torch.Tensor], marker: int = 0):
+    """(pointer, bytes) arguments of the range that follows tensor t (or the marker) in the active chain."""
+    if _chain is None or L2_PREFETCH_BYTES <= 0:
+        return c_void_p(0), c_longlong(0)
+    nxt = _chain.step(t.data_ptr(), t.numel() * t.element_size()) if t is not None else _chain.step(marker, 0)
+    if nxt is None:
+        return c_void_p(0), c_longlong(0)
+    return c_void_p(nxt[0]), c_longlong(min(nxt[1], L2_PREFETCH_BYTES))
+
+
 def fa_decode_tma(q, cache, block_table, cu_q, kv_len, out, first_entry: int, n_entries: int, first_tok: int, n_splits: int,
                   QH: int, KH: int, d: int, page_size: int, window: int, scale: float) -> None:
     """Split-K flash decoding with the key/value tiles brought in by TMA (page size a power of two >= 8)."""
@@ -227,10 +296,11 @@ def fa_decode_tma(q, cache, block_table, cu_q, kv_len, out, first_entry: int, n_
     if n_splits > 1:
         part_o = torch.empty(n_entries * QH * n_splits * d, dtype=torch.float32, device=q.device)
         part_lse = torch.empty(n_entries * QH * n_splits, dtype=torch.float32, device=q.device)
+    nw, nb = _next_range(None, marker=cache.data_ptr())
     _check(lib().rb_fa_decode_tma(_p(q), _p(cache), c_longlong(cache.shape[0]), _p(block_table), _p(cu_q), _p(kv_len), _p(out),
                                   _p(part_o), _p(part_lse), c_int(first_entry), c_int(n_entries), c_int(first_tok),
                                   c_int(n_splits), c_int(QH), c_int(KH), c_int(d), c_int(page_size),
-                                  c_int(block_table.shape[1]), c_int(window), c_float(scale), _stream()), "fa_decode_tma")
+                                  c_int(block_table.shape[1]), c_int(window), c_float(scale), nw, nb, _stream()), "fa_decode_tma")
 
 
 def fa_prefill_tma(q, cache, block_table, cu_q, kv_len, out, first_entry: int, n_entries: int, n_tiles: int,
@@ -330,12 +400,33 @@ def gemm_bf16(a: torch.Tensor, w: torch.Tensor, c: torch.Tensor, accumulate: boo
         return gemm_ref(a, w, c, accumulate)
     if _gemm_ws is None or _gemm_ws.device != a.device:
         _gemm_ws = torch.empty(GEMM_WS_FLOATS, dtype=torch.float32, device=a.device)
+    nw, nb = _next_range(w) if T <= STREAMING_TOKENS else (c_void_p(0), c_longlong(0))
     _check(lib().rb_gemm_bf16(_p(a), _p(w), _p(c), c_int(dt(c)), c_int(int(accumulate)), c_int(T), c_int(N), c_int(K),
                               c_longlong(a.stride(0)), c_longlong(w.stride(0)), c_longlong(c.stride(0)),
-                              _p(_gemm_ws), c_longlong(_gemm_ws.numel()), c_int(splits), _stream()), "gemm_bf16")
+                              _p(_gemm_ws), c_longlong(_gemm_ws.numel()), c_int(splits), nw, nb, _stream()), "gemm_bf16")
 
 
-def gemm_bf16_swiglu(a: torch.Tensor, w_gate_up: torch.Tensor, out: torch.Tensor) -> bool:
+def gemm_bf16_partials(a: torch.Tensor, w: torch.Tensor) -> Optional[torch.Tensor]:
+    """Partial sums [S, T, N] (float32) of a[T,K] @ w[N,K]^T over S ranges of K, for a consumer that adds them
+    up itself (add_rmsnorm with a stacked delta): the split product then needs no reduction of its own, and
+    none of its CTAs waits for another.  None if this product is not one for the streaming kernel (more than
+    STREAMING_TOKENS tokens, operands that TMA cannot address): the caller then runs the plain form."""
+    T, K = a.shape
+    N = w.shape[0]
+    _need(w.shape[1] == K, "gemm: shapes")
+    if not (0 < T <= STREAMING_TOKENS and a.dtype == torch.bfloat16 and w.dtype == torch.bfloat16):
+        return None
+    if a.stride(1) != 1 or w.stride(1) != 1 or a.stride(0) % 8 or w.stride(0) % 8 or a.data_ptr() % 16 or w.data_ptr() % 16:
+        return None
+    S = int(lib().rb_gemm_partials_plan(c_int(T), c_int(N), c_int(K)))
+    out = torch.empty((S, T, N), dtype=torch.float32, device=a.device)
+    nw, nb = _next_range(w)
+    _check(lib().rb_gemm_bf16_partials(_p(a), _p(w), _p(out), c_int(S), c_int(T), c_int(N), c_int(K),
+                                       c_longlong(a.stride(0)), c_longlong(w.stride(0)), nw, nb, _stream()), "gemm_bf16_partials")
+    return out
+
+
+def gemm_bf16_swiglu(a: torch.Tensor, w_gate_up: torch.Tensor, out: torch.Tensor, splits: int = 0) -> bool:
     """out[T,F] (bf16) = silu(a Wg^T) * (a Wu^T), w_gate_up = [Wg; Wu] of shape [2F, K]: one tensor-core
     product with two accumulators and the activation in its epilogue.  Returns False (and does
     nothing) if TMA cannot address the operands; the caller then runs the two-kernel form."""
@@ -346,9 +437,10 @@ def gemm_bf16_swiglu(a: torch.Tensor, w_gate_up: torch.Tensor, out: torch.Tensor
     _need(a.stride(1) == 1 and w_gate_up.stride(1) == 1 and out.stride(1) == 1, "gemm_swiglu: rows contiguous")
     if a.stride(0) % 8 or w_gate_up.stride(0) % 8 or a.data_ptr() % 16 or w_gate_up.data_ptr() % 16:
         return False
+    nw, nb = _next_range(w_gate_up) if T <= STREAMING_TOKENS else (c_void_p(0), c_longlong(0))
     _check(lib().rb_gemm_bf16_swiglu(_p(a), _p(w_gate_up), _p(out), c_int(T), c_int(F_), c_int(K),
                                      c_longlong(a.stride(0)), c_longlong(w_gate_up.stride(0)), c_longlong(out.stride(0)),
-                                     _stream()), "gemm_bf16_swiglu")
+                                     c_int(splits), nw, nb, _stream()), "gemm_bf16_swiglu")
     return True
 
 

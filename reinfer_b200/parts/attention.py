@@ -19,7 +19,7 @@ import torch
 from .. import ops
 from ..weights.params import ParamSpec
 from .base import Mixer, PagedKVSpec, build_part, register_part
-from .linear import matmul
+from .linear import matmul, matmul_into_residual
 from .spec import PartSpec
 
 
@@ -98,7 +98,7 @@ class Attention(Mixer):
                 ops.kv_append(k.view(T, KH * d), qkv[:, (QH + KH) * d:], g.kv_slot, cache.kv, KH, d, g.page_size)
         attn = torch.empty((T, QH, d), dtype=xn.dtype, device=xn.device)
         ops.attention(ctx, q, cache.kv, g, attn, QH, KH, d, self.window or 0, self.scale)
-        matmul(ctx, attn.view(T, QH * d), self.w_o, out=residual, accumulate=True)
+        return matmul_into_residual(ctx, attn.view(T, QH * d), self.w_o, residual)
 
 
 register_part("mixer", "attention", Attention)

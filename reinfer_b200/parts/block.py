@@ -1,21 +1,28 @@
 """Arrangements of a layer's four parts.  'prenorm':
     x += mixer(norm1(x));  x += ffn(norm2(x))       (crates/cuda/src/engine.rs:4071-4333)
 Mixer and feed-forward add into the residual stream themselves (their last product
-accumulates into it), so no separate residual kernel runs."""
+accumulates into it), so no separate residual kernel runs.  Either may instead return
+what is still to be added (a tensor of x's shape, or a stack [S, T, h] of partial sums):
+the block hands it to the norm that reads x next, which adds it on the way; what the
+feed-forward leaves is the block's own result, for the norm of the next block."""
 from __future__ import annotations
 
 from .base import register_part
 
 
 class PreNormBlock:
+    hands_on_sums = True                # forward takes and returns what is still to be added to x
+
     def __init__(self, mixer_norm, mixer, ffn_norm, ffn):
         self.mixer_norm, self.mixer, self.ffn_norm, self.ffn = mixer_norm, mixer, ffn_norm, ffn
 
-    def forward(self, ctx, x, cache) -> None:
-        xn = self.mixer_norm.forward(ctx, x)
-        self.mixer.forward(ctx, xn, x, cache)
-        xn = self.ffn_norm.forward(ctx, x)
-        self.ffn.forward(ctx, xn, x)
+    def forward(self, ctx, x, cache, delta=None):
+        """Runs the layer on the residual stream x (in place).  delta: what the block before left to be
+        added to x first.  Returns what this block leaves to be added (None: nothing)."""
+        xn = self.mixer_norm.forward(ctx, x, delta=delta)
+        delta = self.mixer.forward(ctx, xn, x, cache)
+        xn = self.ffn_norm.forward(ctx, x, delta=delta)
+        return self.ffn.forward(ctx, xn, x)
 
 
 register_part("block", "prenorm", PreNormBlock)

@@ -52,6 +52,7 @@ class StepContext:
     max_kv_len: int = 0
     layer_caches: Dict[str, LayerCache] = field(default_factory=dict)
     shared: Dict[object, torch.Tensor] = field(default_factory=dict)   # what one layer computed for all (per step)
+    defer_residual: bool = False       # parts may return what is to be added to the residual; the next norm adds it
 
     def empty(self, shape, dtype=None) -> torch.Tensor:
         return torch.empty(shape, dtype=dtype or self.dtype, device=self.device)

@@ -10,7 +10,7 @@ import torch
 from .. import ops
 from ..weights.params import ParamSpec
 from .base import FeedForward, register_part
-from .linear import matmul
+from .linear import matmul, matmul_into_residual
 
 
 class SwiGLU(FeedForward):
@@ -31,14 +31,14 @@ class SwiGLU(FeedForward):
         self.w_gate_up = torch.cat([g, u], dim=0).contiguous()
         self.w_down = tensors["down_proj.weight"]
 
-    def forward(self, ctx, xn, residual) -> None:
+    def forward(self, ctx, xn, residual):
         act = torch.empty((xn.shape[0], self.inter), dtype=xn.dtype, device=xn.device)
         fused = xn.dtype == torch.bfloat16 and self.w_gate_up.dtype == torch.bfloat16 and \
             ops.gemm_bf16_swiglu(xn, self.w_gate_up, act)          # activation in the product's epilogue
         if not fused:
             gu = matmul(ctx, xn, self.w_gate_up)
             ops.swiglu(gu, act)
-        matmul(ctx, act, self.w_down, out=residual, accumulate=True)
+        return matmul_into_residual(ctx, act, self.w_down, residual)
 
 
 register_part("ffn", "swiglu", SwiGLU)

@@ -33,3 +33,19 @@ def matmul(ctx, a: torch.Tensor, w: torch.Tensor, out: Optional[torch.Tensor] = 
     else:
         ops.gemm_ref(a, w, out, accumulate)
     return out
+
+
+def matmul_into_residual(ctx, a: torch.Tensor, w: torch.Tensor, residual: torch.Tensor) -> Optional[torch.Tensor]:
+    """residual += a W^T - now, or by the norm that reads the residual next.
+
+    Where the step lets sums be deferred (ctx.defer_residual: every norm of the model adds stacked
+    partial sums) and the product is one of the weight-streaming kind, the product leaves its split
+    partial sums [S, T, N] and this returns them: the caller hands them on as its result, and the next
+    norm adds them to the residual in a fixed order before it normalises.  Otherwise the product is
+    added to the residual here and None is returned."""
+    if getattr(ctx, "defer_residual", False) and ops.fast_gemm_available():
+        parts = ops.gemm_bf16_partials(a, w) if a.shape[0] else None
+        if parts is not None:
+            return parts
+    matmul(ctx, a, w, out=residual, accumulate=True)
+    return None

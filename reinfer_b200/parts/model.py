@@ -8,6 +8,7 @@ from typing import Dict, List, Mapping, Optional, Tuple
 
 import torch
 
+from .. import ops
 from ..weights.params import ParamSpec
 from .base import PagedKVSpec, SlotStateSpec, _REGISTRY, _ensure_builtin, build_part
 from .spec import LayerSpec, ModelSpec, PartSpec
@@ -44,6 +45,7 @@ class Model:
         self.final_norm = build_part("norm", spec.final_norm)
         self.lm_head = build_part("lm_head", spec.lm_head)
         self.order = spec.run_order()
+        self._chain = ops.StreamChain()         # what the streaming kernels of a pass read, in order (for their L2 hints)
         for i in self.order:
             if not 0 <= i < len(self.layers):
                 raise ValueError(f"run order names layer {i} of {len(self.layers)}")
@@ -55,6 +57,11 @@ class Model:
             k = seen.get(i, 0)
             seen[i] = k + 1
             self.run.append((i, self.layers[i].name if k == 0 else f"{self.layers[i].name}#{k}"))
+        # sums may be left for the next norm only if every norm can add a stack of partial sums and every
+        # block hands on what its parts leave
+        norms = [n for l in self.layers for n in (l.mixer_norm, l.ffn_norm)] + [self.final_norm]
+        self._norms_add_partial_sums = all(getattr(n, "adds_partial_sums", False) for n in norms) and \
+            all(getattr(l.block, "hands_on_sums", False) for l in self.layers) and ops.DEFER_SUMS
         by_name = {l.name: l for l in self.layers}
         for l in self.layers:
             src = l.spec.cache_from
@@ -140,13 +147,27 @@ class Model:
         """Run the step's tokens through every layer in run order; return float32 logits
         [len(want_rows), vocab] for the wanted token rows (None if none are wanted)."""
         ctx.shared.clear()                      # what layers share is computed anew in every pass (a captured pass included)
-        x = self.embedding.forward(ctx)
-        for i, key in self.run:
-            self.layers[i].block.forward(ctx, x, ctx.layer_caches[key])
-        if want_rows is None or want_rows.numel() == 0:
-            return None
-        xn = self.final_norm.forward(ctx, x, row_idx=want_rows)
-        return self.lm_head.forward(ctx, xn)
+        previous = ops.set_chain(self._chain)   # the streaming kernels learn from the last pass what they may prefetch
+        self._chain.begin()
+        try:
+            x = self.embedding.forward(ctx)
+            ctx.defer_residual = self._norms_add_partial_sums
+            delta = None                        # what a block left to be added to x by the norm that reads x next
+            for i, key in self.run:
+                block = self.layers[i].block
+                if self._norms_add_partial_sums:
+                    delta = block.forward(ctx, x, ctx.layer_caches[key], delta)
+                else:
+                    block.forward(ctx, x, ctx.layer_caches[key])
+            if want_rows is None or want_rows.numel() == 0:
+                return None                     # (a sum still owed to x is dropped with x)
+            xn = self.final_norm.forward(ctx, x, delta=delta, row_idx=want_rows)
+            logits = self.lm_head.forward(ctx, xn)
+            self._chain.end()                   # a pass that came this far is complete
+            return logits
+        finally:
+            self._chain.live = False
+            ops.set_chain(previous)
 
 
 def expected_params(spec: ModelSpec) -> Dict[str, ParamSpec]:

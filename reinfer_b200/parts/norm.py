@@ -11,6 +11,8 @@ from .base import Norm, register_part
 
 
 class RMSNorm(Norm):
+    adds_partial_sums = True            # delta may be a stack [S, rows, width] of partial sums
+
     def __init__(self, width: int, eps: float):
         self.width, self.eps = int(width), float(eps)
         self.weight = None

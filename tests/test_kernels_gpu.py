@@ -71,6 +71,76 @@ def test_gemm_split_k_is_deterministic(splits):
     assert (c1 - ref).abs().max().item() <= 1e-3 * ref.abs().max().item()
 
 
+@pytest.mark.parametrize("T,N,K", [(1, 128, 256), (8, 4096, 4096), (5, 311, 1000), (33, 130, 520), (64, 1000, 2048), (7, 384, 12288)])
+def test_gemm_partial_sums_and_the_norm_that_adds_them(T, N, K):
+    """A split product may leave its partial sums [S, T, N]; add_rmsnorm adds a stack of them to the residual in
+    ascending order before it normalises - twice the same bits, and the sum is the product."""
+    from reinfer_b200 import ops
+    a, w = rnd(T, K, dtype=torch.bfloat16, seed=1), rnd(N, K, dtype=torch.bfloat16, scale=0.05, seed=2)
+    p1 = ops.gemm_bf16_partials(a, w)
+    p2 = ops.gemm_bf16_partials(a, w)
+    assert ops.kernel_error() == 0
+    assert p1 is not None and p1.dim() == 3 and p1.shape[1:] == (T, N) and p1.dtype == torch.float32
+    assert torch.equal(p1, p2)
+    ref = a.float() @ w.float().t()
+    assert (p1.sum(0) - ref).abs().max().item() <= (2e-5 * math.sqrt(K) + 1e-6) * ref.abs().max().item()
+    if p1.shape[0] > 1:                                     # the ranges of K are disjoint: no partial sum is the whole
+        assert (p1[0] - ref).abs().max().item() > 1e-3 * ref.abs().max().item()
+    # the norm over the residual plus the stack, against the plain statement
+    base = rnd(T, N, seed=3)
+    gamma = rnd(N, seed=4).abs() + 0.5
+    for out_dtype in (torch.bfloat16, torch.float32):
+        x = base.clone()
+        out = torch.empty(T, N, dtype=out_dtype, device=DEV)
+        ops.add_rmsnorm(x, p1, gamma, out, 1e-6)
+        want_x = base.clone()
+        for k in range(p1.shape[0]):
+            want_x += p1[k]
+        assert torch.equal(x, want_x)                       # ascending order, float32: the same bits
+        want = want_x * torch.rsqrt((want_x * want_x).mean(-1, keepdim=True) + 1e-6) * gamma
+        tol = 1e-2 if out_dtype == torch.bfloat16 else 1e-5
+        assert (out.float() - want).abs().max().item() <= tol * want.abs().max().item()
+    # gathered rows: the sums are formed for those rows only and x stays as it was
+    idx = torch.tensor([T - 1, 0], dtype=torch.int32, device=DEV)
+    x = base.clone()
+    out = torch.empty(2, N, dtype=torch.bfloat16, device=DEV)
+    ops.add_rmsnorm(x, p1, gamma, out, 1e-6, row_idx=idx)
+    assert torch.equal(x, base)
+    assert (out.float() - want[idx.long()]).abs().max().item() <= 1e-2 * want.abs().max().item()
+
+
+def test_gemm_plan_and_prefetch_hint():
+    """What the decode product chooses can be asked for; a range to call into L2 changes no result."""
+    import ctypes
+    from reinfer_b200 import ops
+    lib = ops.lib()
+    torch.zeros(1, device=DEV)
+    for N, K, dual in ((6144, 4096, 0), (4096, 12288, 0), (12288, 4096, 1), (151936, 4096, 0), (128, 64, 0)):
+        out = (ctypes.c_int * 9)()
+        assert lib.rb_gemm_plan(N, K, dual, out) == 0
+        assert 1 <= out[0] <= 8
+        tiles = -(-N // 128)
+        assert tiles * out[0] <= max(out[out[0]], tiles), "the chosen split fits the resident CTAs (or is no split)"
+    a, w = rnd(8, 1024, dtype=torch.bfloat16, seed=1), rnd(512, 1024, dtype=torch.bfloat16, scale=0.05, seed=2)
+    nxt = rnd(300, 1000, dtype=torch.bfloat16, seed=3)
+    c0 = torch.empty(8, 512, dtype=torch.float32, device=DEV)
+    c1 = torch.empty_like(c0)
+    ops.gemm_bf16(a, w, c0)
+    chain = ops.StreamChain()
+    old = ops.set_chain(chain)
+    try:
+        for _ in range(2):                                  # the second pass knows what follows each product
+            chain.begin()
+            ops.gemm_bf16(a, w, c1)
+            ops.gemm_bf16(a[:, :1000].contiguous(), nxt, torch.empty(8, 300, dtype=torch.float32, device=DEV))
+            chain.end()
+        assert chain.known == [(w.data_ptr(), w.numel() * 2), (nxt.data_ptr(), nxt.numel() * 2)]
+    finally:
+        ops.set_chain(old)
+    assert ops.kernel_error() == 0
+    assert torch.equal(c0, c1)
+
+
 @pytest.mark.parametrize("ta,tw,tc", [(torch.float32, torch.float32, torch.float32),
                                       (torch.bfloat16, torch.float32, torch.bfloat16),
                                       (torch.float32, torch.bfloat16, torch.float32),
