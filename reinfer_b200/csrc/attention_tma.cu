@@ -576,6 +576,34 @@ __global__ void ft_merge_kernel(const float* __restrict__ part_o, const float* _
     RB_TL_MARK();
     const int t = blockIdx.x, h = blockIdx.y;
     const size_t base = ((size_t)t * QH + h) * n_splits;
+    bf16* orow = out + ((size_t)(first_tok + t) * QH + h) * d;
+    if (n_splits <= 8) {
+        // the usual case: every load of a thread is issued before the first is used (one trip to L2, not two)
+        for (int dim = threadIdx.x; dim < d; dim += blockDim.x) {
+            float l[8], o[8];
+#pragma unroll
+            for (int s = 0; s < 8; ++s) {
+                l[s] = s < n_splits ? part_lse[base + s] : -INFINITY;
+                o[s] = s < n_splits ? part_o[(base + s) * d + dim] : 0.0f;
+            }
+            float M = -INFINITY;
+#pragma unroll
+            for (int s = 0; s < 8; ++s) M = fmaxf(M, l[s]);
+            float W = 0.0f, O = 0.0f;
+            if (M > -INFINITY) {
+#pragma unroll
+                for (int s = 0; s < 8; ++s) {
+                    if (s < n_splits) {
+                        const float w = exp2f(l[s] - M);
+                        W += w;
+                        O += w * o[s];
+                    }
+                }
+            }
+            orow[dim] = __float2bfloat16_rn(W > 0.0f ? O / W : 0.0f);
+        }
+        return;
+    }
     float M = -INFINITY;
     for (int s = 0; s < n_splits; ++s) M = fmaxf(M, part_lse[base + s]);
     for (int dim = threadIdx.x; dim < d; dim += blockDim.x) {
@@ -587,7 +615,7 @@ __global__ void ft_merge_kernel(const float* __restrict__ part_o, const float* _
                 O += w * part_o[(base + s) * d + dim];
             }
         }
-        out[((size_t)(first_tok + t) * QH + h) * d + dim] = __float2bfloat16_rn(W > 0.0f ? O / W : 0.0f);
+        orow[dim] = __float2bfloat16_rn(W > 0.0f ? O / W : 0.0f);
     }
 }
 

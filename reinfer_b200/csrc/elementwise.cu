@@ -127,7 +127,7 @@ add_rmsnorm_cluster_kernel(float* __restrict__ x, const float* __restrict__ delt
                            const TW* __restrict__ w, bf16* __restrict__ out, const int* __restrict__ row_idx, int h, float eps) {
     RB_TL(2);
     __shared__ float red[32];
-    __shared__ float part_ss;
+    __shared__ float part_ss[RN_CL];
     pdl_trigger();
     uint32_t rank;
     asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(rank));
@@ -173,18 +173,18 @@ add_rmsnorm_cluster_kernel(float* __restrict__ x, const float* __restrict__ delt
         ss += t.x * t.x + t.y * t.y + t.z * t.z + t.w * t.w;
     }
     const float mine = block_sum(ss, red);
-    if (threadIdx.x == 0) part_ss = mine;
+    // every CTA writes its part into the slot of its rank in every CTA of the cluster (its own included); after
+    // the one barrier each reads its own shared memory only, so nobody has to outlive its peers
+    if (threadIdx.x < RN_CL) {
+        uint32_t remote;
+        const uint32_t local = (uint32_t)__cvta_generic_to_shared(&part_ss[rank]);
+        asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(remote) : "r"(local), "r"((uint32_t)threadIdx.x));
+        asm volatile("st.shared::cluster.f32 [%0], %1;" ::"r"(remote), "f"(mine) : "memory");
+    }
     asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
     float total = 0.0f;
-    const uint32_t local = (uint32_t)__cvta_generic_to_shared(&part_ss);
 #pragma unroll
-    for (uint32_t c = 0; c < RN_CL; ++c) {                   // rank order: the same sum in every CTA of the row
-        uint32_t remote;
-        float f;
-        asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(remote) : "r"(local), "r"(c));
-        asm volatile("ld.shared::cluster.f32 %0, [%1];" : "=f"(f) : "r"(remote) : "memory");
-        total += f;
-    }
+    for (int c = 0; c < RN_CL; ++c) total += part_ss[c];     // rank order: the same sum in every CTA of the row
     const float rstd = 1.0f / sqrtf(total / (float)h + eps);
     bf16* orow = out + (size_t)r * h + c0;                  // 8-byte aligned: h and the share are multiples of 4
 #pragma unroll
@@ -198,8 +198,72 @@ add_rmsnorm_cluster_kernel(float* __restrict__ x, const float* __restrict__ delt
             *reinterpret_cast<uint2*>(orow + i) = pk;
         }
     }
-    // nobody leaves while its part of the sum may still be read
-    asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+
+// An RMS norm whose division is left to the product that reads it:  x[r,:] += sum_p delta[p][r,:] (ascending),
+// y[r,:] = bfloat16(x[r,:] * w), and sumsq[r, c] = the sum of x^2 over the columns of chunk c (RS_COLS columns a
+// chunk).  The reader multiplies its results for row r by 1/sqrt(sum_c sumsq[r,c] / h + eps), which is the same
+// number as normalising first (a row's factor is a scalar that passes through a product) - and so no CTA here
+// needs another CTA's sum: a decode step's few rows spread over rows x chunks CTAs, each one trip to L2.
+constexpr int RS_THREADS = 256, RS_COLS = RS_THREADS * 4;
+template <typename TW>
+__global__ void __launch_bounds__(RS_THREADS)
+residual_rowscale_kernel(float* __restrict__ x, const float* __restrict__ delta, int n_delta, long long delta_stride,
+                         const TW* __restrict__ w, bf16* __restrict__ y, float* __restrict__ sumsq, int h) {
+    RB_TL(2);
+    __shared__ float red[32];
+    pdl_trigger();
+    const int i = (blockIdx.x * RS_THREADS + threadIdx.x) * 4;      // h is a multiple of 4
+    const bool in = i < h;
+    float4 wv = make_float4(0.f, 0.f, 0.f, 0.f);
+    if (in) { wv.x = to_f32(w[i]); wv.y = to_f32(w[i + 1]); wv.z = to_f32(w[i + 2]); wv.w = to_f32(w[i + 3]); }
+    pdl_wait();
+    RB_TL_MARK();
+    const size_t row = (size_t)blockIdx.y * h;
+    float4 t = make_float4(0.f, 0.f, 0.f, 0.f);
+    if (in) {
+        t = *reinterpret_cast<const float4*>(x + row + i);
+        if (delta) {
+            const float* dr = delta + row + i;
+            for (int p0 = 0; p0 < n_delta; p0 += 8) {          // eight partial sums in flight, added in ascending order
+                float4 d[8];
+#pragma unroll
+                for (int p = 0; p < 8; ++p)
+                    d[p] = p0 + p < n_delta ? *reinterpret_cast<const float4*>(dr + (size_t)(p0 + p) * delta_stride)
+                                            : make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+                for (int p = 0; p < 8; ++p) if (p0 + p < n_delta) { t.x += d[p].x; t.y += d[p].y; t.z += d[p].z; t.w += d[p].w; }
+            }
+            *reinterpret_cast<float4*>(x + row + i) = t;
+        }
+        const __nv_bfloat162 lo = __floats2bfloat162_rn(t.x * wv.x, t.y * wv.y);
+        const __nv_bfloat162 hi = __floats2bfloat162_rn(t.z * wv.z, t.w * wv.w);
+        uint2 pk;
+        pk.x = *reinterpret_cast<const uint32_t*>(&lo); pk.y = *reinterpret_cast<const uint32_t*>(&hi);
+        *reinterpret_cast<uint2*>(y + row + i) = pk;
+    }
+    const float ss = block_sum(t.x * t.x + t.y * t.y + t.z * t.z + t.w * t.w, red);
+    if (threadIdx.x == 0) sumsq[(size_t)blockIdx.y * gridDim.x + blockIdx.x] = ss;
+}
+
+// How many chunks (parts of a row's sum of squares) rb_residual_rowscale writes for rows of h elements.
+extern "C" int rb_rowscale_parts(int h) { return h > 0 ? rb_ceil_div(h, RS_COLS) : 0; }
+
+extern "C" int rb_residual_rowscale(float* x, const float* delta, int n_delta, long long delta_stride, const void* w, int w_dtype,
+                                    void* y, float* sumsq, int rows, int h, void* stream) {
+    if (rows <= 0) return 0;
+    if (h <= 0 || h % 4) RB_REFUSE("rowscale: width %d is not a multiple of 4", h);
+    if (delta && (n_delta < 1 || n_delta > 64 || delta_stride % 4)) RB_REFUSE("rowscale: %d partial sums, %lld apart", n_delta, delta_stride);
+    if ((((uintptr_t)x | (uintptr_t)delta) & 15) || ((uintptr_t)y & 7)) RB_REFUSE("rowscale: operands must be 16-byte aligned");
+    cudaStream_t s = (cudaStream_t)stream;
+    const dim3 grid(rb_ceil_div(h, RS_COLS), rows);
+    if (w_dtype == RB_F32)
+        return rb_launch(residual_rowscale_kernel<float>, grid, dim3(RS_THREADS), 0, s, x, delta, n_delta, delta_stride,
+                         (const float*)w, (bf16*)y, sumsq, h);
+    if (w_dtype == RB_BF16)
+        return rb_launch(residual_rowscale_kernel<bf16>, grid, dim3(RS_THREADS), 0, s, x, delta, n_delta, delta_stride,
+                         (const bf16*)w, (bf16*)y, sumsq, h);
+    RB_REFUSE("rowscale: weight dtype %d", w_dtype);
 }
 
 template <typename TD, typename TW>
@@ -365,8 +429,10 @@ __global__ void qknorm_rope_append_vec_kernel(const bf16* __restrict__ qkv, cons
                                               bf16* __restrict__ q_out, bf16* __restrict__ cache,
                                               int n_tokens, int QH, int KH, int d, int page_size, float eps) {
     RB_TL(3);
-    pdl_trigger(); pdl_wait();
-    RB_TL_MARK();
+    pdl_trigger();
+    // Everything that does not come from the kernels before this one - the step's positions and slots, the
+    // norm weights, the angles - is fetched and computed while they still run; only qkv (and a table of
+    // cosines that an earlier kernel of this step wrote) waits for them.
     const int heads = QH + 2 * KH;
     const long long wglobal = ((long long)blockIdx.x * blockDim.x + threadIdx.x) >> 5;
     const int lane = threadIdx.x & 31;
@@ -380,6 +446,8 @@ __global__ void qknorm_rope_append_vec_kernel(const bf16* __restrict__ qkv, cons
         const int kh = hh - QH - KH;
         const int page = slot / page_size, off = slot % page_size;
         bf16* dst = cache + ((((size_t)page * 2 + 1) * KH + kh) * page_size + off) * d;
+        pdl_wait();
+        RB_TL_MARK();
         for (int i = lane; i < d / 8; i += 32)
             reinterpret_cast<uint4*>(dst)[i] = reinterpret_cast<const uint4*>(src)[i];
         return;
@@ -395,9 +463,26 @@ __global__ void qknorm_rope_append_vec_kernel(const bf16* __restrict__ qkv, cons
         dst = cache + ((((size_t)page * 2 + 0) * KH + (hh - QH)) * page_size + off) * d;
     }
     // this lane's pairs: elements p, p+1 with p = 2*lane + 64*i, and their partners half further
-    float a0[4], a1[4], b0[4], b1[4];                         // head_dim <= 512
+    const int n_it = half / 64;                               // head_dim <= 512
+    float wa0[4], wa1[4], wb0[4], wb1[4], c0[4], s0[4], c1[4], s1[4];
+    const float pos = (float)positions[t];
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        wa0[i] = wa1[i] = wb0[i] = wb1[i] = 1.0f;
+        c0[i] = c1[i] = 1.0f; s0[i] = s1[i] = 0.0f;
+        if (i < n_it) {
+            const int p = 2 * lane + 64 * i;
+            if (w) { wa0[i] = to_f32(w[p]); wa1[i] = to_f32(w[p + 1]); wb0[i] = to_f32(w[p + half]); wb1[i] = to_f32(w[p + half + 1]); }
+            if (!cs_table) {
+                sincosf(pos * inv_freq[p], &s0[i], &c0[i]);
+                sincosf(pos * inv_freq[p + 1], &s1[i], &c1[i]);
+            }
+        }
+    }
+    pdl_wait();
+    RB_TL_MARK();
+    float a0[4], a1[4], b0[4], b1[4];
     float ss = 0.0f;
-    const int n_it = half / 64;
 #pragma unroll
     for (int i = 0; i < 4; ++i) {
         if (i < n_it) {
@@ -406,6 +491,10 @@ __global__ void qknorm_rope_append_vec_kernel(const bf16* __restrict__ qkv, cons
             const float2 hi = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(src + p + half));
             a0[i] = lo.x; a1[i] = lo.y; b0[i] = hi.x; b1[i] = hi.y;
             ss += lo.x * lo.x + lo.y * lo.y + hi.x * hi.x + hi.y * hi.y;
+            if (cs_table) {
+                const float4 v = *reinterpret_cast<const float4*>(cs_table + (size_t)t * half + p);
+                c0[i] = v.x; s0[i] = v.y; c1[i] = v.z; s1[i] = v.w;
+            }
         }
     }
     float rstd = 1.0f;
@@ -413,26 +502,17 @@ __global__ void qknorm_rope_append_vec_kernel(const bf16* __restrict__ qkv, cons
         ss = warp_sum(ss);
         rstd = 1.0f / sqrtf(ss / (float)d + eps);
     }
-    const float pos = (float)positions[t];
 #pragma unroll
     for (int i = 0; i < 4; ++i) {
         if (i < n_it) {
             const int p = 2 * lane + 64 * i;
             float x0 = a0[i], x1 = a1[i], y0 = b0[i], y1 = b1[i];
             if (w) {
-                x0 = x0 * rstd * to_f32(w[p]); x1 = x1 * rstd * to_f32(w[p + 1]);
-                y0 = y0 * rstd * to_f32(w[p + half]); y1 = y1 * rstd * to_f32(w[p + half + 1]);
+                x0 = x0 * rstd * wa0[i]; x1 = x1 * rstd * wa1[i];
+                y0 = y0 * rstd * wb0[i]; y1 = y1 * rstd * wb1[i];
             }
-            float c0, s0, c1, s1;
-            if (cs_table) {
-                const float4 v = *reinterpret_cast<const float4*>(cs_table + (size_t)t * half + p);
-                c0 = v.x; s0 = v.y; c1 = v.z; s1 = v.w;
-            } else {
-                sincosf(pos * inv_freq[p], &s0, &c0);
-                sincosf(pos * inv_freq[p + 1], &s1, &c1);
-            }
-            *reinterpret_cast<__nv_bfloat162*>(dst + p) = __floats2bfloat162_rn(x0 * c0 - y0 * s0, x1 * c1 - y1 * s1);
-            *reinterpret_cast<__nv_bfloat162*>(dst + p + half) = __floats2bfloat162_rn(x0 * s0 + y0 * c0, x1 * s1 + y1 * c1);
+            *reinterpret_cast<__nv_bfloat162*>(dst + p) = __floats2bfloat162_rn(x0 * c0[i] - y0 * s0[i], x1 * c1[i] - y1 * s1[i]);
+            *reinterpret_cast<__nv_bfloat162*>(dst + p + half) = __floats2bfloat162_rn(x0 * s0[i] + y0 * c0[i], x1 * s1[i] + y1 * c1[i]);
         }
     }
 }

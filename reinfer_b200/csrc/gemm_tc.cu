@@ -52,6 +52,20 @@ struct TcShared {                        // after the operand stages, in dynamic
     unsigned long long acc_full;
     uint32_t tmem_base;
     int abort_flag;
+    float row_scale[256];                // the factor that each token's results are multiplied by (1 if none)
+};
+
+// What a product over one token tile may be told beside its operands.
+struct TcExtra {
+    // A range that the CTAs call into L2 once their own weights have arrived (null: none).
+    const void* next_w;
+    long long next_bytes;
+    // The rows of X lack a factor: row t stands for X[t,:] / sqrt(sum_p row_sumsq[t, p] * inv_width + eps) - an
+    // RMS norm whose division is left to this product's epilogue, where it costs one multiplication per
+    // result (null: X is complete).  The parts are added in ascending order.
+    const float* row_sumsq;
+    int sumsq_parts;
+    float inv_width, eps;
 };
 
 // out_mode 0: C = acc as bf16; 1: C = acc as float; 2: C(float) += acc; 3: workspace partial (float, [split][T][N]).
@@ -63,7 +77,7 @@ template <int BN, int STAGES, bool DUAL>
 __global__ void __launch_bounds__(TC_THREADS, (BN <= 64 ? 2 : 1))
 gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_x,
                void* __restrict__ C, float* __restrict__ ws, int T, int N, int K, long long ldc, int out_mode,
-               int kb_per_split, int csplit, const void* __restrict__ next_w, long long next_bytes) {
+               int kb_per_split, int csplit, const TcExtra ex) {
     RB_TL(DUAL ? 7 : 6);
     extern __shared__ __align__(1024) unsigned char smem_raw[];
     constexpr uint32_t W1_BYTES = TC_BM * TC_BK * 2;                // 16 KB per weight tile
@@ -161,6 +175,16 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
         const int q = warp & 3;
         const int feat = n0 + q * 32 + lane;
         pdl_wait();                                            // C may still be in use by the kernels before
+        for (int idx = threadIdx.x - 64; idx < BN; idx += 128) {
+            float f = 1.0f;
+            if (ex.row_sumsq && t0 + idx < T) {
+                float ssq = 0.0f;
+                for (int p = 0; p < ex.sumsq_parts; ++p) ssq += ex.row_sumsq[(size_t)(t0 + idx) * ex.sumsq_parts + p];
+                f = 1.0f / sqrtf(ssq * ex.inv_width + ex.eps);
+            }
+            sh->row_scale[idx] = f;
+        }
+        asm volatile("bar.sync 2, 128;" ::: "memory");         // the four epilogue warps
         if (mbar_wait(smem_u32(&sh->acc_full), 0, abort_flag, 3)) {
             tc_fence_after();
             if (threadIdx.x == 64) TL(4);
@@ -168,7 +192,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
             // stores) and the kernels after it start up, memory would idle: the weights that the next product
             // streams are called into L2 now.
             if (threadIdx.x == 64)
-                l2_prefetch_share(next_w, next_bytes, (blockIdx.z * gridDim.y + blockIdx.y) * gridDim.x + blockIdx.x,
+                l2_prefetch_share(ex.next_w, ex.next_bytes, (blockIdx.z * gridDim.y + blockIdx.y) * gridDim.x + blockIdx.x,
                                   gridDim.x * gridDim.y * gridDim.z);
 #pragma unroll 1
             for (int c0 = 0; c0 < BN; c0 += 16) {
@@ -177,6 +201,14 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
                 tc_ld16(tmem + ((uint32_t)(q * 32) << 16) + (uint32_t)c0, r);
                 if (DUAL) tc_ld16(tmem + ((uint32_t)(q * 32) << 16) + (uint32_t)(BN + c0), r2);
                 tc_ld_wait();
+                if (csplit == 1) {
+#pragma unroll
+                    for (int j = 0; j < 16; ++j) {
+                        const float f = sh->row_scale[c0 + j];
+                        r[j] = __float_as_uint(__uint_as_float(r[j]) * f);
+                        if (DUAL) r2[j] = __float_as_uint(__uint_as_float(r2[j]) * f);
+                    }
+                }
                 if (csplit > 1) {                              // park the accumulator(s) for the cluster's reduction
 #pragma unroll
                     for (int j = 0; j < 16; ++j) {
@@ -252,12 +284,15 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
                 float v[4] = {part[0].x, part[0].y, part[0].z, part[0].w};
 #pragma unroll
                 for (int r = 1; r < 8; ++r) { v[0] += part[r].x; v[1] += part[r].y; v[2] += part[r].z; v[3] += part[r].w; }
+                const float f = sh->row_scale[cb];
+#pragma unroll
+                for (int i = 0; i < 4; ++i) v[i] *= f;
                 if (DUAL) {
                     float u[4] = {part2[0].x, part2[0].y, part2[0].z, part2[0].w};
 #pragma unroll
                     for (int r = 1; r < 8; ++r) { u[0] += part2[r].x; u[1] += part2[r].y; u[2] += part2[r].z; u[3] += part2[r].w; }
 #pragma unroll
-                    for (int i = 0; i < 4; ++i) v[i] = v[i] / (1.0f + expf(-v[i])) * u[i];
+                    for (int i = 0; i < 4; ++i) v[i] = v[i] / (1.0f + expf(-v[i])) * (u[i] * f);
                 }
                 const size_t at = (size_t)(t0 + cb) * ldc + feat;
 #pragma unroll
@@ -574,7 +609,7 @@ static int tc_env_splits(int N, int K) {
 // want_splits: 0 = choose; > 0 = that many through a cluster (at most 8); < 0 = that many through the workspace.
 template <int BN, int STAGES, bool DUAL>
 static int launch_tc(const CUtensorMap& mw, const CUtensorMap& mx, void* C, float* ws, long long ws_floats, int T, int N, int K,
-                     long long ldc, int mode, int want_splits, const void* next_w, long long next_bytes, cudaStream_t s,
+                     long long ldc, int mode, int want_splits, const TcExtra& ex, cudaStream_t s,
                      bool keep_partials = false) {
     constexpr size_t smem = (size_t)STAGES * ((DUAL ? 2 : 1) * TC_BM * TC_BK * 2 + BN * TC_BK * 2) + sizeof(TcShared) + 1024;
     static bool configured = false;
@@ -631,7 +666,7 @@ static int launch_tc(const CUtensorMap& mw, const CUtensorMap& mx, void* C, floa
     }
     cfg.attrs = attr;
     cfg.numAttrs = na;
-    cudaError_t e = cudaLaunchKernelEx(&cfg, gemm_tc_kernel<BN, STAGES, DUAL>, mw, mx, C, ws, T, N, K, ldc, out_mode, kb_per_split, csplit, next_w, next_bytes);
+    cudaError_t e = cudaLaunchKernelEx(&cfg, gemm_tc_kernel<BN, STAGES, DUAL>, mw, mx, C, ws, T, N, K, ldc, out_mode, kb_per_split, csplit, ex);
     if (e != cudaSuccess) { (void)cudaGetLastError(); return (int)e; }
     int rc = RB_LAUNCH_RESULT();
     if (rc) return rc;
@@ -648,18 +683,33 @@ extern "C" int rb_set_gemm_persistent(int mode) { int old = g_tc_persistent; g_t
 
 static int tc_bn(int T) { return T <= 16 ? 16 : T <= 32 ? 32 : T <= 64 ? 64 : T <= 128 ? 128 : 256; }
 
+// The extras of a launch from the entry points' arguments (-1 and a message if they make no sense).
+static int tc_extra(TcExtra* ex, const void* next_w, long long next_bytes, const float* row_sumsq, int sumsq_parts,
+                    int norm_width, float norm_eps, int T) {
+    if ((uintptr_t)next_w & 15) RB_REFUSE("gemm: the range to prefetch must start on a 16-byte boundary");
+    if (row_sumsq && (sumsq_parts < 1 || sumsq_parts > 1024 || norm_width < 1))
+        RB_REFUSE("gemm: a row factor from %d parts over a width of %d", sumsq_parts, norm_width);
+    if (row_sumsq && T > 256) RB_REFUSE("gemm: row factors are for one token tile (%d tokens)", T);
+    ex->next_w = next_w; ex->next_bytes = next_w ? next_bytes : 0;
+    ex->row_sumsq = row_sumsq; ex->sumsq_parts = sumsq_parts;
+    ex->inv_width = row_sumsq ? 1.0f / (float)norm_width : 0.0f; ex->eps = norm_eps;
+    return 0;
+}
+
 // X [T,K] bf16 (row stride ldx), W [N,K] bf16 (row stride ldw), C [T,N] bf16 or float (row stride ldc).
 // ws: float workspace of ws_floats elements for split-K partials beyond a cluster (may be null).
 extern "C" int rb_gemm_bf16(const void* X, const void* W, void* C, int c_dtype, int accumulate, int T, int N, int K,
                             long long ldx, long long ldw, long long ldc, float* ws, long long ws_floats,
-                            int force_splits, const void* next_w, long long next_bytes, void* stream) {
+                            int force_splits, const void* next_w, long long next_bytes,
+                            const float* row_sumsq, int sumsq_parts, int norm_width, float norm_eps, void* stream) {
     if (T <= 0 || N <= 0) return 0;
     if (K <= 0) RB_REFUSE("gemm: K=%d", K);
     if ((ldx % 8) || (ldw % 8) || ((uintptr_t)X & 15) || ((uintptr_t)W & 15))
         RB_REFUSE("gemm: TMA needs 16-byte aligned operands and row strides (ldx %lld, ldw %lld)", ldx, ldw);
     if (accumulate && c_dtype != RB_F32) RB_REFUSE("gemm: accumulation needs a float destination");
-    if ((uintptr_t)next_w & 15) RB_REFUSE("gemm: the range to prefetch must start on a 16-byte boundary");
     if (c_dtype != RB_F32 && c_dtype != RB_BF16) RB_REFUSE("gemm: destination dtype %d", c_dtype);
+    TcExtra ex;
+    if (tc_extra(&ex, next_w, next_bytes, row_sumsq, sumsq_parts, norm_width, norm_eps, T)) return -1;
     cudaStream_t s = (cudaStream_t)stream;
     const int mode = accumulate ? 2 : (c_dtype == RB_F32 ? 1 : 0);
     const int bn = tc_bn(T);
@@ -671,11 +721,11 @@ extern "C" int rb_gemm_bf16(const void* X, const void* W, void* C, int c_dtype, 
     }
     if (rb_tensor_map_bf16(X, T, K, ldx, bn, &mx)) return -1;
     switch (bn) {
-        case 16: return launch_tc<16, 6, false>(mw, mx, C, ws, ws_floats, T, N, K, ldc, mode, force_splits, next_w, next_bytes, s);
-        case 32: return launch_tc<32, 5, false>(mw, mx, C, ws, ws_floats, T, N, K, ldc, mode, force_splits, next_w, next_bytes, s);
-        case 64: return launch_tc<64, 4, false>(mw, mx, C, ws, ws_floats, T, N, K, ldc, mode, force_splits, next_w, next_bytes, s);
-        case 128: return launch_tc<128, 5, false>(mw, mx, C, ws, ws_floats, T, N, K, ldc, mode, force_splits, next_w, next_bytes, s);
-        default: return launch_tc<256, 4, false>(mw, mx, C, ws, ws_floats, T, N, K, ldc, mode, force_splits, next_w, next_bytes, s);
+        case 16: return launch_tc<16, 6, false>(mw, mx, C, ws, ws_floats, T, N, K, ldc, mode, force_splits, ex, s);
+        case 32: return launch_tc<32, 5, false>(mw, mx, C, ws, ws_floats, T, N, K, ldc, mode, force_splits, ex, s);
+        case 64: return launch_tc<64, 4, false>(mw, mx, C, ws, ws_floats, T, N, K, ldc, mode, force_splits, ex, s);
+        case 128: return launch_tc<128, 5, false>(mw, mx, C, ws, ws_floats, T, N, K, ldc, mode, force_splits, ex, s);
+        default: return launch_tc<256, 4, false>(mw, mx, C, ws, ws_floats, T, N, K, ldc, mode, force_splits, ex, s);
     }
 }
 
@@ -706,13 +756,15 @@ extern "C" int rb_gemm_partials_plan(int T, int N, int K) {
 // rb_gemm_partials_plan names: the product without its last sum, which the kernel that reads the result
 // forms on the way (the residual sum and norm, the head norm) - no CTA waits for another.
 extern "C" int rb_gemm_bf16_partials(const void* X, const void* W, float* partials, int splits, int T, int N, int K,
-                                     long long ldx, long long ldw, const void* next_w, long long next_bytes, void* stream) {
+                                     long long ldx, long long ldw, const void* next_w, long long next_bytes,
+                                     const float* row_sumsq, int sumsq_parts, int norm_width, float norm_eps, void* stream) {
     if (T <= 0 || N <= 0) return 0;
     if (K <= 0) RB_REFUSE("gemm: K=%d", K);
     if ((ldx % 8) || (ldw % 8) || ((uintptr_t)X & 15) || ((uintptr_t)W & 15))
         RB_REFUSE("gemm: TMA needs 16-byte aligned operands and row strides (ldx %lld, ldw %lld)", ldx, ldw);
-    if ((uintptr_t)next_w & 15) RB_REFUSE("gemm: the range to prefetch must start on a 16-byte boundary");
     if (T > 256) RB_REFUSE("gemm: partial sums are for one token tile (%d tokens)", T);
+    TcExtra ex;
+    if (tc_extra(&ex, next_w, next_bytes, row_sumsq, sumsq_parts, norm_width, norm_eps, T)) return -1;
     if (splits != rb_gemm_partials_plan(T, N, K)) RB_REFUSE("gemm: %d partial sums where the plan names %d", splits, rb_gemm_partials_plan(T, N, K));
     cudaStream_t s = (cudaStream_t)stream;
     const int bn = tc_bn(T);
@@ -721,11 +773,11 @@ extern "C" int rb_gemm_bf16_partials(const void* X, const void* W, float* partia
     if (rb_tensor_map_bf16(X, T, K, ldx, bn, &mx)) return -1;
     const long long wsf = (long long)splits * T * N;
     switch (bn) {
-        case 16: return launch_tc<16, 6, false>(mw, mx, nullptr, partials, wsf, T, N, K, N, 1, -splits, next_w, next_bytes, s, true);
-        case 32: return launch_tc<32, 5, false>(mw, mx, nullptr, partials, wsf, T, N, K, N, 1, -splits, next_w, next_bytes, s, true);
-        case 64: return launch_tc<64, 4, false>(mw, mx, nullptr, partials, wsf, T, N, K, N, 1, -splits, next_w, next_bytes, s, true);
-        case 128: return launch_tc<128, 5, false>(mw, mx, nullptr, partials, wsf, T, N, K, N, 1, -splits, next_w, next_bytes, s, true);
-        default: return launch_tc<256, 4, false>(mw, mx, nullptr, partials, wsf, T, N, K, N, 1, -splits, next_w, next_bytes, s, true);
+        case 16: return launch_tc<16, 6, false>(mw, mx, nullptr, partials, wsf, T, N, K, N, 1, -splits, ex, s, true);
+        case 32: return launch_tc<32, 5, false>(mw, mx, nullptr, partials, wsf, T, N, K, N, 1, -splits, ex, s, true);
+        case 64: return launch_tc<64, 4, false>(mw, mx, nullptr, partials, wsf, T, N, K, N, 1, -splits, ex, s, true);
+        case 128: return launch_tc<128, 5, false>(mw, mx, nullptr, partials, wsf, T, N, K, N, 1, -splits, ex, s, true);
+        default: return launch_tc<256, 4, false>(mw, mx, nullptr, partials, wsf, T, N, K, N, 1, -splits, ex, s, true);
     }
 }
 
@@ -733,11 +785,13 @@ extern "C" int rb_gemm_bf16_partials(const void* X, const void* W, float* partia
 // accumulators and the activation in the epilogue.  Splits (at most 8) reduce inside a cluster.
 extern "C" int rb_gemm_bf16_swiglu(const void* X, const void* Wgu, void* act, int T, int F, int K,
                                    long long ldx, long long ldw, long long ldc, int force_splits,
-                                   const void* next_w, long long next_bytes, void* stream) {
+                                   const void* next_w, long long next_bytes,
+                                   const float* row_sumsq, int sumsq_parts, int norm_width, float norm_eps, void* stream) {
     if (T <= 0 || F <= 0) return 0;
     if (K <= 0) RB_REFUSE("gemm_swiglu: K=%d", K);
     if (force_splits < 0 || force_splits > 8) RB_REFUSE("gemm_swiglu: %d splits (0 = choose, at most a cluster of 8)", force_splits);
-    if ((uintptr_t)next_w & 15) RB_REFUSE("gemm_swiglu: the range to prefetch must start on a 16-byte boundary");
+    TcExtra ex;
+    if (tc_extra(&ex, next_w, next_bytes, row_sumsq, sumsq_parts, norm_width, norm_eps, T)) return -1;
     if ((ldx % 8) || (ldw % 8) || ((uintptr_t)X & 15) || ((uintptr_t)Wgu & 15))
         RB_REFUSE("gemm_swiglu: TMA needs 16-byte aligned operands and row strides (ldx %lld, ldw %lld)", ldx, ldw);
     cudaStream_t s = (cudaStream_t)stream;
@@ -750,11 +804,11 @@ extern "C" int rb_gemm_bf16_swiglu(const void* X, const void* Wgu, void* act, in
     }
     if (rb_tensor_map_bf16(X, T, K, ldx, bn, &mx)) return -1;
     switch (bn) {
-        case 16: return launch_tc<16, 3, true>(mw, mx, act, nullptr, 0, T, F, K, ldc, 0, force_splits, next_w, next_bytes, s);
-        case 32: return launch_tc<32, 3, true>(mw, mx, act, nullptr, 0, T, F, K, ldc, 0, force_splits, next_w, next_bytes, s);
-        case 64: return launch_tc<64, 4, true>(mw, mx, act, nullptr, 0, T, F, K, ldc, 0, force_splits, next_w, next_bytes, s);
-        case 128: return launch_tc<128, 4, true>(mw, mx, act, nullptr, 0, T, F, K, ldc, 0, force_splits, next_w, next_bytes, s);
-        default: return launch_tc<256, 3, true>(mw, mx, act, nullptr, 0, T, F, K, ldc, 0, force_splits, next_w, next_bytes, s);
+        case 16: return launch_tc<16, 3, true>(mw, mx, act, nullptr, 0, T, F, K, ldc, 0, force_splits, ex, s);
+        case 32: return launch_tc<32, 3, true>(mw, mx, act, nullptr, 0, T, F, K, ldc, 0, force_splits, ex, s);
+        case 64: return launch_tc<64, 4, true>(mw, mx, act, nullptr, 0, T, F, K, ldc, 0, force_splits, ex, s);
+        case 128: return launch_tc<128, 4, true>(mw, mx, act, nullptr, 0, T, F, K, ldc, 0, force_splits, ex, s);
+        default: return launch_tc<256, 3, true>(mw, mx, act, nullptr, 0, T, F, K, ldc, 0, force_splits, ex, s);
     }
 }
 

@@ -128,6 +128,26 @@ def add_rmsnorm(x: torch.Tensor, delta: Optional[torch.Tensor], w: torch.Tensor,
                                 _stream()), "add_rmsnorm")
 
 
+def residual_rowscale(x: torch.Tensor, delta: Optional[torch.Tensor], w: torch.Tensor):
+    """x (float32 [rows,h]) += delta (x's shape, or a stack of partial sums added in ascending order); returns
+    (y, sumsq): y = bfloat16(x * w) and sumsq [rows, parts] float32, the sum of x^2 by chunks of columns.  The
+    product that reads y multiplies its results for row r by 1/sqrt(sum(sumsq[r]) / h + eps): the RMS norm with
+    its division moved behind the product (gemm_bf16(..., row_scale=(sumsq, h, eps)))."""
+    _need(x.dtype == torch.float32 and x.is_contiguous() and x.dim() == 2, "rowscale: x float32 [rows,h] contiguous")
+    rows, h = x.shape
+    n_delta = 0
+    if delta is not None:
+        _need(delta.dtype == torch.float32 and delta.is_contiguous() and delta.numel() % x.numel() == 0 and delta.shape[-1] == h,
+              "rowscale: delta float32 with x's shape (or a stack of it)")
+        n_delta = delta.numel() // x.numel()
+    parts = int(lib().rb_rowscale_parts(c_int(h)))
+    y = torch.empty((rows, h), dtype=torch.bfloat16, device=x.device)
+    sumsq = torch.empty((rows, parts), dtype=torch.float32, device=x.device)
+    _check(lib().rb_residual_rowscale(_p(x), _p(delta), c_int(n_delta), c_longlong(x.numel()), _p(w), c_int(dt(w)),
+                                      _p(y), _p(sumsq), c_int(rows), c_int(h), _stream()), "residual_rowscale")
+    return y, sumsq
+
+
 def residual_add(x: torch.Tensor, delta: torch.Tensor) -> None:
     _need(x.dtype == torch.float32 and x.is_contiguous() and delta.is_contiguous() and x.numel() == delta.numel(),
           "residual_add: x float32, same size")
@@ -279,6 +299,16 @@ def set_chain(chain: Optional[StreamChain]) -> Optional[StreamChain]:
     return old
 
 
+def _row_scale_args(row_scale, T: int):
+    """(sumsq pointer, parts, width, eps) arguments of a product whose rows still lack their RMS factor."""
+    if row_scale is None:
+        return c_void_p(0), c_int(0), c_int(0), c_float(0.0)
+    sumsq, width, eps = row_scale
+    _need(sumsq.dtype == torch.float32 and sumsq.is_contiguous() and sumsq.dim() == 2 and sumsq.shape[0] == T,
+          "gemm: row factors come as float32 [tokens, parts]")
+    return _p(sumsq), c_int(sumsq.shape[1]), c_int(int(width)), c_float(float(eps))
+
+
 def _next_range(t: Optional[torch.Tensor], marker: int = 0):
     """(pointer, bytes) arguments of the range that follows tensor t (or the marker) in the active chain."""
     if _chain is None or L2_PREFETCH_BYTES <= 0:
@@ -386,7 +416,8 @@ def fast_gemm_available() -> bool:
     return True
 
 
-def gemm_bf16(a: torch.Tensor, w: torch.Tensor, c: torch.Tensor, accumulate: bool = False, splits: int = 0) -> None:
+def gemm_bf16(a: torch.Tensor, w: torch.Tensor, c: torch.Tensor, accumulate: bool = False, splits: int = 0,
+              row_scale=None) -> None:
     """c[T,N] (=|+=) a[T,K] @ w[N,K]^T on the tensor cores (tcgen05, TMA); bf16 operands, float
     accumulation, c bfloat16 or float32.  Operands that TMA cannot address (a row stride that is no
     multiple of 8 elements, a base that is not 16-byte aligned) go to the plain kernel instead."""
@@ -397,16 +428,18 @@ def gemm_bf16(a: torch.Tensor, w: torch.Tensor, c: torch.Tensor, accumulate: boo
     _need(a.dtype == torch.bfloat16 and w.dtype == torch.bfloat16, "gemm_bf16: bfloat16 operands")
     _need(a.stride(1) == 1 and w.stride(1) == 1 and c.stride(1) == 1, "gemm: rows contiguous")
     if a.stride(0) % 8 or w.stride(0) % 8 or a.data_ptr() % 16 or w.data_ptr() % 16:
+        _need(row_scale is None, "gemm: row factors need operands that TMA can address")
         return gemm_ref(a, w, c, accumulate)
     if _gemm_ws is None or _gemm_ws.device != a.device:
         _gemm_ws = torch.empty(GEMM_WS_FLOATS, dtype=torch.float32, device=a.device)
     nw, nb = _next_range(w) if T <= STREAMING_TOKENS else (c_void_p(0), c_longlong(0))
     _check(lib().rb_gemm_bf16(_p(a), _p(w), _p(c), c_int(dt(c)), c_int(int(accumulate)), c_int(T), c_int(N), c_int(K),
                               c_longlong(a.stride(0)), c_longlong(w.stride(0)), c_longlong(c.stride(0)),
-                              _p(_gemm_ws), c_longlong(_gemm_ws.numel()), c_int(splits), nw, nb, _stream()), "gemm_bf16")
+                              _p(_gemm_ws), c_longlong(_gemm_ws.numel()), c_int(splits), nw, nb,
+                              *_row_scale_args(row_scale, T), _stream()), "gemm_bf16")
 
 
-def gemm_bf16_partials(a: torch.Tensor, w: torch.Tensor) -> Optional[torch.Tensor]:
+def gemm_bf16_partials(a: torch.Tensor, w: torch.Tensor, row_scale=None) -> Optional[torch.Tensor]:
     """Partial sums [S, T, N] (float32) of a[T,K] @ w[N,K]^T over S ranges of K, for a consumer that adds them
     up itself (add_rmsnorm with a stacked delta): the split product then needs no reduction of its own, and
     none of its CTAs waits for another.  None if this product is not one for the streaming kernel (more than
@@ -422,11 +455,12 @@ def gemm_bf16_partials(a: torch.Tensor, w: torch.Tensor) -> Optional[torch.Tenso
     out = torch.empty((S, T, N), dtype=torch.float32, device=a.device)
     nw, nb = _next_range(w)
     _check(lib().rb_gemm_bf16_partials(_p(a), _p(w), _p(out), c_int(S), c_int(T), c_int(N), c_int(K),
-                                       c_longlong(a.stride(0)), c_longlong(w.stride(0)), nw, nb, _stream()), "gemm_bf16_partials")
+                                       c_longlong(a.stride(0)), c_longlong(w.stride(0)), nw, nb,
+                                       *_row_scale_args(row_scale, T), _stream()), "gemm_bf16_partials")
     return out
 
 
-def gemm_bf16_swiglu(a: torch.Tensor, w_gate_up: torch.Tensor, out: torch.Tensor, splits: int = 0) -> bool:
+def gemm_bf16_swiglu(a: torch.Tensor, w_gate_up: torch.Tensor, out: torch.Tensor, splits: int = 0, row_scale=None) -> bool:
     """out[T,F] (bf16) = silu(a Wg^T) * (a Wu^T), w_gate_up = [Wg; Wu] of shape [2F, K]: one tensor-core
     product with two accumulators and the activation in its epilogue.  Returns False (and does
     nothing) if TMA cannot address the operands; the caller then runs the two-kernel form."""
@@ -440,7 +474,7 @@ def gemm_bf16_swiglu(a: torch.Tensor, w_gate_up: torch.Tensor, out: torch.Tensor
     nw, nb = _next_range(w_gate_up) if T <= STREAMING_TOKENS else (c_void_p(0), c_longlong(0))
     _check(lib().rb_gemm_bf16_swiglu(_p(a), _p(w_gate_up), _p(out), c_int(T), c_int(F_), c_int(K),
                                      c_longlong(a.stride(0)), c_longlong(w_gate_up.stride(0)), c_longlong(out.stride(0)),
-                                     c_int(splits), nw, nb, _stream()), "gemm_bf16_swiglu")
+                                     c_int(splits), nw, nb, *_row_scale_args(row_scale, T), _stream()), "gemm_bf16_swiglu")
     return True
 
 

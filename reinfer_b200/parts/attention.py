@@ -19,7 +19,7 @@ import torch
 from .. import ops
 from ..weights.params import ParamSpec
 from .base import Mixer, PagedKVSpec, build_part, register_part
-from .linear import matmul, matmul_into_residual
+from .linear import matmul, matmul_into_residual, takes_row_scaled
 from .spec import PartSpec
 
 
@@ -68,11 +68,17 @@ class Attention(Mixer):
         if self.position is not None:
             self.position.prepare(device)
 
+    @property
+    def takes_row_scaled(self) -> bool:
+        """The first product (q, k, v) can apply the factor of rows that the norm left without it."""
+        return takes_row_scaled(self.w_qkv)
+
     # ---- the step ------------------------------------------------------------
     def forward(self, ctx, xn, residual, cache) -> None:
         T, QH, KH, d = xn.shape[0], self.QH, self.KH, self.d
         g = cache.group
         qkv = matmul(ctx, xn, self.w_qkv)                                     # [T, (QH+2KH) d]
+        xn = qkv                                                              # (dtype and device from here on)
         q = torch.empty((T, QH, d), dtype=xn.dtype, device=xn.device)
         fused = self.position.fused_rotary() if self.position is not None else (None, 0)
         slots = g.kv_slot if cache.write else None

@@ -8,17 +8,23 @@ ParamSpec) and receives them, already on the device and in their kept dtype, thr
 
   Norm.forward(ctx, x, out=None, delta=None, row_idx=None) -> Tensor
       x: the float32 residual stream [T, h]; if `delta` is given it is added into x
-      first.  Returns the normalised rows in the activation dtype.
+      first (a norm with `adds_partial_sums` also takes a stack [S, T, h] of partial
+      sums).  Returns the normalised rows in the activation dtype.  A norm with
+      `leaves_row_scale` takes `scaled_ok=True` from a block whose reader has
+      `takes_row_scaled`, and may then return a RowScaled instead: rows that still
+      lack their scalar factor, which the reader's first product applies.
   PositionEncoding.apply(ctx, q, k, positions) -> None          (in place, generic path)
       q [T, QH, d], k [T, KH, d].  A mixer may ask `fused_rotary()` for (inv_freq,
       rotated_width) and apply the rotation inside its own kernel instead.
-  Mixer.forward(ctx, xn, residual, cache) -> None
+  Mixer.forward(ctx, xn, residual, cache) -> None | Tensor
       xn: normalised input [T, h] in the activation dtype; the mixer ADDS its output
-      into `residual` (float32 [T, h]).  `cache` is the LayerCache of the layer
+      into `residual` (float32 [T, h]) - or, when `ctx.defer_residual` is set, may
+      return what is still to be added ([T, h] or a stack [S, T, h]) for the next norm.  `cache` is the LayerCache of the layer
       (parts/context.py).  `cache_spec()` / `state_spec()` say what the layer needs
       from the cache manager: paged keys/values and/or a fixed-size state per request.
-  FeedForward.forward(ctx, xn, residual) -> None                 (same convention)
-  Block.forward(ctx, x, cache) -> None                           (x updated in place)
+  FeedForward.forward(ctx, xn, residual) -> None | Tensor        (same convention)
+  Block.forward(ctx, x, cache[, delta]) -> None | Tensor         (x updated in place; a block with
+      `hands_on_sums` takes what the block before left to be added and returns its own)
 """
 from __future__ import annotations
 
@@ -44,6 +50,32 @@ class SlotStateSpec:
     """A state of fixed size per live request, zeroed when the request is admitted."""
     shape: Tuple[int, ...]
     dtype: str = "float32"                      # "float32" or "act" (the activation dtype)
+
+
+@dataclass
+class RowScaled:
+    """Rows that still lack a scalar factor each: row t stands for
+    rows[t] / sqrt(sum(sumsq[t]) / width + eps) - an RMS norm whose division is left to the product
+    that reads the rows, which multiplies its results by the factor (ops.gemm_bf16(..., row_scale=))."""
+    rows: torch.Tensor                  # [T, h] bfloat16: x * weight
+    sumsq: torch.Tensor                 # [T, parts] float32: the sum of x^2 by chunks of columns
+    width: int
+    eps: float
+
+    @property
+    def shape(self):
+        return self.rows.shape
+
+    @property
+    def dtype(self):
+        return self.rows.dtype
+
+    @property
+    def device(self):
+        return self.rows.device
+
+    def scale(self):
+        return (self.sumsq, self.width, self.eps)
 
 
 class Part:

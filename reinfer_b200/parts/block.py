@@ -19,10 +19,17 @@ class PreNormBlock:
     def forward(self, ctx, x, cache, delta=None):
         """Runs the layer on the residual stream x (in place).  delta: what the block before left to be
         added to x first.  Returns what this block leaves to be added (None: nothing)."""
-        xn = self.mixer_norm.forward(ctx, x, delta=delta)
+        xn = _norm(self.mixer_norm, self.mixer, ctx, x, delta)
         delta = self.mixer.forward(ctx, xn, x, cache)
-        xn = self.ffn_norm.forward(ctx, x, delta=delta)
+        xn = _norm(self.ffn_norm, self.ffn, ctx, x, delta)
         return self.ffn.forward(ctx, xn, x)
+
+
+def _norm(norm, reader, ctx, x, delta):
+    """The norm before `reader`; rows without their factor only where both sides know of them."""
+    if getattr(norm, "leaves_row_scale", False) and getattr(reader, "takes_row_scaled", False):
+        return norm.forward(ctx, x, delta=delta, scaled_ok=True)
+    return norm.forward(ctx, x, delta=delta)
 
 
 register_part("block", "prenorm", PreNormBlock)

@@ -9,8 +9,8 @@ import torch
 
 from .. import ops
 from ..weights.params import ParamSpec
-from .base import FeedForward, register_part
-from .linear import matmul, matmul_into_residual
+from .base import FeedForward, RowScaled, register_part
+from .linear import matmul, matmul_into_residual, takes_row_scaled
 
 
 class SwiGLU(FeedForward):
@@ -31,8 +31,17 @@ class SwiGLU(FeedForward):
         self.w_gate_up = torch.cat([g, u], dim=0).contiguous()
         self.w_down = tensors["down_proj.weight"]
 
+    @property
+    def takes_row_scaled(self) -> bool:
+        """The first product (gate and up) can apply the factor of rows that the norm left without it."""
+        return takes_row_scaled(self.w_gate_up)
+
     def forward(self, ctx, xn, residual):
         act = torch.empty((xn.shape[0], self.inter), dtype=xn.dtype, device=xn.device)
+        if isinstance(xn, RowScaled):
+            if not ops.gemm_bf16_swiglu(xn.rows, self.w_gate_up, act, row_scale=xn.scale()):
+                raise ValueError("swiglu: rows without their factor need the tensor-core product")
+            return matmul_into_residual(ctx, act, self.w_down, residual)
         fused = xn.dtype == torch.bfloat16 and self.w_gate_up.dtype == torch.bfloat16 and \
             ops.gemm_bf16_swiglu(xn, self.w_gate_up, act)          # activation in the product's epilogue
         if not fused:

@@ -15,10 +15,22 @@ from typing import Optional
 import torch
 
 from .. import ops
+from .base import RowScaled
 
 
-def matmul(ctx, a: torch.Tensor, w: torch.Tensor, out: Optional[torch.Tensor] = None,
+def takes_row_scaled(w: Optional[torch.Tensor]) -> bool:
+    """Whether products with this weight can apply a row factor in their epilogue (the tensor-core kernel with
+    operands that TMA can address): a part whose first product qualifies may accept RowScaled input."""
+    return w is not None and w.dtype == torch.bfloat16 and w.is_cuda and ops.fast_gemm_available() and \
+        w.stride(1) == 1 and w.stride(0) % 8 == 0 and w.data_ptr() % 16 == 0 and w.shape[1] % 8 == 0
+
+
+def matmul(ctx, a, w: torch.Tensor, out: Optional[torch.Tensor] = None,
            out_dtype: Optional[torch.dtype] = None, accumulate: bool = False) -> torch.Tensor:
+    """a: a tensor [M, K], or RowScaled rows, whose factor the product's epilogue applies."""
+    row_scale = None
+    if isinstance(a, RowScaled):
+        a, row_scale = a.rows, a.scale()
     M, N = a.shape[0], w.shape[0]
     if out is None:
         if accumulate:
@@ -29,8 +41,10 @@ def matmul(ctx, a: torch.Tensor, w: torch.Tensor, out: Optional[torch.Tensor] = 
     if M == 0:
         return out
     if a.dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and ops.fast_gemm_available():
-        ops.gemm_bf16(a, w, out, accumulate)
+        ops.gemm_bf16(a, w, out, accumulate, row_scale=row_scale)
     else:
+        if row_scale is not None:
+            raise ValueError("matmul: rows without their factor need the tensor-core product")
         ops.gemm_ref(a, w, out, accumulate)
     return out
 

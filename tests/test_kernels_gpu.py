@@ -109,6 +109,47 @@ def test_gemm_partial_sums_and_the_norm_that_adds_them(T, N, K):
     assert (out.float() - want[idx.long()]).abs().max().item() <= 1e-2 * want.abs().max().item()
 
 
+@pytest.mark.parametrize("T,h,N", [(1, 128, 256), (8, 4096, 6144), (5, 1000, 311), (33, 520, 130), (64, 2048, 1000)])
+@pytest.mark.parametrize("n_delta", [0, 1, 7])
+def test_norm_whose_division_is_left_to_the_product(T, h, N, n_delta):
+    """residual_rowscale leaves x*w and the parts of sum(x^2); a product that is told of them multiplies its
+    results by the row's factor - together the same as normalising first (plain, cluster-split, gated, partial)."""
+    from reinfer_b200 import ops
+    eps = 1e-6
+    base = rnd(T, h, seed=1, scale=3.0)
+    gamma = rnd(h, seed=2).abs() + 0.5
+    delta = rnd(n_delta, T, h, seed=3) if n_delta else None
+    x = base.clone()
+    y, sumsq = ops.residual_rowscale(x, delta if n_delta != 1 else delta[0], gamma)
+    want_x = base.clone()
+    for k in range(n_delta):
+        want_x += delta[k]
+    assert torch.equal(x, want_x)
+    assert y.dtype == torch.bfloat16 and sumsq.shape[0] == T
+    ss = (want_x.double() ** 2).sum(-1)
+    assert (sumsq.double().sum(-1) - ss).abs().max().item() <= 1e-5 * ss.max().item()
+    assert (y.float() - want_x * gamma).abs().max().item() <= 4e-3 * (want_x * gamma).abs().max().item()
+    xn = y.float() * torch.rsqrt(ss / h + eps).float()[:, None]          # what the rows stand for
+    w = rnd(N, h, dtype=torch.bfloat16, scale=0.05, seed=4)
+    ref = xn @ w.float().t()
+    scale = (sumsq, h, eps)
+    for splits in (0, 1, 3):
+        c = torch.empty(T, N, dtype=torch.float32, device=DEV)
+        ops.gemm_bf16(y, w, c, splits=splits, row_scale=scale)
+        assert (c - ref).abs().max().item() <= 2e-4 * ref.abs().max().item(), f"splits {splits}"
+    p = ops.gemm_bf16_partials(y, w, row_scale=scale)
+    assert (p.sum(0) - ref).abs().max().item() <= 2e-4 * ref.abs().max().item()
+    if N % 2 == 0:
+        F = N // 2
+        act = torch.empty(T, F, dtype=torch.bfloat16, device=DEV)
+        for splits in (0, 1, 2):
+            assert ops.gemm_bf16_swiglu(y, w, act, splits=splits, row_scale=scale)
+            g, u = ref[:, :F], ref[:, F:]
+            want = g / (1 + torch.exp(-g)) * u
+            assert (act.float() - want).abs().max().item() <= 1e-2 * want.abs().max().item(), f"gated, splits {splits}"
+    assert ops.kernel_error() == 0
+
+
 def test_gemm_plan_and_prefetch_hint():
     """What the decode product chooses can be asked for; a range to call into L2 changes no result."""
     import ctypes
