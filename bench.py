@@ -110,6 +110,7 @@ def main() -> int:
     ap.add_argument("--layers", type=int, default=None, help="fewer layers than the configuration (named in config)")
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-points", action="store_true")
+    ap.add_argument("--page-size", type=int, default=64, help="tokens per cache page")
     a = ap.parse_args()
     if a.impl == "reference":
         print(json.dumps({"impl": "reference", "unavailable": "the reference is a Rust workspace (no Python package, "
@@ -134,7 +135,7 @@ def main() -> int:
     raw["num_hidden_layers"] = layers
     cfg = Qwen3Config.from_dict(raw)
     hbm_gbs, tf_burst, tf_sust, peak_src = peaks()
-    page = 16
+    page = a.page_size
     max_b = max(a.batch, 1 if a.no_points else 64)
     ctx_len = a.context
     pool_tokens = max_b * (ctx_len + page) + 4096

@@ -88,7 +88,7 @@ def main(argv=None) -> int:
     r.add_argument("--max-model-len", type=int, default=None, metavar="N")
     r.add_argument("--perf", action="store_true", help="print a machine-parseable PERF line")
     r.add_argument("--dtype", choices=["bfloat16", "float32"], default="bfloat16")
-    r.add_argument("--page-size", type=int, default=16)
+    r.add_argument("--page-size", type=int, default=64)
     r.add_argument("--num-pages", type=int, default=None)
     r.add_argument("--max-num-seqs", type=int, default=8)
     r.add_argument("--max-batch-tokens", type=int, default=2048)

@@ -91,7 +91,7 @@ class Engine:
     weights made on the device (`from_config`)."""
 
     def __init__(self, config, spec, state: Dict[str, torch.Tensor], dtype: torch.dtype, *,
-                 page_size: int = 16, num_pages: Optional[int] = None, max_tokens: Optional[int] = None,
+                 page_size: int = 64, num_pages: Optional[int] = None, max_tokens: Optional[int] = None,
                  max_num_seqs: int = 64, device="cuda:0", memory_fraction: float = 0.9,
                  cuda_graphs: bool = True):
         self.device = torch.device(device)

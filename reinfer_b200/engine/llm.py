@@ -32,7 +32,7 @@ class RequestOutput:
 class LLM:
     def __init__(self, model: Optional[str] = None, *, engine: Optional[Engine] = None, dtype="bfloat16",
                  max_num_seqs: int = 64, max_batch_tokens: int = 2048, max_chunk: Optional[int] = None,
-                 page_size: int = 16, num_pages: Optional[int] = None, max_model_len: Optional[int] = None,
+                 page_size: int = 64, num_pages: Optional[int] = None, max_model_len: Optional[int] = None,
                  seed: int = 0, device="cuda:0", memory_fraction: float = 0.9):
         if engine is None:
             if model is None:

@@ -34,7 +34,7 @@ def main(argv=None) -> int:
         num_key_value_heads=8, head_dim=128, intermediate_size=12288, vocab_size=151936, rope_theta=1e6,
         rms_norm_eps=1e-6, tie_word_embeddings=False, max_position_embeddings=40960))
     B, N = a.batch, a.context
-    eng = Engine.from_config(cfg, seed=0, dtype="bfloat16", page_size=16, max_tokens=B * (N + 64) + 2 * a.prefill_tokens,
+    eng = Engine.from_config(cfg, seed=0, dtype="bfloat16", page_size=64, max_tokens=B * (N + 64) + 2 * a.prefill_tokens,
                              max_num_seqs=B + 1, cuda_graphs=False)
     g = torch.Generator().manual_seed(0)
     for b in range(B):

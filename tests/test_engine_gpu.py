@@ -129,8 +129,9 @@ def test_trace_run_program(models, tmp_path, dtype):
                                  "end": end}))
     out = tmp_path / "out"
     root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    extra = ["--page-size", "16"] if dtype == "float32" else []      # the default page (64 tokens) and a smaller one
     p = subprocess.run([sys.executable, os.path.join(root, "bin", "trace_run"), "--model", model_dir, "--dtype", dtype,
-                        "--out", str(out), "--max-tokens", str(tiny.pool_tokens_needed(steps))],
+                        "--out", str(out), "--max-tokens", str(tiny.pool_tokens_needed(steps))] + extra,
                        input="\n".join(lines) + "\n", capture_output=True, text=True, timeout=600)
     assert p.returncode == 0, p.stderr[-2000:]
     assert [l for l in p.stdout.splitlines() if l.startswith("done")] == [f"done {i}" for i in range(len(steps))]
