@@ -200,6 +200,69 @@ add_rmsnorm_cluster_kernel(float* __restrict__ x, const float* __restrict__ delt
     }
 }
 
+// Many rows of 16-bit activations (a prompt portion): one CTA per row with 16-byte loads and stores, every load of
+// a thread in flight before the first is used.  (The 32-bit path keeps the scalar kernel above, whose sums do not
+// depend on how many rows a step brings.)
+constexpr int RV_THREADS = 256;
+template <typename TW, int VPER>
+__global__ void __launch_bounds__(RV_THREADS)
+add_rmsnorm_vec_kernel(float* __restrict__ x, const float* __restrict__ delta, int n_delta, long long delta_stride,
+                       const TW* __restrict__ w, bf16* __restrict__ out, int h, float eps) {
+    RB_TL(2);
+    __shared__ float red[32];
+    pdl_trigger(); pdl_wait();
+    RB_TL_MARK();
+    const size_t row = (size_t)blockIdx.x * h;
+    float4 v[VPER];
+    float ss = 0.0f;
+#pragma unroll
+    for (int k = 0; k < VPER; ++k) {
+        const int i = (threadIdx.x + k * RV_THREADS) * 4;
+        v[k] = i < h ? *reinterpret_cast<const float4*>(x + row + i) : make_float4(0.f, 0.f, 0.f, 0.f);
+    }
+    if (delta) {
+        for (int p = 0; p < n_delta; ++p) {                        // ascending: a fixed order
+#pragma unroll
+            for (int k = 0; k < VPER; ++k) {
+                const int i = (threadIdx.x + k * RV_THREADS) * 4;
+                if (i < h) {
+                    const float4 d = *reinterpret_cast<const float4*>(delta + (size_t)p * delta_stride + row + i);
+                    v[k].x += d.x; v[k].y += d.y; v[k].z += d.z; v[k].w += d.w;
+                }
+            }
+        }
+#pragma unroll
+        for (int k = 0; k < VPER; ++k) {
+            const int i = (threadIdx.x + k * RV_THREADS) * 4;
+            if (i < h) *reinterpret_cast<float4*>(x + row + i) = v[k];
+        }
+    }
+#pragma unroll
+    for (int k = 0; k < VPER; ++k) ss += v[k].x * v[k].x + v[k].y * v[k].y + v[k].z * v[k].z + v[k].w * v[k].w;
+    const float total = block_sum(ss, red);
+    const float rstd = 1.0f / sqrtf(total / (float)h + eps);
+#pragma unroll
+    for (int k = 0; k < VPER; ++k) {
+        const int i = (threadIdx.x + k * RV_THREADS) * 4;
+        if (i < h) {
+            const __nv_bfloat162 lo = __floats2bfloat162_rn(v[k].x * rstd * to_f32(w[i]), v[k].y * rstd * to_f32(w[i + 1]));
+            const __nv_bfloat162 hi = __floats2bfloat162_rn(v[k].z * rstd * to_f32(w[i + 2]), v[k].w * rstd * to_f32(w[i + 3]));
+            uint2 pk;
+            pk.x = *reinterpret_cast<const uint32_t*>(&lo); pk.y = *reinterpret_cast<const uint32_t*>(&hi);
+            *reinterpret_cast<uint2*>(out + row + i) = pk;
+        }
+    }
+}
+template <typename TW>
+static int launch_add_rmsnorm_vec(float* x, const float* delta, int n_delta, long long delta_stride, const TW* w, bf16* out,
+                                  int rows, int h, float eps, cudaStream_t s) {
+    const int vper = rb_ceil_div(h, RV_THREADS * 4);
+    if (vper <= 1) return rb_launch(add_rmsnorm_vec_kernel<TW, 1>, dim3(rows), dim3(RV_THREADS), 0, s, x, delta, n_delta, delta_stride, w, out, h, eps);
+    if (vper <= 2) return rb_launch(add_rmsnorm_vec_kernel<TW, 2>, dim3(rows), dim3(RV_THREADS), 0, s, x, delta, n_delta, delta_stride, w, out, h, eps);
+    if (vper <= 4) return rb_launch(add_rmsnorm_vec_kernel<TW, 4>, dim3(rows), dim3(RV_THREADS), 0, s, x, delta, n_delta, delta_stride, w, out, h, eps);
+    return rb_launch(add_rmsnorm_vec_kernel<TW, 8>, dim3(rows), dim3(RV_THREADS), 0, s, x, delta, n_delta, delta_stride, w, out, h, eps);
+}
+
 // An RMS norm whose division is left to the product that reads it:  x[r,:] += sum_p delta[p][r,:] (ascending),
 // y[r,:] = bfloat16(x[r,:] * w), and sumsq[r, c] = the sum of x^2 over the columns of chunk c (RS_COLS columns a
 // chunk).  The reader multiplies its results for row r by 1/sqrt(sum_c sumsq[r,c] / h + eps), which is the same
@@ -297,6 +360,11 @@ extern "C" int rb_add_rmsnorm(float* x, const void* delta, int delta_dtype, int 
         if (w_dtype == RB_BF16)
             return rb_launch_cluster(add_rmsnorm_cluster_kernel<bf16>, dim3(RN_CL, rows), dim3(RN_THREADS), RN_CL, 0, s, x,
                                      (const float*)delta, n_delta, delta_stride, (const bf16*)w, (bf16*)out, row_idx, h, eps);
+    }
+    if (out_dtype == RB_BF16 && dd == RB_F32 && !row_idx && rows > 64 && h % 4 == 0 && h <= RV_THREADS * 4 * 8 &&
+        ((((uintptr_t)x | (uintptr_t)delta) & 15) == 0) && (((uintptr_t)out) & 7) == 0 && (!delta || delta_stride % 4 == 0)) {
+        if (w_dtype == RB_F32) return launch_add_rmsnorm_vec<float>(x, (const float*)delta, n_delta, delta_stride, (const float*)w, (bf16*)out, rows, h, eps, s);
+        if (w_dtype == RB_BF16) return launch_add_rmsnorm_vec<bf16>(x, (const float*)delta, n_delta, delta_stride, (const bf16*)w, (bf16*)out, rows, h, eps, s);
     }
     if (dd == RB_F32 && w_dtype == RB_F32) return launch_add_rmsnorm_o<float, float>(x, delta, n_delta, delta_stride, w, out, out_dtype, row_idx, rows, h, eps, s);
     if (dd == RB_F32 && w_dtype == RB_BF16) return launch_add_rmsnorm_o<float, bf16>(x, delta, n_delta, delta_stride, w, out, out_dtype, row_idx, rows, h, eps, s);
@@ -420,7 +488,7 @@ extern "C" int rb_rope_table(const int* positions, const float* inv_freq, void* 
 }
 
 // The same operation for the common layout - bfloat16 activations and cache, the whole head rotated, head_dim a
-// multiple of 64 - with 4-byte loads and stores (a lane owns element pairs 2l, 2l+1 of both halves) and 16-byte
+// multiple of 128 - with 4-byte loads and stores (a lane owns element pairs 2l, 2l+1 of both halves) and 16-byte
 // copies of the value rows; cosines and sines come from the step's table when one is given.
 template <typename TW>
 __global__ void qknorm_rope_append_vec_kernel(const bf16* __restrict__ qkv, const TW* __restrict__ qw, const TW* __restrict__ kw,
@@ -517,6 +585,105 @@ __global__ void qknorm_rope_append_vec_kernel(const bf16* __restrict__ qkv, cons
     }
 }
 
+// The same for many tokens (a prompt portion): a warp takes one token and a group of up to QG_HEADS heads of one
+// kind (query, key or value), so that the token's slot, the cosines and sines and the norm's weights are fetched
+// once per group, and the loads of all its heads are in flight together.  head_dim is 128 * n_it, n_it <= 2 here.
+constexpr int QG_HEADS = 8;
+template <typename TW>
+__global__ void __launch_bounds__(128)
+qknorm_rope_append_grouped_kernel(const bf16* __restrict__ qkv, const TW* __restrict__ qw, const TW* __restrict__ kw,
+                                  const float* __restrict__ inv_freq, const float2* __restrict__ cs_table,
+                                  const int* __restrict__ positions, const int* __restrict__ kv_slot,
+                                  bf16* __restrict__ q_out, bf16* __restrict__ cache,
+                                  int n_tokens, int QH, int KH, int d, int page_size, float eps) {
+    RB_TL(3);
+    pdl_trigger(); pdl_wait();
+    RB_TL_MARK();
+    const int qg = (QH + QG_HEADS - 1) / QG_HEADS, kg = (KH + QG_HEADS - 1) / QG_HEADS;
+    const int groups = qg + 2 * kg;
+    const long long wglobal = ((long long)blockIdx.x * blockDim.x + threadIdx.x) >> 5;
+    const int lane = threadIdx.x & 31;
+    if (wglobal >= (long long)n_tokens * groups) return;
+    const int t = (int)(wglobal / groups), g = (int)(wglobal % groups);
+    const int heads = QH + 2 * KH;
+    const int slot = kv_slot ? kv_slot[t] : -1;
+    const int page = slot >= 0 ? slot / page_size : 0, off = slot >= 0 ? slot % page_size : 0;
+    const bf16* row = qkv + (size_t)t * heads * d;
+    if (g >= qg + kg) {                                            // values: copied as they are
+        if (slot < 0) return;
+        const int h0 = (g - qg - kg) * QG_HEADS, nh = min(QG_HEADS, KH - h0);
+        const int per = d / 8;                                     // 16-byte pieces of a head
+        for (int i = lane; i < nh * per; i += 32) {
+            const int hh = h0 + i / per, c = i % per;
+            bf16* dst = cache + ((((size_t)page * 2 + 1) * KH + hh) * page_size + off) * d;
+            reinterpret_cast<uint4*>(dst)[c] = reinterpret_cast<const uint4*>(row + (size_t)(QH + KH + hh) * d)[c];
+        }
+        return;
+    }
+    const bool is_q = g < qg;
+    if (!is_q && slot < 0) return;
+    const int h0 = is_q ? g * QG_HEADS : (g - qg) * QG_HEADS;
+    const int nh = min(QG_HEADS, (is_q ? QH : KH) - h0);
+    const TW* w = is_q ? qw : kw;
+    const int half = d >> 1, n_it = half / 64;
+    float wa0[2], wa1[2], wb0[2], wb1[2], c0[2], s0[2], c1[2], s1[2];
+    const float pos = (float)positions[t];
+#pragma unroll
+    for (int i = 0; i < 2; ++i) {
+        wa0[i] = wa1[i] = wb0[i] = wb1[i] = 1.0f; c0[i] = c1[i] = 1.0f; s0[i] = s1[i] = 0.0f;
+        if (i < n_it) {
+            const int p = 2 * lane + 64 * i;
+            if (w) { wa0[i] = to_f32(w[p]); wa1[i] = to_f32(w[p + 1]); wb0[i] = to_f32(w[p + half]); wb1[i] = to_f32(w[p + half + 1]); }
+            if (cs_table) {
+                const float4 v = *reinterpret_cast<const float4*>(cs_table + (size_t)t * half + p);
+                c0[i] = v.x; s0[i] = v.y; c1[i] = v.z; s1[i] = v.w;
+            } else {
+                sincosf(pos * inv_freq[p], &s0[i], &c0[i]);
+                sincosf(pos * inv_freq[p + 1], &s1[i], &c1[i]);
+            }
+        }
+    }
+    const bf16* src0 = row + (size_t)((is_q ? 0 : QH) + h0) * d;
+    float2 lo[QG_HEADS][2], hi[QG_HEADS][2];
+#pragma unroll
+    for (int j = 0; j < QG_HEADS; ++j) {
+#pragma unroll
+        for (int i = 0; i < 2; ++i) {
+            lo[j][i] = hi[j][i] = make_float2(0.f, 0.f);
+            if (j < nh && i < n_it) {
+                const int p = 2 * lane + 64 * i;
+                lo[j][i] = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(src0 + (size_t)j * d + p));
+                hi[j][i] = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(src0 + (size_t)j * d + p + half));
+            }
+        }
+    }
+#pragma unroll
+    for (int j = 0; j < QG_HEADS; ++j) {
+        if (j >= nh) break;
+        float rstd = 1.0f;
+        if (w) {
+            float ss = 0.0f;
+#pragma unroll
+            for (int i = 0; i < 2; ++i)
+                ss += lo[j][i].x * lo[j][i].x + lo[j][i].y * lo[j][i].y + hi[j][i].x * hi[j][i].x + hi[j][i].y * hi[j][i].y;
+            ss = warp_sum(ss);
+            rstd = 1.0f / sqrtf(ss / (float)d + eps);
+        }
+        bf16* dst = is_q ? q_out + ((size_t)t * QH + h0 + j) * d
+                         : cache + ((((size_t)page * 2 + 0) * KH + h0 + j) * page_size + off) * d;
+#pragma unroll
+        for (int i = 0; i < 2; ++i) {
+            if (i < n_it) {
+                const int p = 2 * lane + 64 * i;
+                float x0 = lo[j][i].x, x1 = lo[j][i].y, y0 = hi[j][i].x, y1 = hi[j][i].y;
+                if (w) { x0 = x0 * rstd * wa0[i]; x1 = x1 * rstd * wa1[i]; y0 = y0 * rstd * wb0[i]; y1 = y1 * rstd * wb1[i]; }
+                *reinterpret_cast<__nv_bfloat162*>(dst + p) = __floats2bfloat162_rn(x0 * c0[i] - y0 * s0[i], x1 * c1[i] - y1 * s1[i]);
+                *reinterpret_cast<__nv_bfloat162*>(dst + p + half) = __floats2bfloat162_rn(x0 * s0[i] + y0 * c0[i], x1 * s1[i] + y1 * c1[i]);
+            }
+        }
+    }
+}
+
 extern "C" int rb_qknorm_rope_append(const void* qkv, int act_dtype, const void* qw, const void* kw, int w_dtype,
                                      const float* inv_freq, const void* cs_table, const int* positions, const int* kv_slot,
                                      void* q_out, void* k_out, void* cache, int cache_dtype,
@@ -532,8 +699,19 @@ extern "C" int rb_qknorm_rope_append(const void* qkv, int act_dtype, const void*
     cudaStream_t s = (cudaStream_t)stream;
     const long long warps = (long long)n_tokens * (QH + 2 * KH);
     const int blocks = rb_ceil_div(warps, 4);
-    if (act_dtype == RB_BF16 && !k_out && cache && KH > 0 && rot == d && d % 64 == 0 && d <= 512 &&
+    if (act_dtype == RB_BF16 && !k_out && cache && KH > 0 && rot == d && d % 128 == 0 && d <= 512 &&
         (((uintptr_t)qkv | (uintptr_t)q_out | (uintptr_t)cache) & 15) == 0) {
+        if (n_tokens > 64 && d <= 256) {                              // a prompt portion: a warp per token and group of heads
+            const long long gw = (long long)n_tokens * (rb_ceil_div(QH, QG_HEADS) + 2 * rb_ceil_div(KH, QG_HEADS));
+            const int gb = rb_ceil_div(gw, 4);
+            if (w_dtype == RB_F32)
+                return rb_launch(qknorm_rope_append_grouped_kernel<float>, dim3(gb), dim3(128), 0, s, (const bf16*)qkv, (const float*)qw,
+                                 (const float*)kw, inv_freq, (const float2*)cs_table, positions, kv_slot, (bf16*)q_out, (bf16*)cache,
+                                 n_tokens, QH, KH, d, page_size, eps);
+            return rb_launch(qknorm_rope_append_grouped_kernel<bf16>, dim3(gb), dim3(128), 0, s, (const bf16*)qkv, (const bf16*)qw,
+                             (const bf16*)kw, inv_freq, (const float2*)cs_table, positions, kv_slot, (bf16*)q_out, (bf16*)cache,
+                             n_tokens, QH, KH, d, page_size, eps);
+        }
         if (w_dtype == RB_F32)
             return rb_launch(qknorm_rope_append_vec_kernel<float>, dim3(blocks), dim3(128), 0, s, (const bf16*)qkv, (const float*)qw,
                              (const float*)kw, inv_freq, (const float2*)cs_table, positions, kv_slot, (bf16*)q_out, (bf16*)cache,

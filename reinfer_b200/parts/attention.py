@@ -85,7 +85,7 @@ class Attention(Mixer):
         if fused is not None:
             inv_freq, rot = fused
             cs = None
-            if rot == d and d % 64 == 0 and xn.dtype == torch.bfloat16 and inv_freq is not None and T > 64:
+            if rot == d and d % 128 == 0 and xn.dtype == torch.bfloat16 and inv_freq is not None and T > 64:
                 # the angles depend on the step's positions only: for a large step the first layer tabulates
                 # their cosines and sines (a small step computes them in place and saves the launch)
                 key = ("rope", getattr(self.position, "theta", None), rot, inv_freq.numel())    # the same for every layer

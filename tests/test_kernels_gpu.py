@@ -234,6 +234,26 @@ def test_rmsnorm_and_residual(h, rows, out_dtype, w_dtype):
     assert torch.allclose(x3, x + delta.float(), atol=1e-6)
 
 
+@pytest.mark.parametrize("h,rows", [(64, 65), (1000, 70), (4096, 100), (5120, 65), (8192, 66), (12288, 65)])
+@pytest.mark.parametrize("w_dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("n_delta", [0, 1, 3])
+def test_rmsnorm_many_rows(h, rows, w_dtype, n_delta):
+    """A prompt portion's rows of 16-bit activations (the vectorised kernel up to 8192 columns, the scalar one beyond)."""
+    from reinfer_b200 import ops
+    eps = 1e-6
+    base, w = rnd(rows, h, scale=3.0, seed=1), (1 + rnd(h, scale=0.1, seed=2)).to(w_dtype)
+    delta = rnd(n_delta, rows, h, seed=3) if n_delta else None
+    x = base.clone()
+    out = torch.empty(rows, h, dtype=torch.bfloat16, device=DEV)
+    ops.add_rmsnorm(x, delta if n_delta != 1 else delta[0], w, out, eps)
+    want_x = base.clone()
+    for k in range(n_delta):
+        want_x += delta[k]
+    assert torch.equal(x, want_x)
+    want = want_x * torch.rsqrt((want_x * want_x).mean(-1, keepdim=True) + eps) * w.float()
+    assert (out.float() - want).abs().max().item() <= 1e-2 * want.abs().max().item()
+
+
 def test_embedding_gather():
     from reinfer_b200 import ops
     for dtype in (torch.float32, torch.bfloat16):
@@ -255,7 +275,7 @@ def _rope_ref(x, pos, theta, rot):
 
 
 @pytest.mark.parametrize("QH,KH,d,rot,page", [(4, 2, 16, 16, 16), (6, 2, 32, 32, 8), (3, 1, 80, 48, 4), (8, 8, 128, 128, 16),
-                                              (5, 5, 256, 256, 32)])
+                                              (5, 5, 256, 256, 32), (4, 2, 64, 64, 16), (3, 3, 192, 192, 8), (2, 1, 384, 384, 16)])
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
 @pytest.mark.parametrize("norm", [True, False])
 def test_qknorm_rope_append(QH, KH, d, rot, page, dtype, norm):
@@ -290,13 +310,45 @@ def test_qknorm_rope_append(QH, KH, d, rot, page, dtype, norm):
         assert (flat[sl, 0].double() - k[t]).abs().max().item() <= tol * k.abs().max().item()
         assert torch.equal(flat[sl, 1], qkv.view(T, QH + 2 * KH, d)[t, QH + KH:])
     assert bool((flat[untouched.to(DEV)] == 7.0).all())                      # nothing else was written
-    if dtype == torch.bfloat16 and rot == d and d % 64 == 0:
+    if dtype == torch.bfloat16 and rot == d and d % 128 == 0:
         # the same with the step's table of cosines and sines: identical bits
         cache2 = torch.full_like(cache, 7.0)
         q2 = torch.empty_like(q_out)
         ops.qknorm_rope_append(qkv, qw, kw, rope.inv_freq, pos, slots, q2, cache2, QH, KH, d, rot, page, eps,
                                cs_table=ops.rope_table(pos, rope.inv_freq))
         assert torch.equal(q2, q_out) and torch.equal(cache2, cache)
+
+
+@pytest.mark.parametrize("QH,KH,d,page", [(8, 8, 128, 16), (32, 8, 128, 64), (5, 5, 256, 32), (12, 3, 64, 16), (9, 1, 128, 8)])
+@pytest.mark.parametrize("norm", [True, False])
+@pytest.mark.parametrize("table", [True, False])
+def test_qknorm_rope_append_many_tokens(QH, KH, d, page, norm, table):
+    """A prompt portion (more than 64 tokens) goes through the kernel that takes a token's heads in groups: the
+    same bits as the kernel that takes them one by one (run here in pieces of 64 tokens)."""
+    from reinfer_b200 import ops
+    from reinfer_b200.parts.rope import RotaryEncoding
+    T, eps, theta = 150, 1e-6, 1e6
+    pages = -(-T // page) + 2
+    qkv = rnd(T, (QH + 2 * KH) * d, dtype=torch.bfloat16, seed=4)
+    qw = (1 + rnd(d, scale=0.1, seed=5)) if norm else None
+    kw = (1 + rnd(d, scale=0.1, seed=6)) if norm else None
+    pos = (torch.arange(T, dtype=torch.int32) * 7 % 3000).to(DEV)
+    perm = torch.randperm(pages * page, generator=torch.Generator().manual_seed(1))[:T].to(torch.int32)
+    perm[5] = -1
+    slots = perm.to(DEV)
+    rope = RotaryEncoding(d, theta, d)
+    rope.prepare(DEV)
+    cs = ops.rope_table(pos, rope.inv_freq) if table else None
+    cache = torch.full((pages, 2, KH, page, d), 7.0, dtype=torch.bfloat16, device=DEV)
+    q_out = torch.empty(T, QH, d, dtype=torch.bfloat16, device=DEV)
+    ops.qknorm_rope_append(qkv, qw, kw, rope.inv_freq, pos, slots, q_out, cache, QH, KH, d, d, page, eps, cs_table=cs)
+    cache2 = torch.full_like(cache, 7.0)
+    q2 = torch.empty_like(q_out)
+    for a in range(0, T, 64):
+        b = min(T, a + 64)
+        ops.qknorm_rope_append(qkv[a:b], qw, kw, rope.inv_freq, pos[a:b], slots[a:b], q2[a:b], cache2, QH, KH, d, d, page, eps,
+                               cs_table=cs[a:b] if table else None)
+    assert torch.equal(q2, q_out) and torch.equal(cache2, cache)
 
 
 def test_kv_append_and_k_out_path():
