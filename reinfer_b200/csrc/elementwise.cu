@@ -585,102 +585,84 @@ __global__ void qknorm_rope_append_vec_kernel(const bf16* __restrict__ qkv, cons
     }
 }
 
-// The same for many tokens (a prompt portion): a warp takes one token and a group of up to QG_HEADS heads of one
-// kind (query, key or value), so that the token's slot, the cosines and sines and the norm's weights are fetched
-// once per group, and the loads of all its heads are in flight together.  head_dim is 128 * n_it, n_it <= 2 here.
-constexpr int QG_HEADS = 8;
+// The same for many tokens (a prompt portion) and heads of 128: a warp takes one token and a group of up to
+// QG_HEADS heads of one kind (query, key or value).  A lane owns four neighbouring elements of a head (one 8-byte
+// load and store per head); the partner of a rotation pair (p, p + 64) sits in lane ^ 16 and comes by shuffle.  The
+// token's slot, cosines, sines and the norm's weights are fetched once per group, and the loads of all its heads
+// are in flight together.
+constexpr int QG_HEADS = 4;
 template <typename TW>
 __global__ void __launch_bounds__(128)
-qknorm_rope_append_grouped_kernel(const bf16* __restrict__ qkv, const TW* __restrict__ qw, const TW* __restrict__ kw,
-                                  const float* __restrict__ inv_freq, const float2* __restrict__ cs_table,
-                                  const int* __restrict__ positions, const int* __restrict__ kv_slot,
-                                  bf16* __restrict__ q_out, bf16* __restrict__ cache,
-                                  int n_tokens, int QH, int KH, int d, int page_size, float eps) {
+qknorm_rope_append_d128_kernel(const bf16* __restrict__ qkv, const TW* __restrict__ qw, const TW* __restrict__ kw,
+                               const float* __restrict__ inv_freq, const float2* __restrict__ cs_table,
+                               const int* __restrict__ positions, const int* __restrict__ kv_slot,
+                               bf16* __restrict__ q_out, bf16* __restrict__ cache,
+                               int n_tokens, int QH, int KH, int page_size, float eps) {
     RB_TL(3);
     pdl_trigger(); pdl_wait();
     RB_TL_MARK();
+    constexpr int d = 128, half = 64;
     const int qg = (QH + QG_HEADS - 1) / QG_HEADS, kg = (KH + QG_HEADS - 1) / QG_HEADS;
     const int groups = qg + 2 * kg;
     const long long wglobal = ((long long)blockIdx.x * blockDim.x + threadIdx.x) >> 5;
     const int lane = threadIdx.x & 31;
     if (wglobal >= (long long)n_tokens * groups) return;
     const int t = (int)(wglobal / groups), g = (int)(wglobal % groups);
-    const int heads = QH + 2 * KH;
+    const int kind = g < qg ? 0 : (g < qg + kg ? 1 : 2);          // query, key, value
+    const int h0 = (kind == 0 ? g : kind == 1 ? g - qg : g - qg - kg) * QG_HEADS;
+    const int nh = min(QG_HEADS, (kind == 0 ? QH : KH) - h0);
+    const bf16* src0 = qkv + ((size_t)t * (QH + 2 * KH) + (kind == 0 ? 0 : kind == 1 ? QH : QH + KH) + h0) * d + 4 * lane;
+    // every load of the warp is independent of the others: all are issued before the first is used
+    uint2 raw[QG_HEADS];
+#pragma unroll
+    for (int j = 0; j < QG_HEADS; ++j) raw[j] = j < nh ? *reinterpret_cast<const uint2*>(src0 + (size_t)j * d) : make_uint2(0u, 0u);
     const int slot = kv_slot ? kv_slot[t] : -1;
+    const int p = (4 * lane) & (half - 1);                        // the pair index of this lane's first element
+    const TW* w = kind == 0 ? qw : kw;
+    float wv[4] = {1.f, 1.f, 1.f, 1.f}, c[4], sn[4];
+    if (kind != 2) {
+        if (w) {
+#pragma unroll
+            for (int i = 0; i < 4; ++i) wv[i] = to_f32(w[4 * lane + i]);
+        }
+        if (cs_table) {
+            const float4 a = *reinterpret_cast<const float4*>(cs_table + (size_t)t * half + p);
+            const float4 b = *reinterpret_cast<const float4*>(cs_table + (size_t)t * half + p + 2);
+            c[0] = a.x; sn[0] = a.y; c[1] = a.z; sn[1] = a.w; c[2] = b.x; sn[2] = b.y; c[3] = b.z; sn[3] = b.w;
+        } else {
+            const float pos = (float)positions[t];
+#pragma unroll
+            for (int i = 0; i < 4; ++i) sincosf(pos * inv_freq[p + i], &sn[i], &c[i]);
+        }
+    }
+    if (kind != 0 && slot < 0) return;
     const int page = slot >= 0 ? slot / page_size : 0, off = slot >= 0 ? slot % page_size : 0;
-    const bf16* row = qkv + (size_t)t * heads * d;
-    if (g >= qg + kg) {                                            // values: copied as they are
-        if (slot < 0) return;
-        const int h0 = (g - qg - kg) * QG_HEADS, nh = min(QG_HEADS, KH - h0);
-        const int per = d / 8;                                     // 16-byte pieces of a head
-        for (int i = lane; i < nh * per; i += 32) {
-            const int hh = h0 + i / per, c = i % per;
-            bf16* dst = cache + ((((size_t)page * 2 + 1) * KH + hh) * page_size + off) * d;
-            reinterpret_cast<uint4*>(dst)[c] = reinterpret_cast<const uint4*>(row + (size_t)(QH + KH + hh) * d)[c];
-        }
-        return;
-    }
-    const bool is_q = g < qg;
-    if (!is_q && slot < 0) return;
-    const int h0 = is_q ? g * QG_HEADS : (g - qg) * QG_HEADS;
-    const int nh = min(QG_HEADS, (is_q ? QH : KH) - h0);
-    const TW* w = is_q ? qw : kw;
-    const int half = d >> 1, n_it = half / 64;
-    float wa0[2], wa1[2], wb0[2], wb1[2], c0[2], s0[2], c1[2], s1[2];
-    const float pos = (float)positions[t];
-#pragma unroll
-    for (int i = 0; i < 2; ++i) {
-        wa0[i] = wa1[i] = wb0[i] = wb1[i] = 1.0f; c0[i] = c1[i] = 1.0f; s0[i] = s1[i] = 0.0f;
-        if (i < n_it) {
-            const int p = 2 * lane + 64 * i;
-            if (w) { wa0[i] = to_f32(w[p]); wa1[i] = to_f32(w[p + 1]); wb0[i] = to_f32(w[p + half]); wb1[i] = to_f32(w[p + half + 1]); }
-            if (cs_table) {
-                const float4 v = *reinterpret_cast<const float4*>(cs_table + (size_t)t * half + p);
-                c0[i] = v.x; s0[i] = v.y; c1[i] = v.z; s1[i] = v.w;
-            } else {
-                sincosf(pos * inv_freq[p], &s0[i], &c0[i]);
-                sincosf(pos * inv_freq[p + 1], &s1[i], &c1[i]);
-            }
-        }
-    }
-    const bf16* src0 = row + (size_t)((is_q ? 0 : QH) + h0) * d;
-    float2 lo[QG_HEADS][2], hi[QG_HEADS][2];
-#pragma unroll
-    for (int j = 0; j < QG_HEADS; ++j) {
-#pragma unroll
-        for (int i = 0; i < 2; ++i) {
-            lo[j][i] = hi[j][i] = make_float2(0.f, 0.f);
-            if (j < nh && i < n_it) {
-                const int p = 2 * lane + 64 * i;
-                lo[j][i] = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(src0 + (size_t)j * d + p));
-                hi[j][i] = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(src0 + (size_t)j * d + p + half));
-            }
-        }
-    }
+    // low half (lanes 0..15): x c - y s;  high half: y c + x s
 #pragma unroll
     for (int j = 0; j < QG_HEADS; ++j) {
         if (j >= nh) break;
-        float rstd = 1.0f;
+        bf16* dst = kind == 0 ? q_out + ((size_t)t * QH + h0 + j) * d
+                              : cache + ((((size_t)page * 2 + (kind == 2 ? 1 : 0)) * KH + h0 + j) * page_size + off) * d;
+        if (kind == 2) { *reinterpret_cast<uint2*>(dst + 4 * lane) = raw[j]; continue; }
+        const float2 v01 = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&raw[j].x));
+        const float2 v23 = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&raw[j].y));
+        float v[4] = {v01.x, v01.y, v23.x, v23.y};
         if (w) {
-            float ss = 0.0f;
+            const float ss = warp_sum(v[0] * v[0] + v[1] * v[1] + v[2] * v[2] + v[3] * v[3]);
+            const float rstd = 1.0f / sqrtf(ss / (float)d + eps);
 #pragma unroll
-            for (int i = 0; i < 2; ++i)
-                ss += lo[j][i].x * lo[j][i].x + lo[j][i].y * lo[j][i].y + hi[j][i].x * hi[j][i].x + hi[j][i].y * hi[j][i].y;
-            ss = warp_sum(ss);
-            rstd = 1.0f / sqrtf(ss / (float)d + eps);
+            for (int i = 0; i < 4; ++i) v[i] = v[i] * rstd * wv[i];
         }
-        bf16* dst = is_q ? q_out + ((size_t)t * QH + h0 + j) * d
-                         : cache + ((((size_t)page * 2 + 0) * KH + h0 + j) * page_size + off) * d;
+        float o[4];
 #pragma unroll
-        for (int i = 0; i < 2; ++i) {
-            if (i < n_it) {
-                const int p = 2 * lane + 64 * i;
-                float x0 = lo[j][i].x, x1 = lo[j][i].y, y0 = hi[j][i].x, y1 = hi[j][i].y;
-                if (w) { x0 = x0 * rstd * wa0[i]; x1 = x1 * rstd * wa1[i]; y0 = y0 * rstd * wb0[i]; y1 = y1 * rstd * wb1[i]; }
-                *reinterpret_cast<__nv_bfloat162*>(dst + p) = __floats2bfloat162_rn(x0 * c0[i] - y0 * s0[i], x1 * c1[i] - y1 * s1[i]);
-                *reinterpret_cast<__nv_bfloat162*>(dst + p + half) = __floats2bfloat162_rn(x0 * s0[i] + y0 * c0[i], x1 * s1[i] + y1 * c1[i]);
-            }
+        for (int i = 0; i < 4; ++i) {
+            const float other = __shfl_xor_sync(0xffffffffu, v[i], 16);
+            o[i] = lane < 16 ? v[i] * c[i] - other * sn[i] : other * sn[i] + v[i] * c[i];
         }
+        const __nv_bfloat162 lo = __floats2bfloat162_rn(o[0], o[1]), hi = __floats2bfloat162_rn(o[2], o[3]);
+        uint2 pk;
+        pk.x = *reinterpret_cast<const uint32_t*>(&lo); pk.y = *reinterpret_cast<const uint32_t*>(&hi);
+        *reinterpret_cast<uint2*>(dst + 4 * lane) = pk;
     }
 }
 
@@ -701,16 +683,16 @@ extern "C" int rb_qknorm_rope_append(const void* qkv, int act_dtype, const void*
     const int blocks = rb_ceil_div(warps, 4);
     if (act_dtype == RB_BF16 && !k_out && cache && KH > 0 && rot == d && d % 128 == 0 && d <= 512 &&
         (((uintptr_t)qkv | (uintptr_t)q_out | (uintptr_t)cache) & 15) == 0) {
-        if (n_tokens > 64 && d <= 256) {                              // a prompt portion: a warp per token and group of heads
+        if (n_tokens > 64 && d == 128) {                              // a prompt portion: a warp per token and group of heads
             const long long gw = (long long)n_tokens * (rb_ceil_div(QH, QG_HEADS) + 2 * rb_ceil_div(KH, QG_HEADS));
             const int gb = rb_ceil_div(gw, 4);
             if (w_dtype == RB_F32)
-                return rb_launch(qknorm_rope_append_grouped_kernel<float>, dim3(gb), dim3(128), 0, s, (const bf16*)qkv, (const float*)qw,
+                return rb_launch(qknorm_rope_append_d128_kernel<float>, dim3(gb), dim3(128), 0, s, (const bf16*)qkv, (const float*)qw,
                                  (const float*)kw, inv_freq, (const float2*)cs_table, positions, kv_slot, (bf16*)q_out, (bf16*)cache,
-                                 n_tokens, QH, KH, d, page_size, eps);
-            return rb_launch(qknorm_rope_append_grouped_kernel<bf16>, dim3(gb), dim3(128), 0, s, (const bf16*)qkv, (const bf16*)qw,
+                                 n_tokens, QH, KH, page_size, eps);
+            return rb_launch(qknorm_rope_append_d128_kernel<bf16>, dim3(gb), dim3(128), 0, s, (const bf16*)qkv, (const bf16*)qw,
                              (const bf16*)kw, inv_freq, (const float2*)cs_table, positions, kv_slot, (bf16*)q_out, (bf16*)cache,
-                             n_tokens, QH, KH, d, page_size, eps);
+                             n_tokens, QH, KH, page_size, eps);
         }
         if (w_dtype == RB_F32)
             return rb_launch(qknorm_rope_append_vec_kernel<float>, dim3(blocks), dim3(128), 0, s, (const bf16*)qkv, (const float*)qw,

@@ -319,12 +319,12 @@ def test_qknorm_rope_append(QH, KH, d, rot, page, dtype, norm):
         assert torch.equal(q2, q_out) and torch.equal(cache2, cache)
 
 
-@pytest.mark.parametrize("QH,KH,d,page", [(8, 8, 128, 16), (32, 8, 128, 64), (5, 5, 256, 32), (12, 3, 64, 16), (9, 1, 128, 8)])
+@pytest.mark.parametrize("QH,KH,d,page", [(8, 8, 128, 16), (32, 8, 128, 64), (5, 5, 256, 32), (12, 3, 64, 16), (9, 1, 128, 8), (6, 2, 128, 16)])
 @pytest.mark.parametrize("norm", [True, False])
 @pytest.mark.parametrize("table", [True, False])
 def test_qknorm_rope_append_many_tokens(QH, KH, d, page, norm, table):
-    """A prompt portion (more than 64 tokens) goes through the kernel that takes a token's heads in groups: the
-    same bits as the kernel that takes them one by one (run here in pieces of 64 tokens)."""
+    """A prompt portion (more than 64 tokens; heads of 128 go through the kernel that takes a token's heads in
+    groups) against the plain statement, with slots in a random order and one token that is not stored."""
     from reinfer_b200 import ops
     from reinfer_b200.parts.rope import RotaryEncoding
     T, eps, theta = 150, 1e-6, 1e6
@@ -342,13 +342,21 @@ def test_qknorm_rope_append_many_tokens(QH, KH, d, page, norm, table):
     cache = torch.full((pages, 2, KH, page, d), 7.0, dtype=torch.bfloat16, device=DEV)
     q_out = torch.empty(T, QH, d, dtype=torch.bfloat16, device=DEV)
     ops.qknorm_rope_append(qkv, qw, kw, rope.inv_freq, pos, slots, q_out, cache, QH, KH, d, d, page, eps, cs_table=cs)
-    cache2 = torch.full_like(cache, 7.0)
-    q2 = torch.empty_like(q_out)
-    for a in range(0, T, 64):
-        b = min(T, a + 64)
-        ops.qknorm_rope_append(qkv[a:b], qw, kw, rope.inv_freq, pos[a:b], slots[a:b], q2[a:b], cache2, QH, KH, d, d, page, eps,
-                               cs_table=cs[a:b] if table else None)
-    assert torch.equal(q2, q_out) and torch.equal(cache2, cache)
+    x = qkv.float().view(T, QH + 2 * KH, d)
+    q, k = x[:, :QH], x[:, QH:QH + KH]
+    if norm:
+        q = q * torch.rsqrt((q * q).mean(-1, keepdim=True) + eps) * qw
+        k = k * torch.rsqrt((k * k).mean(-1, keepdim=True) + eps) * kw
+    q, k = _rope_ref(q, pos, theta, d), _rope_ref(k, pos, theta, d)
+    assert (q_out.double() - q).abs().max().item() <= 2e-2 * q.abs().max().item()
+    flat = cache.permute(0, 3, 1, 2, 4).reshape(pages * page, 2, KH, d)     # [slot, kv, head, d]
+    stored = slots >= 0
+    sl = slots[stored].long()
+    assert (flat[sl, 0].double() - k[stored]).abs().max().item() <= 2e-2 * k.abs().max().item()
+    assert torch.equal(flat[sl, 1], qkv.view(T, QH + 2 * KH, d)[stored][:, QH + KH:])
+    untouched = torch.ones(pages * page, dtype=torch.bool, device=DEV)
+    untouched[sl] = False
+    assert bool((flat[untouched] == 7.0).all())                              # nothing else was written
 
 
 def test_kv_append_and_k_out_path():
