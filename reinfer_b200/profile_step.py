@@ -1,12 +1,18 @@
 """A few steps of a random-weight model for a profiler to look at:
 
-    python -m reinfer_b200.profile_step --mode decode|prefill --batch B --context N [--layers L] [--steps K]
+    python -m reinfer_b200.profile_step --mode decode|prefill|timeline --batch B --context N [--layers L] [--steps K]
 
 builds the Qwen3-8B shape (or fewer layers of it), fills B requests to N tokens, runs two
 warm-up steps, and brackets K steps of the chosen kind with cudaProfilerStart/Stop, so that
 `ncu --profile-from-start off` sees exactly those (the reference brackets its step with event
 profilers instead, crates/cuda/src/engine.rs:928-1408).  Decode steps are launched eagerly
 (no graph), so every kernel appears as its own launch.
+
+`--mode timeline` needs no profiler: it builds the kernels with -DRB_TIMELINE (every CTA records its start, the
+moment its wait for the kernels before it returned, and its end, by the global timer), replays ONE decode step
+through the CUDA graph as serving does - with programmatic dependent launch, so kernels overlap - after a
+flush of L2, and prints for every launch when its first CTA started, when its wait returned, when its last CTA
+ended, and by how much it moved the end of the step.
 """
 from __future__ import annotations
 
@@ -16,7 +22,7 @@ import sys
 
 def main(argv=None) -> int:
     ap = argparse.ArgumentParser(description=__doc__.split("\n\n")[0])
-    ap.add_argument("--mode", choices=["decode", "prefill"], default="decode")
+    ap.add_argument("--mode", choices=["decode", "prefill", "timeline"], default="decode")
     ap.add_argument("--batch", type=int, default=8)
     ap.add_argument("--context", type=int, default=4000)
     ap.add_argument("--layers", type=int, default=36)
@@ -24,6 +30,10 @@ def main(argv=None) -> int:
     ap.add_argument("--prefill-tokens", type=int, default=2048)
     a = ap.parse_args(argv)
 
+    if a.mode == "timeline":
+        from .csrc import build                   # the flag is part of the build key: a library of its own
+        if "-DRB_TIMELINE" not in build.FLAGS:
+            build.FLAGS.append("-DRB_TIMELINE")
     import torch
     from . import ops
     from .config import Qwen3Config
@@ -35,7 +45,7 @@ def main(argv=None) -> int:
         rms_norm_eps=1e-6, tie_word_embeddings=False, max_position_embeddings=40960))
     B, N = a.batch, a.context
     eng = Engine.from_config(cfg, seed=0, dtype="bfloat16", page_size=64, max_tokens=B * (N + 64) + 2 * a.prefill_tokens,
-                             max_num_seqs=B + 1, cuda_graphs=False)
+                             max_num_seqs=B + 1, cuda_graphs=a.mode == "timeline")
     g = torch.Generator().manual_seed(0)
     for b in range(B):
         toks = torch.randint(0, cfg.vocab_size, (N,), generator=g).tolist()
@@ -45,9 +55,11 @@ def main(argv=None) -> int:
     def decode():
         return eng.step([StepEntry(b, [5 + b], [0]) for b in range(B)])
 
-    for _ in range(2):
+    for _ in range(4 if a.mode == "timeline" else 2):
         decode()
     torch.cuda.synchronize()
+    if a.mode == "timeline":
+        return timeline(ops, torch, decode, B, N, a.layers)
     torch.cuda.profiler.start()
     for k in range(a.steps):
         if a.mode == "decode":
@@ -60,6 +72,58 @@ def main(argv=None) -> int:
     torch.cuda.profiler.stop()
     err = ops.kernel_error()
     print(f"profiled {a.steps} {a.mode} steps, batch {B}, context {N}, layers {a.layers}; kernel error word {err}")
+    return 0 if err == 0 else 1
+
+
+TIMELINE_NAMES = {2: "norm", 3: "qknorm_rope", 4: "fa_decode", 5: "merge", 6: "gemm", 7: "gemm_gated", 8: "gemm_persist",
+                  9: "gemm_gated_p", 10: "fa_prefill"}
+TIMELINE_SETTERS = ("rb_gemm_step_timeline", "rb_attn_step_timeline", "rb_elementwise_step_timeline")
+
+
+def timeline(ops, torch, decode, B, N, layers) -> int:
+    import ctypes
+    lib = ops.lib()
+    cap = 1 << 18
+    buf = torch.zeros(4 + cap * 4, dtype=torch.int64, device="cuda")
+    buf[1] = cap
+    flush = torch.empty(512 << 20, dtype=torch.uint8, device="cuda")
+    flush.zero_()
+    torch.cuda.synchronize()
+    for fn in TIMELINE_SETTERS:
+        getattr(lib, fn)(ctypes.c_void_p(buf.data_ptr()))
+    decode()
+    torch.cuda.synchronize()
+    for fn in TIMELINE_SETTERS:
+        getattr(lib, fn)(ctypes.c_void_p(0))
+    h = buf.cpu()
+    n = min(int(h[0]), cap)
+    rec = h[4:4 + n * 4].view(-1, 4)
+    ids, st, en, mk = (rec[:, 0] >> 32).tolist(), rec[:, 1].tolist(), rec[:, 2].tolist(), rec[:, 3].tolist()
+    # CTAs of one launch: a run (by start time) of records of one kernel whose starts lie before the run's end
+    launches = []
+    for i in sorted(range(n), key=lambda j: st[j]):
+        m = mk[i] or 1 << 62
+        if launches and launches[-1]["id"] == ids[i] and st[i] < launches[-1]["end"] + 200:
+            l = launches[-1]
+            l["end"] = max(l["end"], en[i]); l["n"] += 1; l["mark"] = min(l["mark"], m)
+        else:
+            launches.append(dict(id=ids[i], start=st[i], end=en[i], n=1, mark=m))
+    if not launches:
+        print("no records: the library was not built with -DRB_TIMELINE")
+        return 1
+    t0 = launches[0]["start"]
+    print(f"one decode step by graph replay: batch {B}, context {N}, {layers} layers; {n} CTAs in {len(launches)} launches; us since the first CTA")
+    print(f"{'kernel':12s} {'ctas':>5s} {'start':>9s} {'waited':>9s} {'end':>9s} {'moved the end by':>17s}")
+    prev_end, tot = t0, {}
+    for l in launches:
+        name = TIMELINE_NAMES.get(l["id"], str(l["id"]))
+        adv = max(0, l["end"] - prev_end)
+        prev_end = max(prev_end, l["end"])
+        tot[name] = tot.get(name, 0) + adv
+        waited = (l["mark"] - t0) / 1e3 if l["mark"] < 1 << 62 else float("nan")
+        print(f"{name:12s} {l['n']:5d} {(l['start'] - t0) / 1e3:9.2f} {waited:9.2f} {(l['end'] - t0) / 1e3:9.2f} {adv / 1e3:17.2f}")
+    print("the step's end moved, by kernel (us):", {k: round(v / 1e3, 1) for k, v in tot.items()}, "total", round((prev_end - t0) / 1e3, 1))
+    err = ops.kernel_error()
     return 0 if err == 0 else 1
 
 
