@@ -19,6 +19,7 @@
 // the request's own keys and values ever reaches the arithmetic.
 // Needs a page size that is a power of two >= 8 and head_dim % 8 == 0 (else fa_decode_kernel).
 #include "sm100.cuh"
+#include <stdlib.h>
 
 #define FT_WARPS 4
 #define FT_THREADS 160                       // four consumer warps and one producer warp
@@ -38,6 +39,7 @@ struct FtArgs {
     float scale_log2;
     const void* next_w;                     // decode: a range to call into L2 once this CTA's tiles are requested
     long long next_bytes;
+    int cluster_merge;                      // decode: the CTAs of one (request, kv head) are a cluster and merge themselves
 };
 
 struct FtShared {
@@ -261,12 +263,94 @@ fa_decode_tma_kernel(const __grid_constant__ CUtensorMap map_kv, const FtArgs a)
         }
     }
     __syncthreads();
-    if (*abort_flag) {
+    const bool aborted = *abort_flag != 0;
+    if (aborted) {
         // copies that were issued but never consumed still write this CTA's shared memory: wait for them
         if (threadIdx.x == FT_WARPS * 32)
             for (int it = max(0, issued - NST); it < issued; ++it)
                 mbar_drain(smem_u32(&sh->full[it % NST]), (it / NST) & 1);
         __syncthreads();
+        if (!a.cluster_merge) return;
+    }
+    if (a.cluster_merge) {
+        // The splits of one (request, kv head) are the CTAs of a cluster (rank = split).  Each merges its four warps,
+        // then writes its result - dims [r*dq, (r+1)*dq) to CTA r, its log-sum-exp to all - straight into the
+        // receiving CTAs' shared memory; after one cluster barrier every CTA combines the parts that arrived for its
+        // own dims (ascending split order, as the merge kernel does) and stores them.  Every thread of every CTA
+        // reaches the barrier, whatever happened before; nobody reads remote memory after it.
+        float* recv_o = reinterpret_cast<float*>(sQ + HALVES * Q_HALF + 256);   // [split][Gc][dq], behind FtShared
+        float* recv_l = recv_o + 16 * D + 128;                                  // [split][16]
+        const int dq = (a.d + a.n_splits - 1) / a.n_splits;
+        if (!aborted && warp < FT_WARPS) {
+            if (threadIdx.x == 0)
+                l2_prefetch_share(a.next_w, a.next_bytes, (blockIdx.z * gridDim.y + blockIdx.y) * gridDim.x + blockIdx.x,
+                                  gridDim.x * gridDim.y * gridDim.z);
+#pragma unroll
+            for (int i = 0; i < 2; ++i) {
+                l[i] += __shfl_xor_sync(0xffffffffu, l[i], 1);
+                l[i] += __shfl_xor_sync(0xffffffffu, l[i], 2);
+            }
+            float* sO = reinterpret_cast<float*>(stages);          // [warp][16][D]: the ring is idle now
+            float* sM = sO + FT_WARPS * 16 * D;
+            float* sL = sM + FT_WARPS * 16;
+#pragma unroll
+            for (int j = 0; j < D / 8; ++j) {
+                const int dim = j * 8 + 2 * (lane & 3);
+                sO[(warp * 16 + row0) * D + dim] = o[j][0]; sO[(warp * 16 + row0) * D + dim + 1] = o[j][1];
+                sO[(warp * 16 + row0 + 8) * D + dim] = o[j][2]; sO[(warp * 16 + row0 + 8) * D + dim + 1] = o[j][3];
+            }
+            if ((lane & 3) == 0) {
+                sM[warp * 16 + row0] = m[0]; sM[warp * 16 + row0 + 8] = m[1];
+                sL[warp * 16 + row0] = l[0]; sL[warp * 16 + row0 + 8] = l[1];
+            }
+            asm volatile("bar.sync 1, %0;" ::"n"(FT_WARPS * 32) : "memory");
+            for (int i = threadIdx.x; i < a.Gc * a.d; i += FT_WARPS * 32) {
+                const int row = i / a.d, dim = i % a.d;
+                float M = -INFINITY;
+#pragma unroll
+                for (int w = 0; w < FT_WARPS; ++w) M = fmaxf(M, sM[w * 16 + row]);
+                float L = 0.0f, O = 0.0f;
+                if (M > -INFINITY) {
+#pragma unroll
+                    for (int w = 0; w < FT_WARPS; ++w) {
+                        const float f = exp2f(sM[w * 16 + row] - M);
+                        L += sL[w * 16 + row] * f;
+                        O += sO[(w * 16 + row) * D + dim] * f;
+                    }
+                }
+                const float val = L > 0.0f ? O / L : 0.0f;
+                const int owner = dim / dq, dl = dim - owner * dq;
+                uint32_t remote;
+                asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(remote)
+                             : "r"(smem_u32(recv_o + (split * a.Gc + row) * dq + dl)), "r"((uint32_t)owner));
+                asm volatile("st.shared::cluster.f32 [%0], %1;" ::"r"(remote), "f"(val) : "memory");
+                if (dim < a.n_splits) {                            // (d >= n_splits) this row's log-sum-exp, to CTA `dim`
+                    const float lse = L > 0.0f ? M + log2f(L) : -INFINITY;
+                    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(remote)
+                                 : "r"(smem_u32(recv_l + split * 16 + row)), "r"((uint32_t)dim));
+                    asm volatile("st.shared::cluster.f32 [%0], %1;" ::"r"(remote), "f"(lse) : "memory");
+                }
+            }
+        }
+        __syncwarp();
+        asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+        if (aborted || warp == FT_WARPS) return;
+        for (int i = threadIdx.x; i < a.Gc * dq; i += FT_WARPS * 32) {
+            const int row = i / dq, dl = i - row * dq;
+            const int dim = split * dq + dl;
+            if (dim >= a.d) continue;
+            float M = -INFINITY;
+            for (int s2 = 0; s2 < a.n_splits; ++s2) M = fmaxf(M, recv_l[s2 * 16 + row]);
+            float W = 0.0f, O = 0.0f;
+            if (M > -INFINITY) {
+                for (int s2 = 0; s2 < a.n_splits; ++s2) {
+                    const float w = exp2f(recv_l[s2 * 16 + row] - M);
+                    W += w;
+                    O += w * recv_o[(s2 * a.Gc + row) * dq + dl];
+                }
+            }
+            a.out[((size_t)tok * a.QH + head0 + row) * a.d + dim] = __float2bfloat16_rn(W > 0.0f ? O / W : 0.0f);
+        }
         return;
     }
     if (warp == FT_WARPS) return;                              // the producer has no part in the merge
@@ -569,6 +653,7 @@ fa_prefill_tma_kernel(const __grid_constant__ CUtensorMap map_kv, const FtArgs a
 }
 
 // out[t, h, :] = sum_s w_s o_s / sum_s w_s,  w_s = 2^(lse_s - max lse), splits in ascending order
+constexpr int FT_MERGE_UNROLL = 16;
 __global__ void ft_merge_kernel(const float* __restrict__ part_o, const float* __restrict__ part_lse, bf16* __restrict__ out,
                                 int first_tok, int QH, int d, int n_splits) {
     RB_TL(5);
@@ -577,22 +662,22 @@ __global__ void ft_merge_kernel(const float* __restrict__ part_o, const float* _
     const int t = blockIdx.x, h = blockIdx.y;
     const size_t base = ((size_t)t * QH + h) * n_splits;
     bf16* orow = out + ((size_t)(first_tok + t) * QH + h) * d;
-    if (n_splits <= 8) {
+    if (n_splits <= FT_MERGE_UNROLL) {
         // the usual case: every load of a thread is issued before the first is used (one trip to L2, not two)
         for (int dim = threadIdx.x; dim < d; dim += blockDim.x) {
-            float l[8], o[8];
+            float l[FT_MERGE_UNROLL], o[FT_MERGE_UNROLL];
 #pragma unroll
-            for (int s = 0; s < 8; ++s) {
+            for (int s = 0; s < FT_MERGE_UNROLL; ++s) {
                 l[s] = s < n_splits ? part_lse[base + s] : -INFINITY;
                 o[s] = s < n_splits ? part_o[(base + s) * d + dim] : 0.0f;
             }
             float M = -INFINITY;
 #pragma unroll
-            for (int s = 0; s < 8; ++s) M = fmaxf(M, l[s]);
+            for (int s = 0; s < FT_MERGE_UNROLL; ++s) M = fmaxf(M, l[s]);
             float W = 0.0f, O = 0.0f;
             if (M > -INFINITY) {
 #pragma unroll
-                for (int s = 0; s < 8; ++s) {
+                for (int s = 0; s < FT_MERGE_UNROLL; ++s) {
                     if (s < n_splits) {
                         const float w = exp2f(l[s] - M);
                         W += w;
@@ -624,15 +709,19 @@ static int ft_launch(const CUtensorMap& map, const FtArgs& a, cudaStream_t s) {
     constexpr size_t pipe = (size_t)NST * 2 * HALVES * FT_HALF_BYTES;
     constexpr size_t merge = (size_t)FT_WARPS * 16 * (HALVES * 64 + 2) * sizeof(float);
     static_assert(merge <= pipe, "the merge buffers reuse the stages");
-    constexpr size_t smem = pipe + HALVES * 16 * 128 + sizeof(FtShared) + 1024;
+    static_assert(sizeof(FtShared) <= 256, "the cluster's receive buffers start 256 bytes behind the barriers");
+    // stages, Q, barriers, and what the other splits of a cluster send: [split][Gc][dq] results + [split][16] log-sum-exps
+    constexpr size_t smem = pipe + HALVES * 16 * 128 + 256 + (size_t)(16 * HALVES * 64 + 128 + 8 * 16) * sizeof(float) + 1024;
     static bool done = false;
     if (!done) {
         cudaError_t e = cudaFuncSetAttribute(fa_decode_tma_kernel<HALVES, NST>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         if (e != cudaSuccess) return (int)e;
         done = true;
     }
-    return rb_launch(fa_decode_tma_kernel<HALVES, NST>, dim3(a.n_entries, a.KH * a.chunks, a.n_splits), dim3(FT_THREADS), smem, s,
-                     map, a);
+    const dim3 grid(a.n_entries, a.KH * a.chunks, a.n_splits);
+    if (a.cluster_merge)
+        return rb_launch_cluster(fa_decode_tma_kernel<HALVES, NST>, grid, dim3(FT_THREADS), dim3(1, 1, a.n_splits), smem, s, map, a);
+    return rb_launch(fa_decode_tma_kernel<HALVES, NST>, grid, dim3(FT_THREADS), smem, s, map, a);
 }
 
 // As rb_fa_decode, with `cache` the layer's [num_pages, 2, KH, page_size, d] array described to TMA.
@@ -648,7 +737,10 @@ extern "C" int rb_fa_decode_tma(const void* q, const void* cache, long long num_
     for (int s = 3; s < 16; ++s) if ((1 << s) == page_size) shift = s;
     if (shift < 0) RB_REFUSE("attention (TMA): page size %d is not a power of two >= 8", page_size);
     if (n_splits < 1 || n_splits > 65535) RB_REFUSE("attention: %d splits", n_splits);
-    if (n_splits > 1 && (!part_o || !part_lse)) RB_REFUSE("attention: split decoding needs its scratch");
+    // up to 8 splits are the CTAs of a cluster, which merge their results themselves; more go through scratch and a merge kernel
+    static const char* cl_env = getenv("REINFER_B200_ATTN_CLUSTER");                // "0": always the merge kernel (for comparison)
+    const bool cluster_merge = n_splits >= 2 && n_splits <= 8 && !(cl_env && cl_env[0] == '0') && part_o == nullptr;
+    if (n_splits > 1 && !cluster_merge && (!part_o || !part_lse)) RB_REFUSE("attention: decoding in %d splits needs its scratch", n_splits);
     if (((uintptr_t)cache & 15) || ((uintptr_t)q & 15)) RB_REFUSE("attention (TMA): operands must be 16-byte aligned");
     FtArgs a{};
     a.q = (const bf16*)q; a.block_table = block_table; a.cu_q = cu_q; a.kv_len = kv_len; a.out = (bf16*)out;
@@ -660,6 +752,7 @@ extern "C" int rb_fa_decode_tma(const void* q, const void* cache, long long num_
     a.chunks = G / a.Gc; a.first_entry = first_entry; a.n_entries = n_entries; a.n_splits = n_splits;
     a.scale_log2 = scale * 1.4426950408889634f;
     a.next_w = next_w; a.next_bytes = next_bytes;
+    a.cluster_merge = cluster_merge ? 1 : 0;
     CUtensorMap map;
     const int box_rows = page_size < FT_BN ? page_size : FT_BN;
     if (rb_tensor_map_bf16(cache, num_pages * 2LL * KH * page_size, d, d, box_rows, &map)) return -1;
@@ -668,7 +761,7 @@ extern "C" int rb_fa_decode_tma(const void* q, const void* cache, long long num_
     if (d <= 64) rc = ft_launch<1, 4>(map, a, s);
     else if (d <= 128) rc = ft_launch<2, 3>(map, a, s);
     else rc = ft_launch<4, 2>(map, a, s);
-    if (rc || n_splits == 1) return rc;
+    if (rc || n_splits == 1 || cluster_merge) return rc;
     return rb_launch(ft_merge_kernel, dim3(n_entries, QH), dim3(128), 0, s, (const float*)part_o, (const float*)part_lse,
                      (bf16*)out, first_tok, QH, d, n_splits);
 }

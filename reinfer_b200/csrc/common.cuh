@@ -116,14 +116,14 @@ static inline int rb_launch(void (*kernel)(KArgs...), dim3 grid, dim3 block, siz
     return (int)cudaGetLastError();
 }
 
-// The same for a grid whose CTAs form clusters of cluster_x along x (grid.x a multiple of it).
+// The same for a grid whose CTAs form clusters of the given shape (every grid dimension a multiple of the cluster's).
 template <typename... KArgs, typename... Args>
-static inline int rb_launch_cluster(void (*kernel)(KArgs...), dim3 grid, dim3 block, int cluster_x, size_t smem, cudaStream_t s, Args&&... args) {
+static inline int rb_launch_cluster(void (*kernel)(KArgs...), dim3 grid, dim3 block, dim3 cluster, size_t smem, cudaStream_t s, Args&&... args) {
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = grid; cfg.blockDim = block; cfg.dynamicSmemBytes = smem; cfg.stream = s;
     cudaLaunchAttribute attr[2];
     attr[0].id = cudaLaunchAttributeClusterDimension;
-    attr[0].val.clusterDim.x = cluster_x; attr[0].val.clusterDim.y = 1; attr[0].val.clusterDim.z = 1;
+    attr[0].val.clusterDim.x = cluster.x; attr[0].val.clusterDim.y = cluster.y; attr[0].val.clusterDim.z = cluster.z;
     attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
     attr[1].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = attr;

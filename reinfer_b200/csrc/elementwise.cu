@@ -355,10 +355,10 @@ extern "C" int rb_add_rmsnorm(float* x, const void* delta, int delta_dtype, int 
     if (out_dtype == RB_BF16 && dd == RB_F32 && delta && n_delta > 1 && rows <= 64 && h % (4 * RN_CL) == 0 && h / RN_CL <= RN_THREADS * 4 * RN_VPER &&
         ((((uintptr_t)x | (uintptr_t)delta) & 15) == 0) && (((uintptr_t)out) & 7) == 0 && delta_stride % 4 == 0) {
         if (w_dtype == RB_F32)
-            return rb_launch_cluster(add_rmsnorm_cluster_kernel<float>, dim3(RN_CL, rows), dim3(RN_THREADS), RN_CL, 0, s, x,
+            return rb_launch_cluster(add_rmsnorm_cluster_kernel<float>, dim3(RN_CL, rows), dim3(RN_THREADS), dim3(RN_CL, 1, 1), 0, s, x,
                                      (const float*)delta, n_delta, delta_stride, (const float*)w, (bf16*)out, row_idx, h, eps);
         if (w_dtype == RB_BF16)
-            return rb_launch_cluster(add_rmsnorm_cluster_kernel<bf16>, dim3(RN_CL, rows), dim3(RN_THREADS), RN_CL, 0, s, x,
+            return rb_launch_cluster(add_rmsnorm_cluster_kernel<bf16>, dim3(RN_CL, rows), dim3(RN_THREADS), dim3(RN_CL, 1, 1), 0, s, x,
                                      (const float*)delta, n_delta, delta_stride, (const bf16*)w, (bf16*)out, row_idx, h, eps);
     }
     if (out_dtype == RB_BF16 && dd == RB_F32 && !row_idx && rows > 64 && h % 4 == 0 && h <= RV_THREADS * 4 * 8 &&

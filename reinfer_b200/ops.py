@@ -319,11 +319,19 @@ def _next_range(t: Optional[torch.Tensor], marker: int = 0):
     return c_void_p(nxt[0]), c_longlong(min(nxt[1], L2_PREFETCH_BYTES))
 
 
+DECODE_SLOTS = 296                          # CTAs of the decode attention that are resident at once (two per SM)
+
+
 def fa_decode_tma(q, cache, block_table, cu_q, kv_len, out, first_entry: int, n_entries: int, first_tok: int, n_splits: int,
                   QH: int, KH: int, d: int, page_size: int, window: int, scale: float) -> None:
-    """Split-K flash decoding with the key/value tiles brought in by TMA (page size a power of two >= 8)."""
+    """Split-K flash decoding with the key/value tiles brought in by TMA (page size a power of two >= 8).
+    Up to 8 splits whose CTAs are all resident at once form clusters that merge their results themselves (no scratch,
+    no merge kernel); several waves of CTAs, or more splits, go through scratch and the merge kernel (clusters
+    that wait for a free place on one GPC were measured slower there)."""
     part_o = part_lse = None
-    if n_splits > 1:
+    ctas = n_entries * KH * (QH // KH // fa_group_chunk(QH // KH)) * n_splits
+    in_kernel = ATTN_CLUSTER_MERGE and 2 <= n_splits <= 8 and ctas <= DECODE_SLOTS
+    if n_splits > 1 and not in_kernel:
         part_o = torch.empty(n_entries * QH * n_splits * d, dtype=torch.float32, device=q.device)
         part_lse = torch.empty(n_entries * QH * n_splits, dtype=torch.float32, device=q.device)
     nw, nb = _next_range(None, marker=cache.data_ptr())
@@ -355,7 +363,8 @@ def fa_prefill(q, cache, block_table, cu_q, kv_len, out, first_entry: int, n_ent
 
 
 USE_TMA_ATTENTION = os.environ.get("REINFER_B200_TMA_ATTENTION", "1") != "0"
-def decode_splits(ctas: int, tiles: int, slots: int = 296) -> int:
+ATTN_CLUSTER_MERGE = os.environ.get("REINFER_B200_ATTN_CLUSTER", "1") != "0"
+def decode_splits(ctas: int, tiles: int, slots: int = DECODE_SLOTS) -> int:
     """How many CTAs share one (request, kv head)'s keys.  Model of the launch's time: waves of
     `slots` resident CTAs, each CTA walking tiles/n tiles plus about 2.5 tile-times of fill, drain
     and merge, then a merge kernel that walks the n partial results; the split count with the

@@ -499,6 +499,30 @@ def test_flash_prefill_and_decode_against_plain(QH, KH, d, page, window):
         assert err <= 1.5e-2, f"splits {n_splits}: error {err:.3e}"
 
 
+@pytest.mark.parametrize("QH,KH,d,page", [(32, 8, 128, 64), (8, 1, 128, 16), (14, 2, 64, 8), (3, 1, 256, 64), (5, 5, 80, 32)])
+@pytest.mark.parametrize("n_splits", [2, 3, 4, 7, 8])
+def test_flash_decode_merge_inside_the_cluster_and_by_kernel_agree(QH, KH, d, page, n_splits, monkeypatch):
+    """Up to 8 splits merge inside a cluster of CTAs, or go through scratch and the merge kernel: both add the
+    parts in ascending order with the same formulas, so the results have the same bits (requests shorter than
+    the splits, and one of a single key, included)."""
+    from reinfer_b200 import ops
+    lens = [1, 37, 64, 300, 2000, 131]
+    s = paged_setup(lens, [1] * len(lens), QH, KH, d, page, torch.bfloat16, seed=5)
+    cu_q = torch.arange(len(lens) + 1, dtype=torch.int32, device=DEV)
+    kv_len = torch.tensor(lens, dtype=torch.int32, device=DEV)
+    outs = []
+    for in_kernel in (True, False):
+        monkeypatch.setattr(ops, "ATTN_CLUSTER_MERGE", in_kernel)
+        out = torch.full_like(s["q"], float("nan"))
+        ops.fa_decode_tma(s["q"], s["cache"], s["bt"], cu_q, kv_len, out, 0, len(lens), 0, n_splits, QH, KH, d, page, 0, 0.9 / math.sqrt(d))
+        assert ops.kernel_error() == 0
+        outs.append(out)
+    assert not torch.isnan(outs[0].float()).any()
+    assert torch.equal(outs[0], outs[1])
+    ref = attention_truth(s, QH, KH, 0, 0.9 / math.sqrt(d))
+    assert (outs[0].double().cpu() - ref).abs().max().item() <= 1.5e-2 * ref.abs().max().item()
+
+
 def test_flash_decode_finds_one_far_key_across_splits():
     from reinfer_b200 import ops
     QH, KH, d, page = 8, 2, 64, 16
