@@ -1,0 +1,399 @@
+// Paged causal flash attention for prompt portions on the fifth-generation tensor cores.
+//
+// The formulas are the reference's attention (crates/cuda/kernels/dense_kernels.cu:173-231: scores, causal
+// mask, softmax in float, weighted sum of the values), tiled as flash attention: a CTA owns 128 rows
+// (128 / Gc tokens x the Gc grouped query heads of one kv head) and walks the request's keys in tiles of 64.
+// For every tile
+//     S = Q K^T          tcgen05.mma, 128 x 64 x 128, operands in shared memory, S in tensor memory
+//     P = exp2(S - max)  128 threads, one row each (tcgen05.ld gives a thread its whole row: the row maximum
+//                        and sum need no shuffles), P rounded to bfloat16 into shared memory
+//     O += P V           tcgen05.mma, 128 x 128 x 64, into a second tensor-memory accumulator that the same
+//                        threads read back and add to their row of O in registers (scaled by the maximum's change)
+// Warp 0 feeds key/value tiles by TMA exactly as the mma.sync kernels do (one box per page, key/value and
+// 64-column half onto a full/empty mbarrier ring); warp 1 allocates tensor memory and issues the MMAs;
+// warps 2-5 are the softmax rows.  Both MMA operands must be K-major here: Q [rows][d] and K [keys][d] are,
+// P [rows][keys] is written so, and V [keys][d] is turned into V^T [d][keys] in shared memory by the softmax
+// warps (ldmatrix.trans + stmatrix, 8 x 8 blocks) while the tensor core computes S.
+//
+// Head size 128, page size a power of two >= 8.  Every wait is bounded (2 s); a CTA that gives up raises the
+// error word, lets its copies land, frees its tensor memory and leaves.
+#include "sm100.cuh"
+#include <stdlib.h>
+
+#define FC_BN 64                              // keys per tile
+#define FC_ROWS 128                           // query rows per CTA
+#define FC_D 128
+#define FC_THREADS 192                        // TMA warp, MMA warp, four softmax warps
+#define FC_NST 3
+#define FC_KHALF (FC_BN * 128)                // 64 keys x 128 bytes: one 64-column half of a key (or value) tile
+#define FC_KV_BYTES (2 * FC_KHALF)            // a key tile: two halves
+#define FC_STAGE (2 * FC_KV_BYTES)            // keys and values
+#define FC_QHALF (FC_ROWS * 128)              // 128 rows x 128 bytes
+#define FC_TMEM_COLS 256                      // S: columns 0..63, P V: columns 64..191
+
+struct FcArgs {
+    const bf16* q;
+    const int* block_table;
+    const int* cu_q;
+    const int* kv_len;
+    bf16* out;
+    int QH, KH, page_size, page_shift, max_pages, window;
+    int Gc, chunks, first_entry, n_entries;
+    float scale_log2;
+};
+
+struct FcShared {
+    unsigned long long full[FC_NST];
+    unsigned long long empty[FC_NST];
+    unsigned long long s_full, p_full, o_full;
+    uint32_t tmem_base;
+    int abort_flag;
+};
+
+// byte offset of 16-byte chunk c (8 elements) of row `row` in a K-major tile of 128-byte rows with the 128-byte
+// swizzle; chunks 8.. lie in the next 64-column half, half_bytes further
+__device__ __forceinline__ uint32_t fc_off(int row, int c, int half_bytes) {
+    return (uint32_t)((c >> 3) * half_bytes + row * 128 + (((c & 7) ^ (row & 7)) << 4));
+}
+__device__ __forceinline__ void fc_ldsm_x4_trans(uint32_t (&r)[4], uint32_t addr) {
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(addr));
+}
+__device__ __forceinline__ void fc_stsm_x4(uint32_t addr, const uint32_t (&r)[4]) {
+    asm volatile("stmatrix.sync.aligned.m8n8.x4.shared.b16 [%0], {%1,%2,%3,%4};"
+                 ::"r"(addr), "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]) : "memory");
+}
+__device__ __forceinline__ uint32_t fc_pack(float lo, float hi) {
+    const __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
+    return *reinterpret_cast<const uint32_t*>(&v);
+}
+
+__global__ void __launch_bounds__(FC_THREADS, 1)
+fa_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_kv, const FcArgs a) {
+    RB_TL(11);
+    extern __shared__ __align__(1024) unsigned char smem_raw[];
+    unsigned char* smem = (unsigned char*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+    unsigned char* stages = smem;                                  // [FC_NST][K half 0, K half 1, V half 0, V half 1]
+    unsigned char* sQ = stages + FC_NST * FC_STAGE;                // two halves of [128 rows][64 dims]
+    unsigned char* sP = sQ + 2 * FC_QHALF;                         // [128 rows][64 keys]
+    unsigned char* sVt = sP + FC_QHALF;                            // [128 dims][64 keys]
+    FcShared* sh = (FcShared*)(sVt + FC_QHALF);
+    const uint32_t stages_u = smem_u32(stages), sQ_u = smem_u32(sQ), sP_u = smem_u32(sP), sVt_u = smem_u32(sVt);
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    volatile int* abort_flag = &sh->abort_flag;
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < FC_NST; ++s) {
+            mbar_init(smem_u32(&sh->full[s]), 1);
+            mbar_init(smem_u32(&sh->empty[s]), 1 + FC_ROWS);       // the MMA warp's commit (keys) + the rows (values)
+        }
+        mbar_init(smem_u32(&sh->s_full), 1);
+        mbar_init(smem_u32(&sh->p_full), FC_ROWS);
+        mbar_init(smem_u32(&sh->o_full), 1);
+        sh->abort_flag = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (warp == 1) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&sh->tmem_base)), "r"(FC_TMEM_COLS) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    // shared memory starts at zero: rows that no copy fills are then finite
+    for (int i = threadIdx.x; i < (FC_NST * FC_STAGE + 4 * FC_QHALF) / 16; i += FC_THREADS)
+        reinterpret_cast<uint4*>(smem)[i] = make_uint4(0, 0, 0, 0);
+    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem = sh->tmem_base;
+    pdl_trigger();
+    pdl_wait();
+
+    // which rows: heavy tiles (late in a request: more keys) first
+    const int tpt = FC_ROWS / a.Gc;                                // tokens per CTA
+    int tile = (int)gridDim.x - 1 - (int)blockIdx.x, e = a.first_entry, q_len = 0;
+    for (; e < a.first_entry + a.n_entries; ++e) {
+        q_len = a.cu_q[e + 1] - a.cu_q[e];
+        const int nt = (q_len + tpt - 1) / tpt;
+        if (tile < nt) break;
+        tile -= nt;
+    }
+    const bool none = e >= a.first_entry + a.n_entries;            // uniform: a tile beyond the last entry
+    int n_tiles = 0, q0 = 0, n_tok = 0, kv_end = 0, start_pos = 0, tok_base = 0, t_begin = 0, head0 = 0, kh = 0;
+    const int* bt = a.block_table;
+    if (!none) {
+        q0 = tile * tpt;
+        n_tok = min(tpt, q_len - q0);
+        kh = blockIdx.y / a.chunks;
+        head0 = kh * (a.QH / a.KH) + (blockIdx.y % a.chunks) * a.Gc;
+        kv_end = a.kv_len[e];
+        start_pos = kv_end - q_len;
+        tok_base = a.cu_q[e] + q0;
+        bt = a.block_table + (size_t)e * a.max_pages;
+        const int pos_min = start_pos + q0, pos_max = start_pos + q0 + n_tok - 1;
+        const int lo_min = a.window > 0 ? max(0, pos_min - a.window + 1) : 0;
+        t_begin = lo_min / FC_BN;
+        n_tiles = pos_max / FC_BN + 1 - t_begin;
+        // Q rows (row r = token r / Gc, grouped head r % Gc) into the swizzled K-major layout
+        for (int i = threadIdx.x; i < n_tok * a.Gc * (FC_D / 8); i += FC_THREADS) {
+            const int row = i / (FC_D / 8), c = i % (FC_D / 8);
+            const uint4 v = *reinterpret_cast<const uint4*>(a.q + ((size_t)(tok_base + row / a.Gc) * a.QH + head0 + row % a.Gc) * FC_D + c * 8);
+            *reinterpret_cast<uint4*>(sQ + fc_off(row, c, FC_QHALF)) = v;
+        }
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+    }
+    __syncthreads();
+
+    int issued = 0;                                                // producer: tiles whose copies were issued
+    if (warp == 0) {
+        // ---- producer: runs ahead by up to FC_NST tiles; block-table entries 32 at a time -------------------
+        const int box_rows = min(a.page_size, FC_BN);
+        const int subs = FC_BN / box_rows;
+        const int rows_per_page2 = 2 * a.KH * a.page_size;         // matrix rows of one page (K and V, all heads)
+        int cached_first = 0, cached = -1;
+        bool have = false;
+        for (int it = 0; it < n_tiles; ++it) {
+            const int s = it % FC_NST;
+            const int k0 = (t_begin + it) * FC_BN;
+            const int pi0 = k0 >> a.page_shift;
+            const int need_last = (k0 + (subs - 1) * box_rows) >> a.page_shift;
+            if (!have || need_last >= cached_first + 32) {
+                cached_first = pi0;
+                cached = (pi0 + lane < a.max_pages) ? bt[pi0 + lane] : -1;
+                have = true;
+            }
+            int pages[8];
+            int n_valid = 0;
+#pragma unroll
+            for (int u = 0; u < 8; ++u) {
+                const int key = k0 + u * box_rows;
+                const int pg = __shfl_sync(0xffffffffu, cached, ((key >> a.page_shift) - cached_first) & 31);
+                pages[u] = (u < subs && key < kv_end) ? pg : -1;
+                n_valid += pages[u] >= 0;
+            }
+            bool ok = true;
+            if (lane == 0) {
+                if (it >= FC_NST) ok = mbar_wait(smem_u32(&sh->empty[s]), ((it / FC_NST) & 1) ^ 1, abort_flag, 11);
+                if (ok) {
+                    const uint32_t full = smem_u32(&sh->full[s]);
+                    mbar_expect_tx(full, (uint32_t)(n_valid * 4 * box_rows * 128));
+                    const uint32_t dst0 = stages_u + s * FC_STAGE;
+#pragma unroll
+                    for (int u = 0; u < 8; ++u) {
+                        if (pages[u] >= 0) {
+                            const int key = k0 + u * box_rows;
+                            const int y = pages[u] * rows_per_page2 + kh * a.page_size + (key & (a.page_size - 1));
+#pragma unroll
+                            for (int h = 0; h < 2; ++h) {
+                                tma_load_2d(dst0 + h * FC_KHALF + u * box_rows * 128, &map_kv, h * 64, y, full);
+                                tma_load_2d(dst0 + FC_KV_BYTES + h * FC_KHALF + u * box_rows * 128, &map_kv, h * 64,
+                                            y + a.KH * a.page_size, full);
+                            }
+                        }
+                    }
+                    issued = it + 1;
+                }
+            }
+            if (!__shfl_sync(0xffffffffu, (int)ok, 0)) break;
+        }
+    } else if (warp == 1) {
+        // ---- MMA issuer ----------------------------------------------------------------------------------------
+        if (lane == 0) {
+            constexpr uint32_t idesc_s = make_idesc(FC_BN), idesc_o = make_idesc(FC_D);
+            for (int it = 0; it < n_tiles; ++it) {
+                const int s = it % FC_NST;
+                if (!mbar_wait(smem_u32(&sh->full[s]), (it / FC_NST) & 1, abort_flag, 12)) break;
+                tc_fence_after();
+                // S = Q K^T: d = 128 is two 64-column halves of four 16-wide steps each
+                const uint32_t sK = stages_u + s * FC_STAGE;
+#pragma unroll
+                for (int h = 0; h < 2; ++h) {
+                    const uint64_t dq = make_smem_desc(sQ_u + h * FC_QHALF), dk = make_smem_desc(sK + h * FC_KHALF);
+#pragma unroll
+                    for (int k = 0; k < 4; ++k) tc_mma_bf16(tmem, dq + (uint64_t)(k * 2), dk + (uint64_t)(k * 2), idesc_s, (h | k) != 0);
+                }
+                tc_commit(smem_u32(&sh->s_full));
+                tc_commit(smem_u32(&sh->empty[s]));                // the keys of this stage are read once these MMAs are done
+                // O_tile = P V once the rows have written P and V^T
+                if (!mbar_wait(smem_u32(&sh->p_full), it & 1, abort_flag, 13)) break;
+                tc_fence_after();
+                const uint64_t dp = make_smem_desc(sP_u), dv = make_smem_desc(sVt_u);
+#pragma unroll
+                for (int k = 0; k < 4; ++k) tc_mma_bf16(tmem + FC_BN, dp + (uint64_t)(k * 2), dv + (uint64_t)(k * 2), idesc_o, k != 0);
+                tc_commit(smem_u32(&sh->o_full));
+            }
+        }
+    } else {
+        // ---- softmax rows: thread = row = tensor-memory lane -----------------------------------------------------
+        const int quad = warp & 3;                                 // the lanes this warp may read: 32 * (warp % 4) ..
+        const int row = quad * 32 + lane;
+        const int et = (warp - 2) * 32 + lane;                     // 0..127 among the softmax threads
+        const int ti = row / a.Gc;
+        const bool live = !none && ti < n_tok;
+        const int pos = live ? start_pos + q0 + ti : -1;
+        const int lo = a.window > 0 ? max(0, pos - a.window + 1) : 0;
+        float o[FC_D];
+#pragma unroll
+        for (int j = 0; j < FC_D; ++j) o[j] = 0.0f;
+        float m = -INFINITY, l = 0.0f;
+        const uint32_t lane_base = tmem + ((uint32_t)(quad * 32) << 16);
+        for (int it = 0; it < n_tiles; ++it) {
+            const int s = it % FC_NST;
+            if (!mbar_wait(smem_u32(&sh->full[s]), (it / FC_NST) & 1, abort_flag, 14)) break;
+            const int k0 = (t_begin + it) * FC_BN;
+            unsigned char* sV = stages + s * FC_STAGE + FC_KV_BYTES;
+            if (k0 + FC_BN > kv_end) {
+                // the request's last tile: slots of its last page beyond its length hold foreign data
+                for (int i = et; i < FC_BN * 16; i += FC_ROWS) {
+                    const int r = i / 16, c = i % 16;
+                    if (k0 + r >= kv_end) *reinterpret_cast<uint4*>(sV + fc_off(r, c, FC_KHALF)) = make_uint4(0, 0, 0, 0);
+                }
+                asm volatile("bar.sync 1, %0;" ::"n"(FC_ROWS) : "memory");
+            }
+            // V [keys][dims] -> V^T [dims][keys], 8 x 8 blocks: each warp takes 4 of the 16 dim-blocks, and per
+            // instruction the four key-blocks of half a tile
+            {
+                const uint32_t sV_u = stages_u + s * FC_STAGE + FC_KV_BYTES;
+#pragma unroll
+                for (int db = 0; db < 4; ++db) {
+                    const int dblk = (warp - 2) * 4 + db;          // dims 8*dblk .. +7
+#pragma unroll
+                    for (int kq = 0; kq < 2; ++kq) {               // keys 32*kq .. +31
+                        uint32_t r[4];
+                        // matrix j (lanes 8j..8j+7 give its rows): keys 32*kq + 8*j + i, dims 8*dblk..
+                        const int key = 32 * kq + 8 * (lane >> 3) + (lane & 7);
+                        fc_ldsm_x4_trans(r, sV_u + fc_off(key, dblk, FC_KHALF));
+                        // transposed: matrix j holds [dim i][key 8j..8j+7] -> row dim 8*dblk + i, key chunk 4*kq + j
+                        const int dim = 8 * dblk + (lane & 7);
+                        fc_stsm_x4(sVt_u + fc_off(dim, 4 * kq + (lane >> 3), 0), r);
+                    }
+                }
+            }
+            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");       // zeroing / V^T before the async proxy reads or refills
+            mbar_arrive(smem_u32(&sh->empty[s]));                               // this thread is done with the stage's values
+            // S: this row's 64 scores
+            if (!mbar_wait(smem_u32(&sh->s_full), it & 1, abort_flag, 15)) break;
+            tc_fence_after();
+            uint32_t sr[FC_BN];
+#pragma unroll
+            for (int c = 0; c < FC_BN / 16; ++c) tc_ld16(lane_base + (uint32_t)(c * 16), sr + c * 16);
+            tc_ld_wait();
+            float mx = -INFINITY;
+#pragma unroll
+            for (int j = 0; j < FC_BN; ++j) {
+                const int key = k0 + j;
+                const float v = (key >= lo && key <= pos) ? __uint_as_float(sr[j]) * a.scale_log2 : -INFINITY;
+                sr[j] = __float_as_uint(v);
+                mx = fmaxf(mx, v);
+            }
+            const float m_new = fmaxf(m, mx);
+            const float base = m_new == -INFINITY ? 0.0f : m_new;
+            const float alpha = exp2f(m - base);                   // m = -inf: 0
+            m = m_new;
+            float sum = 0.0f;
+#pragma unroll
+            for (int c = 0; c < FC_BN / 8; ++c) {
+                float p[8];
+#pragma unroll
+                for (int j = 0; j < 8; ++j) { p[j] = exp2f(__uint_as_float(sr[c * 8 + j]) - base); sum += p[j]; }
+                uint4 pk;
+                pk.x = fc_pack(p[0], p[1]); pk.y = fc_pack(p[2], p[3]); pk.z = fc_pack(p[4], p[5]); pk.w = fc_pack(p[6], p[7]);
+                *reinterpret_cast<uint4*>(sP + fc_off(row, c, 0)) = pk;
+            }
+            l = l * alpha + sum;
+            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");       // P before the tensor core reads it
+            tc_fence_before();                                     // S is read: the next tile's MMA may overwrite it
+            mbar_arrive(smem_u32(&sh->p_full));
+#pragma unroll
+            for (int j = 0; j < FC_D; ++j) o[j] *= alpha;
+            // O += P V
+            if (!mbar_wait(smem_u32(&sh->o_full), it & 1, abort_flag, 16)) break;
+            tc_fence_after();
+#pragma unroll
+            for (int c = 0; c < FC_D / 32; ++c) {
+                uint32_t pv[32];
+                tc_ld16(lane_base + (uint32_t)(FC_BN + c * 32), pv);
+                tc_ld16(lane_base + (uint32_t)(FC_BN + c * 32 + 16), pv + 16);
+                tc_ld_wait();
+#pragma unroll
+                for (int j = 0; j < 32; ++j) o[c * 32 + j] += __uint_as_float(pv[j]);
+            }
+            tc_fence_before();
+        }
+        if (live && !*abort_flag) {
+            const float inv = l > 0.0f ? 1.0f / l : 0.0f;
+            bf16* dst = a.out + ((size_t)(tok_base + ti) * a.QH + head0 + row % a.Gc) * FC_D;
+#pragma unroll
+            for (int c = 0; c < FC_D / 8; ++c) {
+                uint4 pk;
+                pk.x = fc_pack(o[c * 8] * inv, o[c * 8 + 1] * inv); pk.y = fc_pack(o[c * 8 + 2] * inv, o[c * 8 + 3] * inv);
+                pk.z = fc_pack(o[c * 8 + 4] * inv, o[c * 8 + 5] * inv); pk.w = fc_pack(o[c * 8 + 6] * inv, o[c * 8 + 7] * inv);
+                reinterpret_cast<uint4*>(dst)[c] = pk;
+            }
+        }
+    }
+    tc_fence_before();
+    __syncthreads();
+    if (*abort_flag && threadIdx.x == 0) {
+        // copies that were issued but never consumed still write this CTA's shared memory: wait for them
+        for (int it = max(0, issued - FC_NST); it < issued; ++it)
+            mbar_drain(smem_u32(&sh->full[it % FC_NST]), (it / FC_NST) & 1);
+    }
+    __syncthreads();
+    if (warp == 1) {
+        __syncwarp();
+        tc_fence_after();
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(FC_TMEM_COLS) : "memory");
+    }
+}
+
+// q [T, QH, 128] bfloat16; cache: one layer's [num_pages, 2, KH, page_size, 128]; entries first_entry .. bring
+// cu_q[e+1] - cu_q[e] tokens each and hold kv_len[e] tokens after this step.  n_tiles: the sum over these
+// entries of ceil(tokens / (128 / Gc)), Gc = the largest of 16, 8, 4, 2, 1 that divides QH / KH.
+extern "C" int rb_fa_prefill_tc(const void* q, const void* cache, long long num_pages, const int* block_table, const int* cu_q,
+                                const int* kv_len, void* out, int first_entry, int n_entries, int n_tiles, int QH, int KH, int d,
+                                int page_size, int max_pages, int window, float scale, void* stream) {
+    if (n_entries <= 0 || n_tiles <= 0) return 0;
+    if (QH <= 0 || KH <= 0 || QH % KH) RB_REFUSE("attention: %d query heads over %d kv heads", QH, KH);
+    if (d != FC_D) RB_REFUSE("attention (tcgen05): head_dim %d, only 128 is built", d);
+    int shift = -1;
+    for (int s = 3; s < 16; ++s) if ((1 << s) == page_size) shift = s;
+    if (shift < 0) RB_REFUSE("attention (tcgen05): page size %d is not a power of two >= 8", page_size);
+    if (((uintptr_t)cache & 15) || ((uintptr_t)q & 15) || ((uintptr_t)out & 15)) RB_REFUSE("attention (tcgen05): operands must be 16-byte aligned");
+    FcArgs a{};
+    a.q = (const bf16*)q; a.block_table = block_table; a.cu_q = cu_q; a.kv_len = kv_len; a.out = (bf16*)out;
+    a.QH = QH; a.KH = KH; a.page_size = page_size; a.page_shift = shift; a.max_pages = max_pages; a.window = window;
+    const int G = QH / KH;
+    a.Gc = 1;
+    for (int c = 16; c >= 1; c >>= 1) if (G % c == 0) { a.Gc = c; break; }
+    a.chunks = G / a.Gc; a.first_entry = first_entry; a.n_entries = n_entries;
+    a.scale_log2 = scale * 1.4426950408889634f;
+    CUtensorMap map;
+    const int box_rows = page_size < FC_BN ? page_size : FC_BN;
+    if (rb_tensor_map_bf16(cache, num_pages * 2LL * KH * page_size, d, d, box_rows, &map)) return -1;
+    constexpr size_t smem = (size_t)FC_NST * FC_STAGE + 4 * FC_QHALF + sizeof(FcShared) + 1024;
+    static bool done = false;
+    if (!done) {
+        cudaError_t e = cudaFuncSetAttribute(fa_prefill_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        if (e != cudaSuccess) return (int)e;
+        done = true;
+    }
+    return rb_launch(fa_prefill_tc_kernel, dim3(n_tiles, KH * a.chunks), dim3(FC_THREADS), smem, (cudaStream_t)stream, map, a);
+}
+
+// The group of query heads that share a CTA's rows, as rb_fa_prefill_tc chooses it (for the caller's tile count).
+extern "C" int rb_fa_prefill_tc_group(int QH, int KH) {
+    if (QH <= 0 || KH <= 0 || QH % KH) return 0;
+    const int G = QH / KH;
+    for (int c = 16; c >= 1; c >>= 1) if (G % c == 0) return c;
+    return 1;
+}
+
+// The error word of this file's kernels (0 = none); synchronises the device.  With reset != 0 it is cleared.
+extern "C" int rb_attn_tc_error(int reset) {
+    int v = 0;
+    if (cudaMemcpyFromSymbol(&v, g_rb_kernel_error, sizeof(int)) != cudaSuccess) return -1;
+    if (reset && v) { int z = 0; cudaMemcpyToSymbol(g_rb_kernel_error, &z, sizeof(int)); }
+    return v;
+}
+
+RB_TL_SETTER(rb_attn_tc_step_timeline)

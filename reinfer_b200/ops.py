@@ -350,6 +350,19 @@ def fa_prefill_tma(q, cache, block_table, cu_q, kv_len, out, first_entry: int, n
            "fa_prefill_tma")
 
 
+def fa_prefill_tc(q, cache, block_table, cu_q, kv_len, out, first_entry: int, n_entries: int, q_lens,
+                  QH: int, KH: int, d: int, page_size: int, window: int, scale: float) -> None:
+    """Paged causal flash attention on the tcgen05 tensor cores (scores and the weighted sum in tensor memory):
+    head size 128, page size a power of two >= 8.  q_lens: the token counts of the entries (host)."""
+    gc = int(lib().rb_fa_prefill_tc_group(c_int(QH), c_int(KH)))
+    tpt = 128 // gc
+    n_tiles = sum(-(-int(n) // tpt) for n in q_lens)
+    _check(lib().rb_fa_prefill_tc(_p(q), _p(cache), c_longlong(cache.shape[0]), _p(block_table), _p(cu_q), _p(kv_len), _p(out),
+                                  c_int(first_entry), c_int(n_entries), c_int(n_tiles), c_int(QH), c_int(KH), c_int(d),
+                                  c_int(page_size), c_int(block_table.shape[1]), c_int(window), c_float(scale), _stream()),
+           "fa_prefill_tc")
+
+
 def tma_pages(page_size: int) -> bool:
     return page_size >= 8 and page_size & (page_size - 1) == 0
 
@@ -364,6 +377,7 @@ def fa_prefill(q, cache, block_table, cu_q, kv_len, out, first_entry: int, n_ent
 
 USE_TMA_ATTENTION = os.environ.get("REINFER_B200_TMA_ATTENTION", "1") != "0"
 ATTN_CLUSTER_MERGE = os.environ.get("REINFER_B200_ATTN_CLUSTER", "1") != "0"
+USE_TC_ATTENTION = os.environ.get("REINFER_B200_TC_ATTENTION", "1") != "0"
 def decode_splits(ctas: int, tiles: int, slots: int = DECODE_SLOTS) -> int:
     """How many CTAs share one (request, kv head)'s keys.  Model of the launch's time: waves of
     `slots` resident CTAs, each CTA walking tiles/n tiles plus about 2.5 tile-times of fill, drain
@@ -398,7 +412,10 @@ def attention(ctx, q: torch.Tensor, cache: torch.Tensor, group, out: torch.Tenso
         decode = fa_decode_tma if (tma_pages(group.page_size) and USE_TMA_ATTENTION) else fa_decode
         decode(q, cache, group.block_table, ctx.cu_q, ctx.kv_len, out, 0, n_dec, 0, n_splits, QH, KH, d,
                group.page_size, window, scale)
-    if E > n_dec:
+    if E > n_dec and d == 128 and USE_TC_ATTENTION and USE_TMA_ATTENTION and tma_pages(group.page_size):
+        fa_prefill_tc(q, cache, group.block_table, ctx.cu_q, ctx.kv_len, out, n_dec, E - n_dec,
+                      [ctx.q_start[e + 1] - ctx.q_start[e] for e in range(n_dec, E)], QH, KH, d, group.page_size, window, scale)
+    elif E > n_dec:
         tpt = 64 // gc
         n_tiles = sum(-(-(ctx.q_start[e + 1] - ctx.q_start[e]) // tpt) for e in range(n_dec, E))
         prefill = fa_prefill_tma if (tma_pages(group.page_size) and USE_TMA_ATTENTION) else fa_prefill
@@ -492,7 +509,8 @@ def kernel_error(reset: bool = True) -> int:
     Synchronises the device."""
     a = int(lib().rb_gemm_error(c_int(int(reset))))
     b = int(lib().rb_attn_error(c_int(int(reset))))
-    return a or b
+    c = int(lib().rb_attn_tc_error(c_int(int(reset))))
+    return a or b or c
 
 
 def sample_params_size() -> int:

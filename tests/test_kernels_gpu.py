@@ -469,7 +469,7 @@ def test_attention_finds_one_far_key():
 
 @pytest.mark.parametrize("QH,KH,d,page", [(4, 2, 16, 16), (6, 2, 32, 8), (14, 2, 64, 4), (5, 5, 80, 32), (8, 1, 128, 16),
                                           (32, 8, 128, 16), (32, 1, 64, 16), (3, 1, 256, 64), (6, 3, 24, 8), (8, 2, 128, 128),
-                                          (4, 4, 192, 16)])
+                                          (4, 4, 192, 16), (6, 1, 128, 64), (7, 7, 128, 8), (32, 2, 128, 32)])
 @pytest.mark.parametrize("window", [0, 37])
 def test_flash_prefill_and_decode_against_plain(QH, KH, d, page, window):
     """The tensor-core kernels on a batch that mixes decode entries and prompt portions which
@@ -487,13 +487,19 @@ def test_flash_prefill_and_decode_against_plain(QH, KH, d, page, window):
     kv_len = torch.tensor(lens, dtype=torch.int32, device=DEV)
     gc = ops.fa_group_chunk(QH // KH)
     kernels = [(ops.fa_decode, ops.fa_prefill)] + ([(ops.fa_decode_tma, ops.fa_prefill_tma)] if ops.tma_pages(page) else [])
+    if d == 128 and ops.tma_pages(page):
+        kernels.append((ops.fa_decode_tma, "tcgen05"))                      # scores and weighted sums in tensor memory
     for n_splits, (decode, prefill) in [(n, f) for n in (1, 3, 8) for f in kernels]:
         out = torch.full_like(s["q"], float("nan"))
         decode(s["q"], s["cache"], s["bt"], cu_q, kv_len, out, 0, 4, 0, n_splits, QH, KH, d, page, window, scale)
         assert ops.kernel_error() == 0
         tpt = 64 // gc
         n_tiles = sum(-(-n // tpt) for n in q_lens[4:])
-        prefill(s["q"], s["cache"], s["bt"], cu_q, kv_len, out, 4, 3, n_tiles, QH, KH, d, page, window, scale)
+        if prefill == "tcgen05":
+            ops.fa_prefill_tc(s["q"], s["cache"], s["bt"], cu_q, kv_len, out, 4, 3, q_lens[4:], QH, KH, d, page, window, scale)
+            assert ops.kernel_error() == 0
+        else:
+            prefill(s["q"], s["cache"], s["bt"], cu_q, kv_len, out, 4, 3, n_tiles, QH, KH, d, page, window, scale)
         assert not torch.isnan(out.float()).any()
         err = (out.double().cpu() - ref).abs().max().item() / ref.abs().max().item()
         assert err <= 1.5e-2, f"splits {n_splits}: error {err:.3e}"
