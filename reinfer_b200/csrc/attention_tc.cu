@@ -11,9 +11,15 @@
 //                        threads read back and add to their row of O in registers (scaled by the maximum's change)
 // Warp 0 feeds key/value tiles by TMA exactly as the mma.sync kernels do (one box per page, key/value and
 // 64-column half onto a full/empty mbarrier ring); warp 1 allocates tensor memory and issues the MMAs;
-// warps 2-5 are the softmax rows.  Both MMA operands must be K-major here: Q [rows][d] and K [keys][d] are,
+// warps 4-11 are the softmax rows.  Both MMA operands must be K-major here: Q [rows][d] and K [keys][d] are,
 // P [rows][keys] is written so, and V [keys][d] is turned into V^T [d][keys] in shared memory by the softmax
 // warps (ldmatrix.trans + stmatrix, 8 x 8 blocks) while the tensor core computes S.
+//
+// Two tiles are in flight: S, P, V^T and the P V accumulator exist twice, and so do the rows - two groups of four
+// warps take the even and the odd tiles, each with its own running maximum, sum and O, which are combined at the end
+// (as the splits of flash decoding are).  While one group waits for its MMA the other computes, and every
+// scheduler of the SM has two warps to choose from.  The MMA warp computes the scores of tile i+1 before the
+// weighted sum of tile i.  Registers follow the roles (setmaxnreg): 40 for the control warps, 232 for the rows.
 //
 // Head size 128, page size a power of two >= 8.  Every wait is bounded (2 s); a CTA that gives up raises the
 // error word, lets its copies land, frees its tensor memory and leaves.
@@ -23,13 +29,13 @@
 #define FC_BN 64                              // keys per tile
 #define FC_ROWS 128                           // query rows per CTA
 #define FC_D 128
-#define FC_THREADS 192                        // TMA warp, MMA warp, four softmax warps
+#define FC_THREADS 384                        // a control group (TMA warp, MMA warp, two idle) and two groups of four row warps
 #define FC_NST 3
 #define FC_KHALF (FC_BN * 128)                // 64 keys x 128 bytes: one 64-column half of a key (or value) tile
 #define FC_KV_BYTES (2 * FC_KHALF)            // a key tile: two halves
 #define FC_STAGE (2 * FC_KV_BYTES)            // keys and values
 #define FC_QHALF (FC_ROWS * 128)              // 128 rows x 128 bytes
-#define FC_TMEM_COLS 256                      // S: columns 0..63, P V: columns 64..191
+#define FC_TMEM_COLS 512                      // S of two tiles: columns 0..127; P V of two tiles: 128..383
 
 struct FcArgs {
     const bf16* q;
@@ -45,7 +51,7 @@ struct FcArgs {
 struct FcShared {
     unsigned long long full[FC_NST];
     unsigned long long empty[FC_NST];
-    unsigned long long s_full, p_full, o_full;
+    unsigned long long s_full[2], p_full[2], o_full[2];
     uint32_t tmem_base;
     int abort_flag;
 };
@@ -63,10 +69,57 @@ __device__ __forceinline__ void fc_stsm_x4(uint32_t addr, const uint32_t (&r)[4]
     asm volatile("stmatrix.sync.aligned.m8n8.x4.shared.b16 [%0], {%1,%2,%3,%4};"
                  ::"r"(addr), "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]) : "memory");
 }
+// 2^x by the special-function unit alone (one instruction; exp2f adds range handling around it).  The arguments
+// here are <= 0 or -inf, where it is accurate to two units in the last place - far inside bfloat16's rounding of P.
+__device__ __forceinline__ float fc_ex2(float x) {
+#ifdef FC_NO_EX2
+    return fmaf(x, 0.001f, 0.5f);
+#else
+    float y;
+    asm("ex2.approx.f32 %0, %1;" : "=f"(y) : "f"(x));
+    return y;
+#endif
+}
 __device__ __forceinline__ uint32_t fc_pack(float lo, float hi) {
+#ifdef FC_NO_CVT
+    return (__float_as_uint(hi) & 0xffff0000u) | (__float_as_uint(lo) >> 16);
+#else
     const __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
     return *reinterpret_cast<const uint32_t*>(&v);
+#endif
 }
+
+// The bounded wait of sm100.cuh with a pause between polls: here up to twelve warps wait for one another on one SM,
+// and a warp that polls without pause takes issue slots from the warps it waits for.
+__device__ __forceinline__ bool fc_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag, int where) {
+    if (mbar_try(bar, parity)) return true;
+    unsigned long long t0 = 0;
+    for (uint32_t it = 0; it < RB_SPIN_LIMIT; ++it) {
+        __nanosleep(40);
+        if (mbar_try(bar, parity)) return true;
+        if ((it & 63u) == 63u) {
+            if (*abort_flag) return false;
+            const unsigned long long now = rb_globaltimer();
+            if (t0 == 0) t0 = now;
+            else if (now - t0 > RB_WAIT_NS) break;
+        }
+    }
+    *abort_flag = where;
+    atomicCAS(&g_rb_kernel_error, 0, (1 << 8) | where);
+    return false;
+}
+
+#ifdef FC_PROFILE
+__device__ unsigned long long g_fc_prof[16];
+#define FC_T(i) do { if (et == 0) { const long long t_ = clock64(); prof[i] += t_ - tprev; tprev = t_; } } while (0)
+extern "C" int rb_fc_prof(unsigned long long* out, int reset) {
+    cudaMemcpyFromSymbol(out, g_fc_prof, sizeof(unsigned long long) * 16);
+    if (reset) { unsigned long long z[16] = {0}; cudaMemcpyToSymbol(g_fc_prof, z, sizeof(z)); }
+    return 0;
+}
+#else
+#define FC_T(i) do { } while (0)
+#endif
 
 __global__ void __launch_bounds__(FC_THREADS, 1)
 fa_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_kv, const FcArgs a) {
@@ -75,9 +128,9 @@ fa_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_kv, const FcArgs a)
     unsigned char* smem = (unsigned char*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
     unsigned char* stages = smem;                                  // [FC_NST][K half 0, K half 1, V half 0, V half 1]
     unsigned char* sQ = stages + FC_NST * FC_STAGE;                // two halves of [128 rows][64 dims]
-    unsigned char* sP = sQ + 2 * FC_QHALF;                         // [128 rows][64 keys]
-    unsigned char* sVt = sP + FC_QHALF;                            // [128 dims][64 keys]
-    FcShared* sh = (FcShared*)(sVt + FC_QHALF);
+    unsigned char* sP = sQ + 2 * FC_QHALF;                         // two of [128 rows][64 keys]
+    unsigned char* sVt = sP + 2 * FC_QHALF;                        // two of [128 dims][64 keys]
+    FcShared* sh = (FcShared*)(sVt + 2 * FC_QHALF);
     const uint32_t stages_u = smem_u32(stages), sQ_u = smem_u32(sQ), sP_u = smem_u32(sP), sVt_u = smem_u32(sVt);
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     volatile int* abort_flag = &sh->abort_flag;
@@ -85,11 +138,13 @@ fa_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_kv, const FcArgs a)
     if (threadIdx.x == 0) {
         for (int s = 0; s < FC_NST; ++s) {
             mbar_init(smem_u32(&sh->full[s]), 1);
-            mbar_init(smem_u32(&sh->empty[s]), 1 + FC_ROWS);       // the MMA warp's commit (keys) + the rows (values)
+            mbar_init(smem_u32(&sh->empty[s]), 1 + 4);             // the MMA warp's commit (keys) + the four row warps (values)
         }
-        mbar_init(smem_u32(&sh->s_full), 1);
-        mbar_init(smem_u32(&sh->p_full), FC_ROWS);
-        mbar_init(smem_u32(&sh->o_full), 1);
+        for (int b = 0; b < 2; ++b) {
+            mbar_init(smem_u32(&sh->s_full[b]), 1);
+            mbar_init(smem_u32(&sh->p_full[b]), 4);                // one arrival per row warp
+            mbar_init(smem_u32(&sh->o_full[b]), 1);
+        }
         sh->abort_flag = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
@@ -97,10 +152,9 @@ fa_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_kv, const FcArgs a)
         asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&sh->tmem_base)), "r"(FC_TMEM_COLS) : "memory");
         asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
     }
-    // shared memory starts at zero: rows that no copy fills are then finite
-    for (int i = threadIdx.x; i < (FC_NST * FC_STAGE + 4 * FC_QHALF) / 16; i += FC_THREADS)
-        reinterpret_cast<uint4*>(smem)[i] = make_uint4(0, 0, 0, 0);
-    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+    // Nothing that a copy or a thread of this CTA did not write reaches the results: value rows at or beyond the
+    // request's length are zeroed before use, scores of such keys and of rows without a token are replaced by
+    // -inf whatever they are, P and V^T are written whole before they are read.
     tc_fence_before();
     __syncthreads();
     tc_fence_after();
@@ -110,7 +164,7 @@ fa_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_kv, const FcArgs a)
 
     // which rows: heavy tiles (late in a request: more keys) first
     const int tpt = FC_ROWS / a.Gc;                                // tokens per CTA
-    int tile = (int)gridDim.x - 1 - (int)blockIdx.x, e = a.first_entry, q_len = 0;
+    int tile = (int)gridDim.y - 1 - (int)blockIdx.y, e = a.first_entry, q_len = 0;   // CTAs start in order of x, then y
     for (; e < a.first_entry + a.n_entries; ++e) {
         q_len = a.cu_q[e + 1] - a.cu_q[e];
         const int nt = (q_len + tpt - 1) / tpt;
@@ -123,8 +177,8 @@ fa_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_kv, const FcArgs a)
     if (!none) {
         q0 = tile * tpt;
         n_tok = min(tpt, q_len - q0);
-        kh = blockIdx.y / a.chunks;
-        head0 = kh * (a.QH / a.KH) + (blockIdx.y % a.chunks) * a.Gc;
+        kh = blockIdx.x / a.chunks;
+        head0 = kh * (a.QH / a.KH) + (blockIdx.x % a.chunks) * a.Gc;
         kv_end = a.kv_len[e];
         start_pos = kv_end - q_len;
         tok_base = a.cu_q[e] + q0;
@@ -144,6 +198,8 @@ fa_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_kv, const FcArgs a)
     __syncthreads();
 
     int issued = 0;                                                // producer: tiles whose copies were issued
+    if (warp < 4) {
+    asm volatile("setmaxnreg.dec.sync.aligned.u32 40;");           // the control group gives registers up ...
     if (warp == 0) {
         // ---- producer: runs ahead by up to FC_NST tiles; block-table entries 32 at a time -------------------
         const int box_rows = min(a.page_size, FC_BN);
@@ -172,7 +228,7 @@ fa_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_kv, const FcArgs a)
             }
             bool ok = true;
             if (lane == 0) {
-                if (it >= FC_NST) ok = mbar_wait(smem_u32(&sh->empty[s]), ((it / FC_NST) & 1) ^ 1, abort_flag, 11);
+                if (it >= FC_NST) ok = fc_wait(smem_u32(&sh->empty[s]), ((it / FC_NST) & 1) ^ 1, abort_flag, 11);
                 if (ok) {
                     const uint32_t full = smem_u32(&sh->full[s]);
                     mbar_expect_tx(full, (uint32_t)(n_valid * 4 * box_rows * 128));
@@ -199,34 +255,46 @@ fa_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_kv, const FcArgs a)
         // ---- MMA issuer ----------------------------------------------------------------------------------------
         if (lane == 0) {
             constexpr uint32_t idesc_s = make_idesc(FC_BN), idesc_o = make_idesc(FC_D);
-            for (int it = 0; it < n_tiles; ++it) {
-                const int s = it % FC_NST;
-                if (!mbar_wait(smem_u32(&sh->full[s]), (it / FC_NST) & 1, abort_flag, 12)) break;
+            // S(i) = Q K(i)^T into score buffer i & 1: d = 128 is two 64-column halves of four 16-wide steps each
+            auto scores = [&](int i) -> bool {
+                const int s = i % FC_NST;
+                if (!fc_wait(smem_u32(&sh->full[s]), (i / FC_NST) & 1, abort_flag, 12)) return false;
                 tc_fence_after();
-                // S = Q K^T: d = 128 is two 64-column halves of four 16-wide steps each
                 const uint32_t sK = stages_u + s * FC_STAGE;
 #pragma unroll
                 for (int h = 0; h < 2; ++h) {
                     const uint64_t dq = make_smem_desc(sQ_u + h * FC_QHALF), dk = make_smem_desc(sK + h * FC_KHALF);
 #pragma unroll
-                    for (int k = 0; k < 4; ++k) tc_mma_bf16(tmem, dq + (uint64_t)(k * 2), dk + (uint64_t)(k * 2), idesc_s, (h | k) != 0);
+                    for (int k = 0; k < 4; ++k)
+                        tc_mma_bf16(tmem + (uint32_t)((i & 1) * FC_BN), dq + (uint64_t)(k * 2), dk + (uint64_t)(k * 2), idesc_s, (h | k) != 0);
                 }
-                tc_commit(smem_u32(&sh->s_full));
+                tc_commit(smem_u32(&sh->s_full[i & 1]));
                 tc_commit(smem_u32(&sh->empty[s]));                // the keys of this stage are read once these MMAs are done
-                // O_tile = P V once the rows have written P and V^T
-                if (!mbar_wait(smem_u32(&sh->p_full), it & 1, abort_flag, 13)) break;
+                return true;
+            };
+            bool ok = n_tiles > 0 && scores(0);
+            for (int it = 0; it < n_tiles && ok; ++it) {
+                // the scores of the next tile while the rows work on this one (its buffer was read two tiles ago)
+                if (it + 1 < n_tiles) ok = scores(it + 1);
+                if (!ok) break;
+                // O_tile(it) = P V once the rows have written P and V^T (the accumulator was read two tiles ago)
+                if (!fc_wait(smem_u32(&sh->p_full[it & 1]), (it >> 1) & 1, abort_flag, 13)) break;
                 tc_fence_after();
-                const uint64_t dp = make_smem_desc(sP_u), dv = make_smem_desc(sVt_u);
+                const uint64_t dp = make_smem_desc(sP_u + (it & 1) * FC_QHALF), dv = make_smem_desc(sVt_u + (it & 1) * FC_QHALF);
 #pragma unroll
-                for (int k = 0; k < 4; ++k) tc_mma_bf16(tmem + FC_BN, dp + (uint64_t)(k * 2), dv + (uint64_t)(k * 2), idesc_o, k != 0);
-                tc_commit(smem_u32(&sh->o_full));
+                for (int k = 0; k < 4; ++k)
+                    tc_mma_bf16(tmem + (uint32_t)(2 * FC_BN + (it & 1) * FC_D), dp + (uint64_t)(k * 2), dv + (uint64_t)(k * 2), idesc_o, k != 0);
+                tc_commit(smem_u32(&sh->o_full[it & 1]));
             }
         }
+    }
     } else {
-        // ---- softmax rows: thread = row = tensor-memory lane -----------------------------------------------------
+        asm volatile("setmaxnreg.inc.sync.aligned.u32 232;");      // ... and the rows take them
+        // ---- softmax rows: thread = row = tensor-memory lane; group g takes tiles g, g + 2, ... ---------------------
+        const int g = (warp - 4) >> 2;
         const int quad = warp & 3;                                 // the lanes this warp may read: 32 * (warp % 4) ..
         const int row = quad * 32 + lane;
-        const int et = (warp - 2) * 32 + lane;                     // 0..127 among the softmax threads
+        const int et = quad * 32 + lane;                           // 0..127 inside the group
         const int ti = row / a.Gc;
         const bool live = !none && ti < n_tok;
         const int pos = live ? start_pos + q0 + ti : -1;
@@ -236,97 +304,166 @@ fa_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_kv, const FcArgs a)
         for (int j = 0; j < FC_D; ++j) o[j] = 0.0f;
         float m = -INFINITY, l = 0.0f;
         const uint32_t lane_base = tmem + ((uint32_t)(quad * 32) << 16);
-        for (int it = 0; it < n_tiles; ++it) {
+        const uint32_t s_col = (uint32_t)(g * FC_BN), o_col = (uint32_t)(2 * FC_BN + g * FC_D);
+        unsigned char* sPg = sP + g * FC_QHALF;
+        const uint32_t sVt_g = sVt_u + g * FC_QHALF;
+#ifdef FC_PROFILE
+        long long prof[8] = {0, 0, 0, 0, 0, 0, 0, 0}, tprev = clock64();
+#endif
+        bool ok = true;
+        for (int it = g; it < n_tiles; it += 2) {
             const int s = it % FC_NST;
-            if (!mbar_wait(smem_u32(&sh->full[s]), (it / FC_NST) & 1, abort_flag, 14)) break;
+            const uint32_t par = (uint32_t)((it >> 1) & 1);
+            FC_T(7);
+            if (!fc_wait(smem_u32(&sh->full[s]), (it / FC_NST) & 1, abort_flag, 14)) { ok = false; break; }
+            FC_T(0);
+            // O += P V of this group's tile before: its accumulator, P and V^T are about to be used again
+            if (it >= 2) {
+                if (!fc_wait(smem_u32(&sh->o_full[g]), par ^ 1, abort_flag, 16)) { ok = false; break; }
+                tc_fence_after();
+                FC_T(4);
+#pragma unroll
+                for (int c = 0; c < FC_D / 64; ++c) {
+                    uint32_t pv[64];
+#pragma unroll
+                    for (int q4 = 0; q4 < 4; ++q4) tc_ld16(lane_base + o_col + (uint32_t)(c * 64 + q4 * 16), pv + q4 * 16);
+                    tc_ld_wait();
+#pragma unroll
+                    for (int j = 0; j < 64; ++j) o[c * 64 + j] += __uint_as_float(pv[j]);
+                }
+                tc_fence_before();
+                FC_T(5);
+            }
             const int k0 = (t_begin + it) * FC_BN;
             unsigned char* sV = stages + s * FC_STAGE + FC_KV_BYTES;
-            if (k0 + FC_BN > kv_end) {
+            const bool tail = k0 + FC_BN > kv_end;
+            if (tail) {
                 // the request's last tile: slots of its last page beyond its length hold foreign data
                 for (int i = et; i < FC_BN * 16; i += FC_ROWS) {
                     const int r = i / 16, c = i % 16;
                     if (k0 + r >= kv_end) *reinterpret_cast<uint4*>(sV + fc_off(r, c, FC_KHALF)) = make_uint4(0, 0, 0, 0);
                 }
-                asm volatile("bar.sync 1, %0;" ::"n"(FC_ROWS) : "memory");
+                if (g == 0) asm volatile("bar.sync 1, %0;" ::"n"(FC_ROWS) : "memory");
+                else asm volatile("bar.sync 2, %0;" ::"n"(FC_ROWS) : "memory");
             }
             // V [keys][dims] -> V^T [dims][keys], 8 x 8 blocks: each warp takes 4 of the 16 dim-blocks, and per
             // instruction the four key-blocks of half a tile
             {
                 const uint32_t sV_u = stages_u + s * FC_STAGE + FC_KV_BYTES;
 #pragma unroll
-                for (int db = 0; db < 4; ++db) {
-                    const int dblk = (warp - 2) * 4 + db;          // dims 8*dblk .. +7
+                for (int half = 0; half < 2; ++half) {
+                    uint32_t r[4][4];
 #pragma unroll
-                    for (int kq = 0; kq < 2; ++kq) {               // keys 32*kq .. +31
-                        uint32_t r[4];
+                    for (int i = 0; i < 4; ++i) {
+                        const int dblk = quad * 4 + half * 2 + (i >> 1), kq = i & 1;    // dims 8*dblk .. +7, keys 32*kq .. +31
                         // matrix j (lanes 8j..8j+7 give its rows): keys 32*kq + 8*j + i, dims 8*dblk..
-                        const int key = 32 * kq + 8 * (lane >> 3) + (lane & 7);
-                        fc_ldsm_x4_trans(r, sV_u + fc_off(key, dblk, FC_KHALF));
+                        fc_ldsm_x4_trans(r[i], sV_u + fc_off(32 * kq + 8 * (lane >> 3) + (lane & 7), dblk, FC_KHALF));
+                    }
+#pragma unroll
+                    for (int i = 0; i < 4; ++i) {
+                        const int dblk = quad * 4 + half * 2 + (i >> 1), kq = i & 1;
                         // transposed: matrix j holds [dim i][key 8j..8j+7] -> row dim 8*dblk + i, key chunk 4*kq + j
-                        const int dim = 8 * dblk + (lane & 7);
-                        fc_stsm_x4(sVt_u + fc_off(dim, 4 * kq + (lane >> 3), 0), r);
+                        fc_stsm_x4(sVt_g + fc_off(8 * dblk + (lane & 7), 4 * kq + (lane >> 3), 0), r[i]);
                     }
                 }
             }
-            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");       // zeroing / V^T before the async proxy reads or refills
-            mbar_arrive(smem_u32(&sh->empty[s]));                               // this thread is done with the stage's values
+            if (tail) asm volatile("fence.proxy.async.shared::cta;" ::: "memory");   // the zeroing, before the stage is refilled
+            __syncwarp();
+            if (lane == 0) mbar_arrive(smem_u32(&sh->empty[s]));                // this warp is done with the stage's values
+            FC_T(1);
             // S: this row's 64 scores
-            if (!mbar_wait(smem_u32(&sh->s_full), it & 1, abort_flag, 15)) break;
+            if (!fc_wait(smem_u32(&sh->s_full[g]), par, abort_flag, 15)) { ok = false; break; }
             tc_fence_after();
+            FC_T(2);
+            // the row's 64 scores in one go (one wait for tensor memory); maxima and sums in four independent chains
+            const bool edge = k0 + FC_BN - 1 > pos || k0 < lo;     // the tile crosses this row's causal edge or window
             uint32_t sr[FC_BN];
 #pragma unroll
-            for (int c = 0; c < FC_BN / 16; ++c) tc_ld16(lane_base + (uint32_t)(c * 16), sr + c * 16);
+            for (int c = 0; c < FC_BN / 16; ++c) tc_ld16(lane_base + s_col + (uint32_t)(c * 16), sr + c * 16);
             tc_ld_wait();
-            float mx = -INFINITY;
+            if (edge) {
 #pragma unroll
-            for (int j = 0; j < FC_BN; ++j) {
-                const int key = k0 + j;
-                const float v = (key >= lo && key <= pos) ? __uint_as_float(sr[j]) * a.scale_log2 : -INFINITY;
-                sr[j] = __float_as_uint(v);
-                mx = fmaxf(mx, v);
+                for (int j = 0; j < FC_BN; ++j) {
+                    const int key = k0 + j;
+                    if (key < lo || key > pos) sr[j] = 0xff800000u;            // -inf
+                }
             }
-            const float m_new = fmaxf(m, mx);
+            float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
+#pragma unroll
+            for (int j = 0; j < FC_BN; ++j) mx4[j & 3] = fmaxf(mx4[j & 3], __uint_as_float(sr[j]));
+            const float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3]));
+            const float m_new = fmaxf(m, mx * a.scale_log2);       // the scale is positive: the maximum of the scaled scores
             const float base = m_new == -INFINITY ? 0.0f : m_new;
-            const float alpha = exp2f(m - base);                   // m = -inf: 0
+            const float alpha = fc_ex2(m - base);                  // m = -inf: 0
             m = m_new;
-            float sum = 0.0f;
+            float sum4[4] = {0.0f, 0.0f, 0.0f, 0.0f};
 #pragma unroll
             for (int c = 0; c < FC_BN / 8; ++c) {
                 float p[8];
 #pragma unroll
-                for (int j = 0; j < 8; ++j) { p[j] = exp2f(__uint_as_float(sr[c * 8 + j]) - base); sum += p[j]; }
+                for (int j = 0; j < 8; ++j) { p[j] = fc_ex2(fmaf(__uint_as_float(sr[c * 8 + j]), a.scale_log2, -base)); sum4[j & 3] += p[j]; }
                 uint4 pk;
                 pk.x = fc_pack(p[0], p[1]); pk.y = fc_pack(p[2], p[3]); pk.z = fc_pack(p[4], p[5]); pk.w = fc_pack(p[6], p[7]);
-                *reinterpret_cast<uint4*>(sP + fc_off(row, c, 0)) = pk;
+                *reinterpret_cast<uint4*>(sPg + fc_off(row, c, 0)) = pk;
             }
+            const float sum = (sum4[0] + sum4[1]) + (sum4[2] + sum4[3]);
             l = l * alpha + sum;
-            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");       // P before the tensor core reads it
-            tc_fence_before();                                     // S is read: the next tile's MMA may overwrite it
-            mbar_arrive(smem_u32(&sh->p_full));
+            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");       // P and V^T before the tensor core reads them
+            tc_fence_before();                                     // S is read: the group's next scores may overwrite it
+            __syncwarp();
+            if (lane == 0) mbar_arrive(smem_u32(&sh->p_full[g]));
+            // O follows the maximum only when it moved (alpha == 1 exactly otherwise) for some row of the warp
+            if (__any_sync(0xffffffffu, alpha != 1.0f)) {
 #pragma unroll
-            for (int j = 0; j < FC_D; ++j) o[j] *= alpha;
-            // O += P V
-            if (!mbar_wait(smem_u32(&sh->o_full), it & 1, abort_flag, 16)) break;
+                for (int j = 0; j < FC_D; ++j) o[j] *= alpha;
+            }
+            FC_T(3);
+        }
+        // the group's last tile
+        const int n_mine = n_tiles > g ? (n_tiles - g + 1) / 2 : 0;
+        if (ok && n_mine > 0 && fc_wait(smem_u32(&sh->o_full[g]), (uint32_t)((n_mine - 1) & 1), abort_flag, 17)) {
             tc_fence_after();
 #pragma unroll
-            for (int c = 0; c < FC_D / 32; ++c) {
-                uint32_t pv[32];
-                tc_ld16(lane_base + (uint32_t)(FC_BN + c * 32), pv);
-                tc_ld16(lane_base + (uint32_t)(FC_BN + c * 32 + 16), pv + 16);
+            for (int c = 0; c < FC_D / 64; ++c) {
+                uint32_t pv[64];
+#pragma unroll
+                for (int q4 = 0; q4 < 4; ++q4) tc_ld16(lane_base + o_col + (uint32_t)(c * 64 + q4 * 16), pv + q4 * 16);
                 tc_ld_wait();
 #pragma unroll
-                for (int j = 0; j < 32; ++j) o[c * 32 + j] += __uint_as_float(pv[j]);
+                for (int j = 0; j < 64; ++j) o[c * 64 + j] += __uint_as_float(pv[j]);
             }
             tc_fence_before();
         }
-        if (live && !*abort_flag) {
-            const float inv = l > 0.0f ? 1.0f / l : 0.0f;
+#ifdef FC_PROFILE
+        if (et == 0) { for (int i = 0; i < 8; ++i) atomicAdd(&g_fc_prof[i], (unsigned long long)prof[i]); atomicAdd(&g_fc_prof[8], (unsigned long long)n_mine); }
+#endif
+        // The two groups' results for a row are combined like two splits: group 1 hands its maximum, sum and O over
+        // through the (now idle) stages, group 0 adds and stores.  Both reach the barrier whatever happened before.
+        float* xo = reinterpret_cast<float*>(stages);              // [128 rows][128] + [128] m + [128] l: 66.5 KB of the ring's 96
+        asm volatile("bar.sync 3, %0;" ::"n"(2 * FC_ROWS) : "memory");          // both groups are done with the ring
+        if (g == 1) {
+#pragma unroll
+            for (int j = 0; j < FC_D; ++j) xo[j * FC_ROWS + row] = o[j];        // column-major: neighbouring rows, neighbouring words
+            xo[FC_D * FC_ROWS + row] = m;
+            xo[FC_D * FC_ROWS + FC_ROWS + row] = l;
+        }
+        asm volatile("bar.sync 3, %0;" ::"n"(2 * FC_ROWS) : "memory");
+        if (g == 0 && live && !*abort_flag) {
+            const float m1 = xo[FC_D * FC_ROWS + row], l1 = xo[FC_D * FC_ROWS + FC_ROWS + row];
+            const float M = fmaxf(m, m1);
+            const float base = M == -INFINITY ? 0.0f : M;
+            const float f0 = fc_ex2(m - base), f1 = fc_ex2(m1 - base);
+            const float L = l * f0 + l1 * f1;
+            const float inv = L > 0.0f ? 1.0f / L : 0.0f;
+            const float w0 = f0 * inv, w1 = f1 * inv;
             bf16* dst = a.out + ((size_t)(tok_base + ti) * a.QH + head0 + row % a.Gc) * FC_D;
 #pragma unroll
             for (int c = 0; c < FC_D / 8; ++c) {
+                float v[8];
+#pragma unroll
+                for (int j = 0; j < 8; ++j) v[j] = o[c * 8 + j] * w0 + xo[(c * 8 + j) * FC_ROWS + row] * w1;
                 uint4 pk;
-                pk.x = fc_pack(o[c * 8] * inv, o[c * 8 + 1] * inv); pk.y = fc_pack(o[c * 8 + 2] * inv, o[c * 8 + 3] * inv);
-                pk.z = fc_pack(o[c * 8 + 4] * inv, o[c * 8 + 5] * inv); pk.w = fc_pack(o[c * 8 + 6] * inv, o[c * 8 + 7] * inv);
+                pk.x = fc_pack(v[0], v[1]); pk.y = fc_pack(v[2], v[3]); pk.z = fc_pack(v[4], v[5]); pk.w = fc_pack(v[6], v[7]);
                 reinterpret_cast<uint4*>(dst)[c] = pk;
             }
         }
@@ -370,14 +507,15 @@ extern "C" int rb_fa_prefill_tc(const void* q, const void* cache, long long num_
     CUtensorMap map;
     const int box_rows = page_size < FC_BN ? page_size : FC_BN;
     if (rb_tensor_map_bf16(cache, num_pages * 2LL * KH * page_size, d, d, box_rows, &map)) return -1;
-    constexpr size_t smem = (size_t)FC_NST * FC_STAGE + 4 * FC_QHALF + sizeof(FcShared) + 1024;
+    constexpr size_t smem = (size_t)FC_NST * FC_STAGE + 6 * FC_QHALF + sizeof(FcShared) + 1024;
     static bool done = false;
     if (!done) {
         cudaError_t e = cudaFuncSetAttribute(fa_prefill_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         if (e != cudaSuccess) return (int)e;
         done = true;
     }
-    return rb_launch(fa_prefill_tc_kernel, dim3(n_tiles, KH * a.chunks), dim3(FC_THREADS), smem, (cudaStream_t)stream, map, a);
+    if (n_tiles > 65535) RB_REFUSE("attention (tcgen05): %d row tiles in one launch", n_tiles);
+    return rb_launch(fa_prefill_tc_kernel, dim3(KH * a.chunks, n_tiles), dim3(FC_THREADS), smem, (cudaStream_t)stream, map, a);
 }
 
 // The group of query heads that share a CTA's rows, as rb_fa_prefill_tc chooses it (for the caller's tile count).
