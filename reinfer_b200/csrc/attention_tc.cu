@@ -30,7 +30,7 @@
 #define FC_ROWS 128                           // query rows per CTA
 #define FC_D 128
 #define FC_THREADS 384                        // a control group (TMA warp, MMA warp, two idle) and two groups of four row warps
-#define FC_NST 3
+#define FC_NST 4
 #define FC_KHALF (FC_BN * 128)                // 64 keys x 128 bytes: one 64-column half of a key (or value) tile
 #define FC_KV_BYTES (2 * FC_KHALF)            // a key tile: two halves
 #define FC_STAGE (2 * FC_KV_BYTES)            // keys and values
@@ -72,21 +72,13 @@ __device__ __forceinline__ void fc_stsm_x4(uint32_t addr, const uint32_t (&r)[4]
 // 2^x by the special-function unit alone (one instruction; exp2f adds range handling around it).  The arguments
 // here are <= 0 or -inf, where it is accurate to two units in the last place - far inside bfloat16's rounding of P.
 __device__ __forceinline__ float fc_ex2(float x) {
-#ifdef FC_NO_EX2
-    return fmaf(x, 0.001f, 0.5f);
-#else
     float y;
     asm("ex2.approx.f32 %0, %1;" : "=f"(y) : "f"(x));
     return y;
-#endif
 }
 __device__ __forceinline__ uint32_t fc_pack(float lo, float hi) {
-#ifdef FC_NO_CVT
-    return (__float_as_uint(hi) & 0xffff0000u) | (__float_as_uint(lo) >> 16);
-#else
     const __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
     return *reinterpret_cast<const uint32_t*>(&v);
-#endif
 }
 
 // The bounded wait of sm100.cuh with a pause between polls: here up to twelve warps wait for one another on one SM,
@@ -108,18 +100,6 @@ __device__ __forceinline__ bool fc_wait(uint32_t bar, uint32_t parity, volatile 
     atomicCAS(&g_rb_kernel_error, 0, (1 << 8) | where);
     return false;
 }
-
-#ifdef FC_PROFILE
-__device__ unsigned long long g_fc_prof[16];
-#define FC_T(i) do { if (et == 0) { const long long t_ = clock64(); prof[i] += t_ - tprev; tprev = t_; } } while (0)
-extern "C" int rb_fc_prof(unsigned long long* out, int reset) {
-    cudaMemcpyFromSymbol(out, g_fc_prof, sizeof(unsigned long long) * 16);
-    if (reset) { unsigned long long z[16] = {0}; cudaMemcpyToSymbol(g_fc_prof, z, sizeof(z)); }
-    return 0;
-}
-#else
-#define FC_T(i) do { } while (0)
-#endif
 
 __global__ void __launch_bounds__(FC_THREADS, 1)
 fa_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_kv, const FcArgs a) {
@@ -307,21 +287,15 @@ fa_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_kv, const FcArgs a)
         const uint32_t s_col = (uint32_t)(g * FC_BN), o_col = (uint32_t)(2 * FC_BN + g * FC_D);
         unsigned char* sPg = sP + g * FC_QHALF;
         const uint32_t sVt_g = sVt_u + g * FC_QHALF;
-#ifdef FC_PROFILE
-        long long prof[8] = {0, 0, 0, 0, 0, 0, 0, 0}, tprev = clock64();
-#endif
         bool ok = true;
         for (int it = g; it < n_tiles; it += 2) {
             const int s = it % FC_NST;
             const uint32_t par = (uint32_t)((it >> 1) & 1);
-            FC_T(7);
             if (!fc_wait(smem_u32(&sh->full[s]), (it / FC_NST) & 1, abort_flag, 14)) { ok = false; break; }
-            FC_T(0);
             // O += P V of this group's tile before: its accumulator, P and V^T are about to be used again
             if (it >= 2) {
                 if (!fc_wait(smem_u32(&sh->o_full[g]), par ^ 1, abort_flag, 16)) { ok = false; break; }
                 tc_fence_after();
-                FC_T(4);
 #pragma unroll
                 for (int c = 0; c < FC_D / 64; ++c) {
                     uint32_t pv[64];
@@ -332,7 +306,6 @@ fa_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_kv, const FcArgs a)
                     for (int j = 0; j < 64; ++j) o[c * 64 + j] += __uint_as_float(pv[j]);
                 }
                 tc_fence_before();
-                FC_T(5);
             }
             const int k0 = (t_begin + it) * FC_BN;
             unsigned char* sV = stages + s * FC_STAGE + FC_KV_BYTES;
@@ -350,31 +323,26 @@ fa_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_kv, const FcArgs a)
             // instruction the four key-blocks of half a tile
             {
                 const uint32_t sV_u = stages_u + s * FC_STAGE + FC_KV_BYTES;
+                uint32_t r[8][4];
 #pragma unroll
-                for (int half = 0; half < 2; ++half) {
-                    uint32_t r[4][4];
+                for (int i = 0; i < 8; ++i) {
+                    const int dblk = quad * 4 + (i >> 1), kq = i & 1;           // dims 8*dblk .. +7, keys 32*kq .. +31
+                    // matrix j (lanes 8j..8j+7 give its rows): keys 32*kq + 8*j + i, dims 8*dblk..
+                    fc_ldsm_x4_trans(r[i], sV_u + fc_off(32 * kq + 8 * (lane >> 3) + (lane & 7), dblk, FC_KHALF));
+                }
 #pragma unroll
-                    for (int i = 0; i < 4; ++i) {
-                        const int dblk = quad * 4 + half * 2 + (i >> 1), kq = i & 1;    // dims 8*dblk .. +7, keys 32*kq .. +31
-                        // matrix j (lanes 8j..8j+7 give its rows): keys 32*kq + 8*j + i, dims 8*dblk..
-                        fc_ldsm_x4_trans(r[i], sV_u + fc_off(32 * kq + 8 * (lane >> 3) + (lane & 7), dblk, FC_KHALF));
-                    }
-#pragma unroll
-                    for (int i = 0; i < 4; ++i) {
-                        const int dblk = quad * 4 + half * 2 + (i >> 1), kq = i & 1;
-                        // transposed: matrix j holds [dim i][key 8j..8j+7] -> row dim 8*dblk + i, key chunk 4*kq + j
-                        fc_stsm_x4(sVt_g + fc_off(8 * dblk + (lane & 7), 4 * kq + (lane >> 3), 0), r[i]);
-                    }
+                for (int i = 0; i < 8; ++i) {
+                    const int dblk = quad * 4 + (i >> 1), kq = i & 1;
+                    // transposed: matrix j holds [dim i][key 8j..8j+7] -> row dim 8*dblk + i, key chunk 4*kq + j
+                    fc_stsm_x4(sVt_g + fc_off(8 * dblk + (lane & 7), 4 * kq + (lane >> 3), 0), r[i]);
                 }
             }
             if (tail) asm volatile("fence.proxy.async.shared::cta;" ::: "memory");   // the zeroing, before the stage is refilled
             __syncwarp();
             if (lane == 0) mbar_arrive(smem_u32(&sh->empty[s]));                // this warp is done with the stage's values
-            FC_T(1);
             // S: this row's 64 scores
             if (!fc_wait(smem_u32(&sh->s_full[g]), par, abort_flag, 15)) { ok = false; break; }
             tc_fence_after();
-            FC_T(2);
             // the row's 64 scores in one go (one wait for tensor memory); maxima and sums in four independent chains
             const bool edge = k0 + FC_BN - 1 > pos || k0 < lo;     // the tile crosses this row's causal edge or window
             uint32_t sr[FC_BN];
@@ -417,7 +385,6 @@ fa_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_kv, const FcArgs a)
 #pragma unroll
                 for (int j = 0; j < FC_D; ++j) o[j] *= alpha;
             }
-            FC_T(3);
         }
         // the group's last tile
         const int n_mine = n_tiles > g ? (n_tiles - g + 1) / 2 : 0;
@@ -434,12 +401,9 @@ fa_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_kv, const FcArgs a)
             }
             tc_fence_before();
         }
-#ifdef FC_PROFILE
-        if (et == 0) { for (int i = 0; i < 8; ++i) atomicAdd(&g_fc_prof[i], (unsigned long long)prof[i]); atomicAdd(&g_fc_prof[8], (unsigned long long)n_mine); }
-#endif
         // The two groups' results for a row are combined like two splits: group 1 hands its maximum, sum and O over
         // through the (now idle) stages, group 0 adds and stores.  Both reach the barrier whatever happened before.
-        float* xo = reinterpret_cast<float*>(stages);              // [128 rows][128] + [128] m + [128] l: 66.5 KB of the ring's 96
+        float* xo = reinterpret_cast<float*>(stages);              // [128 rows][128] + [128] m + [128] l: 66.5 KB of the ring's 128
         asm volatile("bar.sync 3, %0;" ::"n"(2 * FC_ROWS) : "memory");          // both groups are done with the ring
         if (g == 1) {
 #pragma unroll
