@@ -11,11 +11,12 @@
 //                        threads read back and add to their row of O in registers (scaled by the maximum's change)
 // Warp 0 feeds key/value tiles by TMA exactly as the mma.sync kernels do (one box per page, key/value and
 // 64-column half onto a full/empty mbarrier ring); warp 1 allocates tensor memory and issues the MMAs;
-// warps 4-11 are the softmax rows.  Both MMA operands must be K-major here: Q [rows][d] and K [keys][d] are,
-// P [rows][keys] is written so, and V [keys][d] is turned into V^T [d][keys] in shared memory by the softmax
-// warps (ldmatrix.trans + stmatrix, 8 x 8 blocks) while the tensor core computes S.
+// warps 4-11 are the softmax rows.  Q [rows][d], K [keys][d] and P [rows][keys] are K-major operands (the
+// descriptor form of the GEMM); V [keys][d] is used as it lands, as an MN-major operand (instruction
+// descriptor bit 16; in the shared-memory descriptor the leading offset steps to the second 64 dims, the stride
+// offset to the next 8 keys) - nothing is transposed.
 //
-// Two tiles are in flight: S, P, V^T and the P V accumulator exist twice, and so do the rows - two groups of four
+// Two tiles are in flight: S, P and the P V accumulator exist twice, and so do the rows - two groups of four
 // warps take the even and the odd tiles, each with its own running maximum, sum and O, which are combined at the end
 // (as the splits of flash decoding are).  While one group waits for its MMA the other computes, and every
 // scheduler of the SM has two warps to choose from.  The MMA warp computes the scores of tile i+1 before the
@@ -30,7 +31,7 @@
 #define FC_ROWS 128                           // query rows per CTA
 #define FC_D 128
 #define FC_THREADS 384                        // a control group (TMA warp, MMA warp, two idle) and two groups of four row warps
-#define FC_NST 4
+#define FC_NST 5
 #define FC_KHALF (FC_BN * 128)                // 64 keys x 128 bytes: one 64-column half of a key (or value) tile
 #define FC_KV_BYTES (2 * FC_KHALF)            // a key tile: two halves
 #define FC_STAGE (2 * FC_KV_BYTES)            // keys and values
@@ -60,14 +61,6 @@ struct FcShared {
 // swizzle; chunks 8.. lie in the next 64-column half, half_bytes further
 __device__ __forceinline__ uint32_t fc_off(int row, int c, int half_bytes) {
     return (uint32_t)((c >> 3) * half_bytes + row * 128 + (((c & 7) ^ (row & 7)) << 4));
-}
-__device__ __forceinline__ void fc_ldsm_x4_trans(uint32_t (&r)[4], uint32_t addr) {
-    asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];"
-                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(addr));
-}
-__device__ __forceinline__ void fc_stsm_x4(uint32_t addr, const uint32_t (&r)[4]) {
-    asm volatile("stmatrix.sync.aligned.m8n8.x4.shared.b16 [%0], {%1,%2,%3,%4};"
-                 ::"r"(addr), "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]) : "memory");
 }
 // 2^x by the special-function unit alone (one instruction; exp2f adds range handling around it).  The arguments
 // here are <= 0 or -inf, where it is accurate to two units in the last place - far inside bfloat16's rounding of P.
@@ -109,16 +102,15 @@ fa_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_kv, const FcArgs a)
     unsigned char* stages = smem;                                  // [FC_NST][K half 0, K half 1, V half 0, V half 1]
     unsigned char* sQ = stages + FC_NST * FC_STAGE;                // two halves of [128 rows][64 dims]
     unsigned char* sP = sQ + 2 * FC_QHALF;                         // two of [128 rows][64 keys]
-    unsigned char* sVt = sP + 2 * FC_QHALF;                        // two of [128 dims][64 keys]
-    FcShared* sh = (FcShared*)(sVt + 2 * FC_QHALF);
-    const uint32_t stages_u = smem_u32(stages), sQ_u = smem_u32(sQ), sP_u = smem_u32(sP), sVt_u = smem_u32(sVt);
+    FcShared* sh = (FcShared*)(sP + 2 * FC_QHALF);
+    const uint32_t stages_u = smem_u32(stages), sQ_u = smem_u32(sQ), sP_u = smem_u32(sP);
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     volatile int* abort_flag = &sh->abort_flag;
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < FC_NST; ++s) {
             mbar_init(smem_u32(&sh->full[s]), 1);
-            mbar_init(smem_u32(&sh->empty[s]), 1 + 4);             // the MMA warp's commit (keys) + the four row warps (values)
+            mbar_init(smem_u32(&sh->empty[s]), 2);                 // the MMA warp's commits: scores done (keys), P V done (values)
         }
         for (int b = 0; b < 2; ++b) {
             mbar_init(smem_u32(&sh->s_full[b]), 1);
@@ -234,7 +226,7 @@ fa_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_kv, const FcArgs a)
     } else if (warp == 1) {
         // ---- MMA issuer ----------------------------------------------------------------------------------------
         if (lane == 0) {
-            constexpr uint32_t idesc_s = make_idesc(FC_BN), idesc_o = make_idesc(FC_D);
+            constexpr uint32_t idesc_s = make_idesc(FC_BN);
             // S(i) = Q K(i)^T into score buffer i & 1: d = 128 is two 64-column halves of four 16-wide steps each
             auto scores = [&](int i) -> bool {
                 const int s = i % FC_NST;
@@ -249,7 +241,7 @@ fa_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_kv, const FcArgs a)
                         tc_mma_bf16(tmem + (uint32_t)((i & 1) * FC_BN), dq + (uint64_t)(k * 2), dk + (uint64_t)(k * 2), idesc_s, (h | k) != 0);
                 }
                 tc_commit(smem_u32(&sh->s_full[i & 1]));
-                tc_commit(smem_u32(&sh->empty[s]));                // the keys of this stage are read once these MMAs are done
+                tc_commit(smem_u32(&sh->empty[s]));                // the keys of this stage are read once these MMAs are done ...
                 return true;
             };
             bool ok = n_tiles > 0 && scores(0);
@@ -260,11 +252,18 @@ fa_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_kv, const FcArgs a)
                 // O_tile(it) = P V once the rows have written P and V^T (the accumulator was read two tiles ago)
                 if (!fc_wait(smem_u32(&sh->p_full[it & 1]), (it >> 1) & 1, abort_flag, 13)) break;
                 tc_fence_after();
-                const uint64_t dp = make_smem_desc(sP_u + (it & 1) * FC_QHALF), dv = make_smem_desc(sVt_u + (it & 1) * FC_QHALF);
+                // P [rows][keys] is a K-major operand; V [keys][d] as it lies in the stage is an MN-major one: a key's 64
+                // dims (128 bytes) contiguous, keys 128 bytes apart, groups of 8 keys 1024 bytes apart (SBO), the second
+                // 64 dims a half tile further (LBO); an MMA takes 16 keys = 2048 bytes
+                const uint64_t dp = make_smem_desc(sP_u + (it & 1) * FC_QHALF);
+                const uint32_t sVs = stages_u + (it % FC_NST) * FC_STAGE + FC_KV_BYTES;
+                const uint64_t dv = (uint64_t)((sVs >> 4) & 0x3FFFu) | ((uint64_t)(FC_KHALF >> 4) << 16) | ((uint64_t)(1024 >> 4) << 32) | (1ull << 46) | (2ull << 61);
+                constexpr uint32_t idesc_mn = make_idesc(FC_D) | (1u << 16);       // B is MN-major
 #pragma unroll
                 for (int k = 0; k < 4; ++k)
-                    tc_mma_bf16(tmem + (uint32_t)(2 * FC_BN + (it & 1) * FC_D), dp + (uint64_t)(k * 2), dv + (uint64_t)(k * 2), idesc_o, k != 0);
+                    tc_mma_bf16(tmem + (uint32_t)(2 * FC_BN + (it & 1) * FC_D), dp + (uint64_t)(k * 2), dv + (uint64_t)(k * (2048 >> 4)), idesc_mn, k != 0);
                 tc_commit(smem_u32(&sh->o_full[it & 1]));
+                tc_commit(smem_u32(&sh->empty[it % FC_NST]));      // ... and its values once these are
             }
         }
     }
@@ -286,13 +285,11 @@ fa_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_kv, const FcArgs a)
         const uint32_t lane_base = tmem + ((uint32_t)(quad * 32) << 16);
         const uint32_t s_col = (uint32_t)(g * FC_BN), o_col = (uint32_t)(2 * FC_BN + g * FC_D);
         unsigned char* sPg = sP + g * FC_QHALF;
-        const uint32_t sVt_g = sVt_u + g * FC_QHALF;
         bool ok = true;
         for (int it = g; it < n_tiles; it += 2) {
             const int s = it % FC_NST;
             const uint32_t par = (uint32_t)((it >> 1) & 1);
-            if (!fc_wait(smem_u32(&sh->full[s]), (it / FC_NST) & 1, abort_flag, 14)) { ok = false; break; }
-            // O += P V of this group's tile before: its accumulator, P and V^T are about to be used again
+            // O += P V of this group's tile before: its accumulator and P are about to be used again
             if (it >= 2) {
                 if (!fc_wait(smem_u32(&sh->o_full[g]), par ^ 1, abort_flag, 16)) { ok = false; break; }
                 tc_fence_after();
@@ -309,37 +306,15 @@ fa_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_kv, const FcArgs a)
             }
             const int k0 = (t_begin + it) * FC_BN;
             unsigned char* sV = stages + s * FC_STAGE + FC_KV_BYTES;
-            const bool tail = k0 + FC_BN > kv_end;
-            if (tail) {
-                // the request's last tile: slots of its last page beyond its length hold foreign data
+            if (k0 + FC_BN > kv_end) {
+                // the request's last tile: slots of its last page beyond its length hold foreign data - the values
+                // there are zeroed before the tensor core multiplies them (by P = 0, but 0 x NaN is NaN)
+                if (!fc_wait(smem_u32(&sh->full[s]), (it / FC_NST) & 1, abort_flag, 14)) { ok = false; break; }
                 for (int i = et; i < FC_BN * 16; i += FC_ROWS) {
                     const int r = i / 16, c = i % 16;
                     if (k0 + r >= kv_end) *reinterpret_cast<uint4*>(sV + fc_off(r, c, FC_KHALF)) = make_uint4(0, 0, 0, 0);
                 }
-                if (g == 0) asm volatile("bar.sync 1, %0;" ::"n"(FC_ROWS) : "memory");
-                else asm volatile("bar.sync 2, %0;" ::"n"(FC_ROWS) : "memory");
             }
-            // V [keys][dims] -> V^T [dims][keys], 8 x 8 blocks: each warp takes 4 of the 16 dim-blocks, and per
-            // instruction the four key-blocks of half a tile
-            {
-                const uint32_t sV_u = stages_u + s * FC_STAGE + FC_KV_BYTES;
-                uint32_t r[8][4];
-#pragma unroll
-                for (int i = 0; i < 8; ++i) {
-                    const int dblk = quad * 4 + (i >> 1), kq = i & 1;           // dims 8*dblk .. +7, keys 32*kq .. +31
-                    // matrix j (lanes 8j..8j+7 give its rows): keys 32*kq + 8*j + i, dims 8*dblk..
-                    fc_ldsm_x4_trans(r[i], sV_u + fc_off(32 * kq + 8 * (lane >> 3) + (lane & 7), dblk, FC_KHALF));
-                }
-#pragma unroll
-                for (int i = 0; i < 8; ++i) {
-                    const int dblk = quad * 4 + (i >> 1), kq = i & 1;
-                    // transposed: matrix j holds [dim i][key 8j..8j+7] -> row dim 8*dblk + i, key chunk 4*kq + j
-                    fc_stsm_x4(sVt_g + fc_off(8 * dblk + (lane & 7), 4 * kq + (lane >> 3), 0), r[i]);
-                }
-            }
-            if (tail) asm volatile("fence.proxy.async.shared::cta;" ::: "memory");   // the zeroing, before the stage is refilled
-            __syncwarp();
-            if (lane == 0) mbar_arrive(smem_u32(&sh->empty[s]));                // this warp is done with the stage's values
             // S: this row's 64 scores
             if (!fc_wait(smem_u32(&sh->s_full[g]), par, abort_flag, 15)) { ok = false; break; }
             tc_fence_after();
@@ -376,7 +351,7 @@ fa_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_kv, const FcArgs a)
             }
             const float sum = (sum4[0] + sum4[1]) + (sum4[2] + sum4[3]);
             l = l * alpha + sum;
-            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");       // P and V^T before the tensor core reads them
+            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");       // P (and zeroed value rows) before the tensor core reads them
             tc_fence_before();                                     // S is read: the group's next scores may overwrite it
             __syncwarp();
             if (lane == 0) mbar_arrive(smem_u32(&sh->p_full[g]));
@@ -403,7 +378,7 @@ fa_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_kv, const FcArgs a)
         }
         // The two groups' results for a row are combined like two splits: group 1 hands its maximum, sum and O over
         // through the (now idle) stages, group 0 adds and stores.  Both reach the barrier whatever happened before.
-        float* xo = reinterpret_cast<float*>(stages);              // [128 rows][128] + [128] m + [128] l: 66.5 KB of the ring's 128
+        float* xo = reinterpret_cast<float*>(stages);              // [128 rows][128] + [128] m + [128] l: 66.5 KB of the ring's 160
         asm volatile("bar.sync 3, %0;" ::"n"(2 * FC_ROWS) : "memory");          // both groups are done with the ring
         if (g == 1) {
 #pragma unroll
@@ -471,7 +446,7 @@ extern "C" int rb_fa_prefill_tc(const void* q, const void* cache, long long num_
     CUtensorMap map;
     const int box_rows = page_size < FC_BN ? page_size : FC_BN;
     if (rb_tensor_map_bf16(cache, num_pages * 2LL * KH * page_size, d, d, box_rows, &map)) return -1;
-    constexpr size_t smem = (size_t)FC_NST * FC_STAGE + 6 * FC_QHALF + sizeof(FcShared) + 1024;
+    constexpr size_t smem = (size_t)FC_NST * FC_STAGE + 4 * FC_QHALF + sizeof(FcShared) + 1024;
     static bool done = false;
     if (!done) {
         cudaError_t e = cudaFuncSetAttribute(fa_prefill_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
