@@ -378,15 +378,34 @@ def fa_prefill(q, cache, block_table, cu_q, kv_len, out, first_entry: int, n_ent
 USE_TMA_ATTENTION = os.environ.get("REINFER_B200_TMA_ATTENTION", "1") != "0"
 ATTN_CLUSTER_MERGE = os.environ.get("REINFER_B200_ATTN_CLUSTER", "1") != "0"
 USE_TC_ATTENTION = os.environ.get("REINFER_B200_TC_ATTENTION", "1") != "0"
-def decode_splits(ctas: int, tiles: int, slots: int = DECODE_SLOTS) -> int:
-    """How many CTAs share one (request, kv head)'s keys.  Model of the launch's time: waves of
-    `slots` resident CTAs, each CTA walking tiles/n tiles plus about 2.5 tile-times of fill, drain
-    and merge, then a merge kernel that walks the n partial results; the split count with the
-    least estimate wins (ties to the smaller)."""
+def decode_splits(ctas: int, tiles: int, slots: int = DECODE_SLOTS, head_dim: int = 128) -> int:
+    """How many CTAs share one (request, kv head)'s keys: the split count with the least estimated time (ties to
+    the smaller).  The estimate is fitted to measurements of the kernel at batch 1..64 and 4k..32k keys, alone
+    and inside whole decode steps:
+      - every resident CTA has the first three tiles of its share on their way before the kernels in front of it
+        have finished; what is left streams at the memory bandwidth, less what the CTAs' fill and drain cost,
+        which weighs the more the fewer tiles a CTA walks:   bytes left / 6.5 TB/s * (1 + 2.7 / tiles per CTA)
+      - a CTA alone streams a 64-key tile of 128-wide heads in about a microsecond and needs about five to start
+        and finish:                                           (tiles per CTA - 3) * 1 us + 5 us
+      - the larger of the two counts, plus the merge: about 2 us inside a cluster (up to 8 splits, all CTAs
+        resident at once), else a merge kernel of about 3.5 us + 0.1 us per split.
+    (Whole "waves" of CTAs do not matter: a part-filled last wave just gives its CTAs more bandwidth each.)"""
+    tile_us = head_dim / 128.0                              # a lone CTA's time for one tile
+    tile_bw_us = 64 * head_dim * 4 / 6.5e6                  # one tile's bytes at the device's bandwidth
+    ahead = 3                                               # tiles a CTA requests before it has to wait
     best, best_cost = 1, None
     for n in range(1, max(1, min(64, tiles)) + 1):
-        waves = -(-ctas * n // slots)
-        cost = waves * (tiles / n + 2.5) + 0.12 * n        # + the merge kernel's walk over n partial results
+        per = -(-tiles // n)
+        early = min(ctas * tiles, min(ctas * n, slots) * ahead)
+        t_bw = (ctas * tiles - early) * tile_bw_us * (1.0 + 2.7 / per)
+        t_lat = max(0, per - ahead) * tile_us + 5.0
+        if n == 1:
+            merge = 0.0
+        elif n <= 8 and ctas * n <= slots and ATTN_CLUSTER_MERGE:
+            merge = 2.0
+        else:
+            merge = 3.5 + 0.1 * n
+        cost = max(t_bw, t_lat) + merge
         if best_cost is None or cost < best_cost - 1e-9:
             best, best_cost = n, cost
     return best
@@ -408,7 +427,7 @@ def attention(ctx, q: torch.Tensor, cache: torch.Tensor, group, out: torch.Tenso
     if n_dec:
         ctas = n_dec * KH * (QH // KH // gc)
         tiles = -(-ctx.max_kv_len // 64)
-        n_splits = decode_splits(ctas, tiles)
+        n_splits = decode_splits(ctas, tiles, head_dim=d)
         decode = fa_decode_tma if (tma_pages(group.page_size) and USE_TMA_ATTENTION) else fa_decode
         decode(q, cache, group.block_table, ctx.cu_q, ctx.kv_len, out, 0, n_dec, 0, n_splits, QH, KH, d,
                group.page_size, window, scale)
