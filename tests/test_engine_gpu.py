@@ -190,3 +190,36 @@ def test_storage_and_compute_dtype_may_differ(models, store, dtype):
         assert engine.model.layers[0].mixer.w_qkv.dtype == torch.float32
     got = run_steps(engine, steps)
     compare(got, truth(model_dir, seqs), TOL[dtype])
+
+
+@pytest.mark.parametrize("n_requests", [11, 37])
+def test_many_requests_decode_together_with_heads_of_128(tmp_path, n_requests):
+    """More requests than the mixed cuts hold, heads of 128 (the head size of the tcgen05 prefill attention and of
+    the vectorised head norm): prompts of lengths around the 64-key tile and page edges come in two at a time, then
+    all requests decode together - a batch that fills its CUDA-graph bucket only in part (rows of padding), with
+    and without key splits - and every logit row is compared with the plain implementation."""
+    from reinfer_b200.config import Qwen3Config
+    from reinfer_b200.engine import Engine
+    from reinfer_b200.weights import write_random_model
+    raw = dict(architectures=["Qwen3ForCausalLM"], num_hidden_layers=2, hidden_size=256, num_attention_heads=4,
+               num_key_value_heads=2, head_dim=128, intermediate_size=384, vocab_size=1003, rope_theta=1e6,
+               rms_norm_eps=1e-6, tie_word_embeddings=True, max_position_embeddings=1024)
+    d = write_random_model(str(tmp_path / "m"), Qwen3Config.from_dict(raw), seed=9, dtype=torch.bfloat16)
+    g = torch.Generator().manual_seed(4)
+    lens = [1, 2, 63, 64, 65, 127, 128, 129, 200, 31, 300]
+    seqs = {f"r{i}": torch.randint(0, 1003, (lens[i % len(lens)] + 6,), generator=g).tolist() for i in range(n_requests)}
+    cfg, w = plain.read_model(d)
+    want = {r: plain.forward(cfg, w, t, dtype=torch.float32).double() for r, t in seqs.items()}
+    names = list(seqs)
+    steps = []
+    for i in range(0, n_requests, 2):                                   # prompts, two requests a step
+        steps.append(([(r, seqs[r][:-6], [len(seqs[r]) - 7]) for r in names[i:i + 2]], []))
+    for k in range(6, 0, -1):                                           # then everybody decodes
+        steps.append(([(r, [seqs[r][-k]], [0]) for r in names], names if k == 1 else []))
+    engine = Engine.from_model_dir(d, dtype="bfloat16", page_size=64, max_tokens=sum(-(-len(t) // 64) * 64 for t in seqs.values()),
+                                   max_num_seqs=n_requests)
+    got = run_steps(engine, steps)
+    assert len(got) == 7 * n_requests
+    compare(got, want, TOL["bfloat16"])
+    from reinfer_b200 import ops
+    assert ops.kernel_error() == 0
