@@ -273,6 +273,35 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
             const int et = threadIdx.x - 64;                       // 0..127
             const int f4 = (et & 31) * 4, tsub = et >> 5;
             const int feat = n0 + f4;
+            if (!DUAL && feat + 3 < N && (ldc & 3) == 0 && ((uintptr_t)C & 15) == 0 && out_mode != 0) {
+                // float results, four whole features: two tokens a trip (their partial sums from every rank and, for
+                // an accumulating product, the residual's old values are all on their way before the first is used)
+                float* Cf = (float*)C;
+                for (int cb0 = split + tsub * csplit; cb0 < BN && t0 + cb0 < T; cb0 += 8 * csplit) {
+                    const int cb1 = cb0 + 4 * csplit;
+                    const bool two = cb1 < BN && t0 + cb1 < T;
+                    float4 pa[8], pb[8];
+                    const uint32_t m0 = smem_base + (uint32_t)(cb0 * TC_BM + f4) * 4, m1 = smem_base + (uint32_t)(cb1 * TC_BM + f4) * 4;
+#pragma unroll
+                    for (int r = 0; r < 8; ++r) {
+                        pa[r] = r < csplit ? ld_cluster_f32x4(m0, (uint32_t)r) : make_float4(0.f, 0.f, 0.f, 0.f);
+                        pb[r] = (two && r < csplit) ? ld_cluster_f32x4(m1, (uint32_t)r) : make_float4(0.f, 0.f, 0.f, 0.f);
+                    }
+                    float4* d0 = reinterpret_cast<float4*>(Cf + (size_t)(t0 + cb0) * ldc + feat);
+                    float4* d1 = reinterpret_cast<float4*>(Cf + (size_t)(t0 + cb1) * ldc + feat);
+                    float4 oa = make_float4(0.f, 0.f, 0.f, 0.f), ob = oa;
+                    if (out_mode == 2) { oa = *d0; if (two) ob = *d1; }
+                    float4 va = pa[0], vb = pb[0];
+#pragma unroll
+                    for (int r = 1; r < 8; ++r) {
+                        va.x += pa[r].x; va.y += pa[r].y; va.z += pa[r].z; va.w += pa[r].w;
+                        vb.x += pb[r].x; vb.y += pb[r].y; vb.z += pb[r].z; vb.w += pb[r].w;
+                    }
+                    const float fa = sh->row_scale[cb0], fb = two ? sh->row_scale[cb1] : 0.0f;
+                    *d0 = make_float4(oa.x + va.x * fa, oa.y + va.y * fa, oa.z + va.z * fa, oa.w + va.w * fa);
+                    if (two) *d1 = make_float4(ob.x + vb.x * fb, ob.y + vb.y * fb, ob.z + vb.z * fb, ob.w + vb.w * fb);
+                }
+            } else
             for (int cb = split + tsub * csplit; cb < BN && t0 + cb < T; cb += 4 * csplit) {
                 float4 part[8], part2[8];
                 const uint32_t mine = smem_base + (uint32_t)(cb * TC_BM + f4) * 4;
