@@ -77,15 +77,15 @@ class Attention(Mixer):
     def forward(self, ctx, xn, residual, cache) -> None:
         T, QH, KH, d = xn.shape[0], self.QH, self.KH, self.d
         g = cache.group
-        qkv = matmul(ctx, xn, self.w_qkv)                                     # [T, (QH+2KH) d]
-        xn = qkv                                                              # (dtype and device from here on)
-        q = torch.empty((T, QH, d), dtype=xn.dtype, device=xn.device)
+        qkv = matmul(ctx, xn, self.w_qkv)                                     # [T, (QH+2KH) d]; xn may be RowScaled
+        act, dev = qkv.dtype, qkv.device
+        q = torch.empty((T, QH, d), dtype=act, device=dev)
         fused = self.position.fused_rotary() if self.position is not None else (None, 0)
         slots = g.kv_slot if cache.write else None
         if fused is not None:
             inv_freq, rot = fused
             cs = None
-            if rot == d and d % 128 == 0 and xn.dtype == torch.bfloat16 and inv_freq is not None and T > 64:
+            if rot == d and d % 128 == 0 and act == torch.bfloat16 and inv_freq is not None and T > 64:
                 # the angles depend on the step's positions only: for a large step the first layer tabulates
                 # their cosines and sines (a small step computes them in place and saves the launch)
                 key = ("rope", getattr(self.position, "theta", None), rot, inv_freq.numel())    # the same for every layer
@@ -96,13 +96,13 @@ class Attention(Mixer):
                                    cache.kv, QH, KH, d, rot, g.page_size, self.eps, cs_table=cs)
         else:
             # an encoding that is not a plain rotation: norm, then the part's own apply(), then append
-            k = torch.empty((T, KH, d), dtype=xn.dtype, device=xn.device)
+            k = torch.empty((T, KH, d), dtype=act, device=dev)
             ops.qknorm_rope_append(qkv, self.q_norm_w, self.k_norm_w, None, None, None, q, None,
                                    QH, KH, d, 0, g.page_size, self.eps, k_out=k)
             self.position.apply(ctx, q, k, ctx.positions)
             if cache.write:
                 ops.kv_append(k.view(T, KH * d), qkv[:, (QH + KH) * d:], g.kv_slot, cache.kv, KH, d, g.page_size)
-        attn = torch.empty((T, QH, d), dtype=xn.dtype, device=xn.device)
+        attn = torch.empty((T, QH, d), dtype=act, device=dev)
         ops.attention(ctx, q, cache.kv, g, attn, QH, KH, d, self.window or 0, self.scale)
         return matmul_into_residual(ctx, attn.view(T, QH * d), self.w_o, residual)
 
