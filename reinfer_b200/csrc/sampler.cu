@@ -34,6 +34,9 @@ struct RbSampleParams {          // one per row; mirrored by ctypes in sampling/
     int hist_len;                // valid entries of this row's history (<= hist_cap)
     unsigned long long seed;
     unsigned long long step;     // index of this draw in the request's stream
+    const int2* bias;            // bias_len pairs (token id, float bits): added to the logits first of all
+    int bias_len;
+    int reserved;
 };
 
 __device__ __forceinline__ unsigned long long sp_mix(unsigned long long z) {
@@ -102,8 +105,9 @@ sample_kernel(const float* __restrict__ logits, long long ld_logits, const int* 
     const bool penalties = P.hist_len > 0 &&
         (P.repeat_penalty > 1.0f || P.frequency_penalty != 0.0f || P.presence_penalty != 0.0f);
     const bool greedy = !(P.temperature > 0.0f);
+    const bool biased = P.bias_len > 0 && P.bias != nullptr;
 
-    if (greedy && !penalties) {                                // no scratch needed
+    if (greedy && !penalties && !biased) {                     // no scratch needed
         float bv = -INFINITY; int bi = 0x7fffffff;
         for (int i = tid; i < vocab; i += SP_THREADS) {
             const float v = lg[i];
@@ -120,6 +124,14 @@ sample_kernel(const float* __restrict__ logits, long long ld_logits, const int* 
         w[i] = isfinite(v) ? v : -FLT_MAX;
     }
     __syncthreads();
+    if (biased) {
+        // logit_bias comes first in the chain (sampler_kernel.cu:20-24,198-205); ids are distinct, one thread each
+        for (int j = tid; j < P.bias_len; j += SP_THREADS) {
+            const int2 b = P.bias[j];
+            if (b.x >= 0 && b.x < vocab && w[b.x] != -FLT_MAX) w[b.x] += __int_as_float(b.y);
+        }
+        __syncthreads();
+    }
     if (penalties) {
         // one thread per history entry; the first occurrence of a token applies the penalty
         const int* hist = history + (size_t)r * hist_cap;

@@ -17,6 +17,7 @@ class SamplingParams:
     repeat_last_n: int = 64
     frequency_penalty: float = 0.0
     presence_penalty: float = 0.0
+    logit_bias: Tuple[Tuple[int, float], ...] = ()   # (token id, addend) pairs, added to the logits before all else
     seed: Optional[int] = None            # None: derived from the engine's seed and the request's arrival number
     max_tokens: int = 256                 # hard cap of new tokens
     stop_token_ids: Tuple[int, ...] = ()
@@ -27,5 +28,9 @@ class SamplingParams:
             raise ValueError("max_tokens must be >= 0")
         if self.repeat_last_n < 0 or self.repeat_last_n > 64:
             raise ValueError("repeat_last_n must be in 0..64")
+        if len(self.logit_bias) > 1024:
+            raise ValueError("logit_bias takes at most 1024 entries")
+        if len({int(i) for i, _ in self.logit_bias}) != len(self.logit_bias) or any(int(i) < 0 for i, _ in self.logit_bias):
+            raise ValueError("logit_bias: token ids must be distinct and non-negative")
         if self.temperature != self.temperature:
             raise ValueError("temperature is NaN")

@@ -20,7 +20,9 @@ GOLDEN = 0x9E3779B97F4A7C15
 
 RECORD = np.dtype([("temperature", "<f4"), ("top_k", "<i4"), ("top_p", "<f4"), ("min_p", "<f4"),
                    ("repeat_penalty", "<f4"), ("frequency_penalty", "<f4"), ("presence_penalty", "<f4"),
-                   ("hist_len", "<i4"), ("seed", "<u8"), ("step", "<u8")])
+                   ("hist_len", "<i4"), ("seed", "<u8"), ("step", "<u8"), ("bias", "<u8"), ("bias_len", "<i4"),
+                   ("reserved", "<i4")])
+BIAS_CAP = 1024                     # logit_bias entries a request may bring
 
 
 def _mix(z: int) -> int:
@@ -51,6 +53,7 @@ class Sampler:
         self._host_params = torch.empty(self.max_rows * RECORD.itemsize, dtype=torch.uint8, pin_memory=True)
         self._host_hist = torch.empty((self.max_rows, HIST_CAP), dtype=torch.int32, pin_memory=True)
         self._host_out = torch.empty(self.max_rows, dtype=torch.int32, pin_memory=True)
+        self._host_bias = self._dev_bias = None      # [rows, BIAS_CAP, 2] int32 (id, float bits): made when first needed
         self._done = torch.cuda.Event()
 
     def device_records(self, params: Sequence[SamplingParams], seeds: Sequence[int], steps: Sequence[int]) -> torch.Tensor:
@@ -58,7 +61,7 @@ class Sampler:
         launch `ops.sample` themselves)."""
         rec = np.zeros(len(params), dtype=RECORD)
         for r, p in enumerate(params):
-            rec[r] = (p.temperature, p.top_k, p.top_p, p.min_p, 1.0, 0.0, 0.0, 0, seeds[r] & _MASK64, steps[r])
+            rec[r] = (p.temperature, p.top_k, p.top_p, p.min_p, 1.0, 0.0, 0.0, 0, seeds[r] & _MASK64, steps[r], 0, 0, 0)
         return torch.from_numpy(rec.view(np.uint8).copy()).to(self.device)
 
     def sample(self, logits: torch.Tensor, params: Sequence[SamplingParams], seeds: Sequence[int],
@@ -93,7 +96,7 @@ class Sampler:
         else:
             for r, p in enumerate(params):
                 rec[r] = (p.temperature, p.top_k, p.top_p, p.min_p, p.repeat_penalty, p.frequency_penalty,
-                          p.presence_penalty, 0, 0, 0)
+                          p.presence_penalty, 0, 0, 0, 0, 0, 0)
         rec["seed"] = np.fromiter((sd & _MASK64 for sd in seeds), dtype=np.uint64, count=rows)
         rec["step"] = np.fromiter(steps, dtype=np.uint64, count=rows)
         for r, p in enumerate(params):
@@ -103,6 +106,20 @@ class Sampler:
                 hist[r, :len(h)] = h
                 rec[r]["hist_len"] = len(h)
                 any_hist = any_hist or bool(h)
+        if any(p.logit_bias for p in params):
+            # logit_bias (sampler_kernel.cu:161-163,198-205): the pairs go up beside the records, which point at them
+            if self._dev_bias is None:
+                self._host_bias = torch.zeros((self.max_rows, BIAS_CAP, 2), dtype=torch.int32, pin_memory=True)
+                self._dev_bias = torch.zeros((self.max_rows, BIAS_CAP, 2), dtype=torch.int32, device=self.device)
+            hb = self._host_bias.numpy()
+            for r, p in enumerate(params):
+                n = len(p.logit_bias)
+                if n:
+                    hb[r, :n, 0] = np.fromiter((int(i) for i, _ in p.logit_bias), dtype=np.int32, count=n)
+                    hb[r, :n, 1] = np.fromiter((float(v) for _, v in p.logit_bias), dtype=np.float32, count=n).view(np.int32)
+                    rec[r]["bias"] = self._dev_bias.data_ptr() + r * BIAS_CAP * 8
+                    rec[r]["bias_len"] = n
+            self._dev_bias[:rows].copy_(self._host_bias[:rows], non_blocking=True)
         self._host_params.numpy()[:rows * RECORD.itemsize] = rec.view(np.uint8)
         dparams = self._host_params[:rows * RECORD.itemsize].to(self.device, non_blocking=True)
         dhist = self._host_hist[:rows].to(self.device, non_blocking=True) if any_hist else None

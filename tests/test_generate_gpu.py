@@ -129,6 +129,16 @@ def test_sampler_options(model_dirs):
     assert s.sample(rep, [SamplingParams(repeat_penalty=1.5)], [0], [0], [[7, 7, 3]]) == [8]
     assert s.sample(rep, [SamplingParams(presence_penalty=0.5)], [0], [0], [[7]]) == [8]
     assert s.sample(rep, [SamplingParams(repeat_penalty=1.5)], [0], [0], [[3, 4]]) == [7]
+    # logit_bias is added before everything else: it can promote a token, remove one, and comes before the penalties
+    assert s.sample(rep, [SamplingParams(logit_bias=((500, 10.0),))], [0], [0]) == [500]
+    assert s.sample(rep, [SamplingParams(logit_bias=((7, -5.0), (900, 0.5)))], [0], [0]) == [8]
+    assert s.sample(rep, [SamplingParams(logit_bias=((8, 0.2),), repeat_penalty=1.5)], [0], [0], [[8]]) == [7]   # (1.9+0.2)/1.5 < 2
+    two = s.sample(rep.expand(2, V).contiguous(), [SamplingParams(logit_bias=((9, 5.0),)), SamplingParams()], [0, 0], [0, 0])
+    assert two == [9, 7]                                                               # a row's bias is its own
+    draws = {s.sample(rep, [SamplingParams(temperature=1.0, logit_bias=((3, 50.0),))], [5], [i])[0] for i in range(20)}
+    assert draws == {3}
+    with pytest.raises(ValueError):
+        SamplingParams(logit_bias=((1, 0.5), (1, 0.7))).validate()
 
 
 def test_temperature_generation_is_seeded_and_batch_independent(model_dirs):

@@ -17,7 +17,7 @@ def _records(rows, temperature, seed, step0):
     rec = np.zeros(rows, dtype=RECORD)
     for r in range(rows):
         rec[r] = (temperature, 40 if temperature > 0 else 0, 0.9 if temperature > 0 else 1.0, 0.0, 1.3, 0.0, 0.0, 3,
-                  seed + r, step0 + r)
+                  seed + r, step0 + r, 0, 0, 0)                        # (no logit bias)
     return torch.from_numpy(rec.view(np.uint8).copy()).cuda()
 
 
