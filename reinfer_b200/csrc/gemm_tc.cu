@@ -745,6 +745,19 @@ extern "C" int rb_gemm_bf16(const void* X, const void* W, void* C, int c_dtype, 
     CUtensorMap mw, mx;
     if (rb_tensor_map_bf16(W, N, K, ldw, TC_BM, &mw)) return -1;
     if (T > 256 && force_splits == 0 && g_tc_persistent) {          // several token tiles: the persistent schedule
+        // Token tiles of 256 or of 128: whichever needs less time for its rounds over the SMs.  A 128 x 128 tile
+        // reads as many operand bytes from shared memory per MMA as a 128 x 256 one for half the work, so its
+        // rounds count 1.36 times their width; the wider tile wins ties (the weights are read once less often).
+        int dev = 0, sms = 148;
+        cudaGetDevice(&dev);
+        cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+        const long long n_tiles = rb_ceil_div(N, TC_BM);
+        const double c256 = (double)rb_ceil_div((long long)rb_ceil_div(T, 256) * n_tiles, sms) * 256.0;
+        const double c128 = (double)rb_ceil_div((long long)rb_ceil_div(T, 128) * n_tiles, sms) * 128.0 * 1.36;
+        if (c128 < c256) {
+            if (rb_tensor_map_bf16(X, T, K, ldx, 128, &mx)) return -1;
+            return launch_tc_persistent<128, 5, false>(mw, mx, C, T, N, K, ldc, mode, s);
+        }
         if (rb_tensor_map_bf16(X, T, K, ldx, 256, &mx)) return -1;
         return launch_tc_persistent<256, 4, false>(mw, mx, C, T, N, K, ldc, mode, s);
     }
