@@ -7,8 +7,9 @@
 //     S = Q K^T          tcgen05.mma, 128 x 64 x 128, operands in shared memory, S in tensor memory
 //     P = exp2(S - max)  128 threads, one row each (tcgen05.ld gives a thread its whole row: the row maximum
 //                        and sum need no shuffles), P rounded to bfloat16 into shared memory
-//     O += P V           tcgen05.mma, 128 x 128 x 64, into a second tensor-memory accumulator that the same
-//                        threads read back and add to their row of O in registers (scaled by the maximum's change)
+//     O += P V           tcgen05.mma, 128 x 128 x 64, accumulated in tensor memory over all tiles: P and O are scaled
+//                        to a maximum that follows the true one only when it rose by more than 2^8 (then the row's
+//                        thread rescales its lane of O in tensor memory, which is rare), so the rows read O once, at the end
 // Warp 0 feeds key/value tiles by TMA exactly as the mma.sync kernels do (one box per page, key/value and
 // 64-column half onto a full/empty mbarrier ring); warp 1 allocates tensor memory and issues the MMAs;
 // warps 4-11 are the softmax rows.  Q [rows][d], K [keys][d] and P [rows][keys] are K-major operands (the
@@ -36,6 +37,7 @@
 #define FC_KV_BYTES (2 * FC_KHALF)            // a key tile: two halves
 #define FC_STAGE (2 * FC_KV_BYTES)            // keys and values
 #define FC_QHALF (FC_ROWS * 128)              // 128 rows x 128 bytes
+#define FC_RESCALE 8.0f                       // O is brought to a new maximum only when it rose by more than this (log2)
 #define FC_TMEM_COLS 512                      // S of two tiles: columns 0..127; P V of two tiles: 128..383
 
 struct FcArgs {
@@ -62,6 +64,15 @@ struct FcShared {
 __device__ __forceinline__ uint32_t fc_off(int row, int c, int half_bytes) {
     return (uint32_t)((c >> 3) * half_bytes + row * 128 + (((c & 7) ^ (row & 7)) << 4));
 }
+// Sixteen 32-bit columns of this warp's 32 lanes back into tensor memory (the counterpart of tc_ld16).
+__device__ __forceinline__ void fc_st16(uint32_t taddr, const uint32_t* r) {
+    asm volatile(
+        "tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16};"
+        ::"r"(taddr), "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]),
+          "r"(r[8]), "r"(r[9]), "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15]) : "memory");
+}
+__device__ __forceinline__ void fc_st_wait() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
+
 // 2^x by the special-function unit alone (one instruction; exp2f adds range handling around it).  The arguments
 // here are <= 0 or -inf, where it is accurate to two units in the last place - far inside bfloat16's rounding of P.
 __device__ __forceinline__ float fc_ex2(float x) {
@@ -261,7 +272,7 @@ fa_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_kv, const FcArgs a)
                 constexpr uint32_t idesc_mn = make_idesc(FC_D) | (1u << 16);       // B is MN-major
 #pragma unroll
                 for (int k = 0; k < 4; ++k)
-                    tc_mma_bf16(tmem + (uint32_t)(2 * FC_BN + (it & 1) * FC_D), dp + (uint64_t)(k * 2), dv + (uint64_t)(k * (2048 >> 4)), idesc_mn, k != 0);
+                    tc_mma_bf16(tmem + (uint32_t)(2 * FC_BN + (it & 1) * FC_D), dp + (uint64_t)(k * 2), dv + (uint64_t)(k * (2048 >> 4)), idesc_mn, (it >= 2) || k != 0);
                 tc_commit(smem_u32(&sh->o_full[it & 1]));
                 tc_commit(smem_u32(&sh->empty[it % FC_NST]));      // ... and its values once these are
             }
@@ -278,9 +289,8 @@ fa_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_kv, const FcArgs a)
         const bool live = !none && ti < n_tok;
         const int pos = live ? start_pos + q0 + ti : -1;
         const int lo = a.window > 0 ? max(0, pos - a.window + 1) : 0;
-        float o[FC_D];
-#pragma unroll
-        for (int j = 0; j < FC_D; ++j) o[j] = 0.0f;
+        // m: the maximum that P and O are scaled to (it follows the true maximum only in steps larger than
+        // FC_RESCALE, so that O can stay in tensor memory and be accumulated by the MMA itself); l: the sum in that scale
         float m = -INFINITY, l = 0.0f;
         const uint32_t lane_base = tmem + ((uint32_t)(quad * 32) << 16);
         const uint32_t s_col = (uint32_t)(g * FC_BN), o_col = (uint32_t)(2 * FC_BN + g * FC_D);
@@ -289,36 +299,20 @@ fa_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_kv, const FcArgs a)
         for (int it = g; it < n_tiles; it += 2) {
             const int s = it % FC_NST;
             const uint32_t par = (uint32_t)((it >> 1) & 1);
-            // O += P V of this group's tile before: its accumulator and P are about to be used again
-            if (it >= 2) {
-                if (!fc_wait(smem_u32(&sh->o_full[g]), par ^ 1, abort_flag, 16)) { ok = false; break; }
-                tc_fence_after();
-#pragma unroll
-                for (int c = 0; c < FC_D / 64; ++c) {
-                    uint32_t pv[64];
-#pragma unroll
-                    for (int q4 = 0; q4 < 4; ++q4) tc_ld16(lane_base + o_col + (uint32_t)(c * 64 + q4 * 16), pv + q4 * 16);
-                    tc_ld_wait();
-#pragma unroll
-                    for (int j = 0; j < 64; ++j) o[c * 64 + j] += __uint_as_float(pv[j]);
-                }
-                tc_fence_before();
-            }
             const int k0 = (t_begin + it) * FC_BN;
-            unsigned char* sV = stages + s * FC_STAGE + FC_KV_BYTES;
             if (k0 + FC_BN > kv_end) {
                 // the request's last tile: slots of its last page beyond its length hold foreign data - the values
                 // there are zeroed before the tensor core multiplies them (by P = 0, but 0 x NaN is NaN)
                 if (!fc_wait(smem_u32(&sh->full[s]), (it / FC_NST) & 1, abort_flag, 14)) { ok = false; break; }
+                unsigned char* sV = stages + s * FC_STAGE + FC_KV_BYTES;
                 for (int i = et; i < FC_BN * 16; i += FC_ROWS) {
                     const int r = i / 16, c = i % 16;
                     if (k0 + r >= kv_end) *reinterpret_cast<uint4*>(sV + fc_off(r, c, FC_KHALF)) = make_uint4(0, 0, 0, 0);
                 }
             }
-            // S: this row's 64 scores
+            // S: this row's 64 scores in one go (one wait for tensor memory); maxima and sums in four independent chains
             if (!fc_wait(smem_u32(&sh->s_full[g]), par, abort_flag, 15)) { ok = false; break; }
             tc_fence_after();
-            // the row's 64 scores in one go (one wait for tensor memory); maxima and sums in four independent chains
             const bool edge = k0 + FC_BN - 1 > pos || k0 < lo;     // the tile crosses this row's causal edge or window
             uint32_t sr[FC_BN];
 #pragma unroll
@@ -334,11 +328,35 @@ fa_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_kv, const FcArgs a)
             float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
 #pragma unroll
             for (int j = 0; j < FC_BN; ++j) mx4[j & 3] = fmaxf(mx4[j & 3], __uint_as_float(sr[j]));
-            const float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3]));
-            const float m_new = fmaxf(m, mx * a.scale_log2);       // the scale is positive: the maximum of the scaled scores
-            const float base = m_new == -INFINITY ? 0.0f : m_new;
-            const float alpha = fc_ex2(m - base);                  // m = -inf: 0
-            m = m_new;
+            const float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3])) * a.scale_log2;   // the scale is positive
+            // the scale follows the maximum at once while the row has nothing yet (m = -inf: O and l are zero), else
+            // only when the maximum rose by more than FC_RESCALE - P then stays below 2^FC_RESCALE, which bfloat16
+            // and the float accumulators hold as well as values below 1
+            float alpha = 1.0f;
+            if (m == -INFINITY) m = mx;
+            else if (mx > m + FC_RESCALE) { alpha = fc_ex2(m - mx); m = mx; }
+            const bool rescale = __any_sync(0xffffffffu, alpha != 1.0f);
+            // the product before this one (same accumulator, same P buffer) must be done before either is touched
+            if (it >= 2) {
+                if (!fc_wait(smem_u32(&sh->o_full[g]), par ^ 1, abort_flag, 16)) { ok = false; break; }
+                tc_fence_after();
+            }
+            if (rescale && it >= 2) {
+                // rare: O = O * alpha in tensor memory, every lane of the warp with its own factor (1 for most)
+#pragma unroll
+                for (int c = 0; c < FC_D / 32; ++c) {
+                    uint32_t ov[32];
+                    tc_ld16(lane_base + o_col + (uint32_t)(c * 32), ov);
+                    tc_ld16(lane_base + o_col + (uint32_t)(c * 32 + 16), ov + 16);
+                    tc_ld_wait();
+#pragma unroll
+                    for (int j = 0; j < 32; ++j) ov[j] = __float_as_uint(__uint_as_float(ov[j]) * alpha);
+                    fc_st16(lane_base + o_col + (uint32_t)(c * 32), ov);
+                    fc_st16(lane_base + o_col + (uint32_t)(c * 32 + 16), ov + 16);
+                }
+                fc_st_wait();
+            }
+            const float base = m == -INFINITY ? 0.0f : m;
             float sum4[4] = {0.0f, 0.0f, 0.0f, 0.0f};
 #pragma unroll
             for (int c = 0; c < FC_BN / 8; ++c) {
@@ -349,30 +367,24 @@ fa_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_kv, const FcArgs a)
                 pk.x = fc_pack(p[0], p[1]); pk.y = fc_pack(p[2], p[3]); pk.z = fc_pack(p[4], p[5]); pk.w = fc_pack(p[6], p[7]);
                 *reinterpret_cast<uint4*>(sPg + fc_off(row, c, 0)) = pk;
             }
-            const float sum = (sum4[0] + sum4[1]) + (sum4[2] + sum4[3]);
-            l = l * alpha + sum;
+            l = l * alpha + ((sum4[0] + sum4[1]) + (sum4[2] + sum4[3]));
             asm volatile("fence.proxy.async.shared::cta;" ::: "memory");       // P (and zeroed value rows) before the tensor core reads them
-            tc_fence_before();                                     // S is read: the group's next scores may overwrite it
+            tc_fence_before();                                     // S is read, O (if touched) written: the MMA may go on
             __syncwarp();
             if (lane == 0) mbar_arrive(smem_u32(&sh->p_full[g]));
-            // O follows the maximum only when it moved (alpha == 1 exactly otherwise) for some row of the warp
-            if (__any_sync(0xffffffffu, alpha != 1.0f)) {
-#pragma unroll
-                for (int j = 0; j < FC_D; ++j) o[j] *= alpha;
-            }
         }
-        // the group's last tile
+        // the row of O, once the group's last product is done
+        float o[FC_D];
+#pragma unroll
+        for (int j = 0; j < FC_D; ++j) o[j] = 0.0f;
         const int n_mine = n_tiles > g ? (n_tiles - g + 1) / 2 : 0;
         if (ok && n_mine > 0 && fc_wait(smem_u32(&sh->o_full[g]), (uint32_t)((n_mine - 1) & 1), abort_flag, 17)) {
             tc_fence_after();
 #pragma unroll
             for (int c = 0; c < FC_D / 64; ++c) {
-                uint32_t pv[64];
 #pragma unroll
-                for (int q4 = 0; q4 < 4; ++q4) tc_ld16(lane_base + o_col + (uint32_t)(c * 64 + q4 * 16), pv + q4 * 16);
+                for (int q4 = 0; q4 < 4; ++q4) tc_ld16(lane_base + o_col + (uint32_t)(c * 64 + q4 * 16), reinterpret_cast<uint32_t*>(o) + c * 64 + q4 * 16);
                 tc_ld_wait();
-#pragma unroll
-                for (int j = 0; j < 64; ++j) o[c * 64 + j] += __uint_as_float(pv[j]);
             }
             tc_fence_before();
         }

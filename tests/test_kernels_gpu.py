@@ -529,6 +529,39 @@ def test_flash_decode_merge_inside_the_cluster_and_by_kernel_agree(QH, KH, d, pa
     assert (outs[0].double().cpu() - ref).abs().max().item() <= 1.5e-2 * ref.abs().max().item()
 
 
+@pytest.mark.parametrize("direction", ["rising", "falling", "spikes"])
+def test_flash_prefill_tcgen05_when_the_maximum_keeps_moving(direction):
+    """The tcgen05 prefill kernel keeps O in tensor memory, scaled to a maximum that follows the true one only in
+    large steps.  Scores that rise from tile to tile (every tile brings a new maximum far above the last), fall,
+    or spike now and then make it rescale often, seldom, or in the middle of a row's keys - always the plain result."""
+    from reinfer_b200 import ops
+    QH, KH, d, page = 8, 2, 128, 64
+    T = 700
+    s = paged_setup([T], [T], QH, KH, d, page, torch.bfloat16, seed=21)
+    # keys along one direction with a strength that depends on the position; queries all look that way
+    gen = torch.Generator().manual_seed(5)
+    u = torch.zeros(d); u[3] = 1.0
+    pos = torch.arange(T, dtype=torch.float32)
+    strength = {"rising": 0.12 * pos, "falling": 0.12 * (T - pos), "spikes": torch.where(pos.long() % 97 == 5, 60.0, 0.0)}[direction]
+    k_new = (torch.randn(T, KH, d, generator=gen) * 0.3 + strength[:, None, None] * u).to(torch.bfloat16)
+    s["ks"][0] = k_new
+    for i in range(-(-T // page)):
+        m = min(page, T - i * page)
+        s["cache"][int(s["bt"][0, i]), 0, :, :m] = k_new[i * page:i * page + m].transpose(0, 1).to(DEV)
+    q_new = (torch.randn(T, QH, d, generator=gen) * 0.3 + 4.0 * u).to(torch.bfloat16)
+    s["q"] = q_new.to(DEV)
+    scale = 1.0 / math.sqrt(d)
+    ref = attention_truth(s, QH, KH, 0, scale)
+    cu_q = torch.tensor([0, T], dtype=torch.int32, device=DEV)
+    kv_len = torch.tensor([T], dtype=torch.int32, device=DEV)
+    out = torch.full_like(s["q"], float("nan"))
+    ops.fa_prefill_tc(s["q"], s["cache"], s["bt"], cu_q, kv_len, out, 0, 1, [T], QH, KH, d, page, 0, scale)
+    assert ops.kernel_error() == 0
+    assert not torch.isnan(out.float()).any()
+    err = (out.double().cpu() - ref).abs().max().item() / ref.abs().max().item()
+    assert err <= 1.5e-2, f"{direction}: error {err:.3e}"
+
+
 def test_flash_decode_finds_one_far_key_across_splits():
     from reinfer_b200 import ops
     QH, KH, d, page = 8, 2, 64, 16
