@@ -21,7 +21,9 @@
 // warps take the even and the odd tiles, each with its own running maximum, sum and O, which are combined at the end
 // (as the splits of flash decoding are).  While one group waits for its MMA the other computes, and every
 // scheduler of the SM has two warps to choose from.  The MMA warp computes the scores of tile i+1 before the
-// weighted sum of tile i.  Registers follow the roles (setmaxnreg): 40 for the control warps, 232 for the rows.
+// weighted sum of tile i.  Registers follow the roles (setmaxnreg): 40 for the control warps, 232 for the rows - what
+// the control warps give up (128 x 128) must cover what the rows take (256 x 64), for the registers come from the
+// CTA's own allocation and a request for more than it holds waits for ever.
 //
 // Head size 128, page size a power of two >= 8.  Every wait is bounded (2 s); a CTA that gives up raises the
 // error word, lets its copies land, frees its tensor memory and leaves.
