@@ -1,0 +1,85 @@
+"""Host-side decisions of the kernel layer that need no GPU: what the streaming kernels learn about the order
+of the weights, how many CTAs share a request's keys in decode attention, and the sampler's parameter checks."""
+from __future__ import annotations
+
+import pytest
+
+
+def test_stream_chain_learns_the_order_of_a_pass_and_forgets_a_changed_one():
+    from reinfer_b200.ops import StreamChain
+    c = StreamChain()
+    a, b, d = (0x1000, 64), (0x2000, 128), (0x3000, 32)
+    assert c.step(*a) is None                       # outside a pass: nothing is noted
+    c.begin()
+    assert c.step(*a) is None and c.step(*b) is None and c.step(*d) is None     # the first pass only writes down
+    c.end()
+    c.begin()
+    assert c.step(*a) == b and c.step(*b) == d and c.step(*d) == a              # after the last range comes the first
+    c.end()
+    # a pass that streams something else at a place gets no hint there, and the pass after it learns the new order
+    c.begin()
+    assert c.step(*a) == b
+    assert c.step(0x9000, 8) is None
+    assert c.step(*d) == a                          # places are compared one by one: the third still matches
+    c.end()
+    c.begin()
+    assert c.step(*a) == (0x9000, 8) and c.step(0x9000, 8) == d and c.step(*d) == a
+    c.end()
+    # a pass that did not complete (no end()) leaves what is known as it was
+    c.begin()
+    c.step(*b)
+    c.live = False
+    c.begin()
+    assert c.step(*a) == (0x9000, 8)
+    # markers (zero bytes) take a place in the order but are never offered for prefetching
+    m = StreamChain()
+    for _ in range(2):
+        m.begin()
+        r1 = m.step(*a)
+        r2 = m.step(0x7777, 0)
+        r3 = m.step(*b)
+        m.end()
+    assert r1 is None and r2 == b and r3 == a
+    # unaligned ranges are not offered either
+    u = StreamChain()
+    for _ in range(2):
+        u.begin()
+        r = u.step(*a)
+        u.step(0x2008, 64)
+        u.end()
+    assert r is None
+
+
+def test_decode_splits_model():
+    from reinfer_b200.ops import decode_splits
+    # many (request, kv head) pairs: one CTA each streams at the memory bandwidth, splitting only adds fill and drain
+    assert decode_splits(64 * 8, 64) == 1
+    assert decode_splits(32 * 8, 64) == 1
+    # few pairs: splits until enough CTAs stream; up to 8 stay inside a cluster while all are resident at once
+    assert decode_splits(16 * 8, 64) == 2
+    assert decode_splits(8 * 8, 64) == 4
+    assert 2 <= decode_splits(4 * 8, 64) <= 8
+    assert decode_splits(8, 64) > 8                 # one request: more splits than a cluster holds, merged by a kernel
+    # never more splits than tiles, never fewer than one
+    for ctas in (1, 8, 64, 512, 4096):
+        for tiles in (1, 2, 3, 16, 64, 512, 2048):
+            n = decode_splits(ctas, tiles)
+            assert 1 <= n <= max(1, min(64, tiles))
+    assert decode_splits(8, 1) == 1
+    # wider heads: the same decisions at the same number of bytes
+    assert decode_splits(64 * 8, 64, head_dim=256) == 1
+
+
+def test_sampling_params_checks():
+    from reinfer_b200.sampling import SamplingParams
+    SamplingParams(logit_bias=((3, 1.5), (9, -2.0))).validate()
+    with pytest.raises(ValueError):
+        SamplingParams(logit_bias=((3, 1.0), (3, 2.0))).validate()
+    with pytest.raises(ValueError):
+        SamplingParams(logit_bias=((-1, 1.0),)).validate()
+    with pytest.raises(ValueError):
+        SamplingParams(logit_bias=tuple((i, 0.1) for i in range(1025))).validate()
+    with pytest.raises(ValueError):
+        SamplingParams(repeat_last_n=65).validate()
+    with pytest.raises(ValueError):
+        SamplingParams(max_tokens=-1).validate()
