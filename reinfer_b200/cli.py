@@ -33,7 +33,7 @@ def cmd_run(a) -> int:
     t0 = time.perf_counter()
     llm = LLM(a.model, dtype=a.dtype, max_model_len=a.max_model_len, page_size=a.page_size,
               num_pages=a.num_pages, max_num_seqs=a.max_num_seqs, max_batch_tokens=a.max_batch_tokens,
-              seed=a.seed or 0)
+              seed=a.seed or 0, admission=a.admission)
     load_s = time.perf_counter() - t0
     sp = SamplingParams(temperature=a.temperature, top_k=a.top_k or 0, top_p=a.top_p if a.top_p is not None else 1.0,
                         min_p=a.min_p or 0.0, repeat_penalty=a.repeat_penalty or 1.0, seed=a.seed,
@@ -92,6 +92,8 @@ def main(argv=None) -> int:
     r.add_argument("--num-pages", type=int, default=None)
     r.add_argument("--max-num-seqs", type=int, default=8)
     r.add_argument("--max-batch-tokens", type=int, default=2048)
+    r.add_argument("--admission", choices=["pages", "estimate"], default="pages",
+                   help="estimate: also ask that the estimated peak of the running requests fits the cache")
     r.add_argument("prompt", nargs="*", help="token ids; standard input when absent")
     r.set_defaults(fn=cmd_run)
     m = sub.add_parser("random-model", help="write a model folder with seeded random weights")

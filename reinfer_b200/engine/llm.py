@@ -16,6 +16,7 @@ import torch
 from ..config.registry import resolve_eos
 from ..sampling.params import SamplingParams
 from ..sampling.sampler import Sampler, request_seed
+from .admission import AdmissionLimits, EstimateAdmission
 from .engine import Engine, StepEntry
 from .scheduler import Request, Scheduler
 
@@ -33,7 +34,11 @@ class LLM:
     def __init__(self, model: Optional[str] = None, *, engine: Optional[Engine] = None, dtype="bfloat16",
                  max_num_seqs: int = 64, max_batch_tokens: int = 2048, max_chunk: Optional[int] = None,
                  page_size: int = 64, num_pages: Optional[int] = None, max_model_len: Optional[int] = None,
-                 seed: int = 0, device="cuda:0", memory_fraction: float = 0.9):
+                 seed: int = 0, device="cuda:0", memory_fraction: float = 0.9, admission: str = "pages"):
+        """admission: "pages" admits a request when the free pages cover its prompt; "estimate" asks in addition
+        for the estimated peak of everything running to fit the pool (engine/admission.py)."""
+        if admission not in ("pages", "estimate"):
+            raise ValueError(f"admission {admission!r}: pages or estimate")
         if engine is None:
             if model is None:
                 raise ValueError("LLM needs a model folder or an engine")
@@ -45,9 +50,14 @@ class LLM:
         cfg = engine.config
         self.max_model_len = int(max_model_len or getattr(cfg, "max_position_embeddings", 0) or 0) or None
         self.eos = resolve_eos(cfg, model)
-        self.scheduler = Scheduler(engine.cache, max_batch_tokens=max(max_batch_tokens, engine.cache.max_seqs),
+        batch_tokens = max(max_batch_tokens, engine.cache.max_seqs)
+        estimate = None
+        if admission == "estimate":
+            estimate = EstimateAdmission(AdmissionLimits(pool_tokens=engine.cache.total_pages() * engine.cache.page_size,
+                                                         max_requests=engine.cache.max_seqs, max_batch_tokens=batch_tokens))
+        self.scheduler = Scheduler(engine.cache, max_batch_tokens=batch_tokens,
                                    max_chunk=max_chunk, eos_token_ids=self.eos, max_model_len=self.max_model_len,
-                                   release=engine.finish)
+                                   release=engine.finish, admission=estimate)
         self.sampler = Sampler(engine.vocab_size, engine.cache.max_seqs, engine.device)
         self._next_id = 0
         self.requests: Dict[Hashable, Request] = {}

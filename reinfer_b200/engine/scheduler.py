@@ -21,7 +21,10 @@ Decisions, after the reference's scheduler (crates/scheduler/src/batch.rs:69-101
   * a request that cannot fit into an empty pool finishes with reason "too_long";
   * after sampling: stop token -> EOS -> max_tokens, in that order; a stop or EOS token is
     consumed, not emitted; exactly max_tokens tokens are emitted otherwise (req.rs:294-315);
-  * abort is idempotent and releases exactly once (req.rs:330-339).
+  * abort is idempotent and releases exactly once (req.rs:330-339);
+  * optionally (`admission=`) a waiting request must also pass the reference's estimate of the
+    working set's peak (engine/admission.py); a request is never held back by it while nothing
+    else runs, so the queue always moves.
 Scheduling is a pure function of (arrival order, parameters, pool size).
 """
 from __future__ import annotations
@@ -32,6 +35,7 @@ from typing import Callable, Deque, Dict, Hashable, List, Optional, Sequence, Tu
 
 from ..cache.manager import CacheManager
 from ..sampling.params import SamplingParams
+from .admission import EstimateAdmission
 
 WAITING, RUNNING, FINISHED = "waiting", "running", "finished"
 
@@ -90,7 +94,8 @@ class SchedulerOutput:
 class Scheduler:
     def __init__(self, cache: CacheManager, max_batch_tokens: int = 2048, max_chunk: Optional[int] = None,
                  eos_token_ids: Sequence[int] = (), max_model_len: Optional[int] = None,
-                 release: Optional[Callable[[Hashable], None]] = None):
+                 release: Optional[Callable[[Hashable], None]] = None,
+                 admission: Optional[EstimateAdmission] = None):
         if max_batch_tokens <= 0:
             raise ValueError("max_batch_tokens must be positive")
         self.cache = cache
@@ -99,6 +104,7 @@ class Scheduler:
         self.eos = tuple(eos_token_ids)
         self.max_model_len = max_model_len
         self._release = release or (lambda rid: cache.release(rid) if rid in cache else None)
+        self.admission = admission
         self.waiting: Deque[Request] = deque()
         self.running: List[Request] = []
         self._arrivals = 0
@@ -136,6 +142,8 @@ class Scheduler:
         r.state = FINISHED
         r.finish_reason = reason
         self._release(r.request_id)
+        if self.admission is not None and reason in ("stop", "eos", "length"):
+            self.admission.finished(len(r.output))
 
     # ---- one scheduling decision ------------------------------------------------------------
     def schedule(self) -> SchedulerOutput:
@@ -188,6 +196,8 @@ class Scheduler:
 
             # 3. the waiting queue, in order; nothing is admitted in a step that preempted
             admitted = 0
+            first_portions = 0
+            taken: List[Request] = []
             while self.waiting and budget > 0 and not preempted:
                 r = self.waiting[0]
                 limit = self.max_model_len
@@ -208,6 +218,15 @@ class Scheduler:
                     break
                 rest = r.total_len - r.num_computed
                 n = min(rest, self.max_chunk, budget)
+                if self.admission is not None and (self.running or taken):
+                    live = [(len(q.prompt), len(q.output), q.num_computed, q.params.max_tokens) for q in self.running + taken]
+                    used = (cm.total_pages() - cm.free_pages()) * ps
+                    if not self.admission.admits(live, (len(r.prompt), len(r.output), r.num_computed, r.params.max_tokens),
+                                                 used_tokens=used, portion=self.max_chunk, first_portion=n,
+                                                 first_portions_so_far=first_portions):
+                        break
+                first_portions += n
+                taken.append(r)
                 self.waiting.popleft()
                 free -= cm.pages_for(n)
                 promised += cm.pages_for(r.total_len + 1) - cm.pages_for(n)
