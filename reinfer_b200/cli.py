@@ -4,13 +4,16 @@
 works on token ids, so the prompt is a list of integers (separated by blanks or commas),
 from the arguments or, when there are none, from standard input; the generated ids are
 printed on one line.  `--perf` adds the reference's machine-readable line
-(main.rs:700-727).  `reinfer random-model` writes a model folder with seeded random
-weights.
+(main.rs:700-727).  The model is a local folder, or a name looked up under `$REINFER_MODEL_DIR`
+(default `~/.reinfer/models`; main.rs:540-558 - nothing is ever downloaded here).  `--backend`
+takes the reference's names; only `auto` and `cuda` run (main.rs:483-509).  `reinfer random-model`
+writes a model folder with seeded random weights.
 """
 from __future__ import annotations
 
 import argparse
 import json
+import os
 import sys
 import time
 
@@ -23,7 +26,27 @@ def _ids(words):
     return out
 
 
+def resolve_model_dir(model: str) -> str:
+    """A local path wins; else `<model root>/<model>` if a config.json lies there."""
+    if os.path.isdir(model) or os.path.isfile(os.path.join(model, "config.json")):
+        return model
+    root = os.path.expanduser(os.environ.get("REINFER_MODEL_DIR") or os.path.join("~", ".reinfer", "models"))
+    found = os.path.join(root, model)
+    if os.path.isfile(os.path.join(found, "config.json")):
+        return found
+    raise FileNotFoundError(f"model not found locally: {model!r} (tried {found!r}); give a folder with config.json "
+                            f"and safetensors, or set REINFER_MODEL_DIR")
+
+
 def cmd_run(a) -> int:
+    if a.backend not in ("auto", "cuda"):
+        print(f"error: backend {a.backend!r} is not built here; this engine runs on cuda (B200) only", file=sys.stderr)
+        return 2
+    try:
+        a.model = resolve_model_dir(a.model)
+    except FileNotFoundError as e:
+        print(f"error: {e}", file=sys.stderr)
+        return 2
     from .engine.llm import LLM
     from .sampling.params import SamplingParams
     prompt = _ids(a.prompt) if a.prompt else _ids(sys.stdin.read().split())
@@ -77,7 +100,8 @@ def main(argv=None) -> int:
     ap = argparse.ArgumentParser(prog="reinfer", description="B200-native inference engine (token ids in, token ids out)")
     sub = ap.add_subparsers(dest="cmd", required=True)
     r = sub.add_parser("run", help="generate from a prompt of token ids")
-    r.add_argument("model", help="local model folder (config.json + safetensors)")
+    r.add_argument("model", help="local model folder (config.json + safetensors), or a name under $REINFER_MODEL_DIR")
+    r.add_argument("--backend", choices=["auto", "cuda", "ascend", "cpu"], default="auto")
     r.add_argument("-n", dest="max_tokens", type=int, default=256, metavar="MAX_TOKENS", help="max new tokens")
     r.add_argument("-t", dest="temperature", type=float, default=1.0, metavar="TEMP", help="0 = greedy")
     r.add_argument("--top-k", type=int, default=None, metavar="K")

@@ -83,3 +83,29 @@ def test_sampling_params_checks():
         SamplingParams(repeat_last_n=65).validate()
     with pytest.raises(ValueError):
         SamplingParams(max_tokens=-1).validate()
+
+
+# ---------------------------------------------------------------- the command line's host side
+def test_model_folder_resolution(tmp_path, monkeypatch):
+    """A local folder wins; a bare name is looked up under $REINFER_MODEL_DIR (bin/reinfer/src/main.rs:540-558)."""
+    from reinfer_b200.cli import resolve_model_dir
+    local = tmp_path / "here"
+    local.mkdir()
+    assert resolve_model_dir(str(local)) == str(local)
+    root = tmp_path / "models"
+    (root / "org" / "tiny").mkdir(parents=True)
+    (root / "org" / "tiny" / "config.json").write_text("{}")
+    monkeypatch.setenv("REINFER_MODEL_DIR", str(root))
+    assert resolve_model_dir("org/tiny") == str(root / "org" / "tiny")
+    with pytest.raises(FileNotFoundError, match="REINFER_MODEL_DIR"):
+        resolve_model_dir("org/absent")
+
+
+def test_command_line_refuses_other_backends_and_missing_models(tmp_path, capsys, monkeypatch):
+    from reinfer_b200.cli import main
+    monkeypatch.setenv("REINFER_MODEL_DIR", str(tmp_path))
+    assert main(["run", "nobody/nothing", "1", "2"]) == 2
+    assert "model not found locally" in capsys.readouterr().err
+    (tmp_path / "m").mkdir()
+    assert main(["run", str(tmp_path / "m"), "--backend", "cpu", "1", "2"]) == 2
+    assert "cuda" in capsys.readouterr().err
