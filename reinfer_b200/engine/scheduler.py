@@ -19,8 +19,11 @@ Decisions, after the reference's scheduler (crates/scheduler/src/batch.rs:69-101
     generated so far and then goes on generating (the reference restarts the request and
     regenerates, req.rs:346-357);
   * a request that cannot fit into an empty pool finishes with reason "too_long";
-  * after sampling: stop token -> EOS -> max_tokens, in that order; a stop or EOS token is
-    consumed, not emitted; exactly max_tokens tokens are emitted otherwise (req.rs:294-315);
+  * after sampling: stop token or stop sequence -> EOS -> max_tokens, in that order; a stop or EOS
+    token is consumed, not emitted; exactly max_tokens tokens are emitted otherwise
+    (req.rs:294-315).  A stop sequence is a sequence of token ids that ends the output stream
+    (stop.rs:1-13: matched on the raw token stream, the moment its last token is drawn); the
+    tokens of it that were emitted before are taken back from the output as well;
   * abort is idempotent and releases exactly once (req.rs:330-339);
   * optionally (`admission=`) a waiting request must also pass the reference's estimate of the
     working set's peak (engine/admission.py); a request is never held back by it while nothing
@@ -74,6 +77,17 @@ class Request:
     def in_prefill(self) -> bool:
         """True while tokens other than the newest one are still to be computed."""
         return self.total_len - self.num_computed > 1 or not self.output
+
+
+def _stop_sequence_match(sequences, output: List[int], token: int) -> Optional[int]:
+    """If output + [token] ends with one of the sequences: how many tokens of it are already in the output (the
+    longest such sequence wins, so that all of it is taken back).  Empty sequences never match."""
+    best = None
+    for seq in sequences:
+        n = len(seq)
+        if n and seq[-1] == token and n - 1 <= len(output) and list(seq[:-1]) == output[len(output) - (n - 1):]:
+            best = n - 1 if best is None else max(best, n - 1)
+    return best
 
 
 @dataclass
@@ -280,6 +294,9 @@ class Scheduler:
                 reason = "no_token"                         # no finite logit
             elif tok in p.stop_token_ids:
                 reason = "stop"
+            elif (cut := _stop_sequence_match(p.stop_sequences, r.output, tok)) is not None:
+                reason = "stop"
+                del r.output[len(r.output) - cut:]
             elif tok in self.eos and not p.ignore_eos:
                 reason = "eos"
             else:

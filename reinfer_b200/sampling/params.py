@@ -21,6 +21,7 @@ class SamplingParams:
     seed: Optional[int] = None            # None: derived from the engine's seed and the request's arrival number
     max_tokens: int = 256                 # hard cap of new tokens
     stop_token_ids: Tuple[int, ...] = ()
+    stop_sequences: Tuple[Tuple[int, ...], ...] = ()   # token-id sequences; generation stops when one ends the output
     ignore_eos: bool = False
 
     def validate(self) -> None:
@@ -32,5 +33,7 @@ class SamplingParams:
             raise ValueError("logit_bias takes at most 1024 entries")
         if len({int(i) for i, _ in self.logit_bias}) != len(self.logit_bias) or any(int(i) < 0 for i, _ in self.logit_bias):
             raise ValueError("logit_bias: token ids must be distinct and non-negative")
+        if any(t < 0 for seq in self.stop_sequences for t in seq):
+            raise ValueError("stop_sequences: token ids must be non-negative")
         if self.temperature != self.temperature:
             raise ValueError("temperature is NaN")

@@ -171,3 +171,37 @@ def test_same_arrivals_same_schedule():
         lp.run()
         return [[(s.request.request_id, s.start, len(s.tokens), s.sample) for s in h.batch] for h in lp.history]
     assert trace() == trace()
+
+
+def test_stop_sequences_end_the_stream_and_are_taken_back():
+    """A sequence of token ids that ends the output stream stops the request the moment its last token is drawn
+    (crates/scheduler/src/stop.rs:1-13); none of its tokens stays in the output.  A sequence that only begins
+    to match, or matches across the prompt's end, does nothing."""
+    free = Loop(64, max_seqs=2, max_batch_tokens=64)
+    unstopped = req("a", 6, max_tokens=12, ignore_eos=True)
+    free.s.add(unstopped)
+    free.run()
+    whole = unstopped.output
+    assert len(whole) == 12 and len(set(whole)) == 12
+
+    def run(seqs, **kw):
+        loop = Loop(64, max_seqs=2, max_batch_tokens=64)
+        r = req("a", 6, max_tokens=12, ignore_eos=True, stop_sequences=seqs, **kw)
+        loop.s.add(r)
+        loop.run()
+        loop.cm.check()
+        assert loop.cm.free_pages() == loop.cm.total_pages()
+        return r
+
+    r = run((tuple(whole[4:7]),))                      # tokens 4, 5, 6 of the free run: stops there, all three gone
+    assert r.finish_reason == "stop" and r.output == whole[:4]
+    r = run((tuple(whole[0:1]),))                      # a sequence of one token acts like a stop token
+    assert r.finish_reason == "stop" and r.output == []
+    r = run(((whole[5], whole[4]), (), (whole[3], 999)))   # wrong order, empty, a beginning only: no stop
+    assert r.finish_reason == "length" and r.output == whole
+    r = run(((6, whole[0]),))                          # would match only together with the prompt's last token
+    assert r.finish_reason == "length" and r.output == whole
+    r = run((tuple(whole[5:7]), tuple(whole[3:7])))    # two sequences end at the same token: the longer one is taken back
+    assert r.finish_reason == "stop" and r.output == whole[:3]
+    with pytest.raises(ValueError, match="stop_sequences"):
+        run(((1, -2),))
