@@ -1,6 +1,8 @@
 """The scheduler's decisions with a fake step function whose token is a pure function of
 (request, position) - no GPU.  (The idea of the reference's MockExecutor,
 bin/reinfer/src/sched_loop.rs:1594-1781.)"""
+import zlib
+
 import pytest
 
 from reinfer_b200.cache import CacheManager
@@ -12,7 +14,8 @@ SPEC = {"l0": PagedKVSpec(2, 16)}
 
 
 def fake_token(rid, position, vocab=1000):
-    return (hash((str(rid), position)) % (vocab - 10)) + 10
+    """The same in every process (the built-in hash of a string is not)."""
+    return (zlib.crc32(f"{rid}:{position}".encode()) % (vocab - 10)) + 10
 
 
 class Loop:
