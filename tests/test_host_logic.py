@@ -109,3 +109,21 @@ def test_command_line_refuses_other_backends_and_missing_models(tmp_path, capsys
     (tmp_path / "m").mkdir()
     assert main(["run", str(tmp_path / "m"), "--backend", "cpu", "1", "2"]) == 2
     assert "cuda" in capsys.readouterr().err
+
+
+# ---------------------------------------------------------------- bench.py's answers that need no GPU
+def test_bench_refuses_more_than_one_gpu_and_names_the_reference_arm():
+    import json
+    import os
+    import subprocess
+    import sys
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    p = subprocess.run([sys.executable, os.path.join(root, "bench.py"), "--gpus", "2"], capture_output=True, text=True, timeout=300)
+    assert p.returncode == 2
+    said = (p.stdout + p.stderr).strip().splitlines()
+    assert len(said) == 1 and "one GPU" in said[0]
+    p = subprocess.run([sys.executable, os.path.join(root, "bench.py"), "--impl", "reference", "--gpus", "1", "--steps", "2",
+                        "--warmup", "1"], capture_output=True, text=True, timeout=300)
+    assert p.returncode == 0
+    rec = json.loads(p.stdout.strip().splitlines()[-1])
+    assert rec["impl"] == "reference" and rec["unavailable"]
