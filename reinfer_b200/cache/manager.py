@@ -229,6 +229,35 @@ class CacheManager:
                     g.pool.free(p)
         self._free_slots.append(s.slot)
 
+    # ---- undoing a step that failed ------------------------------------------------------
+    def snapshot(self, rids: Sequence[Hashable]):
+        """What `restore` needs to undo admissions and reservations made after this moment for these requests
+        (commits are not undone: a step commits only after it has run)."""
+        snap = {}
+        for rid in rids:
+            s = self._seqs.get(rid)
+            snap[rid] = None if s is None else (s.reserved, [len(t) for t in s.tables])
+        return snap
+
+    def restore(self, snap) -> None:
+        """Give back what was taken since `snapshot`: a request admitted since then leaves altogether (pages and
+        slot); one that was live then keeps the pages it held then and returns the later ones, latest first."""
+        for rid, before in snap.items():
+            s = self._seqs.get(rid)
+            if s is None:
+                continue
+            if before is None:
+                self.release(rid)
+                continue
+            reserved, lens = before
+            for gi, (g, t) in enumerate(zip(self.groups, s.tables)):
+                while len(t) > lens[gi]:
+                    p = t.pop()
+                    s.np_tables[gi][len(t)] = -1
+                    if p >= 0:
+                        g.pool.free(p)
+            s.reserved = max(reserved, s.length)
+
     # ---- per-step tables ---------------------------------------------------------------
     def write_slots(self, rid, group: int, start: int, n: int) -> List[int]:
         """page*page_size+offset for the tokens at positions start..start+n-1."""

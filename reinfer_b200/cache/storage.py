@@ -2,7 +2,7 @@
 `[layers, pages, 2 (k, v), kv_heads, page_size, head_dim]` (a layer's slice is what
 its kernels get; inside a page the layout is head-major, so the keys of one
 (page, head) are one dense `[page_size, head_dim]` tile), and for each layer with a
-fixed-size state one array `[slots, *shape]`.
+fixed-size state one array `[slots + 1, *shape]` (the last row is nobody's).
 (The reference keeps one f16 buffer, K region then V region, layer folded into the
 page index: crates/cuda/src/decode.rs:664-698.)
 """
@@ -31,7 +31,10 @@ class CacheStorage:
         self.layer_state: Dict[str, torch.Tensor] = {}
         for name, spec in manager.states.items():
             sdt = dtype if spec.dtype == "act" else getattr(torch, spec.dtype)
-            self.layer_state[name] = torch.zeros((manager.max_seqs,) + tuple(spec.shape), dtype=sdt, device=self.device)
+            # one row more than there are slots: the last row belongs to nobody (padding rows of a captured
+            # decode step point at it, so that they disturb no request's state)
+            self.layer_state[name] = torch.zeros((manager.max_seqs + 1,) + tuple(spec.shape), dtype=sdt, device=self.device)
+        self.inert_slot = manager.max_seqs
 
     def zero_slot(self, slot: int) -> None:
         """A fixed-size state starts at zero when its request is admitted."""

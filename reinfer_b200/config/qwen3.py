@@ -51,6 +51,10 @@ class Qwen3Config:
     eos_token_ids: Tuple[int, ...] = ()
     architecture: str = "Qwen3ForCausalLM"
 
+    # the family's end-of-sequence id where neither generation_config.json nor config.json
+    # names one (crates/arch/src/llama.rs:423-431)
+    default_eos_ids = (151645,)
+
     # ---- parsing ---------------------------------------------------------
     @classmethod
     def from_dict(cls, d: Mapping[str, Any]) -> "Qwen3Config":

@@ -82,8 +82,9 @@ def load_config(model_dir: str):
 def resolve_eos(config, model_dir: Optional[str] = None) -> Tuple[int, ...]:
     """End-of-sequence ids.  Order of sources as in the reference
     (llama.rs:406-432): generation_config.json, then config.json, then the
-    family's fallback id 151645 for qwen3.  A list-valued `eos_token_id` stops on
-    every id of the list (the reference keeps only the first)."""
+    fallback ids of the architecture's family, which its configuration class
+    states as `default_eos_ids`.  A list-valued `eos_token_id` stops on every id
+    of the list (the reference keeps only the first)."""
     if model_dir is not None:
         gpath = os.path.join(model_dir, "generation_config.json")
         if os.path.exists(gpath):
@@ -97,9 +98,7 @@ def resolve_eos(config, model_dir: Optional[str] = None) -> Tuple[int, ...]:
     ids = tuple(getattr(config, "eos_token_ids", ()) or ())
     if ids:
         return ids
-    if str(getattr(config, "architecture", "")).lower().startswith("qwen3"):
-        return (151645,)
-    return ()
+    return tuple(getattr(config, "default_eos_ids", ()) or ())
 
 
 _builtin_done = False

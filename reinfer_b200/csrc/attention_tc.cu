@@ -27,6 +27,7 @@
 //
 // Head size 128, page size a power of two >= 8.  Every wait is bounded (2 s); a CTA that gives up raises the
 // error word, lets its copies land, frees its tensor memory and leaves.
+#define RB_UNIT 3
 #include "sm100.cuh"
 #include <stdlib.h>
 
@@ -103,7 +104,7 @@ __device__ __forceinline__ bool fc_wait(uint32_t bar, uint32_t parity, volatile 
         }
     }
     *abort_flag = where;
-    atomicCAS(&g_rb_kernel_error, 0, (1 << 8) | where);
+    rb_raise(where);
     return false;
 }
 
@@ -480,11 +481,6 @@ extern "C" int rb_fa_prefill_tc_group(int QH, int KH) {
 }
 
 // The error word of this file's kernels (0 = none); synchronises the device.  With reset != 0 it is cleared.
-extern "C" int rb_attn_tc_error(int reset) {
-    int v = 0;
-    if (cudaMemcpyFromSymbol(&v, g_rb_kernel_error, sizeof(int)) != cudaSuccess) return -1;
-    if (reset && v) { int z = 0; cudaMemcpyToSymbol(g_rb_kernel_error, &z, sizeof(int)); }
-    return v;
-}
+RB_STATUS_EXPORTS(rb_attn_tc_error, rb_attn_tc_bind_status)
 
 RB_TL_SETTER(rb_attn_tc_step_timeline)

@@ -18,6 +18,7 @@
 // shared memory before use, and shared memory is zeroed once at the start, so that nothing but
 // the request's own keys and values ever reaches the arithmetic.
 // Needs a page size that is a power of two >= 8 and head_dim % 8 == 0 (else fa_decode_kernel).
+#define RB_UNIT 2
 #include "sm100.cuh"
 #include <stdlib.h>
 
@@ -806,11 +807,6 @@ extern "C" int rb_fa_prefill_tma(const void* q, const void* cache, long long num
     return ft_launch_prefill<4, 2>(map, a, n_tiles, s);
 }
 
-extern "C" int rb_attn_error(int reset) {
-    int v = 0;
-    if (cudaMemcpyFromSymbol(&v, g_rb_kernel_error, sizeof(int)) != cudaSuccess) return -1;
-    if (reset && v) { int z = 0; cudaMemcpyToSymbol(g_rb_kernel_error, &z, sizeof(int)); }
-    return v;
-}
+RB_STATUS_EXPORTS(rb_attn_error, rb_attn_bind_status)
 
 RB_TL_SETTER(rb_attn_step_timeline)

@@ -21,6 +21,7 @@
 // Every wait on an mbarrier is bounded (two seconds of the global timer): after that the CTA raises
 // an abort flag, its roles leave their loops, outstanding TMA loads are waited for (again
 // bounded), tensor memory is freed, and an error word in global memory tells the host.
+#define RB_UNIT 1
 #include "sm100.cuh"
 #include <stdlib.h>
 
@@ -875,11 +876,6 @@ extern "C" int rb_gemm_plan(int N, int K, int dual, int* out) {
 }
 
 // The error word of the tensor-core kernels (0 = none); synchronises the device.  With reset != 0 it is cleared.
-extern "C" int rb_gemm_error(int reset) {
-    int v = 0;
-    if (cudaMemcpyFromSymbol(&v, g_rb_kernel_error, sizeof(int)) != cudaSuccess) return -1;
-    if (reset && v) { int z = 0; cudaMemcpyToSymbol(g_rb_kernel_error, &z, sizeof(int)); }
-    return v;
-}
+RB_STATUS_EXPORTS(rb_gemm_error, rb_gemm_bind_status)
 
 RB_TL_SETTER(rb_gemm_step_timeline)

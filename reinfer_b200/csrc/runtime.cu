@@ -85,3 +85,52 @@ int rb_tensor_map_bf16(const void* ptr, long long rows, long long cols, long lon
     return 0;
 }
 
+
+// ---- the status word -------------------------------------------------------------------------
+// One int per device in pinned host memory that is mapped into the device.  A kernel whose bounded wait gives up
+// stores its code there (sm100.cuh: rb_raise), so the host learns of it with a plain load at a moment when it has
+// waited for the step anyway (after the sampled tokens arrived), with no call into the device.  Made at the first
+// call on a device, which also tells every translation unit where the word is.
+extern "C" int rb_gemm_bind_status(int*);
+extern "C" int rb_attn_bind_status(int*);
+extern "C" int rb_attn_tc_bind_status(int*);
+extern "C" int rb_selftest_bind_status(int*);
+extern "C" int rb_gemm_error(int);
+extern "C" int rb_attn_error(int);
+extern "C" int rb_attn_tc_error(int);
+extern "C" int rb_selftest_error(int);
+
+#define RB_MAX_DEVICES 64
+static int* g_status_host[RB_MAX_DEVICES] = {nullptr};
+static std::mutex g_status_mu;
+
+// The host address of the current device's status word (NULL on failure, with the reason in rb_last_error).
+extern "C" int* rb_status_host() {
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= RB_MAX_DEVICES) { rb_set_error("status word: no current device"); return nullptr; }
+    std::lock_guard<std::mutex> g(g_status_mu);
+    if (g_status_host[dev]) return g_status_host[dev];
+    int* host = nullptr;
+    int* mapped = nullptr;
+    cudaError_t e = cudaHostAlloc((void**)&host, 64, cudaHostAllocMapped);
+    if (e == cudaSuccess) { *host = 0; e = cudaHostGetDevicePointer((void**)&mapped, host, 0); }
+    if (e != cudaSuccess) { rb_set_error("status word: CUDA error %d", (int)e); return nullptr; }
+    int rc = rb_gemm_bind_status(mapped);
+    if (!rc) rc = rb_attn_bind_status(mapped);
+    if (!rc) rc = rb_attn_tc_bind_status(mapped);
+    if (!rc) rc = rb_selftest_bind_status(mapped);
+    if (rc) { rb_set_error("status word: CUDA error %d while binding it", rc); return nullptr; }
+    g_status_host[dev] = host;
+    return host;
+}
+
+// Clear the status word and every unit's own word (synchronises the device); returns what the status word held.
+extern "C" int rb_status_clear() {
+    int* host = rb_status_host();
+    if (!host) return -1;
+    cudaDeviceSynchronize();
+    const int v = *(volatile int*)host;
+    *(volatile int*)host = 0;
+    rb_gemm_error(1); rb_attn_error(1); rb_attn_tc_error(1); rb_selftest_error(1);
+    return v;
+}

@@ -264,13 +264,14 @@ extern "C" int rb_sample_params_size() { return (int)sizeof(RbSampleParams); }
 // is only a handle; its device address comes from cudaGetSymbolAddress, looked up once per
 // device with that device current, and it is that address the kernel receives.
 #include "sampler_static.h"
+#include <atomic>
 #include <mutex>
 
 static __device__ __align__(256) float g_sample_static_scratch[RB_SAMPLE_STATIC_FLOATS];
 
 #define RB_SAMPLE_STATIC_MAX_DEVICES 64
-static float* g_sample_static_addr[RB_SAMPLE_STATIC_MAX_DEVICES] = {nullptr};
-static std::mutex g_sample_static_mu;
+static std::atomic<float*> g_sample_static_addr[RB_SAMPLE_STATIC_MAX_DEVICES];     // zero-initialised: not looked up yet
+static std::mutex g_sample_static_mu;                                              // taken by a device's first call only
 
 extern "C" int rb_sample_static(const float* logits, long long ld_logits, const int* row_idx, const void* params,
                                 const int* history, int hist_cap, int* out_tokens, int rows, int vocab, void* stream) {
@@ -284,16 +285,17 @@ extern "C" int rb_sample_static(const float* logits, long long ld_logits, const 
     cudaError_t e = cudaGetDevice(&dev);
     if (e != cudaSuccess) return (int)e;
     if (dev < 0 || dev >= RB_SAMPLE_STATIC_MAX_DEVICES) RB_REFUSE("sample_static: device index %d", dev);
-    float* scratch;
-    {
+    float* scratch = g_sample_static_addr[dev].load(std::memory_order_acquire);
+    if (scratch == nullptr) {                                   // first call on this device: look the address up
         std::lock_guard<std::mutex> g(g_sample_static_mu);
-        if (g_sample_static_addr[dev] == nullptr) {            // first call on this device: look the address up
+        scratch = g_sample_static_addr[dev].load(std::memory_order_relaxed);
+        if (scratch == nullptr) {
             void* p = nullptr;
             e = cudaGetSymbolAddress(&p, g_sample_static_scratch);
             if (e != cudaSuccess) return (int)e;
-            g_sample_static_addr[dev] = (float*)p;
+            scratch = (float*)p;
+            g_sample_static_addr[dev].store(scratch, std::memory_order_release);
         }
-        scratch = g_sample_static_addr[dev];
     }
     sample_kernel<<<rows, SP_THREADS, 0, (cudaStream_t)stream>>>(
         logits, ld_logits, row_idx, (const RbSampleParams*)params, history, hist_cap, scratch, out_tokens, vocab);

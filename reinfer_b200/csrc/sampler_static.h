@@ -7,10 +7,15 @@
  * rows x vocab floats in device memory.  Some callers have no way to get one at the moment
  * they want a token: code that runs between the kernels of a latency-critical loop, where
  * cudaMalloc would stall the whole device while it maps memory; a plug-in inside another
- * program that owns every byte of the GPU through its own pool and hands none out; a host
- * callback or a signal-safe path in which taking an allocator's lock is forbidden.  For them
+ * program that owns every byte of the GPU through its own pool and hands none out.  For them
  * the scratch lives inside the library: one array in device memory, of fixed size, that every
  * GPU holds from the moment it loads the library until the process exits.
+ *
+ * It is an ordinary host function all the same: it makes CUDA runtime calls (cudaGetDevice, a
+ * kernel launch, and cudaGetSymbolAddress at the first call on a device), and that first call takes
+ * a mutex.  So it is not for a cudaLaunchHostFunc callback or a signal handler, where runtime
+ * calls are not allowed at all.  After the first call on a device the address is read with one
+ * atomic load and no lock is taken.
  *
  * Limits.  rows * vocab <= RB_SAMPLE_STATIC_FLOATS (2,097,152 floats = 8 MiB per GPU): for
  * example 8 rows of a 262,144-entry vocabulary or 13 rows of Qwen3's 151,936.  Anything larger

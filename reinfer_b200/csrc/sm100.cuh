@@ -7,9 +7,35 @@
 
 #define RB_SPIN_LIMIT (1u << 24)
 
-// 0 ok; else (code << 8 | detail) of the first bounded wait that gave up.  One word per translation unit
-// (device symbols are not shared between separately compiled files); each file exports a reader.
+// 0 ok; else (unit << 16 | 1 << 8 | where) of the first bounded wait that gave up.  One word per translation unit
+// (device symbols are not shared between separately compiled files; a file names its unit with RB_UNIT before it
+// includes this header) and, for the host, one word for all of them in pinned host memory that is mapped into the
+// device (g_rb_status_host, bound by RB_STATUS_EXPORTS' binder): the kernel that gives up writes its code there as
+// well, so the host sees it with a plain load, without a call into the device (runtime.cu: rb_status_host).
+#ifndef RB_UNIT
+#define RB_UNIT 0
+#endif
 static __device__ int g_rb_kernel_error = 0;
+static __device__ int* g_rb_status_host = nullptr;
+
+__device__ __forceinline__ void rb_raise(int where) {
+    const int code = (RB_UNIT << 16) | (1 << 8) | where;
+    if (atomicCAS(&g_rb_kernel_error, 0, code) == 0) {
+        int* h = g_rb_status_host;
+        if (h) { *(volatile int*)h = code; __threadfence_system(); }
+    }
+}
+
+// The reader of this unit's word (synchronises the device; with reset != 0 the word is cleared) and the binder of
+// the host's word.
+#define RB_STATUS_EXPORTS(reader, binder)                                                                   \
+    extern "C" int reader(int reset) {                                                                      \
+        int v = 0;                                                                                          \
+        if (cudaMemcpyFromSymbol(&v, g_rb_kernel_error, sizeof(int)) != cudaSuccess) return -1;              \
+        if (reset && v) { int z = 0; cudaMemcpyToSymbol(g_rb_kernel_error, &z, sizeof(int)); }               \
+        return v;                                                                                           \
+    }                                                                                                       \
+    extern "C" int binder(int* mapped) { return (int)cudaMemcpyToSymbol(g_rb_status_host, &mapped, sizeof(mapped)); }
 
 // ------------------------------------------------------------------ PTX helpers
 __device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
@@ -41,7 +67,8 @@ __device__ __forceinline__ unsigned long long rb_globaltimer() {
     asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
     return t;
 }
-__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag, int where) {
+__device__ __forceinline__ bool mbar_wait_ns(uint32_t bar, uint32_t parity, volatile int* abort_flag, int where,
+                                             unsigned long long limit_ns) {
     unsigned long long t0 = 0;
     for (uint32_t it = 0; it < RB_SPIN_LIMIT; ++it) {
         if (mbar_try(bar, parity)) return true;
@@ -49,12 +76,15 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatil
             if (*abort_flag) return false;
             const unsigned long long now = rb_globaltimer();
             if (t0 == 0) t0 = now;
-            else if (now - t0 > RB_WAIT_NS) break;
+            else if (now - t0 > limit_ns) break;
         }
     }
     *abort_flag = where;
-    atomicCAS(&g_rb_kernel_error, 0, (1 << 8) | where);
+    rb_raise(where);
     return false;
+}
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag, int where) {
+    return mbar_wait_ns(bar, parity, abort_flag, where, RB_WAIT_NS);
 }
 // After a failed wait: let the copies that were issued into this CTA's shared memory land (bounded) before leaving.
 __device__ __forceinline__ void mbar_drain(uint32_t bar, uint32_t parity) {

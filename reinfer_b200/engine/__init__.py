@@ -1,3 +1,3 @@
-from .engine import Engine, StepEntry, EngineError, EmbeddingOov, parse_dtype
+from .engine import Engine, StepEntry, EngineError, EmbeddingOov, KernelWaitTimeout, parse_dtype
 
-__all__ = ["Engine", "StepEntry", "EngineError", "EmbeddingOov", "parse_dtype"]
+__all__ = ["Engine", "StepEntry", "EngineError", "EmbeddingOov", "KernelWaitTimeout", "parse_dtype"]

@@ -33,6 +33,10 @@ class EngineError(RuntimeError):
     pass
 
 
+class KernelWaitTimeout(EngineError):
+    """A kernel gave up a bounded wait and left its output unfinished."""
+
+
 class EmbeddingOov(EngineError):
     """A token id outside the vocabulary, refused before any launch
     (crates/cuda/src/engine.rs:3784-3786)."""
@@ -113,10 +117,15 @@ class Engine:
         self.cache = CacheManager(paged, states, self.page_size, int(num_pages), int(max_num_seqs))
         self.storage = CacheStorage(self.cache, dtype, self.device)
         self._staging = _Staging()
+        ops.status_word()                       # binds the kernels' error word to host memory (before any capture)
+        self._undo = None                       # the cache manager's snapshot from before the step in progress
         self.steps_run = 0
-        # decode-only steps replay a captured CUDA graph per (batch bucket, block-table width);
-        # a model with fixed-size per-request state runs eagerly (padding rows would touch a slot)
-        self.cuda_graphs = bool(cuda_graphs) and not self.storage.layer_state
+        # decode-only steps replay a captured CUDA graph per (batch bucket, block-table width).  Padding rows
+        # point at a slot that belongs to nobody.  A mixer with state takes part only if it says that its
+        # single-token step reads the batch from the device tables alone (`steps_from_device_tables`): what
+        # it read from the host mirrors would be frozen into the capture.
+        stateful = [l.mixer for l in self.model.layers if l.mixer is not None and l.mixer.state_spec() is not None]
+        self.cuda_graphs = bool(cuda_graphs) and all(getattr(m, "steps_from_device_tables", False) for m in stateful)
         self._graphs: Dict[tuple, "_DecodeGraph"] = {}
         self._graph_pool = None
         self.graph_replays = 0
@@ -158,17 +167,47 @@ class Engine:
 
     # ---- the step ----------------------------------------------------------------------
     def step(self, entries: Sequence[StepEntry]) -> Optional[torch.Tensor]:
+        """Runs the entries' tokens as one batch and returns the logits at the wanted places (None if
+        none is wanted).  If anything fails after the cache manager was changed (a kernel wrapper that
+        refuses its arguments, a launch error), the admissions and reservations of this step are undone
+        before the error goes on: every request is as it was before the call.  A kernel whose bounded
+        wait gave up in an earlier step makes this call raise before it launches anything
+        (`check_status`)."""
+        self.check_status()
         entries = [e for e in entries if len(e.tokens) > 0]
-        if self.cuda_graphs and entries and len(entries) <= MAX_GRAPH_BATCH and all(len(e.tokens) == 1 for e in entries):
-            return self._step_graph(entries)
-        ctx, want_rows, lens_after = self._prepare(entries)
-        if ctx is None:
-            return None
-        logits = self.model.forward(ctx, want_rows)
+        try:
+            if self.cuda_graphs and entries and len(entries) <= MAX_GRAPH_BATCH and all(len(e.tokens) == 1 for e in entries):
+                return self._step_graph(entries)
+            ctx, want_rows, lens_after = self._prepare(entries)
+            if ctx is None:
+                return None
+            logits = self.model.forward(ctx, want_rows)
+        except BaseException:
+            self._rollback()
+            raise
+        self._undo = None
         for rid, n in lens_after:
             self.cache.commit(rid, n)
         self.steps_run += 1
         return logits
+
+    def _rollback(self) -> None:
+        undo, self._undo = self._undo, None
+        if undo is not None:
+            self.cache.restore(undo)
+
+    def check_status(self) -> None:
+        """Raise if a kernel's bounded wait has given up (crates/cuda/src/engine.rs:3697-3737 `BarrierTimeout`,
+        :3849-3897 `SyncTimeout` are the reference's form of it).  The word lives in host memory that the
+        kernels write to, so this costs one load; it is complete for every step whose results the host has
+        already waited for (the sampled tokens, a copy of the logits).  After the error: `clear_status`."""
+        code = ops.status_word()
+        if code:
+            raise KernelWaitTimeout(f"{ops.describe_status(code)} (status word 0x{code:x}); the logits of that step "
+                                    f"and what it stored in the cache are not to be trusted")
+
+    def clear_status(self) -> int:
+        return ops.clear_status()
 
     def _graph_key(self, entries: Sequence[StepEntry]):
         B = len(entries)
@@ -196,6 +235,7 @@ class Engine:
         self._staging.upload(host, self.device, into=g.meta)
         g.graph.replay()
         self.graph_replays += 1
+        self._undo = None
         for rid, n in lens_after:
             self.cache.commit(rid, n)
         self.steps_run += 1
@@ -220,6 +260,7 @@ class Engine:
             host, lens_after = self._prepare(entries, fixed=key)
         except OutOfPages:
             return None
+        self._undo = None                               # the pages stay with their requests whatever comes of the handle
         return (key, tuple(request_ids), host, lens_after)
 
     def step_ahead(self, ahead, tokens: Sequence[int]) -> torch.Tensor:
@@ -229,6 +270,7 @@ class Engine:
             if not 0 <= int(t) < self.vocab_size:
                 raise EmbeddingOov(f"token id {t} outside the vocabulary of {self.vocab_size}")
         host[:len(rids)] = tokens                       # the block starts with the token ids (Engine._layout)
+        self.check_status()
         return self._replay(key, host, lens_after, list(range(len(rids))), len(rids))
 
     def finish(self, request_id) -> None:
@@ -271,6 +313,7 @@ class Engine:
             need += max(0, cm.pages_for(cur + len(e.tokens)) - have)
         if need > cm.free_pages():
             raise OutOfPages(f"the step needs {need} more pages, {cm.free_pages()} are free")
+        self._undo = cm.snapshot([e.request_id for e in entries])     # from here on the manager changes
         for e in new:
             slot = cm.admit(e.request_id)
             self.storage.zero_slot(slot)
@@ -318,6 +361,7 @@ class Engine:
         else:
             sec("cu_q")[:] = q_start
         sec("kv_len")[:E_real] = np.asarray(start) + np.asarray(q_len)
+        sec("entry_slot")[:] = self.storage.inert_slot
         sec("entry_slot")[:E_real] = slots
         if R:
             sec("want_rows")[:] = want_rows
@@ -412,9 +456,11 @@ class _DecodeGraph:
         o, n = off["tok_entry"]; host[o:o + n] = np.arange(batch)
         o, n = off["cu_q"]; host[o:o + n] = np.arange(batch + 1)
         o, n = off["want_rows"]; host[o:o + n] = np.arange(batch)
+        inert = engine.storage.inert_slot
+        o, n = off["entry_slot"]; host[o:o + n] = inert
         self.meta = torch.from_numpy(host).to(engine.device)
         ctx = engine._context(self.meta, off, batch, batch, batch, [width] * n_groups, list(range(batch + 1)),
-                              [0] * batch, [0] * batch, 1, width * engine.page_size)
+                              [0] * batch, [inert] * batch, 1, width * engine.page_size)
         o, n = off["want_rows"]
         want = self.meta[o:o + n]
         l0 = ops.launches

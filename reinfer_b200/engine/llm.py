@@ -17,7 +17,7 @@ from ..config.registry import resolve_eos
 from ..sampling.params import SamplingParams
 from ..sampling.sampler import Sampler, request_seed
 from .admission import AdmissionLimits, EstimateAdmission
-from .engine import Engine, StepEntry
+from .engine import Engine, EngineError, StepEntry
 from .scheduler import Request, Scheduler
 
 
@@ -28,6 +28,14 @@ class RequestOutput:
     token_ids: List[int]
     finish_reason: Optional[str]
     preemptions: int = 0
+
+
+def penalty_window(request: Request, last_n: int) -> List[int]:
+    """The tokens that the repeat, frequency and presence penalties look at: the last `last_n` tokens the
+    request has SAMPLED, never its prompt (crates/cuda/src/sampler.rs:109-111 and :369: the history is
+    fed by `history.push(token)` after each draw).  A preempted request keeps its output, so the window
+    is the same after it resumes."""
+    return request.output[-last_n:] if last_n > 0 else []
 
 
 class LLM:
@@ -63,6 +71,8 @@ class LLM:
         self.requests: Dict[Hashable, Request] = {}
         self.last_stats: Dict[str, float] = {}
         self._ahead = None                      # tables of the next step, built while the device was busy
+        self.ahead_used = 0                     # steps that ran on tables prepared one step ahead
+        self.ahead_discarded = 0                # prepared tables that the next decision did not match
 
     # ---- requests -----------------------------------------------------------------------
     def add_request(self, prompt_token_ids: Sequence[int], params: Optional[SamplingParams] = None,
@@ -98,24 +108,36 @@ class LLM:
             return finished
         ahead, self._ahead = self._ahead, None
         rids = tuple(s.request.request_id for s in out.batch)
-        if ahead is not None and ahead[1] == rids and all(len(s.tokens) == 1 and s.sample for s in out.batch):
-            logits = self.engine.step_ahead(ahead, [s.tokens[0] for s in out.batch])
-        else:
-            entries = [StepEntry(s.request.request_id, s.tokens, [len(s.tokens) - 1] if s.sample else [])
-                       for s in out.batch]
-            logits = self.engine.step(entries)
         sampling = [s.request for s in out.batch if s.sample]
         sampled: Dict[Hashable, int] = {}
-        if sampling:
-            n = self.sampler.launch(logits, [r.params for r in sampling], [r.seed for r in sampling],
-                                    [len(r.output) for r in sampling],
-                                    [(lambda k, r=r: r.tokens_from(max(0, r.total_len - k), min(k, r.total_len))) for r in sampling])
-            # the device is busy: prepare the next step if it is likely to be these requests again
-            if len(sampling) == len(out.batch) and not self.scheduler.waiting and \
-                    all(len(r.output) + 1 < r.params.max_tokens for r in sampling):
-                self._ahead = self.engine.prepare_ahead(rids)
-            toks = self.sampler.fetch(n)
-            sampled = {r.request_id: t for r, t in zip(sampling, toks)}
+        try:
+            if ahead is not None and ahead[1] == rids and all(len(s.tokens) == 1 and s.sample for s in out.batch):
+                self.ahead_used += 1
+                logits = self.engine.step_ahead(ahead, [s.tokens[0] for s in out.batch])
+            else:
+                if ahead is not None:
+                    self.ahead_discarded += 1           # (its pages stay with their requests)
+                entries = [StepEntry(s.request.request_id, s.tokens, [len(s.tokens) - 1] if s.sample else [])
+                           for s in out.batch]
+                logits = self.engine.step(entries)
+            if sampling:
+                n = self.sampler.launch(logits, [r.params for r in sampling], [r.seed for r in sampling],
+                                        [len(r.output) for r in sampling],
+                                        [(lambda k, r=r: penalty_window(r, k)) for r in sampling])
+                # the device is busy: prepare the next step if it is likely to be these requests again
+                if len(sampling) == len(out.batch) and not self.scheduler.waiting and \
+                        all(len(r.output) + 1 < r.params.max_tokens for r in sampling):
+                    self._ahead = self.engine.prepare_ahead(rids)
+                toks = self.sampler.fetch(n)
+                sampled = {r.request_id: t for r, t in zip(sampling, toks)}
+                self.engine.check_status()              # the tokens have arrived: the step's kernels are over
+        except EngineError:
+            # a kernel gave up (or the engine refused the step): the requests of this step end with "error" and
+            # give back their pages; the engine refuses further steps until `engine.clear_status()`
+            self._ahead = None
+            for s in out.batch:
+                self.scheduler.fail(s.request)
+            raise
         finished += self.scheduler.update(out.batch, sampled)
         return finished
 

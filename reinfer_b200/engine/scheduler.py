@@ -147,6 +147,14 @@ class Scheduler:
                 return r
         return None
 
+    def fail(self, request: Request, reason: str = "error") -> None:
+        """The step that ran this request failed: it ends with `reason` and gives back what it holds."""
+        if request in self.running:
+            self.running.remove(request)
+        elif request in self.waiting:
+            self.waiting.remove(request)
+        self._finish(request, reason)
+
     def has_work(self) -> bool:
         return bool(self.waiting or self.running)
 

@@ -457,10 +457,6 @@ _gemm_ws = None
 GEMM_WS_FLOATS = 8 << 20          # 32 MB of split-K partials
 
 
-def fast_gemm_available() -> bool:
-    return True
-
-
 def gemm_bf16(a: torch.Tensor, w: torch.Tensor, c: torch.Tensor, accumulate: bool = False, splits: int = 0,
               row_scale=None) -> None:
     """c[T,N] (=|+=) a[T,K] @ w[N,K]^T on the tensor cores (tcgen05, TMA); bf16 operands, float
@@ -523,13 +519,65 @@ def gemm_bf16_swiglu(a: torch.Tensor, w_gate_up: torch.Tensor, out: torch.Tensor
     return True
 
 
+def random_normal(out: torch.Tensor, base: int, mean: float, std: float) -> None:
+    """out[i] = mean + std * n_i, n_i the i-th normal of the counter stream that starts at `base`
+    (weights/random.py states the function); out float32 or bfloat16, contiguous."""
+    _need(out.is_contiguous(), "random_normal: contiguous tensor")
+    _check(lib().rb_random_normal(_p(out), c_int(dt(out)), c_longlong(out.numel()), ctypes.c_ulonglong(base & ((1 << 64) - 1)),
+                                  ctypes.c_double(mean), ctypes.c_double(std), _stream()), "random_normal")
+
+
+def random_ints(out: torch.Tensor, base: int) -> None:
+    _need(out.is_contiguous() and out.dtype == torch.int32, "random_ints: contiguous int32 tensor")
+    _check(lib().rb_random_ints(_p(out), c_longlong(out.numel()), ctypes.c_ulonglong(base & ((1 << 64) - 1)), _stream()),
+           "random_ints")
+
+
 def kernel_error(reset: bool = True) -> int:
     """The error word that a kernel sets when one of its bounded waits gives up (0 = none).
     Synchronises the device."""
-    a = int(lib().rb_gemm_error(c_int(int(reset))))
-    b = int(lib().rb_attn_error(c_int(int(reset))))
-    c = int(lib().rb_attn_tc_error(c_int(int(reset))))
-    return a or b or c
+    words = [int(fn(c_int(int(reset)))) for fn in (lib().rb_gemm_error, lib().rb_attn_error, lib().rb_attn_tc_error,
+                                                   lib().rb_selftest_error)]
+    if reset and any(words):
+        lib().rb_status_clear()
+    return next((w for w in words if w), 0)
+
+
+_status_word = None
+STATUS_UNITS = {1: "tensor-core product (gemm_tc.cu)", 2: "paged attention (attention_tma.cu)",
+                3: "tensor-core prefill attention (attention_tc.cu)", 4: "bounded-wait self-test (selftest.cu)"}
+
+
+def status_word() -> int:
+    """The host's copy of the kernels' error word: 0, or the code of the first bounded wait that gave up.
+    A plain load from pinned memory that the kernels write to; no call into the device, no synchronisation.
+    What it shows is complete for every kernel the host has already waited for."""
+    global _status_word
+    if _status_word is None:
+        fn = lib().rb_status_host
+        fn.restype = ctypes.POINTER(c_int)
+        ptr = fn()
+        if not ptr:
+            raise KernelError(f"status word: {lib().rb_last_error().decode()}")
+        _status_word = ptr
+    return int(_status_word[0])
+
+
+def describe_status(code: int) -> str:
+    unit, where = (code >> 16) & 0xFF, code & 0xFF
+    return f"a bounded wait gave up at point {where} of the {STATUS_UNITS.get(unit, f'unit {unit}')}"
+
+
+def clear_status() -> int:
+    """Clear the status word and the kernels' own words after an error was handled (synchronises the device)."""
+    status_word()
+    return int(lib().rb_status_clear())
+
+
+def test_bounded_wait(limit_ns: int, gave_up: Optional[torch.Tensor] = None) -> None:
+    """Launch the self-test kernel whose wait nobody answers (selftest.cu); it gives up after `limit_ns`."""
+    status_word()                       # the word must be bound before a kernel can write it
+    _check(lib().rb_test_bounded_wait(ctypes.c_ulonglong(int(limit_ns)), _p(gave_up), _stream()), "test_bounded_wait")
 
 
 def sample_params_size() -> int:

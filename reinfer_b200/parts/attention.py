@@ -88,7 +88,7 @@ class Attention(Mixer):
             if rot == d and d % 128 == 0 and act == torch.bfloat16 and inv_freq is not None and T > 64:
                 # the angles depend on the step's positions only: for a large step the first layer tabulates
                 # their cosines and sines (a small step computes them in place and saves the launch)
-                key = ("rope", getattr(self.position, "theta", None), rot, inv_freq.numel())    # the same for every layer
+                key = self.position.table_key()          # equal for layers whose encodings make the same table
                 cs = ctx.shared.get(key)
                 if cs is None:
                     cs = ctx.shared[key] = ops.rope_table(ctx.positions, inv_freq)

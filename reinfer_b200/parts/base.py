@@ -101,11 +101,22 @@ class PositionEncoding(Part):
         rotation of pairs (p, p+rot/2) by pos*inv_freq[p], else None."""
         return None
 
+    def table_key(self):
+        """A hashable value that is equal for two encodings exactly when they make the same per-step table
+        from the same positions: layers with equal keys share one table a step.  The default shares nothing."""
+        return ("position", id(self))
+
     def prepare(self, device) -> None:
         """Build device-side tables (called once, after the weights are bound)."""
 
 
 class Mixer(Part):
+    # A mixer with a state_spec() may set this if its step over single-token entries takes the slots from
+    # ctx.entry_slot (the device table) and nothing about the batch from the host mirrors (ctx.slots, ctx.q_start,
+    # ...): decode-only steps are then replayed from a captured CUDA graph, whose padding rows point at a slot
+    # that belongs to no request.  Otherwise a model with such a mixer runs every step eagerly.
+    steps_from_device_tables = False
+
     def cache_spec(self) -> Optional[PagedKVSpec]:
         return None
 

@@ -1,5 +1,7 @@
-"""Arrangements of a layer's four parts.  'prenorm':
-    x += mixer(norm1(x));  x += ffn(norm2(x))       (crates/cuda/src/engine.rs:4071-4333)
+"""Arrangements of a layer's parts.  A block class is constructed with the layer's parts by
+role (`Block(parts: dict role -> part)`), says with `roles` which ones it needs, and runs the
+layer on the residual stream in `forward(ctx, x, cache)`.  'prenorm':
+    x += mixer(mixer_norm(x));  x += ffn(ffn_norm(x))       (crates/cuda/src/engine.rs:4071-4333)
 Mixer and feed-forward add into the residual stream themselves (their last product
 accumulates into it), so no separate residual kernel runs.  Either may instead return
 what is still to be added (a tensor of x's shape, or a stack [S, T, h] of partial sums):
@@ -10,11 +12,20 @@ from __future__ import annotations
 from .base import register_part
 
 
+def need_roles(block_name: str, parts, roles) -> None:
+    missing = [r for r in roles if r not in parts]
+    if missing:
+        raise ValueError(f"block '{block_name}' needs the roles {list(roles)}; the layer lacks {missing} "
+                         f"(it has {list(parts)})")
+
+
 class PreNormBlock:
+    roles = ("mixer_norm", "mixer", "ffn_norm", "ffn")
     hands_on_sums = True                # forward takes and returns what is still to be added to x
 
-    def __init__(self, mixer_norm, mixer, ffn_norm, ffn):
-        self.mixer_norm, self.mixer, self.ffn_norm, self.ffn = mixer_norm, mixer, ffn_norm, ffn
+    def __init__(self, parts):
+        need_roles("prenorm", parts, self.roles)
+        self.mixer_norm, self.mixer, self.ffn_norm, self.ffn = (parts[r] for r in self.roles)
 
     def forward(self, ctx, x, cache, delta=None):
         """Runs the layer on the residual stream x (in place).  delta: what the block before left to be

@@ -21,7 +21,7 @@ from .base import RowScaled
 def takes_row_scaled(w: Optional[torch.Tensor]) -> bool:
     """Whether products with this weight can apply a row factor in their epilogue (the tensor-core kernel with
     operands that TMA can address): a part whose first product qualifies may accept RowScaled input."""
-    return w is not None and w.dtype == torch.bfloat16 and w.is_cuda and ops.fast_gemm_available() and \
+    return w is not None and w.dtype == torch.bfloat16 and w.is_cuda and \
         w.stride(1) == 1 and w.stride(0) % 8 == 0 and w.data_ptr() % 16 == 0 and w.shape[1] % 8 == 0
 
 
@@ -40,7 +40,7 @@ def matmul(ctx, a, w: torch.Tensor, out: Optional[torch.Tensor] = None,
         raise ValueError("matmul: accumulation needs a float32 destination")
     if M == 0:
         return out
-    if a.dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and ops.fast_gemm_available():
+    if a.dtype == torch.bfloat16 and w.dtype == torch.bfloat16:
         ops.gemm_bf16(a, w, out, accumulate, row_scale=row_scale)
     else:
         if row_scale is not None:
@@ -57,7 +57,7 @@ def matmul_into_residual(ctx, a: torch.Tensor, w: torch.Tensor, residual: torch.
     partial sums [S, T, N] and this returns them: the caller hands them on as its result, and the next
     norm adds them to the residual in a fixed order before it normalises.  Otherwise the product is
     added to the residual here and None is returned."""
-    if getattr(ctx, "defer_residual", False) and ops.fast_gemm_available():
+    if getattr(ctx, "defer_residual", False):
         parts = ops.gemm_bf16_partials(a, w) if a.shape[0] else None
         if parts is not None:
             return parts

@@ -1,5 +1,5 @@
-"""A model built from a `ModelSpec`: embedding, layers (each a block of four parts),
-final norm, output head, and the order in which layers run.  The class knows no
+"""A model built from a `ModelSpec`: embedding, layers (each a block over the parts its
+spec names by role), final norm, output head, and the order in which layers run.  The class knows no
 architecture; everything it does is driven by the spec.
 """
 from __future__ import annotations
@@ -15,23 +15,36 @@ from .spec import LayerSpec, ModelSpec, PartSpec
 
 
 class Layer:
+    """The parts of one layer, built from its spec, and the block that arranges them."""
+
     def __init__(self, spec: LayerSpec):
         self.spec = spec
         self.name = spec.name
-        self.mixer_norm = build_part("norm", spec.mixer_norm)
-        self.mixer = build_part("mixer", spec.mixer)
-        self.ffn_norm = build_part("norm", spec.ffn_norm)
-        self.ffn = build_part("ffn", spec.ffn)
+        self.parts_by_role = {role: build_part(category, pspec) for role, (category, pspec) in spec.parts.items()}
+        mixers = [self.parts_by_role[r] for r, (c, _) in spec.parts.items() if c == "mixer"]
+        self.mixer = mixers[0] if mixers else None           # the part that owns a cache, if the layer has one
+        self.norms = [self.parts_by_role[r] for r, (c, _) in spec.parts.items() if c == "norm"]
         _ensure_builtin()
         try:
             block_cls = _REGISTRY[("block", spec.block)]
         except KeyError:
             raise KeyError(f"no block arrangement '{spec.block}' is registered") from None
-        self.block = block_cls(self.mixer_norm, self.mixer, self.ffn_norm, self.ffn)
+        self.block = block_cls(self.parts_by_role)
+
+    def __getattr__(self, role: str):
+        parts = self.__dict__.get("parts_by_role", {})
+        if role in parts:
+            return parts[role]
+        raise AttributeError(role)
 
     def parts(self):
-        s = self.spec
-        return ((s.mixer_norm, self.mixer_norm), (s.mixer, self.mixer), (s.ffn_norm, self.ffn_norm), (s.ffn, self.ffn))
+        return tuple((pspec, self.parts_by_role[role]) for role, (_, pspec) in self.spec.parts.items())
+
+    def cache_spec(self):
+        return self.mixer.cache_spec() if self.mixer is not None else None
+
+    def state_spec(self):
+        return self.mixer.state_spec() if self.mixer is not None else None
 
 
 class Model:
@@ -59,7 +72,7 @@ class Model:
             self.run.append((i, self.layers[i].name if k == 0 else f"{self.layers[i].name}#{k}"))
         # sums may be left for the next norm only if every norm can add a stack of partial sums and every
         # block hands on what its parts leave
-        norms = [n for l in self.layers for n in (l.mixer_norm, l.ffn_norm)] + [self.final_norm]
+        norms = [n for l in self.layers for n in l.norms] + [self.final_norm]
         self._norms_add_partial_sums = all(getattr(n, "adds_partial_sums", False) for n in norms) and \
             all(getattr(l.block, "hands_on_sums", False) for l in self.layers) and ops.DEFER_SUMS
         by_name = {l.name: l for l in self.layers}
@@ -70,7 +83,7 @@ class Model:
                     raise ValueError(f"layer {l.name} reads the cache of unknown layer {src}")
                 if by_name[src].spec.cache_from is not None:
                     raise ValueError(f"layer {l.name} reads the cache of {src}, which has none of its own")
-                if by_name[src].mixer.cache_spec() != l.mixer.cache_spec():
+                if by_name[src].cache_spec() != l.cache_spec():
                     raise ValueError(f"layer {l.name} and {src} need different caches")
 
     # ---- tensors -------------------------------------------------------------
@@ -111,7 +124,8 @@ class Model:
 
     def prepare(self, device, dtype) -> None:
         for l in self.layers:
-            l.mixer.prepare(device, dtype)
+            if l.mixer is not None:
+                l.mixer.prepare(device, dtype)
 
     # ---- what the cache manager has to provide -------------------------------
     def cache_layout(self):
@@ -122,7 +136,7 @@ class Model:
         states: Dict[str, SlotStateSpec] = {}
         for i, key in self.run:
             l = self.layers[i]
-            cs, ss = l.mixer.cache_spec(), l.mixer.state_spec()
+            cs, ss = l.cache_spec(), l.state_spec()
             if cs is not None and l.spec.cache_from is None:
                 paged[key] = cs
             if ss is not None:
@@ -134,7 +148,7 @@ class Model:
         out = []
         for i, key in self.run:
             l = self.layers[i]
-            if l.mixer.cache_spec() is None:
+            if l.cache_spec() is None:
                 out.append((key, None, False))
             elif l.spec.cache_from is not None:
                 out.append((key, l.spec.cache_from, False))

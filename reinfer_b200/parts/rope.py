@@ -32,6 +32,9 @@ class RotaryEncoding(PositionEncoding):
     def fused_rotary(self):
         return self.inv_freq, self.rotary_dim
 
+    def table_key(self):
+        return ("rope", self.theta, self.rotary_dim)
+
     def apply(self, ctx, q, k, positions) -> None:
         """The unfused form, for a mixer that does not take `fused_rotary()`: q [T, QH, d] and k [T, KH, d]
         are rotated in place (through the same kernel, with the head norm and the cache switched off)."""

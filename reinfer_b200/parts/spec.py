@@ -16,15 +16,57 @@ class PartSpec:
     prefix: str = ""                            # tensor names of the part are prefix + local name
 
 
-@dataclass(frozen=True)
+def role_category(role: str) -> str:
+    """The registry category of a layer's part, read off its role's name: 'mixer' -> mixer, 'ffn' -> ffn,
+    any role that ends in 'norm' -> norm.  A role of another name states its category itself."""
+    if role == "mixer" or role.endswith("_mixer"):
+        return "mixer"
+    if role == "ffn" or role.endswith("_ffn"):
+        return "ffn"
+    if role.endswith("norm"):
+        return "norm"
+    raise ValueError(f"role '{role}' does not tell its category: give it as (category, PartSpec)")
+
+
 class LayerSpec:
-    name: str                                   # unique; also the default tensor prefix of the layer
-    mixer: PartSpec
-    ffn: PartSpec
-    mixer_norm: PartSpec
-    ffn_norm: PartSpec
-    block: str = "prenorm"                      # arrangement of the four parts (registry 'block')
-    cache_from: Optional[str] = None            # read (and do not write) the cache of that layer
+    """A layer: a name, the block arrangement (registry 'block'), and the parts that the arrangement
+    works with, each under a role of the arrangement's choosing.
+
+        LayerSpec("l3", block="prenorm", mixer=..., ffn=..., mixer_norm=..., ffn_norm=...)
+        LayerSpec("l4", block="my_sandwich", mixer=..., ffn=..., pre_mixer_norm=..., post_mixer_norm=..., ...)
+        LayerSpec("l5", block="my_gate", mixer=..., gate=("ffn", PartSpec(...)))
+
+    Roles are keyword arguments: a PartSpec (category read off the role's name, see `role_category`)
+    or a pair (category, PartSpec).  `parts` maps role -> (category, PartSpec) in the order given.
+    Which roles there must be is the block's business, not the framework's: a layer with four norms,
+    with mixer and feed-forward side by side, or without a feed-forward needs a block class and no
+    change here.  At most one part of a layer is a mixer (the part that owns a cache)."""
+
+    def __init__(self, name: str, block: str = "prenorm", cache_from: Optional[str] = None, **roles):
+        self.name = name                            # unique; also the default tensor prefix of the layer
+        self.block = block
+        self.cache_from = cache_from                # read (and do not write) the cache of that layer
+        parts: Dict[str, Tuple[str, PartSpec]] = {}
+        for role, value in roles.items():
+            if isinstance(value, PartSpec):
+                parts[role] = (role_category(role), value)
+            else:
+                category, spec = value
+                if not isinstance(spec, PartSpec):
+                    raise TypeError(f"layer {name}: role '{role}' needs a PartSpec or (category, PartSpec)")
+                parts[role] = (str(category), spec)
+        if sum(1 for c, _ in parts.values() if c == "mixer") > 1:
+            raise ValueError(f"layer {name}: more than one mixer; give the second a layer of its own")
+        self.parts = parts
+
+    def __getattr__(self, role: str) -> PartSpec:
+        parts = self.__dict__.get("parts", {})
+        if role in parts:
+            return parts[role][1]
+        raise AttributeError(role)
+
+    def __repr__(self) -> str:
+        return f"LayerSpec({self.name!r}, block={self.block!r}, roles={list(self.parts)})"
 
 
 @dataclass(frozen=True)

@@ -60,6 +60,7 @@ def main(argv=None) -> int:
             os.replace(tmp, os.path.join(args.out, f"{step}.f32"))
         else:
             torch.cuda.synchronize()
+        engine.check_status()          # the step is over on the device: a kernel that gave up a wait ends the replay
         for rid in rec.get("end", []):
             engine.finish(rid)
         print(f"done {step}", flush=True)

@@ -13,7 +13,6 @@ engine.rs:3213-3224).
 """
 from __future__ import annotations
 
-import hashlib
 import json
 import os
 from typing import Dict, Iterable, Mapping, Optional, Set
@@ -93,37 +92,28 @@ def load_state(model_dir: str, expected: Mapping[str, ParamSpec], compute_dtype:
     return out
 
 
-def _tensor_seed(seed: int, name: str) -> int:
-    h = hashlib.sha256(f"{seed}:{name}".encode("utf-8")).digest()
-    return int.from_bytes(h[:8], "little") & 0x7FFF_FFFF_FFFF_FFFF
-
-
 def random_state(expected: Mapping[str, ParamSpec], seed: int, dtype: torch.dtype,
                  device="cpu") -> Dict[str, torch.Tensor]:
-    """Seeded random tensors for every non-optional expected name: matrices and
-    tables N(0, std), norm weights 1 + N(0, 0.05).  Each tensor has a generator of
-    its own, seeded by (seed, name), so a tensor's values do not depend on which
-    other tensors exist.  Values are drawn in float32 on `device` and then rounded to
-    `dtype`; CPU and GPU generators give different (equally valid) values."""
+    """Seeded random tensors for every expected name: matrices and
+    tables N(0, std), norm weights 1 + N(0, 0.05), integer tables 15-bit uniform.
+    Every element is a fixed function of (seed, tensor name, its row-major index)
+    (weights/random.py), so a tensor's values depend neither on which other
+    tensors exist nor on where they are drawn: a model drawn on the GPU and one
+    written to a folder on the CPU hold the same numbers.  Values are float32,
+    rounded to `dtype`."""
+    from . import random as rnd
     out: Dict[str, torch.Tensor] = {}
     dev = torch.device(device)
     for name, spec in expected.items():
-        if spec.optional:
-            continue
-        g = torch.Generator(device=dev)
-        g.manual_seed(_tensor_seed(seed, name))
+        # (a tensor that a file may lack is drawn too: a random untied model has an output matrix of its own)
         if spec.kind == "int":
-            out[name] = torch.randint(0, 1 << 15, spec.shape, generator=g, device=dev, dtype=torch.int32)
-            continue
-        if spec.init == "zeros":
+            out[name] = rnd.ints(spec.shape, seed, name, dev)
+        elif spec.init == "zeros":
             out[name] = torch.zeros(spec.shape, dtype=dtype, device=dev)
-            continue
-        t = torch.empty(spec.shape, dtype=torch.float32 if dev.type == "cpu" else dtype, device=dev)
-        if spec.init == "norm":
-            t.normal_(0.0, 0.05, generator=g).add_(1.0)
+        elif spec.init == "norm":
+            out[name] = rnd.normal(spec.shape, seed, name, 1.0, 0.05, dtype, dev)
         else:
-            t.normal_(0.0, spec.std, generator=g)
-        out[name] = t.to(dtype)
+            out[name] = rnd.normal(spec.shape, seed, name, 0.0, spec.std, dtype, dev)
     return out
 
 

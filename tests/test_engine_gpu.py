@@ -43,13 +43,15 @@ def truth(model_dir, seqs):
     return _truth_cache[key]
 
 
-def run_steps(engine, steps):
+def run_steps(engine, steps, owners=None):
     """-> {(request, position): logits row (cpu float64)}"""
     from reinfer_b200.engine import StepEntry
     got = {}
     done = {}
     for entries, end in steps:
         logits = engine.step([StepEntry(r, t, w) for r, t, w in entries])
+        if owners is not None:
+            owners.look()
         row = 0
         for r, t, w in entries:
             base = done.get(r, 0)
@@ -90,13 +92,17 @@ def test_cuts_match_plain(models, which, dtype, cut):
     model_dir = models[(which, "f32" if dtype == "float32" else "bf16")]
     seqs = tiny.sequences(which)
     steps = CUTS[cut](seqs)
-    pool = tiny.pool_tokens_needed(steps)
-    engine = Engine.from_model_dir(model_dir, dtype=dtype, page_size=tiny.TINY[which][2], max_tokens=pool,
-                                   max_num_seqs=4)
-    got = run_steps(engine, steps)
+    page = tiny.TINY[which][2]
+    pool = tiny.pool_tokens_needed(steps, page)          # exactly the pages the steps need: not one to spare
+    engine = Engine.from_model_dir(model_dir, dtype=dtype, page_size=page, max_tokens=pool, max_num_seqs=4)
+    owners = tiny.PageOwners(engine.cache)
+    got = run_steps(engine, steps, owners)
     assert len(got) == sum(len(t) for t in seqs.values())
     compare(got, truth(model_dir, seqs), TOL[dtype])
     assert engine.cache.free_pages() == engine.cache.total_pages()
+    if cut == "mixed":
+        # finished requests' pages went to later requests: at least half of the pool had a second owner
+        assert 2 * len(owners.reused) >= engine.cache.total_pages(), (len(owners.reused), engine.cache.total_pages())
 
 
 @pytest.mark.parametrize("which", ["A", "B"])
@@ -109,7 +115,7 @@ def test_float32_cuts_agree_bitwise(models, which):
     for cut in CUTS.values():
         steps = cut(seqs)
         engine = Engine.from_model_dir(model_dir, dtype="float32", page_size=tiny.TINY[which][2],
-                                       max_tokens=tiny.pool_tokens_needed(steps), max_num_seqs=4)
+                                       max_tokens=tiny.pool_tokens_needed(steps, tiny.TINY[which][2]), max_num_seqs=4)
         results.append(run_steps(engine, steps))
     for other in results[1:]:
         for key, row in results[0].items():
@@ -150,31 +156,6 @@ def test_trace_run_program(models, tmp_path, dtype):
     compare(got, want, TOL[dtype])
 
 
-@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-def test_full_size_layer_shape(tmp_path, dtype):
-    """Two layers at the layer sizes of the 8B configuration (hidden 4096, 32/8 heads of 128, feed-forward
-    12288; vocabulary cut to an odd 32003): the tensor-core kernels at the sizes they serve, against the
-    plain implementation, whole and mixed with a pool that is used again."""
-    from reinfer_b200.config import Qwen3Config
-    from reinfer_b200.engine import Engine
-    from reinfer_b200.weights import write_random_model
-    raw = dict(architectures=["Qwen3ForCausalLM"], num_hidden_layers=2, hidden_size=4096, num_attention_heads=32,
-               num_key_value_heads=8, head_dim=128, intermediate_size=12288, vocab_size=32003, rope_theta=1e6,
-               rms_norm_eps=1e-6, tie_word_embeddings=False, max_position_embeddings=4096)
-    d = write_random_model(str(tmp_path / "m"), Qwen3Config.from_dict(raw), seed=3, dtype=torch.bfloat16)
-    g = torch.Generator().manual_seed(1)
-    seqs = {"a": torch.randint(0, 32003, (150,), generator=g).tolist(), "b": torch.randint(0, 32003, (70,), generator=g).tolist(),
-            "c": torch.randint(0, 32003, (300,), generator=g).tolist()}
-    cfg, w = plain.read_model(d)
-    want = {r: plain.forward(cfg, w, t, dtype=torch.float32).double() for r, t in seqs.items()}
-    for cut in (tiny.cut_whole, tiny.cut_mixed):
-        steps = cut(seqs)
-        engine = Engine.from_model_dir(d, dtype=dtype, page_size=16, max_tokens=tiny.pool_tokens_needed(steps), max_num_seqs=4)
-        got = run_steps(engine, steps)
-        compare(got, want, 2e-4 if dtype == "float32" else TOL[dtype])
-        del engine
-
-
 @pytest.mark.parametrize("store,dtype", [("f32", "bfloat16"), ("bf16", "float32")])
 def test_storage_and_compute_dtype_may_differ(models, store, dtype):
     """A folder stored in 32 bits run in bfloat16 (its tensors stay 32-bit: the plain kernels take the
@@ -185,7 +166,7 @@ def test_storage_and_compute_dtype_may_differ(models, store, dtype):
     model_dir = models[(which, store)]
     seqs = tiny.sequences(which)
     steps = tiny.cut_mixed(seqs, seed=5)
-    engine = Engine.from_model_dir(model_dir, dtype=dtype, page_size=8, max_tokens=tiny.pool_tokens_needed(steps), max_num_seqs=4)
+    engine = Engine.from_model_dir(model_dir, dtype=dtype, page_size=8, max_tokens=tiny.pool_tokens_needed(steps, 8), max_num_seqs=4)
     if store == "f32":
         assert engine.model.layers[0].mixer.w_qkv.dtype == torch.float32
     got = run_steps(engine, steps)

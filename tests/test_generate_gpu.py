@@ -158,17 +158,133 @@ def test_temperature_generation_is_seeded_and_batch_independent(model_dirs):
 
 
 def test_preemption_on_the_device_keeps_outputs(model_dirs):
+    """A pool too small for three requests at once: the newest is preempted, recomputes prompt + output when it
+    returns and goes on.  The tokens are the plain implementation's, as in a run that never preempted."""
     from reinfer_b200 import LLM, SamplingParams
     which = "A"
+    cfg, w = plain.read_model(model_dirs[which])
     seqs = list(tiny.sequences(which, lengths=[20, 25, 30]).values())
     sp = SamplingParams(temperature=0.0, max_tokens=40, ignore_eos=True)
+    want = [plain.greedy(cfg, w, p, 40) for p in seqs]
     calm = LLM(model_dirs[which], dtype="float32", page_size=16, num_pages=64, max_num_seqs=4, max_batch_tokens=32)
-    want = [o.token_ids for o in calm.generate(seqs, sp)]
+    assert [o.token_ids for o in calm.generate(seqs, sp)] == want
     tight = LLM(model_dirs[which], dtype="float32", page_size=16, num_pages=9, max_num_seqs=4, max_batch_tokens=32)
     outs = tight.generate(seqs, sp)
-    assert tight.last_stats["preemptions"] > 0
+    assert tight.last_stats["preemptions"] > 0 and sum(o.preemptions for o in outs) > 0
     assert [o.token_ids for o in outs] == want
     assert tight.engine.cache.free_pages() == 9
+    tight.engine.cache.check()
+
+
+def test_preemption_in_bfloat16_follows_plain_teacher_forced(tmp_path):
+    """The same squeeze in bfloat16: a preempted request's recomputed cache must carry it on as before.  Wherever
+    bfloat16 picks a token, the plain logits of ITS sequence call that token best or nearly so, before and after
+    the preemption; and a run that never preempts picks the same tokens."""
+    from reinfer_b200 import LLM, SamplingParams
+    d = tiny.make_model_dir(str(tmp_path / "a16"), "A", torch.bfloat16)
+    cfg, w = plain.read_model(d)
+    seqs = list(tiny.sequences("A", lengths=[20, 25, 30]).values())
+    sp = SamplingParams(temperature=0.0, max_tokens=40, ignore_eos=True)
+    tight = LLM(d, dtype="bfloat16", page_size=16, num_pages=9, max_num_seqs=4, max_batch_tokens=32)
+    outs = tight.generate(seqs, sp)
+    assert sum(o.preemptions for o in outs) > 0
+    for o, prompt in zip(outs, seqs):
+        assert len(o.token_ids) == 40
+        logits = plain.forward(cfg, w, prompt + o.token_ids)
+        for i, tok in enumerate(o.token_ids):
+            row = logits[len(prompt) - 1 + i]
+            assert row[tok] >= row.max() - 3e-2 * row.abs().max(), f"token {i} after {o.preemptions} preemptions"
+    tight.engine.cache.check()
+    assert tight.engine.cache.free_pages() == 9
+
+
+def test_a_step_that_fails_leaves_the_cache_as_it_was(tmp_path, monkeypatch):
+    """A kernel wrapper raises in the middle of a step, after pages were reserved and a new request got its slot:
+    the step's admissions and reservations are undone, the requests are as before, and the same step then runs
+    and gives the logits of an engine that never failed."""
+    from reinfer_b200 import ops
+    from reinfer_b200.engine import Engine, StepEntry
+    d = tiny.make_model_dir(str(tmp_path / "b16"), "B", torch.bfloat16)
+    seqs = tiny.sequences("B", lengths=[40, 21])
+    a, b = seqs["r0"], seqs["r1"]
+
+    def fresh():
+        e = Engine.from_model_dir(d, dtype="bfloat16", page_size=8, num_pages=12, max_num_seqs=2)
+        e.step([StepEntry("a", a[:19], [18])])
+        return e
+    entries = [StepEntry("a", a[19:35], [15]), StepEntry("b", b[:13], [0, 12])]
+    want = fresh().step(entries).clone()
+    e = fresh()
+    before = (e.cache.length("a"), list(e.cache.table("a", 0)), e.cache.slot("a"), e.cache.free_pages(), e.cache.free_slots())
+    calls = {"n": 0}
+    real = ops.attention
+
+    def failing(*args, **kw):
+        calls["n"] += 1
+        if calls["n"] == 2:                             # in the second layer: the first has stored its keys by then
+            raise ops.KernelError("injected")
+        return real(*args, **kw)
+    monkeypatch.setattr(ops, "attention", failing)
+    with pytest.raises(ops.KernelError, match="injected"):
+        e.step(entries)
+    monkeypatch.setattr(ops, "attention", real)
+    e.cache.check()
+    assert "b" not in e.cache
+    assert (e.cache.length("a"), list(e.cache.table("a", 0)), e.cache.slot("a"), e.cache.free_pages(), e.cache.free_slots()) == before
+    got = e.step(entries)
+    assert torch.equal(got, want)
+    # a decode step (replayed from a captured graph) that fails while it is being built: the same
+    one = [StepEntry("a", [a[35]], [0]), StepEntry("b", [b[13]], [0])]
+    before = (e.cache.length("a"), len(e.cache.table("a", 0)), e.cache.length("b"), e.cache.free_pages())
+    calls["n"] = 0
+    monkeypatch.setattr(ops, "attention", failing)
+    with pytest.raises(ops.KernelError, match="injected"):
+        e.step(one)
+    monkeypatch.setattr(ops, "attention", real)
+    e.cache.check()
+    assert (e.cache.length("a"), len(e.cache.table("a", 0)), e.cache.length("b"), e.cache.free_pages()) == before
+    ref = fresh()
+    ref.step(entries)
+    assert torch.equal(e.step(one), ref.step(one))
+
+
+def test_a_wait_that_runs_out_reaches_the_engine(model_dirs):
+    """The kernels bound every wait; one that gives up sets a word that the engine reads.  Here the self-test
+    kernel waits a millisecond for an arrival that never comes (no product kernel is made to fail): the word
+    names it, `Engine.step` and `LLM.step` refuse to go on, the requests of the failed step give back their
+    pages, and after `clear_status` the library and the engine work as before."""
+    from reinfer_b200 import LLM, SamplingParams, ops
+    from reinfer_b200.engine import Engine, KernelWaitTimeout, StepEntry
+    e = Engine.from_model_dir(model_dirs["A"], dtype="float32", page_size=16, num_pages=8, max_num_seqs=2)
+    first = e.step([StepEntry("x", [1, 2, 3], [2])]).clone()
+    assert ops.status_word() == 0
+    try:
+        flag = torch.zeros(1, dtype=torch.int32, device="cuda")
+        ops.test_bounded_wait(1_000_000, flag)
+        torch.cuda.synchronize()
+        assert int(flag.item()) == 1
+        code = ops.status_word()
+        assert code == (4 << 16) | (1 << 8) | 77
+        assert "self-test" in ops.describe_status(code)
+        with pytest.raises(KernelWaitTimeout, match="bounded wait gave up"):
+            e.step([StepEntry("x", [4], [0])])
+        assert e.cache.length("x") == 3                  # nothing was launched, nothing changed
+        llm = LLM(engine=e, max_batch_tokens=16)
+        rid = llm.add_request([5, 6, 7], SamplingParams(max_tokens=3, ignore_eos=True))
+        with pytest.raises(KernelWaitTimeout):
+            llm.step()
+        assert llm.requests[rid].finish_reason == "error" and not llm.has_work()
+        e.cache.check()
+    finally:
+        assert ops.clear_status() in (0, (4 << 16) | (1 << 8) | 77)
+    assert ops.status_word() == 0 and ops.kernel_error() == 0
+    a = torch.randn(5, 64, device="cuda").bfloat16()
+    w = torch.randn(24, 64, device="cuda").bfloat16()
+    c = torch.empty(5, 24, device="cuda")
+    ops.gemm_bf16(a, w, c)
+    assert (c - a.float() @ w.float().t()).abs().max().item() < 1e-2 * c.abs().max().item()
+    again = e.step([StepEntry("y", [1, 2, 3], [2])])
+    assert torch.equal(again, first)
 
 
 def test_out_of_vocabulary_token_is_refused(model_dirs):

@@ -271,7 +271,7 @@ def test_toy_architecture_registered_built_and_stepped(tmp_path):
 
             def run(steps):
                 e = Engine.from_model_dir(d, dtype=dtype, page_size=8, max_tokens=64, max_num_seqs=2)
-                assert not e.cuda_graphs and [g.layers for g in e.cache.groups] == [("l1",)]
+                assert not e.cuda_graphs and [g.layers for g in e.cache.groups] == [("l1",)]     # the toy mixer reads host tables
                 assert sorted(e.storage.layer_state) == ["l0", "l0#1"]
                 rows = {}
                 done = {}
@@ -304,6 +304,178 @@ def test_toy_architecture_registered_built_and_stepped(tmp_path):
         unregister_architecture("ToyStatefulLM")
         for cat, kind in (("mixer", "toy_decay"), ("ffn", "toy_routed"), ("position", "toy_signflip")):
             unregister_part(cat, kind)
+
+
+def test_stateful_mixer_that_reads_device_tables_keeps_the_decode_graphs(tmp_path):
+    """A mixer with state whose single-token step takes its slots from the device table says so, and decode-only
+    steps are then replayed from captured graphs; the rows that pad a batch to its bucket point at a slot that
+    belongs to nobody.  Eleven requests (bucket of sixteen: five rows of padding) decode together; the logits are
+    those of an engine without graphs."""
+    from reinfer_b200.config import register_architecture, unregister_architecture
+    from reinfer_b200.engine import Engine, StepEntry
+    from reinfer_b200.parts.base import Mixer, SlotStateSpec, register_part, unregister_part
+    from reinfer_b200.parts.spec import LayerSpec, ModelSpec, PartSpec
+    from reinfer_b200.weights import write_random_model
+    from reinfer_b200.weights.params import ParamSpec
+
+    class TableDecayMixer(Mixer):
+        steps_from_device_tables = True
+
+        def __init__(self, hidden, width, decay):
+            self.hidden, self.width, self.decay = hidden, width, decay
+
+        def param_specs(self):
+            return {"in.weight": ParamSpec((self.width, self.hidden)), "out.weight": ParamSpec((self.hidden, self.width))}
+
+        def bind(self, t):
+            self.w_in, self.w_out = t["in.weight"], t["out.weight"]
+
+        def state_spec(self):
+            return SlotStateSpec((self.width,), "float32")
+
+        def forward(self, ctx, xn, residual, cache):
+            u = xn.float() @ self.w_in.float().t()
+            if ctx.max_q_len == 1:                          # single tokens: everything from the device tables
+                slots = ctx.entry_slot.long()
+                s = cache.state[slots] * self.decay + u
+                cache.state[slots] = s
+                out = s
+            else:
+                out = torch.empty_like(u)
+                for e in range(ctx.n_entries):
+                    s = cache.state[ctx.slots[e]]
+                    for t in range(ctx.q_start[e], ctx.q_start[e + 1]):
+                        s.mul_(self.decay).add_(u[t])
+                        out[t] = s
+            residual += out @ self.w_out.float().t()
+
+    def spec(cfg):
+        h = cfg.hidden
+        norm = lambda p: PartSpec("rmsnorm", {"width": h, "eps": 1e-5}, p)
+        layers = tuple(LayerSpec(f"l{i}", mixer=PartSpec("toy_table_decay", {"hidden": h, "width": 24, "decay": 0.8}, f"l{i}.mix."),
+                                 ffn=PartSpec("swiglu", {"hidden": h, "intermediate": 48}, f"l{i}.ffn."),
+                                 mixer_norm=norm(f"l{i}.n1."), ffn_norm=norm(f"l{i}.n2.")) for i in range(2))
+        return ModelSpec(hidden_size=h, vocab_size=cfg.vocab, embedding=PartSpec("embedding", {"vocab": cfg.vocab, "hidden": h}, "emb."),
+                         layers=layers, final_norm=norm("final."),
+                         lm_head=PartSpec("linear", {"vocab": cfg.vocab, "hidden": h, "tied": True}, "head."))
+
+    class Config(_ToyConfig):
+        def to_dict(self):
+            return {"architectures": ["ToyTableLM"], "toy_hidden": self.hidden, "toy_vocab": self.vocab}
+
+    register_part("mixer", "toy_table_decay", TableDecayMixer)
+    register_architecture("ToyTableLM", Config, spec)
+    try:
+        d = write_random_model(str(tmp_path / "toy"), Config(), seed=6, dtype=torch.float32)
+        n = 11
+        prompts = {f"r{i}": [(3 * i + 7 * k + 1) % 97 for k in range(2 + i % 4)] for i in range(n)}
+        tails = {r: [(5 * i + 11 * k + 2) % 97 for k in range(5)] for i, r in enumerate(prompts)}
+
+        def run(graphs):
+            e = Engine.from_model_dir(d, dtype="float32", max_tokens=64, max_num_seqs=n, cuda_graphs=graphs)
+            assert e.cuda_graphs == graphs and not e.cache.groups and len(e.storage.layer_state) == 2
+            rows = [e.step([StepEntry(r, p, [len(p) - 1]) for r, p in prompts.items()])]
+            for k in range(5):
+                live = [r for i, r in enumerate(prompts) if not (k >= 3 and i % 3 == 0)]      # some leave early
+                rows.append(e.step([StepEntry(r, [tails[r][k]], [0]) for r in live]))
+                if k == 2:
+                    for i, r in enumerate(prompts):
+                        if i % 3 == 0:
+                            e.finish(r)
+            return torch.cat(rows).double().cpu(), e.graph_replays
+        eager, n0 = run(False)
+        graphed, n1 = run(True)
+        assert n0 == 0 and n1 == 5
+        assert (graphed - eager).abs().max().item() <= 1e-5 * eager.abs().max().item()
+    finally:
+        unregister_architecture("ToyTableLM")
+        unregister_part("mixer", "toy_table_decay")
+
+
+def test_a_block_with_four_norms_needs_a_block_class_only(tmp_path):
+    """A layer is a block over parts named by role, and which roles there are is the block's business: a
+    'sandwich' arrangement (a norm before and a norm after the mixer, and the same around the feed-forward) is
+    defined and registered here, built from a model folder and stepped under several cuts, and agrees with the
+    same arithmetic written with the plain functions."""
+    from reinfer_b200.config import register_architecture, unregister_architecture
+    from reinfer_b200.engine import Engine, StepEntry
+    from reinfer_b200.parts.base import register_part, unregister_part
+    from reinfer_b200.parts.spec import LayerSpec, ModelSpec, PartSpec
+    from reinfer_b200.weights import write_random_model
+
+    class SandwichBlock:
+        roles = ("pre_mixer_norm", "mixer", "post_mixer_norm", "pre_ffn_norm", "ffn", "post_ffn_norm")
+
+        def __init__(self, parts):
+            assert set(self.roles) <= set(parts)
+            self.p = parts
+
+        def forward(self, ctx, x, cache):
+            p = self.p
+            for pre, inner, post, args in ((p["pre_mixer_norm"], p["mixer"], p["post_mixer_norm"], (cache,)),
+                                           (p["pre_ffn_norm"], p["ffn"], p["post_ffn_norm"], ())):
+                branch = torch.zeros_like(x)                        # the inner part adds its output into what it is given
+                inner.forward(ctx, pre.forward(ctx, x), branch, *args)
+                x += post.forward(ctx, branch).float()
+
+    H, V, QH, KH, D, F = 48, 101, 4, 2, 16, 80
+
+    def spec(cfg):
+        norm = lambda p, eps=1e-5: PartSpec("rmsnorm", {"width": H, "eps": eps}, p)
+        layers = tuple(LayerSpec(
+            f"l{i}", block="toy_sandwich",
+            pre_mixer_norm=norm(f"l{i}.n1."), post_mixer_norm=norm(f"l{i}.n2."),
+            mixer=PartSpec("attention", {"hidden": H, "q_heads": QH, "kv_heads": KH, "head_dim": D, "qk_norm": True,
+                                         "qk_norm_eps": 1e-5, "position": {"kind": "rope", "head_dim": D, "theta": 1e4}},
+                           f"l{i}.att."),
+            pre_ffn_norm=norm(f"l{i}.n3."), post_ffn_norm=norm(f"l{i}.n4."),
+            ffn=PartSpec("swiglu", {"hidden": H, "intermediate": F}, f"l{i}.ffn.")) for i in range(2))
+        return ModelSpec(hidden_size=H, vocab_size=V, embedding=PartSpec("embedding", {"vocab": V, "hidden": H}, "emb."),
+                         layers=layers, final_norm=norm("final."),
+                         lm_head=PartSpec("linear", {"vocab": V, "hidden": H, "tied": True}, "head."))
+
+    class Config(_ToyConfig):
+        def to_dict(self):
+            return {"architectures": ["ToySandwichLM"], "toy_hidden": H, "toy_vocab": V}
+
+    def plain_forward(w, tokens):
+        cfg = dict(num_attention_heads=QH, num_key_value_heads=KH, head_dim=D, rms_norm_eps=1e-5, rope_theta=1e4, hidden_size=H)
+        pos = torch.arange(len(tokens))
+        x = plain.embed(w["emb.weight"], tokens)
+        for i in range(2):
+            a = plain.attention_block(plain.rms_norm(x, w[f"l{i}.n1.weight"], 1e-5), w, f"l{i}.att.", cfg, pos)
+            x = x + plain.rms_norm(a, w[f"l{i}.n2.weight"], 1e-5)
+            f = plain.swiglu_ffn(plain.rms_norm(x, w[f"l{i}.n3.weight"], 1e-5), w[f"l{i}.ffn.gate_proj.weight"],
+                                 w[f"l{i}.ffn.up_proj.weight"], w[f"l{i}.ffn.down_proj.weight"])
+            x = x + plain.rms_norm(f, w[f"l{i}.n4.weight"], 1e-5)
+        return plain.linear(plain.rms_norm(x, w["final.weight"], 1e-5), w["emb.weight"])
+
+    register_part("block", "toy_sandwich", SandwichBlock)
+    register_architecture("ToySandwichLM", Config, spec)
+    try:
+        d = write_random_model(str(tmp_path / "toy"), Config(), seed=8, dtype=torch.float32)
+        w = plain.read_safetensors(os.path.join(d, "model.safetensors"))
+        seq = [(13 * i + 2) % V for i in range(37)]
+        ref = plain_forward(w, seq)
+        for cuts in ([37], [9, 2, 17, 1, 1, 7], [1] * 37):
+            e = Engine.from_model_dir(d, dtype="float32", page_size=8, max_tokens=40, max_num_seqs=1)
+            rows, i = [], 0
+            for n in cuts:
+                rows.append(e.step([StepEntry("a", seq[i:i + n], list(range(n)))]).double().cpu())
+                i += n
+            got = torch.cat(rows)
+            assert (got - ref).abs().max().item() <= 1e-4 * ref.abs().max().item()
+        # a layer that lacks a role its block needs is refused when the model is built, by name
+        with pytest.raises(ValueError, match="ffn_norm"):
+            from reinfer_b200.parts.model import Model
+            Model(ModelSpec(hidden_size=H, vocab_size=V, embedding=PartSpec("embedding", {"vocab": V, "hidden": H}, "emb."),
+                            layers=(LayerSpec("l0", block="prenorm", mixer=spec(None).layers[0].mixer,
+                                              ffn=spec(None).layers[0].ffn, mixer_norm=spec(None).layers[0].pre_mixer_norm),),
+                            final_norm=PartSpec("rmsnorm", {"width": H, "eps": 1e-5}, "final."),
+                            lm_head=PartSpec("linear", {"vocab": V, "hidden": H, "tied": True}, "head.")))
+    finally:
+        unregister_architecture("ToySandwichLM")
+        unregister_part("block", "toy_sandwich")
 
 
 def _window_spec(cfg):

@@ -139,3 +139,65 @@ def test_broken_files(tmp_path):
         SafetensorsFile(str(p))
     with pytest.raises(FileNotFoundError):
         open_model_tensors(str(tmp_path / "nothing"))
+
+
+def ulps_apart(a: torch.Tensor, b: torch.Tensor) -> torch.Tensor:
+    """Distance of float32 values in units in the last place (bit patterns as ordered integers)."""
+    def key(t):
+        i = t.contiguous().view(torch.int32).long()
+        return torch.where(i < 0, -(i & 0x7FFFFFFF), i)
+    return (key(a) - key(b)).abs()
+
+
+def same_up_to_library_rounding(a: torch.Tensor, b: torch.Tensor) -> None:
+    """Two evaluations of the generator's formula: equal, but for the rare element whose float64
+    logarithm or cosine differs in its last bit between two mathematical libraries and lies on a
+    float32 rounding boundary (one unit in the last place, a few elements in 10^8)."""
+    apart = ulps_apart(a.float(), b.float())
+    assert int(apart.max()) <= 1
+    assert int((apart > 0).sum()) <= max(1, a.numel() // 1_000_000)
+
+
+@pytest.mark.parametrize("which", ["A", "B"])
+def test_random_weights_are_the_stated_function_of_seed_name_and_index(tmp_path, which):
+    """The package's generator, the folder it writes and the tests' own statement of the rule give the
+    same tensors; a tensor does not depend on the others, nor on the pieces it is drawn in."""
+    import plain_random
+    from reinfer_b200.weights import random as rnd
+    from reinfer_b200.weights import random_state
+    raw, seed, _ = tiny.TINY[which]
+    exp = _expected(raw)
+    drawn = random_state(exp, seed, torch.float32, "cpu")
+    want = plain_random.qwen3_weights(raw, seed)
+    assert sorted(drawn) == sorted(want)
+    for name in want:
+        assert drawn[name].shape == want[name].shape
+        same_up_to_library_rounding(drawn[name], want[name])
+    d = write_random_model(str(tmp_path / "m"), Qwen3Config.from_dict(raw), seed, torch.float32)
+    stored = load_state(d, exp, torch.float32, "cpu")
+    assert all(torch.equal(stored[k], drawn[k]) for k in drawn)
+    # bfloat16: the same float32 values, rounded once
+    b16 = random_state(exp, seed, torch.bfloat16, "cpu")
+    want16 = plain_random.qwen3_weights(raw, seed, store="bfloat16")
+    for name in want16:
+        assert int((b16[name].float() != want16[name]).sum()) <= 1
+    # one tensor alone, and a piece of it from the middle
+    name = "model.layers.1.mlp.down_proj.weight"
+    alone = random_state({name: exp[name]}, seed, torch.float32, "cpu")[name]
+    assert torch.equal(alone, drawn[name])
+    base = rnd.stream_base(seed, name)
+    assert base == plain_random.tensor_base(seed, name)
+    whole = rnd.normal_cpu((alone.numel(),), base, 0.0, 0.02)
+    assert torch.equal(whole.reshape(alone.shape), alone)
+    assert rnd.stream_base(seed + 1, name) != base and rnd.stream_base(seed, name + "x") != base
+
+
+def test_random_weights_have_the_stated_moments():
+    from reinfer_b200.weights import random as rnd
+    t = rnd.normal_cpu((1 << 20,), rnd.stream_base(3, "t"), 0.0, 0.02).double()
+    assert abs(t.mean().item()) < 1e-4 and abs(t.std().item() - 0.02) < 1e-4
+    assert abs(((t / 0.02) ** 4).mean().item() - 3.0) < 0.05            # a normal's fourth moment
+    n = rnd.normal_cpu((1 << 16,), rnd.stream_base(3, "n"), 1.0, 0.05).double()
+    assert abs(n.mean().item() - 1.0) < 1e-3 and abs(n.std().item() - 0.05) < 1e-3
+    i = rnd.ints_cpu((1 << 16,), rnd.stream_base(3, "i"))
+    assert i.dtype == torch.int32 and int(i.min()) >= 0 and int(i.max()) < (1 << 15) and int(i.max()) > 32000

@@ -26,7 +26,7 @@ def make_model_dir(path: str, which: str, store_dtype=torch.float32) -> str:
 def sequences(which: str, lengths=None, seed=7) -> Dict[str, List[int]]:
     cfg = TINY[which][0]
     rnd = random.Random(seed)
-    lengths = lengths or ([5, 17, 33, 70] if which == "A" else [1, 9, 24, 50, 90])
+    lengths = lengths or ([5, 17, 33, 70, 40, 26, 51] if which == "A" else [1, 9, 24, 50, 90, 37, 64, 12, 77, 58])
     return {f"r{i}": [rnd.randrange(cfg["vocab_size"]) for _ in range(n)] for i, n in enumerate(lengths)}
 
 
@@ -88,14 +88,35 @@ def cut_mixed(seqs, seed=3, max_live=4, decode_tail=12) -> List[Step]:
     return steps
 
 
-def pool_tokens_needed(steps: List[Step]) -> int:
-    """Most tokens live at once, each request rounded up to a multiple of 64."""
+def pool_tokens_needed(steps: List[Step], page: int = 64) -> int:
+    """Most tokens that live requests hold at once, each request's count rounded up to whole pages of `page`
+    tokens: with page = the engine's page size this is exactly what the steps need and not a page more (so
+    pages that a finished request gives back are the only ones a later request can get); with page = 64 it
+    is the `--max-tokens` rule of bin/trace_run."""
     held: Dict[str, int] = {}
     worst = 0
     for entries, end in steps:
         for r, t, _ in entries:
             held[r] = held.get(r, 0) + len(t)
-        worst = max(worst, sum(-(-n // 64) * 64 for n in held.values()))
+        worst = max(worst, sum(-(-n // page) * page for n in held.values()))
         for r in end:
             held.pop(r, None)
     return worst
+
+
+class PageOwners:
+    """Watches a cache manager between steps and counts the pages that passed from one request to another."""
+
+    def __init__(self, cache, group: int = 0):
+        self.cache, self.group = cache, group
+        self.owner: Dict[int, str] = {}
+        self.reused = set()
+
+    def look(self) -> None:
+        for rid in self.cache.live():
+            for p in self.cache.table(rid, self.group):
+                if p < 0:
+                    continue
+                if p in self.owner and self.owner[p] != rid:
+                    self.reused.add(p)
+                self.owner[p] = rid
