@@ -2,7 +2,10 @@
 `[layers, pages, 2 (k, v), kv_heads, page_size, head_dim]` (a layer's slice is what
 its kernels get; inside a page the layout is head-major, so the keys of one
 (page, head) are one dense `[page_size, head_dim]` tile), and for each layer with a
-fixed-size state one array `[slots + 1, *shape]` (the last row is nobody's).
+fixed-size state one array `[slots + 1, *shape]` (the last row is nobody's); and the
+slots' own rows: last token, sampler record, recent tokens (the reference keeps these on
+the host, bin/reinfer/src/sched_loop.rs:464-485, and only transient `[B]` rows on the
+device, crates/cuda/src/engine.rs:1854-1875).
 (The reference keeps one f16 buffer, K region then V region, layer folded into the
 page index: crates/cuda/src/decode.rs:664-698.)
 """
@@ -13,6 +16,10 @@ from typing import Dict, List
 import torch
 
 from .manager import CacheManager
+
+
+SLOT_RECORD_BYTES = 64          # sizeof(RbSampleParams); the sampler checks it against the library
+SLOT_HISTORY = 64               # tokens of the penalty window a slot can hold
 
 
 class CacheStorage:
@@ -35,6 +42,12 @@ class CacheStorage:
             # decode step point at it, so that they disturb no request's state)
             self.layer_state[name] = torch.zeros((manager.max_seqs + 1,) + tuple(spec.shape), dtype=sdt, device=self.device)
         self.inert_slot = manager.max_seqs
+        # the request slots' own rows (as many, plus nobody's): the token last drawn for the request, the sampler's
+        # record (parameters, seed, count of draws: csrc/sampler.cu RbSampleParams) and its ring of recent tokens.
+        # The sampler kernel reads and writes them; the host writes a row when a request is admitted.
+        self.slot_token = torch.zeros(manager.max_seqs + 1, dtype=torch.int32, device=self.device)
+        self.slot_records = torch.zeros((manager.max_seqs + 1, SLOT_RECORD_BYTES), dtype=torch.uint8, device=self.device)
+        self.slot_history = torch.zeros((manager.max_seqs + 1, SLOT_HISTORY), dtype=torch.int32, device=self.device)
 
     def zero_slot(self, slot: int) -> None:
         """A fixed-size state starts at zero when its request is admitted."""

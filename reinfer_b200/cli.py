@@ -7,7 +7,9 @@ printed on one line.  `--perf` adds the reference's machine-readable line
 (main.rs:700-727).  The model is a local folder, or a name looked up under `$REINFER_MODEL_DIR`
 (default `~/.reinfer/models`; main.rs:540-558 - nothing is ever downloaded here).  `--backend`
 takes the reference's names; only `auto` and `cuda` run (main.rs:483-509).  `reinfer random-model`
-writes a model folder with seeded random weights.
+writes a model folder with seeded random weights.  `reinfer bench --shape qwen3-8b|4b|32b|<config.json>
+--batch 1,8,64 --prompt-len 2048 --decode-len N` measures a random-weight model of that shape (the
+reference measures through `run --perf` and its server's load generator, main.rs:700-727).
 """
 from __future__ import annotations
 
@@ -96,6 +98,43 @@ def cmd_random_model(a) -> int:
     return 0
 
 
+def cmd_bench(a) -> int:
+    """Prefill and decode throughput of a random-weight model of a given shape (reinfer_b200/measure.py)."""
+    from . import measure
+    batches = [int(b) for b in a.batch.split(",") if b]
+    context = a.context or a.prompt_len + a.decode_len
+    page = a.page_size
+    need = max(batches) * (context + page) + 2 * a.prompt_len + 4096
+    hbm, tf, _, src = measure.peaks()
+    b = measure.Bench(a.shape, layers=a.layers, page_size=page, dtype=a.dtype, pool_tokens=need,
+                      max_num_seqs=max(batches) + 1, seed=a.seed)
+    print(f"{os.path.basename(measure.shape_path(a.shape))}: {b.layers} of {b.full_layers} layers, {b.weight_bytes / 1e9:.2f} GB "
+          f"of weights a step, {b.kv_bytes_per_token} B of cache a token, pages of {page}; peaks {src}: {hbm:.0f} GB/s, "
+          f"{tf:.0f} TFLOP/s", file=sys.stderr)
+    out = {"shape": a.shape, "layers": b.layers, "dtype": a.dtype, "page_size": page}
+    p = b.prefill(a.prompt_len)
+    out["prefill"] = {"tokens": a.prompt_len, "ms": p["ms"], "tokens_per_s": p["value"],
+                      "frac_of_peak": p["flops"] / (p["ms"] * 1e-3) / (tf * 1e12)}
+    print(f"prefill {a.prompt_len:6d} tokens: {p['ms']:8.2f} ms  {p['value']:10.0f} tok/s  {100 * out['prefill']['frac_of_peak']:5.1f} % of the "
+          f"tensor-core peak", file=sys.stderr)
+    out["decode"] = []
+    for B in batches:
+        r = b.decode(B, a.decode_len, 3, context)
+        frac = r["bytes"] / (r["ms_device"] * 1e-3) / 1e9 / hbm
+        out["decode"].append({"batch": B, "context": context, "ms_device": r["ms_device"], "ms_e2e": r["ms_e2e"],
+                              "tokens_per_s": B / r["ms_device"] * 1e3, "e2e_tokens_per_s": B / r["ms_e2e"] * 1e3,
+                              "frac_of_bandwidth": frac})
+        print(f"decode  batch {B:4d} at {context:6d}: {r['ms_device']:8.3f} ms/step  {B / r['ms_device'] * 1e3:10.1f} tok/s on the device, "
+              f"{B / r['ms_e2e'] * 1e3:10.1f} end to end  {100 * frac:5.1f} % of the copy bandwidth", file=sys.stderr)
+    if a.segments:
+        for kind in ("decode", "prefill"):
+            seg = b.segments(kind, B=batches[0], context=context, T=a.prompt_len)
+            print(f"-- one eager {kind} step by segment --", file=sys.stderr)
+            print("\n".join(measure.segment_table(seg, hbm, tf)), file=sys.stderr)
+    print(json.dumps(out))
+    return 0
+
+
 def main(argv=None) -> int:
     ap = argparse.ArgumentParser(prog="reinfer", description="B200-native inference engine (token ids in, token ids out)")
     sub = ap.add_subparsers(dest="cmd", required=True)
@@ -126,6 +165,18 @@ def main(argv=None) -> int:
     m.add_argument("--seed", type=int, default=0)
     m.add_argument("--dtype", choices=["bfloat16", "float32"], default="bfloat16")
     m.set_defaults(fn=cmd_random_model)
+    b = sub.add_parser("bench", help="throughput of a random-weight model of a given shape")
+    b.add_argument("--shape", default="qwen3-8b", help="qwen3-8b, qwen3-4b, qwen3-32b (or 8b, 4b, 32b), or a config.json")
+    b.add_argument("--batch", default="1,8,64", help="decode batch sizes, comma separated")
+    b.add_argument("--prompt-len", type=int, default=2048)
+    b.add_argument("--decode-len", type=int, default=32, help="timed decode steps per batch size")
+    b.add_argument("--context", type=int, default=None, help="tokens a request holds at the end (default prompt + decode)")
+    b.add_argument("--dtype", choices=["bfloat16"], default="bfloat16")
+    b.add_argument("--page-size", type=int, default=16)
+    b.add_argument("--layers", type=int, default=None, help="build only this many layers of the shape")
+    b.add_argument("--seed", type=int, default=0)
+    b.add_argument("--segments", action="store_true", help="also time one eager step of each kind launch by launch")
+    b.set_defaults(fn=cmd_bench)
     a, extra = ap.parse_known_args(argv)
     if extra:
         # token ids that follow options (argparse binds a '*' positional before it sees them)

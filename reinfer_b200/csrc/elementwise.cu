@@ -8,26 +8,35 @@
 // x[t,:] = E[ids[t],:]   (reference: crates/cuda/kernels/dense_kernels.cu:329-336)
 template <typename TW>
 __global__ void embed_gather_kernel(const TW* __restrict__ table, const int* __restrict__ ids,
-                                    float* __restrict__ out, int h, int vocab) {
+                                    const int* __restrict__ slot_token, const int* __restrict__ entry_slot,
+                                    const int* __restrict__ tok_entry, float* __restrict__ out, int h, int vocab) {
     pdl_trigger(); pdl_wait();
     const int t = blockIdx.x;
     int id = ids[t];
-    const bool ok = (id >= 0 && id < vocab);          // the host refuses such ids before launching
+    // a negative id stands for "the token that the sampler drew for this request in the step before": it is in
+    // the request's slot on the device, so the host need not have seen it yet
+    if (id < 0 && slot_token) id = slot_token[entry_slot[tok_entry[t]]];
+    const bool ok = (id >= 0 && id < vocab);          // the host refuses other ids before launching
     const TW* row = table + (size_t)(ok ? id : 0) * h;
     float* o = out + (size_t)t * h;
     for (int i = threadIdx.x; i < h; i += blockDim.x) o[i] = ok ? to_f32(row[i]) : 0.0f;
 }
 
-extern "C" int rb_embed_gather(const void* table, int table_dtype, const int* ids, float* out,
+// slot_token [slots], entry_slot [entries], tok_entry [tokens]: all three, or none (then every id must be >= 0).
+extern "C" int rb_embed_gather(const void* table, int table_dtype, const int* ids, const int* slot_token,
+                               const int* entry_slot, const int* tok_entry, float* out,
                                int n_tokens, int h, int vocab, void* stream) {
     if (n_tokens <= 0) return 0;
     if (h <= 0 || vocab <= 0) RB_REFUSE("embed_gather: hidden=%d vocab=%d", h, vocab);
+    if (slot_token && (!entry_slot || !tok_entry)) RB_REFUSE("embed_gather: tokens from slots need the slot of each entry and the entry of each token");
     cudaStream_t s = (cudaStream_t)stream;
     const int threads = h >= 1024 ? 256 : 128;
     if (table_dtype == RB_F32)
-        return rb_launch(embed_gather_kernel<float>, dim3(n_tokens), dim3(threads), 0, s, (const float*)table, ids, out, h, vocab);
+        return rb_launch(embed_gather_kernel<float>, dim3(n_tokens), dim3(threads), 0, s, (const float*)table, ids,
+                         slot_token, entry_slot, tok_entry, out, h, vocab);
     if (table_dtype == RB_BF16)
-        return rb_launch(embed_gather_kernel<bf16>, dim3(n_tokens), dim3(threads), 0, s, (const bf16*)table, ids, out, h, vocab);
+        return rb_launch(embed_gather_kernel<bf16>, dim3(n_tokens), dim3(threads), 0, s, (const bf16*)table, ids,
+                         slot_token, entry_slot, tok_entry, out, h, vocab);
     RB_REFUSE("embed_gather: table dtype %d", table_dtype);
 }
 

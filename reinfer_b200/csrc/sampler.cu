@@ -36,7 +36,7 @@ struct RbSampleParams {          // one per row; mirrored by ctypes in sampling/
     unsigned long long step;     // index of this draw in the request's stream
     const int2* bias;            // bias_len pairs (token id, float bits): added to the logits first of all
     int bias_len;
-    int reserved;
+    int hist_window;             // slot records only: the history is a ring of this many tokens (0: none is kept)
 };
 
 __device__ __forceinline__ unsigned long long sp_mix(unsigned long long z) {
@@ -89,17 +89,15 @@ __device__ __forceinline__ unsigned long long block_sum_u64(unsigned long long v
     return r;
 }
 
-__global__ void __launch_bounds__(SP_THREADS)
-sample_kernel(const float* __restrict__ logits, long long ld_logits, const int* __restrict__ row_idx,
-              const RbSampleParams* __restrict__ params, const int* __restrict__ history, int hist_cap,
-              float* __restrict__ work, int* __restrict__ out_tokens, int vocab) {
+// One row: the token for logits `lg` under the record P, with `hist` the recent tokens (P.hist_len of them, in
+// any order) and `w` a scratch row of vocab floats.  Every thread of the block returns the same token (-1: no
+// finite logit).
+__device__ int sample_row(const float* __restrict__ lg, const RbSampleParams& P, const int* __restrict__ hist,
+                          float* __restrict__ w, int vocab) {
     __shared__ float sval[32];
     __shared__ int sidx[32];
     __shared__ float red[32];
     __shared__ unsigned long long red64[32];
-    const int r = blockIdx.x;
-    const RbSampleParams P = params[r];
-    const float* lg = logits + (size_t)(row_idx ? row_idx[r] : r) * ld_logits;
     const int tid = threadIdx.x;
 
     const bool penalties = P.hist_len > 0 &&
@@ -114,11 +112,9 @@ sample_kernel(const float* __restrict__ logits, long long ld_logits, const int* 
             if (isfinite(v) && (v > bv || (v == bv && i < bi))) { bv = v; bi = i; }
         }
         block_argmax(bv, bi, sval, sidx);
-        if (tid == 0) out_tokens[r] = (bi == 0x7fffffff) ? -1 : bi;
-        return;
+        return (bi == 0x7fffffff) ? -1 : bi;
     }
 
-    float* w = work + (size_t)r * vocab;
     for (int i = tid; i < vocab; i += SP_THREADS) {
         const float v = lg[i];
         w[i] = isfinite(v) ? v : -FLT_MAX;
@@ -134,7 +130,6 @@ sample_kernel(const float* __restrict__ logits, long long ld_logits, const int* 
     }
     if (penalties) {
         // one thread per history entry; the first occurrence of a token applies the penalty
-        const int* hist = history + (size_t)r * hist_cap;
         for (int j = tid; j < P.hist_len; j += SP_THREADS) {
             const int tok = hist[j];
             if (tok < 0 || tok >= vocab) continue;
@@ -158,8 +153,7 @@ sample_kernel(const float* __restrict__ logits, long long ld_logits, const int* 
             if (v != -FLT_MAX && (v > bv || (v == bv && i < bi))) { bv = v; bi = i; }
         }
         block_argmax(bv, bi, sval, sidx);
-        if (tid == 0) out_tokens[r] = (bi == 0x7fffffff) ? -1 : bi;
-        return;
+        return (bi == 0x7fffffff) ? -1 : bi;
     }
 
     // temperature, maximum
@@ -170,7 +164,7 @@ sample_kernel(const float* __restrict__ logits, long long ld_logits, const int* 
         if (v != -FLT_MAX) { v *= inv_t; w[i] = v; mx = fmaxf(mx, v); }
     }
     mx = block_max(mx, red);
-    if (!(mx > -INFINITY)) { if (tid == 0) out_tokens[r] = -1; return; }
+    if (!(mx > -INFINITY)) return -1;
     __syncthreads();
 
     // survivors are {i : key(i) >= key_floor and w[i] >= val_floor}
@@ -239,7 +233,48 @@ sample_kernel(const float* __restrict__ logits, long long ld_logits, const int* 
         }
         block_argmax(bv, bi, sval, sidx);
     }
-    if (tid == 0) out_tokens[r] = (bi == 0x7fffffff) ? -1 : bi;
+    return (bi == 0x7fffffff) ? -1 : bi;
+}
+
+__global__ void __launch_bounds__(SP_THREADS)
+sample_kernel(const float* __restrict__ logits, long long ld_logits, const int* __restrict__ row_idx,
+              const RbSampleParams* __restrict__ params, const int* __restrict__ history, int hist_cap,
+              float* __restrict__ work, int* __restrict__ out_tokens, int vocab) {
+    const int r = blockIdx.x;
+    const RbSampleParams P = params[r];
+    const float* lg = logits + (size_t)(row_idx ? row_idx[r] : r) * ld_logits;
+    const int tok = sample_row(lg, P, history + (size_t)r * hist_cap, work + (size_t)r * vocab, vocab);
+    if (threadIdx.x == 0) out_tokens[r] = tok;
+}
+
+// The same choice with everything about the request taken from its slot on the device: row r of the logits belongs
+// to the request in slot row_slot[r]; its record (parameters, seed, count of draws so far) and its ring of recent
+// tokens are rows of the slot tables.  The kernel writes the token into the slot (where the next step's embedding
+// finds it), appends it to the ring, counts the draw, and reports the token in out_tokens[r] for the host.  The
+// host writes a slot's record when the request is admitted and never again, so a decode step needs no upload for
+// its sampler and the launch can live in a captured graph.  Two rows of one launch must not name the same slot
+// (but for the slot that belongs to nobody, which rows of padding share: what they leave there is never read).
+__global__ void __launch_bounds__(SP_THREADS)
+sample_slots_kernel(const float* __restrict__ logits, long long ld_logits, const int* __restrict__ row_slot,
+                    RbSampleParams* __restrict__ slot_params, int* __restrict__ slot_history, int hist_cap,
+                    int* __restrict__ slot_token, float* __restrict__ work, int* __restrict__ out_tokens, int vocab) {
+    pdl_trigger(); pdl_wait();
+    const int r = blockIdx.x;
+    const int s = row_slot[r];
+    const RbSampleParams P = slot_params[s];
+    int* hist = slot_history + (size_t)s * hist_cap;
+    const int tok = sample_row(logits + (size_t)r * ld_logits, P, hist, work + (size_t)r * vocab, vocab);
+    __syncthreads();                                        // every thread has read the ring before it changes
+    if (threadIdx.x == 0) {
+        out_tokens[r] = tok;
+        slot_token[s] = tok;
+        slot_params[s].step = P.step + 1ull;
+        const int window = P.hist_window < hist_cap ? P.hist_window : hist_cap;
+        if (window > 0 && tok >= 0) {
+            hist[(int)(P.step % (unsigned long long)window)] = tok;      // the n-th draw lives at n mod window
+            if (P.hist_len < window) slot_params[s].hist_len = P.hist_len + 1;
+        }
+    }
 }
 
 // logits [*, ld_logits] floats; row r of the launch reads logits row row_idx[r] (or r);
@@ -254,6 +289,19 @@ extern "C" int rb_sample(const float* logits, long long ld_logits, const int* ro
     sample_kernel<<<rows, SP_THREADS, 0, (cudaStream_t)stream>>>(
         logits, ld_logits, row_idx, (const RbSampleParams*)params, history, hist_cap, work, out_tokens, vocab);
     return RB_LAUNCH_RESULT();
+}
+
+// logits [rows, ld_logits] floats; row_slot [rows]; slot_params [slots] records; slot_history [slots, hist_cap];
+// slot_token [slots]; work [rows, vocab] floats of scratch; out_tokens [rows].
+extern "C" int rb_sample_slots(const float* logits, long long ld_logits, const int* row_slot, void* slot_params,
+                               int* slot_history, int hist_cap, int* slot_token, float* work, int* out_tokens,
+                               int rows, int vocab, void* stream) {
+    if (rows <= 0) return 0;
+    if (vocab <= 0 || hist_cap <= 0) RB_REFUSE("sample_slots: vocab %d, history of %d", vocab, hist_cap);
+    if (!row_slot || !slot_params || !slot_history || !slot_token || !work || !out_tokens)
+        RB_REFUSE("sample_slots: a table is missing");
+    return rb_launch(sample_slots_kernel, dim3(rows), dim3(SP_THREADS), 0, (cudaStream_t)stream, logits, ld_logits, row_slot,
+                     (RbSampleParams*)slot_params, slot_history, hist_cap, slot_token, work, out_tokens, vocab);
 }
 
 extern "C" int rb_sample_params_size() { return (int)sizeof(RbSampleParams); }

@@ -23,6 +23,7 @@ import torch
 
 from .. import ops
 from ..cache import CacheManager, CacheStorage, OutOfPages
+from ..hostio import PinnedRing
 from ..config.registry import load_config, resolve_architecture
 from ..parts.context import GroupView, LayerCache, StepContext
 from ..parts.model import Model
@@ -42,10 +43,13 @@ class EmbeddingOov(EngineError):
     (crates/cuda/src/engine.rs:3784-3786)."""
 
 
+FROM_SLOT = -1      # in place of a token id: "the token that the sampler drew for this request in the step before"
+
+
 @dataclass
 class StepEntry:
     request_id: Hashable
-    tokens: Sequence[int]
+    tokens: Sequence[int]                    # ids; a single FROM_SLOT for a live request whose last draw the host has not read yet
     want: Sequence[int] = ()                 # indices into `tokens`
 
 
@@ -64,32 +68,6 @@ def parse_dtype(d) -> torch.dtype:
         raise EngineError(f"dtype {d!r}: expected float32 or bfloat16") from None
 
 
-class _Staging:
-    """A small ring of pinned int32 buffers; a buffer is reused only after the copy that read
-    it has finished (an event per buffer)."""
-
-    def __init__(self, n_buffers: int = 4, capacity: int = 1 << 16):
-        self.bufs = [torch.empty(capacity, dtype=torch.int32, pin_memory=True) for _ in range(n_buffers)]
-        self.events: List[Optional[torch.cuda.Event]] = [None] * n_buffers
-        self.i = 0
-
-    def upload(self, host: np.ndarray, device, into: Optional[torch.Tensor] = None) -> torch.Tensor:
-        n = host.shape[0]
-        i = self.i
-        self.i = (self.i + 1) % len(self.bufs)
-        if self.events[i] is not None:
-            self.events[i].synchronize()
-        if self.bufs[i].numel() < n:
-            self.bufs[i] = torch.empty(max(n, 2 * self.bufs[i].numel()), dtype=torch.int32, pin_memory=True)
-        self.bufs[i][:n].numpy()[:] = host
-        dev = into if into is not None else torch.empty(n, dtype=torch.int32, device=device)
-        dev[:n].copy_(self.bufs[i][:n], non_blocking=True)
-        ev = torch.cuda.Event()
-        ev.record()
-        self.events[i] = ev
-        return dev
-
-
 class Engine:
     """Built from a model folder (`from_model_dir`) or from a configuration with random
     weights made on the device (`from_config`)."""
@@ -97,7 +75,9 @@ class Engine:
     def __init__(self, config, spec, state: Dict[str, torch.Tensor], dtype: torch.dtype, *,
                  page_size: int = 64, num_pages: Optional[int] = None, max_tokens: Optional[int] = None,
                  max_num_seqs: int = 64, device="cuda:0", memory_fraction: float = 0.9,
-                 cuda_graphs: bool = True):
+                 cuda_graphs: bool = True, consume_state: bool = False):
+        """consume_state: the dictionary of tensors may be emptied once the parts hold what they need (the parts
+        concatenate some of them; the originals would else stay alive beside the copies)."""
         self.device = torch.device(device)
         torch.cuda.set_device(self.device)
         ops.require_device()
@@ -105,6 +85,9 @@ class Engine:
         self.dtype = dtype
         self.model = Model(spec)
         self.model.bind(state)
+        if consume_state:
+            state.clear()
+            torch.cuda.empty_cache()            # what the copies replaced goes back to the driver before memory is counted
         self.model.prepare(self.device, dtype)
         self.vocab_size = spec.vocab_size
         paged, states = self.model.cache_layout()
@@ -116,9 +99,14 @@ class Engine:
                 num_pages = self._pages_from_memory(paged, memory_fraction, max_num_seqs)
         self.cache = CacheManager(paged, states, self.page_size, int(num_pages), int(max_num_seqs))
         self.storage = CacheStorage(self.cache, dtype, self.device)
-        self._staging = _Staging()
+        self._staging = PinnedRing()
         ops.status_word()                       # binds the kernels' error word to host memory (before any capture)
         self._undo = None                       # the cache manager's snapshot from before the step in progress
+        # What the owner of the engine hangs onto a step (the sampler does): `on_admit(request_id, slot)` when a
+        # request gets its slot; `epilogue(logits, want_slot, rows)` after the forward pass, on the same stream,
+        # with the slot of the request behind each wanted row - inside the captured graph for decode-only steps.
+        self.on_admit = None
+        self._epilogue = None
         self.steps_run = 0
         # decode-only steps replay a captured CUDA graph per (batch bucket, block-table width).  Padding rows
         # point at a slot that belongs to nobody.  A mixer with state takes part only if it says that its
@@ -130,6 +118,16 @@ class Engine:
         self._graph_pool = None
         self.graph_replays = 0
 
+    @property
+    def epilogue(self):
+        return self._epilogue
+
+    @epilogue.setter
+    def epilogue(self, fn) -> None:
+        if fn is not self._epilogue:
+            self._graphs.clear()                # captured steps hold the old epilogue's launches
+        self._epilogue = fn
+
     # ---- construction ---------------------------------------------------------------
     @classmethod
     def from_model_dir(cls, model_dir: str, dtype="bfloat16", device="cuda:0", **kw) -> "Engine":
@@ -138,7 +136,7 @@ class Engine:
         spec = arch.build_spec(config)
         expected = Model(spec).param_specs()
         state = load_state(model_dir, expected, dt, torch.device(device), ignorable=spec.ignorable_tensors)
-        return cls(config, spec, state, dt, device=device, **kw)
+        return cls(config, spec, state, dt, device=device, consume_state=True, **kw)
 
     @classmethod
     def from_config(cls, config, seed: int = 0, dtype="bfloat16", device="cuda:0", **kw) -> "Engine":
@@ -148,7 +146,7 @@ class Engine:
         spec = arch.build_spec(config)
         expected = Model(spec).param_specs()
         state = random_state(expected, seed, dt, torch.device(device))
-        return cls(config, spec, state, dt, device=device, **kw)
+        return cls(config, spec, state, dt, device=device, consume_state=True, **kw)
 
     def _pages_from_memory(self, paged, fraction: float, max_num_seqs: int) -> int:
         """pages = floor((fraction * total - in use) / bytes per page)
@@ -159,16 +157,21 @@ class Engine:
         if per_page == 0:
             return 1
         free, total = torch.cuda.mem_get_info(self.device)
-        budget = int(total * fraction) - (total - free)
+        # what is still to come besides the cache: the sampler's scratch rows and a captured step's logits (a row of
+        # vocabulary floats per request each), the products' workspace, and the activations of the largest step
+        rows = -(-int(max_num_seqs) // 8) * 8
+        reserve = 3 * rows * self.vocab_size * 4 + (4 << 30)
+        budget = int(total * fraction) - (total - free) - reserve
         n = budget // per_page
         if n < 1:
             raise EngineError("no memory left for the cache after the weights")
         return int(n)
 
     # ---- the step ----------------------------------------------------------------------
-    def step(self, entries: Sequence[StepEntry]) -> Optional[torch.Tensor]:
+    def step(self, entries: Sequence[StepEntry], logits: bool = True) -> Optional[torch.Tensor]:
         """Runs the entries' tokens as one batch and returns the logits at the wanted places (None if
-        none is wanted).  If anything fails after the cache manager was changed (a kernel wrapper that
+        none is wanted; with logits=False a caller whose epilogue has used them says that it does not
+        need them, which saves a decode step the copy out of its graph's buffer).  If anything fails after the cache manager was changed (a kernel wrapper that
         refuses its arguments, a launch error), the admissions and reservations of this step are undone
         before the error goes on: every request is as it was before the call.  A kernel whose bounded
         wait gave up in an earlier step makes this call raise before it launches anything
@@ -177,11 +180,13 @@ class Engine:
         entries = [e for e in entries if len(e.tokens) > 0]
         try:
             if self.cuda_graphs and entries and len(entries) <= MAX_GRAPH_BATCH and all(len(e.tokens) == 1 for e in entries):
-                return self._step_graph(entries)
+                return self._step_graph(entries, logits)
             ctx, want_rows, lens_after = self._prepare(entries)
             if ctx is None:
                 return None
-            logits = self.model.forward(ctx, want_rows)
+            out = self.model.forward(ctx, want_rows)
+            if out is not None and self._epilogue is not None:
+                self._epilogue(out, ctx.want_slot, out.shape[0])
         except BaseException:
             self._rollback()
             raise
@@ -189,7 +194,7 @@ class Engine:
         for rid, n in lens_after:
             self.cache.commit(rid, n)
         self.steps_run += 1
-        return logits
+        return out
 
     def _rollback(self) -> None:
         undo, self._undo = self._undo, None
@@ -221,17 +226,20 @@ class Engine:
             width *= 2
         return bucket, width
 
-    def _step_graph(self, entries: Sequence[StepEntry]) -> Optional[torch.Tensor]:
+    def _step_graph(self, entries: Sequence[StepEntry], logits: bool = True) -> Optional[torch.Tensor]:
         """A step of single tokens only: fill the graph's static tables and replay it."""
         key = self._graph_key(entries)
         host, lens_after = self._prepare(entries, fixed=key)
-        return self._replay(key, host, lens_after, [k for k, e in enumerate(entries) if len(e.want) > 0], len(entries))
+        rows = [k for k, e in enumerate(entries) if len(e.want) > 0] if logits else []
+        return self._replay(key, host, lens_after, rows, len(entries))
 
     def _replay(self, key, host, lens_after, rows, B) -> Optional[torch.Tensor]:
-        g = self._graphs.get(key)
+        g = self._graphs.pop(key, None)
         if g is None:
+            while len(self._graphs) >= MAX_GRAPHS:      # the one replayed longest ago goes (its memory returns to the pool)
+                self._graphs.pop(next(iter(self._graphs)))
             g = _DecodeGraph(self, key[0], key[1])
-            self._graphs[key] = g
+        self._graphs[key] = g                           # most recently used last
         self._staging.upload(host, self.device, into=g.meta)
         g.graph.replay()
         self.graph_replays += 1
@@ -263,15 +271,20 @@ class Engine:
         self._undo = None                               # the pages stay with their requests whatever comes of the handle
         return (key, tuple(request_ids), host, lens_after)
 
-    def step_ahead(self, ahead, tokens: Sequence[int]) -> torch.Tensor:
-        """Run the step prepared by `prepare_ahead` with the token ids that have arrived since."""
+    def step_ahead(self, ahead, tokens: Optional[Sequence[int]] = None, logits: bool = True) -> Optional[torch.Tensor]:
+        """Run the step prepared by `prepare_ahead`: with the token ids that have arrived since, or
+        (tokens=None) with every request's token taken from its slot on the device, where the sampler of
+        the step before has left it - then the host need not have seen that step's result at all."""
         key, rids, host, lens_after = ahead
-        for t in tokens:
-            if not 0 <= int(t) < self.vocab_size:
-                raise EmbeddingOov(f"token id {t} outside the vocabulary of {self.vocab_size}")
-        host[:len(rids)] = tokens                       # the block starts with the token ids (Engine._layout)
+        if tokens is None:
+            host[:len(rids)] = FROM_SLOT                # the block starts with the token ids (Engine._layout)
+        else:
+            for t in tokens:
+                if not 0 <= int(t) < self.vocab_size:
+                    raise EmbeddingOov(f"token id {t} outside the vocabulary of {self.vocab_size}")
+            host[:len(rids)] = tokens
         self.check_status()
-        return self._replay(key, host, lens_after, list(range(len(rids))), len(rids))
+        return self._replay(key, host, lens_after, list(range(len(rids))) if logits else [], len(rids))
 
     def finish(self, request_id) -> None:
         """The request is over: its pages and its slot are given back."""
@@ -292,6 +305,8 @@ class Engine:
             seen.add(e.request_id)
             if len(e.tokens) == 1:
                 lo_t = hi_t = int(e.tokens[0])
+                if lo_t == FROM_SLOT and e.request_id in self.cache and self.cache.length(e.request_id) > 0:
+                    lo_t = hi_t = 0                     # taken from the request's slot by the embedding
             else:
                 arr = np.asarray(e.tokens)
                 lo_t, hi_t = int(arr.min()), int(arr.max())
@@ -317,6 +332,8 @@ class Engine:
         for e in new:
             slot = cm.admit(e.request_id)
             self.storage.zero_slot(slot)
+            if self.on_admit is not None:
+                self.on_admit(e.request_id, slot)
         # decode entries first, each kind in the order given
         order = sorted(range(len(entries)), key=lambda i: (len(entries[i].tokens) != 1, i))
         internal = [entries[i] for i in order]
@@ -365,6 +382,14 @@ class Engine:
         sec("entry_slot")[:E_real] = slots
         if R:
             sec("want_rows")[:] = want_rows
+            ws = sec("want_slot")
+            ws[:] = self.storage.inert_slot
+            if fixed is None:
+                ws[:] = [slots[pos_in_internal[id(e)]] for e in entries for _ in e.want]
+            else:                                       # row k is entry k; an entry that wants nothing draws for nobody
+                for k, e in enumerate(internal):
+                    if len(e.want) > 0:
+                        ws[k] = slots[k]
         for g in range(n_groups):
             ks = sec(f"kv_slot{g}")
             ks[:] = -1
@@ -403,7 +428,7 @@ class Engine:
             cur += (n + 3) // 4 * 4
 
         take("token_ids", T); take("positions", T); take("tok_entry", T)
-        take("cu_q", E + 1); take("kv_len", E); take("entry_slot", E); take("want_rows", max(R, 1))
+        take("cu_q", E + 1); take("kv_len", E); take("entry_slot", E); take("want_rows", max(R, 1)); take("want_slot", max(R, 1))
         for g in range(len(max_pages)):
             take(f"kv_slot{g}", T); take(f"block_table{g}", E * max_pages[g])
         return off, cur
@@ -434,11 +459,13 @@ class Engine:
         return StepContext(dtype=self.dtype, device=self.device, n_tokens=T, n_entries=E, n_decode=n_decode,
                            token_ids=dsec("token_ids"), positions=dsec("positions"), tok_entry=dsec("tok_entry"),
                            cu_q=dsec("cu_q"), kv_len=dsec("kv_len"), entry_slot=dsec("entry_slot"),
+                           want_slot=dsec("want_slot"), slot_token=self.storage.slot_token,
                            q_start=q_start, start_pos=start, slots=slots, max_q_len=max_q_len, max_kv_len=max_kv_len,
                            layer_caches=layer_caches)
 
 
 MAX_GRAPH_BATCH = 256
+MAX_GRAPHS = 24             # captured decode steps kept at a time (one per batch bucket and block-table width in use)
 
 
 class _DecodeGraph:
@@ -458,17 +485,24 @@ class _DecodeGraph:
         o, n = off["want_rows"]; host[o:o + n] = np.arange(batch)
         inert = engine.storage.inert_slot
         o, n = off["entry_slot"]; host[o:o + n] = inert
+        o, n = off["want_slot"]; host[o:o + n] = inert
         self.meta = torch.from_numpy(host).to(engine.device)
         ctx = engine._context(self.meta, off, batch, batch, batch, [width] * n_groups, list(range(batch + 1)),
                               [0] * batch, [inert] * batch, 1, width * engine.page_size)
         o, n = off["want_rows"]
         want = self.meta[o:o + n]
+        def run():
+            logits = engine.model.forward(ctx, want)
+            if engine._epilogue is not None:
+                engine._epilogue(logits, ctx.want_slot, batch)
+            return logits
+
         l0 = ops.launches
-        engine.model.forward(ctx, want)                  # eager once: lazy set-up must not fall into the capture
+        run()                                            # eager once: lazy set-up must not fall into the capture
         self.n_launches = ops.launches - l0              # kernels of this library in one replay
         torch.cuda.synchronize()
         if engine._graph_pool is None:
             engine._graph_pool = torch.cuda.graph_pool_handle()
         self.graph = torch.cuda.CUDAGraph()
         with torch.cuda.graph(self.graph, pool=engine._graph_pool):
-            self.logits = engine.model.forward(ctx, want)
+            self.logits = run()

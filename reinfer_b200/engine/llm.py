@@ -18,7 +18,7 @@ from ..sampling.params import SamplingParams
 from ..sampling.sampler import Sampler, request_seed
 from .admission import AdmissionLimits, EstimateAdmission
 from .engine import Engine, EngineError, StepEntry
-from .scheduler import Request, Scheduler
+from .scheduler import RUNNING, Request, Scheduler
 
 
 @dataclass
@@ -28,14 +28,6 @@ class RequestOutput:
     token_ids: List[int]
     finish_reason: Optional[str]
     preemptions: int = 0
-
-
-def penalty_window(request: Request, last_n: int) -> List[int]:
-    """The tokens that the repeat, frequency and presence penalties look at: the last `last_n` tokens the
-    request has SAMPLED, never its prompt (crates/cuda/src/sampler.rs:109-111 and :369: the history is
-    fed by `history.push(token)` after each draw).  A preempted request keeps its output, so the window
-    is the same after it resumes."""
-    return request.output[-last_n:] if last_n > 0 else []
 
 
 class LLM:
@@ -66,13 +58,15 @@ class LLM:
         self.scheduler = Scheduler(engine.cache, max_batch_tokens=batch_tokens,
                                    max_chunk=max_chunk, eos_token_ids=self.eos, max_model_len=self.max_model_len,
                                    release=engine.finish, admission=estimate)
-        self.sampler = Sampler(engine.vocab_size, engine.cache.max_seqs, engine.device)
+        self.sampler = Sampler(engine.vocab_size, -(-engine.cache.max_seqs // 8) * 8, engine.device, storage=engine.storage)
+        engine.on_admit = self._admitted            # a request's slot gets its sampler record
+        engine.epilogue = self.sampler.launch_slots  # the sampler runs right behind the forward pass, on the device's tables
         self._next_id = 0
         self.requests: Dict[Hashable, Request] = {}
         self.last_stats: Dict[str, float] = {}
-        self._ahead = None                      # tables of the next step, built while the device was busy
-        self.ahead_used = 0                     # steps that ran on tables prepared one step ahead
-        self.ahead_discarded = 0                # prepared tables that the next decision did not match
+        self._launched = None                   # a step launched ahead of its scheduling: (batch, tokens on their way)
+        self.steps_launched_ahead = 0           # steps that were launched before the step before them was read
+        self.ahead_rows_dropped = 0             # rows of such steps that belonged to requests which had ended
 
     # ---- requests -----------------------------------------------------------------------
     def add_request(self, prompt_token_ids: Sequence[int], params: Optional[SamplingParams] = None,
@@ -93,53 +87,85 @@ class LLM:
         self.scheduler.abort(request_id)
 
     def has_work(self) -> bool:
-        return self.scheduler.has_work()
+        return self.scheduler.has_work() or self._launched is not None
 
+    def _admitted(self, request_id, slot: int) -> None:
+        r = self.requests.get(request_id)
+        if r is not None:
+            self.sampler.assign(slot, r.params, r.seed, r.output)
+
+    # ---- one step -------------------------------------------------------------------------
     def step(self) -> List[Request]:
-        """One scheduler decision, one engine step, one sampler launch.  Returns the requests
-        that finished in it.
+        """One scheduler decision, one engine step with the sampler behind it, and the reading of its tokens.
+        Returns the requests that finished in it.
 
-        While the device runs the step, the host already builds the next step's tables under the guess
-        that the same requests simply go on decoding (`Engine.prepare_ahead`); if the next decision is
-        exactly that, only the sampled token ids are filled in before the replay."""
-        out = self.scheduler.schedule()
-        finished = list(out.finished)
-        if not out.batch:
-            return finished
-        ahead, self._ahead = self._ahead, None
-        rids = tuple(s.request.request_id for s in out.batch)
-        sampling = [s.request for s in out.batch if s.sample]
-        sampled: Dict[Hashable, int] = {}
+        The device never waits for the host between two decode steps: as soon as a step is launched and it is
+        sure that the same requests decode again after it (nobody waits, nobody reaches its token limit), the
+        step after it is launched too - its token ids are not known on the host yet, the embedding takes them
+        from the requests' slots on the device, where the sampler has put them.  Only then are the first
+        step's tokens read.  A request that turns out to end there (a stop token, end of sequence) has one row
+        in the step already running; that row is dropped, its request's pages are given back as always."""
+        finished: List[Request] = []
+        cur, self._launched = self._launched, None
+        if cur is None:
+            out = self.scheduler.schedule()
+            finished += out.finished
+            if not out.batch:
+                return finished
+            cur = (out.batch, None, None)
+        batch, tokens, rows = cur
+        ahead = None
         try:
-            if ahead is not None and ahead[1] == rids and all(len(s.tokens) == 1 and s.sample for s in out.batch):
-                self.ahead_used += 1
-                logits = self.engine.step_ahead(ahead, [s.tokens[0] for s in out.batch])
-            else:
-                if ahead is not None:
-                    self.ahead_discarded += 1           # (its pages stay with their requests)
-                entries = [StepEntry(s.request.request_id, s.tokens, [len(s.tokens) - 1] if s.sample else [])
-                           for s in out.batch]
-                logits = self.engine.step(entries)
+            if tokens is None:
+                tokens = self._launch(batch)
+            sampling = [s.request for s in batch if s.sample]
+            if rows is None:
+                rows = list(range(len(sampling)))
+            ahead = self._launch_ahead(batch)
+            sampled: Dict[Hashable, int] = {}
             if sampling:
-                n = self.sampler.launch(logits, [r.params for r in sampling], [r.seed for r in sampling],
-                                        [len(r.output) for r in sampling],
-                                        [(lambda k, r=r: penalty_window(r, k)) for r in sampling])
-                # the device is busy: prepare the next step if it is likely to be these requests again
-                if len(sampling) == len(out.batch) and not self.scheduler.waiting and \
-                        all(len(r.output) + 1 < r.params.max_tokens for r in sampling):
-                    self._ahead = self.engine.prepare_ahead(rids)
-                toks = self.sampler.fetch(n)
-                sampled = {r.request_id: t for r, t in zip(sampling, toks)}
-                self.engine.check_status()              # the tokens have arrived: the step's kernels are over
+                got = tokens.result()
+                sampled = {r.request_id: got[k] for r, k in zip(sampling, rows)}
+            self.engine.check_status()                  # the tokens have arrived: the step's kernels are over
         except EngineError:
             # a kernel gave up (or the engine refused the step): the requests of this step end with "error" and
             # give back their pages; the engine refuses further steps until `engine.clear_status()`
-            self._ahead = None
-            for s in out.batch:
+            for s in batch:
                 self.scheduler.fail(s.request)
             raise
-        finished += self.scheduler.update(out.batch, sampled)
+        finished += self.scheduler.update(batch, sampled)
+        if ahead is not None:
+            ahead_requests, ahead_tokens = ahead
+            alive = [(k, r) for k, r in enumerate(ahead_requests) if r.state == RUNNING]
+            self.ahead_rows_dropped += len(ahead_requests) - len(alive)
+            if alive:
+                self._launched = (self.scheduler.schedule_decode([r for _, r in alive]), ahead_tokens, [k for k, _ in alive])
         return finished
+
+    def _launch(self, batch):
+        """Run the batch through the engine (the sampler is its epilogue) and start the tokens' way to the host."""
+        entries = [StepEntry(s.request.request_id, s.tokens, [len(s.tokens) - 1] if s.sample else []) for s in batch]
+        self.engine.step(entries, logits=False)
+        n = sum(1 for s in batch if s.sample)
+        return self.sampler.download(n) if n else None
+
+    def _launch_ahead(self, batch):
+        """If the step after `batch` (which is launched, not read) is sure to be "the same requests, one token
+        each", launch it now.  Returns (its requests, its tokens on their way) or None."""
+        if not self.engine.cuda_graphs or self.scheduler.waiting or len(batch) != len(self.scheduler.running):
+            return None
+        limit = self.max_model_len
+        for s in batch:
+            r = s.request
+            if not s.sample or r.state != RUNNING or len(r.output) + 1 >= r.params.max_tokens or \
+                    (limit and r.total_len + 2 >= limit):
+                return None
+        handle = self.engine.prepare_ahead([s.request.request_id for s in batch])
+        if handle is None:
+            return None
+        self.engine.step_ahead(handle, None, logits=False)
+        self.steps_launched_ahead += 1
+        return [s.request for s in batch], self.sampler.download(len(batch))
 
     def generate(self, prompt_token_ids: Union[Sequence[int], Sequence[Sequence[int]]],
                  sampling_params: Union[None, SamplingParams, Sequence[SamplingParams]] = None) -> List[RequestOutput]:

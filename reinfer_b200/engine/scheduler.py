@@ -275,6 +275,20 @@ class Scheduler:
         self.stats["scheduled_tokens"] += sum(len(s.tokens) for s in batch)
         return SchedulerOutput(batch, preempted, finished)
 
+    def schedule_decode(self, requests: Sequence[Request]) -> List[Scheduled]:
+        """The batch of a step that is already running: these running requests, each with the one token drawn
+        for it last.  (The entry point launches such a step before it has read the step before, when that one
+        was sure to be followed by "everybody decodes again"; requests that turned out to end there are simply
+        not named here, and their rows of the running step are dropped.)"""
+        batch = []
+        for r in requests:
+            if r.state != RUNNING or r.in_prefill:
+                raise ValueError(f"request {r.request_id!r} is not decoding")
+            batch.append(Scheduled(r, r.num_computed, r.tokens_from(r.num_computed, 1), True))
+        self.stats["steps"] += 1
+        self.stats["scheduled_tokens"] += len(batch)
+        return batch
+
     def _preempt(self, r: Request) -> None:
         self.running.remove(r)
         self._release(r.request_id)

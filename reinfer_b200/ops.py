@@ -70,9 +70,61 @@ def require_device() -> None:
 launches = 0          # kernels of this library launched so far (every wrapper passes through _check)
 
 
-def _check(rc: int, what: str) -> None:
+class SegmentProfiler:
+    """CUDA-event times of the launches of a step, by named segment (the idea of the reference's DecodeProfiler
+    and PrefillProfiler: cudaEvent pairs around named segments, crates/cuda/src/engine.rs:928-1408, 6675-6975).
+    While a profiler is installed (`set_profiler`) every wrapper records an event behind its launch; a launch's
+    time is the span from the event before it to its own, so the launches are seen one after the other, without
+    the overlap that programmatic dependent launch gives them in a plain run: compare shares, as with a profiler.
+    Each wrapper also says what the launch has to compute and to move, which gives achieved FLOP/s and bytes/s."""
+
+    def __init__(self) -> None:
+        self.marks = []                                     # (name, flops, bytes, event)
+        self.start = None
+
+    def begin(self) -> None:
+        self.marks = []
+        self.start = torch.cuda.Event(enable_timing=True)
+        self.start.record()
+
+    def mark(self, name: str, flops: float, nbytes: float) -> None:
+        if self.start is None:
+            return
+        ev = torch.cuda.Event(enable_timing=True)
+        ev.record()
+        self.marks.append((name, flops, nbytes, ev))
+
+    def summary(self):
+        """name -> {"n", "us", "tflops", "gbs"} (synchronises); insertion order = order of first launch."""
+        torch.cuda.synchronize()
+        out, prev = {}, self.start
+        for name, flops, nbytes, ev in self.marks:
+            us = prev.elapsed_time(ev) * 1e3
+            prev = ev
+            d = out.setdefault(name, {"n": 0, "us": 0.0, "flops": 0.0, "bytes": 0.0})
+            d["n"] += 1; d["us"] += us; d["flops"] += flops; d["bytes"] += nbytes
+        for d in out.values():
+            t = max(d["us"], 1e-9) * 1e-6
+            d["tflops"] = d.pop("flops") / t / 1e12
+            d["gbs"] = d.pop("bytes") / t / 1e9
+        return out
+
+
+_profiler: Optional["SegmentProfiler"] = None
+
+
+def set_profiler(p: Optional["SegmentProfiler"]) -> Optional["SegmentProfiler"]:
+    """Install (or, with None, remove) the profiler that the wrappers report to; returns the previous one."""
+    global _profiler
+    old, _profiler = _profiler, p
+    return old
+
+
+def _check(rc: int, what: str, flops: float = 0.0, nbytes: float = 0.0) -> None:
     global launches
     launches += 1
+    if _profiler is not None and rc == 0:
+        _profiler.mark(what, flops, nbytes)
     if rc == 0:
         return
     if rc < 0:
@@ -101,12 +153,14 @@ def _need(cond: bool, msg: str) -> None:
 
 
 # ------------------------------------------------------------------ wrappers
-def embed_gather(table: torch.Tensor, ids: torch.Tensor, out: torch.Tensor) -> None:
-    """out[t,:] (float32) = table[ids[t],:]"""
+def embed_gather(table: torch.Tensor, ids: torch.Tensor, out: torch.Tensor, slot_token: Optional[torch.Tensor] = None,
+                 entry_slot: Optional[torch.Tensor] = None, tok_entry: Optional[torch.Tensor] = None) -> None:
+    """out[t,:] (float32) = table[ids[t],:]; where ids[t] < 0 and the slot tables are given, the id is
+    slot_token[entry_slot[tok_entry[t]]]: the token that the sampler left in the request's slot."""
     _need(out.dtype == torch.float32 and ids.dtype == torch.int32, "embed_gather: out float32, ids int32")
     _need(table.is_contiguous() and out.is_contiguous(), "embed_gather: contiguous tensors")
-    _check(lib().rb_embed_gather(_p(table), dt(table), _p(ids), _p(out), c_int(ids.numel()),
-                                 c_int(table.shape[1]), c_int(table.shape[0]), _stream()), "embed_gather")
+    _check(lib().rb_embed_gather(_p(table), dt(table), _p(ids), _p(slot_token), _p(entry_slot), _p(tok_entry), _p(out),
+                                 c_int(ids.numel()), c_int(table.shape[1]), c_int(table.shape[0]), _stream()), "embed_gather")
 
 
 def add_rmsnorm(x: torch.Tensor, delta: Optional[torch.Tensor], w: torch.Tensor, out: torch.Tensor,
@@ -207,19 +261,20 @@ def gemm_ref(a: torch.Tensor, w: torch.Tensor, c: torch.Tensor, accumulate: bool
     _need(a.stride(1) == 1 and w.stride(1) == 1 and c.stride(1) == 1, "gemm: rows contiguous")
     _check(lib().rb_gemm_ref(_p(a), c_int(dt(a)), _p(w), c_int(dt(w)), _p(c), c_int(dt(c)), c_int(int(accumulate)),
                              c_int(M), c_int(N), c_int(K), c_longlong(a.stride(0)), c_longlong(w.stride(0)),
-                             c_longlong(c.stride(0)), _stream()), "gemm_ref")
+                             c_longlong(c.stride(0)), _stream()), f"gemm_fma {N}x{K}", 2.0 * M * N * K,
+           float(M * K * a.element_size() + N * K * w.element_size() + M * N * c.element_size()))
 
 
 def paged_attention_ref(q: torch.Tensor, cache: torch.Tensor, block_table: torch.Tensor, tok_row: torch.Tensor,
                         positions: torch.Tensor, out: torch.Tensor, QH: int, KH: int, d: int, page_size: int,
-                        window: int, scale: float) -> None:
+                        window: int, scale: float, work=(0.0, 0.0)) -> None:
     _need(q.is_contiguous() and out.is_contiguous() and cache.is_contiguous() and block_table.is_contiguous(),
           "attention: contiguous")
     _need(q.dtype == cache.dtype == out.dtype, "attention: one dtype for q, cache and out")
     _check(lib().rb_paged_attention_ref(_p(q), _p(cache), c_int(dt(q)), _p(block_table), _p(tok_row), _p(positions),
                                         _p(out), c_int(q.shape[0]), c_int(QH), c_int(KH), c_int(d), c_int(page_size),
                                         c_int(block_table.shape[1]), c_int(window), c_float(scale), _stream()),
-           "paged_attention_ref")
+           "paged_attention_ref", *work)
 
 
 def fa_group_chunk(group: int) -> int:
@@ -231,7 +286,7 @@ def fa_group_chunk(group: int) -> int:
 
 
 def fa_decode(q, cache, block_table, cu_q, kv_len, out, first_entry: int, n_entries: int, first_tok: int, n_splits: int,
-              QH: int, KH: int, d: int, page_size: int, window: int, scale: float) -> None:
+              QH: int, KH: int, d: int, page_size: int, window: int, scale: float, work=(0.0, 0.0)) -> None:
     """Split-K flash decoding (tensor cores) for entries that bring one token each."""
     part_o = part_lse = None
     if n_splits > 1:
@@ -240,7 +295,7 @@ def fa_decode(q, cache, block_table, cu_q, kv_len, out, first_entry: int, n_entr
     _check(lib().rb_fa_decode(_p(q), _p(cache), _p(block_table), _p(cu_q), _p(kv_len), _p(out), _p(part_o), _p(part_lse),
                               c_int(first_entry), c_int(n_entries), c_int(first_tok), c_int(n_splits), c_int(QH), c_int(KH),
                               c_int(d), c_int(page_size), c_int(block_table.shape[1]), c_int(window), c_float(scale),
-                              _stream()), "fa_decode")
+                              _stream()), "fa_decode", *work)
     if n_splits > 1:
         global launches
         launches += 1                      # the merge kernel
@@ -323,7 +378,7 @@ DECODE_SLOTS = 296                          # CTAs of the decode attention that 
 
 
 def fa_decode_tma(q, cache, block_table, cu_q, kv_len, out, first_entry: int, n_entries: int, first_tok: int, n_splits: int,
-                  QH: int, KH: int, d: int, page_size: int, window: int, scale: float) -> None:
+                  QH: int, KH: int, d: int, page_size: int, window: int, scale: float, work=(0.0, 0.0)) -> None:
     """Split-K flash decoding with the key/value tiles brought in by TMA (page size a power of two >= 8).
     Up to 8 splits whose CTAs are all resident at once form clusters that merge their results themselves (no scratch,
     no merge kernel); several waves of CTAs, or more splits, go through scratch and the merge kernel (clusters
@@ -338,20 +393,20 @@ def fa_decode_tma(q, cache, block_table, cu_q, kv_len, out, first_entry: int, n_
     _check(lib().rb_fa_decode_tma(_p(q), _p(cache), c_longlong(cache.shape[0]), _p(block_table), _p(cu_q), _p(kv_len), _p(out),
                                   _p(part_o), _p(part_lse), c_int(first_entry), c_int(n_entries), c_int(first_tok),
                                   c_int(n_splits), c_int(QH), c_int(KH), c_int(d), c_int(page_size),
-                                  c_int(block_table.shape[1]), c_int(window), c_float(scale), nw, nb, _stream()), "fa_decode_tma")
+                                  c_int(block_table.shape[1]), c_int(window), c_float(scale), nw, nb, _stream()), "fa_decode_tma", *work)
 
 
 def fa_prefill_tma(q, cache, block_table, cu_q, kv_len, out, first_entry: int, n_entries: int, n_tiles: int,
-                   QH: int, KH: int, d: int, page_size: int, window: int, scale: float) -> None:
+                   QH: int, KH: int, d: int, page_size: int, window: int, scale: float, work=(0.0, 0.0)) -> None:
     """Paged causal flash attention with the key/value tiles brought in by TMA."""
     _check(lib().rb_fa_prefill_tma(_p(q), _p(cache), c_longlong(cache.shape[0]), _p(block_table), _p(cu_q), _p(kv_len), _p(out),
                                    c_int(first_entry), c_int(n_entries), c_int(n_tiles), c_int(QH), c_int(KH), c_int(d),
                                    c_int(page_size), c_int(block_table.shape[1]), c_int(window), c_float(scale), _stream()),
-           "fa_prefill_tma")
+           "fa_prefill_tma", *work)
 
 
 def fa_prefill_tc(q, cache, block_table, cu_q, kv_len, out, first_entry: int, n_entries: int, q_lens,
-                  QH: int, KH: int, d: int, page_size: int, window: int, scale: float) -> None:
+                  QH: int, KH: int, d: int, page_size: int, window: int, scale: float, work=(0.0, 0.0)) -> None:
     """Paged causal flash attention on the tcgen05 tensor cores (scores and the weighted sum in tensor memory):
     head size 128, page size a power of two >= 8.  q_lens: the token counts of the entries (host)."""
     gc = int(lib().rb_fa_prefill_tc_group(c_int(QH), c_int(KH)))
@@ -360,7 +415,7 @@ def fa_prefill_tc(q, cache, block_table, cu_q, kv_len, out, first_entry: int, n_
     _check(lib().rb_fa_prefill_tc(_p(q), _p(cache), c_longlong(cache.shape[0]), _p(block_table), _p(cu_q), _p(kv_len), _p(out),
                                   c_int(first_entry), c_int(n_entries), c_int(n_tiles), c_int(QH), c_int(KH), c_int(d),
                                   c_int(page_size), c_int(block_table.shape[1]), c_int(window), c_float(scale), _stream()),
-           "fa_prefill_tc")
+           "fa_prefill_tc", *work)
 
 
 def tma_pages(page_size: int) -> bool:
@@ -368,11 +423,11 @@ def tma_pages(page_size: int) -> bool:
 
 
 def fa_prefill(q, cache, block_table, cu_q, kv_len, out, first_entry: int, n_entries: int, n_tiles: int,
-               QH: int, KH: int, d: int, page_size: int, window: int, scale: float) -> None:
+               QH: int, KH: int, d: int, page_size: int, window: int, scale: float, work=(0.0, 0.0)) -> None:
     """Paged causal flash attention (tensor cores) for entries that bring several tokens."""
     _check(lib().rb_fa_prefill(_p(q), _p(cache), _p(block_table), _p(cu_q), _p(kv_len), _p(out), c_int(first_entry),
                                c_int(n_entries), c_int(n_tiles), c_int(QH), c_int(KH), c_int(d), c_int(page_size),
-                               c_int(block_table.shape[1]), c_int(window), c_float(scale), _stream()), "fa_prefill")
+                               c_int(block_table.shape[1]), c_int(window), c_float(scale), _stream()), "fa_prefill", *work)
 
 
 USE_TMA_ATTENTION = os.environ.get("REINFER_B200_TMA_ATTENTION", "1") != "0"
@@ -416,13 +471,28 @@ def attention(ctx, q: torch.Tensor, cache: torch.Tensor, group, out: torch.Tenso
     """Attention of a step's tokens over their requests' pages.  float32 (and head sizes the
     tensor-core kernels do not take) runs the plain kernel; bfloat16 runs flash decoding for the
     entries with one token and the paged flash prefill kernel for the others."""
+    n_dec, E = ctx.n_decode, ctx.n_entries
+    dec_work = pre_work = (0.0, 0.0)
+    if _profiler is not None:
+        def work(first, last):
+            """(flops, bytes) that attention over entries first..last-1 has to do: two products of 2*d per (query head,
+            key) pair the causal mask lets through, and every key and value of the request read once."""
+            fl = by = 0.0
+            for e in range(first, last):
+                n, s0 = ctx.q_start[e + 1] - ctx.q_start[e], ctx.start_pos[e]
+                pairs = n * s0 + n * (n + 1) / 2
+                if window:
+                    pairs = min(pairs, n * window)
+                fl += 4.0 * QH * d * pairs
+                by += ((min(s0 + n, window + n) if window else s0 + n) * KH * 2 + 2 * n * QH) * d * q.element_size()
+            return fl, by
+        dec_work, pre_work = work(0, n_dec), work(n_dec, E)
     if q.dtype != torch.bfloat16 or d % 8 or d > 256:
         paged_attention_ref(q, cache, group.block_table, ctx.tok_entry, ctx.positions, out, QH, KH, d,
-                            group.page_size, window, scale)
+                            group.page_size, window, scale, work=(dec_work[0] + pre_work[0], dec_work[1] + pre_work[1]))
         return
     _need(q.is_contiguous() and out.is_contiguous() and cache.is_contiguous() and group.block_table.is_contiguous(),
           "attention: contiguous")
-    n_dec, E = ctx.n_decode, ctx.n_entries
     gc = fa_group_chunk(QH // KH)
     if n_dec:
         ctas = n_dec * KH * (QH // KH // gc)
@@ -430,16 +500,17 @@ def attention(ctx, q: torch.Tensor, cache: torch.Tensor, group, out: torch.Tenso
         n_splits = decode_splits(ctas, tiles, head_dim=d)
         decode = fa_decode_tma if (tma_pages(group.page_size) and USE_TMA_ATTENTION) else fa_decode
         decode(q, cache, group.block_table, ctx.cu_q, ctx.kv_len, out, 0, n_dec, 0, n_splits, QH, KH, d,
-               group.page_size, window, scale)
+               group.page_size, window, scale, work=dec_work)
     if E > n_dec and d == 128 and USE_TC_ATTENTION and USE_TMA_ATTENTION and tma_pages(group.page_size):
         fa_prefill_tc(q, cache, group.block_table, ctx.cu_q, ctx.kv_len, out, n_dec, E - n_dec,
-                      [ctx.q_start[e + 1] - ctx.q_start[e] for e in range(n_dec, E)], QH, KH, d, group.page_size, window, scale)
+                      [ctx.q_start[e + 1] - ctx.q_start[e] for e in range(n_dec, E)], QH, KH, d, group.page_size, window, scale,
+                      work=pre_work)
     elif E > n_dec:
         tpt = 64 // gc
         n_tiles = sum(-(-(ctx.q_start[e + 1] - ctx.q_start[e]) // tpt) for e in range(n_dec, E))
         prefill = fa_prefill_tma if (tma_pages(group.page_size) and USE_TMA_ATTENTION) else fa_prefill
         prefill(q, cache, group.block_table, ctx.cu_q, ctx.kv_len, out, n_dec, E - n_dec, n_tiles, QH, KH, d,
-                group.page_size, window, scale)
+                group.page_size, window, scale, work=pre_work)
 
 
 def sample(logits: torch.Tensor, row_idx: Optional[torch.Tensor], params: torch.Tensor, history: Optional[torch.Tensor],
@@ -451,6 +522,21 @@ def sample(logits: torch.Tensor, row_idx: Optional[torch.Tensor], params: torch.
     _need(work.numel() >= rows * vocab and work.dtype == torch.float32, "sample: scratch of rows*vocab floats")
     _check(lib().rb_sample(_p(logits), c_longlong(logits.stride(0)), _p(row_idx), _p(params), _p(history),
                            c_int(hist_cap), _p(work), _p(out_tokens), c_int(rows), c_int(vocab), _stream()), "sample")
+
+
+def sample_slots(logits: torch.Tensor, row_slot: torch.Tensor, slot_params: torch.Tensor, slot_history: torch.Tensor,
+                 slot_token: torch.Tensor, work: torch.Tensor, out_tokens: torch.Tensor, rows: int) -> None:
+    """One token per row of `logits`, every request's parameters, seed, draw count and recent tokens taken from
+    (and the token written to) its slot: row r belongs to slot row_slot[r] (csrc/sampler.cu)."""
+    _need(logits.dtype == torch.float32 and logits.stride(1) == 1, "sample_slots: float32 logits")
+    vocab = logits.shape[1]
+    _need(work.numel() >= rows * vocab and work.dtype == torch.float32, "sample_slots: scratch of rows*vocab floats")
+    _need(row_slot.dtype == torch.int32 and slot_token.dtype == torch.int32 and slot_history.dtype == torch.int32 and
+          slot_params.dtype == torch.uint8 and slot_params.is_contiguous() and slot_history.is_contiguous(),
+          "sample_slots: int32 tables, records as bytes")
+    _check(lib().rb_sample_slots(_p(logits), c_longlong(logits.stride(0)), _p(row_slot), _p(slot_params), _p(slot_history),
+                                 c_int(slot_history.shape[1]), _p(slot_token), _p(work), _p(out_tokens), c_int(rows),
+                                 c_int(vocab), _stream()), "sample_slots")
 
 
 _gemm_ws = None
@@ -477,7 +563,8 @@ def gemm_bf16(a: torch.Tensor, w: torch.Tensor, c: torch.Tensor, accumulate: boo
     _check(lib().rb_gemm_bf16(_p(a), _p(w), _p(c), c_int(dt(c)), c_int(int(accumulate)), c_int(T), c_int(N), c_int(K),
                               c_longlong(a.stride(0)), c_longlong(w.stride(0)), c_longlong(c.stride(0)),
                               _p(_gemm_ws), c_longlong(_gemm_ws.numel()), c_int(splits), nw, nb,
-                              *_row_scale_args(row_scale, T), _stream()), "gemm_bf16")
+                              *_row_scale_args(row_scale, T), _stream()), f"gemm {N}x{K}",
+           2.0 * T * N * K, 2.0 * (T * K + N * K) + T * N * c.element_size())
 
 
 def gemm_bf16_partials(a: torch.Tensor, w: torch.Tensor, row_scale=None) -> Optional[torch.Tensor]:
@@ -497,7 +584,8 @@ def gemm_bf16_partials(a: torch.Tensor, w: torch.Tensor, row_scale=None) -> Opti
     nw, nb = _next_range(w)
     _check(lib().rb_gemm_bf16_partials(_p(a), _p(w), _p(out), c_int(S), c_int(T), c_int(N), c_int(K),
                                        c_longlong(a.stride(0)), c_longlong(w.stride(0)), nw, nb,
-                                       *_row_scale_args(row_scale, T), _stream()), "gemm_bf16_partials")
+                                       *_row_scale_args(row_scale, T), _stream()), f"gemm {N}x{K}",
+           2.0 * T * N * K, 2.0 * (T * K + N * K) + 4.0 * S * T * N)
     return out
 
 
@@ -515,7 +603,8 @@ def gemm_bf16_swiglu(a: torch.Tensor, w_gate_up: torch.Tensor, out: torch.Tensor
     nw, nb = _next_range(w_gate_up) if T <= STREAMING_TOKENS else (c_void_p(0), c_longlong(0))
     _check(lib().rb_gemm_bf16_swiglu(_p(a), _p(w_gate_up), _p(out), c_int(T), c_int(F_), c_int(K),
                                      c_longlong(a.stride(0)), c_longlong(w_gate_up.stride(0)), c_longlong(out.stride(0)),
-                                     c_int(splits), nw, nb, *_row_scale_args(row_scale, T), _stream()), "gemm_bf16_swiglu")
+                                     c_int(splits), nw, nb, *_row_scale_args(row_scale, T), _stream()),
+           f"gemm+swiglu {2 * F_}x{K}", 4.0 * T * F_ * K, 2.0 * (T * K + 2 * F_ * K + T * F_))
     return True
 
 

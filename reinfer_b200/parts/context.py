@@ -44,6 +44,8 @@ class StepContext:
     cu_q: torch.Tensor                 # [E+1] first token of each entry
     kv_len: torch.Tensor               # [E] tokens of the request after this step
     entry_slot: torch.Tensor           # [E] request slot (row of fixed-size states)
+    want_slot: Optional[torch.Tensor] = None   # [R] the slot of the request behind each wanted row
+    slot_token: Optional[torch.Tensor] = None  # [slots] the token last drawn for each slot's request (token id < 0: take this)
     # host mirrors
     q_start: List[int] = field(default_factory=list)      # E+1
     start_pos: List[int] = field(default_factory=list)    # E

@@ -26,7 +26,7 @@ class Embedding(Part):
 
     def forward(self, ctx) -> torch.Tensor:
         x = torch.empty((ctx.n_tokens, self.hidden), dtype=torch.float32, device=ctx.device)
-        ops.embed_gather(self.weight, ctx.token_ids, x)
+        ops.embed_gather(self.weight, ctx.token_ids, x, ctx.slot_token, ctx.entry_slot, ctx.tok_entry)
         return x
 
 

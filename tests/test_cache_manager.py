@@ -136,3 +136,23 @@ def test_random_orders_keep_the_invariants(seed):
     cm.check()
     assert all(g.pool.in_use == 0 and g.pool.allocs == g.pool.frees for g in cm.groups)
     assert cm.free_slots() == 4 and n_ok > 50
+
+
+def test_snapshot_and_restore_undo_admissions_and_reservations():
+    """What a failed step needs: the requests it admitted leave, the ones that were live keep what they held."""
+    from reinfer_b200.cache import CacheManager
+    from reinfer_b200.parts.base import PagedKVSpec
+    cm = CacheManager({"a0": PagedKVSpec(2, 16), "w0": PagedKVSpec(2, 16, window=8)}, {}, 4, 12, 3)
+    cm.admit("x"); cm.reserve("x", 10); cm.commit("x", 10)
+    before = ([list(cm.table("x", g)) for g in range(2)], cm.free_pages(), cm.free_slots(), cm.length("x"))
+    snap = cm.snapshot(["x", "y"])
+    cm.admit("y"); cm.reserve("y", 7); cm.reserve("x", 19)
+    assert cm.free_pages() < before[1]
+    cm.restore(snap)
+    cm.check()
+    assert "y" not in cm
+    assert ([list(cm.table("x", g)) for g in range(2)], cm.free_pages(), cm.free_slots(), cm.length("x")) == before
+    cm.reserve("x", 19); cm.commit("x", 19)                 # and life goes on
+    cm.release("x")
+    cm.check()
+    assert cm.free_pages() == 12 and cm.free_slots() == 3

@@ -287,6 +287,98 @@ def test_a_wait_that_runs_out_reaches_the_engine(model_dirs):
     assert torch.equal(again, first)
 
 
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_requests_leave_a_decoding_batch_at_different_steps(tmp_path, dtype):
+    """Distinct token limits, a stop token, a stop sequence and the end-of-sequence id of config.json, all
+    honoured: the requests leave the batch one after another while the others go on.  Decode steps are replayed
+    from graphs and launched ahead of the reading of the step before; a request that ends by a token the host
+    could not foresee has a row in the step already running, which is dropped.  The outputs are the plain
+    implementation's greedy tokens cut at the same places (bfloat16: checked token by token against the plain
+    logits of its own sequence)."""
+    import json
+    from reinfer_b200 import LLM, SamplingParams
+    store = torch.float32 if dtype == "float32" else torch.bfloat16
+    d = tiny.make_model_dir(str(tmp_path / "m"), "B", store)
+    cfg, w = plain.read_model(d)
+    prompts = list(tiny.sequences("B", lengths=[9, 24, 5, 17, 30, 12], seed=13).values())
+    free_run = [plain.greedy(cfg, w, p, 24) for p in prompts]
+    # the end-of-sequence id: what request 0 draws as its 11th token; request 1 stops on its own 7th token;
+    # request 2 on the sequence of its 13th and 14th
+    eos = free_run[0][10]
+    raw = json.load(open(f"{d}/config.json"))
+    raw["eos_token_id"] = eos
+    json.dump(raw, open(f"{d}/config.json", "w"))
+    params = [SamplingParams(max_tokens=24), SamplingParams(max_tokens=24, stop_token_ids=(free_run[1][6],)),
+              SamplingParams(max_tokens=24, stop_sequences=((free_run[2][12], free_run[2][13]),)),
+              SamplingParams(max_tokens=5), SamplingParams(max_tokens=16, ignore_eos=True), SamplingParams(max_tokens=21)]
+
+    def cut(tokens, p):
+        out = []
+        for t in tokens[:p.max_tokens]:
+            if t in p.stop_token_ids:
+                return out, "stop"
+            if any(len(q) and list(q) == (out + [t])[-len(q):] for q in p.stop_sequences):
+                return out[:len(out) - (max(len(q) for q in p.stop_sequences if list(q) == (out + [t])[-len(q):]) - 1)], "stop"
+            if t == eos and not p.ignore_eos:
+                return out, "eos"
+            out.append(t)
+        return out, "length"
+    llm = LLM(d, dtype=dtype, page_size=8, num_pages=64, max_num_seqs=8, max_batch_tokens=64)
+    assert llm.eos == (eos,)
+    outs = llm.generate(prompts, params)
+    assert llm.engine.graph_replays > 0 and llm.steps_launched_ahead > 0 and llm.ahead_rows_dropped > 0
+    assert llm.engine.cache.free_pages() == 64 and not llm.has_work()
+    llm.engine.cache.check()
+    if dtype == "float32":
+        for o, free, p in zip(outs, free_run, params):
+            want, why = cut(free, p)
+            assert (o.token_ids, o.finish_reason) == (want, why), f"request {o.request_id}"
+        assert len({len(o.token_ids) for o in outs}) >= 4            # they did leave at different steps
+    else:
+        for o, prompt, p in zip(outs, prompts, params):
+            logits = plain.forward(cfg, w, prompt + o.token_ids)
+            for i, tok in enumerate(o.token_ids):
+                row = logits[len(prompt) - 1 + i]
+                assert row[tok] >= row.max() - 3e-2 * row.abs().max()
+            assert len(o.token_ids) <= p.max_tokens and o.finish_reason in ("stop", "eos", "length")
+            assert (o.finish_reason == "length") == (len(o.token_ids) == p.max_tokens)
+
+
+def test_penalties_through_the_slots_follow_the_host_driven_sampler(model_dirs):
+    """Generation with a repetition and a presence penalty, a logit bias and a temperature: the sampler works from
+    the requests' slots on the device (record, ring of drawn tokens, draw count kept by the kernel itself).  The
+    same tokens come out when every step's logits are sampled by the host-driven entry point with the history and
+    step count that the host keeps - and when the pool is so small that requests are preempted and return."""
+    from reinfer_b200 import LLM, SamplingParams
+    from reinfer_b200.engine import Engine, StepEntry
+    from reinfer_b200.sampling import Sampler
+    which = "A"
+    prompts = list(tiny.sequences(which, lengths=[6, 11, 19], seed=17).values())
+    sps = [SamplingParams(temperature=0.0, repeat_penalty=1.4, repeat_last_n=5, max_tokens=30, ignore_eos=True),
+           SamplingParams(temperature=0.9, seed=5, presence_penalty=0.7, frequency_penalty=0.2, max_tokens=30, ignore_eos=True),
+           SamplingParams(temperature=0.7, seed=6, top_k=20, logit_bias=((3, 2.0), (9, -4.0)), repeat_penalty=1.2,
+                          max_tokens=30, ignore_eos=True)]
+    llm = LLM(model_dirs[which], dtype="float32", page_size=16, num_pages=64, max_num_seqs=4, max_batch_tokens=32)
+    got = [o.token_ids for o in llm.generate(prompts, sps)]
+    tight = LLM(model_dirs[which], dtype="float32", page_size=16, num_pages=6, max_num_seqs=4, max_batch_tokens=32)
+    outs = tight.generate(prompts, sps)
+    assert sum(o.preemptions for o in outs) > 0
+    assert [o.token_ids for o in outs] == got
+    # the reference run: one request at a time, logits from the step function, the host-driven sampler
+    e = Engine.from_model_dir(model_dirs[which], dtype="float32", page_size=16, num_pages=64, max_num_seqs=1)
+    s = Sampler(e.vocab_size, 1, "cuda")
+    for prompt, sp, toks in zip(prompts, sps, got):
+        out = []
+        logits = e.step([StepEntry("r", prompt, [len(prompt) - 1])])
+        for n in range(sp.max_tokens):
+            t = s.sample(logits, [sp], [sp.seed or 0], [n], [out[-sp.repeat_last_n:]])[0]
+            out.append(t)
+            logits = e.step([StepEntry("r", [t], [0])])
+        e.finish("r")
+        if sp.seed is not None or sp.temperature == 0.0:
+            assert out == toks
+
+
 def test_out_of_vocabulary_token_is_refused(model_dirs):
     from reinfer_b200.engine import EmbeddingOov, Engine, StepEntry
     e = Engine.from_model_dir(model_dirs["A"], dtype="float32", max_tokens=64, max_num_seqs=1)

@@ -127,3 +127,55 @@ def test_bench_refuses_more_than_one_gpu_and_names_the_reference_arm():
     assert p.returncode == 0
     rec = json.loads(p.stdout.strip().splitlines()[-1])
     assert rec["impl"] == "reference" and rec["unavailable"]
+
+
+def test_penalty_window_holds_sampled_tokens_only():
+    """What the repeat / frequency / presence penalties look at: the last `repeat_last_n` tokens the request has
+    drawn - none of its prompt - laid out as the ring that the kernel goes on writing (draw n at n mod window)."""
+    from reinfer_b200.sampling.sampler import history_ring
+    ring, valid = history_ring([], 64)                       # the first token: nothing to penalise yet
+    assert valid == 0 and ring.shape == (64,)
+    ring, valid = history_ring([7, 8, 9], 64)                # fewer draws than the window
+    assert valid == 3 and ring[:3].tolist() == [7, 8, 9]
+    drawn = list(range(100, 110))                            # more draws than the window: the last 4, each at n mod 4
+    ring, valid = history_ring(drawn, 4)
+    assert valid == 4 and sorted(ring.tolist()) == [106, 107, 108, 109]
+    assert all(ring[n % 4] == drawn[n] for n in range(6, 10))
+    # a request that was preempted keeps its output and returns with the same ring (the prompt never enters)
+    again, valid2 = history_ring(list(drawn), 4)
+    assert valid2 == valid and again.tolist() == ring.tolist()
+    assert history_ring([1, 2, 3], 0)[1] == 0                # penalties off: no window
+
+
+def test_a_failed_step_ends_its_requests_and_stops_the_loop():
+    """The entry point's answer to an engine error (a kernel whose bounded wait gave up sets a word that
+    `Engine.step` raises on): nothing of the step is recorded, its requests end with "error" and give back
+    what they hold, and the error goes on to the caller."""
+    from reinfer_b200.cache import CacheManager
+    from reinfer_b200.engine.engine import KernelWaitTimeout
+    from reinfer_b200.engine.scheduler import Request, Scheduler
+    from reinfer_b200.parts.base import PagedKVSpec
+    from reinfer_b200.sampling import SamplingParams
+    cm = CacheManager({"l0": PagedKVSpec(2, 16)}, {}, 4, 16, 4)
+    released = []
+
+    def release(rid):
+        released.append(rid)
+        if rid in cm:
+            cm.release(rid)
+    s = Scheduler(cm, max_batch_tokens=32, release=release)
+    a, b = Request("a", [1, 2, 3], SamplingParams(max_tokens=4)), Request("b", [4, 5], SamplingParams(max_tokens=4))
+    s.add(a); s.add(b)
+    out = s.schedule()
+    for x in out.batch:                                      # what the engine does before it launches
+        cm.admit(x.request.request_id)
+        cm.reserve(x.request.request_id, len(x.tokens))
+    try:
+        raise KernelWaitTimeout("a bounded wait gave up")    # what Engine.step / check_status raise
+    except KernelWaitTimeout:
+        for x in out.batch:
+            s.fail(x.request)
+    assert a.finish_reason == b.finish_reason == "error" and not a.output and a.num_computed == 0
+    assert sorted(released) == ["a", "b"] and not s.has_work()
+    assert cm.free_pages() == cm.total_pages() and cm.free_slots() == 4
+    cm.check()
