@@ -2,10 +2,15 @@
 cache, one function per part, torch on the CPU only.  It shares no code with
 `reinfer_b200`; tests compare the engine with it.
 
-It rests on the formulas of the reference alone (its model code is Rust plus CUDA
-and cannot be compiled or imported here): every function cites the reference file
-and line whose arithmetic it restates.  `dtype` is the precision it computes in:
-float64 by default, so that it is a truth for the 32-bit engine too.
+The reference's model code is Rust plus CUDA; the Rust cannot be compiled here, so
+the forward pass as a whole rests on the reference's formulas: every function cites
+the file and line whose arithmetic it restates.  The parts, however, are held
+against the reference's own CUDA kernels: tests/golden/make_golden.py compiles those
+kernels unchanged and records what they compute (RMSNorm, the rotation, per-head
+norm before rotation, SwiGLU, the masked softmax, grouped decode attention over a
+paged cache, the sampler's draws), and tests/test_golden.py compares the functions
+below with those records.  `dtype` is the precision it computes in: float64 by
+default, so that it is a truth for the 32-bit engine too.
 """
 from __future__ import annotations
 
