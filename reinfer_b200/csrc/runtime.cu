@@ -86,6 +86,40 @@ int rb_tensor_map_bf16(const void* ptr, long long rows, long long cols, long lon
 }
 
 
+// A map over one layer's paged cache [pages, 2 (keys, values), kv_heads, page_size, 128] bfloat16 that brings the keys (or
+// the values) of one (page, kv head) in ONE request, laid out for the tensor cores: the 128 dims of a key are split
+// into two 64-dim halves and the keys into groups of eight, and the box arrives as [group][half][8 keys][64 dims] -
+// 1,024-byte atoms of the 128-byte swizzle, a group's two halves side by side, groups 2,048 bytes apart.  So a tile
+// of 64 keys from pages of any size (8, 16, 32, 64 tokens) has ONE layout, and a page costs one request instead
+// of one per half (two per page with a plain 2-D map).  Dimensions, innermost first: 64 dims (2 bytes apart), 8
+// keys (256 bytes), 2 halves (128 bytes), page_size / 8 groups (2,048 bytes), and (page, k|v, head) folded into one
+// index of page_size * 256 bytes.  (The halves' stride is smaller than the keys': the driver asks only that strides
+// are multiples of 16 bytes.)
+int rb_tensor_map_kv_pages(const void* cache, long long num_pages, int kv_heads, int page_size, CUtensorMap* out) {
+    static std::unordered_map<MapKey, CUtensorMap, MapKeyHash> cache_maps;
+    static std::mutex mu;
+    MapKey key{cache, num_pages, kv_heads, page_size, -5};
+    std::lock_guard<std::mutex> g(mu);
+    auto it = cache_maps.find(key);
+    if (it != cache_maps.end()) { *out = it->second; return 0; }
+    auto enc = get_encode();
+    if (!enc) RB_REFUSE("tensor map: the driver offers no cuTensorMapEncodeTiled");
+    if (page_size < 8 || page_size % 8) RB_REFUSE("tensor map: pages of %d tokens (a multiple of 8 is needed)", page_size);
+    const int groups = page_size / 8;
+    cuuint64_t dims[5] = {64, 8, 2, (cuuint64_t)groups, (cuuint64_t)num_pages * 2ull * (cuuint64_t)kv_heads};
+    cuuint64_t strides[4] = {256, 128, 2048, (cuuint64_t)page_size * 256ull};
+    cuuint32_t box[5] = {64, 8, 2, (cuuint32_t)(groups < 8 ? groups : 8), 1};
+    cuuint32_t estr[5] = {1, 1, 1, 1, 1};
+    CUresult r = enc(out, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 5, const_cast<void*>(cache), dims, strides, box, estr,
+                     CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                     CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) RB_REFUSE("tensor map (cache pages): cuTensorMapEncodeTiled failed with %d (pages %lld heads %d page size %d)",
+                                     (int)r, num_pages, kv_heads, page_size);
+    if (cache_maps.size() > 1024) cache_maps.clear();
+    cache_maps.emplace(key, *out);
+    return 0;
+}
+
 // ---- the status word -------------------------------------------------------------------------
 // One int per device in pinned host memory that is mapped into the device.  A kernel whose bounded wait gives up
 // stores its code there (sm100.cuh: rb_raise), so the host learns of it with a plain load at a moment when it has

@@ -169,3 +169,18 @@ __host__ __device__ constexpr uint32_t make_idesc(int bn) {
 // columns] (128 bytes), 128-byte swizzle, out-of-bounds elements read as zero.  Maps are cached by
 // (address, extents, stride, box): a map depends on nothing else, so a cached one never goes stale.
 int rb_tensor_map_bf16(const void* ptr, long long rows, long long cols, long long ld, int box_rows, CUtensorMap* out);
+// A map over a layer's paged cache that brings one (page, kv head)'s keys or values in one request, as
+// [8-key group][64-dim half][8 keys][64 dims] (runtime.cu).
+int rb_tensor_map_kv_pages(const void* cache, long long num_pages, int kv_heads, int page_size, CUtensorMap* out);
+
+// One box of a 5-D map (coordinates innermost first) into shared memory.
+__device__ __forceinline__ void tma_load_5d(uint32_t dst, const CUtensorMap* map, int c0, int c1, int c2, int c3, int c4, uint32_t bar) {
+    asm volatile(
+        "cp.async.bulk.tensor.5d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3, %4, %5, %6}], [%7];"
+        ::"r"(dst), "l"(map), "r"(c0), "r"(c1), "r"(c2), "r"(c3), "r"(c4), "r"(bar) : "memory");
+}
+// Shared-memory operand descriptor like make_smem_desc with the leading and stride offsets given (bytes).
+__device__ __forceinline__ uint64_t make_smem_desc_lbo_sbo(uint32_t saddr, uint32_t lbo, uint32_t sbo) {
+    return (uint64_t)((saddr >> 4) & 0x3FFFu) | ((uint64_t)((lbo >> 4) & 0x3FFFu) << 16) | ((uint64_t)((sbo >> 4) & 0x3FFFu) << 32) |
+           (1ull << 46) | (2ull << 61);
+}

@@ -410,7 +410,7 @@ def fa_prefill_tc(q, cache, block_table, cu_q, kv_len, out, first_entry: int, n_
     """Paged causal flash attention on the tcgen05 tensor cores (scores and the weighted sum in tensor memory):
     head size 128, page size a power of two >= 8.  q_lens: the token counts of the entries (host)."""
     gc = int(lib().rb_fa_prefill_tc_group(c_int(QH), c_int(KH)))
-    tpt = 128 // gc
+    tpt = int(lib().rb_fa_prefill_tc_rows()) // gc              # tokens that one CTA takes
     n_tiles = sum(-(-int(n) // tpt) for n in q_lens)
     _check(lib().rb_fa_prefill_tc(_p(q), _p(cache), c_longlong(cache.shape[0]), _p(block_table), _p(cu_q), _p(kv_len), _p(out),
                                   c_int(first_entry), c_int(n_entries), c_int(n_tiles), c_int(QH), c_int(KH), c_int(d),
