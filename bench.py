@@ -146,7 +146,7 @@ def main() -> int:
             points[f"b{B}_context"] = c
     mixed = None
     if mixed_run:
-        bench.mixed(4, 128, 1024, 2048, 8, seed=1)                # warm: the step sizes' first launches
+        bench.mixed(32, 128, 4096, 2048, 128, seed=0)             # warm: the same run once (first launches, graph captures)
         mixed = bench.mixed(32, 128, 4096, 2048, 128, seed=0)
     seg = {}
     if not a.no_segments:

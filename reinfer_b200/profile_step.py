@@ -1,8 +1,9 @@
 """A few steps of a random-weight model for a profiler to look at:
 
-    python -m reinfer_b200.profile_step --mode decode|prefill|timeline --batch B --context N [--layers L] [--steps K]
+    python -m reinfer_b200.profile_step --mode decode|prefill|timeline [--shape qwen3-8b|4b|32b|<config.json>]
+                                        --batch B --context N [--layers L] [--steps K] [--page-size P]
 
-builds the Qwen3-8B shape (or fewer layers of it), fills B requests to N tokens, runs two
+builds a random-weight model of the shape (reinfer_b200/shapes/, or fewer layers of it), fills B requests to N tokens, runs two
 warm-up steps, and brackets K steps of the chosen kind with cudaProfilerStart/Stop, so that
 `ncu --profile-from-start off` sees exactly those (the reference brackets its step with event
 profilers instead, crates/cuda/src/engine.rs:928-1408).  Decode steps are launched eagerly
@@ -25,7 +26,9 @@ def main(argv=None) -> int:
     ap.add_argument("--mode", choices=["decode", "prefill", "timeline"], default="decode")
     ap.add_argument("--batch", type=int, default=8)
     ap.add_argument("--context", type=int, default=4000)
-    ap.add_argument("--layers", type=int, default=36)
+    ap.add_argument("--shape", default="qwen3-8b", help="a file of reinfer_b200/shapes (qwen3-8b, 4b, 32b) or a config.json")
+    ap.add_argument("--layers", type=int, default=None, help="build only this many layers of the shape")
+    ap.add_argument("--page-size", type=int, default=16)
     ap.add_argument("--steps", type=int, default=2)
     ap.add_argument("--prefill-tokens", type=int, default=2048)
     a = ap.parse_args(argv)
@@ -35,17 +38,15 @@ def main(argv=None) -> int:
         if "-DRB_TIMELINE" not in build.FLAGS:
             build.FLAGS.append("-DRB_TIMELINE")
     import torch
-    from . import ops
-    from .config import Qwen3Config
+    from . import measure, ops
     from .engine import Engine, StepEntry
 
-    cfg = Qwen3Config.from_dict(dict(
-        architectures=["Qwen3ForCausalLM"], num_hidden_layers=a.layers, hidden_size=4096, num_attention_heads=32,
-        num_key_value_heads=8, head_dim=128, intermediate_size=12288, vocab_size=151936, rope_theta=1e6,
-        rms_norm_eps=1e-6, tie_word_embeddings=False, max_position_embeddings=40960))
+    _raw, cfg, _full = measure.load_shape(a.shape, a.layers)
+    a.layers = int(_raw["num_hidden_layers"])
     B, N = a.batch, a.context
-    eng = Engine.from_config(cfg, seed=0, dtype="bfloat16", page_size=64, max_tokens=B * (N + 64) + 2 * a.prefill_tokens,
-                             max_num_seqs=B + 1, cuda_graphs=a.mode == "timeline")
+    eng = Engine.from_config(cfg, seed=0, dtype="bfloat16", page_size=a.page_size,
+                             max_tokens=B * (N + a.page_size) + 2 * a.prefill_tokens, max_num_seqs=B + 1,
+                             cuda_graphs=a.mode == "timeline")
     g = torch.Generator().manual_seed(0)
     for b in range(B):
         toks = torch.randint(0, cfg.vocab_size, (N,), generator=g).tolist()
