@@ -71,7 +71,10 @@ __device__ __forceinline__ uint32_t ft_off(int row, int chunk, int half_bytes) {
     return (uint32_t)((chunk >> 3) * half_bytes + row * 128 + (((chunk & 7) ^ (row & 7)) << 4));
 }
 
-template <int HALVES, int NST>
+// P5: the map is the 5-D one of runtime.cu (head size 128): ONE request brings a page's keys (or values) for this kv head,
+// as [8-key group][64-dim half][8 keys][64 dims] - groups 2,048 bytes apart, a group's second half 1,024 bytes on - instead
+// of one request per page and half into [half][64 keys][64 dims].
+template <int HALVES, int NST, bool P5>
 __global__ void __launch_bounds__(FT_THREADS)
 fa_decode_tma_kernel(const __grid_constant__ CUtensorMap map_kv, const FtArgs a) {
     RB_TL(4);
@@ -79,6 +82,11 @@ fa_decode_tma_kernel(const __grid_constant__ CUtensorMap map_kv, const FtArgs a)
     constexpr int KV_BYTES = HALVES * FT_HALF_BYTES;           // one K (or V) tile
     constexpr int STAGE = 2 * KV_BYTES;
     constexpr int Q_HALF = 16 * 128;
+    // byte offset of 16-byte chunk c of key `row` inside a key (or value) tile
+    auto kv_off = [](int row, int c) -> uint32_t {
+        return P5 ? (uint32_t)((row >> 3) * 2048 + (c >> 3) * 1024 + (row & 7) * 128 + (((c & 7) ^ (row & 7)) << 4))
+                  : ft_off(row, c, FT_HALF_BYTES);
+    };
     extern __shared__ __align__(1024) unsigned char smem_raw[];
     unsigned char* smem = (unsigned char*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
     unsigned char* stages = smem;
@@ -179,12 +187,19 @@ fa_decode_tma_kernel(const __grid_constant__ CUtensorMap map_kv, const FtArgs a)
                     for (int u = 0; u < 8; ++u) {
                         if (pages[u] >= 0) {
                             const int key = k0 + u * box_rows;
-                            const int y = pages[u] * rows_per_page2 + kh * a.page_size + (key & (a.page_size - 1));
+                            if (P5) {
+                                const int grp = (key & (a.page_size - 1)) >> 3, j = pages[u] * 2 * a.KH + kh;
+                                const uint32_t dst = dst0 + (uint32_t)(u * (box_rows >> 3) * 2048);
+                                tma_load_5d(dst, &map_kv, 0, 0, 0, grp, j, full);
+                                tma_load_5d(dst + KV_BYTES, &map_kv, 0, 0, 0, grp, j + a.KH, full);
+                            } else {
+                                const int y = pages[u] * rows_per_page2 + kh * a.page_size + (key & (a.page_size - 1));
 #pragma unroll
-                            for (int h = 0; h < HALVES; ++h) {
-                                tma_load_2d(dst0 + h * FT_HALF_BYTES + u * box_rows * 128, &map_kv, h * 64, y, full);
-                                tma_load_2d(dst0 + KV_BYTES + h * FT_HALF_BYTES + u * box_rows * 128, &map_kv, h * 64,
-                                            y + a.KH * a.page_size, full);
+                                for (int h = 0; h < HALVES; ++h) {
+                                    tma_load_2d(dst0 + h * FT_HALF_BYTES + u * box_rows * 128, &map_kv, h * 64, y, full);
+                                    tma_load_2d(dst0 + KV_BYTES + h * FT_HALF_BYTES + u * box_rows * 128, &map_kv, h * 64,
+                                                y + a.KH * a.page_size, full);
+                                }
                             }
                         }
                     }
@@ -205,8 +220,8 @@ fa_decode_tma_kernel(const __grid_constant__ CUtensorMap map_kv, const FtArgs a)
                 for (int i = threadIdx.x; i < FT_BN * HALVES * 8; i += FT_WARPS * 32) {
                     const int row = i / (HALVES * 8), c = i % (HALVES * 8);
                     if (k0 + row >= kv_end) {
-                        *reinterpret_cast<uint4*>(stages + s * STAGE + ft_off(row, c, FT_HALF_BYTES)) = make_uint4(0, 0, 0, 0);
-                        *reinterpret_cast<uint4*>(stages + s * STAGE + KV_BYTES + ft_off(row, c, FT_HALF_BYTES)) = make_uint4(0, 0, 0, 0);
+                        *reinterpret_cast<uint4*>(stages + s * STAGE + kv_off(row, c)) = make_uint4(0, 0, 0, 0);
+                        *reinterpret_cast<uint4*>(stages + s * STAGE + KV_BYTES + kv_off(row, c)) = make_uint4(0, 0, 0, 0);
                     }
                 }
                 asm volatile("fence.proxy.async.shared::cta;" ::: "memory");   // before a later copy refills this stage
@@ -220,7 +235,7 @@ fa_decode_tma_kernel(const __grid_constant__ CUtensorMap map_kv, const FtArgs a)
             for (int ks = 0; ks < D / 16; ++ks) {
                 uint32_t qa[4], kb[4];
                 ft_ldsm_x4(qa, sQ_u + ft_off((lane & 7) + 8 * ((lane >> 3) & 1), ks * 2 + (lane >> 4), Q_HALF));
-                ft_ldsm_x4(kb, sK + ft_off(koff + (lane & 7) + 8 * (lane >> 4), ks * 2 + ((lane >> 3) & 1), FT_HALF_BYTES));
+                ft_ldsm_x4(kb, sK + kv_off(koff + (lane & 7) + 8 * (lane >> 4), ks * 2 + ((lane >> 3) & 1)));
                 ft_mma(sc[0], qa, kb[0], kb[1]);
                 ft_mma(sc[1], qa, kb[2], kb[3]);
             }
@@ -254,7 +269,7 @@ fa_decode_tma_kernel(const __grid_constant__ CUtensorMap map_kv, const FtArgs a)
 #pragma unroll
             for (int dp = 0; dp < D / 16; ++dp) {
                 uint32_t vb[4];
-                ft_ldsm_x4_trans(vb, sV + ft_off(koff + (lane & 7) + 8 * ((lane >> 3) & 1), dp * 2 + (lane >> 4), FT_HALF_BYTES));
+                ft_ldsm_x4_trans(vb, sV + kv_off(koff + (lane & 7) + 8 * ((lane >> 3) & 1), dp * 2 + (lane >> 4)));
                 ft_mma(o[2 * dp], pa, vb[0], vb[1]);
                 ft_mma(o[2 * dp + 1], pa, vb[2], vb[3]);
             }
@@ -705,7 +720,7 @@ __global__ void ft_merge_kernel(const float* __restrict__ part_o, const float* _
     }
 }
 
-template <int HALVES, int NST>
+template <int HALVES, int NST, bool P5 = false>
 static int ft_launch(const CUtensorMap& map, const FtArgs& a, cudaStream_t s) {
     constexpr size_t pipe = (size_t)NST * 2 * HALVES * FT_HALF_BYTES;
     constexpr size_t merge = (size_t)FT_WARPS * 16 * (HALVES * 64 + 2) * sizeof(float);
@@ -715,14 +730,14 @@ static int ft_launch(const CUtensorMap& map, const FtArgs& a, cudaStream_t s) {
     constexpr size_t smem = pipe + HALVES * 16 * 128 + 256 + (size_t)(16 * HALVES * 64 + 128 + 8 * 16) * sizeof(float) + 1024;
     static bool done = false;
     if (!done) {
-        cudaError_t e = cudaFuncSetAttribute(fa_decode_tma_kernel<HALVES, NST>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        cudaError_t e = cudaFuncSetAttribute(fa_decode_tma_kernel<HALVES, NST, P5>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         if (e != cudaSuccess) return (int)e;
         done = true;
     }
     const dim3 grid(a.n_entries, a.KH * a.chunks, a.n_splits);
     if (a.cluster_merge)
-        return rb_launch_cluster(fa_decode_tma_kernel<HALVES, NST>, grid, dim3(FT_THREADS), dim3(1, 1, a.n_splits), smem, s, map, a);
-    return rb_launch(fa_decode_tma_kernel<HALVES, NST>, grid, dim3(FT_THREADS), smem, s, map, a);
+        return rb_launch_cluster(fa_decode_tma_kernel<HALVES, NST, P5>, grid, dim3(FT_THREADS), dim3(1, 1, a.n_splits), smem, s, map, a);
+    return rb_launch(fa_decode_tma_kernel<HALVES, NST, P5>, grid, dim3(FT_THREADS), smem, s, map, a);
 }
 
 // As rb_fa_decode, with `cache` the layer's [num_pages, 2, KH, page_size, d] array described to TMA.
@@ -756,12 +771,17 @@ extern "C" int rb_fa_decode_tma(const void* q, const void* cache, long long num_
     a.cluster_merge = cluster_merge ? 1 : 0;
     CUtensorMap map;
     const int box_rows = page_size < FT_BN ? page_size : FT_BN;
-    if (rb_tensor_map_bf16(cache, num_pages * 2LL * KH * page_size, d, d, box_rows, &map)) return -1;
     cudaStream_t s = (cudaStream_t)stream;
     int rc;
-    if (d <= 64) rc = ft_launch<1, 4>(map, a, s);
-    else if (d <= 128) rc = ft_launch<2, 3>(map, a, s);
-    else rc = ft_launch<4, 2>(map, a, s);
+    if (d == 128) {                                    // heads of exactly 128: a page's keys in one request
+        if (rb_tensor_map_kv_pages(cache, num_pages, KH, page_size, &map)) return -1;
+        rc = ft_launch<2, 3, true>(map, a, s);
+    } else {
+        if (rb_tensor_map_bf16(cache, num_pages * 2LL * KH * page_size, d, d, box_rows, &map)) return -1;
+        if (d <= 64) rc = ft_launch<1, 4>(map, a, s);
+        else if (d <= 128) rc = ft_launch<2, 3>(map, a, s);
+        else rc = ft_launch<4, 2>(map, a, s);
+    }
     if (rc || n_splits == 1 || cluster_merge) return rc;
     return rb_launch(ft_merge_kernel, dim3(n_entries, QH), dim3(128), 0, s, (const float*)part_o, (const float*)part_lse,
                      (bf16*)out, first_tok, QH, d, n_splits);

@@ -248,7 +248,9 @@ class Bench:
                 engine.finish(("seg", "w"))
                 entries = [StepEntry(("seg", 0), self.tokens(T), [T - 1])]
             torch.cuda.synchronize()
-            torch.cuda._sleep(4_000_000)                                # the host queues the whole step meanwhile
+            # the host needs a few milliseconds to queue a step's launches and events: the device sleeps meanwhile, so
+            # that no launch waits for the host and a launch's span is the kernel's own time
+            torch.cuda._sleep(60_000_000 if kind == "decode" else 20_000_000)
             old = ops.set_profiler(prof)
             prof.begin()
             try:
