@@ -152,7 +152,10 @@ class Bench:
         from .engine.llm import LLM
         from .sampling import SamplingParams
         torch, engine = self.torch, self.engine
-        start_len = max(context - steps - warmup - 3 * B - 2, 1)
+        # the request admitted first decodes while the others still run their prompts (a prompt takes context / 2,048
+        # steps): leave that many tokens of room, so that no request passes `context` (and no block table outgrows the
+        # captured step's width) before the timed steps end
+        start_len = max(context - steps - warmup - B * (-(-context // 2048) + 1) - 2, 1)
         llm = LLM(engine=engine, max_batch_tokens=2048, seed=0)
         sp = SamplingParams(temperature=0.0, max_tokens=1 << 20, ignore_eos=True)
         for _ in range(B):
