@@ -43,8 +43,22 @@ __device__ __forceinline__ unsigned long long tl_now() {
 extern "C" int rb_gemm_timeline(unsigned long long* buf) {
     return (int)cudaMemcpyToSymbol(g_tc_timeline, &buf, sizeof(buf));
 }
+// The persistent kernels also write, per CTA and per tile they take (at most `g_tc_tile_cap` of them), ten words to the
+// buffer of rb_gemm_tile_trace(): MMA thread: tile begun (ns), cycles it waited for operand stages, last product issued
+// (ns), cycles its commits took; epilogue: accumulator ready (ns), accumulator drained (ns);
+// producer: first request of the tile issued (ns), cycles it waited for free stages; MMA thread again: cycles from
+// tile begun to last product issued, cycles its products took to issue.  Ten words a tile.
+__device__ unsigned long long* g_tc_tiles = nullptr;
+__device__ int g_tc_tile_cap = 0;
+#define TT(local, slot, value) do { if (g_tc_tiles && (local) < g_tc_tile_cap) g_tc_tiles[((size_t)blockIdx.x * g_tc_tile_cap + (local)) * 10 + (slot)] = (value); } while (0)
+extern "C" int rb_gemm_tile_trace(unsigned long long* buf, int cap) {
+    cudaError_t e = cudaMemcpyToSymbol(g_tc_tiles, &buf, sizeof(buf));
+    if (e == cudaSuccess) e = cudaMemcpyToSymbol(g_tc_tile_cap, &cap, sizeof(cap));
+    return (int)e;
+}
 #else
 #define TL(slot) do { } while (0)
+#define TT(local, slot, value) do { } while (0)
 #endif
 
 struct TcShared {                        // after the operand stages, in dynamic shared memory
@@ -116,61 +130,60 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
     if (threadIdx.x == 0) TL(1);
     int issued = 0;                                   // producer: k-blocks whose loads were issued
 
+    // The two issuing warps stay converged (every lane walks the loop and waits at the barriers) and lane 0 issues
+    // through predicated instructions: an issuing lane alone inside a branch pays about a hundred cycles more for
+    // every asynchronous instruction.
+    const uint32_t lead = lane == 0 ? 1u : 0u;
     if (warp == 0) {
-        if (lane == 0) {
-            // Weights never change, so their first tiles are fetched at once, while the kernels
-            // before this one may still be running; the activations wait for them to finish.
-            pdl_trigger();
-            const int pre = min(nkb, STAGES);
-            for (int kb = 0; kb < pre; ++kb) {
-                const uint32_t full = smem_u32(&sh->full[kb]);
-                mbar_expect_tx(full, STAGE_BYTES);
-                tma_load_2d(smem_base + kb * STAGE_BYTES, &map_w, (kb0 + kb) * TC_BK, n0, full);
-                if (DUAL) tma_load_2d(smem_base + kb * STAGE_BYTES + W1_BYTES, &map_w, (kb0 + kb) * TC_BK, N + n0, full);
-            }
-            pdl_wait();
-            RB_TL_MARK();
-            for (int kb = 0; kb < pre; ++kb)
-                tma_load_2d(smem_base + kb * STAGE_BYTES + W_BYTES, &map_x, (kb0 + kb) * TC_BK, t0, smem_u32(&sh->full[kb]));
-            issued = pre;
-            for (int kb = pre; kb < nkb; ++kb) {
-                const int s = kb % STAGES;
-                const uint32_t round = kb / STAGES;
-                if (!mbar_wait(smem_u32(&sh->empty[s]), (round & 1) ^ 1, abort_flag, 1)) break;
-                const uint32_t full = smem_u32(&sh->full[s]);
-                mbar_expect_tx(full, STAGE_BYTES);
-                const uint32_t dst = smem_base + s * STAGE_BYTES;
-                const int kx = (kb0 + kb) * TC_BK;
-                tma_load_2d(dst, &map_w, kx, n0, full);
-                if (DUAL) tma_load_2d(dst + W1_BYTES, &map_w, kx, N + n0, full);
-                tma_load_2d(dst + W_BYTES, &map_x, kx, t0, full);
-                issued = kb + 1;
-            }
+        // Weights never change, so their first tiles are fetched at once, while the kernels
+        // before this one may still be running; the activations wait for them to finish.
+        pdl_trigger();
+        const int pre = min(nkb, STAGES);
+        for (int kb = 0; kb < pre; ++kb) {
+            const uint32_t full = smem_u32(&sh->full[kb]);
+            mbar_expect_tx_lead(full, STAGE_BYTES, lead);
+            tma_load_2d_lead(smem_base + kb * STAGE_BYTES, &map_w, (kb0 + kb) * TC_BK, n0, full, lead);
+            if (DUAL) tma_load_2d_lead(smem_base + kb * STAGE_BYTES + W1_BYTES, &map_w, (kb0 + kb) * TC_BK, N + n0, full, lead);
+        }
+        pdl_wait();
+        if (lead) RB_TL_MARK();
+        for (int kb = 0; kb < pre; ++kb)
+            tma_load_2d_lead(smem_base + kb * STAGE_BYTES + W_BYTES, &map_x, (kb0 + kb) * TC_BK, t0, smem_u32(&sh->full[kb]), lead);
+        issued = pre;
+        for (int kb = pre; kb < nkb; ++kb) {
+            const int s = kb % STAGES;
+            const uint32_t round = kb / STAGES;
+            if (!mbar_wait(smem_u32(&sh->empty[s]), (round & 1) ^ 1, abort_flag, 1)) break;
+            const uint32_t full = smem_u32(&sh->full[s]);
+            mbar_expect_tx_lead(full, STAGE_BYTES, lead);
+            const uint32_t dst = smem_base + s * STAGE_BYTES;
+            const int kx = (kb0 + kb) * TC_BK;
+            tma_load_2d_lead(dst, &map_w, kx, n0, full, lead);
+            if (DUAL) tma_load_2d_lead(dst + W1_BYTES, &map_w, kx, N + n0, full, lead);
+            tma_load_2d_lead(dst + W_BYTES, &map_x, kx, t0, full, lead);
+            issued = kb + 1;
         }
     } else if (warp == 1) {
-        if (lane == 0) {
-            constexpr uint32_t idesc = make_idesc(BN);
-            bool ok = true;
-            for (int kb = 0; kb < nkb && ok; ++kb) {
-                const int s = kb % STAGES;
-                const uint32_t round = kb / STAGES;
-                ok = mbar_wait(smem_u32(&sh->full[s]), round & 1, abort_flag, 2);
-                if (!ok) break;
-                if (kb == 0) TL(2);
-                tc_fence_after();
-                const uint32_t a = smem_base + s * STAGE_BYTES;
-                const uint64_t da = make_smem_desc(a), db = make_smem_desc(a + W_BYTES);
-                const uint64_t da2 = make_smem_desc(a + W1_BYTES);
+        constexpr uint32_t idesc = make_idesc(BN);
+        bool ok = true;
+        for (int kb = 0; kb < nkb && ok; ++kb) {
+            const int s = kb % STAGES;
+            const uint32_t round = kb / STAGES;
+            ok = mbar_wait(smem_u32(&sh->full[s]), round & 1, abort_flag, 2);   // TMA's bytes, seen through the barrier
+            if (!ok) break;
+            if (kb == 0 && lead) TL(2);
+            const uint32_t a = smem_base + s * STAGE_BYTES;
+            const uint64_t da = make_smem_desc(a), db = make_smem_desc(a + W_BYTES);
+            const uint64_t da2 = make_smem_desc(a + W1_BYTES);
 #pragma unroll
-                for (int k = 0; k < TC_BK / 16; ++k) {               // 32 bytes further along K inside the swizzled row
-                    tc_mma_bf16(tmem, da + (uint64_t)(k * 2), db + (uint64_t)(k * 2), idesc, (kb | k) != 0);
-                    if (DUAL) tc_mma_bf16(tmem + BN, da2 + (uint64_t)(k * 2), db + (uint64_t)(k * 2), idesc, (kb | k) != 0);
-                }
-                tc_commit(smem_u32(&sh->empty[s]));                   // frees the stage when these MMAs are done
+            for (int k = 0; k < TC_BK / 16; ++k) {               // 32 bytes further along K inside the swizzled row
+                tc_mma_bf16_lead(tmem, da + (uint64_t)(k * 2), db + (uint64_t)(k * 2), idesc, (kb | k) != 0, lead);
+                if (DUAL) tc_mma_bf16_lead(tmem + BN, da2 + (uint64_t)(k * 2), db + (uint64_t)(k * 2), idesc, (kb | k) != 0, lead);
             }
-            if (ok) tc_commit(smem_u32(&sh->acc_full));
-            TL(3);
+            tc_commit_lead(smem_u32(&sh->empty[s]), lead);       // frees the stage when these MMAs are done
         }
+        if (ok) tc_commit_lead(smem_u32(&sh->acc_full), lead);
+        if (lead) TL(3);
     } else {
         // epilogue: warp w may read tensor-memory lanes 32*(w%4) .. +31
         const int q = warp & 3;
@@ -361,17 +374,23 @@ struct TcPersistShared {
     int abort_flag;
 };
 
-template <int BN, int STAGES, bool DUAL>
+template <int BN, int STAGES, int MODE>
 __global__ void __launch_bounds__(TC_THREADS, 1)
 gemm_tc_persistent_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_x,
                           void* __restrict__ C, int T, int N, int K, long long ldc, int out_mode, int t_tiles, int n_tiles) {
+    // MODE 0: a tile is 128 features (the M operand) x BN tokens.  MODE 1 (the gated pair) and MODE 2: a tile is 128
+    // tokens (the M operand) x 256 weight rows (the N operand): 128 gate rows and the 128 up rows of the same features,
+    // or 256 features.  A lane of the accumulator is then a token, and the epilogue writes 16 features of it at a time.
+    constexpr bool DUAL = MODE == 1, FLIP = MODE != 0;
+    constexpr int FEATS = MODE == 2 ? 2 * TC_BM : TC_BM;          // features per tile
     RB_TL(DUAL ? 9 : 8);
     extern __shared__ __align__(1024) unsigned char smem_raw[];
     constexpr uint32_t W1_BYTES = TC_BM * TC_BK * 2;
-    constexpr uint32_t W_BYTES = (DUAL ? 2 : 1) * W1_BYTES;
+    constexpr uint32_t W_BYTES = (FLIP ? 2 : 1) * W1_BYTES;
     constexpr uint32_t X_BYTES = BN * TC_BK * 2;
     constexpr uint32_t STAGE_BYTES = W_BYTES + X_BYTES;
-    constexpr uint32_t ACC_COLS = (DUAL ? 2 : 1) * BN;            // columns of one accumulator stage
+    static_assert(!FLIP || BN == 128, "with the tokens as the M operand a tile has 128 of them");
+    constexpr uint32_t ACC_COLS = FLIP ? 2 * TC_BM : BN;          // columns of one accumulator stage
     static_assert(2 * ACC_COLS <= 512, "two accumulator stages must fit tensor memory");
     constexpr uint32_t TMEM_COLS = 2 * ACC_COLS <= 32 ? 32 : 2 * ACC_COLS <= 64 ? 64 : 2 * ACC_COLS <= 128 ? 128 : 2 * ACC_COLS <= 256 ? 256 : 512;
     unsigned char* smem = (unsigned char*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
@@ -398,95 +417,208 @@ gemm_tc_persistent_kernel(const __grid_constant__ CUtensorMap map_w, const __gri
     __syncthreads();
     tc_fence_after();
     const uint32_t tmem = sh->tmem_base;
-    long long issued = 0;                               // producer: k-blocks (over all its tiles) whose loads were issued
+    uint32_t issued = 0;                                // producer: k-blocks (over all its tiles) whose loads were issued
 
+    // The two issuing warps stay converged: every lane walks the loop and waits at the barriers, lane 0 alone issues
+    // (predicated instructions).  Stage index and parity are counters, barrier addresses and operand descriptors are
+    // sums with constants.
+    const uint32_t full0 = smem_u32(&sh->full[0]), empty0 = smem_u32(&sh->empty[0]);
+    const uint32_t lead = lane == 0 ? 1u : 0u;
     if (warp == 0) {
-        if (lane == 0) {
-            pdl_trigger();
-            pdl_wait();
-            long long it = 0;
-            bool ok = true;
-            for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x) {
-                const int t0 = (tile % t_tiles) * BN, n0 = (tile / t_tiles) * TC_BM;
-                for (int kb = 0; kb < nkb; ++kb, ++it) {
-                    const int s = (int)(it % STAGES);
-                    const uint32_t round = (uint32_t)(it / STAGES);
-                    ok = mbar_wait(smem_u32(&sh->empty[s]), (round & 1) ^ 1, abort_flag, 11);
-                    if (!ok) break;
-                    const uint32_t full = smem_u32(&sh->full[s]);
-                    mbar_expect_tx(full, STAGE_BYTES);
-                    const uint32_t dst = smem_base + s * STAGE_BYTES;
-                    tma_load_2d(dst, &map_w, kb * TC_BK, n0, full);
-                    if (DUAL) tma_load_2d(dst + W1_BYTES, &map_w, kb * TC_BK, N + n0, full);
-                    tma_load_2d(dst + W_BYTES, &map_x, kb * TC_BK, t0, full);
-                    issued = it + 1;
-                }
+        pdl_trigger();
+        pdl_wait();
+        bool ok = true;
+        uint32_t s = 0, ph = 1;                           // a stage's first use finds it free
+        [[maybe_unused]] int plocal = 0;
+        for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x, ++plocal) {
+            const int t0 = (tile % t_tiles) * BN, n0 = (tile / t_tiles) * FEATS;
+            [[maybe_unused]] long long waited = 0;
+            for (int kb = 0; kb < nkb; ++kb) {
+#ifdef RB_TIMELINE
+                const long long c0 = clock64();
+#endif
+                ok = mbar_wait(empty0 + 8 * s, ph, abort_flag, 11);
+#ifdef RB_TIMELINE
+                waited += clock64() - c0;
+                if (kb == 0 && lead) TT(plocal, 6, tl_now());
+#endif
+                if (!ok) break;
+                const uint32_t full = full0 + 8 * s;
+                mbar_expect_tx_lead(full, STAGE_BYTES, lead);
+                const uint32_t dst = smem_base + s * STAGE_BYTES;
+                tma_load_2d_lead(dst, &map_w, kb * TC_BK, n0, full, lead);      // MODE 2: the map's box has 256 rows
+                if (DUAL) tma_load_2d_lead(dst + W1_BYTES, &map_w, kb * TC_BK, N + n0, full, lead);
+                tma_load_2d_lead(dst + W_BYTES, &map_x, kb * TC_BK, t0, full, lead);
+                ++issued;
+                if (++s == STAGES) { s = 0; ph ^= 1; }
             }
+            if (lead) TT(plocal, 7, (unsigned long long)waited);
         }
     } else if (warp == 1) {
-        if (lane == 0) {
-            constexpr uint32_t idesc = make_idesc(BN);
-            long long it = 0;
-            bool ok = true;
-            int local = 0;
-            for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x, ++local) {
-                const int a = local & 1;
-                ok = mbar_wait(smem_u32(&sh->acc_empty[a]), ((uint32_t)(local >> 1) & 1) ^ 1, abort_flag, 12);   // drained by the epilogue
-                if (!ok) break;
-                tc_fence_after();
-                const uint32_t acc = tmem + (uint32_t)a * ACC_COLS;
-                for (int kb = 0; kb < nkb; ++kb, ++it) {
-                    const int s = (int)(it % STAGES);
-                    ok = mbar_wait(smem_u32(&sh->full[s]), (uint32_t)(it / STAGES) & 1, abort_flag, 13);
+        constexpr uint32_t idesc = make_idesc(FLIP ? 2 * TC_BM : BN);
+        const uint64_t dw0 = make_smem_desc(smem_base), dx0 = make_smem_desc(smem_base + W_BYTES);
+        bool ok = true;
+        uint32_t s = 0, ph = 0;
+        int local = 0;
+        // Whether the next stage has landed is asked while this stage's products are being issued, so that the
+        // answer's latency is not part of the serial loop; only an answer of "not yet" leads to a wait.
+        bool landed = false;
+        for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x, ++local) {
+            const int a = local & 1;
+            ok = mbar_wait(smem_u32(&sh->acc_empty[a]), ((uint32_t)(local >> 1) & 1) ^ 1, abort_flag, 12);   // drained by the epilogue
+            if (!ok) break;
+#ifdef RB_TIMELINE
+            if (lead) TT(local, 0, tl_now());
+            long long waited = 0, t_mma = 0, t_commit = 0;
+            const long long cb = clock64();
+#endif
+            tc_fence_after();
+            const uint32_t acc = tmem + (uint32_t)a * ACC_COLS;
+            for (int kb = 0; kb < nkb; ++kb) {
+                if (!landed) {
+#ifdef RB_TIMELINE
+                    const long long c0 = clock64();
+#endif
+                    ok = mbar_wait(full0 + 8 * s, ph, abort_flag, 13);   // TMA's bytes, seen through the barrier: no tcgen05 fence is due
+#ifdef RB_TIMELINE
+                    waited += clock64() - c0;
+#endif
                     if (!ok) break;
-                    tc_fence_after();
-                    const uint32_t base = smem_base + s * STAGE_BYTES;
-                    const uint64_t da = make_smem_desc(base), db = make_smem_desc(base + W_BYTES);
-                    const uint64_t da2 = make_smem_desc(base + W1_BYTES);
-#pragma unroll
-                    for (int k = 0; k < TC_BK / 16; ++k) {
-                        tc_mma_bf16(acc, da + (uint64_t)(k * 2), db + (uint64_t)(k * 2), idesc, (kb | k) != 0);
-                        if (DUAL) tc_mma_bf16(acc + BN, da2 + (uint64_t)(k * 2), db + (uint64_t)(k * 2), idesc, (kb | k) != 0);
-                    }
-                    tc_commit(smem_u32(&sh->empty[s]));
                 }
-                if (ok) tc_commit(smem_u32(&sh->acc_full[a]));
+                const uint64_t off = (uint64_t)(s * (STAGE_BYTES >> 4));     // the address field counts 16-byte units
+                const uint64_t da = dw0 + off, db = dx0 + off;
+                const uint32_t s_next = s + 1 == STAGES ? 0 : s + 1, ph_next = s + 1 == STAGES ? ph ^ 1 : ph;
+#ifdef RB_TIMELINE
+                const long long c1 = clock64();
+#endif
+                if (FLIP) tc_mma_bf16_lead(acc, db, da, idesc, kb != 0, lead);
+                else tc_mma_bf16_lead(acc, da, db, idesc, kb != 0, lead);
+                landed = mbar_test(full0 + 8 * s_next, ph_next);
+#pragma unroll
+                for (int k = 1; k < TC_BK / 16; ++k) {
+                    if (FLIP) tc_mma_bf16_lead(acc, db + (uint64_t)(k * 2), da + (uint64_t)(k * 2), idesc, 1, lead);
+                    else tc_mma_bf16_lead(acc, da + (uint64_t)(k * 2), db + (uint64_t)(k * 2), idesc, 1, lead);
+                }
+#ifdef RB_TIMELINE
+                const long long c2 = clock64();
+#endif
+                tc_commit_lead(empty0 + 8 * s, lead);
+#ifdef RB_TIMELINE
+                t_mma += c2 - c1;
+                t_commit += clock64() - c2;
+#endif
+                s = s_next; ph = ph_next;
             }
+            if (ok) tc_commit_lead(smem_u32(&sh->acc_full[a]), lead);
+#ifdef RB_TIMELINE
+            if (lead) { TT(local, 1, (unsigned long long)waited); TT(local, 2, tl_now()); TT(local, 8, (unsigned long long)(clock64() - cb)); TT(local, 9, (unsigned long long)t_mma); TT(local, 3, (unsigned long long)t_commit); }
+#endif
         }
     } else {
         const int q = warp & 3;
         pdl_wait();
         int local = 0;
+        const bool vec_ok = (ldc % 8 == 0) && (((uintptr_t)C & 15) == 0);
         for (int tile = blockIdx.x; tile < total_tiles; tile += gridDim.x, ++local) {
             const int a = local & 1;
-            const int t0 = (tile % t_tiles) * BN, n0 = (tile / t_tiles) * TC_BM;
-            const int feat = n0 + q * 32 + lane;
+            const int t0 = (tile % t_tiles) * BN, n0 = (tile / t_tiles) * FEATS;
             if (!mbar_wait(smem_u32(&sh->acc_full[a]), (uint32_t)(local >> 1) & 1, abort_flag, 14)) break;
+#ifdef RB_TIMELINE
+            if (warp == 2 && lane == 0) TT(local, 4, tl_now());
+#endif
             tc_fence_after();
             const uint32_t acc = tmem + ((uint32_t)(q * 32) << 16) + (uint32_t)a * ACC_COLS;
+            if (DUAL) {
+                // a lane is a token; columns 0..127 hold its gate features, 128..255 the up features of the same tile
+                const int tok = t0 + q * 32 + lane;
+                bf16* row = (bf16*)C + (size_t)tok * ldc + n0;
+#pragma unroll 1
+                for (int c0 = 0; c0 < TC_BM; c0 += 16) {
+                    if (n0 + c0 >= N) break;
+                    uint32_t r[16], r2[16];
+                    tc_ld16(acc + (uint32_t)c0, r);
+                    tc_ld16(acc + (uint32_t)(TC_BM + c0), r2);
+                    tc_ld_wait();
+                    if (tok < T) {
+                        uint32_t o[8];
+#pragma unroll
+                        for (int j = 0; j < 8; ++j) {
+                            const float g0 = __uint_as_float(r[2 * j]), u0 = __uint_as_float(r2[2 * j]);
+                            const float g1 = __uint_as_float(r[2 * j + 1]), u1 = __uint_as_float(r2[2 * j + 1]);
+                            const __nv_bfloat162 v = __floats2bfloat162_rn(g0 / (1.0f + expf(-g0)) * u0, g1 / (1.0f + expf(-g1)) * u1);
+                            o[j] = *(const uint32_t*)&v;
+                        }
+                        if (vec_ok && n0 + c0 + 16 <= N) {
+                            *(uint4*)(row + c0) = make_uint4(o[0], o[1], o[2], o[3]);
+                            *(uint4*)(row + c0 + 8) = make_uint4(o[4], o[5], o[6], o[7]);
+                        } else {
+                            const bf16* ov = (const bf16*)o;
+#pragma unroll
+                            for (int j = 0; j < 16; ++j) if (n0 + c0 + j < N) row[c0 + j] = ov[j];
+                        }
+                    }
+                }
+            } else if (FLIP) {
+                // a lane is a token; its 256 columns are 256 features
+                const int tok = t0 + q * 32 + lane;
+                const bool vec4 = (ldc % 4 == 0) && (((uintptr_t)C & 15) == 0);
+#pragma unroll 1
+                for (int c0 = 0; c0 < FEATS; c0 += 16) {
+                    if (n0 + c0 >= N) break;
+                    uint32_t r[16];
+                    tc_ld16(acc + (uint32_t)c0, r);
+                    tc_ld_wait();
+                    if (tok >= T) continue;
+                    const bool whole = n0 + c0 + 16 <= N;
+                    if (out_mode == 0) {
+                        bf16* row = (bf16*)C + (size_t)tok * ldc + n0 + c0;
+                        uint32_t o[8];
+#pragma unroll
+                        for (int j = 0; j < 8; ++j) {
+                            const __nv_bfloat162 v = __floats2bfloat162_rn(__uint_as_float(r[2 * j]), __uint_as_float(r[2 * j + 1]));
+                            o[j] = *(const uint32_t*)&v;
+                        }
+                        if (vec_ok && whole) {
+                            *(uint4*)row = make_uint4(o[0], o[1], o[2], o[3]);
+                            *(uint4*)(row + 8) = make_uint4(o[4], o[5], o[6], o[7]);
+                        } else {
+                            const bf16* ov = (const bf16*)o;
+#pragma unroll
+                            for (int j = 0; j < 16; ++j) if (n0 + c0 + j < N) row[j] = ov[j];
+                        }
+                    } else {
+                        float* row = (float*)C + (size_t)tok * ldc + n0 + c0;
+                        if (vec4 && whole) {
+                            float4 v[4];
+#pragma unroll
+                            for (int j = 0; j < 4; ++j) v[j] = out_mode == 2 ? *(const float4*)(row + 4 * j) : make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+                            for (int j = 0; j < 4; ++j)
+                                *(float4*)(row + 4 * j) = make_float4(v[j].x + __uint_as_float(r[4 * j]), v[j].y + __uint_as_float(r[4 * j + 1]),
+                                                                      v[j].z + __uint_as_float(r[4 * j + 2]), v[j].w + __uint_as_float(r[4 * j + 3]));
+                        } else {
+#pragma unroll
+                            for (int j = 0; j < 16; ++j)
+                                if (n0 + c0 + j < N) row[j] = (out_mode == 2 ? row[j] : 0.0f) + __uint_as_float(r[j]);
+                        }
+                    }
+                }
+            } else {
+            const int feat = n0 + q * 32 + lane;
 #pragma unroll 1
             for (int c0 = 0; c0 < BN; c0 += 16) {
                 if (t0 + c0 >= T) break;
-                uint32_t r[16], r2[16];
+                uint32_t r[16];
                 tc_ld16(acc + (uint32_t)c0, r);
-                if (DUAL) tc_ld16(acc + (uint32_t)(BN + c0), r2);
                 tc_ld_wait();
                 if (feat < N) {
                     const int nt = min(16, T - t0 - c0);
-                    if (DUAL) {
-                        bf16* cp = (bf16*)C + (size_t)(t0 + c0) * ldc + feat;
-#pragma unroll
-                        for (int j = 0; j < 16; ++j) {
-                            const float g = __uint_as_float(r[j]), u = __uint_as_float(r2[j]);
-                            if (j < nt) cp[(size_t)j * ldc] = __float2bfloat16_rn(g / (1.0f + expf(-g)) * u);
-                        }
-                    } else if (out_mode == 2) {
+                    if (out_mode == 2) {
+                        // one addition per element, done where the element lives (a reduction without a return value):
+                        // the same sum as load, add, store, without the load's way back
                         float* cp = (float*)C + (size_t)(t0 + c0) * ldc + feat;
-                        float old[16];
 #pragma unroll
-                        for (int j = 0; j < 16; ++j) old[j] = j < nt ? cp[(size_t)j * ldc] : 0.0f;
-#pragma unroll
-                        for (int j = 0; j < 16; ++j) if (j < nt) cp[(size_t)j * ldc] = old[j] + __uint_as_float(r[j]);
+                        for (int j = 0; j < 16; ++j) if (j < nt) red_add_f32(cp + (size_t)j * ldc, __uint_as_float(r[j]));
                     } else if (out_mode == 0) {
                         bf16* cp = (bf16*)C + (size_t)(t0 + c0) * ldc + feat;
 #pragma unroll
@@ -498,18 +630,22 @@ gemm_tc_persistent_kernel(const __grid_constant__ CUtensorMap map_w, const __gri
                     }
                 }
             }
+            }
             // this warp has read its quarter of the accumulator: the MMA thread may refill it once all four have
             tc_fence_before();
             __syncwarp();
             if (lane == 0) mbar_arrive(smem_u32(&sh->acc_empty[a]));
+#ifdef RB_TIMELINE
+            if (warp == 2 && lane == 0) TT(local, 5, tl_now());
+#endif
         }
     }
     tc_fence_before();
     __syncthreads();
     if (*abort_flag && threadIdx.x == 0) {
-        for (long long it = issued > STAGES ? issued - STAGES : 0; it < issued; ++it) {
+        for (uint32_t it = issued > STAGES ? issued - STAGES : 0; it < issued; ++it) {
             const uint32_t bar = smem_u32(&sh->full[it % STAGES]);
-            const uint32_t parity = (uint32_t)(it / STAGES) & 1;
+            const uint32_t parity = (it / STAGES) & 1;
             mbar_drain(bar, parity);
         }
     }
@@ -521,24 +657,24 @@ gemm_tc_persistent_kernel(const __grid_constant__ CUtensorMap map_w, const __gri
     }
 }
 
-template <int BN, int STAGES, bool DUAL>
+template <int BN, int STAGES, int MODE>
 static int launch_tc_persistent(const CUtensorMap& mw, const CUtensorMap& mx, void* C, int T, int N, int K, long long ldc,
                                 int mode, cudaStream_t s) {
-    constexpr size_t smem = (size_t)STAGES * ((DUAL ? 2 : 1) * TC_BM * TC_BK * 2 + BN * TC_BK * 2) + sizeof(TcPersistShared) + 1024;
+    constexpr size_t smem = (size_t)STAGES * ((MODE ? 2 : 1) * TC_BM * TC_BK * 2 + BN * TC_BK * 2) + sizeof(TcPersistShared) + 1024;
     static bool configured = false;
     static int sms = 0;
     if (!configured) {
-        cudaError_t e = cudaFuncSetAttribute(gemm_tc_persistent_kernel<BN, STAGES, DUAL>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        cudaError_t e = cudaFuncSetAttribute(gemm_tc_persistent_kernel<BN, STAGES, MODE>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         if (e != cudaSuccess) return (int)e;
         int dev = 0;
         cudaGetDevice(&dev);
         cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
         configured = true;
     }
-    const int t_tiles = rb_ceil_div(T, BN), n_tiles = rb_ceil_div(N, TC_BM);
+    const int t_tiles = rb_ceil_div(T, BN), n_tiles = rb_ceil_div(N, MODE == 2 ? 2 * TC_BM : TC_BM);
     const int total = t_tiles * n_tiles;
     const int grid = total < sms ? total : sms;
-    return rb_launch(gemm_tc_persistent_kernel<BN, STAGES, DUAL>, dim3(grid), dim3(TC_THREADS), smem, s, mw, mx, C, T, N, K, ldc,
+    return rb_launch(gemm_tc_persistent_kernel<BN, STAGES, MODE>, dim3(grid), dim3(TC_THREADS), smem, s, mw, mx, C, T, N, K, ldc,
                      mode, t_tiles, n_tiles);
 }
 
@@ -711,6 +847,11 @@ static int g_tc_persistent = 1;
 // Schedule of products with several token tiles: 0 = one CTA per tile, 1 = persistent CTAs.  Returns the old value.
 extern "C" int rb_set_gemm_persistent(int mode) { int old = g_tc_persistent; g_tc_persistent = mode ? 1 : 0; return old; }
 
+static int g_tc_token_lanes = -1;
+// Persistent products of several token tiles: 1 = a token per accumulator lane (128 tokens x 256 features a tile),
+// 0 = a feature per lane (128 features x 256 or 128 tokens), -1 = chosen by the output mode.  Returns the old value.
+extern "C" int rb_set_gemm_token_lanes(int v) { int old = g_tc_token_lanes; g_tc_token_lanes = v < 0 ? -1 : (v ? 1 : 0); return old; }
+
 static int tc_bn(int T) { return T <= 16 ? 16 : T <= 32 ? 32 : T <= 64 ? 64 : T <= 128 ? 128 : 256; }
 
 // The extras of a launch from the entry points' arguments (-1 and a message if they make no sense).
@@ -749,6 +890,15 @@ extern "C" int rb_gemm_bf16(const void* X, const void* W, void* C, int c_dtype, 
         // Token tiles of 256 or of 128: whichever needs less time for its rounds over the SMs.  A 128 x 128 tile
         // reads as many operand bytes from shared memory per MMA as a 128 x 256 one for half the work, so its
         // rounds count 1.36 times their width; the wider tile wins ties (the weights are read once less often).
+        // Results that are stored (not added to what is there) go out faster with a token per lane: 32 bytes of a row at
+        // a time instead of 2, which shortens the one epilogue that nothing hides, the last.  Results that are added go
+        // out as reductions of 128 contiguous bytes with a feature per lane.  rb_set_gemm_token_lanes forces one form.
+        const bool flip = g_tc_token_lanes >= 0 ? g_tc_token_lanes != 0 : mode != 2;
+        if (flip) {
+            if (rb_tensor_map_bf16(W, N, K, ldw, 256, &mw)) return -1;
+            if (rb_tensor_map_bf16(X, T, K, ldx, 128, &mx)) return -1;
+            return launch_tc_persistent<128, 4, 2>(mw, mx, C, T, N, K, ldc, mode, s);
+        }
         int dev = 0, sms = 148;
         cudaGetDevice(&dev);
         cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
@@ -757,10 +907,26 @@ extern "C" int rb_gemm_bf16(const void* X, const void* W, void* C, int c_dtype, 
         const double c128 = (double)rb_ceil_div((long long)rb_ceil_div(T, 128) * n_tiles, sms) * 128.0 * 1.36;
         if (c128 < c256) {
             if (rb_tensor_map_bf16(X, T, K, ldx, 128, &mx)) return -1;
-            return launch_tc_persistent<128, 5, false>(mw, mx, C, T, N, K, ldc, mode, s);
+            return launch_tc_persistent<128, 5, 0>(mw, mx, C, T, N, K, ldc, mode, s);
         }
+#ifdef RB_TIMELINE
+        if (const char* v = getenv("REINFER_B200_TRACE_TILE")) {     // "BN,STAGES": other pipelines, to be compared in the tile trace
+            int tb = 0, ts = 0;
+            if (sscanf(v, "%d,%d", &tb, &ts) == 2) {
+                if (rb_tensor_map_bf16(X, T, K, ldx, tb, &mx)) return -1;
+                if (tb == 256 && ts == 2) return launch_tc_persistent<256, 2, 0>(mw, mx, C, T, N, K, ldc, mode, s);
+                if (tb == 256 && ts == 3) return launch_tc_persistent<256, 3, 0>(mw, mx, C, T, N, K, ldc, mode, s);
+                if (tb == 128 && ts == 3) return launch_tc_persistent<128, 3, 0>(mw, mx, C, T, N, K, ldc, mode, s);
+                if (tb == 128 && ts == 4) return launch_tc_persistent<128, 4, 0>(mw, mx, C, T, N, K, ldc, mode, s);
+                if (tb == 128 && ts == 6) return launch_tc_persistent<128, 6, 0>(mw, mx, C, T, N, K, ldc, mode, s);
+                if (tb == 64 && ts == 4) return launch_tc_persistent<64, 4, 0>(mw, mx, C, T, N, K, ldc, mode, s);
+                if (tb == 64 && ts == 8) return launch_tc_persistent<64, 8, 0>(mw, mx, C, T, N, K, ldc, mode, s);
+                RB_REFUSE("REINFER_B200_TRACE_TILE=%s is not instantiated", v);
+            }
+        }
+#endif
         if (rb_tensor_map_bf16(X, T, K, ldx, 256, &mx)) return -1;
-        return launch_tc_persistent<256, 4, false>(mw, mx, C, T, N, K, ldc, mode, s);
+        return launch_tc_persistent<256, 4, 0>(mw, mx, C, T, N, K, ldc, mode, s);
     }
     if (rb_tensor_map_bf16(X, T, K, ldx, bn, &mx)) return -1;
     switch (bn) {
@@ -843,7 +1009,7 @@ extern "C" int rb_gemm_bf16_swiglu(const void* X, const void* Wgu, void* act, in
     if (rb_tensor_map_bf16(Wgu, 2LL * F, K, ldw, TC_BM, &mw)) return -1;
     if (T > 256 && g_tc_persistent) {                               // two accumulators x two stages: 128-token tiles
         if (rb_tensor_map_bf16(X, T, K, ldx, 128, &mx)) return -1;
-        return launch_tc_persistent<128, 4, true>(mw, mx, act, T, F, K, ldc, 0, s);
+        return launch_tc_persistent<128, 4, 1>(mw, mx, act, T, F, K, ldc, 0, s);
     }
     if (rb_tensor_map_bf16(X, T, K, ldx, bn, &mx)) return -1;
     switch (bn) {

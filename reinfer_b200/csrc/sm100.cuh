@@ -58,6 +58,20 @@ __device__ __forceinline__ bool mbar_try(uint32_t bar, uint32_t parity) {
         : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
     return ok != 0;
 }
+// *p += v in global memory with nothing coming back.
+__device__ __forceinline__ void red_add_f32(float* p, float v) {
+    asm volatile("red.global.add.f32 [%0], %1;" ::"l"(p), "f"(v) : "memory");
+}
+// A look at the barrier that never suspends the thread (try_wait may, for a while, when the phase is not complete).
+__device__ __forceinline__ bool mbar_test(uint32_t bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
+    return ok != 0;
+}
 // Bounded wait: gives up after RB_WAIT_NS nanoseconds of the global timer (or RB_SPIN_LIMIT polls,
 // whichever comes first).  Returns false if the CTA is aborting, or if this wait gave up - then it
 // raises the CTA's abort flag and records where in the error word.
@@ -124,6 +138,38 @@ __device__ __forceinline__ void tc_mma_bf16(uint32_t tmem_d, uint64_t desc_a, ui
         "setp.ne.b32 p, %4, 0;\n\t"
         "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
         ::"r"(tmem_d), "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate) : "memory");
+}
+// Forms for a warp that stays converged and lets one lane issue (lead != 0 in that lane only).  A warp whose issuing
+// lane runs alone inside a branch pays for it at every asynchronous instruction: measured on the persistent product,
+// about a hundred cycles for each tcgen05.mma, tcgen05.commit and TMA request, whatever its size.
+__device__ __forceinline__ void tc_mma_bf16_lead(uint32_t tmem_d, uint64_t desc_a, uint64_t desc_b, uint32_t idesc, uint32_t accumulate, uint32_t lead) {
+    asm volatile(
+        "{\n\t.reg .pred p, q;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "setp.ne.b32 q, %5, 0;\n\t"
+        "@q tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+        ::"r"(tmem_d), "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate), "r"(lead) : "memory");
+}
+__device__ __forceinline__ void tc_commit_lead(uint32_t bar, uint32_t lead) {
+    asm volatile(
+        "{\n\t.reg .pred q;\n\t"
+        "setp.ne.b32 q, %1, 0;\n\t"
+        "@q tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];\n\t}"
+        ::"r"(bar), "r"(lead) : "memory");
+}
+__device__ __forceinline__ void tma_load_2d_lead(uint32_t dst, const CUtensorMap* map, int x, int y, uint32_t bar, uint32_t lead) {
+    asm volatile(
+        "{\n\t.reg .pred q;\n\t"
+        "setp.ne.b32 q, %5, 0;\n\t"
+        "@q cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];\n\t}"
+        ::"r"(dst), "l"(map), "r"(x), "r"(y), "r"(bar), "r"(lead) : "memory");
+}
+__device__ __forceinline__ void mbar_expect_tx_lead(uint32_t bar, uint32_t bytes, uint32_t lead) {
+    asm volatile(
+        "{\n\t.reg .pred q;\n\t"
+        "setp.ne.b32 q, %2, 0;\n\t"
+        "@q mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;\n\t}"
+        ::"r"(bar), "r"(bytes), "r"(lead) : "memory");
 }
 __device__ __forceinline__ void tc_ld16(uint32_t taddr, uint32_t* r) {
     asm volatile(

@@ -44,6 +44,9 @@ def lib():
         if os.environ.get("REINFER_B200_GEMM_SCHEDULE"):
             # 0: one CTA per tile, 1: persistent CTAs (default) for prompt portions
             _lib.rb_set_gemm_persistent(int(os.environ["REINFER_B200_GEMM_SCHEDULE"]))
+        if os.environ.get("REINFER_B200_GEMM_TOKEN_LANES"):
+            # prompt portions: 1 a token per accumulator lane, 0 a feature per lane; default by the output mode
+            _lib.rb_set_gemm_token_lanes(int(os.environ["REINFER_B200_GEMM_TOKEN_LANES"]))
         if os.environ.get("REINFER_B200_PDL", "1") == "0":
             _lib.rb_set_pdl(0)          # launch every kernel fully serialised (for comparisons)
     return _lib
@@ -541,6 +544,13 @@ def sample_slots(logits: torch.Tensor, row_slot: torch.Tensor, slot_params: torc
 
 _gemm_ws = None
 GEMM_WS_FLOATS = 8 << 20          # 32 MB of split-K partials
+
+
+def set_gemm_token_lanes(value: int) -> int:
+    """Which form the tensor-core product over several token tiles takes: 1 a token per accumulator lane, 0 a
+    feature per lane, -1 chosen by the output mode (stored results: tokens; added results: features).  Returns the
+    old setting; for tests and comparisons."""
+    return int(lib().rb_set_gemm_token_lanes(c_int(int(value))))
 
 
 def gemm_bf16(a: torch.Tensor, w: torch.Tensor, c: torch.Tensor, accumulate: bool = False, splits: int = 0,

@@ -60,12 +60,22 @@ def test_gemm_swiglu_epilogue(T, F, K):
 
 @pytest.mark.parametrize("T,N,K", [(257, 256, 64), (300, 700, 320), (1000, 130, 520), (2048, 4096, 1024), (777, 1000, 4104),
                                    (513, 384, 8192)])
-def test_gemm_over_many_token_tiles_to_the_roundings_own_width(T, N, K):
+@pytest.mark.parametrize("token_lanes", [-1, 0, 1])
+def test_gemm_over_many_token_tiles_to_the_roundings_own_width(T, N, K, token_lanes):
     """Prompt portions run persistent CTAs over the output tiles.  Sizes with ragged edges in every direction, every
-    output mode and the SwiGLU epilogue, held to what the arithmetic allows: a float32 result to the accumulation's
-    rounding, a bfloat16 result to one rounding to bfloat16 (4e-3 of the scale) - a wrong 16-column step of K, one of
-    K / 16, moves a result by about sqrt(16 / K) of the scale (6 % at K = 4,096) and would show."""
+    output mode and the SwiGLU epilogue, in both forms of the kernel (a feature or a token per accumulator lane; -1:
+    the form that serving takes for each output mode), held to what the arithmetic allows: a float32 result to the
+    accumulation's rounding, a bfloat16 result to one rounding to bfloat16 (4e-3 of the scale) - a wrong 16-column
+    step of K, one of K / 16, moves a result by about sqrt(16 / K) of the scale (6 % at K = 4,096) and would show."""
     from reinfer_b200 import ops
+    old = ops.set_gemm_token_lanes(token_lanes)
+    try:
+        _many_token_tiles(ops, T, N, K)
+    finally:
+        ops.set_gemm_token_lanes(old)
+
+
+def _many_token_tiles(ops, T, N, K):
     a = rnd(T, K, dtype=torch.bfloat16, seed=1)
     w = rnd(N, K, dtype=torch.bfloat16, scale=0.05, seed=2)
     ref = a.float() @ w.float().t()
