@@ -111,8 +111,11 @@ fa_decode_tma_kernel(const __grid_constant__ CUtensorMap map_kv, const FtArgs a)
     // The step's tables (lengths, block table) were complete before its first kernel began, and the keys of
     // earlier positions were written by earlier steps: both may be read while the kernels before this one still
     // run.  Only the query rows and the new token's key and value wait for them.
-    const int e = a.first_entry + blockIdx.x;
-    const int kh = blockIdx.y / a.chunks, chunk = blockIdx.y % a.chunks;
+    // CTAs start in the order of their linear index: x (the kv head and chunk) fastest, then y (the entry).  A caller
+    // that names its longest requests first thus has the CTAs with most keys begin first and the short ones fill
+    // the slots as they come free - which is what balances a batch of unequal lengths.
+    const int e = a.first_entry + blockIdx.y;
+    const int kh = blockIdx.x / a.chunks, chunk = blockIdx.x % a.chunks;
     const int head0 = kh * (a.QH / a.KH) + chunk * a.Gc;
     const int split = blockIdx.z;
     const int kv_end = a.kv_len[e];
@@ -720,6 +723,41 @@ __global__ void ft_merge_kernel(const float* __restrict__ part_o, const float* _
     }
 }
 
+#define FT_MAX_CLUSTER 16                   // splits that merge themselves inside one cluster
+template <int HALVES, int NST>
+constexpr size_t ft_decode_smem() {
+    return (size_t)NST * 2 * HALVES * FT_HALF_BYTES + HALVES * 16 * 128 + 256 +
+           (size_t)(16 * HALVES * 64 + 128 + FT_MAX_CLUSTER * 16) * sizeof(float) + 1024;
+}
+
+// How many CTAs of the decode kernel for this head size can be resident at once as clusters of n (0: such clusters
+// cannot be launched here).
+template <int HALVES, int NST, bool P5>
+static int ft_cluster_slots(int n) {
+    constexpr size_t smem = ft_decode_smem<HALVES, NST>();
+    if (cudaFuncSetAttribute(fa_decode_tma_kernel<HALVES, NST, P5>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess ||
+        cudaFuncSetAttribute(fa_decode_tma_kernel<HALVES, NST, P5>, cudaFuncAttributeNonPortableClusterSizeAllowed, 1) != cudaSuccess) {
+        (void)cudaGetLastError();
+        return 0;
+    }
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(1, 1, n); cfg.blockDim = dim3(FT_THREADS); cfg.dynamicSmemBytes = smem;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = 1; attr[0].val.clusterDim.y = 1; attr[0].val.clusterDim.z = n;
+    cfg.attrs = attr; cfg.numAttrs = 1;
+    int clusters = 0;
+    if (cudaOccupancyMaxActiveClusters(&clusters, fa_decode_tma_kernel<HALVES, NST, P5>, &cfg) != cudaSuccess) { (void)cudaGetLastError(); return 0; }
+    return clusters * n;
+}
+extern "C" int rb_fa_decode_cluster_slots(int d, int n) {
+    if (n < 2 || n > FT_MAX_CLUSTER) return 0;
+    if (d == 128) return ft_cluster_slots<2, 3, true>(n);
+    if (d <= 64) return ft_cluster_slots<1, 4, false>(n);
+    if (d <= 128) return ft_cluster_slots<2, 3, false>(n);
+    return ft_cluster_slots<4, 2, false>(n);
+}
+
 template <int HALVES, int NST, bool P5 = false>
 static int ft_launch(const CUtensorMap& map, const FtArgs& a, cudaStream_t s) {
     constexpr size_t pipe = (size_t)NST * 2 * HALVES * FT_HALF_BYTES;
@@ -727,14 +765,17 @@ static int ft_launch(const CUtensorMap& map, const FtArgs& a, cudaStream_t s) {
     static_assert(merge <= pipe, "the merge buffers reuse the stages");
     static_assert(sizeof(FtShared) <= 256, "the cluster's receive buffers start 256 bytes behind the barriers");
     // stages, Q, barriers, and what the other splits of a cluster send: [split][Gc][dq] results + [split][16] log-sum-exps
-    constexpr size_t smem = pipe + HALVES * 16 * 128 + 256 + (size_t)(16 * HALVES * 64 + 128 + 8 * 16) * sizeof(float) + 1024;
+    constexpr size_t smem = ft_decode_smem<HALVES, NST>();
     static bool done = false;
     if (!done) {
         cudaError_t e = cudaFuncSetAttribute(fa_decode_tma_kernel<HALVES, NST, P5>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         if (e != cudaSuccess) return (int)e;
+        // clusters of more than 8 CTAs (up to 16 splits merge themselves) are not portable: the kernel has to allow them
+        e = cudaFuncSetAttribute(fa_decode_tma_kernel<HALVES, NST, P5>, cudaFuncAttributeNonPortableClusterSizeAllowed, 1);
+        if (e != cudaSuccess) return (int)e;
         done = true;
     }
-    const dim3 grid(a.n_entries, a.KH * a.chunks, a.n_splits);
+    const dim3 grid(a.KH * a.chunks, a.n_entries, a.n_splits);
     if (a.cluster_merge)
         return rb_launch_cluster(fa_decode_tma_kernel<HALVES, NST, P5>, grid, dim3(FT_THREADS), dim3(1, 1, a.n_splits), smem, s, map, a);
     return rb_launch(fa_decode_tma_kernel<HALVES, NST, P5>, grid, dim3(FT_THREADS), smem, s, map, a);
@@ -753,9 +794,10 @@ extern "C" int rb_fa_decode_tma(const void* q, const void* cache, long long num_
     for (int s = 3; s < 16; ++s) if ((1 << s) == page_size) shift = s;
     if (shift < 0) RB_REFUSE("attention (TMA): page size %d is not a power of two >= 8", page_size);
     if (n_splits < 1 || n_splits > 65535) RB_REFUSE("attention: %d splits", n_splits);
-    // up to 8 splits are the CTAs of a cluster, which merge their results themselves; more go through scratch and a merge kernel
+    if (n_entries > 65535) RB_REFUSE("attention: %d decoding entries in one launch (at most 65535)", n_entries);
+    // up to 16 splits are the CTAs of a cluster, which merge their results themselves; more go through scratch and a merge kernel
     static const char* cl_env = getenv("REINFER_B200_ATTN_CLUSTER");                // "0": always the merge kernel (for comparison)
-    const bool cluster_merge = n_splits >= 2 && n_splits <= 8 && !(cl_env && cl_env[0] == '0') && part_o == nullptr;
+    const bool cluster_merge = n_splits >= 2 && n_splits <= FT_MAX_CLUSTER && n_splits <= d && !(cl_env && cl_env[0] == '0') && part_o == nullptr;
     if (n_splits > 1 && !cluster_merge && (!part_o || !part_lse)) RB_REFUSE("attention: decoding in %d splits needs its scratch", n_splits);
     if (((uintptr_t)cache & 15) || ((uintptr_t)q & 15)) RB_REFUSE("attention (TMA): operands must be 16-byte aligned");
     FtArgs a{};

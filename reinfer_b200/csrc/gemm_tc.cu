@@ -374,23 +374,26 @@ struct TcPersistShared {
     int abort_flag;
 };
 
-template <int BN, int STAGES, int MODE>
+template <int BN, int STAGES, int MODE, int ROWS = 2 * TC_BM>
 __global__ void __launch_bounds__(TC_THREADS, 1)
 gemm_tc_persistent_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_x,
                           void* __restrict__ C, int T, int N, int K, long long ldc, int out_mode, int t_tiles, int n_tiles) {
     // MODE 0: a tile is 128 features (the M operand) x BN tokens.  MODE 1 (the gated pair) and MODE 2: a tile is 128
-    // tokens (the M operand) x 256 weight rows (the N operand): 128 gate rows and the 128 up rows of the same features,
-    // or 256 features.  A lane of the accumulator is then a token, and the epilogue writes 16 features of it at a time.
+    // tokens (the M operand) x ROWS weight rows (the N operand; a multiple of 32 up to 256): ROWS / 2 gate rows and the
+    // ROWS / 2 up rows of the same features, or ROWS features.  A lane of the accumulator is then a token, and the
+    // epilogue writes 16 features of it at a time.  Fewer rows leave room for a stage more.
     constexpr bool DUAL = MODE == 1, FLIP = MODE != 0;
-    constexpr int FEATS = MODE == 2 ? 2 * TC_BM : TC_BM;          // features per tile
+    static_assert(ROWS % 32 == 0 && ROWS >= 32 && ROWS <= 2 * TC_BM, "rows of the N operand");
+    constexpr int FEATS = MODE == 2 ? ROWS : MODE == 1 ? ROWS / 2 : TC_BM;   // features per tile
     RB_TL(DUAL ? 9 : 8);
     extern __shared__ __align__(1024) unsigned char smem_raw[];
-    constexpr uint32_t W1_BYTES = TC_BM * TC_BK * 2;
+    constexpr uint32_t W1_BYTES = (FLIP ? ROWS / 2 : TC_BM) * TC_BK * 2;     // the gate rows (DUAL), or half of the rows
     constexpr uint32_t W_BYTES = (FLIP ? 2 : 1) * W1_BYTES;
+    static_assert(W1_BYTES % 1024 == 0, "the second box starts on a swizzle atom");
     constexpr uint32_t X_BYTES = BN * TC_BK * 2;
     constexpr uint32_t STAGE_BYTES = W_BYTES + X_BYTES;
     static_assert(!FLIP || BN == 128, "with the tokens as the M operand a tile has 128 of them");
-    constexpr uint32_t ACC_COLS = FLIP ? 2 * TC_BM : BN;          // columns of one accumulator stage
+    constexpr uint32_t ACC_COLS = FLIP ? 2 * TC_BM : BN;          // columns of one accumulator stage (ROWS of them used)
     static_assert(2 * ACC_COLS <= 512, "two accumulator stages must fit tensor memory");
     constexpr uint32_t TMEM_COLS = 2 * ACC_COLS <= 32 ? 32 : 2 * ACC_COLS <= 64 ? 64 : 2 * ACC_COLS <= 128 ? 128 : 2 * ACC_COLS <= 256 ? 256 : 512;
     unsigned char* smem = (unsigned char*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
@@ -446,7 +449,7 @@ gemm_tc_persistent_kernel(const __grid_constant__ CUtensorMap map_w, const __gri
                 const uint32_t full = full0 + 8 * s;
                 mbar_expect_tx_lead(full, STAGE_BYTES, lead);
                 const uint32_t dst = smem_base + s * STAGE_BYTES;
-                tma_load_2d_lead(dst, &map_w, kb * TC_BK, n0, full, lead);      // MODE 2: the map's box has 256 rows
+                tma_load_2d_lead(dst, &map_w, kb * TC_BK, n0, full, lead);      // MODE 2: the map's box has ROWS rows, MODE 1: ROWS / 2
                 if (DUAL) tma_load_2d_lead(dst + W1_BYTES, &map_w, kb * TC_BK, N + n0, full, lead);
                 tma_load_2d_lead(dst + W_BYTES, &map_x, kb * TC_BK, t0, full, lead);
                 ++issued;
@@ -455,7 +458,7 @@ gemm_tc_persistent_kernel(const __grid_constant__ CUtensorMap map_w, const __gri
             if (lead) TT(plocal, 7, (unsigned long long)waited);
         }
     } else if (warp == 1) {
-        constexpr uint32_t idesc = make_idesc(FLIP ? 2 * TC_BM : BN);
+        constexpr uint32_t idesc = make_idesc(FLIP ? ROWS : BN);
         const uint64_t dw0 = make_smem_desc(smem_base), dx0 = make_smem_desc(smem_base + W_BYTES);
         bool ok = true;
         uint32_t s = 0, ph = 0;
@@ -529,15 +532,15 @@ gemm_tc_persistent_kernel(const __grid_constant__ CUtensorMap map_w, const __gri
             tc_fence_after();
             const uint32_t acc = tmem + ((uint32_t)(q * 32) << 16) + (uint32_t)a * ACC_COLS;
             if (DUAL) {
-                // a lane is a token; columns 0..127 hold its gate features, 128..255 the up features of the same tile
+                // a lane is a token; columns 0..FEATS-1 hold its gate features, the next FEATS the up features of the same tile
                 const int tok = t0 + q * 32 + lane;
                 bf16* row = (bf16*)C + (size_t)tok * ldc + n0;
 #pragma unroll 1
-                for (int c0 = 0; c0 < TC_BM; c0 += 16) {
+                for (int c0 = 0; c0 < FEATS; c0 += 16) {
                     if (n0 + c0 >= N) break;
                     uint32_t r[16], r2[16];
                     tc_ld16(acc + (uint32_t)c0, r);
-                    tc_ld16(acc + (uint32_t)(TC_BM + c0), r2);
+                    tc_ld16(acc + (uint32_t)(FEATS + c0), r2);
                     tc_ld_wait();
                     if (tok < T) {
                         uint32_t o[8];
@@ -589,13 +592,13 @@ gemm_tc_persistent_kernel(const __grid_constant__ CUtensorMap map_w, const __gri
                     } else {
                         float* row = (float*)C + (size_t)tok * ldc + n0 + c0;
                         if (vec4 && whole) {
-                            float4 v[4];
 #pragma unroll
-                            for (int j = 0; j < 4; ++j) v[j] = out_mode == 2 ? *(const float4*)(row + 4 * j) : make_float4(0.f, 0.f, 0.f, 0.f);
-#pragma unroll
-                            for (int j = 0; j < 4; ++j)
-                                *(float4*)(row + 4 * j) = make_float4(v[j].x + __uint_as_float(r[4 * j]), v[j].y + __uint_as_float(r[4 * j + 1]),
-                                                                      v[j].z + __uint_as_float(r[4 * j + 2]), v[j].w + __uint_as_float(r[4 * j + 3]));
+                            for (int j = 0; j < 4; ++j) {
+                                const float4 v = make_float4(__uint_as_float(r[4 * j]), __uint_as_float(r[4 * j + 1]),
+                                                             __uint_as_float(r[4 * j + 2]), __uint_as_float(r[4 * j + 3]));
+                                if (out_mode == 2) red_add_f32x4(row + 4 * j, v);
+                                else *(float4*)(row + 4 * j) = v;
+                            }
                         } else {
 #pragma unroll
                             for (int j = 0; j < 16; ++j)
@@ -657,24 +660,25 @@ gemm_tc_persistent_kernel(const __grid_constant__ CUtensorMap map_w, const __gri
     }
 }
 
-template <int BN, int STAGES, int MODE>
+template <int BN, int STAGES, int MODE, int ROWS = 2 * TC_BM>
 static int launch_tc_persistent(const CUtensorMap& mw, const CUtensorMap& mx, void* C, int T, int N, int K, long long ldc,
                                 int mode, cudaStream_t s) {
-    constexpr size_t smem = (size_t)STAGES * ((MODE ? 2 : 1) * TC_BM * TC_BK * 2 + BN * TC_BK * 2) + sizeof(TcPersistShared) + 1024;
+    constexpr size_t smem = (size_t)STAGES * ((MODE ? ROWS : TC_BM) * TC_BK * 2 + BN * TC_BK * 2) + sizeof(TcPersistShared) + 1024;
+    static_assert(smem <= 232448, "stages beyond the shared memory of an SM");
     static bool configured = false;
     static int sms = 0;
     if (!configured) {
-        cudaError_t e = cudaFuncSetAttribute(gemm_tc_persistent_kernel<BN, STAGES, MODE>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        cudaError_t e = cudaFuncSetAttribute(gemm_tc_persistent_kernel<BN, STAGES, MODE, ROWS>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         if (e != cudaSuccess) return (int)e;
         int dev = 0;
         cudaGetDevice(&dev);
         cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
         configured = true;
     }
-    const int t_tiles = rb_ceil_div(T, BN), n_tiles = rb_ceil_div(N, MODE == 2 ? 2 * TC_BM : TC_BM);
+    const int t_tiles = rb_ceil_div(T, BN), n_tiles = rb_ceil_div(N, MODE == 2 ? ROWS : MODE == 1 ? ROWS / 2 : TC_BM);
     const int total = t_tiles * n_tiles;
     const int grid = total < sms ? total : sms;
-    return rb_launch(gemm_tc_persistent_kernel<BN, STAGES, MODE>, dim3(grid), dim3(TC_THREADS), smem, s, mw, mx, C, T, N, K, ldc,
+    return rb_launch(gemm_tc_persistent_kernel<BN, STAGES, MODE, ROWS>, dim3(grid), dim3(TC_THREADS), smem, s, mw, mx, C, T, N, K, ldc,
                      mode, t_tiles, n_tiles);
 }
 
@@ -847,10 +851,18 @@ static int g_tc_persistent = 1;
 // Schedule of products with several token tiles: 0 = one CTA per tile, 1 = persistent CTAs.  Returns the old value.
 extern "C" int rb_set_gemm_persistent(int mode) { int old = g_tc_persistent; g_tc_persistent = mode ? 1 : 0; return old; }
 
-static int g_tc_token_lanes = -1;
+static int g_tc_token_lanes = 1;
 // Persistent products of several token tiles: 1 = a token per accumulator lane (128 tokens x 256 features a tile),
-// 0 = a feature per lane (128 features x 256 or 128 tokens), -1 = chosen by the output mode.  Returns the old value.
-extern "C" int rb_set_gemm_token_lanes(int v) { int old = g_tc_token_lanes; g_tc_token_lanes = v < 0 ? -1 : (v ? 1 : 0); return old; }
+// 0 = a feature per lane (128 features x 256 or 128 tokens).  Returns the old value.
+extern "C" int rb_set_gemm_token_lanes(int v) { int old = g_tc_token_lanes; g_tc_token_lanes = v ? 1 : 0; return old; }
+
+static int g_tc_tile_feats = 0;
+// Weight rows per tile of the token-lane forms: 0 = chosen per product, 256 (four stages) or 224 (five).  Returns the old value.
+extern "C" int rb_set_gemm_tile_features(int v) {
+    int old = g_tc_tile_feats;
+    g_tc_tile_feats = (v == 256 || v == 224) ? v : 0;
+    return old;
+}
 
 static int tc_bn(int T) { return T <= 16 ? 16 : T <= 32 ? 32 : T <= 64 ? 64 : T <= 128 ? 128 : 256; }
 
@@ -890,14 +902,26 @@ extern "C" int rb_gemm_bf16(const void* X, const void* W, void* C, int c_dtype, 
         // Token tiles of 256 or of 128: whichever needs less time for its rounds over the SMs.  A 128 x 128 tile
         // reads as many operand bytes from shared memory per MMA as a 128 x 256 one for half the work, so its
         // rounds count 1.36 times their width; the wider tile wins ties (the weights are read once less often).
-        // Results that are stored (not added to what is there) go out faster with a token per lane: 32 bytes of a row at
-        // a time instead of 2, which shortens the one epilogue that nothing hides, the last.  Results that are added go
-        // out as reductions of 128 contiguous bytes with a feature per lane.  rb_set_gemm_token_lanes forces one form.
-        const bool flip = g_tc_token_lanes >= 0 ? g_tc_token_lanes != 0 : mode != 2;
+        // A token per accumulator lane (128 tokens x 256 features a tile): a lane writes 32 bytes of its row at a time
+        // (stored results) or adds 16 bytes at a time where they live (added results), which keeps the one epilogue that
+        // nothing hides, the last, short.  rb_set_gemm_token_lanes(0) runs the form with a feature per lane instead.
+        const bool flip = g_tc_token_lanes != 0;
         if (flip) {
-            if (rb_tensor_map_bf16(W, N, K, ldw, 256, &mw)) return -1;
+            // 256 features a tile in four stages, or 224 in five: a 64-deep k-step costs a tile about 600 cycles with
+            // four stages in flight whatever its width (the operands' latency sets the pace, not their bytes) and about
+            // 500 with five (then issuing the step's products does); the narrower tile wins where its count does not
+            // add a round over the SMs.
+            int dev = 0, sms = 148;
+            cudaGetDevice(&dev);
+            cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+            const int t_tiles = rb_ceil_div(T, 128);
+            const double c256 = 600.0 * rb_ceil_div((long long)rb_ceil_div(N, 256) * t_tiles, sms);
+            const double c224 = 500.0 * rb_ceil_div((long long)rb_ceil_div(N, 224) * t_tiles, sms);
+            const bool narrow = g_tc_tile_feats ? g_tc_tile_feats == 224 : c224 < c256;
+            if (rb_tensor_map_bf16(W, N, K, ldw, narrow ? 224 : 256, &mw)) return -1;
             if (rb_tensor_map_bf16(X, T, K, ldx, 128, &mx)) return -1;
-            return launch_tc_persistent<128, 4, 2>(mw, mx, C, T, N, K, ldc, mode, s);
+            if (narrow) return launch_tc_persistent<128, 5, 2, 224>(mw, mx, C, T, N, K, ldc, mode, s);
+            return launch_tc_persistent<128, 4, 2, 256>(mw, mx, C, T, N, K, ldc, mode, s);
         }
         int dev = 0, sms = 148;
         cudaGetDevice(&dev);
@@ -1007,9 +1031,10 @@ extern "C" int rb_gemm_bf16_swiglu(const void* X, const void* Wgu, void* act, in
     const int bn = tc_bn(T);
     CUtensorMap mw, mx;
     if (rb_tensor_map_bf16(Wgu, 2LL * F, K, ldw, TC_BM, &mw)) return -1;
-    if (T > 256 && g_tc_persistent) {                               // two accumulators x two stages: 128-token tiles
+    if (T > 256 && g_tc_persistent) {                               // tiles of 128 tokens x (128 gate + 128 up) weight rows
+        // (112 + 112 rows in five stages were measured too: 292 against 290 us at the 8B shape, 154 against 149 at 4B)
         if (rb_tensor_map_bf16(X, T, K, ldx, 128, &mx)) return -1;
-        return launch_tc_persistent<128, 4, 1>(mw, mx, act, T, F, K, ldc, 0, s);
+        return launch_tc_persistent<128, 4, 1, 256>(mw, mx, act, T, F, K, ldc, 0, s);
     }
     if (rb_tensor_map_bf16(X, T, K, ldx, bn, &mx)) return -1;
     switch (bn) {

@@ -224,7 +224,12 @@ class Engine:
         width = 8
         while width < need_pages:
             width *= 2
-        return bucket, width
+        # how full the batch's block tables are, in eighths: requests of unequal lengths want their keys split
+        # over more CTAs than the longest alone would suggest, and a captured step keeps the split it was made with
+        total = sum(-(-((self.cache.length(e.request_id) if e.request_id in self.cache else 0) + 1) // 64) for e in entries)
+        widest = max(1, width * self.page_size // 64)
+        fill = min(FILL_STEPS, max(1, (2 * FILL_STEPS * total + B * widest) // (2 * B * widest)))
+        return bucket, width, fill
 
     def _step_graph(self, entries: Sequence[StepEntry], logits: bool = True) -> Optional[torch.Tensor]:
         """A step of single tokens only: fill the graph's static tables and replay it."""
@@ -238,7 +243,7 @@ class Engine:
         if g is None:
             while len(self._graphs) >= MAX_GRAPHS:      # the one replayed longest ago goes (its memory returns to the pool)
                 self._graphs.pop(next(iter(self._graphs)))
-            g = _DecodeGraph(self, key[0], key[1])
+            g = _DecodeGraph(self, key[0], key[1], key[2])
         self._graphs[key] = g                           # most recently used last
         self._staging.upload(host, self.device, into=g.meta)
         g.graph.replay()
@@ -413,6 +418,9 @@ class Engine:
         dev = self._staging.upload(host, self.device)
         ctx = self._context(dev, off, T, E, n_decode, max_pages, [int(v) for v in q_start], list(start), slots,
                             max(q_len), max(s + n for s, n in zip(start, q_len)))
+        if n_decode:
+            tiles = [-(-(s + 1) // 64) for s in start[:n_decode]]
+            ctx.decode_kv_tiles = (sum(tiles), max(tiles))
         o, n = off["want_rows"]
         return ctx, (dev[o:o + n] if R else None), lens_after
 
@@ -465,7 +473,8 @@ class Engine:
 
 
 MAX_GRAPH_BATCH = 256
-MAX_GRAPHS = 24             # captured decode steps kept at a time (one per batch bucket and block-table width in use)
+MAX_GRAPHS = 24
+FILL_STEPS = 8                          # a captured decode step is made for block tables filled to so many eighths             # captured decode steps kept at a time (one per batch bucket and block-table width in use)
 
 
 class _DecodeGraph:
@@ -473,7 +482,7 @@ class _DecodeGraph:
     Its tables live in `meta` (a static int32 block the engine refills before every replay); its
     logits [batch, vocab] in `logits`."""
 
-    def __init__(self, engine: "Engine", batch: int, width: int):
+    def __init__(self, engine: "Engine", batch: int, width: int, fill: int = FILL_STEPS):
         n_groups = len(engine.cache.groups)
         off, total = Engine._layout(batch, batch, batch, [width] * n_groups)
         host = np.zeros(total, dtype=np.int32)
@@ -489,6 +498,8 @@ class _DecodeGraph:
         self.meta = torch.from_numpy(host).to(engine.device)
         ctx = engine._context(self.meta, off, batch, batch, batch, [width] * n_groups, list(range(batch + 1)),
                               [0] * batch, [inert] * batch, 1, width * engine.page_size)
+        widest = max(1, width * engine.page_size // 64)
+        ctx.decode_kv_tiles = (max(batch, batch * widest * fill // FILL_STEPS), widest)     # block tables filled to `fill` eighths
         o, n = off["want_rows"]
         want = self.meta[o:o + n]
         def run():

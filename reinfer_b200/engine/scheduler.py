@@ -198,7 +198,9 @@ class Scheduler:
                     preempted.append(v)
                 continue
             free = cm.free_pages()
-            for r in decoding[:budget]:
+            # who decodes is decided by arrival; in the batch they stand longest first (the attention kernel starts
+            # its CTAs in the order of the entries, and the ones with most keys should begin first)
+            for r in sorted(decoding[:budget], key=lambda r: (-r.num_computed, r.arrival)):
                 free -= pages_more(r, r.num_computed + 1)
                 batch.append(Scheduled(r, r.num_computed, r.tokens_from(r.num_computed, 1), True))
                 budget -= 1

@@ -45,8 +45,11 @@ def lib():
             # 0: one CTA per tile, 1: persistent CTAs (default) for prompt portions
             _lib.rb_set_gemm_persistent(int(os.environ["REINFER_B200_GEMM_SCHEDULE"]))
         if os.environ.get("REINFER_B200_GEMM_TOKEN_LANES"):
-            # prompt portions: 1 a token per accumulator lane, 0 a feature per lane; default by the output mode
+            # prompt portions: 1 a token per accumulator lane (default), 0 a feature per lane
             _lib.rb_set_gemm_token_lanes(int(os.environ["REINFER_B200_GEMM_TOKEN_LANES"]))
+        if os.environ.get("REINFER_B200_GEMM_TILE_ROWS"):
+            # prompt portions: 256 or 224 weight rows a tile; default chosen per product
+            _lib.rb_set_gemm_tile_features(int(os.environ["REINFER_B200_GEMM_TILE_ROWS"]))
         if os.environ.get("REINFER_B200_PDL", "1") == "0":
             _lib.rb_set_pdl(0)          # launch every kernel fully serialised (for comparisons)
     return _lib
@@ -378,17 +381,30 @@ def _next_range(t: Optional[torch.Tensor], marker: int = 0):
 
 
 DECODE_SLOTS = 296                          # CTAs of the decode attention that are resident at once (two per SM)
+MAX_CLUSTER_SPLITS = 16                     # splits that can merge inside one cluster (more than 8: not portable, asked of the device)
+_cluster_slots: dict = {}
+
+
+def decode_cluster_slots(d: int, n: int) -> int:
+    """CTAs of the decode attention that can be resident at once as clusters of n: the fixed figure for portable
+    clusters, what the device's occupancy calculation says for larger ones (0: cannot be launched)."""
+    if n <= 8:
+        return DECODE_SLOTS
+    key = (d, n)
+    if key not in _cluster_slots:
+        _cluster_slots[key] = min(DECODE_SLOTS, int(lib().rb_fa_decode_cluster_slots(c_int(d), c_int(n))))
+    return _cluster_slots[key]
 
 
 def fa_decode_tma(q, cache, block_table, cu_q, kv_len, out, first_entry: int, n_entries: int, first_tok: int, n_splits: int,
                   QH: int, KH: int, d: int, page_size: int, window: int, scale: float, work=(0.0, 0.0)) -> None:
     """Split-K flash decoding with the key/value tiles brought in by TMA (page size a power of two >= 8).
-    Up to 8 splits whose CTAs are all resident at once form clusters that merge their results themselves (no scratch,
+    Up to 16 splits whose CTAs are all resident at once form clusters that merge their results themselves (no scratch,
     no merge kernel); several waves of CTAs, or more splits, go through scratch and the merge kernel (clusters
     that wait for a free place on one GPC were measured slower there)."""
     part_o = part_lse = None
     ctas = n_entries * KH * (QH // KH // fa_group_chunk(QH // KH)) * n_splits
-    in_kernel = ATTN_CLUSTER_MERGE and 2 <= n_splits <= 8 and ctas <= DECODE_SLOTS
+    in_kernel = ATTN_CLUSTER_MERGE and 2 <= n_splits <= min(MAX_CLUSTER_SPLITS, d) and ctas <= decode_cluster_slots(d, n_splits)
     if n_splits > 1 and not in_kernel:
         part_o = torch.empty(n_entries * QH * n_splits * d, dtype=torch.float32, device=q.device)
         part_lse = torch.empty(n_entries * QH * n_splits, dtype=torch.float32, device=q.device)
@@ -436,30 +452,41 @@ def fa_prefill(q, cache, block_table, cu_q, kv_len, out, first_entry: int, n_ent
 USE_TMA_ATTENTION = os.environ.get("REINFER_B200_TMA_ATTENTION", "1") != "0"
 ATTN_CLUSTER_MERGE = os.environ.get("REINFER_B200_ATTN_CLUSTER", "1") != "0"
 USE_TC_ATTENTION = os.environ.get("REINFER_B200_TC_ATTENTION", "1") != "0"
-def decode_splits(ctas: int, tiles: int, slots: int = DECODE_SLOTS, head_dim: int = 128) -> int:
+def decode_splits(ctas: int, tiles: int, slots: int = DECODE_SLOTS, head_dim: int = 128, cluster_slots=None,
+                  total_tiles: Optional[int] = None) -> int:
     """How many CTAs share one (request, kv head)'s keys: the split count with the least estimated time (ties to
-    the smaller).  The estimate is fitted to measurements of the kernel at batch 1..64 and 4k..32k keys, alone
-    and inside whole decode steps:
+    the smaller).  `ctas` (request, kv head) pairs, the longest of `tiles` 64-key tiles, `total_tiles` over all pairs
+    (default: all as long as the longest).  The estimate is fitted to measurements of the kernel at batch 1..64 and
+    4k..32k keys, alone and inside whole decode steps:
       - every resident CTA has the first three tiles of its share on their way before the kernels in front of it
         have finished; what is left streams at the memory bandwidth, less what the CTAs' fill and drain cost,
         which weighs the more the fewer tiles a CTA walks:   bytes left / 6.5 TB/s * (1 + 2.7 / tiles per CTA)
       - a CTA alone streams a 64-key tile of 128-wide heads in about a microsecond and needs about five to start
-        and finish:                                           (tiles per CTA - 3) * 1 us + 5 us
-      - the larger of the two counts, plus the merge: about 2 us inside a cluster (up to 8 splits, all CTAs
-        resident at once), else a merge kernel of about 3.5 us + 0.1 us per split.
+        and finish; the kernel lasts as long as the CTA with most tiles:   (most tiles per CTA - 3) * 1 us + 5 us
+        (requests of unequal lengths: the longest alone decides this term, so splitting pays although the
+        CTAs then come in several waves)
+      - the larger of the two counts, plus the merge: about 2 us inside a cluster (up to 16 splits, all CTAs
+        resident at once: `cluster_slots(n)` says how many CTAs that is for clusters of more than 8), else a merge
+        kernel of about 3.5 us + 0.1 us per split.
     (Whole "waves" of CTAs do not matter: a part-filled last wave just gives its CTAs more bandwidth each.)"""
+    if cluster_slots is None:
+        cluster_slots = lambda n: decode_cluster_slots(head_dim, n)
+    if total_tiles is None:
+        total_tiles = ctas * tiles
+    total_tiles = max(min(total_tiles, ctas * tiles), 1)
     tile_us = head_dim / 128.0                              # a lone CTA's time for one tile
     tile_bw_us = 64 * head_dim * 4 / 6.5e6                  # one tile's bytes at the device's bandwidth
     ahead = 3                                               # tiles a CTA requests before it has to wait
     best, best_cost = 1, None
     for n in range(1, max(1, min(64, tiles)) + 1):
-        per = -(-tiles // n)
-        early = min(ctas * tiles, min(ctas * n, slots) * ahead)
-        t_bw = (ctas * tiles - early) * tile_bw_us * (1.0 + 2.7 / per)
+        per = -(-tiles // n)                                # the longest request's CTAs
+        per_avg = max(total_tiles / (ctas * n), 1.0)
+        early = min(total_tiles, min(ctas * n, slots) * ahead)
+        t_bw = (total_tiles - early) * tile_bw_us * (1.0 + 2.7 / per_avg)
         t_lat = max(0, per - ahead) * tile_us + 5.0
         if n == 1:
             merge = 0.0
-        elif n <= 8 and ctas * n <= slots and ATTN_CLUSTER_MERGE:
+        elif n <= min(MAX_CLUSTER_SPLITS, head_dim) and ATTN_CLUSTER_MERGE and ctas * n <= (slots if n <= 8 else min(slots, cluster_slots(n))):
             merge = 2.0
         else:
             merge = 3.5 + 0.1 * n
@@ -500,7 +527,9 @@ def attention(ctx, q: torch.Tensor, cache: torch.Tensor, group, out: torch.Tenso
     if n_dec:
         ctas = n_dec * KH * (QH // KH // gc)
         tiles = -(-ctx.max_kv_len // 64)
-        n_splits = decode_splits(ctas, tiles, head_dim=d)
+        pairs = KH * (QH // KH // gc)
+        total = ctx.decode_kv_tiles[0] * pairs if ctx.decode_kv_tiles else None
+        n_splits = decode_splits(ctas, tiles, head_dim=d, total_tiles=total)
         decode = fa_decode_tma if (tma_pages(group.page_size) and USE_TMA_ATTENTION) else fa_decode
         decode(q, cache, group.block_table, ctx.cu_q, ctx.kv_len, out, 0, n_dec, 0, n_splits, QH, KH, d,
                group.page_size, window, scale, work=dec_work)
@@ -548,9 +577,15 @@ GEMM_WS_FLOATS = 8 << 20          # 32 MB of split-K partials
 
 def set_gemm_token_lanes(value: int) -> int:
     """Which form the tensor-core product over several token tiles takes: 1 a token per accumulator lane, 0 a
-    feature per lane, -1 chosen by the output mode (stored results: tokens; added results: features).  Returns the
-    old setting; for tests and comparisons."""
+    feature per lane.  Returns the old setting; for tests and comparisons."""
     return int(lib().rb_set_gemm_token_lanes(c_int(int(value))))
+
+
+def set_gemm_tile_features(value: int) -> int:
+    """Weight rows per tile of the products over several token tiles (token-lane forms): 256 (four stages in
+    flight), 224 (five), or 0 = chosen per product by the rounds its tiles need over the SMs.  Returns the old
+    setting; for tests and comparisons."""
+    return int(lib().rb_set_gemm_tile_features(c_int(int(value))))
 
 
 def gemm_bf16(a: torch.Tensor, w: torch.Tensor, c: torch.Tensor, accumulate: bool = False, splits: int = 0,

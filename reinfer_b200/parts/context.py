@@ -7,7 +7,7 @@ first.  All device tables are int32.
 from __future__ import annotations
 
 from dataclasses import dataclass, field
-from typing import Dict, List, Optional
+from typing import Tuple, Dict, List, Optional
 
 import torch
 
@@ -52,6 +52,7 @@ class StepContext:
     slots: List[int] = field(default_factory=list)        # E
     max_q_len: int = 0
     max_kv_len: int = 0
+    decode_kv_tiles: Optional[Tuple[int, int]] = None     # (sum, largest) of the decode entries' 64-key tiles; None: all as max_kv_len
     layer_caches: Dict[str, LayerCache] = field(default_factory=dict)
     shared: Dict[object, torch.Tensor] = field(default_factory=dict)   # what one layer computed for all (per step)
     defer_residual: bool = False       # parts may return what is to be added to the residual; the next norm adds it

@@ -51,21 +51,33 @@ def test_stream_chain_learns_the_order_of_a_pass_and_forgets_a_changed_one():
 
 
 def test_decode_splits_model():
-    from reinfer_b200.ops import decode_splits
+    from functools import partial
+    from reinfer_b200 import ops
+    # what the device says about clusters of more than 8 CTAs is an argument here: all slots, or none
+    decode_splits = partial(ops.decode_splits, cluster_slots=lambda n: ops.DECODE_SLOTS)
+    portable_only = partial(ops.decode_splits, cluster_slots=lambda n: 0)
     # many (request, kv head) pairs: one CTA each streams at the memory bandwidth, splitting only adds fill and drain
     assert decode_splits(64 * 8, 64) == 1
     assert decode_splits(32 * 8, 64) == 1
-    # few pairs: splits until enough CTAs stream; up to 8 stay inside a cluster while all are resident at once
+    # few pairs: splits until enough CTAs stream; they stay inside a cluster while all are resident at once
     assert decode_splits(16 * 8, 64) == 2
     assert decode_splits(8 * 8, 64) == 4
     assert 2 <= decode_splits(4 * 8, 64) <= 8
-    assert decode_splits(8, 64) > 8                 # one request: more splits than a cluster holds, merged by a kernel
+    # one request: as many splits as the largest cluster holds; where the device allows only portable clusters,
+    # more splits than a cluster holds, merged by a kernel
+    assert decode_splits(8, 64) == 16
+    assert portable_only(8, 64) > 8 and portable_only(8, 64) != 16
     # never more splits than tiles, never fewer than one
     for ctas in (1, 8, 64, 512, 4096):
         for tiles in (1, 2, 3, 16, 64, 512, 2048):
-            n = decode_splits(ctas, tiles)
-            assert 1 <= n <= max(1, min(64, tiles))
+            for f in (decode_splits, portable_only):
+                n = f(ctas, tiles)
+                assert 1 <= n <= max(1, min(64, tiles))
     assert decode_splits(8, 1) == 1
+    # requests of unequal lengths (32 of them, the longest 67 tiles, 36 on average): one CTA per pair would last as
+    # long as the longest request; two splits halve that although the CTAs no longer fit the device at once
+    assert decode_splits(32 * 8, 67) == 1
+    assert decode_splits(32 * 8, 67, total_tiles=32 * 8 * 36) == 2
     # wider heads: the same decisions at the same number of bytes
     assert decode_splits(64 * 8, 64, head_dim=256) == 1
 

@@ -60,19 +60,21 @@ def test_gemm_swiglu_epilogue(T, F, K):
 
 @pytest.mark.parametrize("T,N,K", [(257, 256, 64), (300, 700, 320), (1000, 130, 520), (2048, 4096, 1024), (777, 1000, 4104),
                                    (513, 384, 8192)])
-@pytest.mark.parametrize("token_lanes", [-1, 0, 1])
+@pytest.mark.parametrize("token_lanes", [0, 1, 224, 256])
 def test_gemm_over_many_token_tiles_to_the_roundings_own_width(T, N, K, token_lanes):
     """Prompt portions run persistent CTAs over the output tiles.  Sizes with ragged edges in every direction, every
-    output mode and the SwiGLU epilogue, in both forms of the kernel (a feature or a token per accumulator lane; -1:
-    the form that serving takes for each output mode), held to what the arithmetic allows: a float32 result to the
+    output mode and the SwiGLU epilogue, in both forms of the kernel (a feature or a token per accumulator lane), held to what the arithmetic allows: a float32 result to the
     accumulation's rounding, a bfloat16 result to one rounding to bfloat16 (4e-3 of the scale) - a wrong 16-column
     step of K, one of K / 16, moves a result by about sqrt(16 / K) of the scale (6 % at K = 4,096) and would show."""
     from reinfer_b200 import ops
-    old = ops.set_gemm_token_lanes(token_lanes)
+    # (values above 1: the token-lane forms with tiles of that many weight rows instead of the width the launcher picks)
+    old = ops.set_gemm_token_lanes(1 if token_lanes else 0)
+    old_feats = ops.set_gemm_tile_features(token_lanes if token_lanes > 1 else 0)
     try:
         _many_token_tiles(ops, T, N, K)
     finally:
         ops.set_gemm_token_lanes(old)
+        ops.set_gemm_tile_features(old_feats)
 
 
 def _many_token_tiles(ops, T, N, K):
@@ -547,11 +549,12 @@ def test_flash_prefill_and_decode_against_plain(QH, KH, d, page, window):
 
 
 @pytest.mark.parametrize("QH,KH,d,page", [(32, 8, 128, 64), (8, 1, 128, 16), (14, 2, 64, 8), (3, 1, 256, 64), (5, 5, 80, 32)])
-@pytest.mark.parametrize("n_splits", [2, 3, 4, 7, 8])
+@pytest.mark.parametrize("n_splits", [2, 3, 4, 7, 8, 11, 16])
 def test_flash_decode_merge_inside_the_cluster_and_by_kernel_agree(QH, KH, d, page, n_splits, monkeypatch):
-    """Up to 8 splits merge inside a cluster of CTAs, or go through scratch and the merge kernel: both add the
-    parts in ascending order with the same formulas, so the results have the same bits (requests shorter than
-    the splits, and one of a single key, included)."""
+    """Up to 16 splits merge inside a cluster of CTAs (more than 8: where the device can place such clusters and
+    all of them at once), or go through scratch and the merge kernel: both add the parts in ascending order with
+    the same formulas, so the results have the same bits (requests shorter than the splits, and one of a single
+    key, included)."""
     from reinfer_b200 import ops
     lens = [1, 37, 64, 300, 2000, 131]
     s = paged_setup(lens, [1] * len(lens), QH, KH, d, page, torch.bfloat16, seed=5)
