@@ -259,28 +259,24 @@ fa_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_kv, const FcArgs a)
                 pages[u] = (u < subs && key < kv_end) ? pg : -1;
                 n_valid += pages[u] >= 0;
             }
-            bool ok = true;
-            if (lane == 0) {
-                if (it >= FC_NST) ok = fc_wait(smem_u32(&sh->empty[s]), ((it / FC_NST) & 1) ^ 1, abort_flag, 11);
-                if (ok) {
-                    const uint32_t full = smem_u32(&sh->full[s]);
-                    mbar_expect_tx(full, (uint32_t)(n_valid * 2 * box_keys * 256));
-                    const uint32_t dst0 = stages_u + s * FC_STAGE;
+            // every lane waits, lane 0's requests take effect (a lane alone inside a branch pays for each of them)
+            const uint32_t lead = lane == 0 ? 1u : 0u;
+            if (it >= FC_NST && !fc_wait(smem_u32(&sh->empty[s]), ((it / FC_NST) & 1) ^ 1, abort_flag, 11)) break;
+            const uint32_t full = smem_u32(&sh->full[s]);
+            mbar_expect_tx_lead(full, (uint32_t)(n_valid * 2 * box_keys * 256), lead);
+            const uint32_t dst0 = stages_u + s * FC_STAGE;
 #pragma unroll
-                    for (int u = 0; u < 8; ++u) {
-                        if (pages[u] >= 0) {
-                            const int key = k0 + u * box_keys;
-                            const int grp = (key & (a.page_size - 1)) >> 3;          // first 8-key group inside the page
-                            const int j = pages[u] * 2 * a.KH + kh;                 // (page, keys, head); values: + KH
-                            const uint32_t dst = dst0 + (uint32_t)(u * (box_keys >> 3) * FC_GROUP);
-                            tma_load_5d(dst, &map_kv, 0, 0, 0, grp, j, full);
-                            tma_load_5d(dst + FC_KV_BYTES, &map_kv, 0, 0, 0, grp, j + a.KH, full);
-                        }
-                    }
-                    issued = it + 1;
+            for (int u = 0; u < 8; ++u) {
+                if (pages[u] >= 0) {
+                    const int key = k0 + u * box_keys;
+                    const int grp = (key & (a.page_size - 1)) >> 3;          // first 8-key group inside the page
+                    const int j = pages[u] * 2 * a.KH + kh;                 // (page, keys, head); values: + KH
+                    const uint32_t dst = dst0 + (uint32_t)(u * (box_keys >> 3) * FC_GROUP);
+                    tma_load_5d_lead(dst, &map_kv, 0, 0, 0, grp, j, full, lead);
+                    tma_load_5d_lead(dst + FC_KV_BYTES, &map_kv, 0, 0, 0, grp, j + a.KH, full, lead);
                 }
             }
-            if (!__shfl_sync(0xffffffffu, (int)ok, 0)) break;
+            issued = it + 1;
         }
     } else if (warp == 1) {
         // ---- issuer of the scores: every lane runs the loop, lane 0's instructions take effect ---------------------

@@ -179,37 +179,33 @@ fa_decode_tma_kernel(const __grid_constant__ CUtensorMap map_kv, const FtArgs a)
                 pages[u] = (u < subs && key < kv_end) ? pg : -1;
                 n_valid += pages[u] >= 0;
             }
-            bool ok = true;
-            if (lane == 0) {
-                if (it >= NST) ok = mbar_wait(smem_u32(&sh->empty[s]), ((it / NST) & 1) ^ 1, abort_flag, 5);
-                if (ok) {
-                    const uint32_t full = smem_u32(&sh->full[s]);
-                    mbar_expect_tx(full, (uint32_t)(n_valid * 2 * HALVES * box_rows * 128));
-                    const uint32_t dst0 = stages_u + s * STAGE;
+            // every lane waits, lane 0's requests take effect (a lane alone inside a branch pays for each of them)
+            const uint32_t lead = lane == 0 ? 1u : 0u;
+            if (it >= NST && !mbar_wait(smem_u32(&sh->empty[s]), ((it / NST) & 1) ^ 1, abort_flag, 5)) break;
+            const uint32_t full = smem_u32(&sh->full[s]);
+            mbar_expect_tx_lead(full, (uint32_t)(n_valid * 2 * HALVES * box_rows * 128), lead);
+            const uint32_t dst0 = stages_u + s * STAGE;
 #pragma unroll
-                    for (int u = 0; u < 8; ++u) {
-                        if (pages[u] >= 0) {
-                            const int key = k0 + u * box_rows;
-                            if (P5) {
-                                const int grp = (key & (a.page_size - 1)) >> 3, j = pages[u] * 2 * a.KH + kh;
-                                const uint32_t dst = dst0 + (uint32_t)(u * (box_rows >> 3) * 2048);
-                                tma_load_5d(dst, &map_kv, 0, 0, 0, grp, j, full);
-                                tma_load_5d(dst + KV_BYTES, &map_kv, 0, 0, 0, grp, j + a.KH, full);
-                            } else {
-                                const int y = pages[u] * rows_per_page2 + kh * a.page_size + (key & (a.page_size - 1));
+            for (int u = 0; u < 8; ++u) {
+                if (pages[u] >= 0) {
+                    const int key = k0 + u * box_rows;
+                    if (P5) {
+                        const int grp = (key & (a.page_size - 1)) >> 3, j = pages[u] * 2 * a.KH + kh;
+                        const uint32_t dst = dst0 + (uint32_t)(u * (box_rows >> 3) * 2048);
+                        tma_load_5d_lead(dst, &map_kv, 0, 0, 0, grp, j, full, lead);
+                        tma_load_5d_lead(dst + KV_BYTES, &map_kv, 0, 0, 0, grp, j + a.KH, full, lead);
+                    } else {
+                        const int y = pages[u] * rows_per_page2 + kh * a.page_size + (key & (a.page_size - 1));
 #pragma unroll
-                                for (int h = 0; h < HALVES; ++h) {
-                                    tma_load_2d(dst0 + h * FT_HALF_BYTES + u * box_rows * 128, &map_kv, h * 64, y, full);
-                                    tma_load_2d(dst0 + KV_BYTES + h * FT_HALF_BYTES + u * box_rows * 128, &map_kv, h * 64,
-                                                y + a.KH * a.page_size, full);
-                                }
-                            }
+                        for (int h = 0; h < HALVES; ++h) {
+                            tma_load_2d_lead(dst0 + h * FT_HALF_BYTES + u * box_rows * 128, &map_kv, h * 64, y, full, lead);
+                            tma_load_2d_lead(dst0 + KV_BYTES + h * FT_HALF_BYTES + u * box_rows * 128, &map_kv, h * 64,
+                                             y + a.KH * a.page_size, full, lead);
                         }
                     }
-                    issued = it + 1;
                 }
             }
-            if (!__shfl_sync(0xffffffffu, (int)ok, 0)) break;
+            issued = it + 1;
         }
     } else {
         // ---- consumer warps --------------------------------------------------------------------
