@@ -1,6 +1,6 @@
 """A few steps of a random-weight model for a profiler to look at:
 
-    python -m reinfer_b200.profile_step --mode decode|prefill|timeline [--shape qwen3-8b|4b|32b|<config.json>]
+    python -m reinfer_b200.profile_step --mode decode|prefill|timeline|gemm-tiles [--shape qwen3-8b|4b|32b|<config.json>]
                                         --batch B --context N [--layers L] [--steps K] [--page-size P]
 
 builds a random-weight model of the shape (reinfer_b200/shapes/, or fewer layers of it), fills B requests to N tokens, runs two
@@ -14,6 +14,10 @@ moment its wait for the kernels before it returned, and its end, by the global t
 through the CUDA graph as serving does - with programmatic dependent launch, so kernels overlap - after a
 flush of L2, and prints for every launch when its first CTA started, when its wait returned, when its last CTA
 ended, and by how much it moved the end of the step.
+
+`--mode gemm-tiles` (the same build flag) runs the four products of one layer of the shape over --prefill-tokens
+tokens and prints, for every tile a persistent CTA walks, what its issuing threads did: how long the tile's products
+took to issue, how long the issuing thread waited for operands, the producer for free stages, and the epilogue's span.
 """
 from __future__ import annotations
 
@@ -23,7 +27,7 @@ import sys
 
 def main(argv=None) -> int:
     ap = argparse.ArgumentParser(description=__doc__.split("\n\n")[0])
-    ap.add_argument("--mode", choices=["decode", "prefill", "timeline"], default="decode")
+    ap.add_argument("--mode", choices=["decode", "prefill", "timeline", "gemm-tiles"], default="decode")
     ap.add_argument("--batch", type=int, default=8)
     ap.add_argument("--context", type=int, default=4000)
     ap.add_argument("--shape", default="qwen3-8b", help="a file of reinfer_b200/shapes (qwen3-8b, 4b, 32b) or a config.json")
@@ -33,7 +37,7 @@ def main(argv=None) -> int:
     ap.add_argument("--prefill-tokens", type=int, default=2048)
     a = ap.parse_args(argv)
 
-    if a.mode == "timeline":
+    if a.mode in ("timeline", "gemm-tiles"):
         from .csrc import build                   # the flag is part of the build key: a library of its own
         if "-DRB_TIMELINE" not in build.FLAGS:
             build.FLAGS.append("-DRB_TIMELINE")
@@ -43,6 +47,8 @@ def main(argv=None) -> int:
 
     _raw, cfg, _full = measure.load_shape(a.shape, a.layers)
     a.layers = int(_raw["num_hidden_layers"])
+    if a.mode == "gemm-tiles":
+        return gemm_tiles(ops, torch, _raw, a.prefill_tokens)
     B, N = a.batch, a.context
     eng = Engine.from_config(cfg, seed=0, dtype="bfloat16", page_size=a.page_size,
                              max_tokens=B * (N + a.page_size) + 2 * a.prefill_tokens, max_num_seqs=B + 1,
@@ -73,6 +79,54 @@ def main(argv=None) -> int:
     torch.cuda.profiler.stop()
     err = ops.kernel_error()
     print(f"profiled {a.steps} {a.mode} steps, batch {B}, context {N}, layers {a.layers}; kernel error word {err}")
+    return 0 if err == 0 else 1
+
+
+def gemm_tiles(ops, torch, raw, T: int) -> int:
+    """The tile trace of the persistent products (gemm_tc.cu, rb_gemm_tile_trace): ten words per CTA and tile."""
+    import ctypes
+    lib = ops.lib()
+    if not hasattr(lib, "rb_gemm_tile_trace"):
+        print("the library was not built with -DRB_TIMELINE")
+        return 1
+    h, F = int(raw["hidden_size"]), int(raw["intermediate_size"])
+    qkv = (int(raw["num_attention_heads"]) + 2 * int(raw["num_key_value_heads"])) * int(raw["head_dim"])
+    o_in = int(raw["num_attention_heads"]) * int(raw["head_dim"])
+    CAP, W, dev = 16, 10, "cuda"
+    sms = torch.cuda.get_device_properties(0).multi_processor_count
+    print(f"tiles of the four products of a layer over {T} tokens; per local tile of a CTA (mean over the CTAs that have it):")
+    print("  product          tile  ctas  begin us  span us  k-step ns  SM MHz  issue clk/k  commit clk/k  wait operands clk/k  "
+          "producer waits clk/k  epilogue us  drained at us")
+    for name, N, K, kind in (("qkv", qkv, h, "store"), ("o", h, o_in, "add"), ("gate/up", F, h, "swiglu"), ("down", h, F, "add")):
+        x = (torch.randn(T, K, device=dev) * 0.1).bfloat16()
+        ws = [(torch.randn(2 * N if kind == "swiglu" else N, K, device=dev) * 0.02).bfloat16() for _ in range(4)]
+        c = torch.zeros(T, N, device=dev, dtype=torch.float32 if kind == "add" else torch.bfloat16)
+        go = (lambda w: ops.gemm_bf16_swiglu(x, w, c)) if kind == "swiglu" else (lambda w: ops.gemm_bf16(x, w, c, accumulate=kind == "add"))
+        for w in ws[:3]:
+            go(w)
+        torch.cuda.synchronize()
+        buf = torch.zeros(sms * CAP * W, dtype=torch.int64, device=dev)
+        lib.rb_gemm_tile_trace(ctypes.c_void_p(buf.data_ptr()), ctypes.c_int(CAP))
+        go(ws[3])
+        torch.cuda.synchronize()
+        lib.rb_gemm_tile_trace(ctypes.c_void_p(0), ctypes.c_int(0))
+        b = buf.cpu().view(sms, CAP, W).double()
+        nkb = -(-K // 64)
+        started = b[:, :, 6][b[:, :, 6] > 0]
+        if started.numel() == 0:
+            print(f"  {name}: no records (the product did not take the persistent kernel)")
+            continue
+        t0 = started.min()
+        for l in range(CAP):
+            m = b[:, l, 0] > 0
+            if not m.any():
+                break
+            f = lambda i: b[:, l, i][m]
+            span = f(2) - f(0)
+            print(f"  {name + ' ' + str(N) + 'x' + str(K):16s} {l:4d} {int(m.sum()):5d} {((f(0) - t0) / 1e3).mean():9.2f} {(span / 1e3).mean():8.2f} "
+                  f"{(span / nkb).mean():10.1f} {(f(8) / span * 1e3).mean():7.0f} {(f(9) / nkb).mean():12.0f} {(f(3) / nkb).mean():13.0f} "
+                  f"{(f(1) / nkb).mean():20.0f} {(f(7) / nkb).mean():21.0f} {((f(5) - f(4)) / 1e3).mean():12.2f} {((f(5) - t0) / 1e3).max():14.2f}")
+    err = ops.kernel_error()
     return 0 if err == 0 else 1
 
 
