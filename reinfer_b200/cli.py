@@ -77,6 +77,8 @@ def cmd_run(a) -> int:
     tpot = (dt - (first or 0.0)) / max(n - 1, 1) * 1e3
     print(f"{n} tokens in {dt:.3f}s (≈{n / dt if dt > 0 else 0:.1f} tok/s, first-token {(first or 0) * 1e3:.1f} ms), "
           f"finish={r.finish_reason}", file=sys.stderr)
+    for line in llm.profile_report():
+        print(line, file=sys.stderr)
     if a.perf:
         print(f"PERF model={a.model} dtype={a.dtype} load_s={load_s:.2f} prompt_tokens={len(prompt)} "
               f"new_tokens={n} ttft_ms={(first or 0) * 1e3:.3f} tpot_ms={tpot:.3f} "

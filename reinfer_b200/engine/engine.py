@@ -291,6 +291,13 @@ class Engine:
         self.check_status()
         return self._replay(key, host, lens_after, list(range(len(rids))) if logits else [], len(rids))
 
+    def check_guards(self) -> None:
+        """Raises if a guard page beside a layer's cache pages no longer holds its pattern (a store reached a page
+        index of -1 or of the pool's size).  Synchronises the device: for tests and for looking into a fault."""
+        bad = self.storage.check_guards()
+        if bad:
+            raise EngineError("guard pages of the cache were written: " + ", ".join(bad))
+
     def finish(self, request_id) -> None:
         """The request is over: its pages and its slot are given back."""
         if request_id in self.cache:

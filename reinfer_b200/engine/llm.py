@@ -7,6 +7,7 @@ engine.
 """
 from __future__ import annotations
 
+import os
 import time
 from dataclasses import dataclass, field
 from typing import Dict, Hashable, List, Optional, Sequence, Union
@@ -64,6 +65,14 @@ class LLM:
         self._next_id = 0
         self.requests: Dict[Hashable, Request] = {}
         self.last_stats: Dict[str, float] = {}
+        # REINFER_B200_STEP_PROFILE=decode|prefill[:every]: every so many steps (20) of that kind run eagerly with an
+        # event behind every launch; `profile_report()` (the command line prints it at the end) gives their mean by
+        # kernel family (the reference's REINFER_DECODE_PROFILE / REINFER_PREFILL_PROFILE, crates/cuda/src/engine.rs:928-1408)
+        spec = os.environ.get("REINFER_B200_STEP_PROFILE", "")
+        self._profile_kind, _, every = spec.partition(":")
+        self._profile_every = max(1, int(every)) if every.isdigit() else 20
+        self._profile_seen = 0
+        self._profile_runs: List[Dict] = []
         self._launched = None                   # a step launched ahead of its scheduling: (batch, tokens on their way)
         self.steps_launched_ahead = 0           # steps that were launched before the step before them was read
         self.ahead_rows_dropped = 0             # rows of such steps that belonged to requests which had ended
@@ -145,9 +154,48 @@ class LLM:
     def _launch(self, batch):
         """Run the batch through the engine (the sampler is its epilogue) and start the tokens' way to the host."""
         entries = [StepEntry(s.request.request_id, s.tokens, [len(s.tokens) - 1] if s.sample else []) for s in batch]
+        if self._profile_kind and self._profile_kind == ("decode" if all(len(s.tokens) == 1 for s in batch) else "prefill"):
+            self._profile_seen += 1
+            if self._profile_due(self._profile_seen):
+                self._profiled_step(entries)
+                n = sum(1 for s in batch if s.sample)
+                return self.sampler.download(n) if n else None
         self.engine.step(entries, logits=False)
         n = sum(1 for s in batch if s.sample)
         return self.sampler.download(n) if n else None
+
+    def _profile_due(self, count: int) -> bool:
+        return self._profile_every == 1 or count % self._profile_every == 1
+
+    def _profiled_step(self, entries) -> None:
+        from .. import ops
+        graphs, self.engine.cuda_graphs = self.engine.cuda_graphs, False
+        prof = ops.SegmentProfiler()
+        old = ops.set_profiler(prof)
+        prof.begin()
+        try:
+            self.engine.step(entries, logits=False)
+        finally:
+            ops.set_profiler(old)
+            self.engine.cuda_graphs = graphs
+        self._profile_runs.append(prof.summary())
+
+    def profile_report(self) -> List[str]:
+        """Lines of the mean over the profiled steps, by kernel family (empty without REINFER_B200_STEP_PROFILE)."""
+        if not self._profile_runs:
+            return []
+        from .. import measure
+        mean: Dict = {}
+        for run in self._profile_runs:
+            for name, d in run.items():
+                m = mean.setdefault(name, {"n": 0, "us": 0.0, "tflops": 0.0, "gbs": 0.0})
+                for k in m:
+                    m[k] += d[k] / len(self._profile_runs)
+        for m in mean.values():
+            m["n"] = int(round(m["n"]))
+        hbm, tf, _, src = measure.peaks()
+        return [f"-- mean of {len(self._profile_runs)} eager {self._profile_kind} steps by kernel family (peaks {src}) --"] + \
+            measure.segment_table(mean, hbm, tf)
 
     def _launch_ahead(self, batch):
         """If the step after `batch` (which is launched, not read) is sure to be "the same requests, one token
@@ -160,6 +208,10 @@ class LLM:
             if not s.sample or r.state != RUNNING or len(r.output) + 1 >= r.params.max_tokens or \
                     (limit and r.total_len + 2 >= limit):
                 return None
+        if self._profile_kind == "decode":
+            if self._profile_due(self._profile_seen + 1):
+                return None                             # the next decode step is one to profile: it takes the ordinary way
+            self._profile_seen += 1
         handle = self.engine.prepare_ahead([s.request.request_id for s in batch])
         if handle is None:
             return None

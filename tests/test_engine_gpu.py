@@ -63,6 +63,7 @@ def run_steps(engine, steps, owners=None):
             engine.finish(r)
             done.pop(r, None)
         engine.cache.check()
+    engine.check_guards()                       # no store reached a page beside a layer's own
     return got
 
 

@@ -379,6 +379,39 @@ def test_penalties_through_the_slots_follow_the_host_driven_sampler(model_dirs):
             assert out == toks
 
 
+def test_step_profile_flag_changes_no_token(model_dirs, monkeypatch):
+    """REINFER_B200_STEP_PROFILE runs some steps eagerly with events behind every launch: the same tokens, and a
+    report by kernel family."""
+    from reinfer_b200.engine.llm import LLM
+    from reinfer_b200.sampling import SamplingParams
+    sp = SamplingParams(temperature=0.0, max_tokens=12, ignore_eos=True)
+    prompts = [t[:9] for t in list(tiny.sequences("A").values())[:2]]
+    plain_run = LLM(model_dirs["A"], dtype="bfloat16", max_num_seqs=4, page_size=16, num_pages=32).generate(prompts, sp)
+    monkeypatch.setenv("REINFER_B200_STEP_PROFILE", "decode:3")
+    llm = LLM(model_dirs["A"], dtype="bfloat16", max_num_seqs=4, page_size=16, num_pages=32)
+    outs = llm.generate(prompts, sp)
+    assert [o.token_ids for o in outs] == [o.token_ids for o in plain_run]
+    report = llm.profile_report()
+    assert len(llm._profile_runs) >= 3 and report and "decode" in report[0]
+    assert any(line.startswith("sample_slots") for line in report) and any(line.startswith("total") for line in report)
+
+
+def test_guard_pages_tell_of_a_store_beside_the_pool(model_dirs):
+    """The pages around a layer's own hold a pattern; a store to page -1 (made here by hand) is reported with the
+    layer's name, and nothing else is."""
+    from reinfer_b200.engine import Engine, EngineError, StepEntry
+    engine = Engine.from_model_dir(model_dirs["A"], dtype="bfloat16", max_tokens=256, max_num_seqs=2)
+    engine.step([StepEntry("a", list(range(3, 40)), [36])])
+    engine.check_guards()
+    name, kv = next(iter(engine.storage.layer_kv.items()))
+    page_elems = kv[0].numel()
+    flat = kv.reshape(-1)
+    torch.as_strided(flat, (4,), (1,), flat.storage_offset() - page_elems + 5).fill_(1.0)     # four elements of page -1
+    with pytest.raises(EngineError, match=f"{name}: before"):
+        engine.check_guards()
+    assert engine.storage.check_guards() == [f"{name}: before"]
+
+
 def test_out_of_vocabulary_token_is_refused(model_dirs):
     from reinfer_b200.engine import EmbeddingOov, Engine, StepEntry
     e = Engine.from_model_dir(model_dirs["A"], dtype="float32", max_tokens=64, max_num_seqs=1)
