@@ -152,6 +152,22 @@ __device__ __forceinline__ bool fc_wait(uint32_t bar, uint32_t parity, volatile 
     return false;
 }
 
+// With -DRB_TIMELINE lane 0 of every warp adds up, over the key tiles of its CTA, the cycles it spent in each of its
+// waits and in its own work, into the buffer of rb_fa_tc_trace(): [warp][8] sums over all CTAs (atomics) and, in word 7
+// of a warp's row, the number of (CTA, key tile) pairs counted.  A development aid: where a key tile's time goes.
+#ifdef RB_TIMELINE
+__device__ unsigned long long* g_fc_trace = nullptr;
+extern "C" int rb_fa_tc_trace(unsigned long long* buf) { return (int)cudaMemcpyToSymbol(g_fc_trace, &buf, sizeof(buf)); }
+#define FC_T0() const long long fc_t0 = clock64()
+#define FC_ADD(slot) do { fc_acc[slot] += clock64() - fc_t0; } while (0)
+#define FC_FLUSH(n) do { if (g_fc_trace && lane == 0) { for (int q = 0; q < 7; ++q) atomicAdd(g_fc_trace + warp * 8 + q, (unsigned long long)fc_acc[q]); \
+                         atomicAdd(g_fc_trace + warp * 8 + 7, (unsigned long long)(n)); } } while (0)
+#else
+#define FC_T0() do { } while (0)
+#define FC_ADD(slot) do { } while (0)
+#define FC_FLUSH(n) do { } while (0)
+#endif
+
 __global__ void __launch_bounds__(FC_THREADS, 1)
 fa_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_kv, const FcArgs a) {
     RB_TL(11);
@@ -169,7 +185,7 @@ fa_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_kv, const FcArgs a)
     if (threadIdx.x == 0) {
         for (int s = 0; s < FC_NST; ++s) {
             mbar_init(smem_u32(&sh->full[s]), 1);
-            mbar_init(smem_u32(&sh->empty[s]), 2);                 // the MMA warp's commits: scores done (keys), P V done (values)
+            mbar_init(smem_u32(&sh->empty[s]), 3);                 // the issuers' commits: scores of either row tile done (keys), P V done (values)
         }
         for (int t = 0; t < FC_TILES; ++t)
             for (int b = 0; b < 2; ++b) {
@@ -232,6 +248,7 @@ fa_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_kv, const FcArgs a)
     __syncthreads();
 
     int issued = 0;                                                // producer: tiles whose copies were issued
+    [[maybe_unused]] long long fc_acc[7] = {0, 0, 0, 0, 0, 0, 0};
     if (warp < 4) {
     asm volatile("setmaxnreg.dec.sync.aligned.u32 88;");           // the control group gives registers up ...
     if (warp == 0) {
@@ -261,7 +278,8 @@ fa_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_kv, const FcArgs a)
             }
             // every lane waits, lane 0's requests take effect (a lane alone inside a branch pays for each of them)
             const uint32_t lead = lane == 0 ? 1u : 0u;
-            if (it >= FC_NST && !fc_wait(smem_u32(&sh->empty[s]), ((it / FC_NST) & 1) ^ 1, abort_flag, 11)) break;
+            { FC_T0(); if (it >= FC_NST && !fc_wait(smem_u32(&sh->empty[s]), ((it / FC_NST) & 1) ^ 1, abort_flag, 11)) break; FC_ADD(0); }
+            FC_T0();
             const uint32_t full = smem_u32(&sh->full[s]);
             mbar_expect_tx_lead(full, (uint32_t)(n_valid * 2 * box_keys * 256), lead);
             const uint32_t dst0 = stages_u + s * FC_STAGE;
@@ -277,42 +295,41 @@ fa_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_kv, const FcArgs a)
                 }
             }
             issued = it + 1;
+            FC_ADD(1);
         }
-    } else if (warp == 1) {
-        // ---- issuer of the scores: every lane runs the loop, lane 0's instructions take effect ---------------------
-        // S_t(i) = Q_t K(i)^T into score buffer i & 1 of both row tiles, as soon as the keys have landed and the rows
+        FC_FLUSH(n_tiles);
+    } else if (warp == 1 || warp == 3) {
+        // ---- issuers of the scores, one warp per row tile: every lane runs the loop, lane 0's instructions take effect
+        // S_t(i) = Q_t K(i)^T into score buffer i & 1 of row tile t, as soon as the keys have landed and the rows
         // have taken the scores of two tiles ago out of that buffer: the scores run ahead of the rows, whatever the
         // products P V are doing.  d = 128 is two 64-column halves of four 16-wide steps each; the keys' 8-row groups
-        // lie 2,048 bytes apart, their second half 1,024 bytes on.
+        // lie 2,048 bytes apart, their second half 1,024 bytes on.  (One warp for both tiles had 16 products and 3
+        // commits to issue per key tile, about 65 cycles each: more than the products take to run.)
         const uint32_t lead = lane == 0 ? 1u : 0u;
+        const int t = warp == 1 ? 0 : 1;
         constexpr uint32_t idesc_s = make_idesc(FC_BN);
+        const uint64_t dq0 = make_smem_desc(sQ_u + (t * 2) * FC_QHALF), dq1 = make_smem_desc(sQ_u + (t * 2 + 1) * FC_QHALF);
         for (int i = 0; i < n_tiles; ++i) {
             const int s = i % FC_NST;
-            if (!fc_wait(smem_u32(&sh->full[s]), (i / FC_NST) & 1, abort_flag, 12)) break;
-            bool ok = true;
-            if (i >= 2) {
-#pragma unroll
-                for (int t = 0; t < FC_TILES; ++t)
-                    ok = ok && fc_wait(smem_u32(&sh->s_free[t][i & 1]), (uint32_t)(((i >> 1) & 1) ^ 1), abort_flag, 20);
-            }
-            if (!ok) break;
+            { FC_T0(); if (!fc_wait(smem_u32(&sh->full[s]), (i / FC_NST) & 1, abort_flag, 12)) break; FC_ADD(0); }
+            { FC_T0(); if (i >= 2 && !fc_wait(smem_u32(&sh->s_free[t][i & 1]), (uint32_t)(((i >> 1) & 1) ^ 1), abort_flag, 20)) break; FC_ADD(1); }
+            FC_T0();
             tc_fence_after();
             const uint32_t sK = stages_u + s * FC_STAGE;
 #pragma unroll
-            for (int t = 0; t < FC_TILES; ++t) {
+            for (int h = 0; h < 2; ++h) {
+                const uint64_t dq = h ? dq1 : dq0;
+                const uint64_t dk = make_smem_desc_lbo_sbo(sK + h * FC_HALF, 16, FC_GROUP);
 #pragma unroll
-                for (int h = 0; h < 2; ++h) {
-                    const uint64_t dq = make_smem_desc(sQ_u + (t * 2 + h) * FC_QHALF);
-                    const uint64_t dk = make_smem_desc_lbo_sbo(sK + h * FC_HALF, 16, FC_GROUP);
-#pragma unroll
-                    for (int k = 0; k < 4; ++k)
-                        fc_mma_ss(tmem + (uint32_t)((t * 2 + (i & 1)) * FC_BN), dq + (uint64_t)(k * 2), dk + (uint64_t)(k * 2), idesc_s,
-                                  (h | k) != 0, lead);
-                }
-                fc_commit_lead(smem_u32(&sh->s_full[t][i & 1]), lead);
+                for (int k = 0; k < 4; ++k)
+                    fc_mma_ss(tmem + (uint32_t)((t * 2 + (i & 1)) * FC_BN), dq + (uint64_t)(k * 2), dk + (uint64_t)(k * 2), idesc_s,
+                              (h | k) != 0, lead);
             }
+            fc_commit_lead(smem_u32(&sh->s_full[t][i & 1]), lead);
             fc_commit_lead(smem_u32(&sh->empty[s]), lead);         // the keys of this stage are read once these MMAs are done ...
+            FC_ADD(2);
         }
+        FC_FLUSH(n_tiles);
     } else if (warp == 2) {
         // ---- issuer of the weighted sums: O_t += P_t V once the rows of tile t have written P -----------------------
         const uint32_t lead = lane == 0 ? 1u : 0u;
@@ -326,7 +343,8 @@ fa_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_kv, const FcArgs a)
             const uint64_t dv = make_smem_desc_lbo_sbo(sVs, FC_HALF, FC_GROUP);
 #pragma unroll
             for (int t = 0; t < FC_TILES; ++t) {
-                if (!fc_wait(smem_u32(&sh->p_full[t][it & 1]), (it >> 1) & 1, abort_flag, 13)) { ok = false; break; }
+                { FC_T0(); if (!fc_wait(smem_u32(&sh->p_full[t][it & 1]), (it >> 1) & 1, abort_flag, 13)) { ok = false; break; } FC_ADD(0); }
+                FC_T0();
                 tc_fence_after();
                 const uint64_t dp = make_smem_desc(sP_u + (t * 2 + (it & 1)) * FC_QHALF);
 #pragma unroll
@@ -334,10 +352,12 @@ fa_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_kv, const FcArgs a)
                     fc_mma_ss(tmem + (uint32_t)(FC_TILES * 2 * FC_BN + t * FC_D), dp + (uint64_t)(k * 2),
                               dv + (uint64_t)(k * ((2 * FC_GROUP) >> 4)), idesc_mn, (it > 0) || k != 0, lead);
                 fc_commit_lead(smem_u32(&sh->o_full[t][it & 1]), lead);
+                FC_ADD(2);
             }
             if (!ok) break;
             fc_commit_lead(smem_u32(&sh->empty[it % FC_NST]), lead);   // ... and its values once these are
         }
+        FC_FLUSH(n_tiles);
     }
     } else {
         asm volatile("setmaxnreg.inc.sync.aligned.u32 208;");      // ... and the rows take them
@@ -372,7 +392,10 @@ fa_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_kv, const FcArgs a)
                 asm volatile("fence.proxy.async.shared::cta;" ::: "memory");   // the zeros, before the tensor core reads the values
             }
             // S: this row's 64 scores in one go (one wait for tensor memory); maxima and sums in four independent chains
-            if (!fc_wait(smem_u32(&sh->s_full[t][b]), par, abort_flag, 15)) { ok = false; break; }
+            { FC_T0(); if (!fc_wait(smem_u32(&sh->s_full[t][b]), par, abort_flag, 15)) { ok = false; break; } FC_ADD(0); }
+#ifdef RB_TIMELINE
+            const long long fc_tile0 = clock64();
+#endif
             tc_fence_after();
             const bool edge = k0 + FC_BN - 1 > pos || k0 < lo;     // the tile crosses this row's causal edge or window
             uint32_t sr[FC_BN];
@@ -380,6 +403,9 @@ fa_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_kv, const FcArgs a)
 #pragma unroll
             for (int c = 0; c < FC_BN / 16; ++c) tc_ld16(lane_base + s_col + (uint32_t)(c * 16), sr + c * 16);
             tc_ld_wait();
+#ifdef RB_TIMELINE
+            fc_acc[1] += clock64() - fc_tile0;
+#endif
             tc_fence_before();
             __syncwarp();
             if (lane == 0) mbar_arrive(smem_u32(&sh->s_free[t][b]));          // this buffer may take the scores of tile it + 2
@@ -392,7 +418,9 @@ fa_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_kv, const FcArgs a)
             }
             // this P buffer was read by the product of two key tiles ago, which must be done before it is written again
             if (it >= 2) {
+                FC_T0();
                 if (!fc_wait(smem_u32(&sh->o_full[t][b]), par ^ 1, abort_flag, 16)) { ok = false; break; }
+                FC_ADD(2);
             }
             unsigned char* sPb = sP + (t * 2 + b) * FC_QHALF;
             // P = 2^(S * scale - base), rounded to bfloat16, into the buffer; and its row sum
@@ -451,7 +479,11 @@ fa_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_kv, const FcArgs a)
             tc_fence_before();                                     // O (if touched) is written: the product may go on
             __syncwarp();
             if (lane == 0) mbar_arrive(smem_u32(&sh->p_full[t][b]));
+#ifdef RB_TIMELINE
+            fc_acc[4] += clock64() - fc_tile0;
+#endif
         }
+        FC_FLUSH(n_tiles);
         // the row of O, once the tile's last products are done (the last one on each of the two barriers)
         if (ok && n_tiles > 0) {
             const int last = n_tiles - 1;
