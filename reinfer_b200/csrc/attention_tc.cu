@@ -14,7 +14,7 @@
 //                          row's thread rescales its lane of O in tensor memory, which is rare), so the rows read O once
 // Warp 0 feeds key/value tiles by TMA: ONE request brings the keys (or the values) of a page for this kv head, laid
 // out as [8-key group][64-dim half][8 keys][64 dims] whatever the page size is (the 5-D map of runtime.cu).  Warp 1
-// allocates tensor memory and issues the scores, warp 2 issues the weighted sums; warps 4-7 are the rows of tile A,
+// allocates tensor memory and issues the scores of tile A, warp 3 those of tile B, warp 2 the weighted sums; warps 4-7 are the rows of tile A,
 // warps 8-11 the rows of tile B.  Q [rows][d], K [keys][d] and P [rows][keys] are K-major operands; V [keys][d] is
 // used as it lands, as an MN-major operand (instruction descriptor bit 16; in the shared-memory descriptor the
 // leading offset steps to the second 64 dims, the stride offset to the next 8 keys) - nothing is transposed.
@@ -28,6 +28,14 @@
 // and nothing but the row's last read of O and the reuse of a P buffer two tiles later waits for them.  (Keeping P in
 // tensor memory over the scores it came from - the A operand of the product may lie there - was built and measured:
 // it ties the scores' buffer to the product's completion and was no faster.)
+// What bounds a key tile now (the kernel's own trace, -DRB_TIMELINE: lane 0 of every warp adds up its waits and its
+// work): of the 2,100 cycles a key tile takes, a row warp spends 1,270 in its 64 exponentials per row - two row warps
+// share a scheduler's special-function unit (16 results a cycle and SM), so the 16,384 exponentials of a key tile
+// cannot take less than 1,024 cycles; the issuers wait.  Two threads per row (half the chain each, the row's maximum
+// agreed through shared memory) were built and measured slower (690 against 623 us at 8,192 tokens): the
+// exponentials are the same, the exchange comes on top.  Rounding P with integer instructions instead of the
+// conversion: no change.  What would help is fewer exponentials on that unit (a polynomial on the FMA pipe for a
+// part of them), which is not built.
 // Registers follow the roles (setmaxnreg): 88 for the control warps, 208 for the rows - what the control warps give up
 // (128 threads x 80) must cover what the rows take (256 threads x 40), for the registers come from the CTA's own
 // allocation (384 x 168) and a request for more than it holds waits for ever.
@@ -443,11 +451,21 @@ fa_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_kv, const FcArgs a)
             // by side, and only a warp in which some row's scale has to move (always in a row's first tile) does its
             // exponentials again.
             float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
+#ifdef RB_TIMELINE
+            const long long fc_c3 = clock64();
+#endif
 #pragma unroll
             for (int j = 0; j < FC_BN; ++j) mx4[j & 3] = fmaxf(mx4[j & 3], __uint_as_float(sr[j]));
             const float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3])) * a.scale_log2;   // the scale is positive
             float sum = 0.0f;
+#ifdef RB_TIMELINE
+            const long long fc_c5 = clock64();
+            fc_acc[3] += fc_c5 - fc_c3;
+#endif
             if (it > 0) sum = emit(m == -INFINITY ? 0.0f : m);
+#ifdef RB_TIMELINE
+            fc_acc[5] += clock64() - fc_c5;
+#endif
             const bool moves = (m == -INFINITY) ? (mx != -INFINITY) : (mx > m + FC_RESCALE);
             if (it == 0 || __any_sync(0xffffffffu, moves)) {
                 float alpha = 1.0f;
@@ -475,11 +493,15 @@ fa_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_kv, const FcArgs a)
                 sum = emit(m == -INFINITY ? 0.0f : m);
             }
             l += sum;
+#ifdef RB_TIMELINE
+            const long long fc_c6 = clock64();
+#endif
             asm volatile("fence.proxy.async.shared::cta;" ::: "memory");       // P (and zeroed value rows) before the tensor core reads them
             tc_fence_before();                                     // O (if touched) is written: the product may go on
             __syncwarp();
             if (lane == 0) mbar_arrive(smem_u32(&sh->p_full[t][b]));
 #ifdef RB_TIMELINE
+            fc_acc[6] += clock64() - fc_c6;
             fc_acc[4] += clock64() - fc_tile0;
 #endif
         }
