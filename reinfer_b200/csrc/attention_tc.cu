@@ -29,13 +29,14 @@
 // tensor memory over the scores it came from - the A operand of the product may lie there - was built and measured:
 // it ties the scores' buffer to the product's completion and was no faster.)
 // What bounds a key tile now (the kernel's own trace, -DRB_TIMELINE: lane 0 of every warp adds up its waits and its
-// work): of the 2,100 cycles a key tile takes, a row warp spends 1,270 in its 64 exponentials per row - two row warps
-// share a scheduler's special-function unit (16 results a cycle and SM), so the 16,384 exponentials of a key tile
-// cannot take less than 1,024 cycles; the issuers wait.  Two threads per row (half the chain each, the row's maximum
-// agreed through shared memory) were built and measured slower (690 against 623 us at 8,192 tokens): the
-// exponentials are the same, the exchange comes on top.  Rounding P with integer instructions instead of the
-// conversion: no change.  What would help is fewer exponentials on that unit (a polynomial on the FMA pipe for a
-// part of them), which is not built.
+// work): of the 2,100 cycles a key tile takes, a row warp works 1,970 (the issuers wait for it): 1,270 in P (64
+// scale-and-subtract, exponential, sum, 32 conversions, 8 stores a row), of which 760 are the exponentials' (two row
+// warps share a scheduler's special-function unit).  With the exponentials taken out the tile still takes 1,900: then
+// the rows wait for the scores, whose issuer needs 900 cycles for a tile's 8 products and 2 commits.  Both sides are
+// that close, so neither alone buys much.  Built, measured, left out: two threads per row (half the chain each, the
+// row's maximum agreed through shared memory: 690 against 623 us at 8,192 tokens); a part of the exponentials as a
+// cubic on the FMA pipe (3 of 8: 671 us, 1 of 2: 724 - nine instructions for one); P rounded by integer instructions
+// instead of the conversion (no change).
 // Registers follow the roles (setmaxnreg): 88 for the control warps, 208 for the rows - what the control warps give up
 // (128 threads x 80) must cover what the rows take (256 threads x 40), for the registers come from the CTA's own
 // allocation (384 x 168) and a request for more than it holds waits for ever.
