@@ -682,6 +682,179 @@ static int launch_tc_persistent(const CUtensorMap& mw, const CUtensorMap& mx, vo
                      mode, t_tiles, n_tiles);
 }
 
+// The gated pair over 65 .. 128 tokens (a decode step of that many requests): one tile per CTA, 128 tokens (the M
+// operand; rows beyond T are zero-filled by TMA) x 64 gate + 64 up weight rows (the N operand), the whole depth K, three
+// stages of 32 KB - two CTAs fit an SM, and F / 64 CTAs stream the weights (192 at the 8B shape, where 128-row tiles
+// gave 96 CTAs on 148 SMs with eight products to issue per k-step: 4.4 TB/s).  A lane of the accumulator is a token;
+// its row factor (the deferred RMS norm) multiplies gate and up before the activation.  The weights' first stages are
+// requested before the kernels in front of this one have finished, the tokens after.
+struct TcStreamShared {
+    unsigned long long full[4];
+    unsigned long long empty[4];
+    unsigned long long acc_full;
+    uint32_t tmem_base;
+    int abort_flag;
+};
+#define TCS_ROWS 64                      // gate rows (and up rows) per tile
+template <int STAGES, int XROWS>
+__global__ void __launch_bounds__(TC_THREADS, 2)
+gemm_tc_gated_stream_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_x,
+                            bf16* __restrict__ act, int T, int F, int K, long long ldc, TcExtra ex) {
+    RB_TL(7);
+    extern __shared__ __align__(1024) unsigned char smem_raw[];
+    constexpr uint32_t W1_BYTES = TCS_ROWS * TC_BK * 2;            // the gate rows of a stage; the up rows follow
+    constexpr uint32_t W_BYTES = 2 * W1_BYTES;
+    // XROWS tokens are fetched (64 when there are no more: the product still reads 128 rows, the 64 beyond lie in
+    // the next stage's weights or in the slack behind the last stage - whatever they hold lands in accumulator lanes of
+    // tokens that do not exist and is never read)
+    constexpr uint32_t X_BYTES = XROWS * TC_BK * 2;
+    constexpr uint32_t STAGE_BYTES = W_BYTES + X_BYTES;
+    constexpr uint32_t TMEM_COLS = 2 * TCS_ROWS;
+    unsigned char* smem = (unsigned char*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+    TcStreamShared* sh = (TcStreamShared*)(smem + (size_t)STAGES * STAGE_BYTES + (128 - XROWS) * TC_BK * 2);
+    const uint32_t smem_base = smem_u32(smem);
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int n0 = blockIdx.x * TCS_ROWS;
+    const int nkb = (K + TC_BK - 1) / TC_BK;
+    volatile int* abort_flag = &sh->abort_flag;
+    if (*(volatile int*)&g_rb_kernel_error) return;               // an earlier launch gave up: fail fast, the host will see the word
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < STAGES; ++s) { mbar_init(smem_u32(&sh->full[s]), 1); mbar_init(smem_u32(&sh->empty[s]), 1); }
+        mbar_init(smem_u32(&sh->acc_full), 1);
+        sh->abort_flag = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+    }
+    if (warp == 1) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&sh->tmem_base)), "r"(TMEM_COLS) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem = sh->tmem_base;
+    const uint32_t full0 = smem_u32(&sh->full[0]), empty0 = smem_u32(&sh->empty[0]);
+    const uint32_t lead = lane == 0 ? 1u : 0u;                     // the issuing warps stay converged; lane 0's instructions take effect
+    int issued = 0;
+
+    if (warp == 0) {
+        pdl_trigger();
+        const int pre = min(nkb, STAGES);
+        for (int kb = 0; kb < pre; ++kb) {                         // the weights never change: fetched at once
+            const uint32_t full = full0 + 8 * kb;
+            mbar_expect_tx_lead(full, STAGE_BYTES, lead);
+            tma_load_2d_lead(smem_base + kb * STAGE_BYTES, &map_w, kb * TC_BK, n0, full, lead);
+            tma_load_2d_lead(smem_base + kb * STAGE_BYTES + W1_BYTES, &map_w, kb * TC_BK, F + n0, full, lead);
+        }
+        pdl_wait();
+        if (lead) RB_TL_MARK();
+        for (int kb = 0; kb < pre; ++kb)
+            tma_load_2d_lead(smem_base + kb * STAGE_BYTES + W_BYTES, &map_x, kb * TC_BK, 0, full0 + 8 * kb, lead);
+        issued = pre;
+        for (int kb = pre; kb < nkb; ++kb) {
+            const int s = kb % STAGES;
+            if (!mbar_wait(empty0 + 8 * s, ((uint32_t)(kb / STAGES) & 1) ^ 1, abort_flag, 31)) break;
+            const uint32_t full = full0 + 8 * s, dst = smem_base + s * STAGE_BYTES;
+            mbar_expect_tx_lead(full, STAGE_BYTES, lead);
+            tma_load_2d_lead(dst, &map_w, kb * TC_BK, n0, full, lead);
+            tma_load_2d_lead(dst + W1_BYTES, &map_w, kb * TC_BK, F + n0, full, lead);
+            tma_load_2d_lead(dst + W_BYTES, &map_x, kb * TC_BK, 0, full, lead);
+            issued = kb + 1;
+        }
+        // this CTA's weights are on their way: the weights that the next product streams are called into L2
+        if (lead) l2_prefetch_share(ex.next_w, ex.next_bytes, blockIdx.x, gridDim.x);
+    } else if (warp == 1) {
+        constexpr uint32_t idesc = make_idesc(2 * TCS_ROWS);
+        const uint64_t dw0 = make_smem_desc(smem_base), dx0 = make_smem_desc(smem_base + W_BYTES);
+        bool ok = true;
+        for (int kb = 0; kb < nkb; ++kb) {
+            const int s = kb % STAGES;
+            ok = mbar_wait(full0 + 8 * s, (uint32_t)(kb / STAGES) & 1, abort_flag, 32);
+            if (!ok) break;
+            const uint64_t off = (uint64_t)(s * (STAGE_BYTES >> 4));
+#pragma unroll
+            for (int k = 0; k < TC_BK / 16; ++k)                   // the tokens are the M operand, the 128 weight rows the N operand
+                tc_mma_bf16_lead(tmem, dx0 + off + (uint64_t)(k * 2), dw0 + off + (uint64_t)(k * 2), idesc, (kb | k) != 0, lead);
+            tc_commit_lead(empty0 + 8 * s, lead);
+        }
+        if (ok) tc_commit_lead(smem_u32(&sh->acc_full), lead);
+    } else {
+        const int q = warp & 3;
+        const int tok = q * 32 + lane;
+        pdl_wait();
+        float f = 1.0f;                                            // this token's row factor
+        if (ex.row_sumsq && tok < T) {
+            float ssq = 0.0f;
+            for (int p = 0; p < ex.sumsq_parts; ++p) ssq += ex.row_sumsq[(size_t)tok * ex.sumsq_parts + p];
+            f = 1.0f / sqrtf(ssq * ex.inv_width + ex.eps);
+        }
+        const bool vec_ok = (ldc % 8 == 0) && (((uintptr_t)act & 15) == 0);
+        if (mbar_wait(smem_u32(&sh->acc_full), 0, abort_flag, 33)) {
+            tc_fence_after();
+            const uint32_t acc = tmem + ((uint32_t)(q * 32) << 16);
+            bf16* row = act + (size_t)tok * ldc + n0;
+#pragma unroll 1
+            for (int c0 = 0; c0 < TCS_ROWS; c0 += 16) {
+                if (n0 + c0 >= F) break;
+                uint32_t r[16], r2[16];
+                tc_ld16(acc + (uint32_t)c0, r);
+                tc_ld16(acc + (uint32_t)(TCS_ROWS + c0), r2);
+                tc_ld_wait();
+                if (tok >= T) continue;
+                uint32_t o[8];
+#pragma unroll
+                for (int j = 0; j < 8; ++j) {
+                    const float g0 = __uint_as_float(r[2 * j]) * f, u0 = __uint_as_float(r2[2 * j]) * f;
+                    const float g1 = __uint_as_float(r[2 * j + 1]) * f, u1 = __uint_as_float(r2[2 * j + 1]) * f;
+                    const __nv_bfloat162 v = __floats2bfloat162_rn(g0 / (1.0f + expf(-g0)) * u0, g1 / (1.0f + expf(-g1)) * u1);
+                    o[j] = *(const uint32_t*)&v;
+                }
+                if (vec_ok && n0 + c0 + 16 <= F) {
+                    *(uint4*)(row + c0) = make_uint4(o[0], o[1], o[2], o[3]);
+                    *(uint4*)(row + c0 + 8) = make_uint4(o[4], o[5], o[6], o[7]);
+                } else {
+                    const bf16* ov = (const bf16*)o;
+#pragma unroll
+                    for (int j = 0; j < 16; ++j) if (n0 + c0 + j < F) row[c0 + j] = ov[j];
+                }
+            }
+        }
+    }
+    tc_fence_before();
+    __syncthreads();
+    if (*abort_flag && threadIdx.x == 0) {
+        for (int kb = max(0, issued - STAGES); kb < issued; ++kb)
+            mbar_drain(smem_u32(&sh->full[kb % STAGES]), (uint32_t)(kb / STAGES) & 1);
+    }
+    __syncthreads();
+    if (warp == 1) {
+        __syncwarp();
+        tc_fence_after();
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(TMEM_COLS) : "memory");
+    }
+}
+
+template <int STAGES, int XROWS>
+static int launch_tc_gated_stream(const void* X, const void* Wgu, void* act, int T, int F, int K, long long ldx, long long ldw,
+                                  long long ldc, const TcExtra& ex, cudaStream_t s) {
+    constexpr size_t smem = (size_t)STAGES * (2 * TCS_ROWS * TC_BK * 2 + XROWS * TC_BK * 2) + (128 - XROWS) * TC_BK * 2 +
+                            sizeof(TcStreamShared) + 1024;
+    static_assert(smem <= 113 * 1024, "two CTAs to an SM");
+    static bool configured = false;
+    if (!configured) {
+        cudaError_t e = cudaFuncSetAttribute(gemm_tc_gated_stream_kernel<STAGES, XROWS>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        if (e != cudaSuccess) return (int)e;
+        (void)cudaFuncSetAttribute(gemm_tc_gated_stream_kernel<STAGES, XROWS>, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared);
+        configured = true;
+    }
+    CUtensorMap mw, mx;
+    if (rb_tensor_map_bf16(Wgu, 2LL * F, K, ldw, TCS_ROWS, &mw)) return -1;
+    if (rb_tensor_map_bf16(X, T, K, ldx, XROWS, &mx)) return -1;
+    return rb_launch(gemm_tc_gated_stream_kernel<STAGES, XROWS>, dim3(rb_ceil_div(F, TCS_ROWS)), dim3(TC_THREADS), smem, s, mw, mx,
+                     (bf16*)act, T, F, K, ldc, ex);
+}
+
 // Sum of the split partials in split order, then store / accumulate.  mode as OUT_MODE 0..2.
 __global__ void splitk_reduce_kernel(const float* __restrict__ ws, void* __restrict__ C, int T, int N, long long ldc,
                                      int splits, int mode) {
@@ -855,6 +1028,11 @@ static int g_tc_token_lanes = 1;
 // Persistent products of several token tiles: 1 = a token per accumulator lane (128 tokens x 256 features a tile),
 // 0 = a feature per lane (128 features x 256 or 128 tokens).  Returns the old value.
 extern "C" int rb_set_gemm_token_lanes(int v) { int old = g_tc_token_lanes; g_tc_token_lanes = v ? 1 : 0; return old; }
+
+static int g_tc_gated_stream = 1;
+// The gated pair over 65 .. 128 tokens: 1 = the streaming kernel with a token per lane (64 + 64 weight rows a CTA),
+// 0 = the kernel with a feature per lane (128 + 128 rows a CTA).  Returns the old value.
+extern "C" int rb_set_gemm_gated_stream(int v) { int old = g_tc_gated_stream; g_tc_gated_stream = v ? 1 : 0; return old; }
 
 static int g_tc_tile_feats = 0;
 // Weight rows per tile of the token-lane forms: 0 = chosen per product, 256 (four stages) or 224 (five).  Returns the old value.
@@ -1036,6 +1214,11 @@ extern "C" int rb_gemm_bf16_swiglu(const void* X, const void* Wgu, void* act, in
         if (rb_tensor_map_bf16(X, T, K, ldx, 128, &mx)) return -1;
         return launch_tc_persistent<128, 4, 1, 256>(mw, mx, act, T, F, K, ldc, 0, s);
     }
+    // 65 .. 128 tokens: F / 64 CTAs, two to an SM.  (For 33 .. 64 tokens the same kernel, also with 64-token stages of
+    // 24 KB, is faster alone - 40 against 44 us at the 8B shape - but the decode step around it is not: 9.86 against
+    // 9.78 ms at batch 64; its 192 CTAs leave the product after it no SM to start on early.)
+    if (T > 64 && T <= 128 && force_splits == 0 && g_tc_gated_stream)
+        return launch_tc_gated_stream<3, 128>(X, Wgu, act, T, F, K, ldx, ldw, ldc, ex, s);
     if (rb_tensor_map_bf16(X, T, K, ldx, bn, &mx)) return -1;
     switch (bn) {
         case 16: return launch_tc<16, 3, true>(mw, mx, act, nullptr, 0, T, F, K, ldc, 0, force_splits, ex, s);

@@ -47,6 +47,9 @@ def lib():
         if os.environ.get("REINFER_B200_GEMM_TOKEN_LANES"):
             # prompt portions: 1 a token per accumulator lane (default), 0 a feature per lane
             _lib.rb_set_gemm_token_lanes(int(os.environ["REINFER_B200_GEMM_TOKEN_LANES"]))
+        if os.environ.get("REINFER_B200_GEMM_GATED_STREAM"):
+            # the gated pair over 65 .. 128 tokens: 1 the streaming kernel with a token per lane (default), 0 a feature per lane
+            _lib.rb_set_gemm_gated_stream(int(os.environ["REINFER_B200_GEMM_GATED_STREAM"]))
         if os.environ.get("REINFER_B200_GEMM_TILE_ROWS"):
             # prompt portions: 256 or 224 weight rows a tile; default chosen per product
             _lib.rb_set_gemm_tile_features(int(os.environ["REINFER_B200_GEMM_TILE_ROWS"]))

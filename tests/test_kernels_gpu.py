@@ -44,7 +44,7 @@ def test_gemm_tensor_core(T, N, K, mode):
 
 
 @pytest.mark.parametrize("T,F,K", [(1, 128, 64), (1, 12288, 4096), (8, 12288, 4096), (5, 160, 96), (17, 300, 200), (40, 1000, 512),
-                                   (64, 2048, 1024), (100, 130, 72), (129, 640, 264), (300, 520, 520), (2048, 1024, 512),
+                                   (64, 2048, 1024), (100, 130, 72), (65, 1000, 520), (128, 9728, 2560), (129, 640, 264), (300, 520, 520), (2048, 1024, 512),
                                    (200, 512, 512), (130, 1024, 2048), (256, 256, 4096)])
 def test_gemm_swiglu_epilogue(T, F, K):
     from reinfer_b200 import ops
@@ -152,7 +152,7 @@ def test_gemm_partial_sums_and_the_norm_that_adds_them(T, N, K):
     assert (out.float() - want[idx.long()]).abs().max().item() <= 1e-2 * want.abs().max().item()
 
 
-@pytest.mark.parametrize("T,h,N", [(1, 128, 256), (8, 4096, 6144), (5, 1000, 311), (33, 520, 130), (64, 2048, 1000)])
+@pytest.mark.parametrize("T,h,N", [(1, 128, 256), (8, 4096, 6144), (5, 1000, 311), (33, 520, 130), (64, 2048, 1000), (100, 1040, 260)])
 @pytest.mark.parametrize("n_delta", [0, 1, 7])
 def test_norm_whose_division_is_left_to_the_product(T, h, N, n_delta):
     """residual_rowscale leaves x*w and the parts of sum(x^2); a product that is told of them multiplies its
@@ -181,7 +181,9 @@ def test_norm_whose_division_is_left_to_the_product(T, h, N, n_delta):
         ops.gemm_bf16(y, w, c, splits=splits, row_scale=scale)
         assert (c - ref).abs().max().item() <= 2e-4 * ref.abs().max().item(), f"splits {splits}"
     p = ops.gemm_bf16_partials(y, w, row_scale=scale)
-    assert (p.sum(0) - ref).abs().max().item() <= 2e-4 * ref.abs().max().item()
+    assert (p is None) == (T > ops.STREAMING_TOKENS)          # partial sums are for streaming products only
+    if p is not None:
+        assert (p.sum(0) - ref).abs().max().item() <= 2e-4 * ref.abs().max().item()
     if N % 2 == 0:
         F = N // 2
         act = torch.empty(T, F, dtype=torch.bfloat16, device=DEV)
