@@ -166,19 +166,25 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
     } else if (warp == 1) {
         constexpr uint32_t idesc = make_idesc(BN);
         bool ok = true;
+        bool landed = false;                                     // the next stage's barrier is looked at while this stage's products are issued
         for (int kb = 0; kb < nkb && ok; ++kb) {
             const int s = kb % STAGES;
             const uint32_t round = kb / STAGES;
-            ok = mbar_wait(smem_u32(&sh->full[s]), round & 1, abort_flag, 2);   // TMA's bytes, seen through the barrier
-            if (!ok) break;
+            if (!landed) {
+                ok = mbar_wait(smem_u32(&sh->full[s]), round & 1, abort_flag, 2);   // TMA's bytes, seen through the barrier
+                if (!ok) break;
+            }
             if (kb == 0 && lead) TL(2);
             const uint32_t a = smem_base + s * STAGE_BYTES;
             const uint64_t da = make_smem_desc(a), db = make_smem_desc(a + W_BYTES);
             const uint64_t da2 = make_smem_desc(a + W1_BYTES);
+            tc_mma_bf16_lead(tmem, da, db, idesc, kb != 0, lead);
+            if (DUAL) tc_mma_bf16_lead(tmem + BN, da2, db, idesc, kb != 0, lead);
+            landed = kb + 1 < nkb && mbar_test(smem_u32(&sh->full[(kb + 1) % STAGES]), (uint32_t)((kb + 1) / STAGES) & 1);
 #pragma unroll
-            for (int k = 0; k < TC_BK / 16; ++k) {               // 32 bytes further along K inside the swizzled row
-                tc_mma_bf16_lead(tmem, da + (uint64_t)(k * 2), db + (uint64_t)(k * 2), idesc, (kb | k) != 0, lead);
-                if (DUAL) tc_mma_bf16_lead(tmem + BN, da2 + (uint64_t)(k * 2), db + (uint64_t)(k * 2), idesc, (kb | k) != 0, lead);
+            for (int k = 1; k < TC_BK / 16; ++k) {               // 32 bytes further along K inside the swizzled row
+                tc_mma_bf16_lead(tmem, da + (uint64_t)(k * 2), db + (uint64_t)(k * 2), idesc, 1, lead);
+                if (DUAL) tc_mma_bf16_lead(tmem + BN, da2 + (uint64_t)(k * 2), db + (uint64_t)(k * 2), idesc, 1, lead);
             }
             tc_commit_lead(smem_u32(&sh->empty[s]), lead);       // frees the stage when these MMAs are done
         }
