@@ -132,16 +132,6 @@ __device__ __forceinline__ void l2_prefetch_share(const void* base, long long by
 }
 __device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
 __device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
-__device__ __forceinline__ void tc_commit(uint32_t bar) {
-    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
-}
-__device__ __forceinline__ void tc_mma_bf16(uint32_t tmem_d, uint64_t desc_a, uint64_t desc_b, uint32_t idesc, uint32_t accumulate) {
-    asm volatile(
-        "{\n\t.reg .pred p;\n\t"
-        "setp.ne.b32 p, %4, 0;\n\t"
-        "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
-        ::"r"(tmem_d), "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate) : "memory");
-}
 // Forms for a warp that stays converged and lets one lane issue (lead != 0 in that lane only).  A warp whose issuing
 // lane runs alone inside a branch pays for it at every asynchronous instruction: measured on the persistent product,
 // about a hundred cycles for each tcgen05.mma, tcgen05.commit and TMA request, whatever its size.
@@ -222,12 +212,7 @@ int rb_tensor_map_bf16(const void* ptr, long long rows, long long cols, long lon
 // [8-key group][64-dim half][8 keys][64 dims] (runtime.cu).
 int rb_tensor_map_kv_pages(const void* cache, long long num_pages, int kv_heads, int page_size, CUtensorMap* out);
 
-// One box of a 5-D map (coordinates innermost first) into shared memory.
-__device__ __forceinline__ void tma_load_5d(uint32_t dst, const CUtensorMap* map, int c0, int c1, int c2, int c3, int c4, uint32_t bar) {
-    asm volatile(
-        "cp.async.bulk.tensor.5d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3, %4, %5, %6}], [%7];"
-        ::"r"(dst), "l"(map), "r"(c0), "r"(c1), "r"(c2), "r"(c3), "r"(c4), "r"(bar) : "memory");
-}
+// One box of a 5-D map (coordinates innermost first) into shared memory, issued by the lane whose `lead` is not 0.
 __device__ __forceinline__ void tma_load_5d_lead(uint32_t dst, const CUtensorMap* map, int c0, int c1, int c2, int c3, int c4, uint32_t bar, uint32_t lead) {
     asm volatile(
         "{\n\t.reg .pred q;\n\t"
