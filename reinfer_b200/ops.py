@@ -141,7 +141,14 @@ def _check(rc: int, what: str, flops: float = 0.0, nbytes: float = 0.0) -> None:
     raise KernelError(f"{what}: CUDA error {rc} at launch")
 
 
+_raw_stream = getattr(torch._C, "_cuda_getCurrentRawStream", None)
+
+
 def _stream() -> c_void_p:
+    """torch's current stream as a raw handle (by torch's own short way where it has one: a step makes hundreds of
+    launches and each asks)."""
+    if _raw_stream is not None:
+        return c_void_p(_raw_stream(torch.cuda.current_device()))
     return c_void_p(torch.cuda.current_stream().cuda_stream)
 
 
@@ -455,6 +462,15 @@ def fa_prefill(q, cache, block_table, cu_q, kv_len, out, first_entry: int, n_ent
 USE_TMA_ATTENTION = os.environ.get("REINFER_B200_TMA_ATTENTION", "1") != "0"
 ATTN_CLUSTER_MERGE = os.environ.get("REINFER_B200_ATTN_CLUSTER", "1") != "0"
 USE_TC_ATTENTION = os.environ.get("REINFER_B200_TC_ATTENTION", "1") != "0"
+MIXED_OVERLAP = os.environ.get("REINFER_B200_MIXED_OVERLAP", "1") != "0"   # decode attention beside the portions' attention
+_side_streams: dict = {}
+
+
+def _side_stream(device) -> "torch.cuda.Stream":
+    key = torch.device(device).index or 0
+    if key not in _side_streams:
+        _side_streams[key] = torch.cuda.Stream(device=device)
+    return _side_streams[key]
 def decode_splits(ctas: int, tiles: int, slots: int = DECODE_SLOTS, head_dim: int = 128, cluster_slots=None,
                   total_tiles: Optional[int] = None) -> int:
     """How many CTAs share one (request, kv head)'s keys: the split count with the least estimated time (ties to
@@ -472,7 +488,11 @@ def decode_splits(ctas: int, tiles: int, slots: int = DECODE_SLOTS, head_dim: in
         resident at once: `cluster_slots(n)` says how many CTAs that is for clusters of more than 8), else a merge
         kernel of about 3.5 us + 0.1 us per split.
     (Whole "waves" of CTAs do not matter: a part-filled last wave just gives its CTAs more bandwidth each.)"""
+    key = None
     if cluster_slots is None:
+        key = (ctas, tiles, slots, head_dim, total_tiles, ATTN_CLUSTER_MERGE)
+        if key in _splits_memo:
+            return _splits_memo[key]
         cluster_slots = lambda n: decode_cluster_slots(head_dim, n)
     if total_tiles is None:
         total_tiles = ctas * tiles
@@ -496,7 +516,14 @@ def decode_splits(ctas: int, tiles: int, slots: int = DECODE_SLOTS, head_dim: in
         cost = max(t_bw, t_lat) + merge
         if best_cost is None or cost < best_cost - 1e-9:
             best, best_cost = n, cost
+    if key is not None:
+        if len(_splits_memo) > 4096:
+            _splits_memo.clear()
+        _splits_memo[key] = best
     return best
+
+
+_splits_memo: dict = {}
 
 
 def attention(ctx, q: torch.Tensor, cache: torch.Tensor, group, out: torch.Tensor, QH: int, KH: int, d: int,
@@ -527,15 +554,32 @@ def attention(ctx, q: torch.Tensor, cache: torch.Tensor, group, out: torch.Tenso
     _need(q.is_contiguous() and out.is_contiguous() and cache.is_contiguous() and group.block_table.is_contiguous(),
           "attention: contiguous")
     gc = fa_group_chunk(QH // KH)
+    joined = None
     if n_dec:
         ctas = n_dec * KH * (QH // KH // gc)
-        tiles = -(-ctx.max_kv_len // 64)
         pairs = KH * (QH // KH // gc)
+        tiles = ctx.decode_kv_tiles[1] if ctx.decode_kv_tiles else -(-ctx.max_kv_len // 64)
         total = ctx.decode_kv_tiles[0] * pairs if ctx.decode_kv_tiles else None
         n_splits = decode_splits(ctas, tiles, head_dim=d, total_tiles=total)
         decode = fa_decode_tma if (tma_pages(group.page_size) and USE_TMA_ATTENTION) else fa_decode
-        decode(q, cache, group.block_table, ctx.cu_q, ctx.kv_len, out, 0, n_dec, 0, n_splits, QH, KH, d,
-               group.page_size, window, scale, work=dec_work)
+        if E > n_dec and MIXED_OVERLAP and _profiler is None and not torch.cuda.is_current_stream_capturing():
+            # A step with prompt portions beside decoding requests: the two attention kernels read the same inputs
+            # and write different rows, and the decoding requests' kernel leaves most SMs idle (a few CTAs with long
+            # chains).  It runs on a stream of its own beside the portions' kernel; the main stream goes on when
+            # both are done.
+            main = torch.cuda.current_stream()
+            ready = torch.cuda.Event()
+            ready.record(main)
+            side = _side_stream(q.device)
+            side.wait_event(ready)
+            with torch.cuda.stream(side):
+                decode(q, cache, group.block_table, ctx.cu_q, ctx.kv_len, out, 0, n_dec, 0, n_splits, QH, KH, d,
+                       group.page_size, window, scale, work=dec_work)
+                joined = torch.cuda.Event()
+                joined.record(side)
+        else:
+            decode(q, cache, group.block_table, ctx.cu_q, ctx.kv_len, out, 0, n_dec, 0, n_splits, QH, KH, d,
+                   group.page_size, window, scale, work=dec_work)
     if E > n_dec and d == 128 and USE_TC_ATTENTION and USE_TMA_ATTENTION and tma_pages(group.page_size):
         fa_prefill_tc(q, cache, group.block_table, ctx.cu_q, ctx.kv_len, out, n_dec, E - n_dec,
                       [ctx.q_start[e + 1] - ctx.q_start[e] for e in range(n_dec, E)], QH, KH, d, group.page_size, window, scale,
@@ -546,6 +590,8 @@ def attention(ctx, q: torch.Tensor, cache: torch.Tensor, group, out: torch.Tenso
         prefill = fa_prefill_tma if (tma_pages(group.page_size) and USE_TMA_ATTENTION) else fa_prefill
         prefill(q, cache, group.block_table, ctx.cu_q, ctx.kv_len, out, n_dec, E - n_dec, n_tiles, QH, KH, d,
                 group.page_size, window, scale, work=pre_work)
+    if joined is not None:
+        torch.cuda.current_stream().wait_event(joined)
 
 
 def sample(logits: torch.Tensor, row_idx: Optional[torch.Tensor], params: torch.Tensor, history: Optional[torch.Tensor],
