@@ -378,19 +378,39 @@ struct TcPersistShared {
     unsigned long long acc_empty[2];
     uint32_t tmem_base;
     int abort_flag;
+    __align__(16) float head_w[2][128];      // MODE 3: the q and k norm weights
+};
+
+// MODE 3 of the persistent kernel: the product is the attention's q/k/v projection with heads of 128, and a tile's 256
+// features are two whole heads of its 128 tokens.  The epilogue then does what a kernel of its own did on the rounded
+// projection (elementwise.cu, qknorm_rope_append): per head the RMS norm over its 128 features with the q or k weights,
+// the half-split rotation by the step's table of cosines and sines, and the store - query heads to q_out [T, QH, 128],
+// key and value heads into the token's slot of the layer's cache pages.  A thread holds its token's whole head in its
+// accumulator lane, so norm and rotation need no exchange; and the projection never goes to memory.
+struct TcHeads {
+    bf16* q_out;
+    bf16* cache;                 // the layer's [pages, 2, KH, page_size, 128]
+    const int* kv_slot;          // [T] page * page_size + offset of each token, -1: store no key or value
+    const float2* cs_table;      // [T, 64] (cos, sin) of each token's angles
+    const void* q_w;             // [128] norm weights (w_f32: float, else bfloat16)
+    const void* k_w;
+    int w_f32, QH, KH, page_size;
+    float eps;
 };
 
 template <int BN, int STAGES, int MODE, int ROWS = 2 * TC_BM>
 __global__ void __launch_bounds__(TC_THREADS, 1)
 gemm_tc_persistent_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_x,
-                          void* __restrict__ C, int T, int N, int K, long long ldc, int out_mode, int t_tiles, int n_tiles) {
+                          void* __restrict__ C, int T, int N, int K, long long ldc, int out_mode, int t_tiles, int n_tiles,
+                          TcHeads hd) {
     // MODE 0: a tile is 128 features (the M operand) x BN tokens.  MODE 1 (the gated pair) and MODE 2: a tile is 128
     // tokens (the M operand) x ROWS weight rows (the N operand; a multiple of 32 up to 256): ROWS / 2 gate rows and the
     // ROWS / 2 up rows of the same features, or ROWS features.  A lane of the accumulator is then a token, and the
     // epilogue writes 16 features of it at a time.  Fewer rows leave room for a stage more.
-    constexpr bool DUAL = MODE == 1, FLIP = MODE != 0;
+    constexpr bool DUAL = MODE == 1, FLIP = MODE != 0, HEADS = MODE == 3;
+    static_assert(!HEADS || ROWS == 2 * TC_BM, "two heads of 128 a tile");
     static_assert(ROWS % 32 == 0 && ROWS >= 32 && ROWS <= 2 * TC_BM, "rows of the N operand");
-    constexpr int FEATS = MODE == 2 ? ROWS : MODE == 1 ? ROWS / 2 : TC_BM;   // features per tile
+    constexpr int FEATS = (MODE == 2 || MODE == 3) ? ROWS : MODE == 1 ? ROWS / 2 : TC_BM;   // features per tile
     RB_TL(DUAL ? 9 : 8);
     extern __shared__ __align__(1024) unsigned char smem_raw[];
     constexpr uint32_t W1_BYTES = (FLIP ? ROWS / 2 : TC_BM) * TC_BK * 2;     // the gate rows (DUAL), or half of the rows
@@ -528,6 +548,12 @@ gemm_tc_persistent_kernel(const __grid_constant__ CUtensorMap map_w, const __gri
         pdl_wait();
         int local = 0;
         const bool vec_ok = (ldc % 8 == 0) && (((uintptr_t)C & 15) == 0);
+        if (HEADS) {                                               // the norm weights, once, for the four epilogue warps
+            const int i = threadIdx.x - 64;                        // 0..127
+            sh->head_w[0][i] = hd.w_f32 ? ((const float*)hd.q_w)[i] : __bfloat162float(((const bf16*)hd.q_w)[i]);
+            sh->head_w[1][i] = hd.w_f32 ? ((const float*)hd.k_w)[i] : __bfloat162float(((const bf16*)hd.k_w)[i]);
+            asm volatile("bar.sync 1, 128;" ::: "memory");
+        }
         for (int tile = blockIdx.x; tile < total_tiles; tile += gridDim.x, ++local) {
             const int a = local & 1;
             const int t0 = (tile % t_tiles) * BN, n0 = (tile / t_tiles) * FEATS;
@@ -565,6 +591,95 @@ gemm_tc_persistent_kernel(const __grid_constant__ CUtensorMap map_w, const __gri
 #pragma unroll
                             for (int j = 0; j < 16; ++j) if (n0 + c0 + j < N) row[c0 + j] = ov[j];
                         }
+                    }
+                }
+            } else if (HEADS) {
+                const int tok = t0 + q * 32 + lane;
+                const bool live = tok < T;
+                const int slot = live && hd.kv_slot ? hd.kv_slot[tok] : -1;
+                const float2* cs = hd.cs_table + (size_t)(live ? tok : 0) * 64;
+#pragma unroll 1
+                for (int hh = 0; hh < 2; ++hh) {
+                    const int head = n0 / 128 + hh;                       // of QH + 2 KH heads: queries, keys, values
+                    if (head >= hd.QH + 2 * hd.KH) break;
+                    const uint32_t hcol = acc + (uint32_t)(hh * 128);
+                    const int kind = head < hd.QH ? 0 : head < hd.QH + hd.KH ? 1 : 2;
+                    bf16* dst = nullptr;
+                    if (kind == 0) {
+                        if (live) dst = hd.q_out + ((size_t)tok * hd.QH + head) * 128;
+                    } else if (slot >= 0) {
+                        const int kh = head - hd.QH - (kind == 2 ? hd.KH : 0);
+                        const size_t page = (size_t)(slot / hd.page_size), off = (size_t)(slot % hd.page_size);
+                        dst = hd.cache + (((page * 2 + (kind == 2 ? 1 : 0)) * hd.KH + kh) * hd.page_size + off) * 128;
+                    }
+                    if (kind == 2) {
+#pragma unroll 1
+                        for (int c0 = 0; c0 < 128; c0 += 16) {
+                            uint32_t r[16];
+                            tc_ld16(hcol + (uint32_t)c0, r);
+                            tc_ld_wait();
+                            if (!dst) continue;
+                            uint32_t o[8];
+#pragma unroll
+                            for (int j = 0; j < 8; ++j) {
+                                const __nv_bfloat162 v = __floats2bfloat162_rn(__uint_as_float(r[2 * j]), __uint_as_float(r[2 * j + 1]));
+                                o[j] = *(const uint32_t*)&v;
+                            }
+                            *(uint4*)(dst + c0) = make_uint4(o[0], o[1], o[2], o[3]);
+                            *(uint4*)(dst + c0 + 8) = make_uint4(o[4], o[5], o[6], o[7]);
+                        }
+                        continue;
+                    }
+                    // the head as the separate kernel sees it: rounded to bfloat16 first
+                    float ss = 0.0f;
+#pragma unroll 1
+                    for (int c0 = 0; c0 < 128; c0 += 16) {
+                        uint32_t r[16];
+                        tc_ld16(hcol + (uint32_t)c0, r);
+                        tc_ld_wait();
+#pragma unroll
+                        for (int j = 0; j < 16; ++j) {
+                            const float v = __bfloat162float(__float2bfloat16_rn(__uint_as_float(r[j])));
+                            ss = fmaf(v, v, ss);
+                        }
+                    }
+                    const float rstd = 1.0f / sqrtf(ss / 128.0f + hd.eps);
+                    const float4* wv = reinterpret_cast<const float4*>(sh->head_w[kind]);
+                    const float4* cs4 = reinterpret_cast<const float4*>(cs);       // two (cos, sin) pairs each
+#pragma unroll 1
+                    for (int c0 = 0; c0 < 64; c0 += 16) {
+                        uint32_t lo[16], hi[16];
+                        tc_ld16(hcol + (uint32_t)c0, lo);
+                        tc_ld16(hcol + (uint32_t)(64 + c0), hi);
+                        float4 ang[8];                                      // this token's 16 angles of the chunk
+#pragma unroll
+                        for (int j = 0; j < 8; ++j) ang[j] = cs4[c0 / 2 + j];
+                        tc_ld_wait();
+                        if (!dst) continue;
+                        uint32_t ol[8], oh[8];
+#pragma unroll
+                        for (int j = 0; j < 4; ++j) {                       // four features of each half a trip
+                            const float4 wl = wv[c0 / 4 + j], wh = wv[16 + c0 / 4 + j];
+                            const float wls[4] = {wl.x, wl.y, wl.z, wl.w}, whs[4] = {wh.x, wh.y, wh.z, wh.w};
+                            const float cc[4] = {ang[2 * j].x, ang[2 * j].z, ang[2 * j + 1].x, ang[2 * j + 1].z};
+                            const float sn[4] = {ang[2 * j].y, ang[2 * j].w, ang[2 * j + 1].y, ang[2 * j + 1].w};
+                            float xo[4], yo[4];
+#pragma unroll
+                            for (int u = 0; u < 4; ++u) {
+                                const float x = __bfloat162float(__float2bfloat16_rn(__uint_as_float(lo[4 * j + u]))) * rstd * wls[u];
+                                const float y = __bfloat162float(__float2bfloat16_rn(__uint_as_float(hi[4 * j + u]))) * rstd * whs[u];
+                                xo[u] = x * cc[u] - y * sn[u];             // low half: x c - y s
+                                yo[u] = x * sn[u] + y * cc[u];             // high half: y c + x s
+                            }
+                            const __nv_bfloat162 p0 = __floats2bfloat162_rn(xo[0], xo[1]), p1 = __floats2bfloat162_rn(xo[2], xo[3]);
+                            const __nv_bfloat162 r0 = __floats2bfloat162_rn(yo[0], yo[1]), r1 = __floats2bfloat162_rn(yo[2], yo[3]);
+                            ol[2 * j] = *(const uint32_t*)&p0; ol[2 * j + 1] = *(const uint32_t*)&p1;
+                            oh[2 * j] = *(const uint32_t*)&r0; oh[2 * j + 1] = *(const uint32_t*)&r1;
+                        }
+                        *(uint4*)(dst + c0) = make_uint4(ol[0], ol[1], ol[2], ol[3]);
+                        *(uint4*)(dst + c0 + 8) = make_uint4(ol[4], ol[5], ol[6], ol[7]);
+                        *(uint4*)(dst + 64 + c0) = make_uint4(oh[0], oh[1], oh[2], oh[3]);
+                        *(uint4*)(dst + 64 + c0 + 8) = make_uint4(oh[4], oh[5], oh[6], oh[7]);
                     }
                 }
             } else if (FLIP) {
@@ -668,7 +783,7 @@ gemm_tc_persistent_kernel(const __grid_constant__ CUtensorMap map_w, const __gri
 
 template <int BN, int STAGES, int MODE, int ROWS = 2 * TC_BM>
 static int launch_tc_persistent(const CUtensorMap& mw, const CUtensorMap& mx, void* C, int T, int N, int K, long long ldc,
-                                int mode, cudaStream_t s) {
+                                int mode, cudaStream_t s, const TcHeads& hd = TcHeads{}) {
     constexpr size_t smem = (size_t)STAGES * ((MODE ? ROWS : TC_BM) * TC_BK * 2 + BN * TC_BK * 2) + sizeof(TcPersistShared) + 1024;
     static_assert(smem <= 232448, "stages beyond the shared memory of an SM");
     static bool configured = false;
@@ -681,11 +796,11 @@ static int launch_tc_persistent(const CUtensorMap& mw, const CUtensorMap& mx, vo
         cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
         configured = true;
     }
-    const int t_tiles = rb_ceil_div(T, BN), n_tiles = rb_ceil_div(N, MODE == 2 ? ROWS : MODE == 1 ? ROWS / 2 : TC_BM);
+    const int t_tiles = rb_ceil_div(T, BN), n_tiles = rb_ceil_div(N, (MODE == 2 || MODE == 3) ? ROWS : MODE == 1 ? ROWS / 2 : TC_BM);
     const int total = t_tiles * n_tiles;
     const int grid = total < sms ? total : sms;
     return rb_launch(gemm_tc_persistent_kernel<BN, STAGES, MODE, ROWS>, dim3(grid), dim3(TC_THREADS), smem, s, mw, mx, C, T, N, K, ldc,
-                     mode, t_tiles, n_tiles);
+                     mode, t_tiles, n_tiles, hd);
 }
 
 // The gated pair over 65 .. 128 tokens (a decode step of that many requests): one tile per CTA, 128 tokens (the M
@@ -1196,6 +1311,31 @@ extern "C" int rb_gemm_bf16_partials(const void* X, const void* W, float* partia
         case 128: return launch_tc<128, 5, false>(mw, mx, nullptr, partials, wsf, T, N, K, N, 1, -splits, ex, s, true);
         default: return launch_tc<256, 4, false>(mw, mx, nullptr, partials, wsf, T, N, K, N, 1, -splits, ex, s, true);
     }
+}
+
+// The attention's q/k/v projection over a prompt portion with everything that follows it per head: X [T, K] bf16,
+// W [(QH + 2 KH) * 128, K] bf16 (query heads, key heads, value heads); q_out [T, QH, 128] gets the normalised and
+// rotated queries, the layer's cache pages the keys (normalised, rotated) and the values of every token whose kv_slot
+// is not negative.  Heads of 128, the whole head rotated, several token tiles (T > 256): the caller takes the
+// two-kernel way otherwise.
+extern "C" int rb_gemm_qkv_heads(const void* X, const void* W, int T, int K, long long ldx, long long ldw, int QH, int KH,
+                                 void* q_out, void* cache, const int* kv_slot, const void* cs_table, const void* q_w,
+                                 const void* k_w, int w_dtype, float eps, int page_size, void* stream) {
+    if (T <= 256) RB_REFUSE("gemm_qkv_heads: %d tokens (more than 256: the persistent product)", T);
+    if (QH <= 0 || KH <= 0 || K <= 0 || page_size <= 0) RB_REFUSE("gemm_qkv_heads: heads %d/%d, K %d, page %d", QH, KH, K, page_size);
+    if ((ldx % 8) || (ldw % 8) || ((uintptr_t)X & 15) || ((uintptr_t)W & 15))
+        RB_REFUSE("gemm_qkv_heads: TMA needs 16-byte aligned operands and row strides (ldx %lld, ldw %lld)", ldx, ldw);
+    if (!q_out || !cache || !cs_table || !q_w || !k_w) RB_REFUSE("gemm_qkv_heads: q_out, cache, table and both norm weights are needed");
+    if (((uintptr_t)q_out & 15) || ((uintptr_t)cache & 15)) RB_REFUSE("gemm_qkv_heads: destinations must be 16-byte aligned");
+    if (w_dtype != RB_F32 && w_dtype != RB_BF16) RB_REFUSE("gemm_qkv_heads: norm weights of dtype %d", w_dtype);
+    TcHeads hd{};
+    hd.q_out = (bf16*)q_out; hd.cache = (bf16*)cache; hd.kv_slot = kv_slot; hd.cs_table = (const float2*)cs_table;
+    hd.q_w = q_w; hd.k_w = k_w; hd.w_f32 = w_dtype == RB_F32; hd.QH = QH; hd.KH = KH; hd.page_size = page_size; hd.eps = eps;
+    const int N = (QH + 2 * KH) * 128;
+    CUtensorMap mw, mx;
+    if (rb_tensor_map_bf16(W, N, K, ldw, 256, &mw)) return -1;
+    if (rb_tensor_map_bf16(X, T, K, ldx, 128, &mx)) return -1;
+    return launch_tc_persistent<128, 4, 3, 256>(mw, mx, nullptr, T, N, K, 0, 0, (cudaStream_t)stream, hd);
 }
 
 // act[T,F] (bfloat16) = silu(X Wg^T) * (X Wu^T) for Wgu = [Wg; Wu] of shape [2F, K]: one product with two

@@ -661,6 +661,37 @@ def gemm_bf16(a: torch.Tensor, w: torch.Tensor, c: torch.Tensor, accumulate: boo
            2.0 * T * N * K, 2.0 * (T * K + N * K) + T * N * c.element_size())
 
 
+# REINFER_B200_QKV_HEADS=0: the q/k/v projection and the per-head work as two kernels at every size (a development switch).
+QKV_HEADS = os.environ.get("REINFER_B200_QKV_HEADS", "1") != "0"
+
+
+def gemm_qkv_heads(a: torch.Tensor, w_qkv: torch.Tensor, q_out: torch.Tensor, cache: torch.Tensor, kv_slot: torch.Tensor,
+                   cs_table: torch.Tensor, q_w: torch.Tensor, k_w: torch.Tensor, QH: int, KH: int, page_size: int, eps: float) -> bool:
+    """The q/k/v projection of a prompt portion with the per-head work in its epilogue (heads of 128): q_out [T, QH, 128]
+    gets the normalised, rotated queries, the cache pages the keys and values at kv_slot.  cs_table [T, 64, 2] float32
+    from rope_table.  Returns False (and does nothing) where this form does not apply - at most 256 tokens, operands
+    that TMA cannot address - and the caller runs the product and qknorm_rope_append one after the other."""
+    T, K = a.shape
+    if not QKV_HEADS:
+        return False
+    if T <= 256 or a.dtype != torch.bfloat16 or w_qkv.dtype != torch.bfloat16 or q_out.dtype != torch.bfloat16 or cache.dtype != torch.bfloat16:
+        return False
+    if a.stride(1) != 1 or w_qkv.stride(1) != 1 or a.stride(0) % 8 or w_qkv.stride(0) % 8 or a.data_ptr() % 16 or w_qkv.data_ptr() % 16:
+        return False
+    _need(w_qkv.shape == ((QH + 2 * KH) * 128, K), "gemm_qkv_heads: weight shape")
+    _need(q_out.is_contiguous() and tuple(q_out.shape) == (T, QH, 128) and cache.is_contiguous(), "gemm_qkv_heads: q_out [T, QH, 128], cache contiguous")
+    _need(q_w.dtype == k_w.dtype and q_w.numel() == 128 and k_w.numel() == 128 and q_w.is_contiguous() and k_w.is_contiguous(),
+          "gemm_qkv_heads: norm weights [128] of one dtype")
+    _need(cs_table.dtype == torch.float32 and cs_table.is_contiguous() and cs_table.numel() == T * 128, "gemm_qkv_heads: table [T, 64, 2] float32")
+    _need(kv_slot.dtype == torch.int32 and kv_slot.numel() >= T, "gemm_qkv_heads: kv_slot int32 [T]")
+    N = (QH + 2 * KH) * 128
+    _check(lib().rb_gemm_qkv_heads(_p(a), _p(w_qkv), c_int(T), c_int(K), c_longlong(a.stride(0)), c_longlong(w_qkv.stride(0)),
+                                   c_int(QH), c_int(KH), _p(q_out), _p(cache), _p(kv_slot), _p(cs_table), _p(q_w), _p(k_w),
+                                   c_int(dt(q_w)), c_float(eps), c_int(page_size), _stream()),
+           f"gemm+heads {N}x{K}", 2.0 * T * N * K, float(T * K * 2 + N * K * 2 + T * N * 2))
+    return True
+
+
 def gemm_bf16_partials(a: torch.Tensor, w: torch.Tensor, row_scale=None) -> Optional[torch.Tensor]:
     """Partial sums [S, T, N] (float32) of a[T,K] @ w[N,K]^T over S ranges of K, for a consumer that adds them
     up itself (add_rmsnorm with a stacked delta): the split product then needs no reduction of its own, and

@@ -364,6 +364,52 @@ def test_qknorm_rope_append(QH, KH, d, rot, page, dtype, norm):
         assert torch.equal(q2, q_out) and torch.equal(cache2, cache)
 
 
+@pytest.mark.parametrize("T,QH,KH,K,page,wdt", [(300, 4, 2, 264, 16, torch.float32), (700, 5, 1, 520, 64, torch.bfloat16),
+                                                (1027, 32, 8, 1024, 16, torch.bfloat16), (513, 3, 3, 72, 8, torch.float32)])
+def test_qkv_projection_with_the_heads_work_in_its_epilogue(T, QH, KH, K, page, wdt):
+    """The q/k/v projection of a prompt portion that normalises, rotates and stores its heads itself, against the
+    product followed by the kernel that does the same on the rounded projection: the same queries, and the same
+    keys and values in the same slots (slots in a random order, some tokens not stored, ragged last token tile,
+    an odd number of heads so that the last tile holds one head only); nothing else in the cache is touched."""
+    from reinfer_b200 import ops
+    from reinfer_b200.parts.rope import RotaryEncoding
+    d, eps, theta = 128, 1e-6, 1e6
+    N = (QH + 2 * KH) * d
+    x = rnd(T, K, dtype=torch.bfloat16, seed=1)
+    w = rnd(N, K, dtype=torch.bfloat16, scale=0.06, seed=2)
+    qw = (1 + rnd(d, scale=0.1, seed=5)).to(wdt)
+    kw = (1 + rnd(d, scale=0.1, seed=6)).to(wdt)
+    pos = (torch.arange(T, dtype=torch.int32) * 7 % 3000).to(DEV)
+    pages = -(-T // page) + 3
+    perm = torch.randperm(pages * page, generator=torch.Generator().manual_seed(1))[:T].to(torch.int32)
+    perm[5] = -1
+    perm[T - 1] = -1
+    slots = perm.to(DEV)
+    rope = RotaryEncoding(d, theta, d)
+    rope.prepare(DEV)
+    cs = ops.rope_table(pos, rope.inv_freq)
+    # the two-kernel way
+    qkv = torch.empty(T, N, dtype=torch.bfloat16, device=DEV)
+    ops.gemm_bf16(x, w, qkv)
+    cache_ref = torch.full((pages, 2, KH, page, d), 7.0, dtype=torch.bfloat16, device=DEV)
+    q_ref = torch.empty(T, QH, d, dtype=torch.bfloat16, device=DEV)
+    ops.qknorm_rope_append(qkv, qw, kw, rope.inv_freq, pos, slots, q_ref, cache_ref, QH, KH, d, d, page, eps, cs_table=cs)
+    # the one-kernel way
+    cache = torch.full((pages, 2, KH, page, d), 7.0, dtype=torch.bfloat16, device=DEV)
+    q_out = torch.full((T, QH, d), float("nan"), dtype=torch.bfloat16, device=DEV)
+    assert ops.gemm_qkv_heads(x, w, q_out, cache, slots, cs, qw, kw, QH, KH, page, eps)
+    assert ops.kernel_error() == 0
+    assert not torch.isnan(q_out.float()).any()
+    # the same arithmetic on the same rounded projection, but for the order of the sum of squares: a unit of bfloat16
+    qs = q_ref.float().abs().max().item()
+    assert (q_out.float() - q_ref.float()).abs().max().item() <= 8e-3 * qs
+    assert (q_out != q_ref).float().mean().item() < 0.02
+    ks = cache_ref[:, 0].float().abs().max().item()
+    assert (cache[:, 0].float() - cache_ref[:, 0].float()).abs().max().item() <= 8e-3 * ks
+    assert torch.equal(cache[:, 1], cache_ref[:, 1])                        # values are copied as they are
+    assert not ops.gemm_qkv_heads(x[:200], w, q_out[:200], cache, slots, cs[:200], qw, kw, QH, KH, page, eps)   # one token tile: the other way
+
+
 @pytest.mark.parametrize("QH,KH,d,page", [(8, 8, 128, 16), (32, 8, 128, 64), (5, 5, 256, 32), (12, 3, 64, 16), (9, 1, 128, 8), (6, 2, 128, 16)])
 @pytest.mark.parametrize("norm", [True, False])
 @pytest.mark.parametrize("table", [True, False])
