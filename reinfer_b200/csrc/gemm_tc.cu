@@ -81,7 +81,42 @@ struct TcExtra {
     const float* row_sumsq;
     int sumsq_parts;
     float inv_width, eps;
+    // An accumulating product (out_mode 2) that is reduced inside a cluster may also prepare the rows for the RMS norm
+    // that reads the sum next (null: no): prep_rows [T, N] bfloat16 gets (C + product) * prep_w per feature - the norm
+    // without its division - and prep_sumsq [T, N / 128] the sum of squares of the new C over each tile's 128
+    // features, from which the product that reads the rows forms their factor (row_sumsq there).
+    const void* prep_w;
+    int prep_w_f32;
+    bf16* prep_rows;
+    float* prep_sumsq;
+    // The product is the attention's q/k/v projection with heads of 128 (a tile of 128 features is one head), reduced
+    // inside a cluster: the CTAs do the per-head work on their sums themselves (h_q_out null: no) - the RMS norm of
+    // query and key heads with h_q_w / h_k_w (null: none), the half-split rotation by positions[t] * inv_freq, queries
+    // to h_q_out [T, QH, 128], keys and values into the slot h_kv_slot[t] of the layer's cache pages (what
+    // qknorm_rope_append of elementwise.cu does on the stored projection; the sums are rounded to bfloat16 first, as
+    // they are there).
+    bf16* h_q_out;
+    bf16* h_cache;
+    const int* h_kv_slot;
+    const int* h_positions;
+    const float* h_inv_freq;
+    const void* h_q_w;
+    const void* h_k_w;
+    int h_w_f32, h_QH, h_KH, h_page;
+    float h_eps;
 };
+
+// Cosines, sines and norm weights of the four features f4 .. f4 + 3 of a query or key head for token t (heads in the
+// cluster's reduction; weights 1 where the heads have no norm).
+__device__ __forceinline__ void head_angles_weights(const TcExtra& ex, bool is_q, int t, int f4, float* c, float* s, float* w) {
+    const void* wv = is_q ? ex.h_q_w : ex.h_k_w;
+    const float pos = (float)ex.h_positions[t];
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        w[i] = !wv ? 1.0f : ex.h_w_f32 ? ((const float*)wv)[f4 + i] : __bfloat162float(((const bf16*)wv)[f4 + i]);
+        sincosf(pos * ex.h_inv_freq[(f4 & 63) + i], &s[i], &c[i]);
+    }
+}
 
 // out_mode 0: C = acc as bf16; 1: C = acc as float; 2: C(float) += acc; 3: workspace partial (float, [split][T][N]).
 // csplit > 1: the grid.z CTAs of one tile are a cluster; out_mode (0..2) is applied to the sum over the cluster.
@@ -129,6 +164,9 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
     const uint32_t tmem = sh->tmem_base;
     if (threadIdx.x == 0) TL(1);
     int issued = 0;                                   // producer: k-blocks whose loads were issued
+    // heads in the cluster's reduction: what an epilogue thread needs for its first token, fetched while the weights stream
+    float hp_c[4] = {1.f, 1.f, 1.f, 1.f}, hp_s[4] = {0.f, 0.f, 0.f, 0.f}, hp_w[4] = {1.f, 1.f, 1.f, 1.f};
+    int hp_slot = -1;
 
     // The two issuing warps stay converged (every lane walks the loop and waits at the barriers) and lane 0 issues
     // through predicated instructions: an issuing lane alone inside a branch pays about a hundred cycles more for
@@ -194,6 +232,14 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
         // epilogue: warp w may read tensor-memory lanes 32*(w%4) .. +31
         const int q = warp & 3;
         const int feat = n0 + q * 32 + lane;
+        if (!DUAL && ex.h_q_out && csplit > 1) {
+            // positions, slots, norm weights and frequencies come from before the step: nothing here waits
+            const int et = threadIdx.x - 64, f4 = (et & 31) * 4, cb = split + (et >> 5) * csplit, hh = blockIdx.y;
+            if (cb < BN && t0 + cb < T) {
+                hp_slot = ex.h_kv_slot ? ex.h_kv_slot[t0 + cb] : -1;
+                if (hh < ex.h_QH + ex.h_KH) head_angles_weights(ex, hh < ex.h_QH, t0 + cb, f4, hp_c, hp_s, hp_w);
+            }
+        }
         pdl_wait();                                            // C may still be in use by the kernels before
         for (int idx = threadIdx.x - 64; idx < BN; idx += 128) {
             float f = 1.0f;
@@ -318,8 +364,37 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
                         vb.x += pb[r].x; vb.y += pb[r].y; vb.z += pb[r].z; vb.w += pb[r].w;
                     }
                     const float fa = sh->row_scale[cb0], fb = two ? sh->row_scale[cb1] : 0.0f;
-                    *d0 = make_float4(oa.x + va.x * fa, oa.y + va.y * fa, oa.z + va.z * fa, oa.w + va.w * fa);
-                    if (two) *d1 = make_float4(ob.x + vb.x * fb, ob.y + vb.y * fb, ob.z + vb.z * fb, ob.w + vb.w * fb);
+                    const float4 na = make_float4(oa.x + va.x * fa, oa.y + va.y * fa, oa.z + va.z * fa, oa.w + va.w * fa);
+                    const float4 nb = make_float4(ob.x + vb.x * fb, ob.y + vb.y * fb, ob.z + vb.z * fb, ob.w + vb.w * fb);
+                    *d0 = na;
+                    if (two) *d1 = nb;
+                    if (ex.prep_rows) {
+                        // the warp holds the tile's 128 features of one token (two tokens): the next norm's rows and
+                        // this tile's part of the sum of squares
+                        float4 w;
+                        if (ex.prep_w_f32) w = *reinterpret_cast<const float4*>((const float*)ex.prep_w + feat);
+                        else {
+                            const uint2 wb = *reinterpret_cast<const uint2*>((const bf16*)ex.prep_w + feat);
+                            const float2 w01 = __bfloat1622float2(*(const __nv_bfloat162*)&wb.x), w23 = __bfloat1622float2(*(const __nv_bfloat162*)&wb.y);
+                            w = make_float4(w01.x, w01.y, w23.x, w23.y);
+                        }
+                        float sa = na.x * na.x + na.y * na.y + na.z * na.z + na.w * na.w;
+                        float sb = nb.x * nb.x + nb.y * nb.y + nb.z * nb.z + nb.w * nb.w;
+#pragma unroll
+                        for (int o = 16; o > 0; o >>= 1) {
+                            sa += __shfl_xor_sync(0xffffffffu, sa, o);
+                            sb += __shfl_xor_sync(0xffffffffu, sb, o);
+                        }
+                        const int parts = N / TC_BM;
+                        const __nv_bfloat162 a01 = __floats2bfloat162_rn(na.x * w.x, na.y * w.y), a23 = __floats2bfloat162_rn(na.z * w.z, na.w * w.w);
+                        *reinterpret_cast<uint2*>(ex.prep_rows + (size_t)(t0 + cb0) * N + feat) = make_uint2(*(const uint32_t*)&a01, *(const uint32_t*)&a23);
+                        if (lane == 0) ex.prep_sumsq[(size_t)(t0 + cb0) * parts + blockIdx.y] = sa;
+                        if (two) {
+                            const __nv_bfloat162 b01 = __floats2bfloat162_rn(nb.x * w.x, nb.y * w.y), b23 = __floats2bfloat162_rn(nb.z * w.z, nb.w * w.w);
+                            *reinterpret_cast<uint2*>(ex.prep_rows + (size_t)(t0 + cb1) * N + feat) = make_uint2(*(const uint32_t*)&b01, *(const uint32_t*)&b23);
+                            if (lane == 0) ex.prep_sumsq[(size_t)(t0 + cb1) * parts + blockIdx.y] = sb;
+                        }
+                    }
                 }
             } else
             for (int cb = split + tsub * csplit; cb < BN && t0 + cb < T; cb += 4 * csplit) {
@@ -336,6 +411,45 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
                 const float f = sh->row_scale[cb];
 #pragma unroll
                 for (int i = 0; i < 4; ++i) v[i] *= f;
+                if (!DUAL && ex.h_q_out) {
+                    // the warp holds one head of token t: lanes 0-15 the low half (four features each), lane ^ 16 the partner
+                    const int t = t0 + cb, hh = blockIdx.y;
+                    const int kind = hh < ex.h_QH ? 0 : hh < ex.h_QH + ex.h_KH ? 1 : 2;
+                    const bool first = cb == split + tsub * csplit;          // what was fetched before the weights arrived
+                    const int slot = first ? hp_slot : ex.h_kv_slot ? ex.h_kv_slot[t] : -1;
+                    if (!first && kind < 2) head_angles_weights(ex, kind == 0, t, f4, hp_c, hp_s, hp_w);
+#pragma unroll
+                    for (int i = 0; i < 4; ++i) v[i] = __bfloat162float(__float2bfloat16_rn(v[i]));
+                    bf16* dst = nullptr;
+                    if (kind == 0) dst = ex.h_q_out + ((size_t)t * ex.h_QH + hh) * 128;
+                    else if (slot >= 0) {
+                        const int page = slot / ex.h_page, off = slot % ex.h_page;
+                        const int kh = kind == 1 ? hh - ex.h_QH : hh - ex.h_QH - ex.h_KH;
+                        dst = ex.h_cache + ((((size_t)page * 2 + (kind - 1)) * ex.h_KH + kh) * ex.h_page + off) * 128;
+                    }
+                    float o[4] = {v[0], v[1], v[2], v[3]};
+                    if (kind < 2) {
+                        if (kind == 0 ? ex.h_q_w : ex.h_k_w) {
+                            float ss = v[0] * v[0] + v[1] * v[1] + v[2] * v[2] + v[3] * v[3];
+#pragma unroll
+                            for (int sft = 16; sft > 0; sft >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, sft);
+                            const float rstd = 1.0f / sqrtf(ss / 128.0f + ex.h_eps);
+#pragma unroll
+                            for (int i = 0; i < 4; ++i) v[i] = v[i] * rstd * hp_w[i];
+                        }
+                        const bool low = f4 < 64;
+#pragma unroll
+                        for (int i = 0; i < 4; ++i) {
+                            const float other = __shfl_xor_sync(0xffffffffu, v[i], 16);
+                            o[i] = low ? v[i] * hp_c[i] - other * hp_s[i] : other * hp_s[i] + v[i] * hp_c[i];
+                        }
+                    }
+                    if (dst) {
+                        const __nv_bfloat162 p01 = __floats2bfloat162_rn(o[0], o[1]), p23 = __floats2bfloat162_rn(o[2], o[3]);
+                        *reinterpret_cast<uint2*>(dst + f4) = make_uint2(*(const uint32_t*)&p01, *(const uint32_t*)&p23);
+                    }
+                    continue;
+                }
                 if (DUAL) {
                     float u[4] = {part2[0].x, part2[0].y, part2[0].z, part2[0].w};
 #pragma unroll
@@ -1175,6 +1289,9 @@ static int tc_extra(TcExtra* ex, const void* next_w, long long next_bytes, const
     ex->next_w = next_w; ex->next_bytes = next_w ? next_bytes : 0;
     ex->row_sumsq = row_sumsq; ex->sumsq_parts = sumsq_parts;
     ex->inv_width = row_sumsq ? 1.0f / (float)norm_width : 0.0f; ex->eps = norm_eps;
+    ex->prep_w = nullptr; ex->prep_w_f32 = 0; ex->prep_rows = nullptr; ex->prep_sumsq = nullptr;
+    ex->h_q_out = nullptr; ex->h_cache = nullptr; ex->h_kv_slot = nullptr; ex->h_positions = nullptr; ex->h_inv_freq = nullptr;
+    ex->h_q_w = ex->h_k_w = nullptr; ex->h_w_f32 = 0; ex->h_QH = ex->h_KH = 0; ex->h_page = 1; ex->h_eps = 0.0f;
     return 0;
 }
 
@@ -1258,6 +1375,89 @@ extern "C" int rb_gemm_bf16(const void* X, const void* W, void* C, int c_dtype, 
         case 64: return launch_tc<64, 4, false>(mw, mx, C, ws, ws_floats, T, N, K, ldc, mode, force_splits, ex, s);
         case 128: return launch_tc<128, 5, false>(mw, mx, C, ws, ws_floats, T, N, K, ldc, mode, force_splits, ex, s);
         default: return launch_tc<256, 4, false>(mw, mx, C, ws, ws_floats, T, N, K, ldc, mode, force_splits, ex, s);
+    }
+}
+
+// C (float, [T, N], row stride ldc) += X W^T for one token tile, reduced inside a cluster, with the rows of the RMS norm
+// that reads C next prepared by the same CTAs: prep_rows [T, N] bfloat16 = new C * norm_w (the norm without its
+// division), prep_sumsq [T, N / 128] = the new C's sum of squares by tiles of 128 features.  One token tile, N a
+// multiple of 128; refused otherwise (the caller then runs the product and the norm one after the other).
+extern "C" int rb_gemm_bf16_residual_norm(const void* X, const void* W, float* C, int T, int N, int K, long long ldx, long long ldw,
+                                          long long ldc, const void* norm_w, int norm_w_dtype, void* prep_rows, float* prep_sumsq,
+                                          const void* next_w, long long next_bytes, const float* row_sumsq, int sumsq_parts,
+                                          int norm_width, float norm_eps, void* stream) {
+    if (T <= 0 || N <= 0) return 0;
+    if (K <= 0) RB_REFUSE("gemm: K=%d", K);
+    if (T > 256 || N % TC_BM || K < 2 * TC_BK)
+        RB_REFUSE("gemm_residual_norm: one token tile, features in tiles of 128, two blocks of K at least (T %d, N %d, K %d)", T, N, K);
+    if ((ldc & 3) || ((uintptr_t)C & 15) || ((uintptr_t)prep_rows & 7) || ((uintptr_t)norm_w & 15))
+        RB_REFUSE("gemm_residual_norm: 16-byte aligned sum and weight, rows 8-byte aligned (ldc %lld)", ldc);
+    if ((ldx % 8) || (ldw % 8) || ((uintptr_t)X & 15) || ((uintptr_t)W & 15))
+        RB_REFUSE("gemm: TMA needs 16-byte aligned operands and row strides (ldx %lld, ldw %lld)", ldx, ldw);
+    if (!norm_w || !prep_rows || !prep_sumsq) RB_REFUSE("gemm: the norm's weight and both of its outputs are needed");
+    if (norm_w_dtype != RB_F32 && norm_w_dtype != RB_BF16) RB_REFUSE("gemm: norm weight of dtype %d", norm_w_dtype);
+    TcExtra ex;
+    if (tc_extra(&ex, next_w, next_bytes, row_sumsq, sumsq_parts, norm_width, norm_eps, T)) return -1;
+    ex.prep_w = norm_w; ex.prep_w_f32 = norm_w_dtype == RB_F32; ex.prep_rows = (bf16*)prep_rows; ex.prep_sumsq = prep_sumsq;
+    cudaStream_t s = (cudaStream_t)stream;
+    const int bn = tc_bn(T);
+    CUtensorMap mw, mx;
+    if (rb_tensor_map_bf16(W, N, K, ldw, TC_BM, &mw)) return -1;
+    if (rb_tensor_map_bf16(X, T, K, ldx, bn, &mx)) return -1;
+    // the cluster's size as the plain product would choose it, but never one CTA alone: the reduction's code does the norm's part
+    const int total_kb = rb_ceil_div(K, TC_BK), tiles = rb_ceil_div(N, TC_BM);
+    int sp = tc_env_splits(N, K);
+    switch (bn) {
+#define RB_CASE(BN_, ST_) \
+        case BN_: { \
+            constexpr size_t smem = (size_t)ST_ * (TC_BM * TC_BK * 2 + BN_ * TC_BK * 2) + sizeof(TcShared) + 1024; \
+            if (!sp) sp = tc_choose_splits<BN_, ST_, false>(tiles, total_kb, smem, nullptr); \
+            if (sp < 2) sp = 2; \
+            return launch_tc<BN_, ST_, false>(mw, mx, C, nullptr, 0, T, N, K, ldc, 2, sp, ex, s); }
+        RB_CASE(16, 6) RB_CASE(32, 5) RB_CASE(64, 4) RB_CASE(128, 5)
+        default: RB_CASE(256, 4)
+#undef RB_CASE
+    }
+}
+
+// The q/k/v projection of a decode step's few rows with the per-head work done by the cluster that reduces it (heads of
+// 128, the whole head rotated; see TcExtra): X [T, K] bf16, W [(QH + 2 KH) * 128, K] bf16.  One token tile.
+extern "C" int rb_gemm_qkv_heads_stream(const void* X, const void* W, int T, int K, long long ldx, long long ldw, int QH, int KH,
+                                        void* q_out, void* cache, const int* kv_slot, const int* positions, const float* inv_freq,
+                                        const void* q_w, const void* k_w, int w_dtype, float eps, int page_size,
+                                        const void* next_w, long long next_bytes, const float* row_sumsq, int sumsq_parts,
+                                        int norm_width, float norm_eps, void* stream) {
+    if (T <= 0) return 0;
+    if (T > 256 || K < 2 * TC_BK) RB_REFUSE("gemm_qkv_heads_stream: one token tile and two blocks of K at least (T %d, K %d)", T, K);
+    if (QH <= 0 || KH <= 0 || page_size <= 0) RB_REFUSE("gemm_qkv_heads_stream: heads %d/%d, page %d", QH, KH, page_size);
+    if ((ldx % 8) || (ldw % 8) || ((uintptr_t)X & 15) || ((uintptr_t)W & 15))
+        RB_REFUSE("gemm: TMA needs 16-byte aligned operands and row strides (ldx %lld, ldw %lld)", ldx, ldw);
+    if (!q_out || !positions || !inv_freq || (!cache && kv_slot)) RB_REFUSE("gemm_qkv_heads_stream: q_out, positions, inv_freq (and a cache for the slots) are needed");
+    if (((uintptr_t)q_out & 7) || ((uintptr_t)cache & 7)) RB_REFUSE("gemm_qkv_heads_stream: destinations must be 8-byte aligned");
+    if ((q_w == nullptr) != (k_w == nullptr)) RB_REFUSE("gemm_qkv_heads_stream: q and k norm weights come together");
+    if (q_w && w_dtype != RB_F32 && w_dtype != RB_BF16) RB_REFUSE("gemm_qkv_heads_stream: norm weights of dtype %d", w_dtype);
+    TcExtra ex;
+    if (tc_extra(&ex, next_w, next_bytes, row_sumsq, sumsq_parts, norm_width, norm_eps, T)) return -1;
+    ex.h_q_out = (bf16*)q_out; ex.h_cache = (bf16*)cache; ex.h_kv_slot = kv_slot; ex.h_positions = positions; ex.h_inv_freq = inv_freq;
+    ex.h_q_w = q_w; ex.h_k_w = k_w; ex.h_w_f32 = w_dtype == RB_F32; ex.h_QH = QH; ex.h_KH = KH; ex.h_page = page_size; ex.h_eps = eps;
+    cudaStream_t s = (cudaStream_t)stream;
+    const int N = (QH + 2 * KH) * 128;
+    const int bn = tc_bn(T);
+    CUtensorMap mw, mx;
+    if (rb_tensor_map_bf16(W, N, K, ldw, TC_BM, &mw)) return -1;
+    if (rb_tensor_map_bf16(X, T, K, ldx, bn, &mx)) return -1;
+    const int total_kb = rb_ceil_div(K, TC_BK), tiles = rb_ceil_div(N, TC_BM);
+    int sp = tc_env_splits(N, K);
+    switch (bn) {
+#define RB_CASE(BN_, ST_) \
+        case BN_: { \
+            constexpr size_t smem = (size_t)ST_ * (TC_BM * TC_BK * 2 + BN_ * TC_BK * 2) + sizeof(TcShared) + 1024; \
+            if (!sp) sp = tc_choose_splits<BN_, ST_, false>(tiles, total_kb, smem, nullptr); \
+            if (sp < 2) sp = 2; \
+            return launch_tc<BN_, ST_, false>(mw, mx, nullptr, nullptr, 0, T, N, K, N, 0, sp, ex, s); }
+        RB_CASE(16, 6) RB_CASE(32, 5) RB_CASE(64, 4) RB_CASE(128, 5)
+        default: RB_CASE(256, 4)
+#undef RB_CASE
     }
 }
 

@@ -692,6 +692,38 @@ def gemm_qkv_heads(a: torch.Tensor, w_qkv: torch.Tensor, q_out: torch.Tensor, ca
     return True
 
 
+def gemm_qkv_heads_stream(a, w_qkv: torch.Tensor, q_out: torch.Tensor, cache: torch.Tensor, kv_slot: Optional[torch.Tensor],
+                          positions: torch.Tensor, inv_freq: torch.Tensor, q_w: Optional[torch.Tensor], k_w: Optional[torch.Tensor],
+                          QH: int, KH: int, page_size: int, eps: float, row_scale=None) -> bool:
+    """The q/k/v projection of a decode step's few rows (heads of 128) whose cluster does the per-head work on its sums:
+    q_out [T, QH, 128] gets the normalised, rotated queries, the cache pages the keys and values at kv_slot (None:
+    nothing is stored).  Returns False (and does nothing) where this form does not apply, and the caller runs the
+    product and qknorm_rope_append one after the other."""
+    T, K = a.shape
+    if not (QKV_HEADS and 0 < T <= STREAMING_TOKENS and K >= 128 and a.dtype == torch.bfloat16 and w_qkv.dtype == torch.bfloat16 and
+            q_out.dtype == torch.bfloat16 and cache.dtype == torch.bfloat16):
+        return False
+    if a.stride(1) != 1 or w_qkv.stride(1) != 1 or a.stride(0) % 8 or w_qkv.stride(0) % 8 or a.data_ptr() % 16 or w_qkv.data_ptr() % 16:
+        return False
+    _need(w_qkv.shape == ((QH + 2 * KH) * 128, K), "gemm_qkv_heads_stream: weight shape")
+    _need(q_out.is_contiguous() and tuple(q_out.shape) == (T, QH, 128) and cache.is_contiguous(), "gemm_qkv_heads_stream: q_out [T, QH, 128], cache contiguous")
+    _need((q_w is None) == (k_w is None), "gemm_qkv_heads_stream: q and k norm weights come together")
+    if q_w is not None:
+        _need(q_w.dtype == k_w.dtype and q_w.numel() == 128 and k_w.numel() == 128 and q_w.is_contiguous() and k_w.is_contiguous(),
+              "gemm_qkv_heads_stream: norm weights [128] of one dtype")
+    _need(inv_freq.dtype == torch.float32 and inv_freq.numel() == 64 and inv_freq.is_contiguous(), "gemm_qkv_heads_stream: inv_freq float32 [64]")
+    _need(positions.dtype == torch.int32 and positions.numel() >= T, "gemm_qkv_heads_stream: positions int32 [T]")
+    _need(kv_slot is None or (kv_slot.dtype == torch.int32 and kv_slot.numel() >= T), "gemm_qkv_heads_stream: kv_slot int32 [T]")
+    N = (QH + 2 * KH) * 128
+    nw, nb = _next_range(w_qkv)
+    _check(lib().rb_gemm_qkv_heads_stream(_p(a), _p(w_qkv), c_int(T), c_int(K), c_longlong(a.stride(0)), c_longlong(w_qkv.stride(0)),
+                                          c_int(QH), c_int(KH), _p(q_out), _p(cache), _p(kv_slot), _p(positions), _p(inv_freq),
+                                          _p(q_w), _p(k_w), c_int(dt(q_w) if q_w is not None else 0), c_float(eps), c_int(page_size),
+                                          nw, nb, *_row_scale_args(row_scale, T), _stream()),
+           f"gemm+heads {N}x{K}", 2.0 * T * N * K, float(T * K * 2 + N * K * 2 + T * N * 2))
+    return True
+
+
 def gemm_bf16_partials(a: torch.Tensor, w: torch.Tensor, row_scale=None) -> Optional[torch.Tensor]:
     """Partial sums [S, T, N] (float32) of a[T,K] @ w[N,K]^T over S ranges of K, for a consumer that adds them
     up itself (add_rmsnorm with a stacked delta): the split product then needs no reduction of its own, and
@@ -712,6 +744,36 @@ def gemm_bf16_partials(a: torch.Tensor, w: torch.Tensor, row_scale=None) -> Opti
                                        *_row_scale_args(row_scale, T), _stream()), f"gemm {N}x{K}",
            2.0 * T * N * K, 2.0 * (T * K + N * K) + 4.0 * S * T * N)
     return out
+
+
+# REINFER_B200_PRODUCT_NORM=0: a decode step's o and down projections never prepare the next norm's rows themselves
+# (they leave partial sums, or add into the residual, and the norm runs as a kernel of its own).
+PRODUCT_NORM = os.environ.get("REINFER_B200_PRODUCT_NORM", "1") != "0"
+
+
+def gemm_bf16_residual_norm(a: torch.Tensor, w: torch.Tensor, residual: torch.Tensor, norm_w: torch.Tensor, row_scale=None):
+    """residual[T,N] (float32) += a[T,K] @ w[N,K]^T for a decode step's few rows, the product reduced inside a
+    cluster whose CTAs also prepare what the RMS norm with weight norm_w would make of the new residual: returns
+    (rows, sumsq) as residual_rowscale does (rows = bfloat16(residual * norm_w), sumsq [T, N/128] the sum of squares
+    by tiles of 128 columns), or None (and does nothing) where this form does not apply."""
+    T, K = a.shape
+    N = w.shape[0]
+    _need(w.shape[1] == K and tuple(residual.shape) == (T, N), "gemm: shapes")
+    if not (PRODUCT_NORM and 0 < T <= STREAMING_TOKENS and a.dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and
+            residual.dtype == torch.float32 and N % 128 == 0 and K >= 128 and norm_w.numel() == N and norm_w.is_contiguous() and
+            norm_w.dtype in (torch.float32, torch.bfloat16) and norm_w.data_ptr() % 16 == 0):
+        return None
+    if a.stride(1) != 1 or w.stride(1) != 1 or a.stride(0) % 8 or w.stride(0) % 8 or a.data_ptr() % 16 or w.data_ptr() % 16 or \
+            residual.stride(1) != 1 or residual.stride(0) % 4 or residual.data_ptr() % 16:
+        return None
+    rows = torch.empty((T, N), dtype=torch.bfloat16, device=a.device)
+    sumsq = torch.empty((T, N // 128), dtype=torch.float32, device=a.device)
+    nw, nb = _next_range(w)
+    _check(lib().rb_gemm_bf16_residual_norm(_p(a), _p(w), _p(residual), c_int(T), c_int(N), c_int(K), c_longlong(a.stride(0)),
+                                            c_longlong(w.stride(0)), c_longlong(residual.stride(0)), _p(norm_w), c_int(dt(norm_w)),
+                                            _p(rows), _p(sumsq), nw, nb, *_row_scale_args(row_scale, T), _stream()),
+           f"gemm+norm {N}x{K}", 2.0 * T * N * K, 2.0 * (T * K + N * K) + 14.0 * T * N)
+    return rows, sumsq
 
 
 def gemm_bf16_swiglu(a: torch.Tensor, w_gate_up: torch.Tensor, out: torch.Tensor, splits: int = 0, row_scale=None) -> bool:

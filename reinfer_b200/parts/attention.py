@@ -18,7 +18,7 @@ import torch
 
 from .. import ops
 from ..weights.params import ParamSpec
-from .base import Mixer, PagedKVSpec, build_part, register_part
+from .base import Mixer, PagedKVSpec, RowScaled, build_part, register_part
 from .linear import matmul, matmul_into_residual, takes_row_scaled
 from .spec import PartSpec
 
@@ -88,6 +88,16 @@ class Attention(Mixer):
                 cs = ctx.shared[key] = ops.rope_table(ctx.positions, fused[0])
             q = torch.empty((T, QH, d), dtype=xn.dtype, device=xn.device)
             if ops.gemm_qkv_heads(xn, self.w_qkv, q, cache.kv, slots, cs, self.q_norm_w, self.k_norm_w, QH, KH, g.page_size, self.eps):
+                attn = torch.empty((T, QH, d), dtype=xn.dtype, device=xn.device)
+                ops.attention(ctx, q, cache.kv, g, attn, QH, KH, d, self.window or 0, self.scale)
+                return matmul_into_residual(ctx, attn.view(T, QH * d), self.w_o, residual)
+        if fused is not None and d == 128 and fused[1] == d and fused[0] is not None and 0 < T <= ops.STREAMING_TOKENS and \
+                xn.dtype == torch.bfloat16 and (self.q_norm_w is None) == (self.k_norm_w is None):
+            # a decode step's few rows with heads of 128: the cluster that reduces the projection does the per-head work
+            rows, scale = (xn.rows, xn.scale()) if isinstance(xn, RowScaled) else (xn, None)
+            q = torch.empty((T, QH, d), dtype=xn.dtype, device=xn.device)
+            if ops.gemm_qkv_heads_stream(rows, self.w_qkv, q, cache.kv, slots, ctx.positions, fused[0], self.q_norm_w, self.k_norm_w,
+                                         QH, KH, g.page_size, self.eps, row_scale=scale):
                 attn = torch.empty((T, QH, d), dtype=xn.dtype, device=xn.device)
                 ops.attention(ctx, q, cache.kv, g, attn, QH, KH, d, self.window or 0, self.scale)
                 return matmul_into_residual(ctx, attn.view(T, QH * d), self.w_o, residual)

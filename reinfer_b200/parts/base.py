@@ -78,6 +78,15 @@ class RowScaled:
         return (self.sumsq, self.width, self.eps)
 
 
+@dataclass
+class PreparedRows:
+    """What a product that added into the residual stream made for the norm that reads the stream next: that norm's
+    rows without their factor.  Handed on in the place of a sum still to be added; only `norm` can take it."""
+    norm: object
+    rows: torch.Tensor                  # [T, h] bfloat16: the new residual * the norm's weight
+    sumsq: torch.Tensor                 # [T, parts] float32
+
+
 class Part:
     def param_specs(self) -> Dict[str, ParamSpec]:
         return {}

@@ -31,9 +31,26 @@ class PreNormBlock:
         """Runs the layer on the residual stream x (in place).  delta: what the block before left to be
         added to x first.  Returns what this block leaves to be added (None: nothing)."""
         xn = _norm(self.mixer_norm, self.mixer, ctx, x, delta)
-        delta = self.mixer.forward(ctx, xn, x, cache)
-        xn = _norm(self.ffn_norm, self.ffn, ctx, x, delta)
-        return self.ffn.forward(ctx, xn, x)
+        after = getattr(ctx, "norm_after_block", None)
+        ctx.norm_ahead = self.ffn_norm if _prepares(self.ffn_norm, self.ffn) else None
+        try:
+            delta = self.mixer.forward(ctx, xn, x, cache)
+            xn = _norm(self.ffn_norm, self.ffn, ctx, x, delta)
+            ctx.norm_ahead = after
+            return self.ffn.forward(ctx, xn, x)
+        finally:
+            ctx.norm_ahead = None
+
+    def entry_norm(self):
+        """The norm that reads the residual stream first in this block, if the part before this block may do that
+        norm's work in its last product (else None)."""
+        return self.mixer_norm if _prepares(self.mixer_norm, self.mixer) else None
+
+
+def _prepares(norm, reader) -> bool:
+    """Whether a product before `norm` may make the norm's rows itself: the norm knows how and hands rows without
+    their factor to a reader that takes them."""
+    return hasattr(norm, "prepared_by") and getattr(norm, "leaves_row_scale", False) and getattr(reader, "takes_row_scaled", False)
 
 
 def _norm(norm, reader, ctx, x, delta):

@@ -56,6 +56,11 @@ class StepContext:
     layer_caches: Dict[str, LayerCache] = field(default_factory=dict)
     shared: Dict[object, torch.Tensor] = field(default_factory=dict)   # what one layer computed for all (per step)
     defer_residual: bool = False       # parts may return what is to be added to the residual; the next norm adds it
+    # The norm that reads the residual stream next, named by a block (or the model's loop) where the part that runs now
+    # may do that norm's work in its last product and hand its rows on instead of a sum (`matmul_into_residual`);
+    # None: nobody asked.  `norm_after_block`: the same for the last part of a block, set by the loop over the layers.
+    norm_ahead: Optional[object] = None
+    norm_after_block: Optional[object] = None
 
     def empty(self, shape, dtype=None) -> torch.Tensor:
         return torch.empty(shape, dtype=dtype or self.dtype, device=self.device)

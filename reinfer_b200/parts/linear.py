@@ -56,7 +56,15 @@ def matmul_into_residual(ctx, a: torch.Tensor, w: torch.Tensor, residual: torch.
     partial sums) and the product is one of the weight-streaming kind, the product leaves its split
     partial sums [S, T, N] and this returns them: the caller hands them on as its result, and the next
     norm adds them to the residual in a fixed order before it normalises.  Otherwise the product is
-    added to the residual here and None is returned."""
+    added to the residual here and None is returned.
+
+    Where a block named the norm that reads the residual next (ctx.norm_ahead) and that norm can have its rows made
+    by the product itself, the product adds into the residual and this returns those rows (PreparedRows)."""
+    norm = getattr(ctx, "norm_ahead", None)
+    if norm is not None and a.shape[0] and a.dtype == torch.bfloat16 and w.dtype == torch.bfloat16:
+        made = norm.prepared_by(ctx, a, w, residual)
+        if made is not None:
+            return made
     if getattr(ctx, "defer_residual", False):
         parts = ops.gemm_bf16_partials(a, w) if a.shape[0] else None
         if parts is not None:

@@ -167,12 +167,17 @@ class Model:
             x = self.embedding.forward(ctx)
             ctx.defer_residual = self._norms_add_partial_sums
             delta = None                        # what a block left to be added to x by the norm that reads x next
-            for i, key in self.run:
+            for n, (i, key) in enumerate(self.run):
                 block = self.layers[i].block
                 if self._norms_add_partial_sums:
+                    # the block that runs next may let this one's last product do its first norm's work
+                    nxt = self.layers[self.run[n + 1][0]].block if n + 1 < len(self.run) else None
+                    entry = getattr(nxt, "entry_norm", None) if getattr(nxt, "hands_on_sums", False) else None
+                    ctx.norm_after_block = entry() if entry is not None else None
                     delta = block.forward(ctx, x, ctx.layer_caches[key], delta)
                 else:
                     block.forward(ctx, x, ctx.layer_caches[key])
+            ctx.norm_after_block = None
             if want_rows is None or want_rows.numel() == 0:
                 return None                     # (a sum still owed to x is dropped with x)
             xn = self.final_norm.forward(ctx, x, delta=delta, row_idx=want_rows)

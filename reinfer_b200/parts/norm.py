@@ -7,7 +7,7 @@ import torch
 
 from .. import ops
 from ..weights.params import ParamSpec
-from .base import Norm, RowScaled, register_part
+from .base import Norm, PreparedRows, RowScaled, register_part
 
 
 class RMSNorm(Norm):
@@ -24,7 +24,20 @@ class RMSNorm(Norm):
     def bind(self, tensors):
         self.weight = tensors["weight"]
 
+    def prepared_by(self, ctx, a, w, residual):
+        """residual += a w^T by a product that also makes this norm's rows of the new residual (a decode step's few
+        rows, bfloat16): PreparedRows for forward(..., delta=that, scaled_ok=True), or None where that form does not
+        apply and nothing was done."""
+        if self.weight is None or ctx.dtype != torch.bfloat16 or not ops.DEFER_SUMS or residual.shape[1] != self.width:
+            return None
+        made = ops.gemm_bf16_residual_norm(a, w, residual, self.weight)
+        return None if made is None else PreparedRows(self, made[0], made[1])
+
     def forward(self, ctx, x, out=None, delta=None, row_idx=None, scaled_ok=False):
+        if isinstance(delta, PreparedRows):
+            if delta.norm is not self or not scaled_ok or out is not None or row_idx is not None:
+                raise ValueError("rmsnorm: rows prepared by a product are for the norm and the reader they were made for")
+            return RowScaled(delta.rows, delta.sumsq, self.width, self.eps)
         if scaled_ok and out is None and row_idx is None and ctx.dtype == torch.bfloat16 and ops.DEFER_SUMS and \
                 0 < x.shape[0] <= ops.STREAMING_TOKENS and self.width % 4 == 0 and \
                 (delta is None or delta.dtype == torch.float32):

@@ -195,6 +195,47 @@ def test_norm_whose_division_is_left_to_the_product(T, h, N, n_delta):
     assert ops.kernel_error() == 0
 
 
+@pytest.mark.parametrize("T,K,N", [(1, 256, 128), (8, 4096, 4096), (8, 12288, 4096), (5, 1000 - 8, 384), (33, 520, 1280), (64, 2048, 2560), (100, 1040, 256)])
+@pytest.mark.parametrize("wdt", [torch.float32, torch.bfloat16])
+def test_product_that_prepares_the_next_norm(T, K, N, wdt):
+    """A decode step's product into the residual whose cluster also makes the next norm's rows: the residual gets the
+    product, the rows are the new residual times the norm's weight, and the parts add up to its sum of squares, so
+    that a product told of them gives what normalising first gives.  One token tile only."""
+    from reinfer_b200 import ops
+    eps = 1e-6
+    a = rnd(T, K, dtype=torch.bfloat16, seed=1)
+    w = rnd(N, K, dtype=torch.bfloat16, scale=0.05, seed=2)
+    base = rnd(T, N, seed=3, scale=2.0)
+    gamma = (rnd(N, seed=4).abs() + 0.5).to(wdt)
+    x = base.clone()
+    made = ops.gemm_bf16_residual_norm(a, w, x, gamma)
+    assert (made is None) == (T > ops.STREAMING_TOKENS)
+    if made is None:
+        assert torch.equal(x, base)
+        return
+    rows, sumsq = made
+    want_x = base + a.float() @ w.float().t()
+    assert (x - want_x).abs().max().item() <= 2e-4 * want_x.abs().max().item()
+    assert rows.dtype == torch.bfloat16 and tuple(sumsq.shape) == (T, N // 128)
+    assert (rows.float() - x * gamma.float()).abs().max().item() <= 4e-3 * (x * gamma.float()).abs().max().item()
+    ss = (x.double() ** 2).sum(-1)
+    assert (sumsq.double().sum(-1) - ss).abs().max().item() <= 1e-5 * ss.max().item()
+    xn = rows.float() * torch.rsqrt(ss / N + eps).float()[:, None]
+    w2 = rnd(200, N, dtype=torch.bfloat16, scale=0.05, seed=5)
+    c = torch.empty(T, 200, dtype=torch.float32, device=DEV)
+    ops.gemm_bf16(rows, w2, c, row_scale=(sumsq, N, eps))
+    ref = xn @ w2.float().t()
+    assert (c - ref).abs().max().item() <= 2e-4 * ref.abs().max().item()
+    # a second product in a row, with rows that lack their factor as its own input
+    x2 = base.clone()
+    w3 = rnd(N, N, dtype=torch.bfloat16, scale=0.05, seed=6)
+    made2 = ops.gemm_bf16_residual_norm(rows, w3, x2, gamma, row_scale=(sumsq, N, eps))
+    want2 = base + xn @ w3.float().t()
+    assert (x2 - want2).abs().max().item() <= 3e-4 * want2.abs().max().item()
+    assert (made2[0].float() - x2 * gamma.float()).abs().max().item() <= 4e-3 * (x2 * gamma.float()).abs().max().item()
+    assert ops.kernel_error() == 0
+
+
 def test_gemm_plan_and_prefetch_hint():
     """What the decode product chooses can be asked for; a range to call into L2 changes no result."""
     import ctypes
@@ -408,6 +449,60 @@ def test_qkv_projection_with_the_heads_work_in_its_epilogue(T, QH, KH, K, page, 
     assert (cache[:, 0].float() - cache_ref[:, 0].float()).abs().max().item() <= 8e-3 * ks
     assert torch.equal(cache[:, 1], cache_ref[:, 1])                        # values are copied as they are
     assert not ops.gemm_qkv_heads(x[:200], w, q_out[:200], cache, slots, cs[:200], qw, kw, QH, KH, page, eps)   # one token tile: the other way
+
+
+@pytest.mark.parametrize("T,QH,KH,K,page", [(1, 32, 8, 4096, 16), (8, 32, 8, 4096, 16), (7, 3, 1, 520, 8), (33, 8, 2, 1024, 64), (64, 5, 5, 256, 16)])
+@pytest.mark.parametrize("wdt", [torch.float32, torch.bfloat16, None])
+@pytest.mark.parametrize("scaled", [False, True])
+def test_decode_qkv_projection_whose_cluster_does_the_heads_work(T, QH, KH, K, page, wdt, scaled):
+    """The q/k/v projection of a decode step's rows whose cluster normalises, rotates and stores the heads, against
+    the product followed by the kernel that does the same on the stored projection: the same queries, keys and values
+    in the same slots (with and without norm weights, rows with and without their factor, one token that is not
+    stored, no slots at all); nothing else in the cache is touched."""
+    from reinfer_b200 import ops
+    from reinfer_b200.parts.rope import RotaryEncoding
+    d, eps, theta = 128, 1e-6, 1e6
+    N = (QH + 2 * KH) * d
+    x = rnd(T, K, dtype=torch.bfloat16, seed=1)
+    w = rnd(N, K, dtype=torch.bfloat16, scale=0.06, seed=2)
+    qw = (1 + rnd(d, scale=0.1, seed=5)).to(wdt) if wdt is not None else None
+    kw = (1 + rnd(d, scale=0.1, seed=6)).to(wdt) if wdt is not None else None
+    pos = (torch.arange(T, dtype=torch.int32) * 977 % 30000).to(DEV)
+    pages = -(-T // page) + 3
+    perm = torch.randperm(pages * page, generator=torch.Generator().manual_seed(1))[:T].to(torch.int32)
+    if T > 2:
+        perm[1] = -1
+    slots = perm.to(DEV)
+    rope = RotaryEncoding(d, theta, d)
+    rope.prepare(DEV)
+    scale = None
+    if scaled:
+        sumsq = (rnd(T, 3, seed=9).abs() * K).contiguous()
+        scale = (sumsq, K, eps)
+    for use_slots in (slots, None):
+        qkv = torch.empty(T, N, dtype=torch.bfloat16, device=DEV)
+        ops.gemm_bf16(x, w, qkv, row_scale=scale)
+        cache_ref = torch.full((pages, 2, KH, page, d), 7.0, dtype=torch.bfloat16, device=DEV)
+        q_ref = torch.empty(T, QH, d, dtype=torch.bfloat16, device=DEV)
+        ops.qknorm_rope_append(qkv, qw, kw, rope.inv_freq, pos, use_slots, q_ref, cache_ref, QH, KH, d, d, page, eps)
+        cache = torch.full((pages, 2, KH, page, d), 7.0, dtype=torch.bfloat16, device=DEV)
+        q_out = torch.full((T, QH, d), float("nan"), dtype=torch.bfloat16, device=DEV)
+        assert ops.gemm_qkv_heads_stream(x, w, q_out, cache, use_slots, pos, rope.inv_freq, qw, kw, QH, KH, page, eps, row_scale=scale)
+        assert ops.kernel_error() == 0
+        assert not torch.isnan(q_out.float()).any()
+        qs = q_ref.float().abs().max().item()
+        assert (q_out.float() - q_ref.float()).abs().max().item() <= 8e-3 * qs
+        assert (q_out != q_ref).float().mean().item() < 0.02
+        ks = cache_ref[:, 0].float().abs().max().item()
+        assert (cache[:, 0].float() - cache_ref[:, 0].float()).abs().max().item() <= 8e-3 * ks
+        # values are the rounded sums as they are; the two ways may split K differently, so a sum may round the other way
+        vs = cache_ref[:, 1].float().abs().max().item()
+        assert (cache[:, 1].float() - cache_ref[:, 1].float()).abs().max().item() <= 8e-3 * vs
+        assert (cache[:, 1] != cache_ref[:, 1]).float().mean().item() < 0.02
+        untouched = cache_ref == 7.0
+        assert torch.equal(cache[untouched], cache_ref[untouched])
+    assert not ops.gemm_qkv_heads_stream(x.repeat(70, 1)[:70], w, torch.empty(70, QH, d, dtype=torch.bfloat16, device=DEV), cache, None,
+                                         pos.repeat(70)[:70].contiguous(), rope.inv_freq, qw, kw, QH, KH, page, eps)   # over the streaming size: the other way
 
 
 @pytest.mark.parametrize("QH,KH,d,page", [(8, 8, 128, 16), (32, 8, 128, 64), (5, 5, 256, 32), (12, 3, 64, 16), (9, 1, 128, 8), (6, 2, 128, 16)])
