@@ -43,6 +43,18 @@ struct FtArgs {
     int cluster_merge;                      // decode: the CTAs of one (request, kv head) are a cluster and merge themselves
 };
 
+// With -DRB_TIMELINE a caller may hand the decode kernel a buffer of eight 64-bit words per CTA (linear block index) that
+// get the global timer at: 0 the CTA's start, 1 shared memory zeroed, 2 the kernels before done, 3 the first tile landed,
+// 4 the last tile used, 5 this CTA's part sent, 6 the cluster's barrier passed, 7 the end.
+#ifdef RB_TIMELINE
+__device__ unsigned long long* g_ft_trace = nullptr;
+extern "C" int rb_fa_decode_trace(unsigned long long* buf) { return (int)cudaMemcpyToSymbol(g_ft_trace, &buf, sizeof(buf)); }
+__device__ __forceinline__ unsigned long long ft_now() { unsigned long long t; asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t)); return t; }
+#define FT_T(slot) do { if (g_ft_trace) g_ft_trace[(size_t)((blockIdx.z * gridDim.y + blockIdx.y) * gridDim.x + blockIdx.x) * 8 + (slot)] = ft_now(); } while (0)
+#else
+#define FT_T(slot) do { } while (0)
+#endif
+
 struct FtShared {
     unsigned long long full[4];
     unsigned long long empty[4];
@@ -97,6 +109,7 @@ fa_decode_tma_kernel(const __grid_constant__ CUtensorMap map_kv, const FtArgs a)
     volatile int* abort_flag = &sh->abort_flag;
 
     if (threadIdx.x == 0) {
+        FT_T(0);
         for (int s = 0; s < NST; ++s) { mbar_init(smem_u32(&sh->full[s]), 1); mbar_init(smem_u32(&sh->empty[s]), FT_WARPS); }
         sh->abort_flag = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
@@ -106,6 +119,7 @@ fa_decode_tma_kernel(const __grid_constant__ CUtensorMap map_kv, const FtArgs a)
         reinterpret_cast<uint4*>(smem)[i] = make_uint4(0, 0, 0, 0);
     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");   // the zeroing precedes the TMA writes
     __syncthreads();
+    if (threadIdx.x == 0) FT_T(1);
     pdl_trigger();
 
     // The step's tables (lengths, block table) were complete before its first kernel began, and the keys of
@@ -131,6 +145,7 @@ fa_decode_tma_kernel(const __grid_constant__ CUtensorMap map_kv, const FtArgs a)
     if (warp < FT_WARPS) {
         pdl_wait();
         RB_TL_MARK();
+        if (threadIdx.x == 0) FT_T(2);
         // Q rows (row r = query head head0 + r) into the swizzled layout, by the consumer warps that read them
         for (int i = threadIdx.x; i < a.Gc * (a.d / 8); i += FT_WARPS * 32) {
             const int row = i / (a.d / 8), c = i % (a.d / 8);
@@ -212,6 +227,7 @@ fa_decode_tma_kernel(const __grid_constant__ CUtensorMap map_kv, const FtArgs a)
         for (int it = 0; it < n_tiles; ++it) {
             const int s = it % NST;
             if (!mbar_wait(smem_u32(&sh->full[s]), (it / NST) & 1, abort_flag, 4)) break;
+            if (it == 0 && threadIdx.x == 0) FT_T(3);
             const uint32_t sK = stages_u + s * STAGE, sV = sK + KV_BYTES;
             const int k0 = (t_begin + it) * FT_BN;
             if (k0 + FT_BN > kv_end) {
@@ -276,6 +292,7 @@ fa_decode_tma_kernel(const __grid_constant__ CUtensorMap map_kv, const FtArgs a)
             __syncwarp();
             if (lane == 0) mbar_arrive(smem_u32(&sh->empty[s]));
         }
+        if (threadIdx.x == 0) FT_T(4);
     }
     __syncthreads();
     const bool aborted = *abort_flag != 0;
@@ -305,50 +322,70 @@ fa_decode_tma_kernel(const __grid_constant__ CUtensorMap map_kv, const FtArgs a)
                 l[i] += __shfl_xor_sync(0xffffffffu, l[i], 1);
                 l[i] += __shfl_xor_sync(0xffffffffu, l[i], 2);
             }
-            float* sO = reinterpret_cast<float*>(stages);          // [warp][16][D]: the ring is idle now
-            float* sM = sO + FT_WARPS * 16 * D;
+            // [warp][16][D + 8]: the ring is idle now.  Rows of heads that exist only; a row is 8 floats longer than
+            // the head, so that the 8-byte stores of a warp's lanes fall into 32 different banks.
+            constexpr int SD = D + 8;
+            float* sO = reinterpret_cast<float*>(stages);
+            float* sM = sO + FT_WARPS * 16 * SD;
             float* sL = sM + FT_WARPS * 16;
 #pragma unroll
             for (int j = 0; j < D / 8; ++j) {
                 const int dim = j * 8 + 2 * (lane & 3);
-                sO[(warp * 16 + row0) * D + dim] = o[j][0]; sO[(warp * 16 + row0) * D + dim + 1] = o[j][1];
-                sO[(warp * 16 + row0 + 8) * D + dim] = o[j][2]; sO[(warp * 16 + row0 + 8) * D + dim + 1] = o[j][3];
+                if (row0 < a.Gc) *reinterpret_cast<float2*>(sO + (warp * 16 + row0) * SD + dim) = make_float2(o[j][0], o[j][1]);
+                if (row0 + 8 < a.Gc) *reinterpret_cast<float2*>(sO + (warp * 16 + row0 + 8) * SD + dim) = make_float2(o[j][2], o[j][3]);
             }
             if ((lane & 3) == 0) {
                 sM[warp * 16 + row0] = m[0]; sM[warp * 16 + row0 + 8] = m[1];
                 sL[warp * 16 + row0] = l[0]; sL[warp * 16 + row0 + 8] = l[1];
             }
             asm volatile("bar.sync 1, %0;" ::"n"(FT_WARPS * 32) : "memory");
-            for (int i = threadIdx.x; i < a.Gc * a.d; i += FT_WARPS * 32) {
-                const int row = i / a.d, dim = i % a.d;
-                float M = -INFINITY;
-#pragma unroll
-                for (int w = 0; w < FT_WARPS; ++w) M = fmaxf(M, sM[w * 16 + row]);
-                float L = 0.0f, O = 0.0f;
-                if (M > -INFINITY) {
-#pragma unroll
-                    for (int w = 0; w < FT_WARPS; ++w) {
-                        const float f = exp2f(sM[w * 16 + row] - M);
-                        L += sL[w * 16 + row] * f;
-                        O += sO[(w * 16 + row) * D + dim] * f;
-                    }
-                }
-                const float val = L > 0.0f ? O / L : 0.0f;
+            // a thread takes one dim of every row: its owner and the address there are found once
+            for (int dim = threadIdx.x; dim < a.d; dim += FT_WARPS * 32) {
                 const int owner = dim / dq, dl = dim - owner * dq;
                 uint32_t remote;
                 asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(remote)
-                             : "r"(smem_u32(recv_o + (split * a.Gc + row) * dq + dl)), "r"((uint32_t)owner));
-                asm volatile("st.shared::cluster.f32 [%0], %1;" ::"r"(remote), "f"(val) : "memory");
-                if (dim < a.n_splits) {                            // (d >= n_splits) this row's log-sum-exp, to CTA `dim`
-                    const float lse = L > 0.0f ? M + log2f(L) : -INFINITY;
-                    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(remote)
-                                 : "r"(smem_u32(recv_l + split * 16 + row)), "r"((uint32_t)dim));
-                    asm volatile("st.shared::cluster.f32 [%0], %1;" ::"r"(remote), "f"(lse) : "memory");
+                             : "r"(smem_u32(recv_o + (split * a.Gc) * dq + dl)), "r"((uint32_t)owner));
+                for (int row = 0; row < a.Gc; ++row) {
+                    float mw[FT_WARPS];
+                    float M = -INFINITY;
+#pragma unroll
+                    for (int w = 0; w < FT_WARPS; ++w) { mw[w] = sM[w * 16 + row]; M = fmaxf(M, mw[w]); }
+                    float L = 0.0f, O = 0.0f;
+                    if (M > -INFINITY) {
+#pragma unroll
+                        for (int w = 0; w < FT_WARPS; ++w) {
+                            const float f = exp2f(mw[w] - M);
+                            L += sL[w * 16 + row] * f;
+                            O += sO[(w * 16 + row) * SD + dim] * f;
+                        }
+                    }
+                    const float val = L > 0.0f ? O / L : 0.0f;
+                    asm volatile("st.shared::cluster.f32 [%0], %1;" ::"r"(remote + (uint32_t)(row * dq) * 4u), "f"(val) : "memory");
                 }
+            }
+            // every row's log-sum-exp, to every CTA of the cluster
+            for (int i = threadIdx.x; i < a.Gc * a.n_splits; i += FT_WARPS * 32) {
+                const int row = i / a.n_splits, target = i - row * a.n_splits;
+                float mw[FT_WARPS];
+                float M = -INFINITY;
+#pragma unroll
+                for (int w = 0; w < FT_WARPS; ++w) { mw[w] = sM[w * 16 + row]; M = fmaxf(M, mw[w]); }
+                float L = 0.0f;
+                if (M > -INFINITY) {
+#pragma unroll
+                    for (int w = 0; w < FT_WARPS; ++w) L += sL[w * 16 + row] * exp2f(mw[w] - M);
+                }
+                const float lse = L > 0.0f ? M + log2f(L) : -INFINITY;
+                uint32_t remote;
+                asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(remote)
+                             : "r"(smem_u32(recv_l + split * 16 + row)), "r"((uint32_t)target));
+                asm volatile("st.shared::cluster.f32 [%0], %1;" ::"r"(remote), "f"(lse) : "memory");
             }
         }
         __syncwarp();
+        if (threadIdx.x == 0) FT_T(5);
         asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+        if (threadIdx.x == 0) FT_T(6);
         if (aborted || warp == FT_WARPS) return;
         for (int i = threadIdx.x; i < a.Gc * dq; i += FT_WARPS * 32) {
             const int row = i / dq, dl = i - row * dq;
@@ -366,6 +403,7 @@ fa_decode_tma_kernel(const __grid_constant__ CUtensorMap map_kv, const FtArgs a)
             }
             a.out[((size_t)tok * a.QH + head0 + row) * a.d + dim] = __float2bfloat16_rn(W > 0.0f ? O / W : 0.0f);
         }
+        if (threadIdx.x == 0) FT_T(7);
         return;
     }
     if (warp == FT_WARPS) return;                              // the producer has no part in the merge
@@ -380,42 +418,45 @@ fa_decode_tma_kernel(const __grid_constant__ CUtensorMap map_kv, const FtArgs a)
         l[i] += __shfl_xor_sync(0xffffffffu, l[i], 1);
         l[i] += __shfl_xor_sync(0xffffffffu, l[i], 2);
     }
-    float* sO = reinterpret_cast<float*>(stages);              // [warp][16][D]
-    float* sM = sO + FT_WARPS * 16 * D;
+    constexpr int SD = D + 8;                                  // as above: padded rows, existing heads only
+    float* sO = reinterpret_cast<float*>(stages);              // [warp][16][D + 8]
+    float* sM = sO + FT_WARPS * 16 * SD;
     float* sL = sM + FT_WARPS * 16;
 #pragma unroll
     for (int j = 0; j < D / 8; ++j) {
         const int dim = j * 8 + 2 * (lane & 3);
-        sO[(warp * 16 + row0) * D + dim] = o[j][0]; sO[(warp * 16 + row0) * D + dim + 1] = o[j][1];
-        sO[(warp * 16 + row0 + 8) * D + dim] = o[j][2]; sO[(warp * 16 + row0 + 8) * D + dim + 1] = o[j][3];
+        if (row0 < a.Gc) *reinterpret_cast<float2*>(sO + (warp * 16 + row0) * SD + dim) = make_float2(o[j][0], o[j][1]);
+        if (row0 + 8 < a.Gc) *reinterpret_cast<float2*>(sO + (warp * 16 + row0 + 8) * SD + dim) = make_float2(o[j][2], o[j][3]);
     }
     if ((lane & 3) == 0) {
         sM[warp * 16 + row0] = m[0]; sM[warp * 16 + row0 + 8] = m[1];
         sL[warp * 16 + row0] = l[0]; sL[warp * 16 + row0 + 8] = l[1];
     }
     asm volatile("bar.sync 1, %0;" ::"n"(FT_WARPS * 32) : "memory");
-    for (int i = threadIdx.x; i < a.Gc * a.d; i += FT_WARPS * 32) {
-        const int row = i / a.d, dim = i % a.d;
-        float M = -INFINITY;
+    for (int dim = threadIdx.x; dim < a.d; dim += FT_WARPS * 32) {
+        for (int row = 0; row < a.Gc; ++row) {
+            float mw[FT_WARPS];
+            float M = -INFINITY;
 #pragma unroll
-        for (int w = 0; w < FT_WARPS; ++w) M = fmaxf(M, sM[w * 16 + row]);
-        float L = 0.0f, O = 0.0f;
-        if (M > -INFINITY) {
+            for (int w = 0; w < FT_WARPS; ++w) { mw[w] = sM[w * 16 + row]; M = fmaxf(M, mw[w]); }
+            float L = 0.0f, O = 0.0f;
+            if (M > -INFINITY) {
 #pragma unroll
-            for (int w = 0; w < FT_WARPS; ++w) {
-                const float f = exp2f(sM[w * 16 + row] - M);
-                L += sL[w * 16 + row] * f;
-                O += sO[(w * 16 + row) * D + dim] * f;
+                for (int w = 0; w < FT_WARPS; ++w) {
+                    const float f = exp2f(mw[w] - M);
+                    L += sL[w * 16 + row] * f;
+                    O += sO[(w * 16 + row) * SD + dim] * f;
+                }
             }
-        }
-        const float val = L > 0.0f ? O / L : 0.0f;
-        const int head = head0 + row;
-        if (a.n_splits == 1) {
-            a.out[((size_t)tok * a.QH + head) * a.d + dim] = __float2bfloat16_rn(val);
-        } else {
-            const size_t pi = ((size_t)(tok - a.cu_q[a.first_entry]) * a.QH + head) * a.n_splits + split;
-            a.part_o[pi * a.d + dim] = val;
-            if (dim == 0) a.part_lse[pi] = L > 0.0f ? M + log2f(L) : -INFINITY;
+            const float val = L > 0.0f ? O / L : 0.0f;
+            const int head = head0 + row;
+            if (a.n_splits == 1) {
+                a.out[((size_t)tok * a.QH + head) * a.d + dim] = __float2bfloat16_rn(val);
+            } else {
+                const size_t pi = ((size_t)(tok - a.cu_q[a.first_entry]) * a.QH + head) * a.n_splits + split;
+                a.part_o[pi * a.d + dim] = val;
+                if (dim == 0) a.part_lse[pi] = L > 0.0f ? M + log2f(L) : -INFINITY;
+            }
         }
     }
 }
@@ -757,7 +798,7 @@ extern "C" int rb_fa_decode_cluster_slots(int d, int n) {
 template <int HALVES, int NST, bool P5 = false>
 static int ft_launch(const CUtensorMap& map, const FtArgs& a, cudaStream_t s) {
     constexpr size_t pipe = (size_t)NST * 2 * HALVES * FT_HALF_BYTES;
-    constexpr size_t merge = (size_t)FT_WARPS * 16 * (HALVES * 64 + 2) * sizeof(float);
+    constexpr size_t merge = (size_t)FT_WARPS * 16 * (HALVES * 64 + 8 + 2) * sizeof(float);
     static_assert(merge <= pipe, "the merge buffers reuse the stages");
     static_assert(sizeof(FtShared) <= 256, "the cluster's receive buffers start 256 bytes behind the barriers");
     // stages, Q, barriers, and what the other splits of a cluster send: [split][Gc][dq] results + [split][16] log-sum-exps

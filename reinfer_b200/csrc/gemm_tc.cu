@@ -167,6 +167,8 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
     // heads in the cluster's reduction: what an epilogue thread needs for its first token, fetched while the weights stream
     float hp_c[4] = {1.f, 1.f, 1.f, 1.f}, hp_s[4] = {0.f, 0.f, 0.f, 0.f}, hp_w[4] = {1.f, 1.f, 1.f, 1.f};
     int hp_slot = -1;
+    // an accumulating product reduced by its cluster: the old sums of this thread's first two tokens, fetched likewise
+    float4 pre_a = make_float4(0.f, 0.f, 0.f, 0.f), pre_b = pre_a;
 
     // The two issuing warps stay converged (every lane walks the loop and waits at the barriers) and lane 0 issues
     // through predicated instructions: an issuing lane alone inside a branch pays about a hundred cycles more for
@@ -241,6 +243,13 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
             }
         }
         pdl_wait();                                            // C may still be in use by the kernels before
+        if (!DUAL && csplit > 1 && out_mode == 2 && (ldc & 3) == 0 && ((uintptr_t)C & 15) == 0) {
+            const int et = threadIdx.x - 64, f4 = (et & 31) * 4, cb0 = split + (et >> 5) * csplit, cb1 = cb0 + 4 * csplit;
+            if (n0 + f4 + 3 < N) {
+                if (cb0 < BN && t0 + cb0 < T) pre_a = *reinterpret_cast<const float4*>((const float*)C + (size_t)(t0 + cb0) * ldc + n0 + f4);
+                if (cb1 < BN && t0 + cb1 < T) pre_b = *reinterpret_cast<const float4*>((const float*)C + (size_t)(t0 + cb1) * ldc + n0 + f4);
+            }
+        }
         for (int idx = threadIdx.x - 64; idx < BN; idx += 128) {
             float f = 1.0f;
             if (ex.row_sumsq && t0 + idx < T) {
@@ -356,7 +365,10 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
                     float4* d0 = reinterpret_cast<float4*>(Cf + (size_t)(t0 + cb0) * ldc + feat);
                     float4* d1 = reinterpret_cast<float4*>(Cf + (size_t)(t0 + cb1) * ldc + feat);
                     float4 oa = make_float4(0.f, 0.f, 0.f, 0.f), ob = oa;
-                    if (out_mode == 2) { oa = *d0; if (two) ob = *d1; }
+                    if (out_mode == 2) {
+                        if (cb0 == split + tsub * csplit) { oa = pre_a; ob = pre_b; }      // fetched while the weights streamed
+                        else { oa = *d0; if (two) ob = *d1; }
+                    }
                     float4 va = pa[0], vb = pb[0];
 #pragma unroll
                     for (int r = 1; r < 8; ++r) {

@@ -146,10 +146,16 @@ def timeline(ops, torch, decode, B, N, layers) -> int:
     torch.cuda.synchronize()
     for fn in TIMELINE_SETTERS:
         getattr(lib, fn)(ctypes.c_void_p(buf.data_ptr()))
+    # the decode attention's own stamps: eight per CTA, every launch writes over the one before, so the last layer's stay
+    phases = torch.zeros(8192 * 8, dtype=torch.int64, device="cuda") if hasattr(lib, "rb_fa_decode_trace") else None
+    if phases is not None:
+        lib.rb_fa_decode_trace(ctypes.c_void_p(phases.data_ptr()))
     decode()
     torch.cuda.synchronize()
     for fn in TIMELINE_SETTERS:
         getattr(lib, fn)(ctypes.c_void_p(0))
+    if phases is not None:
+        lib.rb_fa_decode_trace(ctypes.c_void_p(0))
     h = buf.cpu()
     n = min(int(h[0]), cap)
     rec = h[4:4 + n * 4].view(-1, 4)
@@ -178,6 +184,20 @@ def timeline(ops, torch, decode, B, N, layers) -> int:
         waited = (l["mark"] - t0) / 1e3 if l["mark"] < 1 << 62 else float("nan")
         print(f"{name:12s} {l['n']:5d} {(l['start'] - t0) / 1e3:9.2f} {waited:9.2f} {(l['end'] - t0) / 1e3:9.2f} {adv / 1e3:17.2f}")
     print("the step's end moved, by kernel (us):", {k: round(v / 1e3, 1) for k, v in tot.items()}, "total", round((prev_end - t0) / 1e3, 1))
+    if phases is not None:
+        t = phases.view(-1, 8).cpu()
+        t = t[t[:, 0] > 0]
+        if t.shape[0]:
+            first = t[:, 0].min()
+            rel = (t - first).double() / 1e3
+            rel[t == 0] = float("nan")
+            print(f"decode attention of the last layer, {t.shape[0]} CTAs, us since its first CTA began (mean / min / max over the CTAs):")
+            for i, name in enumerate(("began", "shared memory zeroed", "kernels before done", "first tile landed", "last tile used",
+                                      "own part sent", "cluster barrier passed", "end")):
+                col = rel[:, i]
+                col = col[~torch.isnan(col)]
+                if col.numel():
+                    print(f"   {name:22s} {col.mean().item():7.2f} {col.min().item():7.2f} {col.max().item():7.2f}")
     err = ops.kernel_error()
     return 0 if err == 0 else 1
 
