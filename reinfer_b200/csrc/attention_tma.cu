@@ -83,6 +83,51 @@ __device__ __forceinline__ uint32_t ft_off(int row, int chunk, int half_bytes) {
     return (uint32_t)((chunk >> 3) * half_bytes + row * 128 + (((chunk & 7) ^ (row & 7)) << 4));
 }
 
+// The end of the decode kernel: its four warps hold partial results (o, running maximum m, sum l) for the same 16 rows
+// over different keys.  ft_merge_park puts them side by side in shared memory - rows of heads that exist only; a row is
+// 8 floats longer than the head, so that the 8-byte stores of a warp's lanes fall into 32 different banks; sF gets
+// [warp][16] maxima and, 64 floats on, sums.  After a barrier ft_merge_weights lets one thread per row turn them into
+// each warp's share of the row (exp2(m_w - M) / L, in sF's first half) and the row's log-sum-exp; after another barrier a
+// row's merged value for a dim is the sum over the warps of their value times their share: no exponential and no
+// division per element.
+template <int D>
+__device__ __forceinline__ void ft_merge_park(float* sO, float* sF, const float (&o)[D / 8][4], const float (&m)[2], float (&l)[2],
+                                              int Gc, int warp, int lane) {
+    constexpr int SD = D + 8;
+    const int row0 = lane >> 2;
+#pragma unroll
+    for (int i = 0; i < 2; ++i) {
+        l[i] += __shfl_xor_sync(0xffffffffu, l[i], 1);
+        l[i] += __shfl_xor_sync(0xffffffffu, l[i], 2);
+    }
+#pragma unroll
+    for (int j = 0; j < D / 8; ++j) {
+        const int dim = j * 8 + 2 * (lane & 3);
+        if (row0 < Gc) *reinterpret_cast<float2*>(sO + (warp * 16 + row0) * SD + dim) = make_float2(o[j][0], o[j][1]);
+        if (row0 + 8 < Gc) *reinterpret_cast<float2*>(sO + (warp * 16 + row0 + 8) * SD + dim) = make_float2(o[j][2], o[j][3]);
+    }
+    if ((lane & 3) == 0) {
+        sF[warp * 16 + row0] = m[0]; sF[warp * 16 + row0 + 8] = m[1];
+        sF[FT_WARPS * 16 + warp * 16 + row0] = l[0]; sF[FT_WARPS * 16 + warp * 16 + row0 + 8] = l[1];
+    }
+}
+__device__ __forceinline__ void ft_merge_weights(float* sF, float* sLse, int Gc) {
+    const int row = threadIdx.x;
+    if (row >= Gc) return;
+    float mw[FT_WARPS], M = -INFINITY, L = 0.0f;
+#pragma unroll
+    for (int w = 0; w < FT_WARPS; ++w) { mw[w] = sF[w * 16 + row]; M = fmaxf(M, mw[w]); }
+#pragma unroll
+    for (int w = 0; w < FT_WARPS; ++w) {
+        mw[w] = M > -INFINITY ? exp2f(mw[w] - M) : 0.0f;
+        L += sF[FT_WARPS * 16 + w * 16 + row] * mw[w];
+    }
+    const float inv = L > 0.0f ? 1.0f / L : 0.0f;
+#pragma unroll
+    for (int w = 0; w < FT_WARPS; ++w) sF[w * 16 + row] = mw[w] * inv;
+    sLse[row] = L > 0.0f ? M + log2f(L) : -INFINITY;
+}
+
 // P5: the map is the 5-D one of runtime.cu (head size 128): ONE request brings a page's keys (or values) for this kv head,
 // as [8-key group][64-dim half][8 keys][64 dims] - groups 2,048 bytes apart, a group's second half 1,024 bytes on - instead
 // of one request per page and half into [half][64 keys][64 dims].
@@ -222,6 +267,12 @@ fa_decode_tma_kernel(const __grid_constant__ CUtensorMap map_kv, const FtArgs a)
             }
             issued = it + 1;
         }
+        // this CTA's keys and values are all requested: while they arrive, are used and merged, and the kernels after
+        // this one start up, memory would idle - the weights that the next product streams are called into L2 now
+        // (by this warp, which has nothing left to do; the consumers' merge waits for nobody)
+        if (lane == 0)
+            l2_prefetch_share(a.next_w, a.next_bytes, (blockIdx.z * gridDim.y + blockIdx.y) * gridDim.x + blockIdx.x,
+                              gridDim.x * gridDim.y * gridDim.z);
     } else {
         // ---- consumer warps --------------------------------------------------------------------
         for (int it = 0; it < n_tiles; ++it) {
@@ -314,30 +365,13 @@ fa_decode_tma_kernel(const __grid_constant__ CUtensorMap map_kv, const FtArgs a)
         float* recv_l = recv_o + 16 * D + 128;                                  // [split][16]
         const int dq = (a.d + a.n_splits - 1) / a.n_splits;
         if (!aborted && warp < FT_WARPS) {
-            if (threadIdx.x == 0)
-                l2_prefetch_share(a.next_w, a.next_bytes, (blockIdx.z * gridDim.y + blockIdx.y) * gridDim.x + blockIdx.x,
-                                  gridDim.x * gridDim.y * gridDim.z);
-#pragma unroll
-            for (int i = 0; i < 2; ++i) {
-                l[i] += __shfl_xor_sync(0xffffffffu, l[i], 1);
-                l[i] += __shfl_xor_sync(0xffffffffu, l[i], 2);
-            }
-            // [warp][16][D + 8]: the ring is idle now.  Rows of heads that exist only; a row is 8 floats longer than
-            // the head, so that the 8-byte stores of a warp's lanes fall into 32 different banks.
             constexpr int SD = D + 8;
             float* sO = reinterpret_cast<float*>(stages);
-            float* sM = sO + FT_WARPS * 16 * SD;
-            float* sL = sM + FT_WARPS * 16;
-#pragma unroll
-            for (int j = 0; j < D / 8; ++j) {
-                const int dim = j * 8 + 2 * (lane & 3);
-                if (row0 < a.Gc) *reinterpret_cast<float2*>(sO + (warp * 16 + row0) * SD + dim) = make_float2(o[j][0], o[j][1]);
-                if (row0 + 8 < a.Gc) *reinterpret_cast<float2*>(sO + (warp * 16 + row0 + 8) * SD + dim) = make_float2(o[j][2], o[j][3]);
-            }
-            if ((lane & 3) == 0) {
-                sM[warp * 16 + row0] = m[0]; sM[warp * 16 + row0 + 8] = m[1];
-                sL[warp * 16 + row0] = l[0]; sL[warp * 16 + row0 + 8] = l[1];
-            }
+            float* sF = sO + FT_WARPS * 16 * SD;                   // [warp][16]: a warp's share of a row, after ft_merge_weights
+            float* sLse = sF + 2 * FT_WARPS * 16;                  // [16]
+            ft_merge_park<D>(sO, sF, o, m, l, a.Gc, warp, lane);
+            asm volatile("bar.sync 1, %0;" ::"n"(FT_WARPS * 32) : "memory");
+            ft_merge_weights(sF, sLse, a.Gc);
             asm volatile("bar.sync 1, %0;" ::"n"(FT_WARPS * 32) : "memory");
             // a thread takes one dim of every row: its owner and the address there are found once
             for (int dim = threadIdx.x; dim < a.d; dim += FT_WARPS * 32) {
@@ -345,41 +379,21 @@ fa_decode_tma_kernel(const __grid_constant__ CUtensorMap map_kv, const FtArgs a)
                 uint32_t remote;
                 asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(remote)
                              : "r"(smem_u32(recv_o + (split * a.Gc) * dq + dl)), "r"((uint32_t)owner));
+#pragma unroll 4
                 for (int row = 0; row < a.Gc; ++row) {
-                    float mw[FT_WARPS];
-                    float M = -INFINITY;
+                    float O = 0.0f;
 #pragma unroll
-                    for (int w = 0; w < FT_WARPS; ++w) { mw[w] = sM[w * 16 + row]; M = fmaxf(M, mw[w]); }
-                    float L = 0.0f, O = 0.0f;
-                    if (M > -INFINITY) {
-#pragma unroll
-                        for (int w = 0; w < FT_WARPS; ++w) {
-                            const float f = exp2f(mw[w] - M);
-                            L += sL[w * 16 + row] * f;
-                            O += sO[(w * 16 + row) * SD + dim] * f;
-                        }
-                    }
-                    const float val = L > 0.0f ? O / L : 0.0f;
-                    asm volatile("st.shared::cluster.f32 [%0], %1;" ::"r"(remote + (uint32_t)(row * dq) * 4u), "f"(val) : "memory");
+                    for (int w = 0; w < FT_WARPS; ++w) O += sO[(w * 16 + row) * SD + dim] * sF[w * 16 + row];
+                    asm volatile("st.shared::cluster.f32 [%0], %1;" ::"r"(remote + (uint32_t)(row * dq) * 4u), "f"(O) : "memory");
                 }
             }
             // every row's log-sum-exp, to every CTA of the cluster
             for (int i = threadIdx.x; i < a.Gc * a.n_splits; i += FT_WARPS * 32) {
                 const int row = i / a.n_splits, target = i - row * a.n_splits;
-                float mw[FT_WARPS];
-                float M = -INFINITY;
-#pragma unroll
-                for (int w = 0; w < FT_WARPS; ++w) { mw[w] = sM[w * 16 + row]; M = fmaxf(M, mw[w]); }
-                float L = 0.0f;
-                if (M > -INFINITY) {
-#pragma unroll
-                    for (int w = 0; w < FT_WARPS; ++w) L += sL[w * 16 + row] * exp2f(mw[w] - M);
-                }
-                const float lse = L > 0.0f ? M + log2f(L) : -INFINITY;
                 uint32_t remote;
                 asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(remote)
                              : "r"(smem_u32(recv_l + split * 16 + row)), "r"((uint32_t)target));
-                asm volatile("st.shared::cluster.f32 [%0], %1;" ::"r"(remote), "f"(lse) : "memory");
+                asm volatile("st.shared::cluster.f32 [%0], %1;" ::"r"(remote), "f"(sLse[row]) : "memory");
             }
         }
         __syncwarp();
@@ -407,55 +421,28 @@ fa_decode_tma_kernel(const __grid_constant__ CUtensorMap map_kv, const FtArgs a)
         return;
     }
     if (warp == FT_WARPS) return;                              // the producer has no part in the merge
-    // this CTA's keys and values have arrived: while the partial results are merged and the kernels after this
-    // one start up, memory would idle - the weights that the next product streams are called into L2 now
-    if (threadIdx.x == 0)
-        l2_prefetch_share(a.next_w, a.next_bytes, (blockIdx.z * gridDim.y + blockIdx.y) * gridDim.x + blockIdx.x,
-                          gridDim.x * gridDim.y * gridDim.z);
     // merge the four warps (fixed order), then store or hand to the merge kernel
-#pragma unroll
-    for (int i = 0; i < 2; ++i) {
-        l[i] += __shfl_xor_sync(0xffffffffu, l[i], 1);
-        l[i] += __shfl_xor_sync(0xffffffffu, l[i], 2);
-    }
-    constexpr int SD = D + 8;                                  // as above: padded rows, existing heads only
+    constexpr int SD = D + 8;
     float* sO = reinterpret_cast<float*>(stages);              // [warp][16][D + 8]
-    float* sM = sO + FT_WARPS * 16 * SD;
-    float* sL = sM + FT_WARPS * 16;
-#pragma unroll
-    for (int j = 0; j < D / 8; ++j) {
-        const int dim = j * 8 + 2 * (lane & 3);
-        if (row0 < a.Gc) *reinterpret_cast<float2*>(sO + (warp * 16 + row0) * SD + dim) = make_float2(o[j][0], o[j][1]);
-        if (row0 + 8 < a.Gc) *reinterpret_cast<float2*>(sO + (warp * 16 + row0 + 8) * SD + dim) = make_float2(o[j][2], o[j][3]);
-    }
-    if ((lane & 3) == 0) {
-        sM[warp * 16 + row0] = m[0]; sM[warp * 16 + row0 + 8] = m[1];
-        sL[warp * 16 + row0] = l[0]; sL[warp * 16 + row0 + 8] = l[1];
-    }
+    float* sF = sO + FT_WARPS * 16 * SD;
+    float* sLse = sF + 2 * FT_WARPS * 16;
+    ft_merge_park<D>(sO, sF, o, m, l, a.Gc, warp, lane);
+    asm volatile("bar.sync 1, %0;" ::"n"(FT_WARPS * 32) : "memory");
+    ft_merge_weights(sF, sLse, a.Gc);
     asm volatile("bar.sync 1, %0;" ::"n"(FT_WARPS * 32) : "memory");
     for (int dim = threadIdx.x; dim < a.d; dim += FT_WARPS * 32) {
+#pragma unroll 4
         for (int row = 0; row < a.Gc; ++row) {
-            float mw[FT_WARPS];
-            float M = -INFINITY;
+            float O = 0.0f;
 #pragma unroll
-            for (int w = 0; w < FT_WARPS; ++w) { mw[w] = sM[w * 16 + row]; M = fmaxf(M, mw[w]); }
-            float L = 0.0f, O = 0.0f;
-            if (M > -INFINITY) {
-#pragma unroll
-                for (int w = 0; w < FT_WARPS; ++w) {
-                    const float f = exp2f(mw[w] - M);
-                    L += sL[w * 16 + row] * f;
-                    O += sO[(w * 16 + row) * SD + dim] * f;
-                }
-            }
-            const float val = L > 0.0f ? O / L : 0.0f;
+            for (int w = 0; w < FT_WARPS; ++w) O += sO[(w * 16 + row) * SD + dim] * sF[w * 16 + row];
             const int head = head0 + row;
             if (a.n_splits == 1) {
-                a.out[((size_t)tok * a.QH + head) * a.d + dim] = __float2bfloat16_rn(val);
+                a.out[((size_t)tok * a.QH + head) * a.d + dim] = __float2bfloat16_rn(O);
             } else {
                 const size_t pi = ((size_t)(tok - a.cu_q[a.first_entry]) * a.QH + head) * a.n_splits + split;
-                a.part_o[pi * a.d + dim] = val;
-                if (dim == 0) a.part_lse[pi] = L > 0.0f ? M + log2f(L) : -INFINITY;
+                a.part_o[pi * a.d + dim] = O;
+                if (dim == 0) a.part_lse[pi] = sLse[row];
             }
         }
     }
@@ -798,7 +785,7 @@ extern "C" int rb_fa_decode_cluster_slots(int d, int n) {
 template <int HALVES, int NST, bool P5 = false>
 static int ft_launch(const CUtensorMap& map, const FtArgs& a, cudaStream_t s) {
     constexpr size_t pipe = (size_t)NST * 2 * HALVES * FT_HALF_BYTES;
-    constexpr size_t merge = (size_t)FT_WARPS * 16 * (HALVES * 64 + 8 + 2) * sizeof(float);
+    constexpr size_t merge = ((size_t)FT_WARPS * 16 * (HALVES * 64 + 8 + 2) + 16) * sizeof(float);
     static_assert(merge <= pipe, "the merge buffers reuse the stages");
     static_assert(sizeof(FtShared) <= 256, "the cluster's receive buffers start 256 bytes behind the barriers");
     // stages, Q, barriers, and what the other splits of a cluster send: [split][Gc][dq] results + [split][16] log-sum-exps

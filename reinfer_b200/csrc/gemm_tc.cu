@@ -524,11 +524,20 @@ struct TcHeads {
     float eps;
 };
 
+// Rows that lack their factor, for the token-lane forms of the persistent kernel (MODE 1 .. 3; row_sumsq null: rows are
+// complete): token t stands for X[t,:] / sqrt(sum_p row_sumsq[t, p] * inv_width + eps), and its lane multiplies its
+// results by that - the norm's division behind the product, as in TcExtra.
+struct TcRows {
+    const float* row_sumsq;
+    int sumsq_parts;
+    float inv_width, eps;
+};
+
 template <int BN, int STAGES, int MODE, int ROWS = 2 * TC_BM>
 __global__ void __launch_bounds__(TC_THREADS, 1)
 gemm_tc_persistent_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_x,
                           void* __restrict__ C, int T, int N, int K, long long ldc, int out_mode, int t_tiles, int n_tiles,
-                          TcHeads hd) {
+                          TcHeads hd, TcRows rs) {
     // MODE 0: a tile is 128 features (the M operand) x BN tokens.  MODE 1 (the gated pair) and MODE 2: a tile is 128
     // tokens (the M operand) x ROWS weight rows (the N operand; a multiple of 32 up to 256): ROWS / 2 gate rows and the
     // ROWS / 2 up rows of the same features, or ROWS features.  A lane of the accumulator is then a token, and the
@@ -689,6 +698,13 @@ gemm_tc_persistent_kernel(const __grid_constant__ CUtensorMap map_w, const __gri
 #endif
             tc_fence_after();
             const uint32_t acc = tmem + ((uint32_t)(q * 32) << 16) + (uint32_t)a * ACC_COLS;
+            float rf = 1.0f;                                       // the factor that this lane's token still lacks
+            if (FLIP && rs.row_sumsq && t0 + q * 32 + lane < T) {
+                const float* parts = rs.row_sumsq + (size_t)(t0 + q * 32 + lane) * rs.sumsq_parts;
+                float ssq = 0.0f;
+                for (int p = 0; p < rs.sumsq_parts; ++p) ssq += parts[p];
+                rf = 1.0f / sqrtf(ssq * rs.inv_width + rs.eps);
+            }
             if (DUAL) {
                 // a lane is a token; columns 0..FEATS-1 hold its gate features, the next FEATS the up features of the same tile
                 const int tok = t0 + q * 32 + lane;
@@ -704,8 +720,8 @@ gemm_tc_persistent_kernel(const __grid_constant__ CUtensorMap map_w, const __gri
                         uint32_t o[8];
 #pragma unroll
                         for (int j = 0; j < 8; ++j) {
-                            const float g0 = __uint_as_float(r[2 * j]), u0 = __uint_as_float(r2[2 * j]);
-                            const float g1 = __uint_as_float(r[2 * j + 1]), u1 = __uint_as_float(r2[2 * j + 1]);
+                            const float g0 = __uint_as_float(r[2 * j]) * rf, u0 = __uint_as_float(r2[2 * j]) * rf;
+                            const float g1 = __uint_as_float(r[2 * j + 1]) * rf, u1 = __uint_as_float(r2[2 * j + 1]) * rf;
                             const __nv_bfloat162 v = __floats2bfloat162_rn(g0 / (1.0f + expf(-g0)) * u0, g1 / (1.0f + expf(-g1)) * u1);
                             o[j] = *(const uint32_t*)&v;
                         }
@@ -748,7 +764,7 @@ gemm_tc_persistent_kernel(const __grid_constant__ CUtensorMap map_w, const __gri
                             uint32_t o[8];
 #pragma unroll
                             for (int j = 0; j < 8; ++j) {
-                                const __nv_bfloat162 v = __floats2bfloat162_rn(__uint_as_float(r[2 * j]), __uint_as_float(r[2 * j + 1]));
+                                const __nv_bfloat162 v = __floats2bfloat162_rn(__uint_as_float(r[2 * j]) * rf, __uint_as_float(r[2 * j + 1]) * rf);
                                 o[j] = *(const uint32_t*)&v;
                             }
                             *(uint4*)(dst + c0) = make_uint4(o[0], o[1], o[2], o[3]);
@@ -765,7 +781,7 @@ gemm_tc_persistent_kernel(const __grid_constant__ CUtensorMap map_w, const __gri
                         tc_ld_wait();
 #pragma unroll
                         for (int j = 0; j < 16; ++j) {
-                            const float v = __bfloat162float(__float2bfloat16_rn(__uint_as_float(r[j])));
+                            const float v = __bfloat162float(__float2bfloat16_rn(__uint_as_float(r[j]) * rf));
                             ss = fmaf(v, v, ss);
                         }
                     }
@@ -792,8 +808,8 @@ gemm_tc_persistent_kernel(const __grid_constant__ CUtensorMap map_w, const __gri
                             float xo[4], yo[4];
 #pragma unroll
                             for (int u = 0; u < 4; ++u) {
-                                const float x = __bfloat162float(__float2bfloat16_rn(__uint_as_float(lo[4 * j + u]))) * rstd * wls[u];
-                                const float y = __bfloat162float(__float2bfloat16_rn(__uint_as_float(hi[4 * j + u]))) * rstd * whs[u];
+                                const float x = __bfloat162float(__float2bfloat16_rn(__uint_as_float(lo[4 * j + u]) * rf)) * rstd * wls[u];
+                                const float y = __bfloat162float(__float2bfloat16_rn(__uint_as_float(hi[4 * j + u]) * rf)) * rstd * whs[u];
                                 xo[u] = x * cc[u] - y * sn[u];             // low half: x c - y s
                                 yo[u] = x * sn[u] + y * cc[u];             // high half: y c + x s
                             }
@@ -819,6 +835,10 @@ gemm_tc_persistent_kernel(const __grid_constant__ CUtensorMap map_w, const __gri
                     tc_ld16(acc + (uint32_t)c0, r);
                     tc_ld_wait();
                     if (tok >= T) continue;
+                    if (rs.row_sumsq) {
+#pragma unroll
+                        for (int j = 0; j < 16; ++j) r[j] = __float_as_uint(__uint_as_float(r[j]) * rf);
+                    }
                     const bool whole = n0 + c0 + 16 <= N;
                     if (out_mode == 0) {
                         bf16* row = (bf16*)C + (size_t)tok * ldc + n0 + c0;
@@ -909,7 +929,7 @@ gemm_tc_persistent_kernel(const __grid_constant__ CUtensorMap map_w, const __gri
 
 template <int BN, int STAGES, int MODE, int ROWS = 2 * TC_BM>
 static int launch_tc_persistent(const CUtensorMap& mw, const CUtensorMap& mx, void* C, int T, int N, int K, long long ldc,
-                                int mode, cudaStream_t s, const TcHeads& hd = TcHeads{}) {
+                                int mode, cudaStream_t s, const TcHeads& hd = TcHeads{}, const TcRows& rs = TcRows{}) {
     constexpr size_t smem = (size_t)STAGES * ((MODE ? ROWS : TC_BM) * TC_BK * 2 + BN * TC_BK * 2) + sizeof(TcPersistShared) + 1024;
     static_assert(smem <= 232448, "stages beyond the shared memory of an SM");
     static bool configured = false;
@@ -926,7 +946,7 @@ static int launch_tc_persistent(const CUtensorMap& mw, const CUtensorMap& mx, vo
     const int total = t_tiles * n_tiles;
     const int grid = total < sms ? total : sms;
     return rb_launch(gemm_tc_persistent_kernel<BN, STAGES, MODE, ROWS>, dim3(grid), dim3(TC_THREADS), smem, s, mw, mx, C, T, N, K, ldc,
-                     mode, t_tiles, n_tiles, hd);
+                     mode, t_tiles, n_tiles, hd, rs);
 }
 
 // The gated pair over 65 .. 128 tokens (a decode step of that many requests): one tile per CTA, 128 tokens (the M
@@ -1292,12 +1312,37 @@ extern "C" int rb_set_gemm_tile_features(int v) {
 static int tc_bn(int T) { return T <= 16 ? 16 : T <= 32 ? 32 : T <= 64 ? 64 : T <= 128 ? 128 : 256; }
 
 // The extras of a launch from the entry points' arguments (-1 and a message if they make no sense).
+static TcRows tc_rows(const TcExtra& ex) {
+    TcRows rs{};
+    rs.row_sumsq = ex.row_sumsq; rs.sumsq_parts = ex.sumsq_parts; rs.inv_width = ex.inv_width; rs.eps = ex.eps;
+    return rs;
+}
+
+// Weight rows per tile of the token-lane persistent product of T tokens and N features: 256 in four stages, or 224 in
+// five.  A 64-deep k-step costs a tile about 600 cycles with four stages in flight whatever its width (the operands'
+// latency sets the pace, not their bytes) and about 500 with five (then issuing the step's products does); the narrower
+// tile wins where its count does not add a round over the SMs.
+static int tc_token_lane_rows(int T, int N) {
+    if (g_tc_tile_feats) return g_tc_tile_feats;
+    int dev = 0, sms = 148;
+    cudaGetDevice(&dev);
+    cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+    const int t_tiles = rb_ceil_div(T, 128);
+    const double c256 = 600.0 * rb_ceil_div((long long)rb_ceil_div(N, 256) * t_tiles, sms);
+    const double c224 = 500.0 * rb_ceil_div((long long)rb_ceil_div(N, 224) * t_tiles, sms);
+    return c224 < c256 ? 224 : 256;
+}
+
+// Whether a product over T tokens applies row factors (rows that lack their RMS factor) in its epilogue: the streaming
+// kernels always do, the persistent ones in their token-lane forms.
+extern "C" int rb_gemm_row_scale_ok(int T) { return T <= 256 || (g_tc_persistent && g_tc_token_lanes) ? 1 : 0; }
+
 static int tc_extra(TcExtra* ex, const void* next_w, long long next_bytes, const float* row_sumsq, int sumsq_parts,
                     int norm_width, float norm_eps, int T) {
     if ((uintptr_t)next_w & 15) RB_REFUSE("gemm: the range to prefetch must start on a 16-byte boundary");
     if (row_sumsq && (sumsq_parts < 1 || sumsq_parts > 1024 || norm_width < 1))
         RB_REFUSE("gemm: a row factor from %d parts over a width of %d", sumsq_parts, norm_width);
-    if (row_sumsq && T > 256) RB_REFUSE("gemm: row factors are for one token tile (%d tokens)", T);
+    if (row_sumsq && !rb_gemm_row_scale_ok(T)) RB_REFUSE("gemm: row factors over %d tokens need the token-lane persistent product", T);
     ex->next_w = next_w; ex->next_bytes = next_w ? next_bytes : 0;
     ex->row_sumsq = row_sumsq; ex->sumsq_parts = sumsq_parts;
     ex->inv_width = row_sumsq ? 1.0f / (float)norm_width : 0.0f; ex->eps = norm_eps;
@@ -1335,22 +1380,13 @@ extern "C" int rb_gemm_bf16(const void* X, const void* W, void* C, int c_dtype, 
         // nothing hides, the last, short.  rb_set_gemm_token_lanes(0) runs the form with a feature per lane instead.
         const bool flip = g_tc_token_lanes != 0;
         if (flip) {
-            // 256 features a tile in four stages, or 224 in five: a 64-deep k-step costs a tile about 600 cycles with
-            // four stages in flight whatever its width (the operands' latency sets the pace, not their bytes) and about
-            // 500 with five (then issuing the step's products does); the narrower tile wins where its count does not
-            // add a round over the SMs.
-            int dev = 0, sms = 148;
-            cudaGetDevice(&dev);
-            cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
-            const int t_tiles = rb_ceil_div(T, 128);
-            const double c256 = 600.0 * rb_ceil_div((long long)rb_ceil_div(N, 256) * t_tiles, sms);
-            const double c224 = 500.0 * rb_ceil_div((long long)rb_ceil_div(N, 224) * t_tiles, sms);
-            const bool narrow = g_tc_tile_feats ? g_tc_tile_feats == 224 : c224 < c256;
+            const bool narrow = tc_token_lane_rows(T, N) == 224;
             if (rb_tensor_map_bf16(W, N, K, ldw, narrow ? 224 : 256, &mw)) return -1;
             if (rb_tensor_map_bf16(X, T, K, ldx, 128, &mx)) return -1;
-            if (narrow) return launch_tc_persistent<128, 5, 2, 224>(mw, mx, C, T, N, K, ldc, mode, s);
-            return launch_tc_persistent<128, 4, 2, 256>(mw, mx, C, T, N, K, ldc, mode, s);
+            if (narrow) return launch_tc_persistent<128, 5, 2, 224>(mw, mx, C, T, N, K, ldc, mode, s, TcHeads{}, tc_rows(ex));
+            return launch_tc_persistent<128, 4, 2, 256>(mw, mx, C, T, N, K, ldc, mode, s, TcHeads{}, tc_rows(ex));
         }
+        if (row_sumsq) RB_REFUSE("gemm: row factors over %d tokens need the token-lane persistent product", T);
         int dev = 0, sms = 148;
         cudaGetDevice(&dev);
         cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
@@ -1380,6 +1416,7 @@ extern "C" int rb_gemm_bf16(const void* X, const void* W, void* C, int c_dtype, 
         if (rb_tensor_map_bf16(X, T, K, ldx, 256, &mx)) return -1;
         return launch_tc_persistent<256, 4, 0>(mw, mx, C, T, N, K, ldc, mode, s);
     }
+    if (row_sumsq && T > 256) RB_REFUSE("gemm: row factors over %d tokens need the token-lane persistent product", T);
     if (rb_tensor_map_bf16(X, T, K, ldx, bn, &mx)) return -1;
     switch (bn) {
         case 16: return launch_tc<16, 6, false>(mw, mx, C, ws, ws_floats, T, N, K, ldc, mode, force_splits, ex, s);
@@ -1393,15 +1430,18 @@ extern "C" int rb_gemm_bf16(const void* X, const void* W, void* C, int c_dtype, 
 // C (float, [T, N], row stride ldc) += X W^T for one token tile, reduced inside a cluster, with the rows of the RMS norm
 // that reads C next prepared by the same CTAs: prep_rows [T, N] bfloat16 = new C * norm_w (the norm without its
 // division), prep_sumsq [T, N / 128] = the new C's sum of squares by tiles of 128 features.  One token tile, N a
-// multiple of 128; refused otherwise (the caller then runs the product and the norm one after the other).
+// multiple of 128; refused otherwise (the caller then runs the product and the norm one after the other).  (Over several
+// token tiles the same in the persistent product's epilogue was measured: no faster at the 8B shape, 5 % slower at 4B -
+// the lanes have to load the old sums where they now only send additions, and the last tile's epilogue hides behind nothing.)
 extern "C" int rb_gemm_bf16_residual_norm(const void* X, const void* W, float* C, int T, int N, int K, long long ldx, long long ldw,
                                           long long ldc, const void* norm_w, int norm_w_dtype, void* prep_rows, float* prep_sumsq,
                                           const void* next_w, long long next_bytes, const float* row_sumsq, int sumsq_parts,
                                           int norm_width, float norm_eps, void* stream) {
     if (T <= 0 || N <= 0) return 0;
     if (K <= 0) RB_REFUSE("gemm: K=%d", K);
-    if (T > 256 || N % TC_BM || K < 2 * TC_BK)
-        RB_REFUSE("gemm_residual_norm: one token tile, features in tiles of 128, two blocks of K at least (T %d, N %d, K %d)", T, N, K);
+    if (T > 256) RB_REFUSE("gemm_residual_norm: one token tile (%d tokens)", T);
+    if (N % TC_BM || K < 2 * TC_BK)
+        RB_REFUSE("gemm_residual_norm: features in tiles of 128, two blocks of K at least (N %d, K %d)", N, K);
     if ((ldc & 3) || ((uintptr_t)C & 15) || ((uintptr_t)prep_rows & 7) || ((uintptr_t)norm_w & 15))
         RB_REFUSE("gemm_residual_norm: 16-byte aligned sum and weight, rows 8-byte aligned (ldc %lld)", ldc);
     if ((ldx % 8) || (ldw % 8) || ((uintptr_t)X & 15) || ((uintptr_t)W & 15))
@@ -1532,7 +1572,8 @@ extern "C" int rb_gemm_bf16_partials(const void* X, const void* W, float* partia
 // two-kernel way otherwise.
 extern "C" int rb_gemm_qkv_heads(const void* X, const void* W, int T, int K, long long ldx, long long ldw, int QH, int KH,
                                  void* q_out, void* cache, const int* kv_slot, const void* cs_table, const void* q_w,
-                                 const void* k_w, int w_dtype, float eps, int page_size, void* stream) {
+                                 const void* k_w, int w_dtype, float eps, int page_size,
+                                 const float* row_sumsq, int sumsq_parts, int norm_width, float norm_eps, void* stream) {
     if (T <= 256) RB_REFUSE("gemm_qkv_heads: %d tokens (more than 256: the persistent product)", T);
     if (QH <= 0 || KH <= 0 || K <= 0 || page_size <= 0) RB_REFUSE("gemm_qkv_heads: heads %d/%d, K %d, page %d", QH, KH, K, page_size);
     if ((ldx % 8) || (ldw % 8) || ((uintptr_t)X & 15) || ((uintptr_t)W & 15))
@@ -1547,7 +1588,9 @@ extern "C" int rb_gemm_qkv_heads(const void* X, const void* W, int T, int K, lon
     CUtensorMap mw, mx;
     if (rb_tensor_map_bf16(W, N, K, ldw, 256, &mw)) return -1;
     if (rb_tensor_map_bf16(X, T, K, ldx, 128, &mx)) return -1;
-    return launch_tc_persistent<128, 4, 3, 256>(mw, mx, nullptr, T, N, K, 0, 0, (cudaStream_t)stream, hd);
+    TcExtra ex;
+    if (tc_extra(&ex, nullptr, 0, row_sumsq, sumsq_parts, norm_width, norm_eps, T)) return -1;
+    return launch_tc_persistent<128, 4, 3, 256>(mw, mx, nullptr, T, N, K, 0, 0, (cudaStream_t)stream, hd, tc_rows(ex));
 }
 
 // act[T,F] (bfloat16) = silu(X Wg^T) * (X Wu^T) for Wgu = [Wg; Wu] of shape [2F, K]: one product with two
@@ -1570,8 +1613,9 @@ extern "C" int rb_gemm_bf16_swiglu(const void* X, const void* Wgu, void* act, in
     if (T > 256 && g_tc_persistent) {                               // tiles of 128 tokens x (128 gate + 128 up) weight rows
         // (112 + 112 rows in five stages were measured too: 292 against 290 us at the 8B shape, 154 against 149 at 4B)
         if (rb_tensor_map_bf16(X, T, K, ldx, 128, &mx)) return -1;
-        return launch_tc_persistent<128, 4, 1, 256>(mw, mx, act, T, F, K, ldc, 0, s);
+        return launch_tc_persistent<128, 4, 1, 256>(mw, mx, act, T, F, K, ldc, 0, s, TcHeads{}, tc_rows(ex));
     }
+    if (row_sumsq && T > 256) RB_REFUSE("gemm_swiglu: row factors over %d tokens need the persistent product", T);
     // 65 .. 128 tokens: F / 64 CTAs, two to an SM.  (For 33 .. 64 tokens the same kernel, also with 64-token stages of
     // 24 KB, is faster alone - 40 against 44 us at the 8B shape - but the decode step around it is not: 9.86 against
     // 9.78 ms at batch 64; its 192 CTAs leave the product after it no SM to start on early.)

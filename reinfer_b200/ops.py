@@ -370,6 +370,11 @@ def set_chain(chain: Optional[StreamChain]) -> Optional[StreamChain]:
     return old
 
 
+def row_scale_ok(T: int) -> bool:
+    """Whether the tensor-core products over T tokens apply the factor of rows that lack it (RowScaled input)."""
+    return bool(lib().rb_gemm_row_scale_ok(c_int(int(T))))
+
+
 def _row_scale_args(row_scale, T: int):
     """(sumsq pointer, parts, width, eps) arguments of a product whose rows still lack their RMS factor."""
     if row_scale is None:
@@ -666,7 +671,8 @@ QKV_HEADS = os.environ.get("REINFER_B200_QKV_HEADS", "1") != "0"
 
 
 def gemm_qkv_heads(a: torch.Tensor, w_qkv: torch.Tensor, q_out: torch.Tensor, cache: torch.Tensor, kv_slot: torch.Tensor,
-                   cs_table: torch.Tensor, q_w: torch.Tensor, k_w: torch.Tensor, QH: int, KH: int, page_size: int, eps: float) -> bool:
+                   cs_table: torch.Tensor, q_w: torch.Tensor, k_w: torch.Tensor, QH: int, KH: int, page_size: int, eps: float,
+                   row_scale=None) -> bool:
     """The q/k/v projection of a prompt portion with the per-head work in its epilogue (heads of 128): q_out [T, QH, 128]
     gets the normalised, rotated queries, the cache pages the keys and values at kv_slot.  cs_table [T, 64, 2] float32
     from rope_table.  Returns False (and does nothing) where this form does not apply - at most 256 tokens, operands
@@ -675,6 +681,8 @@ def gemm_qkv_heads(a: torch.Tensor, w_qkv: torch.Tensor, q_out: torch.Tensor, ca
     if not QKV_HEADS:
         return False
     if T <= 256 or a.dtype != torch.bfloat16 or w_qkv.dtype != torch.bfloat16 or q_out.dtype != torch.bfloat16 or cache.dtype != torch.bfloat16:
+        return False
+    if row_scale is not None and not row_scale_ok(T):
         return False
     if a.stride(1) != 1 or w_qkv.stride(1) != 1 or a.stride(0) % 8 or w_qkv.stride(0) % 8 or a.data_ptr() % 16 or w_qkv.data_ptr() % 16:
         return False
@@ -687,7 +695,7 @@ def gemm_qkv_heads(a: torch.Tensor, w_qkv: torch.Tensor, q_out: torch.Tensor, ca
     N = (QH + 2 * KH) * 128
     _check(lib().rb_gemm_qkv_heads(_p(a), _p(w_qkv), c_int(T), c_int(K), c_longlong(a.stride(0)), c_longlong(w_qkv.stride(0)),
                                    c_int(QH), c_int(KH), _p(q_out), _p(cache), _p(kv_slot), _p(cs_table), _p(q_w), _p(k_w),
-                                   c_int(dt(q_w)), c_float(eps), c_int(page_size), _stream()),
+                                   c_int(dt(q_w)), c_float(eps), c_int(page_size), *_row_scale_args(row_scale, T), _stream()),
            f"gemm+heads {N}x{K}", 2.0 * T * N * K, float(T * K * 2 + N * K * 2 + T * N * 2))
     return True
 

@@ -80,14 +80,16 @@ class Attention(Mixer):
         fused = self.position.fused_rotary() if self.position is not None else (None, 0)
         slots = g.kv_slot if cache.write else None
         if fused is not None and d == 128 and fused[1] == d and fused[0] is not None and T > 256 and slots is not None and \
-                isinstance(xn, torch.Tensor) and xn.dtype == torch.bfloat16 and self.q_norm_w is not None and self.k_norm_w is not None:
+                xn.dtype == torch.bfloat16 and self.q_norm_w is not None and self.k_norm_w is not None:
             # a prompt portion with heads of 128: norm, rotation and the stores are the projection's own epilogue
             key = self.position.table_key()
             cs = ctx.shared.get(key)
             if cs is None:
                 cs = ctx.shared[key] = ops.rope_table(ctx.positions, fused[0])
             q = torch.empty((T, QH, d), dtype=xn.dtype, device=xn.device)
-            if ops.gemm_qkv_heads(xn, self.w_qkv, q, cache.kv, slots, cs, self.q_norm_w, self.k_norm_w, QH, KH, g.page_size, self.eps):
+            rows, scale = (xn.rows, xn.scale()) if isinstance(xn, RowScaled) else (xn, None)
+            if ops.gemm_qkv_heads(rows, self.w_qkv, q, cache.kv, slots, cs, self.q_norm_w, self.k_norm_w, QH, KH, g.page_size, self.eps,
+                                  row_scale=scale):
                 attn = torch.empty((T, QH, d), dtype=xn.dtype, device=xn.device)
                 ops.attention(ctx, q, cache.kv, g, attn, QH, KH, d, self.window or 0, self.scale)
                 return matmul_into_residual(ctx, attn.view(T, QH * d), self.w_o, residual)
