@@ -160,15 +160,18 @@ def timeline(ops, torch, decode, B, N, layers) -> int:
     n = min(int(h[0]), cap)
     rec = h[4:4 + n * 4].view(-1, 4)
     ids, st, en, mk = (rec[:, 0] >> 32).tolist(), rec[:, 1].tolist(), rec[:, 2].tolist(), rec[:, 3].tolist()
-    # CTAs of one launch: a run (by start time) of records of one kernel whose starts lie before the run's end
+    blk = (rec[:, 0] & 0xFFFFFFFF).tolist()
+    # CTAs of one launch: a run (by start time) of records of one kernel whose starts lie before the run's end; a block
+    # index that the run has already seen begins the next launch of the same kernel (the device hands out a launch's
+    # CTAs only when all of the launch before it have been handed out)
     launches = []
     for i in sorted(range(n), key=lambda j: st[j]):
         m = mk[i] or 1 << 62
-        if launches and launches[-1]["id"] == ids[i] and st[i] < launches[-1]["end"] + 200:
+        if launches and launches[-1]["id"] == ids[i] and st[i] < launches[-1]["end"] + 200 and blk[i] not in launches[-1]["blocks"]:
             l = launches[-1]
-            l["end"] = max(l["end"], en[i]); l["n"] += 1; l["mark"] = min(l["mark"], m)
+            l["end"] = max(l["end"], en[i]); l["n"] += 1; l["mark"] = min(l["mark"], m); l["blocks"].add(blk[i])
         else:
-            launches.append(dict(id=ids[i], start=st[i], end=en[i], n=1, mark=m))
+            launches.append(dict(id=ids[i], start=st[i], end=en[i], n=1, mark=m, blocks={blk[i]}))
     if not launches:
         print("no records: the library was not built with -DRB_TIMELINE")
         return 1
