@@ -23,6 +23,9 @@
 // bounded), tensor memory is freed, and an error word in global memory tells the host.
 #define RB_UNIT 1
 #include "sm100.cuh"
+#ifndef RB_SPLIT_BARRIER
+#define RB_SPLIT_BARRIER 1     // development: 0 = every thread arrives at the cluster's second barrier only after its stores
+#endif
 #include <stdlib.h>
 
 #define TC_BM 128            // output features per CTA (MMA M)
@@ -340,6 +343,9 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
     if (csplit > 1) {
         // every CTA of the cluster reaches both barriers, whatever happened before
         cluster_sync_all();                                    // all accumulators are parked
+        // The second barrier (nobody leaves while its memory is being read) is split: a thread arrives as soon as its last
+        // loads from the peers are in its registers, stores its results, and waits only then.
+        bool arrived = false;
         if (warp >= 2 && !*abort_flag) {
             // reduce-scatter: CTA `split` sums and stores the tokens c = split, split + csplit, ...  A thread
             // takes four neighbouring features (one 16-byte load per rank over distributed shared memory),
@@ -374,6 +380,10 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
                     for (int r = 1; r < 8; ++r) {
                         va.x += pa[r].x; va.y += pa[r].y; va.z += pa[r].z; va.w += pa[r].w;
                         vb.x += pb[r].x; vb.y += pb[r].y; vb.z += pb[r].z; vb.w += pb[r].w;
+                    }
+                    if (RB_SPLIT_BARRIER && !(cb0 + 8 * csplit < BN && t0 + cb0 + 8 * csplit < T)) {           // this thread's last trip
+                        cluster_arrive_after(va.x + va.y + va.z + va.w + vb.x + vb.y + vb.z + vb.w);
+                        arrived = true;
                     }
                     const float fa = sh->row_scale[cb0], fb = two ? sh->row_scale[cb1] : 0.0f;
                     const float4 na = make_float4(oa.x + va.x * fa, oa.y + va.y * fa, oa.z + va.z * fa, oa.w + va.w * fa);
@@ -420,6 +430,16 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
                 float v[4] = {part[0].x, part[0].y, part[0].z, part[0].w};
 #pragma unroll
                 for (int r = 1; r < 8; ++r) { v[0] += part[r].x; v[1] += part[r].y; v[2] += part[r].z; v[3] += part[r].w; }
+                float u[4] = {0.f, 0.f, 0.f, 0.f};
+                if (DUAL) {
+                    u[0] = part2[0].x; u[1] = part2[0].y; u[2] = part2[0].z; u[3] = part2[0].w;
+#pragma unroll
+                    for (int r = 1; r < 8; ++r) { u[0] += part2[r].x; u[1] += part2[r].y; u[2] += part2[r].z; u[3] += part2[r].w; }
+                }
+                if (RB_SPLIT_BARRIER && !(cb + 4 * csplit < BN && t0 + cb + 4 * csplit < T)) {                 // this thread's last trip
+                    cluster_arrive_after(v[0] + v[1] + v[2] + v[3] + u[0] + u[1] + u[2] + u[3]);
+                    arrived = true;
+                }
                 const float f = sh->row_scale[cb];
 #pragma unroll
                 for (int i = 0; i < 4; ++i) v[i] *= f;
@@ -463,9 +483,6 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
                     continue;
                 }
                 if (DUAL) {
-                    float u[4] = {part2[0].x, part2[0].y, part2[0].z, part2[0].w};
-#pragma unroll
-                    for (int r = 1; r < 8; ++r) { u[0] += part2[r].x; u[1] += part2[r].y; u[2] += part2[r].z; u[3] += part2[r].w; }
 #pragma unroll
                     for (int i = 0; i < 4; ++i) v[i] = v[i] / (1.0f + expf(-v[i])) * (u[i] * f);
                 }
@@ -480,7 +497,8 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
             }
         }
         if (threadIdx.x == 64) TL(6);
-        cluster_sync_all();                                    // nobody leaves while its memory is being read
+        if (!arrived) cluster_arrive_after(0.0f);              // threads that read nothing (or gave up) arrive here
+        cluster_wait_all();                                    // nobody leaves while its memory is being read
     }
     if (threadIdx.x == 0) TL(7);
     if (warp == 1) {

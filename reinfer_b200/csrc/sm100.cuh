@@ -177,6 +177,15 @@ __device__ __forceinline__ void cluster_sync_all() {
     __syncwarp();                                       // .aligned: the whole warp must arrive together
     asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
 }
+// The two halves of a cluster barrier for a CTA that is done with its peers' shared memory before it is done with its
+// own work: a thread arrives once the values it loaded from its peers are in its registers (`consumed` depends on every
+// one of them, so the instruction cannot issue before they have come), goes on with work that touches no peer, and
+// waits before it leaves - when the wait returns, every thread of the cluster has arrived, so nobody still reads this
+// CTA's memory.  Not .aligned: threads of a warp may arrive from different places.
+__device__ __forceinline__ void cluster_arrive_after(float consumed) {
+    asm volatile("barrier.cluster.arrive.release;" ::"f"(consumed) : "memory");
+}
+__device__ __forceinline__ void cluster_wait_all() { asm volatile("barrier.cluster.wait.acquire;" ::: "memory"); }
 __device__ __forceinline__ float ld_cluster_f32(uint32_t local_addr, uint32_t rank) {
     uint32_t remote;
     float v;
