@@ -174,6 +174,51 @@ def test_storage_and_compute_dtype_may_differ(models, store, dtype):
     compare(got, truth(model_dir, seqs), TOL[dtype])
 
 
+def test_a_decode_layer_is_five_launches_and_equals_the_separate_kernels(tmp_path, monkeypatch):
+    """With heads of 128 and a width in tiles of 128 a decode step's layer runs as five launches (the norms, the
+    residual sums and the per-head work ride in the products' reductions).  The count is asserted, so that a silent
+    fall back to the separate kernels shows; and the logits equal, to rounding, those of the same step with the
+    separate kernels (the switches that bring them back), which in turn follow the plain implementation."""
+    from reinfer_b200 import ops
+    from reinfer_b200.config import Qwen3Config
+    from reinfer_b200.engine import Engine
+    from reinfer_b200.weights import write_random_model
+    layers = 3
+    raw = dict(architectures=["Qwen3ForCausalLM"], num_hidden_layers=layers, hidden_size=256, num_attention_heads=4,
+               num_key_value_heads=2, head_dim=128, intermediate_size=384, vocab_size=1003, rope_theta=1e6,
+               rms_norm_eps=1e-6, tie_word_embeddings=False, max_position_embeddings=1024)
+    d = write_random_model(str(tmp_path / "m"), Qwen3Config.from_dict(raw), seed=3, dtype=torch.bfloat16)
+    g = torch.Generator().manual_seed(8)
+    seqs = {f"r{i}": torch.randint(0, 1003, (n,), generator=g).tolist() for i, n in enumerate((70, 9, 130))}
+    names = list(seqs)
+    steps = [([(r, seqs[r][:-4], [len(seqs[r]) - 5]) for r in names], [])]
+    for k in range(4, 0, -1):
+        steps.append(([(r, [seqs[r][-k]], [0]) for r in names], names if k == 1 else []))
+    cfg, w = plain.read_model(d)
+    want = {r: plain.forward(cfg, w, t, dtype=torch.float32).double() for r, t in seqs.items()}
+
+    def run(product_norm, qkv_heads):
+        monkeypatch.setattr(ops, "PRODUCT_NORM", product_norm)
+        monkeypatch.setattr(ops, "QKV_HEADS", qkv_heads)
+        engine = Engine.from_model_dir(d, dtype="bfloat16", page_size=16, max_tokens=3 * 192, max_num_seqs=4)
+        got = run_steps(engine, steps)
+        graphs = list(engine._graphs.values())
+        assert graphs, "decode steps replay a graph"
+        return got, graphs[0].n_launches
+
+    fused, n_fused = run(True, True)
+    apart, n_apart = run(False, False)
+    # embedding, final norm, head - and the first layer's norm, which no product precedes; five a layer against eight
+    assert n_fused == 4 + 5 * layers, n_fused
+    assert n_apart == 3 + 8 * layers, n_apart
+    compare(fused, want, TOL["bfloat16"])
+    compare(apart, want, TOL["bfloat16"])
+    for key in fused:
+        a, b = fused[key].double(), apart[key].double()
+        assert (a - b).abs().max().item() <= 2e-2 * max(b.abs().max().item(), 1.0)
+    assert ops.kernel_error() == 0
+
+
 @pytest.mark.parametrize("n_requests", [11, 37])
 def test_many_requests_decode_together_with_heads_of_128(tmp_path, n_requests):
     """More requests than the mixed cuts hold, heads of 128 (the head size of the tcgen05 prefill attention and of
