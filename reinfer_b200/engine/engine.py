@@ -18,6 +18,7 @@ from __future__ import annotations
 from dataclasses import dataclass, field
 from typing import Dict, Hashable, List, Optional, Sequence
 
+import gc
 import numpy as np
 import torch
 
@@ -522,5 +523,16 @@ class _DecodeGraph:
         if engine._graph_pool is None:
             engine._graph_pool = torch.cuda.graph_pool_handle()
         self.graph = torch.cuda.CUDAGraph()
-        with torch.cuda.graph(self.graph, pool=engine._graph_pool):
-            self.logits = run()
+        # Nothing may free device or pinned memory while a stream captures (the capture is then invalid, and the next
+        # launch says so).  Python's collector can: an engine that the program dropped earlier - its graphs, their
+        # pool, its pinned buffers - is garbage with cycles and goes whenever the collector next runs.  So it runs
+        # now, and not again before the capture has ended.
+        was_enabled = gc.isenabled()
+        gc.collect()
+        gc.disable()
+        try:
+            with torch.cuda.graph(self.graph, pool=engine._graph_pool):
+                self.logits = run()
+        finally:
+            if was_enabled:
+                gc.enable()
