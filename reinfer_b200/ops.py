@@ -492,7 +492,12 @@ def decode_splits(ctas: int, tiles: int, slots: int = DECODE_SLOTS, head_dim: in
       - the larger of the two counts, plus the merge: about 2 us inside a cluster (up to 16 splits, all CTAs
         resident at once: `cluster_slots(n)` says how many CTAs that is for clusters of more than 8), else a merge
         kernel of about 3.5 us + 0.1 us per split.
-    (Whole "waves" of CTAs do not matter: a part-filled last wave just gives its CTAs more bandwidth each.)"""
+      - more CTAs than can be resident come in waves: the full waves stream at the bandwidth, but the CTAs of a
+        part-filled last wave run with few others and cannot use what the rest left free - each walks its tiles at a
+        lone CTA's pace.  (40-56 requests over 4k keys, one split: 384 CTAs on 296 places took as long as 512;
+        three splits took a tenth off the step at 40 and 48 requests, none at 56.)"""
+    if _FORCED_SPLITS:
+        return max(1, min(_FORCED_SPLITS, tiles))
     key = None
     if cluster_slots is None:
         key = (ctas, tiles, slots, head_dim, total_tiles, ATTN_CLUSTER_MERGE)
@@ -518,7 +523,14 @@ def decode_splits(ctas: int, tiles: int, slots: int = DECODE_SLOTS, head_dim: in
             merge = 2.0
         else:
             merge = 3.5 + 0.1 * n
-        cost = max(t_bw, t_lat) + merge
+        t_wave = 0.0
+        if ctas * n > slots:
+            full, rest = divmod(ctas * n, slots)
+            fill_drain = 1.0 + 2.7 / per_avg
+            t_wave = full * per_avg * max(tile_us, slots * tile_bw_us) * fill_drain
+            if rest:
+                t_wave += per_avg * max(tile_us, rest * tile_bw_us) * fill_drain
+        cost = max(t_bw, t_lat, t_wave) + merge
         if best_cost is None or cost < best_cost - 1e-9:
             best, best_cost = n, cost
     if key is not None:
@@ -529,6 +541,8 @@ def decode_splits(ctas: int, tiles: int, slots: int = DECODE_SLOTS, head_dim: in
 
 
 _splits_memo: dict = {}
+# REINFER_B200_ATTN_SPLITS=n: every decode attention launch splits its keys n ways (a development switch, to measure the model against)
+_FORCED_SPLITS = int(os.environ.get("REINFER_B200_ATTN_SPLITS", "0") or 0)
 
 
 def attention(ctx, q: torch.Tensor, cache: torch.Tensor, group, out: torch.Tensor, QH: int, KH: int, d: int,

@@ -59,6 +59,13 @@ def test_decode_splits_model():
     # many (request, kv head) pairs: one CTA each streams at the memory bandwidth, splitting only adds fill and drain
     assert decode_splits(64 * 8, 64) == 1
     assert decode_splits(32 * 8, 64) == 1
+    # a few more pairs than the device holds at once: unsplit, the CTAs of the part-filled last wave would walk their
+    # tiles alone; three splits make the waves short (measured at 40 and 48 requests), but not where the last wave
+    # is well filled anyway (56, 64)
+    assert decode_splits(40 * 8, 64) in (3, 4)             # measured: 3 and 4 alike, a tenth faster than 1
+    assert decode_splits(48 * 8, 64) in (2, 3)             # measured: 3, then 2; 4 no better than 1
+    assert decode_splits(56 * 8, 64) == 1
+    assert decode_splits(37 * 8, 64) == 1                  # exactly the places there are
     # few pairs: splits until enough CTAs stream; they stay inside a cluster while all are resident at once
     assert decode_splits(16 * 8, 64) == 2
     assert decode_splits(8 * 8, 64) == 4
