@@ -109,7 +109,7 @@ class Engine:
         self.on_admit = None
         self._epilogue = None
         self.steps_run = 0
-        # decode-only steps replay a captured CUDA graph per (batch bucket, block-table width).  Padding rows
+        # decode-only steps replay a captured CUDA graph per (batch bucket, block-table width, the mixers' plan).  Padding rows
         # point at a slot that belongs to nobody.  A mixer with state takes part only if it says that its
         # single-token step reads the batch from the device tables alone (`steps_from_device_tables`): what
         # it read from the host mirrors would be frozen into the capture.
@@ -118,6 +118,9 @@ class Engine:
         self._graphs: Dict[tuple, "_DecodeGraph"] = {}
         self._graph_pool = None
         self.graph_replays = 0
+        # the first mixer that can say what a decode step fixes beyond its shapes (Mixer.decode_plan); None: nobody can
+        self._planner = next((l.mixer.decode_plan for l in self.model.layers
+                              if l.mixer is not None and callable(getattr(l.mixer, "decode_plan", None))), None)
 
     @property
     def epilogue(self):
@@ -230,7 +233,14 @@ class Engine:
         total = sum(-(-((self.cache.length(e.request_id) if e.request_id in self.cache else 0) + 1) // 64) for e in entries)
         widest = max(1, width * self.page_size // 64)
         fill = min(FILL_STEPS, max(1, (2 * FILL_STEPS * total + B * widest) // (2 * B * widest)))
-        return bucket, width, fill
+        # what the mixers fix beyond the shapes (the attention: its key splits) is asked for the requests there are, not
+        # for the rows of their bucket - 18 requests want another split than 24 - and for their keys as they are, to
+        # an eighth of the widest table; batches with the same answer share a captured step
+        plan = None
+        if self._planner is not None:
+            tiles = max(B, B * widest * fill // FILL_STEPS)
+            plan = self._planner(B, widest, tiles)
+        return bucket, width, plan if plan is not None else fill
 
     def _step_graph(self, entries: Sequence[StepEntry], logits: bool = True) -> Optional[torch.Tensor]:
         """A step of single tokens only: fill the graph's static tables and replay it."""
@@ -481,8 +491,8 @@ class Engine:
 
 
 MAX_GRAPH_BATCH = 256
-MAX_GRAPHS = 24
-FILL_STEPS = 8                          # a captured decode step is made for block tables filled to so many eighths             # captured decode steps kept at a time (one per batch bucket and block-table width in use)
+MAX_GRAPHS = 24                         # captured decode steps kept at a time (one per batch bucket, block-table width and plan in use)
+FILL_STEPS = 8                          # the keys in a batch's block tables are counted to so many eighths of the widest table
 
 
 class _DecodeGraph:
@@ -490,7 +500,7 @@ class _DecodeGraph:
     Its tables live in `meta` (a static int32 block the engine refills before every replay); its
     logits [batch, vocab] in `logits`."""
 
-    def __init__(self, engine: "Engine", batch: int, width: int, fill: int = FILL_STEPS):
+    def __init__(self, engine: "Engine", batch: int, width: int, plan=None):
         n_groups = len(engine.cache.groups)
         off, total = Engine._layout(batch, batch, batch, [width] * n_groups)
         host = np.zeros(total, dtype=np.int32)
@@ -507,7 +517,11 @@ class _DecodeGraph:
         ctx = engine._context(self.meta, off, batch, batch, batch, [width] * n_groups, list(range(batch + 1)),
                               [0] * batch, [inert] * batch, 1, width * engine.page_size)
         widest = max(1, width * engine.page_size // 64)
-        ctx.decode_kv_tiles = (max(batch, batch * widest * fill // FILL_STEPS), widest)     # block tables filled to `fill` eighths
+        if engine._planner is not None:
+            ctx.decode_plan = plan                          # the third part of the key is the mixers' plan
+        else:
+            fill = plan if plan is not None else FILL_STEPS # without a planner it is the tables' fill in eighths
+            ctx.decode_kv_tiles = (max(batch, batch * widest * fill // FILL_STEPS), widest)
         o, n = off["want_rows"]
         want = self.meta[o:o + n]
         def run():

@@ -396,6 +396,10 @@ def _next_range(t: Optional[torch.Tensor], marker: int = 0):
 
 
 DECODE_SLOTS = 296                          # CTAs of the decode attention that are resident at once (two per SM)
+# Clusters merge their splits themselves only while they fill at most this share of the places the device reports: a
+# cluster needs its places on one GPC at once, and near the limit clusters wait for one another (measured: 13 splits
+# of 16 pairs on 208 of 221 places, 7 splits of 40 pairs on 280 of 296, each 4 % slower a step than a neighbouring count)
+CLUSTER_FILL = 0.9
 MAX_CLUSTER_SPLITS = 16                     # splits that can merge inside one cluster (more than 8: not portable, asked of the device)
 _cluster_slots: dict = {}
 
@@ -419,7 +423,7 @@ def fa_decode_tma(q, cache, block_table, cu_q, kv_len, out, first_entry: int, n_
     that wait for a free place on one GPC were measured slower there)."""
     part_o = part_lse = None
     ctas = n_entries * KH * (QH // KH // fa_group_chunk(QH // KH)) * n_splits
-    in_kernel = ATTN_CLUSTER_MERGE and 2 <= n_splits <= min(MAX_CLUSTER_SPLITS, d) and ctas <= decode_cluster_slots(d, n_splits)
+    in_kernel = ATTN_CLUSTER_MERGE and 2 <= n_splits <= min(MAX_CLUSTER_SPLITS, d) and ctas <= CLUSTER_FILL * decode_cluster_slots(d, n_splits)
     if n_splits > 1 and not in_kernel:
         part_o = torch.empty(n_entries * QH * n_splits * d, dtype=torch.float32, device=q.device)
         part_lse = torch.empty(n_entries * QH * n_splits, dtype=torch.float32, device=q.device)
@@ -491,7 +495,8 @@ def decode_splits(ctas: int, tiles: int, slots: int = DECODE_SLOTS, head_dim: in
         CTAs then come in several waves)
       - the larger of the two counts, plus the merge: about 2 us inside a cluster (up to 16 splits, all CTAs
         resident at once: `cluster_slots(n)` says how many CTAs that is for clusters of more than 8), else a merge
-        kernel of about 3.5 us + 0.1 us per split.
+        kernel of about 6 us + 0.1 us per split (a launch more in the step's chain; at 9 and 12 requests the count
+        that still merges in its clusters beat the next one, which does not, by 2-3.5 us a layer).
       - more CTAs than can be resident come in waves: the full waves stream at the bandwidth, but the CTAs of a
         part-filled last wave run with few others and cannot use what the rest left free - each walks its tiles at a
         lone CTA's pace.  (40-56 requests over 4k keys, one split: 384 CTAs on 296 places took as long as 512;
@@ -519,10 +524,11 @@ def decode_splits(ctas: int, tiles: int, slots: int = DECODE_SLOTS, head_dim: in
         t_lat = max(0, per - ahead) * tile_us + 5.0
         if n == 1:
             merge = 0.0
-        elif n <= min(MAX_CLUSTER_SPLITS, head_dim) and ATTN_CLUSTER_MERGE and ctas * n <= (slots if n <= 8 else min(slots, cluster_slots(n))):
+        elif n <= min(MAX_CLUSTER_SPLITS, head_dim) and ATTN_CLUSTER_MERGE and \
+                ctas * n <= CLUSTER_FILL * (slots if n <= 8 else min(slots, cluster_slots(n))):
             merge = 2.0
         else:
-            merge = 3.5 + 0.1 * n
+            merge = 6.0 + 0.1 * n
         t_wave = 0.0
         if ctas * n > slots:
             full, rest = divmod(ctas * n, slots)
@@ -575,11 +581,13 @@ def attention(ctx, q: torch.Tensor, cache: torch.Tensor, group, out: torch.Tenso
     gc = fa_group_chunk(QH // KH)
     joined = None
     if n_dec:
-        ctas = n_dec * KH * (QH // KH // gc)
         pairs = KH * (QH // KH // gc)
+        ctas = n_dec * pairs
         tiles = ctx.decode_kv_tiles[1] if ctx.decode_kv_tiles else -(-ctx.max_kv_len // 64)
         total = ctx.decode_kv_tiles[0] * pairs if ctx.decode_kv_tiles else None
-        n_splits = decode_splits(ctas, tiles, head_dim=d, total_tiles=total)
+        plan = getattr(ctx, "decode_plan", None)              # a captured step: the split it was made for
+        n_splits = max(1, min(int(plan), tiles)) if isinstance(plan, int) and not _FORCED_SPLITS else \
+            decode_splits(ctas, tiles, head_dim=d, total_tiles=total)
         decode = fa_decode_tma if (tma_pages(group.page_size) and USE_TMA_ATTENTION) else fa_decode
         if E > n_dec and MIXED_OVERLAP and _profiler is None and not torch.cuda.is_current_stream_capturing():
             # A step with prompt portions beside decoding requests: the two attention kernels read the same inputs

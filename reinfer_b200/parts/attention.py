@@ -73,6 +73,13 @@ class Attention(Mixer):
         """The first product (q, k, v) can apply the factor of rows that the norm left without it."""
         return takes_row_scaled(self.w_qkv)
 
+    def decode_plan(self, live: int, largest_tiles: int, total_tiles: int):
+        """What a decode step of `live` requests, whose keys fill `total_tiles` 64-key tiles (the longest
+        `largest_tiles`), fixes beyond its shapes: in how many parts the attention splits a request's keys.  A captured
+        step is made for one plan and reused by every batch that asks for the same (the engine keys its graphs by it)."""
+        pairs = self.KH * ((self.QH // self.KH) // ops.fa_group_chunk(self.QH // self.KH))
+        return ops.decode_splits(max(1, live) * pairs, max(1, largest_tiles), head_dim=self.d, total_tiles=max(1, total_tiles) * pairs)
+
     # ---- the step ------------------------------------------------------------
     def forward(self, ctx, xn, residual, cache) -> None:
         T, QH, KH, d = xn.shape[0], self.QH, self.KH, self.d

@@ -126,6 +126,10 @@ class Mixer(Part):
     # that belongs to no request.  Otherwise a model with such a mixer runs every step eagerly.
     steps_from_device_tables = False
 
+    # Optional: decode_plan(live, largest_tiles, total_tiles) -> hashable.  What a decode step fixes beyond its shapes
+    # (the attention: its key splits) for that many requests and 64-key tiles.  The engine asks the first mixer that
+    # has it, keys its captured steps by the answer and hands it back as ctx.decode_plan.
+
     def cache_spec(self) -> Optional[PagedKVSpec]:
         return None
 

@@ -53,6 +53,7 @@ class StepContext:
     max_q_len: int = 0
     max_kv_len: int = 0
     decode_kv_tiles: Optional[Tuple[int, int]] = None     # (sum, largest) of the decode entries' 64-key tiles; None: all as max_kv_len
+    decode_plan: Optional[object] = None                  # what the mixer's decode_plan() answered for this step (a captured step is made for one)
     layer_caches: Dict[str, LayerCache] = field(default_factory=dict)
     shared: Dict[object, torch.Tensor] = field(default_factory=dict)   # what one layer computed for all (per step)
     defer_residual: bool = False       # parts may return what is to be added to the residual; the next norm adds it

@@ -71,9 +71,9 @@ def test_decode_splits_model():
     assert decode_splits(8 * 8, 64) == 4
     assert 2 <= decode_splits(4 * 8, 64) <= 8
     # one request: as many splits as the largest cluster holds; where the device allows only portable clusters,
-    # more splits than a cluster holds, merged by a kernel
+    # the largest portable cluster or more splits than that, merged by a kernel
     assert decode_splits(8, 64) == 16
-    assert portable_only(8, 64) > 8 and portable_only(8, 64) != 16
+    assert portable_only(8, 64) >= 8 and portable_only(8, 64) != 16
     # never more splits than tiles, never fewer than one
     for ctas in (1, 8, 64, 512, 4096):
         for tiles in (1, 2, 3, 16, 64, 512, 2048):
