@@ -198,3 +198,81 @@ def test_a_failed_step_ends_its_requests_and_stops_the_loop():
     assert sorted(released) == ["a", "b"] and not s.has_work()
     assert cm.free_pages() == cm.total_pages() and cm.free_slots() == 4
     cm.check()
+
+
+# ---------------------------------------------------------------- a block's hand-overs, with stand-in parts (no device)
+
+def test_prenorm_block_hands_sums_and_prepared_rows_on():
+    """What the pre-norm arrangement passes between its parts, seen with stand-ins on the CPU: a part's return value
+    (nothing, a sum still to be added, or rows that a product prepared for the norm that reads the residual next)
+    reaches exactly that norm; the norm that a part may prepare for is named only while that part runs, and only if
+    norm and reader both know the form; across blocks the model's loop names the next block's first norm."""
+    import torch
+    from reinfer_b200.parts.base import PreparedRows, RowScaled
+    from reinfer_b200.parts.block import PreNormBlock
+
+    log = []
+
+    class Ctx:
+        norm_ahead = None
+        norm_after_block = None
+
+    class NormStandIn:
+        adds_partial_sums = True
+
+        def __init__(self, name, scaled):
+            self.name, self.leaves_row_scale = name, scaled
+            if scaled:
+                self.prepared_by = lambda ctx, a, w, residual: PreparedRows(self, torch.ones(2, 4), torch.ones(2, 1))
+
+        def forward(self, ctx, x, out=None, delta=None, row_idx=None, scaled_ok=False):
+            log.append((self.name, type(delta).__name__, scaled_ok))
+            if isinstance(delta, PreparedRows):
+                assert delta.norm is self and scaled_ok
+                return RowScaled(delta.rows, delta.sumsq, 4, 1e-6)
+            return x + (0 if delta is None else delta)
+
+    class PartStandIn:
+        def __init__(self, name, takes, result):
+            self.name, self.takes_row_scaled, self.result = name, takes, result
+
+        def forward(self, ctx, xn, residual, cache=None):
+            ahead = ctx.norm_ahead
+            log.append((self.name, type(xn).__name__, None if ahead is None else ahead.name))
+            if self.result == "prepared" and ahead is not None:
+                return ahead.prepared_by(ctx, None, None, residual)
+            return torch.full((2, 4), 0.5) if self.result == "sum" else None
+
+    x = torch.zeros(2, 4)
+    # both sides know the form: the mixer is told of the ffn's norm, prepares its rows, the ffn gets them as RowScaled;
+    # the ffn is told of the norm after the block (here: the next block's first norm) and hands its rows out
+    n1, n2, nxt = NormStandIn("mixer_norm", True), NormStandIn("ffn_norm", True), NormStandIn("next", True)
+    block = PreNormBlock({"mixer_norm": n1, "mixer": PartStandIn("mixer", True, "prepared"),
+                          "ffn_norm": n2, "ffn": PartStandIn("ffn", True, "prepared")})
+    ctx = Ctx()
+    ctx.norm_after_block = nxt
+    out = block.forward(ctx, x, None, None)
+    assert isinstance(out, PreparedRows) and out.norm is nxt
+    assert ctx.norm_ahead is None                                   # named only while the part runs
+    assert log == [("mixer_norm", "NoneType", True), ("mixer", "Tensor", "ffn_norm"),
+                   ("ffn_norm", "PreparedRows", True), ("ffn", "RowScaled", "next")]
+    assert block.entry_norm() is n1
+    # a reader that does not take rows without their factor: nobody is named, sums go the plain way
+    log.clear()
+    block = PreNormBlock({"mixer_norm": n1, "mixer": PartStandIn("mixer", False, "sum"),
+                          "ffn_norm": n2, "ffn": PartStandIn("ffn", False, None)})
+    ctx = Ctx()
+    assert block.forward(ctx, x, None, torch.ones(2, 4)) is None
+    assert log == [("mixer_norm", "Tensor", False), ("mixer", "Tensor", None),
+                   ("ffn_norm", "Tensor", False), ("ffn", "Tensor", None)]
+    assert block.entry_norm() is None
+    # a norm that cannot have its rows prepared is never named, whatever its reader takes
+    plain_norm = NormStandIn("plain", False)
+    block = PreNormBlock({"mixer_norm": plain_norm, "mixer": PartStandIn("mixer", True, "prepared"),
+                          "ffn_norm": plain_norm, "ffn": PartStandIn("ffn", True, "prepared")})
+    log.clear()
+    ctx = Ctx()
+    ctx.norm_after_block = nxt
+    out = block.forward(ctx, x, None, None)
+    assert [e[2] for e in log if e[0] == "mixer"] == [None]          # the mixer was told of no norm
+    assert isinstance(out, PreparedRows)                            # the ffn still prepares for the next block's norm
