@@ -533,9 +533,12 @@ def decode_splits(ctas: int, tiles: int, slots: int = DECODE_SLOTS, head_dim: in
         if ctas * n > slots:
             full, rest = divmod(ctas * n, slots)
             fill_drain = 1.0 + 2.7 / per_avg
-            t_wave = full * per_avg * max(tile_us, slots * tile_bw_us) * fill_drain
+            wave = per_avg * max(tile_us, slots * tile_bw_us) * fill_drain
+            t_wave = full * wave
             if rest:
-                t_wave += per_avg * max(tile_us, rest * tile_bw_us) * fill_drain
+                # (the CTAs of a wave end within about a seventh of its length of one another, and the next begin as
+                # they do: that much of the last wave runs beside the one before it)
+                t_wave += per_avg * max(tile_us, rest * tile_bw_us) * fill_drain - 0.15 * wave
         cost = max(t_bw, t_lat, t_wave) + merge
         if best_cost is None or cost < best_cost - 1e-9:
             best, best_cost = n, cost
